@@ -1,0 +1,316 @@
+"""TEST INFRASTRUCTURE ONLY: numpy front-ends of the CPU oracle.
+
+Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU-baseline legs of ``bench.py`` may import
+this package, and only as the checker.  The product (``binarybrain_b200``) never does.
+
+``port``  : oracle/lut6_oracle.c, the plain-C restatement of the reference's CPU arithmetic.
+``ref``   : oracle/_ref/libbbref.so, the unmodified reference headers behind oracle/ref_driver.cpp
+            (present where it was built from a reference checkout; ``ref.available()`` tells).
+
+Array conventions: fp32 frames ``[node, frame]`` C-contiguous; bit frames ``[node, words]`` uint32
+with 32 frames per word, LSB first; wiring ``[out, 6]`` int32; ``W`` ``[out, 64]`` float32; binary
+tables ``[out, 2]`` int32.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_PORT_SO = os.path.join(_HERE, "liblut6_oracle.so")
+_REF_SO = os.path.join(_HERE, "_ref", "libbbref.so")
+
+_f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+_i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
+_u32p = np.ctypeslib.ndpointer(np.uint32, flags="C_CONTIGUOUS")
+
+
+def build():
+    """Compile the oracle (and oracle/_ref when a reference checkout is present)."""
+    subprocess.check_call(["make", "-s", "-C", _HERE, "all"])
+
+
+def _vp(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def pack_bits(bits):
+    """[node, frame] of {0,1} -> [node, ceil(frame/32)] uint32, frame f at bit f&31 of word f>>5."""
+    bits = np.asarray(bits).astype(np.uint8)
+    n, f = bits.shape
+    words = (f + 31) // 32
+    pad = np.zeros((n, words * 32), np.uint8)
+    pad[:, :f] = bits
+    return np.packbits(pad.reshape(n, words, 32), axis=2, bitorder="little").view(np.uint32).reshape(n, words).copy()
+
+
+def unpack_bits(words, frames):
+    words = np.ascontiguousarray(words, np.uint32)
+    n = words.shape[0]
+    b = np.unpackbits(words.view(np.uint8).reshape(n, -1), axis=1, bitorder="little")
+    return b[:, :frames].copy()
+
+
+class _Port:
+    """oracle/lut6_oracle.c"""
+
+    def __init__(self):
+        self._lib = None
+
+    @property
+    def lib(self):
+        if self._lib is None:
+            if not os.path.exists(_PORT_SO):
+                build()
+            self._lib = C.CDLL(_PORT_SO)
+        return self._lib
+
+    # -- StochasticLut6 ---------------------------------------------------------------------
+    def sl6_forward(self, x, idx, W, frames=None, binary=False, lut_binarize=False, bias=0.25, want_bits=False):
+        bit_in = x.dtype == np.uint32
+        x = np.ascontiguousarray(x)
+        F = frames if frames is not None else x.shape[1]
+        O = idx.shape[0]
+        y = np.zeros((O, F), np.float32)
+        yb = np.zeros((O, (F + 31) // 32), np.uint32) if want_bits else None
+        self.lib.oracle_sl6_forward(
+            C.c_int(bit_in), _vp(x), C.c_size_t(x.shape[1]), _vp(y), C.c_size_t(F), _vp(yb), C.c_size_t((F + 31) // 32),
+            _vp(np.ascontiguousarray(idx, np.int32)), _vp(np.ascontiguousarray(W, np.float32)),
+            C.c_int(O), C.c_int(F), C.c_int(binary), C.c_int(lut_binarize), C.c_float(bias))
+        return (y, yb) if want_bits else y
+
+    def sl6_backward(self, x, dy, idx, W, n_in, dW=None, frames=None, binary=False, lut_binarize=False, bias=0.25):
+        bit_in = x.dtype == np.uint32
+        x = np.ascontiguousarray(x)
+        dy = np.ascontiguousarray(dy, np.float32)
+        O, F = dy.shape
+        dx = np.zeros((n_in, F), np.float32)
+        dW = np.zeros((O, 64), np.float32) if dW is None else np.ascontiguousarray(dW, np.float32).copy()
+        self.lib.oracle_sl6_backward(
+            C.c_int(bit_in), _vp(x), C.c_size_t(x.shape[1]), _vp(dy), C.c_size_t(F), _vp(dx), C.c_size_t(F),
+            _vp(np.ascontiguousarray(idx, np.int32)), _vp(np.ascontiguousarray(W, np.float32)), _vp(dW),
+            C.c_int(n_in), C.c_int(O), C.c_int(F), C.c_int(binary), C.c_int(lut_binarize), C.c_float(bias))
+        return dx, dW
+
+    # -- DifferentiableLut6 -----------------------------------------------------------------
+    def dl6_forward_train(self, x, idx, W, running_mean, running_var, frames=None, gamma=0.3, beta=0.5, momentum=0.9,
+                          bias=0.25, lut_binarize=False, binary=True):
+        bit_in = x.dtype == np.uint32
+        x = np.ascontiguousarray(x)
+        F = frames if frames is not None else x.shape[1]
+        O = idx.shape[0]
+        y = np.zeros((O, F), np.float32)
+        ypre = np.zeros((O, F), np.float32)
+        yb = np.zeros((O, (F + 31) // 32), np.uint32)
+        mean = np.zeros(O, np.float32)
+        rstd = np.zeros(O, np.float32)
+        rm = np.ascontiguousarray(running_mean, np.float32).copy()
+        rv = np.ascontiguousarray(running_var, np.float32).copy()
+        self.lib.oracle_dl6_forward_train(
+            C.c_int(bit_in), _vp(x), C.c_size_t(x.shape[1]), _vp(y), C.c_size_t(F), _vp(yb), C.c_size_t((F + 31) // 32), _vp(ypre),
+            _vp(np.ascontiguousarray(idx, np.int32)), _vp(np.ascontiguousarray(W, np.float32)),
+            _vp(mean), _vp(rstd), _vp(rm), _vp(rv),
+            C.c_float(gamma), C.c_float(beta), C.c_float(momentum), C.c_float(bias),
+            C.c_int(O), C.c_int(F), C.c_int(lut_binarize), C.c_int(1 if bit_in else binary))
+        return dict(y=y, y_bits=yb, y_pre=ypre, mean=mean, rstd=rstd, running_mean=rm, running_var=rv)
+
+    def dl6_forward_infer(self, x, idx, W, running_mean, running_var, frames=None, gamma=0.3, beta=0.5, bias=0.25,
+                          lut_binarize=False, binary=True):
+        bit_in = x.dtype == np.uint32
+        x = np.ascontiguousarray(x)
+        F = frames if frames is not None else x.shape[1]
+        O = idx.shape[0]
+        y = np.zeros((O, F), np.float32)
+        ypre = np.zeros((O, F), np.float32)
+        yb = np.zeros((O, (F + 31) // 32), np.uint32)
+        self.lib.oracle_dl6_forward_infer(
+            C.c_int(bit_in), _vp(x), C.c_size_t(x.shape[1]), _vp(y), C.c_size_t(F), _vp(yb), C.c_size_t((F + 31) // 32), _vp(ypre),
+            _vp(np.ascontiguousarray(idx, np.int32)), _vp(np.ascontiguousarray(W, np.float32)),
+            _vp(np.ascontiguousarray(running_mean, np.float32)), _vp(np.ascontiguousarray(running_var, np.float32)),
+            C.c_float(gamma), C.c_float(beta), C.c_float(bias), C.c_int(O), C.c_int(F), C.c_int(lut_binarize),
+            C.c_int(1 if bit_in else binary))
+        return dict(y=y, y_bits=yb, y_pre=ypre)
+
+    def dl6_backward(self, x, dy, idx, W, mean, rstd, n_in, dW=None, frames=None, gamma=0.3, beta=0.5, bias=0.25,
+                     lut_binarize=False, binary=True):
+        bit_in = x.dtype == np.uint32
+        x = np.ascontiguousarray(x)
+        dy = np.ascontiguousarray(dy, np.float32)
+        O, F = dy.shape
+        dx = np.zeros((n_in, F), np.float32)
+        dW = np.zeros((O, 64), np.float32) if dW is None else np.ascontiguousarray(dW, np.float32).copy()
+        self.lib.oracle_dl6_backward(
+            C.c_int(bit_in), _vp(x), C.c_size_t(x.shape[1]), _vp(dy), C.c_size_t(F), _vp(dx), C.c_size_t(F),
+            _vp(np.ascontiguousarray(idx, np.int32)), _vp(np.ascontiguousarray(W, np.float32)), _vp(dW),
+            _vp(np.ascontiguousarray(mean, np.float32)), _vp(np.ascontiguousarray(rstd, np.float32)),
+            C.c_float(gamma), C.c_float(beta), C.c_float(bias), C.c_int(n_in), C.c_int(O), C.c_int(F),
+            C.c_int(lut_binarize), C.c_int(1 if bit_in else binary))
+        return dx, dW
+
+    # -- StochasticBatchNormalization ---------------------------------------------------------
+    def sbn_forward_train(self, x, running_mean, running_var, gamma=0.2, beta=0.5, momentum=0.9):
+        x = np.ascontiguousarray(x, np.float32)
+        O, F = x.shape
+        y = np.zeros_like(x)
+        mean = np.zeros(O, np.float32)
+        rstd = np.zeros(O, np.float32)
+        rm = np.ascontiguousarray(running_mean, np.float32).copy()
+        rv = np.ascontiguousarray(running_var, np.float32).copy()
+        self.lib.oracle_sbn_forward_train(_vp(x), _vp(y), C.c_size_t(F), _vp(mean), _vp(rstd), _vp(rm), _vp(rv),
+                                          C.c_float(gamma), C.c_float(beta), C.c_float(momentum), C.c_int(O), C.c_int(F))
+        return dict(y=y, mean=mean, rstd=rstd, running_mean=rm, running_var=rv)
+
+    def sbn_reforward(self, x, mean, rstd, gamma=0.2, beta=0.5):
+        x = np.ascontiguousarray(x, np.float32)
+        O, F = x.shape
+        y = np.zeros_like(x)
+        self.lib.oracle_sbn_reforward(_vp(x), _vp(y), C.c_size_t(F), _vp(np.ascontiguousarray(mean, np.float32)),
+                                      _vp(np.ascontiguousarray(rstd, np.float32)), C.c_float(gamma), C.c_float(beta), C.c_int(O), C.c_int(F))
+        return y
+
+    def sbn_forward_infer(self, x, mean, var, gamma=0.2, beta=0.5):
+        x = np.ascontiguousarray(x, np.float32)
+        O, F = x.shape
+        y = np.zeros_like(x)
+        self.lib.oracle_sbn_forward_infer(_vp(x), _vp(y), C.c_size_t(F), _vp(np.ascontiguousarray(mean, np.float32)),
+                                          _vp(np.ascontiguousarray(var, np.float32)), C.c_float(gamma), C.c_float(beta), C.c_int(O), C.c_int(F))
+        return y
+
+    def sbn_backward(self, x, dy, mean, rstd, gamma=0.2):
+        x = np.ascontiguousarray(x, np.float32)
+        dy = np.ascontiguousarray(dy, np.float32)
+        O, F = x.shape
+        dx = np.zeros_like(x)
+        self.lib.oracle_sbn_backward(_vp(x), _vp(dy), _vp(dx), C.c_size_t(F), _vp(np.ascontiguousarray(mean, np.float32)),
+                                     _vp(np.ascontiguousarray(rstd, np.float32)), C.c_float(gamma), C.c_int(O), C.c_int(F))
+        return dx
+
+    # -- BinaryLut6 ---------------------------------------------------------------------------
+    def binary_lut6_forward(self, x_words, idx, table, frames):
+        x_words = np.ascontiguousarray(x_words, np.uint32)
+        O = idx.shape[0]
+        y = np.zeros((O, x_words.shape[1]), np.uint32)
+        self.lib.oracle_binary_lut6_forward(_vp(x_words), _vp(y), C.c_size_t(x_words.shape[1]),
+                                            _vp(np.ascontiguousarray(idx, np.int32)), _vp(np.ascontiguousarray(table, np.int32)),
+                                            C.c_int(O), C.c_int(frames))
+        return y
+
+    # -- Adam ---------------------------------------------------------------------------------
+    def adam_update(self, p, g, m, v, state, lr=0.001, beta1=0.9, beta2=0.999):
+        """In place on float32 arrays p, g, m, v; ``state`` is a 2-element float32 array [b1^t, b2^t] starting at 1."""
+        self.lib.oracle_adam_update(_vp(p), _vp(g), _vp(m), _vp(v), C.c_size_t(p.size), C.c_float(lr), C.c_float(beta1),
+                                    C.c_float(beta2), C.c_void_p(state.ctypes.data), C.c_void_p(state.ctypes.data + 4))
+
+
+class _Ref:
+    """oracle/_ref/libbbref.so: the unmodified reference CPU path."""
+
+    def __init__(self):
+        self._lib = None
+
+    def available(self):
+        return os.path.exists(_REF_SO)
+
+    @property
+    def lib(self):
+        if self._lib is None:
+            self._lib = C.CDLL(_REF_SO)
+        return self._lib
+
+    def num_threads(self):
+        return int(self.lib.bbref_num_threads())
+
+    def stochastic_lut6(self, x, idx, W, frames=None, binary=False, lut_binarize=False, host_simd=True, dy=None, dW=None):
+        bit_in = x.dtype == np.uint32
+        x = np.ascontiguousarray(x)
+        F = frames if frames is not None else x.shape[1]
+        O, I = idx.shape[0], x.shape[0]
+        y = np.zeros((O, F), np.float32)
+        t = np.zeros(2, np.float64)
+        dx = dWo = None
+        if dy is not None:
+            dy = np.ascontiguousarray(dy, np.float32)
+            dx = np.zeros((I, F), np.float32)
+            dWo = np.zeros((O, 64), np.float32) if dW is None else np.ascontiguousarray(dW, np.float32).copy()
+        self.lib.bbref_stochastic_lut6(
+            C.c_int(bit_in), _vp(x), C.c_int(I), C.c_int(O), C.c_int(F), _vp(np.ascontiguousarray(idx, np.int32)),
+            _vp(np.ascontiguousarray(W, np.float32)), C.c_int(binary), C.c_int(lut_binarize), C.c_int(host_simd),
+            _vp(y), _vp(dy), _vp(dx), _vp(dWo), _vp(t))
+        return dict(y=y, dx=dx, dW=dWo, t_fwd=t[0], t_bwd=t[1])
+
+    def differentiable_lut6(self, x, idx, W, frames=None, batch_norm=True, binary=True, lut_binarize=False, gamma=0.3, beta=0.5,
+                            momentum=0.9, running_mean=None, running_var=None, train=True, dy=None, dW=None):
+        bit_io = x.dtype == np.uint32
+        x = np.ascontiguousarray(x)
+        F = frames if frames is not None else x.shape[1]
+        O, I = idx.shape[0], x.shape[0]
+        y = np.zeros((O, (F + 31) // 32), np.uint32) if bit_io else np.zeros((O, F), np.float32)
+        mean = np.zeros(O, np.float32)
+        rstd = np.zeros(O, np.float32)
+        rm = np.zeros(O, np.float32) if running_mean is None else np.ascontiguousarray(running_mean, np.float32).copy()
+        rv = np.ones(O, np.float32) if running_var is None else np.ascontiguousarray(running_var, np.float32).copy()
+        t = np.zeros(2, np.float64)
+        dx = dWo = None
+        if dy is not None:
+            dy = np.ascontiguousarray(dy, np.float32)
+            dx = np.zeros((I, F), np.float32)
+            dWo = np.zeros((O, 64), np.float32) if dW is None else np.ascontiguousarray(dW, np.float32).copy()
+        self.lib.bbref_differentiable_lut6(
+            C.c_int(bit_io), _vp(x), C.c_int(I), C.c_int(O), C.c_int(F), _vp(np.ascontiguousarray(idx, np.int32)),
+            _vp(np.ascontiguousarray(W, np.float32)), C.c_int(batch_norm), C.c_int(binary), C.c_int(lut_binarize),
+            C.c_float(gamma), C.c_float(beta), C.c_float(momentum), _vp(rm), _vp(rv), C.c_int(train),
+            _vp(y), _vp(mean), _vp(rstd), _vp(dy), _vp(dx), _vp(dWo), _vp(t))
+        return dict(y=y, mean=mean, rstd=rstd, running_mean=rm, running_var=rv, dx=dx, dW=dWo, t_fwd=t[0], t_bwd=t[1])
+
+    def binary_lut6(self, x_words, idx, table, frames, host_simd=True):
+        x_words = np.ascontiguousarray(x_words, np.uint32)
+        assert x_words.shape[1] == (frames + 31) // 32
+        O, I = idx.shape[0], x_words.shape[0]
+        y = np.zeros((O, x_words.shape[1]), np.uint32)
+        t = np.zeros(2, np.float64)
+        self.lib.bbref_binary_lut6(_vp(x_words), C.c_int(I), C.c_int(O), C.c_int(frames), _vp(np.ascontiguousarray(idx, np.int32)),
+                                   _vp(np.ascontiguousarray(table, np.int32)), C.c_int(host_simd), _vp(y), _vp(t))
+        return dict(y=y, t_fwd=t[0])
+
+    def stochastic_bn(self, x, mode=0, gamma=0.2, beta=0.5, momentum=0.9, running_mean=None, running_var=None, dy=None):
+        x = np.ascontiguousarray(x, np.float32)
+        O, F = x.shape
+        y = np.zeros_like(x)
+        mean = np.zeros(O, np.float32)
+        rstd = np.zeros(O, np.float32)
+        rm = np.zeros(O, np.float32) if running_mean is None else np.ascontiguousarray(running_mean, np.float32).copy()
+        rv = np.ones(O, np.float32) if running_var is None else np.ascontiguousarray(running_var, np.float32).copy()
+        dx = None
+        if dy is not None:
+            dy = np.ascontiguousarray(dy, np.float32)
+            dx = np.zeros_like(x)
+        self.lib.bbref_stochastic_bn(_vp(x), C.c_int(O), C.c_int(F), C.c_float(gamma), C.c_float(beta), C.c_float(momentum),
+                                     _vp(rm), _vp(rv), C.c_int(mode), _vp(y), _vp(mean), _vp(rstd), _vp(dy), _vp(dx))
+        return dict(y=y, mean=mean, rstd=rstd, running_mean=rm, running_var=rv, dx=dx)
+
+    def init_layer(self, n_in, n_out, seed=1, connection=""):
+        idx = np.zeros((n_out, 6), np.int32)
+        W = np.zeros((n_out, 64), np.float32)
+        self.lib.bbref_init_layer(C.c_int(n_in), C.c_int(n_out), C.c_uint64(seed), C.c_char_p(connection.encode()), _vp(idx), _vp(W))
+        return idx, W
+
+    def differentiable_lut6_adam(self, x, idx, W, dy, steps, batch_norm=True, binary=False, lut_binarize=False, gamma=0.3, beta=0.5,
+                                 momentum=0.9, lr=0.001, beta1=0.9, beta2=0.999):
+        x = np.ascontiguousarray(x, np.float32)
+        dy = np.ascontiguousarray(dy, np.float32)
+        I, F = x.shape
+        O = idx.shape[0]
+        Wo = np.ascontiguousarray(W, np.float32).copy()
+        y = np.zeros((O, F), np.float32)
+        rm = np.zeros(O, np.float32)
+        rv = np.zeros(O, np.float32)
+        self.lib.bbref_differentiable_lut6_adam(
+            _vp(x), C.c_int(I), C.c_int(O), C.c_int(F), _vp(np.ascontiguousarray(idx, np.int32)), _vp(Wo),
+            C.c_int(batch_norm), C.c_int(binary), C.c_int(lut_binarize), C.c_float(gamma), C.c_float(beta), C.c_float(momentum),
+            _vp(dy), C.c_int(steps), C.c_float(lr), C.c_float(beta1), C.c_float(beta2), _vp(y), _vp(rm), _vp(rv))
+        return dict(W=Wo, y=y, running_mean=rm, running_var=rv)
+
+
+port = _Port()
+ref = _Ref()

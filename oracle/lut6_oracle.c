@@ -1,0 +1,361 @@
+/* TEST INFRASTRUCTURE ONLY.
+ *
+ * CPU restatement, in plain C, of the arithmetic of BinaryBrain's 6-input LUT layer family.
+ * It is the checker the CUDA kernels are compared with; the product never links, imports or
+ * executes it.  Every function names the reference code (file:line inside ryuz/BinaryBrain
+ * v4.3.2) whose results it restates.
+ *
+ * Parity status: PINNED.  tests/test_oracle_pin.py compares every function below with the
+ * unmodified reference headers compiled into oracle/_ref/libbbref.so (oracle/ref_driver.cpp),
+ * and with the committed fixtures under tests/golden/ that were produced by that library.
+ *
+ * Layouts (host memory):
+ *   fp32 frames : row per node, `stride` floats per row, frame f at row[f]
+ *   bit frames  : row per node, `stride` uint32 per row, frame f = bit (f & 31) of word (f >> 5)
+ *                 (include/bb/DataType.h:612-647, LSB first)
+ *   wiring      : idx[node*6 + k]                         (include/bb/FixedSizeConnectionTable.h:24-216)
+ *   W           : W[node*64 + i], bit k of i <-> input k  (include/bb/StochasticOperation.h:95-114)
+ */
+#include <stdint.h>
+#include <stddef.h>
+#include <string.h>
+#include <math.h>
+
+typedef struct {
+    int   binary;        /* x -> 0.5 +/- bias by (x > 0.5)  (fp32 input only; bit input always is) */
+    int   lut_binarize;  /* W -> {0,1} by (W > 0.5) */
+    float bias;          /* unbinarize_bias, 0.25 in the reference */
+} lut_mode_t;
+
+static inline int get_bit(uint32_t const *row, int f) { return (int)((row[f >> 5] >> (f & 31)) & 1u); }
+
+static inline void set_bit(uint32_t *row, int f, int v)
+{
+    uint32_t m = 1u << (f & 31);
+    if (v) row[f >> 5] |= m; else row[f >> 5] &= ~m;
+}
+
+/* Input conditioning shared by every CPU branch:
+ * include/bb/DifferentiableLutN.h:779-786 and include/bb/StochasticLutN.h:527-535. */
+static inline void fetch_x(float xv[6], int bit_input, void const *x, size_t x_stride, int const *idx6, int f, lut_mode_t const *m)
+{
+    for (int i = 0; i < 6; ++i) {
+        float v;
+        if (bit_input) v = (float)get_bit((uint32_t const *)x + (size_t)idx6[i] * x_stride, f);
+        else           v = ((float const *)x)[(size_t)idx6[i] * x_stride + f];
+        if (bit_input || m->binary) xv[i] = 0.5f + ((v > 0.5f) ? +m->bias : -m->bias);
+        else                        xv[i] = fminf(1.0f, fmaxf(0.0f, v));
+    }
+}
+
+static inline void fetch_W(float Wv[64], float const *W, int node, lut_mode_t const *m)
+{
+    for (int i = 0; i < 64; ++i) {
+        float w = W[(size_t)node * 64 + i];
+        Wv[i] = m->lut_binarize ? ((w > 0.5f) ? 1.0f : 0.0f) : w;    /* DifferentiableLutN.h:765-771 */
+    }
+}
+
+/* include/bb/StochasticOperation.h:95-114  StochasticOperation_Lut_Forward */
+static inline float lut_forward(float const x[6], float const W[64])
+{
+    float acc = 0.0f;
+    for (int i = 0; i < 64; ++i) {
+        float w = W[i];
+        for (int j = 0; j < 6; ++j) w *= ((i >> j) & 1) ? x[j] : (1.0f - x[j]);
+        acc += w;
+    }
+    return acc;
+}
+
+/* include/bb/StochasticOperation.h:118-152  StochasticOperation_Lut_Backward */
+static inline void lut_backward(float const x[6], float dx[6], float dy, float const W[64], float dW[64])
+{
+    for (int i = 0; i < 64; ++i) {
+        float dw = dy;
+        for (int j = 0; j < 6; ++j) dw *= ((i >> j) & 1) ? x[j] : (1.0f - x[j]);
+        dW[i] += dw;
+    }
+    for (int i = 0; i < 6; ++i) {
+        dx[i] = 0.0f;
+        for (int j = 0; j < 64; ++j) {
+            float w = ((j >> i) & 1) ? +W[j] : -W[j];
+            for (int k = 0; k < 6; ++k) if (i != k) w *= ((j >> k) & 1) ? x[k] : (1.0f - x[k]);
+            dx[i] += w;
+        }
+        dx[i] *= dy;
+    }
+}
+
+/* ------------------------------------------------------------------------------------------
+ * StochasticLut6 (no batch norm)
+ * forward : include/bb/StochasticLutN.h:512-559 (generic), StochasticLutSimd.h:25-190 (AVX2)
+ *           y = clip(lut(x), 0, 1); y_bit_out packs (y > 0.5) as DifferentiableLutN.h:990-993 does
+ * backward: include/bb/StochasticLutN.h:668-752; dx = sum over consuming nodes; dW accumulated
+ * ------------------------------------------------------------------------------------------ */
+void oracle_sl6_forward(int bit_input, void const *x, size_t x_stride, float *y, size_t y_stride, uint32_t *y_bits, size_t yb_stride,
+                        int const *idx, float const *W, int O, int F, int binary, int lut_binarize, float bias)
+{
+    lut_mode_t m = { binary, lut_binarize, bias };
+    #pragma omp parallel for
+    for (int node = 0; node < O; ++node) {
+        float Wv[64]; fetch_W(Wv, W, node, &m);
+        for (int f = 0; f < F; ++f) {
+            float xv[6]; fetch_x(xv, bit_input, x, x_stride, idx + node * 6, f, &m);
+            float v = lut_forward(xv, Wv);
+            if (y_bits) set_bit(y_bits + (size_t)node * yb_stride, f, v > 0.5f);
+            v = fmaxf(0.0f, v); v = fminf(1.0f, v);
+            if (y) y[(size_t)node * y_stride + f] = v;
+        }
+    }
+}
+
+void oracle_sl6_backward(int bit_input, void const *x, size_t x_stride, float const *dy, size_t dy_stride, float *dx, size_t dx_stride,
+                         int const *idx, float const *W, float *dW, int I, int O, int F, int binary, int lut_binarize, float bias)
+{
+    lut_mode_t m = { binary, lut_binarize, bias };
+    for (int i = 0; i < I; ++i) memset(dx + (size_t)i * dx_stride, 0, sizeof(float) * F);
+    for (int node = 0; node < O; ++node) {
+        float Wv[64]; fetch_W(Wv, W, node, &m);
+        float dWv[64] = {0};
+        for (int f = 0; f < F; ++f) {
+            float xv[6]; fetch_x(xv, bit_input, x, x_stride, idx + node * 6, f, &m);
+            float dxv[6];
+            lut_backward(xv, dxv, dy[(size_t)node * dy_stride + f], Wv, dWv);
+            for (int i = 0; i < 6; ++i) dx[(size_t)idx[node * 6 + i] * dx_stride + f] += dxv[i];
+        }
+        for (int i = 0; i < 64; ++i) dW[(size_t)node * 64 + i] += dWv[i];
+    }
+}
+
+/* ------------------------------------------------------------------------------------------
+ * DifferentiableLut6 = LUT6 + scalar-gamma/beta batch norm over frames + hard-tanh / binarize
+ * training forward : include/bb/DifferentiableLutN.h:747-845
+ * inference forward: include/bb/DifferentiableLutN.h:847-905
+ * backward         : include/bb/DifferentiableLutN.h:1157-1266
+ * y (fp32) gets {0,1} in binary mode, clip(.,0,1) otherwise; y_bits (optional) packs (y_bn > 0.5).
+ * y_pre (optional) receives the batch-normalised value before binarize/clip so that callers can
+ * tell a genuine mismatch from a value sitting on a decision threshold.
+ * ------------------------------------------------------------------------------------------ */
+void oracle_dl6_forward_train(int bit_input, void const *x, size_t x_stride, float *y, size_t y_stride, uint32_t *y_bits, size_t yb_stride,
+                              float *y_pre, int const *idx, float const *W,
+                              float *mean_out, float *rstd_out, float *running_mean, float *running_var,
+                              float gamma, float beta, float momentum, float bias,
+                              int O, int F, int lut_binarize, int binary)
+{
+    lut_mode_t m = { binary, lut_binarize, bias };
+    float rF = 1.0f / (float)F;
+    #pragma omp parallel for
+    for (int node = 0; node < O; ++node) {
+        float Wv[64]; fetch_W(Wv, W, node, &m);
+        /* Kahan sums of y and y*y: DifferentiableLutN.h:775-802 */
+        float s1 = 0, c1 = 0, y1, t1, s2 = 0, c2 = 0, y2, t2;
+        for (int f = 0; f < F; ++f) {
+            float xv[6]; fetch_x(xv, bit_input, x, x_stride, idx + node * 6, f, &m);
+            float v = lut_forward(xv, Wv);
+            y1 = v - c1;       t1 = s1 + y1; c1 = (t1 - s1) - y1; s1 = t1;
+            y2 = (v * v) - c2; t2 = s2 + y2; c2 = (t2 - s2) - y2; s2 = t2;
+        }
+        float mean = s1 * rF;
+        /* DifferentiableLutN.h:805 writes (s2*rF) - (mean*mean); with the reference's own build flags
+         * (-O2 -mfma, GCC's default -ffp-contract=fast) that is one fused multiply-subtract, spelled
+         * out here so that the result does not depend on this file's compiler. */
+        float var  = fmaxf(1.0e-5f, fmaf(s2, rF, -(mean * mean)));
+        float rstd = 1.0f / sqrtf(var);
+        running_mean[node] = running_mean[node] * momentum + mean * (1.0f - momentum);
+        running_var[node]  = running_var[node]  * momentum + var  * (1.0f - momentum);
+        mean_out[node] = mean;
+        rstd_out[node] = rstd;
+        for (int f = 0; f < F; ++f) {
+            float xv[6]; fetch_x(xv, bit_input, x, x_stride, idx + node * 6, f, &m);
+            float v = lut_forward(xv, Wv);
+            v = (v - mean) * rstd;
+            v = v * gamma + beta;
+            if (y_pre)  y_pre[(size_t)node * y_stride + f] = v;
+            if (y_bits) set_bit(y_bits + (size_t)node * yb_stride, f, v > 0.5f);
+            if (binary) v = (v > 0.5f) ? 1.0f : 0.0f;
+            else { v = fminf(v, 1.0f); v = fmaxf(v, 0.0f); }
+            if (y) y[(size_t)node * y_stride + f] = v;
+        }
+    }
+}
+
+void oracle_dl6_forward_infer(int bit_input, void const *x, size_t x_stride, float *y, size_t y_stride, uint32_t *y_bits, size_t yb_stride,
+                              float *y_pre, int const *idx, float const *W,
+                              float const *running_mean, float const *running_var,
+                              float gamma, float beta, float bias, int O, int F, int lut_binarize, int binary)
+{
+    lut_mode_t m = { binary, lut_binarize, bias };
+    #pragma omp parallel for
+    for (int node = 0; node < O; ++node) {
+        float Wv[64]; fetch_W(Wv, W, node, &m);
+        float mean = running_mean[node];
+        float rstd = 1.0f / sqrtf(running_var[node]);       /* DifferentiableLutN.h:866-868 */
+        for (int f = 0; f < F; ++f) {
+            float xv[6]; fetch_x(xv, bit_input, x, x_stride, idx + node * 6, f, &m);
+            float v = lut_forward(xv, Wv);
+            v = (v - mean) * rstd;
+            v = v * gamma + beta;
+            if (y_pre)  y_pre[(size_t)node * y_stride + f] = v;
+            if (y_bits) set_bit(y_bits + (size_t)node * yb_stride, f, v > 0.5f);
+            if (binary) v = (v > 0.5f) ? 1.0f : 0.0f;
+            else { v = fminf(v, 1.0f); v = fmaxf(v, 0.0f); }
+            if (y) y[(size_t)node * y_stride + f] = v;
+        }
+    }
+}
+
+void oracle_dl6_backward(int bit_input, void const *x, size_t x_stride, float const *dy, size_t dy_stride, float *dx, size_t dx_stride,
+                         int const *idx, float const *W, float *dW, float const *mean_in, float const *rstd_in,
+                         float gamma, float beta, float bias, int I, int O, int F, int lut_binarize, int binary)
+{
+    lut_mode_t m = { binary, lut_binarize, bias };
+    float rF = 1.0f / (float)F;
+    for (int i = 0; i < I; ++i) memset(dx + (size_t)i * dx_stride, 0, sizeof(float) * F);
+    for (int node = 0; node < O; ++node) {
+        float Wv[64]; fetch_W(Wv, W, node, &m);
+        float dWv[64] = {0};
+        float mean = mean_in[node], rstd = rstd_in[node], rstd2 = rstd * rstd;
+        float dmeanx = 0, dstd = 0;
+        for (int f = 0; f < F; ++f) {           /* DifferentiableLutN.h:1190-1220 */
+            float xv[6]; fetch_x(xv, bit_input, x, x_stride, idx + node * 6, f, &m);
+            float v = lut_forward(xv, Wv);
+            float tanh_x = ((v - mean) * rstd) * gamma + beta;
+            float g = dy[(size_t)node * dy_stride + f];
+            if (tanh_x <= 0.0f) g = 0.0f;
+            if (tanh_x >= 1.0f) g = 0.0f;
+            float xc = v - mean, dxn = gamma * g;
+            dstd   += -(dxn * xc * rstd2);
+            dmeanx += -(dxn * rstd);
+        }
+        float dvar  = dstd * rstd;
+        float dmean = (dmeanx - (mean * dvar)) * rF;
+        for (int f = 0; f < F; ++f) {           /* DifferentiableLutN.h:1225-1258 */
+            float xv[6]; fetch_x(xv, bit_input, x, x_stride, idx + node * 6, f, &m);
+            float v = lut_forward(xv, Wv);
+            float tanh_x = ((v - mean) * rstd) * gamma + beta;
+            float g = dy[(size_t)node * dy_stride + f];
+            if (tanh_x <= 0.0f) g = 0.0f;
+            if (tanh_x >= 1.0f) g = 0.0f;
+            float dxn = g * gamma, dxc = dxn * rstd;
+            float gg  = dxc + dmean + (v * dvar * rF);
+            float dxv[6];
+            lut_backward(xv, dxv, gg, Wv, dWv);
+            for (int i = 0; i < 6; ++i) dx[(size_t)idx[node * 6 + i] * dx_stride + f] += dxv[i];
+        }
+        for (int i = 0; i < 64; ++i) dW[(size_t)node * 64 + i] += dWv[i];
+    }
+}
+
+/* ------------------------------------------------------------------------------------------
+ * StochasticBatchNormalization (stand-alone), generic CPU branch
+ * training forward : include/bb/StochasticBatchNormalization.h:521-594 (two-pass variance,
+ *                    var = max(0,var), rstd = 1/(sqrt(var)+1e-7))
+ * re-forward       : include/bb/StochasticBatchNormalization.h:655-682
+ * inference forward: include/bb/StochasticBatchNormalization.h:596-614 written as gain*x+offset.
+ *                    The reference takes the offset's mean from its per-batch mean tensor
+ *                    (:603); the operator ABI only carries the running statistics
+ *                    (include/bbcu/bbcu.h:911-923), so `mean` here is whatever the caller passes.
+ * backward         : include/bb/StochasticBatchNormalization.h:808-852
+ * ------------------------------------------------------------------------------------------ */
+void oracle_sbn_forward_train(float const *x, float *y, size_t stride, float *mean_out, float *rstd_out,
+                              float *running_mean, float *running_var, float gamma, float beta, float momentum, int O, int F)
+{
+    #pragma omp parallel for
+    for (int node = 0; node < O; ++node) {
+        float const *xr = x + (size_t)node * stride;
+        float mean = 0;
+        for (int f = 0; f < F; ++f) mean += xr[f];
+        mean /= (float)F;
+        float var = 0;
+        for (int f = 0; f < F; ++f) { float xc = xr[f] - mean; var += xc * xc; }
+        var /= (float)F;
+        var = fmaxf(0.0f, var);
+        float rstd = 1.0f / (sqrtf(var) + 1.0e-7f);
+        running_mean[node] = running_mean[node] * momentum + mean * (1.0f - momentum);
+        running_var[node]  = running_var[node]  * momentum + var  * (1.0f - momentum);
+        mean_out[node] = mean; rstd_out[node] = rstd;
+        for (int f = 0; f < F; ++f) {
+            float v = (xr[f] - mean) * rstd;
+            y[(size_t)node * stride + f] = v * gamma + beta;
+        }
+    }
+}
+
+void oracle_sbn_reforward(float const *x, float *y, size_t stride, float const *mean, float const *rstd, float gamma, float beta, int O, int F)
+{
+    for (int node = 0; node < O; ++node)
+        for (int f = 0; f < F; ++f) {
+            float v = (x[(size_t)node * stride + f] - mean[node]) * rstd[node];
+            y[(size_t)node * stride + f] = v * gamma + beta;
+        }
+}
+
+void oracle_sbn_forward_infer(float const *x, float *y, size_t stride, float const *mean, float const *var, float gamma, float beta, int O, int F)
+{
+    for (int node = 0; node < O; ++node) {
+        float gain   = gamma / (sqrtf(var[node]) + 1.0e-7f);
+        float offset = beta - (gamma * mean[node] / (sqrtf(var[node]) + 1.0e-7f));
+        for (int f = 0; f < F; ++f) y[(size_t)node * stride + f] = gain * x[(size_t)node * stride + f] + offset;
+    }
+}
+
+void oracle_sbn_backward(float const *x, float const *dy, float *dx, size_t stride, float const *mean_in, float const *rstd_in, float gamma, int O, int F)
+{
+    #pragma omp parallel for
+    for (int node = 0; node < O; ++node) {
+        float mean = mean_in[node], rstd = rstd_in[node], dmeanx = 0, dstd = 0;
+        for (int f = 0; f < F; ++f) {
+            float xc = x[(size_t)node * stride + f] - mean;
+            float dxn = gamma * dy[(size_t)node * stride + f];
+            dstd   += -(dxn * xc * (rstd * rstd));
+            dmeanx += -(dxn * rstd);
+        }
+        float dvar  = dstd * rstd;
+        float dmean = (dmeanx - (mean * dvar)) / (float)F;
+        for (int f = 0; f < F; ++f) {
+            float dxn = dy[(size_t)node * stride + f] * gamma;
+            float dxc = dxn * rstd;
+            dx[(size_t)node * stride + f] = dxc + dmean + (x[(size_t)node * stride + f] * dvar / (float)F);
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------------------------
+ * BinaryLut6 bit-packed inference forward
+ * include/bb/BinaryLutN.h:436-463 (generic) and :322-433 (AVX2): index bit k = input k,
+ * y = bit `index` of the node's 64-bit table stored as two int32 (BinaryLutN.h:43-46,279-284).
+ * Frames >= F inside the last word are written as 0 here; callers compare F frames only.
+ * ------------------------------------------------------------------------------------------ */
+void oracle_binary_lut6_forward(uint32_t const *x, uint32_t *y, size_t stride, int const *idx, int32_t const *table, int O, int F)
+{
+    #pragma omp parallel for
+    for (int node = 0; node < O; ++node) {
+        uint64_t t = ((uint64_t)(uint32_t)table[node * 2 + 1] << 32) | (uint32_t)table[node * 2];
+        uint32_t *yr = y + (size_t)node * stride;
+        memset(yr, 0, sizeof(uint32_t) * ((F + 31) / 32));
+        for (int f = 0; f < F; ++f) {
+            int index = 0;
+            for (int k = 0; k < 6; ++k) index |= get_bit(x + (size_t)idx[node * 6 + k] * stride, f) << k;
+            if ((t >> index) & 1u) yr[f >> 5] |= 1u << (f & 31);
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------------------------
+ * Adam as the layer's optimizer applies it (include/bb/OptimizerAdam.h:142-184 CPU branch):
+ *   lr_t = lr * sqrt(1 - b2^t) / (1 - b1^t);  m += (1-b1)(g-m);  v += (1-b2)(g*g-v);
+ *   p -= lr_t * m / (sqrt(v) + 1e-7);  then the gradient is zeroed (include/bb/Optimizer.h:29-33).
+ * b1t / b2t are the running powers, updated by the caller's state here.
+ * ------------------------------------------------------------------------------------------ */
+void oracle_adam_update(float *p, float *g, float *mbuf, float *vbuf, size_t n, float lr, float beta1, float beta2, float *b1t, float *b2t)
+{
+    *b1t *= beta1; *b2t *= beta2;
+    float lr_t = lr * sqrtf(1.0f - *b2t) / (1.0f - *b1t);
+    for (size_t i = 0; i < n; ++i) {
+        mbuf[i] += (1.0f - beta1) * (g[i] - mbuf[i]);
+        vbuf[i] += (1.0f - beta2) * (g[i] * g[i] - vbuf[i]);
+        p[i] -= lr_t * mbuf[i] / (sqrtf(vbuf[i]) + 1.0e-7f);
+        g[i] = 0.0f;
+    }
+}

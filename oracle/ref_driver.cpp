@@ -1,0 +1,388 @@
+// TEST INFRASTRUCTURE ONLY -- never linked into, imported by or executed from the product path.
+//
+// Thin extern "C" driver around the *unmodified* BinaryBrain header-only CPU implementation.
+// It is compiled against the reference's own headers where they lie (-I<reference>/include, no
+// BB_WITH_CUDA) by oracle/Makefile into oracle/_ref/libbbref.so.  Nothing of the reference is
+// copied here: this file only instantiates the reference's public classes, feeds them caller
+// supplied wiring / tables / frames, and copies the results back out.
+//
+// Used for: (1) pinning oracle/lut6_oracle.c, (2) generating tests/golden/*.npz,
+//           (3) the "reference" CPU-baseline arm of bench.py.
+//
+// Dense array conventions of this driver (all host memory):
+//   fp32 frames  : [node][frame]  contiguous, no padding
+//   bit frames   : [node][words]  32 frames per uint32, LSB first, words = ceil(frames/32)
+//   wiring       : [out_node][6]  int32
+//   W            : [out_node][64] fp32
+//   binary table : [out_node][2]  int32 (bit i of the 64-bit table = output for input index i)
+
+#include <cstdint>
+#include <cstring>
+#include <chrono>
+#include <vector>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#include "bb/StochasticLutN.h"
+#include "bb/DifferentiableLutN.h"
+#include "bb/BinaryLutN.h"
+#include "bb/StochasticBatchNormalization.h"
+#include "bb/OptimizerAdam.h"
+
+namespace {
+
+using clk = std::chrono::steady_clock;
+inline double secs(clk::time_point a, clk::time_point b) { return std::chrono::duration<double>(b - a).count(); }
+
+void put_fp32(bb::FrameBuffer &buf, float const *src, int nodes, int frames)
+{
+    auto ptr = buf.Lock<float>(true);
+    for (int n = 0; n < nodes; ++n) {
+        std::memcpy(ptr.GetAddr(n), src + (size_t)n * frames, sizeof(float) * frames);
+    }
+}
+
+void get_fp32(bb::FrameBuffer const &buf, float *dst, int nodes, int frames)
+{
+    auto ptr = buf.LockConst<float>();
+    for (int n = 0; n < nodes; ++n) {
+        std::memcpy(dst + (size_t)n * frames, ptr.GetAddr(n), sizeof(float) * frames);
+    }
+}
+
+void put_bit(bb::FrameBuffer &buf, std::uint32_t const *src, int nodes, int frames)
+{
+    int words = (frames + 31) / 32;
+    auto mem  = buf.LockMemory(true);
+    auto base = (std::uint8_t *)mem.GetAddr();
+    auto stride = buf.GetFrameStride();
+    for (int n = 0; n < nodes; ++n) {
+        std::memset(base + (size_t)n * stride, 0, stride);
+        std::memcpy(base + (size_t)n * stride, src + (size_t)n * words, sizeof(std::uint32_t) * words);
+    }
+}
+
+void get_bit(bb::FrameBuffer const &buf, std::uint32_t *dst, int nodes, int frames)
+{
+    int words = (frames + 31) / 32;
+    auto mem  = buf.LockMemoryConst();
+    auto base = (std::uint8_t const *)mem.GetAddr();
+    auto stride = buf.GetFrameStride();
+    for (int n = 0; n < nodes; ++n) {
+        std::memcpy(dst + (size_t)n * words, base + (size_t)n * stride, sizeof(std::uint32_t) * words);
+        if (frames % 32) {   // padding bits are not part of the result
+            dst[(size_t)n * words + words - 1] &= (1u << (frames % 32)) - 1u;
+        }
+    }
+}
+
+template <class Layer>
+void set_wiring(Layer &lut, int const *idx, int out_nodes)
+{
+    for (int n = 0; n < out_nodes; ++n)
+        for (int i = 0; i < 6; ++i)
+            lut->SetNodeConnectionIndex(n, i, idx[n * 6 + i]);
+}
+
+template <class Layer>
+void set_W(Layer &lut, float const *W, int out_nodes)
+{
+    auto p = lut->lock_W();
+    for (int n = 0; n < out_nodes; ++n)
+        for (int i = 0; i < 64; ++i)
+            p(n, i) = W[n * 64 + i];
+}
+
+template <class Layer>
+void get_dW(Layer &lut, float *dW, int out_nodes)
+{
+    auto p = lut->lock_dW_const();
+    for (int n = 0; n < out_nodes; ++n)
+        for (int i = 0; i < 64; ++i)
+            dW[n * 64 + i] = p(n, i);
+}
+
+template <class Layer>
+void set_dW(Layer &lut, float const *dW, int out_nodes)
+{
+    auto p = lut->lock_dW();
+    for (int n = 0; n < out_nodes; ++n)
+        for (int i = 0; i < 64; ++i)
+            p(n, i) = dW[n * 64 + i];
+}
+
+template <typename BinType>
+int run_stochastic(void const *x, int I, int O, int F, int const *idx, float const *W,
+                   int binary, int lut_binarize, int host_simd,
+                   float *y, float const *dy, float *dx, float *dW, double *t)
+{
+    auto lut = bb::StochasticLutN<6, BinType, float>::Create(O);
+    lut->SendCommand("host_only true");
+    lut->SendCommand(binary ? "binary true" : "binary false");
+    lut->SendCommand(lut_binarize ? "lut_binarize true" : "lut_binarize false");
+    lut->SendCommand(host_simd ? "host_simd true" : "host_simd false");
+
+    bb::FrameBuffer x_buf(F, {I}, bb::DataType<BinType>::type, true);
+    lut->SetInputShape(x_buf.GetShape());
+    set_wiring(lut, idx, O);
+    set_W(lut, W, O);
+    if (std::is_same<BinType, float>::value) put_fp32(x_buf, (float const *)x, I, F);
+    else                                     put_bit(x_buf, (std::uint32_t const *)x, I, F);
+
+    auto t0 = clk::now();
+    auto y_buf = lut->Forward(x_buf, true);
+    auto t1 = clk::now();
+    if (y) get_fp32(y_buf, y, O, F);
+    if (t) t[0] = secs(t0, t1);
+
+    if (dy) {
+        bb::FrameBuffer dy_buf(F, {O}, BB_TYPE_FP32, true);
+        put_fp32(dy_buf, dy, O, F);
+        if (dW) set_dW(lut, dW, O);          // dW is accumulated into: start from the caller's values
+        auto t2 = clk::now();
+        auto dx_buf = lut->Backward(dy_buf);
+        auto t3 = clk::now();
+        if (dx) get_fp32(dx_buf, dx, I, F);
+        if (dW) get_dW(lut, dW, O);
+        if (t) t[1] = secs(t2, t3);
+    }
+    return 0;
+}
+
+template <typename BinType>
+int run_differentiable(void const *x, int I, int O, int F, int const *idx, float const *W,
+                       int batch_norm, int binary, int lut_binarize,
+                       float gamma, float beta, float momentum,
+                       float *running_mean, float *running_var, int train,
+                       void *y, float *mean, float *rstd,
+                       float const *dy, float *dx, float *dW, double *t)
+{
+    using Layer = bb::DifferentiableLutN<6, BinType, float>;
+    typename Layer::create_t c;
+    c.output_shape = {O};
+    c.batch_norm   = batch_norm != 0;
+    c.binary       = binary != 0;
+    c.momentum     = momentum;
+    c.gamma        = gamma;
+    c.beta         = beta;
+    auto lut = Layer::Create(c);
+    lut->SendCommand("host_only true");
+    lut->SendCommand(lut_binarize ? "lut_binarize true" : "lut_binarize false");
+
+    bb::FrameBuffer x_buf(F, {I}, bb::DataType<BinType>::type, true);
+    lut->SetInputShape(x_buf.GetShape());
+    set_wiring(lut, idx, O);
+    set_W(lut, W, O);
+    if (running_mean && running_var) {
+        auto m = lut->lock_mean();
+        auto v = lut->lock_var();
+        for (int n = 0; n < O; ++n) { m[n] = running_mean[n]; v[n] = running_var[n]; }
+    }
+    if (std::is_same<BinType, float>::value) put_fp32(x_buf, (float const *)x, I, F);
+    else                                     put_bit(x_buf, (std::uint32_t const *)x, I, F);
+
+    auto t0 = clk::now();
+    auto y_buf = lut->Forward(x_buf, train != 0);
+    auto t1 = clk::now();
+    if (t) t[0] = secs(t0, t1);
+    if (y) {
+        if (std::is_same<BinType, float>::value) get_fp32(y_buf, (float *)y, O, F);
+        else                                     get_bit(y_buf, (std::uint32_t *)y, O, F);
+    }
+    if (train && batch_norm) {
+        auto m = lut->lock_tmp_mean_const();
+        auto r = lut->lock_tmp_rstd_const();
+        for (int n = 0; n < O; ++n) { if (mean) mean[n] = m[n]; if (rstd) rstd[n] = r[n]; }
+    }
+    if (running_mean && running_var) {
+        auto m = lut->lock_mean_const();
+        auto v = lut->lock_var_const();
+        for (int n = 0; n < O; ++n) { running_mean[n] = m[n]; running_var[n] = v[n]; }
+    }
+
+    if (train && dy) {
+        bb::FrameBuffer dy_buf(F, {O}, BB_TYPE_FP32, true);
+        put_fp32(dy_buf, dy, O, F);
+        if (dW) set_dW(lut, dW, O);
+        auto t2 = clk::now();
+        auto dx_buf = lut->Backward(dy_buf);
+        auto t3 = clk::now();
+        if (dx) get_fp32(dx_buf, dx, I, F);
+        if (dW) get_dW(lut, dW, O);
+        if (t) t[1] = secs(t2, t3);
+    }
+    return 0;
+}
+
+}   // namespace
+
+
+extern "C" {
+
+// bb::StochasticLutN<6,float|Bit,float>::Forward (+Backward when dy != NULL), CPU branch.
+int bbref_stochastic_lut6(int bit_input, void const *x, int I, int O, int F, int const *idx, float const *W,
+                          int binary, int lut_binarize, int host_simd,
+                          float *y, float const *dy, float *dx, float *dW, double *t)
+{
+    if (bit_input) return run_stochastic<bb::Bit>(x, I, O, F, idx, W, 1, lut_binarize, host_simd, y, dy, dx, dW, t);
+    return run_stochastic<float>(x, I, O, F, idx, W, binary, lut_binarize, host_simd, y, dy, dx, dW, t);
+}
+
+// bb::DifferentiableLutN<6,float|Bit,float>::Forward (+Backward when dy != NULL), generic CPU branch.
+int bbref_differentiable_lut6(int bit_io, void const *x, int I, int O, int F, int const *idx, float const *W,
+                              int batch_norm, int binary, int lut_binarize,
+                              float gamma, float beta, float momentum,
+                              float *running_mean, float *running_var, int train,
+                              void *y, float *mean, float *rstd,
+                              float const *dy, float *dx, float *dW, double *t)
+{
+    if (bit_io) return run_differentiable<bb::Bit>(x, I, O, F, idx, W, batch_norm, 1, lut_binarize, gamma, beta, momentum,
+                                                  running_mean, running_var, train, y, mean, rstd, dy, dx, dW, t);
+    return run_differentiable<float>(x, I, O, F, idx, W, batch_norm, binary, lut_binarize, gamma, beta, momentum,
+                                     running_mean, running_var, train, y, mean, rstd, dy, dx, dW, t);
+}
+
+// bb::BinaryLutN<6,bb::Bit>::Forward, AVX2 (host_simd=1) or generic (host_simd=0) CPU branch.
+int bbref_binary_lut6(std::uint32_t const *x, int I, int O, int F, int const *idx, std::int32_t const *table,
+                      int host_simd, std::uint32_t *y, double *t)
+{
+    auto lut = bb::BinaryLutN<6, bb::Bit, float>::Create(O);
+    lut->SendCommand("host_only true");
+    lut->SendCommand(host_simd ? "host_simd true" : "host_simd false");
+    bb::FrameBuffer x_buf(F, {I}, BB_TYPE_BIT, true);
+    lut->SetInputShape(x_buf.GetShape());
+    for (int n = 0; n < O; ++n) {
+        for (int i = 0; i < 6; ++i) lut->SetNodeConnectionIndex(n, i, idx[n * 6 + i]);
+        for (int i = 0; i < 64; ++i) lut->SetLutTable(n, i, ((table[n * 2 + (i >> 5)] >> (i & 31)) & 1) != 0);
+    }
+    put_bit(x_buf, x, I, F);
+    auto t0 = clk::now();
+    auto y_buf = lut->Forward(x_buf, false);
+    auto t1 = clk::now();
+    if (t) t[0] = secs(t0, t1);
+    if (y) get_bit(y_buf, y, O, F);
+    return 0;
+}
+
+// bb::StochasticBatchNormalization<float>: mode 0 = Forward(train), 1 = Forward(inference), 2 = ReForward.
+// Backward runs after a training forward when dy != NULL.
+int bbref_stochastic_bn(float const *x, int O, int F, float gamma, float beta, float momentum,
+                        float *running_mean, float *running_var, int mode,
+                        float *y, float *mean, float *rstd, float const *dy, float *dx)
+{
+    auto bn = bb::StochasticBatchNormalization<float>::Create(momentum, gamma, beta);
+    bn->SendCommand("host_only true");
+    bb::FrameBuffer x_buf(F, {O}, BB_TYPE_FP32, true);
+    bn->SetInputShape(x_buf.GetShape());
+    put_fp32(x_buf, x, O, F);
+    if (running_mean && running_var) {
+        auto m = bn->lock_mean();
+        auto v = bn->lock_var();
+        for (int n = 0; n < O; ++n) { m[n] = running_mean[n]; v[n] = running_var[n]; }
+    }
+    bb::FrameBuffer y_buf;
+    if (mode == 2) {
+        y_buf = bn->Forward(x_buf, true);      // establishes mean/rstd
+        bn->Backward(bb::FrameBuffer(F, {O}, BB_TYPE_FP32, true));
+        y_buf = bn->ReForward(x_buf);
+    } else {
+        y_buf = bn->Forward(x_buf, mode == 0);
+    }
+    if (y) get_fp32(y_buf, y, O, F);
+    {
+        auto m = bn->lock_tmp_mean_const();
+        auto r = bn->lock_tmp_rstd_const();
+        for (int n = 0; n < O; ++n) { if (mean) mean[n] = m[n]; if (rstd) rstd[n] = r[n]; }
+    }
+    if (running_mean && running_var) {
+        auto m = bn->lock_mean_const();
+        auto v = bn->lock_var_const();
+        for (int n = 0; n < O; ++n) { running_mean[n] = m[n]; running_var[n] = v[n]; }
+    }
+    if (dy && mode != 1) {
+        bb::FrameBuffer dy_buf(F, {O}, BB_TYPE_FP32, true);
+        put_fp32(dy_buf, dy, O, F);
+        auto dx_buf = bn->Backward(dy_buf);
+        if (dx) get_fp32(dx_buf, dx, O, F);
+    }
+    return 0;
+}
+
+// The reference's seeded wiring and table initialisation of a fresh layer
+// (FixedSizeConnectionTable::InitializeConnection + Tensor::InitNormalDistribution).
+int bbref_init_layer(int I, int O, std::uint64_t seed, char const *connection, int *idx, float *W)
+{
+    bb::DifferentiableLutN<6, float, float>::create_t c;
+    c.output_shape = {O};
+    c.seed         = seed;
+    c.connection   = connection ? connection : "";
+    auto lut = bb::DifferentiableLutN<6, float, float>::Create(c);
+    lut->SetInputShape({I});
+    for (int n = 0; n < O; ++n)
+        for (int i = 0; i < 6; ++i)
+            idx[n * 6 + i] = (int)lut->GetNodeConnectionIndex(n, i);
+    auto p = lut->lock_W_const();
+    for (int n = 0; n < O; ++n)
+        for (int i = 0; i < 64; ++i)
+            W[n * 64 + i] = p(n, i);
+    return 0;
+}
+
+// steps x { DifferentiableLutN forward(train) -> backward(dy) -> OptimizerAdam::Update } on fixed x, dy.
+int bbref_differentiable_lut6_adam(float const *x, int I, int O, int F, int const *idx, float *W,
+                                   int batch_norm, int binary, int lut_binarize,
+                                   float gamma, float beta, float momentum,
+                                   float const *dy, int steps, float lr, float beta1, float beta2,
+                                   float *y_last, float *running_mean, float *running_var)
+{
+    using Layer = bb::DifferentiableLutN<6, float, float>;
+    Layer::create_t c;
+    c.output_shape = {O};
+    c.batch_norm = batch_norm != 0; c.binary = binary != 0;
+    c.momentum = momentum; c.gamma = gamma; c.beta = beta;
+    auto lut = Layer::Create(c);
+    lut->SendCommand("host_only true");
+    lut->SendCommand(lut_binarize ? "lut_binarize true" : "lut_binarize false");
+    bb::FrameBuffer x_buf(F, {I}, BB_TYPE_FP32, true);
+    lut->SetInputShape(x_buf.GetShape());
+    set_wiring(lut, idx, O);
+    set_W(lut, W, O);
+    put_fp32(x_buf, x, I, F);
+    bb::FrameBuffer dy_buf(F, {O}, BB_TYPE_FP32, true);
+    put_fp32(dy_buf, dy, O, F);
+
+    bb::OptimizerAdam<float>::create_t oc;
+    oc.learning_rate = lr; oc.beta1 = beta1; oc.beta2 = beta2;
+    auto opt = bb::OptimizerAdam<float>::Create(oc);
+    opt->SetVariables(lut->GetParameters(), lut->GetGradients());
+
+    bb::FrameBuffer y_buf;
+    for (int s = 0; s < steps; ++s) {
+        y_buf = lut->Forward(x_buf, true);
+        lut->Backward(dy_buf);
+        opt->Update();
+    }
+    if (y_last) get_fp32(y_buf, y_last, O, F);
+    {
+        auto p = lut->lock_W_const();
+        for (int n = 0; n < O; ++n) for (int i = 0; i < 64; ++i) W[n * 64 + i] = p(n, i);
+    }
+    if (running_mean && running_var) {
+        auto m = lut->lock_mean_const();
+        auto v = lut->lock_var_const();
+        for (int n = 0; n < O; ++n) { running_mean[n] = m[n]; running_var[n] = v[n]; }
+    }
+    return 0;
+}
+
+int bbref_num_threads(void)
+{
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+}   // extern "C"

@@ -1,0 +1,163 @@
+"""Regenerates tests/golden/lut6_golden.npz from the UNMODIFIED reference CPU path.
+
+Run where a reference checkout exists (oracle/Makefile builds oracle/_ref/libbbref.so from the
+reference headers with the reference's own flags: g++ -O2 -mavx2 -mfma -fopenmp -std=c++14):
+
+    make -C oracle && python tests/golden/make_golden.py
+
+Shapes follow the reference's own unit tests: StochasticLutNTest.cpp:235-246 and :437-449,
+SparseLutNTest.cpp:308-370, BinaryLutTest.cpp:187-190.  Inputs come from numpy's PCG64 with the
+seeds below; wiring and tables are drawn here and handed to the reference object, the way the
+reference's tests copy them between their CPU and GPU objects (StochasticLutNTest.cpp:36-53).
+"""
+import os
+import sys
+
+import numpy as np
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", ".."))
+from oracle import ref, pack_bits  # noqa: E402
+
+OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lut6_golden.npz")
+
+
+def wiring(rng, n_in, n_out):
+    return np.stack([rng.permutation(n_in)[:6] for _ in range(n_out)]).astype(np.int32)
+
+
+def main():
+    assert ref.available(), "build oracle/_ref first (make -C oracle)"
+    g = {}
+    rng = np.random.default_rng(20240601)
+
+    # StochasticLutN<6,float> CPU (generic branch, host_simd=false) and the AVX2 branch where F % 8 == 0
+    for (I, O, F) in [(6, 1, 1), (14, 16, 8), (14, 64, 3), (13, 17, 193)]:
+        for binary in (0, 1):
+            for lb in (0, 1):
+                k = f"sl6_{I}_{O}_{F}_b{binary}_l{lb}"
+                idx = wiring(rng, I, O)
+                W = np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32)
+                x = rng.random((I, F), dtype=np.float32)
+                dy = rng.random((O, F), dtype=np.float32)
+                dW0 = rng.random((O, 64), dtype=np.float32)
+                r = ref.stochastic_lut6(x, idx, W, binary=binary, lut_binarize=lb, host_simd=False, dy=dy, dW=dW0)
+                g.update({k + "_idx": idx, k + "_W": W, k + "_x": x, k + "_dy": dy, k + "_dW0": dW0,
+                          k + "_y": r["y"], k + "_dx": r["dx"], k + "_dW": r["dW"]})
+                if F % 8 == 0:
+                    r = ref.stochastic_lut6(x, idx, W, binary=binary, lut_binarize=lb, host_simd=True, dy=dy, dW=dW0)
+                    g.update({k + "_y_simd": r["y"], k + "_dx_simd": r["dx"], k + "_dW_simd": r["dW"]})
+
+    # StochasticLutN<6,Bit>
+    for (I, O, F) in [(14, 16, 8), (13, 17, 161)]:
+        for lb in (0, 1):
+            k = f"sl6bit_{I}_{O}_{F}_l{lb}"
+            idx = wiring(rng, I, O)
+            W = np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32)
+            xb = pack_bits(rng.random((I, F)) > 0.5)
+            dy = rng.random((O, F), dtype=np.float32)
+            r = ref.stochastic_lut6(xb, idx, W, frames=F, lut_binarize=lb, dy=dy)
+            g.update({k + "_idx": idx, k + "_W": W, k + "_x": xb, k + "_dy": dy, k + "_y": r["y"], k + "_dx": r["dx"], k + "_dW": r["dW"]})
+
+    # DifferentiableLutN<6,float> with batch norm (generic CPU branch), train + inference
+    for (I, O, F) in [(6, 1, 1), (12, 2, 39), (24, 16, 64), (16, 16, 131)]:
+        for binary in (0, 1):
+            for lb in (0, 1):
+                k = f"dl6_{I}_{O}_{F}_b{binary}_l{lb}"
+                idx = wiring(rng, I, O)
+                W = np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32)
+                x = rng.random((I, F), dtype=np.float32)
+                dy = rng.random((O, F), dtype=np.float32)
+                rm0 = rng.random(O, dtype=np.float32)
+                rv0 = rng.random(O, dtype=np.float32) + 0.5
+                r = ref.differentiable_lut6(x, idx, W, binary=binary, lut_binarize=lb, running_mean=rm0, running_var=rv0, dy=dy)
+                ri = ref.differentiable_lut6(x, idx, W, binary=binary, lut_binarize=lb, running_mean=rm0, running_var=rv0, train=False)
+                g.update({k + "_idx": idx, k + "_W": W, k + "_x": x, k + "_dy": dy, k + "_rm0": rm0, k + "_rv0": rv0,
+                          k + "_y": r["y"], k + "_mean": r["mean"], k + "_rstd": r["rstd"], k + "_rm": r["running_mean"],
+                          k + "_rv": r["running_var"], k + "_dx": r["dx"], k + "_dW": r["dW"], k + "_y_infer": ri["y"]})
+
+    # DifferentiableLutN<6,Bit>
+    for (I, O, F) in [(12, 2, 39), (24, 16, 64), (16, 16, 131)]:
+        for lb in (0, 1):
+            k = f"dl6bit_{I}_{O}_{F}_l{lb}"
+            idx = wiring(rng, I, O)
+            W = np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32)
+            xb = pack_bits(rng.random((I, F)) > 0.5)
+            dy = rng.random((O, F), dtype=np.float32)
+            r = ref.differentiable_lut6(xb, idx, W, frames=F, lut_binarize=lb, dy=dy)
+            ri = ref.differentiable_lut6(xb, idx, W, frames=F, lut_binarize=lb, running_mean=r["running_mean"],
+                                         running_var=r["running_var"], train=False)
+            g.update({k + "_idx": idx, k + "_W": W, k + "_x": xb, k + "_dy": dy, k + "_y": r["y"], k + "_mean": r["mean"],
+                      k + "_rstd": r["rstd"], k + "_rm": r["running_mean"], k + "_rv": r["running_var"], k + "_dx": r["dx"],
+                      k + "_dW": r["dW"], k + "_y_infer": ri["y"]})
+
+    # DifferentiableLutN without batch norm, fp32 and Bit
+    for binary in (0, 1):
+        k = f"dl6nobn_14_16_40_b{binary}"
+        idx = wiring(rng, 14, 16)
+        W = np.clip(rng.normal(0.5, 0.25, (16, 64)), 0, 1).astype(np.float32)
+        x = rng.random((14, 40), dtype=np.float32)
+        dy = rng.random((16, 40), dtype=np.float32)
+        r = ref.differentiable_lut6(x, idx, W, batch_norm=False, binary=binary, dy=dy)
+        g.update({k + "_idx": idx, k + "_W": W, k + "_x": x, k + "_dy": dy, k + "_y": r["y"], k + "_dx": r["dx"], k + "_dW": r["dW"]})
+    k = "dl6nobnbit_14_16_70"
+    idx = wiring(rng, 14, 16)
+    W = np.clip(rng.normal(0.5, 0.25, (16, 64)), 0, 1).astype(np.float32)
+    xb = pack_bits(rng.random((14, 70)) > 0.5)
+    dy = rng.random((16, 70), dtype=np.float32)
+    r = ref.differentiable_lut6(xb, idx, W, frames=70, batch_norm=False, dy=dy)
+    g.update({k + "_idx": idx, k + "_W": W, k + "_x": xb, k + "_dy": dy, k + "_y": r["y"], k + "_dx": r["dx"], k + "_dW": r["dW"]})
+
+    # BinaryLutN<6,Bit>: AVX2 and generic branches
+    for (I, O, F) in [(16, 16, 32), (40, 33, 300)]:
+        k = f"bl6_{I}_{O}_{F}"
+        idx = wiring(rng, I, O)
+        table = rng.integers(-2**31, 2**31, (O, 2)).astype(np.int32)
+        xb = pack_bits(rng.random((I, F)) > 0.5)
+        r0 = ref.binary_lut6(xb, idx, table, F, host_simd=False)
+        r1 = ref.binary_lut6(xb, idx, table, F, host_simd=True)
+        assert (r0["y"] == r1["y"]).all()
+        g.update({k + "_idx": idx, k + "_table": table, k + "_x": xb, k + "_y": r0["y"]})
+
+    # StochasticBatchNormalization<float>
+    for (O, F) in [(3, 1), (16, 39), (8, 200)]:
+        k = f"sbn_{O}_{F}"
+        x = rng.random((O, F), dtype=np.float32)
+        dy = rng.random((O, F), dtype=np.float32)
+        rm0 = rng.random(O, dtype=np.float32)
+        rv0 = rng.random(O, dtype=np.float32) + 0.5
+        r = ref.stochastic_bn(x, mode=0, running_mean=rm0, running_var=rv0, dy=dy)
+        r2 = ref.stochastic_bn(x, mode=2, running_mean=rm0, running_var=rv0)
+        g.update({k + "_x": x, k + "_dy": dy, k + "_rm0": rm0, k + "_rv0": rv0, k + "_y": r["y"], k + "_mean": r["mean"],
+                  k + "_rstd": r["rstd"], k + "_rm": r["running_mean"], k + "_rv": r["running_var"], k + "_dx": r["dx"],
+                  k + "_y_re": r2["y"]})
+
+    # A fresh layer's seeded wiring and table, as the reference draws them (layer seed 1)
+    idx, W = ref.init_layer(32, 16, 1)
+    g.update({"init_32_16_s1_idx": idx, "init_32_16_s1_W": W})
+    idx, W = ref.init_layer(784, 1024, 1)
+    g.update({"init_784_1024_s1_idx_head": idx[:8], "init_784_1024_s1_idx_sum": np.array([idx.astype(np.int64).sum()]),
+              "init_784_1024_s1_W_head": W[:2]})
+
+    # 100 Adam steps on a small DifferentiableLut6 layer (fixed x, dy).
+    # "adam": batch norm on, tables N(0.5, 0.25): well conditioned.  "adamnobn": batch norm off, tables
+    # N(0.5, 0.01) as a fresh layer has them.  (Batch norm on WITH N(0.5, 0.01) tables is not a usable
+    # fixture: the per-node variance sits at the 1e-5 clamp, and two builds of the reference that differ
+    # only in FMA contraction already end 1.5e-3 apart after 100 steps.)
+    I, O, F = 24, 16, 64
+    idx = wiring(rng, I, O)
+    x = rng.random((I, F), dtype=np.float32)
+    dy = (rng.random((O, F), dtype=np.float32) - 0.5) * 0.1
+    W = np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32)
+    r = ref.differentiable_lut6_adam(x, idx, W, dy, 100, binary=False)
+    g.update({"adam_idx": idx, "adam_W0": W, "adam_x": x, "adam_dy": dy, "adam_W100": r["W"], "adam_y100": r["y"],
+              "adam_rm100": r["running_mean"], "adam_rv100": r["running_var"]})
+    W = np.clip(rng.normal(0.5, 0.01, (O, 64)), 0, 1).astype(np.float32)
+    r = ref.differentiable_lut6_adam(x, idx, W, dy, 100, batch_norm=False, binary=False)
+    g.update({"adamnobn_W0": W, "adamnobn_W100": r["W"], "adamnobn_y100": r["y"]})
+
+    np.savez_compressed(OUT, **g)
+    print("wrote", OUT, os.path.getsize(OUT), "bytes,", len(g), "arrays")
+
+
+if __name__ == "__main__":
+    main()
