@@ -1,0 +1,127 @@
+// BinaryLut6: bit-packed 6-input LUT inference forward.
+//
+// Semantics of BinaryBrain include/bb/BinaryLutN.h:436-463: for every frame the six input bits form an
+// index (input k -> bit k) into the node's 64-entry truth table.  Frames are processed 32 per word
+// as a multiplexer tree over whole words: 32 two-way selects on x0 between table constants, then
+// 16/8/4/2/1 selects on x1..x5 -- 63 three-input logic ops (LOP3) per 32 frames, against the 448 of
+// the reference kernel's 64 masked AND chains (cuda/BinaryLut6.cu:82-160).
+//
+// Mapping: one warp per output node, one 128-bit load per lane and input row, so a warp reads 512
+// contiguous bytes of each of its six rows per iteration; CTAs of consecutive node groups share a
+// word tile so the tile's input rows stay in L2 for the ~6 nodes that read each of them.
+#include "common.cuh"
+
+namespace bb200 {
+
+constexpr int kBlWarps = 8;
+
+struct BlArgs {
+    const uint32_t *x;
+    uint32_t *y;
+    const int *idx;
+    const int *table;
+    int O, nwords, Tw, groups;
+    long long stride;
+};
+
+// level-1 select masks of a node: v_k = (x0 & A[k]) ^ B[k] equals table bit 2k (x0 = 0) / 2k+1 (x0 = 1)
+__device__ __forceinline__ uint32_t lut6_word(uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3, uint32_t x4, uint32_t x5,
+                                              const uint32_t (&A)[32], const uint32_t (&B)[32])
+{
+    uint32_t v[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) v[k] = (x0 & A[k]) ^ B[k];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) v[k] = (v[2 * k] & ~x1) | (v[2 * k + 1] & x1);
+#pragma unroll
+    for (int k = 0; k < 8; ++k)  v[k] = (v[2 * k] & ~x2) | (v[2 * k + 1] & x2);
+#pragma unroll
+    for (int k = 0; k < 4; ++k)  v[k] = (v[2 * k] & ~x3) | (v[2 * k + 1] & x3);
+#pragma unroll
+    for (int k = 0; k < 2; ++k)  v[k] = (v[2 * k] & ~x4) | (v[2 * k + 1] & x4);
+    return (v[0] & ~x5) | (v[1] & x5);
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(kBlWarps * 32)
+k_binary_lut6(const BlArgs a)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x / a.groups;
+    const int node = (blockIdx.x % a.groups) * kBlWarps + warp;
+    if (node >= a.O) return;
+
+    const uint32_t t0 = (uint32_t)__ldg(a.table + 2 * (size_t)node);
+    const uint32_t t1 = (uint32_t)__ldg(a.table + 2 * (size_t)node + 1);
+    uint32_t A[32], B[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+        const uint32_t t  = (k < 16) ? t0 : t1;
+        const uint32_t lo = (t >> ((2 * k) & 31)) & 1u, hi = (t >> ((2 * k + 1) & 31)) & 1u;
+        B[k] = 0u - lo;
+        A[k] = 0u - (lo ^ hi);
+    }
+    const uint32_t *rows[6];
+#pragma unroll
+    for (int j = 0; j < 6; ++j) rows[j] = a.x + (size_t)__ldg(a.idx + (size_t)node * 6 + j) * a.stride;
+    uint32_t *yrow = a.y + (size_t)node * a.stride;
+
+    const int w_begin = tile * a.Tw;
+    const int w_end   = min(a.nwords, w_begin + a.Tw);
+    if (VEC) {
+        for (int w = w_begin + 4 * lane; w < w_end; w += 128) {
+            uint4 xv[6];
+#pragma unroll
+            for (int j = 0; j < 6; ++j) xv[j] = __ldg(reinterpret_cast<const uint4 *>(rows[j] + w));
+            uint4 o;
+            o.x = lut6_word(xv[0].x, xv[1].x, xv[2].x, xv[3].x, xv[4].x, xv[5].x, A, B);
+            o.y = lut6_word(xv[0].y, xv[1].y, xv[2].y, xv[3].y, xv[4].y, xv[5].y, A, B);
+            o.z = lut6_word(xv[0].z, xv[1].z, xv[2].z, xv[3].z, xv[4].z, xv[5].z, A, B);
+            o.w = lut6_word(xv[0].w, xv[1].w, xv[2].w, xv[3].w, xv[4].w, xv[5].w, A, B);
+            *reinterpret_cast<uint4 *>(yrow + w) = o;
+        }
+    } else {
+        for (int w = w_begin + lane; w < w_end; w += 32) {
+            uint32_t xv[6];
+#pragma unroll
+            for (int j = 0; j < 6; ++j) xv[j] = __ldg(rows[j] + w);
+            yrow[w] = lut6_word(xv[0], xv[1], xv[2], xv[3], xv[4], xv[5], A, B);
+        }
+    }
+}
+
+}   // namespace bb200
+
+using namespace bb200;
+
+extern "C" int bbcu_bit_BinaryLut6_Forward(const int *x, int *y, const int *idx, const int *table, int node_size, int frame_size,
+                                           int frame_stride, bbcu_stream_t stream)
+{
+    BB200_REQUIRE_PTR(x); BB200_REQUIRE_PTR(y); BB200_REQUIRE_PTR(idx); BB200_REQUIRE_PTR(table);
+    BB200_REQUIRE(node_size >= 0 && frame_size >= 0, BBCU_ERR_BAD_SIZE);
+    BB200_REQUIRE((long long)frame_stride * 32 >= frame_size, BBCU_ERR_BAD_STRIDE);
+    if (node_size == 0 || frame_size == 0) return BBCU_OK;
+
+    BlArgs a;
+    a.x = reinterpret_cast<const uint32_t *>(x); a.y = reinterpret_cast<uint32_t *>(y); a.idx = idx; a.table = table;
+    a.O = node_size; a.stride = frame_stride;
+    a.nwords = (frame_size + 31) / 32;
+    a.groups = (node_size + kBlWarps - 1) / kBlWarps;
+    // 128-bit path: rows start 16-byte aligned and whole uint4 groups fit inside the row stride
+    const bool vec = (frame_stride % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
+    if (vec) a.nwords = (a.nwords + 3) & ~3;
+    // word tile: frame_tile() counts in frames; a word is 32 of them
+    const int tf = frame_tile(2LL * node_size, 1, a.groups, a.nwords * 32, 1024 * 32);
+    a.Tw = ((tf / 32 + 127) / 128) * 128;
+    const long long blocks = (long long)((a.nwords + a.Tw - 1) / a.Tw) * a.groups;
+    BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+    if (vec) k_binary_lut6<true><<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
+    else     k_binary_lut6<false><<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
+    return launch_status();
+}
+
+extern "C" int bbcu_bit_BinatyLut6_Forward(const int *x, int *y, const int *idx, const int *table, int node_size, int frame_size,
+                                           int frame_stride, bbcu_stream_t stream)
+{
+    return bbcu_bit_BinaryLut6_Forward(x, y, idx, table, node_size, frame_size, frame_stride, stream);
+}

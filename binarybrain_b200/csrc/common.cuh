@@ -1,0 +1,41 @@
+// Host-side helpers shared by the operator launchers: argument checks, launch-error capture,
+// per-stream scratch memory and the frame-tile heuristic.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stddef.h>
+
+#include "../../include/bbcu_b200.h"
+
+namespace bb200 {
+
+#define BB200_REQUIRE_PTR(p)   do { if ((p) == nullptr) return BBCU_ERR_NULL_POINTER; } while (0)
+#define BB200_REQUIRE(cond, e) do { if (!(cond)) return (e); } while (0)
+#define BB200_CUDA(call)       do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return (int)e_; } while (0)
+
+constexpr int kFramesPerIterHost = 128;   // frames one warp covers per iteration (32 lanes x 4)
+
+inline int launch_status() { return (int)cudaPeekAtLastError(); }
+
+// Device properties read once per device.
+struct DeviceInfo {
+    int sm_count;
+    size_t l2_bytes;
+};
+const DeviceInfo &device_info();
+
+// Scratch memory private to (device, stream): grows on demand through the device heap, is reused by
+// later calls on the same stream and is released by bbcu_LocalHeap_GarbageCollect().  Stream order
+// makes back-to-back calls on one stream safe; different streams get different blocks.
+void *stream_scratch(cudaStream_t stream, size_t bytes);
+
+// Frames handled by one CTA pass.  The gathered input rows of a frame tile (and, in the backward
+// pass, the dx rows it reduces into) have to stay resident in L2 while every output node of the
+// layer consumes them, so the tile narrows as the layer widens; it widens again, up to max_tile,
+// while that still leaves enough CTAs to fill the machine.
+int frame_tile(long long rows_touched, int bits_per_row_frame, int node_groups, int frame_size, int max_tile);
+
+inline cudaStream_t as_stream(bbcu_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+}   // namespace bb200

@@ -1,0 +1,174 @@
+// Device-side core of the 6-input stochastic LUT: the 63-lerp multilinear tree, its reverse
+// pass, and the warp-level reduction of the 64 per-table-entry gradients.
+//
+// A LUT6 node computes  y = sum_{i<64} W[i] * prod_{j<6} (bit_j(i) ? x_j : 1 - x_j)
+// (BinaryBrain include/bb/StochasticOperation.h:95-114).  That multilinear form is evaluated as a
+// binary tree of 63 linear interpolations, one level per input:
+//     level 1: t1[k] = W[2k] + x0 * (W[2k+1] - W[2k])            k < 32
+//     level 2: t2[k] = t1[2k] + x1 * (t1[2k+1] - t1[2k])         k < 16   ... down to y at level 6.
+// The reverse pass walks the same tree: the gradient arriving at a lerp node splits into g*t and
+// g - g*t for its children and contributes g * (b - a) to that level's input gradient; the 32
+// gradients that reach level 1 are the table-entry gradients (times x0 / 1 - x0).
+//
+// Work mapping used by every LUT kernel: one warp owns one output node for a run of frames; in one
+// iteration a warp covers 128 frames and lane l handles frames  base + 32*q + l,  q = 0..3, so every
+// global access of a warp is one fully used 128-byte line and a bit-packed row needs exactly one
+// 32-bit word per q.  Nothing here needs alignment beyond 4 bytes, and frame tails are masked.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace bb200 {
+
+constexpr int kWarpsPerCta   = 8;     // one output node per warp
+constexpr int kFramesPerIter = 128;   // 32 lanes x 4 frames
+constexpr unsigned kFull     = 0xffffffffu;
+
+// Per-node table staged in shared memory as 32 (w, d) pairs: level 1 is t1[k] = fma(x0, d, w).
+__device__ __forceinline__ void stage_table(float2 *tab, const float *__restrict__ W, int node, int lane, int lut_binarize)
+{
+    __syncwarp();
+    float2 v = reinterpret_cast<const float2 *>(W + (size_t)node * 64)[lane];
+    if (lut_binarize) {
+        v.x = v.x > 0.5f ? 1.0f : 0.0f;
+        v.y = v.y > 0.5f ? 1.0f : 0.0f;
+    }
+    tab[lane] = make_float2(v.x, v.y - v.x);
+    __syncwarp();
+}
+
+// Input conditioning of the reference's CPU path (include/bb/DifferentiableLutN.h:779-786):
+// binary mode maps x to 0.5 +/- bias by (x > 0.5), otherwise x is clipped to [0, 1].
+__device__ __forceinline__ float condition_x(float v, int binary, float bias)
+{
+    return binary ? (0.5f + (v > 0.5f ? bias : -bias)) : fminf(1.0f, fmaxf(0.0f, v));
+}
+
+__device__ __forceinline__ float lut6_forward(const float2 *tab, const float (&x)[6])
+{
+    float t[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) { float2 wd = tab[k]; t[k] = fmaf(x[0], wd.y, wd.x); }
+#pragma unroll
+    for (int k = 0; k < 16; ++k) t[k] = fmaf(x[1], t[2 * k + 1] - t[2 * k], t[2 * k]);
+#pragma unroll
+    for (int k = 0; k < 8; ++k)  t[k] = fmaf(x[2], t[2 * k + 1] - t[2 * k], t[2 * k]);
+#pragma unroll
+    for (int k = 0; k < 4; ++k)  t[k] = fmaf(x[3], t[2 * k + 1] - t[2 * k], t[2 * k]);
+#pragma unroll
+    for (int k = 0; k < 2; ++k)  t[k] = fmaf(x[4], t[2 * k + 1] - t[2 * k], t[2 * k]);
+    return fmaf(x[5], t[1] - t[0], t[0]);
+}
+
+// The (b - a) differences of levels 2..6, kept between the forward and the reverse pass.
+struct LerpDiffs {
+    float d2[16], d3[8], d4[4], d5[2], d6;
+};
+
+__device__ __forceinline__ float lut6_forward_keep(const float2 *tab, const float (&x)[6], LerpDiffs &D)
+{
+    float t[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) { float2 wd = tab[k]; t[k] = fmaf(x[0], wd.y, wd.x); }
+#pragma unroll
+    for (int k = 0; k < 16; ++k) { D.d2[k] = t[2 * k + 1] - t[2 * k]; t[k] = fmaf(x[1], D.d2[k], t[2 * k]); }
+#pragma unroll
+    for (int k = 0; k < 8; ++k)  { D.d3[k] = t[2 * k + 1] - t[2 * k]; t[k] = fmaf(x[2], D.d3[k], t[2 * k]); }
+#pragma unroll
+    for (int k = 0; k < 4; ++k)  { D.d4[k] = t[2 * k + 1] - t[2 * k]; t[k] = fmaf(x[3], D.d4[k], t[2 * k]); }
+#pragma unroll
+    for (int k = 0; k < 2; ++k)  { D.d5[k] = t[2 * k + 1] - t[2 * k]; t[k] = fmaf(x[4], D.d5[k], t[2 * k]); }
+    D.d6 = t[1] - t[0];
+    return fmaf(x[5], D.d6, t[0]);
+}
+
+// Reverse pass for one frame: g is the gradient arriving at y.  Adds the 64 table-entry gradients
+// into acc (acc[i] belongs to W[i]) and returns the six input gradients in dx.
+__device__ __forceinline__ void lut6_reverse(const float2 *tab, const float (&x)[6], const LerpDiffs &D, float g,
+                                             float (&acc)[64], float (&dx)[6])
+{
+    float gt[32];
+    dx[5] = g * D.d6;
+    gt[1] = g * x[5];
+    gt[0] = g - gt[1];
+
+    dx[4] = fmaf(gt[1], D.d5[1], gt[0] * D.d5[0]);
+#pragma unroll
+    for (int k = 1; k >= 0; --k) { float hi = gt[k] * x[4]; gt[2 * k] = gt[k] - hi; gt[2 * k + 1] = hi; }
+
+    {
+        float s = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) s = fmaf(gt[k], D.d4[k], s);
+        dx[3] = s;
+    }
+#pragma unroll
+    for (int k = 3; k >= 0; --k) { float hi = gt[k] * x[3]; gt[2 * k] = gt[k] - hi; gt[2 * k + 1] = hi; }
+
+    {
+        float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 8; k += 2) { s0 = fmaf(gt[k], D.d3[k], s0); s1 = fmaf(gt[k + 1], D.d3[k + 1], s1); }
+        dx[2] = s0 + s1;
+    }
+#pragma unroll
+    for (int k = 7; k >= 0; --k) { float hi = gt[k] * x[2]; gt[2 * k] = gt[k] - hi; gt[2 * k + 1] = hi; }
+
+    {
+        float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 16; k += 2) { s0 = fmaf(gt[k], D.d2[k], s0); s1 = fmaf(gt[k + 1], D.d2[k + 1], s1); }
+        dx[1] = s0 + s1;
+    }
+#pragma unroll
+    for (int k = 15; k >= 0; --k) { float hi = gt[k] * x[1]; gt[2 * k] = gt[k] - hi; gt[2 * k + 1] = hi; }
+
+    {
+        float s0 = 0.0f, s1 = 0.0f;
+        const float nx0 = 1.0f - x[0];
+#pragma unroll
+        for (int k = 0; k < 32; k += 2) {
+            s0 = fmaf(gt[k], tab[k].y, s0);
+            s1 = fmaf(gt[k + 1], tab[k + 1].y, s1);
+        }
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+            acc[2 * k]     = fmaf(gt[k], nx0, acc[2 * k]);
+            acc[2 * k + 1] = fmaf(gt[k], x[0], acc[2 * k + 1]);
+        }
+        dx[0] = s0 + s1;
+    }
+}
+
+// Sums acc[i] over the 32 lanes of a warp with a halving butterfly (62 shuffles instead of 64 x 5):
+// afterwards lane l holds the warp totals of entries 2l and 2l+1 in acc[0], acc[1].
+template <int N, int MASK>
+__device__ __forceinline__ void butterfly_step(float (&a)[64], int lane)
+{
+    const bool upper = (lane & MASK) != 0;
+#pragma unroll
+    for (int i = 0; i < N / 2; ++i) {
+        float send = upper ? a[i] : a[i + N / 2];
+        float keep = upper ? a[i + N / 2] : a[i];
+        a[i] = keep + __shfl_xor_sync(kFull, send, MASK);
+    }
+}
+
+__device__ __forceinline__ void warp_reduce_scatter64(float (&a)[64], int lane)
+{
+    butterfly_step<64, 16>(a, lane);
+    butterfly_step<32, 8>(a, lane);
+    butterfly_step<16, 4>(a, lane);
+    butterfly_step<8, 2>(a, lane);
+    butterfly_step<4, 1>(a, lane);
+}
+
+__device__ __forceinline__ double warp_sum(double v)
+{
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(kFull, v, m);
+    return v;
+}
+
+}   // namespace bb200

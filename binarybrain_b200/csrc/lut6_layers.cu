@@ -1,0 +1,686 @@
+// StochasticLut6 and DifferentiableLut6 operators (forward, backward, fp32 and bit-packed inputs).
+//
+// Results follow the reference's CPU branches:
+//   StochasticLutN      include/bb/StochasticLutN.h:512-559 (forward), :668-752 (backward)
+//   DifferentiableLutN  include/bb/DifferentiableLutN.h:747-905 (forward), :1157-1266 (backward)
+// i.e. no gradient zeroing at x in {0,1} and no clamp of the raw LUT value before batch norm, both of
+// which the reference's old CUDA kernels do (cuda/StochasticLut.cuh:191-193,430-470) and its CPU code does not.
+//
+// Schedule: a CTA is 8 warps = 8 consecutive output nodes working on one frame tile; consecutive CTAs
+// walk the node groups of the SAME frame tile, so the input rows of that tile are fetched from HBM once
+// and then hit in L2 for the other ~5 nodes that read them.
+#include "common.cuh"
+#include "lut6_core.cuh"
+
+namespace bb200 {
+
+enum Phase {
+    PH_PLAIN = 0,   // y = clip(raw, 0, 1)           (bit out: raw > 0.5)
+    PH_STATS = 1,   // per-node sum(raw), sum(raw^2) into fp64 sums; fp32 out: raw stored for the normalise pass
+    PH_NORM  = 2,   // y = act((raw - mean) * rstd * gamma + beta)
+};
+
+struct FwdArgs {
+    const void *x;          // float or uint32 rows
+    float      *y;          // fp32 out (may be null in PH_STATS for bit output)
+    uint32_t   *ybits;      // bit out
+    const int  *idx;
+    const float *W;
+    const float *mean;      // PH_NORM
+    const float *rstd;      // PH_NORM: rstd, or the running variance when stat_is_var
+    double     *sums;       // PH_STATS: [O][2]
+    float gamma, beta, bias;
+    int O, F, T;
+    long long xs, ys;       // row strides in elements (floats / words)
+    int lut_binarize, binary, stat_is_var, groups;
+};
+
+template <bool XBIT>
+__device__ __forceinline__ void gather_x(float (&xv)[4][6], const void *x, long long xs, const int (&rows)[6], int base, int lane, int F,
+                                         int binary, float bias)
+{
+    if (XBIT) {
+        const uint32_t *xw = static_cast<const uint32_t *>(x);
+#pragma unroll
+        for (int j = 0; j < 6; ++j) {
+            const uint32_t *row = xw + (size_t)rows[j] * xs + (base >> 5);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t w = (base + 32 * q < F) ? __ldg(row + q) : 0u;
+                xv[q][j] = 0.5f + (((w >> lane) & 1u) ? bias : -bias);
+            }
+        }
+    } else {
+        const float *xf = static_cast<const float *>(x);
+#pragma unroll
+        for (int j = 0; j < 6; ++j) {
+            const float *row = xf + (size_t)rows[j] * xs + base + lane;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float v = (base + 32 * q + lane < F) ? __ldg(row + 32 * q) : 0.0f;
+                xv[q][j] = condition_x(v, binary, bias);
+            }
+        }
+    }
+}
+
+template <bool XBIT, int PHASE, bool YBIT>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+k_lut6_forward(const FwdArgs a)
+{
+    __shared__ float2 s_tab[kWarpsPerCta][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x / a.groups;
+    const int node = (blockIdx.x % a.groups) * kWarpsPerCta + warp;
+    if (node >= a.O) return;
+
+    float2 *tab = s_tab[warp];
+    stage_table(tab, a.W, node, lane, a.lut_binarize);
+    int rows[6];
+#pragma unroll
+    for (int j = 0; j < 6; ++j) rows[j] = __ldg(a.idx + (size_t)node * 6 + j);
+
+    float mean = 0.0f, scale = 0.0f;
+    if (PHASE == PH_NORM) {
+        mean = a.mean[node];
+        float r = a.rstd[node];
+        if (a.stat_is_var) r = 1.0f / sqrtf(r);        // DifferentiableLutN.h:866-868
+        scale = r;
+    }
+    double s1 = 0.0, s2 = 0.0;
+
+    const int f_begin = tile * a.T;
+    const int f_end   = min(a.F, f_begin + a.T);
+    for (int base = f_begin; base < f_end; base += kFramesPerIter) {
+        float xv[4][6];
+        gather_x<XBIT>(xv, a.x, a.xs, rows, base, lane, a.F, a.binary, a.bias);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int f = base + 32 * q + lane;
+            const bool live = f < a.F;
+            float v = lut6_forward(tab, xv[q]);
+            if (PHASE == PH_STATS) {
+                if (live) { s1 += (double)v; s2 += (double)v * (double)v; }
+                if (!YBIT && live) a.y[(size_t)node * a.ys + f] = v;
+            } else {
+                if (PHASE == PH_NORM) {
+                    v = (v - mean) * scale;
+                    v = v * a.gamma + a.beta;
+                }
+                if (YBIT) {
+                    unsigned m = __ballot_sync(kFull, live && v > 0.5f);
+                    if (lane == 0 && base + 32 * q < a.F) a.ybits[(size_t)node * a.ys + ((base >> 5) + q)] = m;
+                } else if (live) {
+                    if (PHASE == PH_NORM && a.binary) v = v > 0.5f ? 1.0f : 0.0f;
+                    else                              v = fmaxf(0.0f, fminf(1.0f, v));
+                    a.y[(size_t)node * a.ys + f] = v;
+                }
+            }
+        }
+    }
+    if (PHASE == PH_STATS) {
+        s1 = warp_sum(s1);
+        s2 = warp_sum(s2);
+        if (lane == 0) {
+            atomicAdd(a.sums + 2 * (size_t)node, s1);
+            atomicAdd(a.sums + 2 * (size_t)node + 1, s2);
+        }
+    }
+}
+
+// mean / var / rstd and the running statistics from the fp64 sums (DifferentiableLutN.h:804-812).
+__global__ void k_bn_finalize(const double *__restrict__ sums, float *mean_out, float *rstd_out, float *running_mean, float *running_var,
+                              float momentum, int O, long long total_frames)
+{
+    int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= O) return;
+    const float rF   = 1.0f / (float)total_frames;
+    const float s1   = (float)sums[2 * (size_t)n];
+    const float s2   = (float)sums[2 * (size_t)n + 1];
+    const float mean = s1 * rF;
+    // one fused multiply-subtract, which is what the reference's build flags make of (s2*rF) - (mean*mean)
+    const float var  = fmaxf(1.0e-5f, fmaf(s2, rF, -(mean * mean)));
+    const float rstd = 1.0f / sqrtf(var);
+    running_mean[n] = running_mean[n] * momentum + mean * (1.0f - momentum);
+    running_var[n]  = running_var[n]  * momentum + var  * (1.0f - momentum);
+    mean_out[n] = mean;
+    rstd_out[n] = rstd;
+}
+
+// In-place normalise of the raw LUT values stored by PH_STATS: one CTA per (node, 4096-frame chunk).
+__global__ void __launch_bounds__(256)
+k_bn_normalize_inplace(float *y, const float *__restrict__ mean_buf, const float *__restrict__ rstd_buf, float gamma, float beta,
+                       int F, long long ys, int binary, int chunks)
+{
+    const int node = blockIdx.x / chunks, chunk = blockIdx.x % chunks;
+    const float mean = mean_buf[node], rstd = rstd_buf[node];
+    float *row = y + (size_t)node * ys;
+    const int f0 = chunk * 4096;
+    const int f1 = min(F, f0 + 4096);
+    const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
+    if (vec) {
+        for (int f = f0 + threadIdx.x * 4; f < f1; f += 1024) {
+            if (f + 3 < f1) {
+                float4 v = *reinterpret_cast<float4 *>(row + f);
+                float o[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float t = (o[i] - mean) * rstd;
+                    t = t * gamma + beta;
+                    o[i] = binary ? (t > 0.5f ? 1.0f : 0.0f) : fmaxf(0.0f, fminf(1.0f, t));
+                }
+                *reinterpret_cast<float4 *>(row + f) = make_float4(o[0], o[1], o[2], o[3]);
+            } else {
+                for (int g = f; g < f1; ++g) {
+                    float t = (row[g] - mean) * rstd;
+                    t = t * gamma + beta;
+                    row[g] = binary ? (t > 0.5f ? 1.0f : 0.0f) : fmaxf(0.0f, fminf(1.0f, t));
+                }
+            }
+        }
+    } else {
+        for (int f = f0 + threadIdx.x; f < f1; f += 256) {
+            float t = (row[f] - mean) * rstd;
+            t = t * gamma + beta;
+            row[f] = binary ? (t > 0.5f ? 1.0f : 0.0f) : fmaxf(0.0f, fminf(1.0f, t));
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward
+// ---------------------------------------------------------------------------------------------
+struct BwdArgs {
+    const void *x;
+    const float *dy;
+    float *dx;
+    const int *idx;
+    const float *W;
+    float *dW;
+    const float *mean, *rstd;     // batch norm only
+    const float *dmean, *dvar;    // batch norm apply pass
+    double *sums;                 // batch norm stats pass: [O][2] = (dstd, dmeanx)
+    float gamma, beta, bias, rF;
+    int O, F, T;
+    long long xs, dys, dxs;
+    int lut_binarize, binary, groups;
+};
+
+// Batch-norm statistics of the backward pass (DifferentiableLutN.h:1190-1220): the hard-tanh mask is
+// re-derived from the recomputed forward value; dstd = sum -(g*dy*(raw-mean)*rstd^2), dmeanx = sum -(g*dy*rstd).
+template <bool XBIT>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+k_lut6_backward_stats(const BwdArgs a)
+{
+    __shared__ float2 s_tab[kWarpsPerCta][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x / a.groups;
+    const int node = (blockIdx.x % a.groups) * kWarpsPerCta + warp;
+    if (node >= a.O) return;
+    float2 *tab = s_tab[warp];
+    stage_table(tab, a.W, node, lane, a.lut_binarize);
+    int rows[6];
+#pragma unroll
+    for (int j = 0; j < 6; ++j) rows[j] = __ldg(a.idx + (size_t)node * 6 + j);
+    const float mean = a.mean[node], rstd = a.rstd[node], rstd2 = rstd * rstd;
+    double dstd = 0.0, dmeanx = 0.0;
+
+    const int f_begin = tile * a.T;
+    const int f_end   = min(a.F, f_begin + a.T);
+    for (int base = f_begin; base < f_end; base += kFramesPerIter) {
+        float xv[4][6];
+        gather_x<XBIT>(xv, a.x, a.xs, rows, base, lane, a.F, a.binary, a.bias);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int f = base + 32 * q + lane;
+            if (f < a.F) {
+                float v = lut6_forward(tab, xv[q]);
+                float tanh_x = ((v - mean) * rstd) * a.gamma + a.beta;
+                float g = __ldg(a.dy + (size_t)node * a.dys + f);
+                if (tanh_x <= 0.0f || tanh_x >= 1.0f) g = 0.0f;
+                float dxn = a.gamma * g;
+                dstd   -= (double)(dxn * (v - mean) * rstd2);
+                dmeanx -= (double)(dxn * rstd);
+            }
+        }
+    }
+    dstd = warp_sum(dstd);
+    dmeanx = warp_sum(dmeanx);
+    if (lane == 0) {
+        atomicAdd(a.sums + 2 * (size_t)node, dstd);
+        atomicAdd(a.sums + 2 * (size_t)node + 1, dmeanx);
+    }
+}
+
+__global__ void k_bn_backward_finalize(const double *__restrict__ sums, const float *__restrict__ mean_buf, const float *__restrict__ rstd_buf,
+                                       float *dmean_out, float *dvar_out, int O, long long total_frames)
+{
+    int n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= O) return;
+    const float rF = 1.0f / (float)total_frames;
+    const float dstd = (float)sums[2 * (size_t)n], dmeanx = (float)sums[2 * (size_t)n + 1];
+    const float dvar = dstd * rstd_buf[n];
+    dvar_out[n]  = dvar;
+    dmean_out[n] = (dmeanx - (mean_buf[n] * dvar)) * rF;
+}
+
+// dW / dx.  BN = true folds the batch-norm backward (DifferentiableLutN.h:1225-1258) in front of the LUT's.
+// dx rows must be zero on entry: every node adds its six input gradients with red.global.add.f32, which
+// resolve in L2 where the tile's dx rows are resident.
+template <bool XBIT, bool BN>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, 1)
+k_lut6_backward(const BwdArgs a)
+{
+    __shared__ float2 s_tab[kWarpsPerCta][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x / a.groups;
+    const int node = (blockIdx.x % a.groups) * kWarpsPerCta + warp;
+    if (node >= a.O) return;
+    float2 *tab = s_tab[warp];
+    stage_table(tab, a.W, node, lane, a.lut_binarize);
+    int rows[6];
+#pragma unroll
+    for (int j = 0; j < 6; ++j) rows[j] = __ldg(a.idx + (size_t)node * 6 + j);
+
+    float mean = 0.0f, rstd = 0.0f, dmean = 0.0f, dvar_rF = 0.0f;
+    if (BN) {
+        mean = a.mean[node];
+        rstd = a.rstd[node];
+        dmean = a.dmean[node];
+        dvar_rF = a.dvar[node];
+    }
+    float acc[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+
+    const int f_begin = tile * a.T;
+    const int f_end   = min(a.F, f_begin + a.T);
+    for (int base = f_begin; base < f_end; base += kFramesPerIter) {
+        float xv[4][6];
+        gather_x<XBIT>(xv, a.x, a.xs, rows, base, lane, a.F, a.binary, a.bias);
+        float dyv[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int f = base + 32 * q + lane;
+            dyv[q] = (f < a.F) ? __ldg(a.dy + (size_t)node * a.dys + f) : 0.0f;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int f = base + 32 * q + lane;
+            LerpDiffs D;
+            float v = lut6_forward_keep(tab, xv[q], D);
+            float g = dyv[q];
+            if (BN) {
+                float tanh_x = ((v - mean) * rstd) * a.gamma + a.beta;
+                if (tanh_x <= 0.0f || tanh_x >= 1.0f) g = 0.0f;
+                float dxc = (g * a.gamma) * rstd;
+                g = dxc + dmean + (v * dvar_rF * a.rF);
+                if (f >= a.F) g = 0.0f;
+            }
+            float dxv[6];
+            lut6_reverse(tab, xv[q], D, g, acc, dxv);
+            if (f < a.F) {
+#pragma unroll
+                for (int j = 0; j < 6; ++j) atomicAdd(a.dx + (size_t)rows[j] * a.dxs + f, dxv[j]);
+            }
+        }
+    }
+    warp_reduce_scatter64(acc, lane);
+    float *dst = a.dW + (size_t)node * 64 + 2 * lane;
+    atomicAdd(dst, acc[0]);
+    atomicAdd(dst + 1, acc[1]);
+}
+
+// ---------------------------------------------------------------------------------------------
+// launchers
+// ---------------------------------------------------------------------------------------------
+static int check_common(const void *x, const void *y, const int *idx, const float *W, int O, int F, long long stride)
+{
+    BB200_REQUIRE_PTR(x); BB200_REQUIRE_PTR(y); BB200_REQUIRE_PTR(idx); BB200_REQUIRE_PTR(W);
+    BB200_REQUIRE(O >= 0 && F >= 0, BBCU_ERR_BAD_SIZE);
+    BB200_REQUIRE(stride >= 0, BBCU_ERR_BAD_STRIDE);
+    BB200_REQUIRE((reinterpret_cast<uintptr_t>(W) & 7) == 0, BBCU_ERR_BAD_STRIDE);
+    return BBCU_OK;
+}
+
+template <bool XBIT, int PHASE, bool YBIT>
+static int launch_forward(FwdArgs a, int max_tile, cudaStream_t st)
+{
+    if (a.O == 0 || a.F == 0) return BBCU_OK;
+    a.groups = (a.O + kWarpsPerCta - 1) / kWarpsPerCta;
+    a.T = frame_tile(6LL * a.O, XBIT ? 1 : 32, a.groups, a.F, max_tile);
+    const long long tiles = (a.F + a.T - 1) / a.T;
+    const long long blocks = tiles * a.groups;
+    BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+    k_lut6_forward<XBIT, PHASE, YBIT><<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(a);
+    return launch_status();
+}
+
+template <bool XBIT>
+static int forward_plain(const void *x, float *y, uint32_t *ybits, const int *idx, const float *W, int O, int F, long long xs, long long ys,
+                         int binary, int lut_binarize, float bias, cudaStream_t st)
+{
+    FwdArgs a = {};
+    a.x = x; a.y = y; a.ybits = ybits; a.idx = idx; a.W = W; a.bias = bias;
+    a.O = O; a.F = F; a.xs = xs; a.ys = ys; a.lut_binarize = lut_binarize; a.binary = binary;
+    if (ybits) return launch_forward<XBIT, PH_PLAIN, true>(a, 2048, st);
+    return launch_forward<XBIT, PH_PLAIN, false>(a, 2048, st);
+}
+
+template <bool XBIT>
+static int backward_common(BwdArgs a, bool bn, long long total_frames, float *dmean_out, float *dvar_out, const double *ext_sums,
+                           int I, cudaStream_t st)
+{
+    // dx starts from zero (the reference's CPU path: dx_buf.FillZero(), DifferentiableLutN.h:1159)
+    if (I > 0 && a.dxs > 0) BB200_CUDA(cudaMemsetAsync(a.dx, 0, sizeof(float) * (size_t)I * a.dxs, st));
+    if (a.O == 0 || a.F == 0) return BBCU_OK;
+    a.groups = (a.O + kWarpsPerCta - 1) / kWarpsPerCta;
+    const long long rows = (long long)(I < 6LL * a.O ? I : 6LL * a.O);
+    a.T = frame_tile(rows, (XBIT ? 1 : 32) + 32, a.groups, a.F, 1024);
+    const long long tiles = (a.F + a.T - 1) / a.T;
+    const long long blocks = tiles * a.groups;
+    BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+    a.rF = 1.0f / (float)total_frames;
+    if (bn) {
+        if (ext_sums == nullptr) {
+            double *sums = static_cast<double *>(stream_scratch(st, sizeof(double) * 2 * (size_t)a.O));
+            BB200_REQUIRE(sums != nullptr, BBCU_ERR_NO_MEMORY);
+            BB200_CUDA(cudaMemsetAsync(sums, 0, sizeof(double) * 2 * (size_t)a.O, st));
+            a.sums = sums;
+            k_lut6_backward_stats<XBIT><<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(a);
+            BB200_CUDA(cudaPeekAtLastError());
+            ext_sums = sums;
+        }
+        k_bn_backward_finalize<<<(a.O + 255) / 256, 256, 0, st>>>(ext_sums, a.mean, a.rstd, dmean_out, dvar_out, a.O, total_frames);
+        BB200_CUDA(cudaPeekAtLastError());
+        a.dmean = dmean_out; a.dvar = dvar_out;
+        k_lut6_backward<XBIT, true><<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(a);
+    } else {
+        k_lut6_backward<XBIT, false><<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(a);
+    }
+    return launch_status();
+}
+
+}   // namespace bb200
+
+using namespace bb200;
+
+// ------------------------------------------------------------------------------------------- StochasticLut6
+extern "C" int bbcu_fp32_StochasticLut6_Forward(const float *x, float *y, const int *idx, const float *W, int node_size, int frame_size,
+                                                int frame_stride, int input_binary, int lut_binarize, float unbinarize_bias, bbcu_stream_t stream)
+{
+    int rc = check_common(x, y, idx, W, node_size, frame_size, frame_stride);
+    if (rc) return rc;
+    BB200_REQUIRE(frame_stride >= frame_size, BBCU_ERR_BAD_STRIDE);
+    return forward_plain<false>(x, y, nullptr, idx, W, node_size, frame_size, frame_stride, frame_stride, input_binary, lut_binarize,
+                                unbinarize_bias, as_stream(stream));
+}
+
+extern "C" int bbcu_bit_fp32_StochasticLut6_Forward(const int *x, float *y, const int *idx, const float *W, int node_size, int frame_size,
+                                                    int frame_stride, int bin_frame_stride, int lut_binarize, float unbinarize_bias,
+                                                    bbcu_stream_t stream)
+{
+    int rc = check_common(x, y, idx, W, node_size, frame_size, frame_stride);
+    if (rc) return rc;
+    BB200_REQUIRE(frame_stride >= frame_size && (long long)bin_frame_stride * 32 >= frame_size, BBCU_ERR_BAD_STRIDE);
+    return forward_plain<true>(x, y, nullptr, idx, W, node_size, frame_size, bin_frame_stride, frame_stride, 1, lut_binarize,
+                               unbinarize_bias, as_stream(stream));
+}
+
+extern "C" int bbcu_bit_bit_fp32_StochasticLut6_Forward(const int *x, int *y, const int *idx, const float *W, int node_size, int frame_size,
+                                                        int frame_stride, int lut_binarize, float unbinarize_bias, bbcu_stream_t stream)
+{
+    int rc = check_common(x, y, idx, W, node_size, frame_size, frame_stride);
+    if (rc) return rc;
+    BB200_REQUIRE((long long)frame_stride * 32 >= frame_size, BBCU_ERR_BAD_STRIDE);
+    return forward_plain<true>(x, nullptr, reinterpret_cast<uint32_t *>(y), idx, W, node_size, frame_size, frame_stride, frame_stride, 1,
+                               lut_binarize, unbinarize_bias, as_stream(stream));
+}
+
+extern "C" int bbcu_fp32_StochasticLut6_Backward(const float *x, const float *dy, float *dx, float *dx_tmp, const int *idx, const int *rev,
+                                                 const float *W, float *dW, int reverse_index_stride, int input_node_size, int output_node_size,
+                                                 int frame_size, int frame_stride, int tmp_frame_size, int tmp_frame_stride,
+                                                 int input_binary, int lut_binarize, float unbinarize_bias, bbcu_stream_t stream)
+{
+    (void)dx_tmp; (void)rev; (void)reverse_index_stride; (void)tmp_frame_size; (void)tmp_frame_stride;
+    int rc = check_common(x, dx, idx, W, output_node_size, frame_size, frame_stride);
+    if (rc) return rc;
+    BB200_REQUIRE_PTR(dy); BB200_REQUIRE_PTR(dW);
+    BB200_REQUIRE(input_node_size >= 0, BBCU_ERR_BAD_SIZE);
+    BB200_REQUIRE(frame_stride >= frame_size, BBCU_ERR_BAD_STRIDE);
+    BwdArgs a = {};
+    a.x = x; a.dy = dy; a.dx = dx; a.idx = idx; a.W = W; a.dW = dW; a.bias = unbinarize_bias;
+    a.O = output_node_size; a.F = frame_size; a.xs = frame_stride; a.dys = frame_stride; a.dxs = frame_stride;
+    a.lut_binarize = lut_binarize; a.binary = input_binary;
+    return backward_common<false>(a, false, frame_size > 0 ? frame_size : 1, nullptr, nullptr, nullptr, input_node_size, as_stream(stream));
+}
+
+extern "C" int bbcu_bit_fp32_StochasticLut6_Backward(const int *x, const float *dy, float *dx, float *dx_tmp, const int *idx, const int *rev,
+                                                     const float *W, float *dW, int reverse_index_stride, int input_node_size,
+                                                     int output_node_size, int frame_size, int frame_stride, int bin_frame_stride,
+                                                     int tmp_frame_size, int tmp_frame_stride, int lut_binarize, float unbinarize_bias,
+                                                     bbcu_stream_t stream)
+{
+    (void)dx_tmp; (void)rev; (void)reverse_index_stride; (void)tmp_frame_size; (void)tmp_frame_stride;
+    int rc = check_common(x, dx, idx, W, output_node_size, frame_size, frame_stride);
+    if (rc) return rc;
+    BB200_REQUIRE_PTR(dy); BB200_REQUIRE_PTR(dW);
+    BB200_REQUIRE(input_node_size >= 0, BBCU_ERR_BAD_SIZE);
+    BB200_REQUIRE(frame_stride >= frame_size && (long long)bin_frame_stride * 32 >= frame_size, BBCU_ERR_BAD_STRIDE);
+    BwdArgs a = {};
+    a.x = x; a.dy = dy; a.dx = dx; a.idx = idx; a.W = W; a.dW = dW; a.bias = unbinarize_bias;
+    a.O = output_node_size; a.F = frame_size; a.xs = bin_frame_stride; a.dys = frame_stride; a.dxs = frame_stride;
+    a.lut_binarize = lut_binarize; a.binary = 1;
+    return backward_common<true>(a, false, frame_size > 0 ? frame_size : 1, nullptr, nullptr, nullptr, input_node_size, as_stream(stream));
+}
+
+// ------------------------------------------------------------------------------------------- DifferentiableLut6
+static int dl6_finalize_and_normalize(float *y, const double *sums, float *mean, float *rstd, float *rmean, float *rvar,
+                                      float gamma, float beta, float momentum, int O, int F, long long ys, long long total_frames,
+                                      int binary, cudaStream_t st)
+{
+    if (O == 0) return BBCU_OK;
+    k_bn_finalize<<<(O + 255) / 256, 256, 0, st>>>(sums, mean, rstd, rmean, rvar, momentum, O, total_frames);
+    BB200_CUDA(cudaPeekAtLastError());
+    if (y != nullptr && F > 0) {
+        const int chunks = (F + 4095) / 4096;
+        const long long blocks = (long long)O * chunks;
+        BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+        k_bn_normalize_inplace<<<(unsigned)blocks, 256, 0, st>>>(y, mean, rstd, gamma, beta, F, ys, binary, chunks);
+    }
+    return launch_status();
+}
+
+extern "C" int bbcu_fp32_DifferentiableLut6_ForwardStats(const float *x, float *y, const int *idx, const float *W, double *dev_sums,
+                                                         float unbinarize_bias, int node_size, int frame_size, int frame_stride,
+                                                         int lut_binarize, int binary_mode, bbcu_stream_t stream)
+{
+    int rc = check_common(x, y, idx, W, node_size, frame_size, frame_stride);
+    if (rc) return rc;
+    BB200_REQUIRE_PTR(dev_sums);
+    BB200_REQUIRE(frame_stride >= frame_size, BBCU_ERR_BAD_STRIDE);
+    cudaStream_t st = as_stream(stream);
+    BB200_CUDA(cudaMemsetAsync(dev_sums, 0, sizeof(double) * 2 * (size_t)node_size, st));
+    FwdArgs a = {};
+    a.x = x; a.y = y; a.idx = idx; a.W = W; a.sums = dev_sums; a.bias = unbinarize_bias;
+    a.O = node_size; a.F = frame_size; a.xs = frame_stride; a.ys = frame_stride; a.lut_binarize = lut_binarize; a.binary = binary_mode;
+    return launch_forward<false, PH_STATS, false>(a, 2048, st);
+}
+
+extern "C" int bbcu_fp32_DifferentiableLut6_ForwardNormalize(float *y, const double *dev_sums, float *mean, float *rstd, float *rmean,
+                                                             float *rvar, float gamma, float beta, float momentum, int node_size,
+                                                             int frame_size, int frame_stride, long long total_frame_size, int binary_mode,
+                                                             bbcu_stream_t stream)
+{
+    BB200_REQUIRE_PTR(y); BB200_REQUIRE_PTR(dev_sums); BB200_REQUIRE_PTR(mean); BB200_REQUIRE_PTR(rstd); BB200_REQUIRE_PTR(rmean); BB200_REQUIRE_PTR(rvar);
+    BB200_REQUIRE(node_size >= 0 && frame_size >= 0 && total_frame_size >= frame_size && total_frame_size > 0, BBCU_ERR_BAD_SIZE);
+    BB200_REQUIRE(frame_stride >= frame_size, BBCU_ERR_BAD_STRIDE);
+    return dl6_finalize_and_normalize(y, dev_sums, mean, rstd, rmean, rvar, gamma, beta, momentum, node_size, frame_size, frame_stride,
+                                      total_frame_size, binary_mode, as_stream(stream));
+}
+
+extern "C" int bbcu_fp32_DifferentiableLut6_ForwardTraining(const float *x, float *y, const int *idx, const float *W, float *mean, float *rstd,
+                                                            float *rmean, float *rvar, float gamma, float beta, float momentum,
+                                                            float unbinarize_bias, int node_size, int frame_size, int frame_stride,
+                                                            int lut_binarize, int binary_mode, bbcu_stream_t stream)
+{
+    BB200_REQUIRE_PTR(mean); BB200_REQUIRE_PTR(rstd); BB200_REQUIRE_PTR(rmean); BB200_REQUIRE_PTR(rvar);
+    BB200_REQUIRE(frame_size > 0 || node_size == 0, BBCU_ERR_BAD_SIZE);
+    if (node_size == 0) return BBCU_OK;
+    cudaStream_t st = as_stream(stream);
+    double *sums = static_cast<double *>(stream_scratch(st, sizeof(double) * 2 * (size_t)(node_size > 0 ? node_size : 0)));
+    BB200_REQUIRE(sums != nullptr, BBCU_ERR_NO_MEMORY);
+    int rc = bbcu_fp32_DifferentiableLut6_ForwardStats(x, y, idx, W, sums, unbinarize_bias, node_size, frame_size, frame_stride, lut_binarize,
+                                                       binary_mode, stream);
+    if (rc) return rc;
+    return dl6_finalize_and_normalize(y, sums, mean, rstd, rmean, rvar, gamma, beta, momentum, node_size, frame_size, frame_stride, frame_size,
+                                      binary_mode, st);
+}
+
+extern "C" int bbcu_bit_fp32_DifferentiableLut6_ForwardTraining(const int *x, int *y, const int *idx, const float *W, float *mean, float *rstd,
+                                                                float *rmean, float *rvar, float gamma, float beta, float momentum,
+                                                                float unbinarize_bias, int node_size, int frame_size, int frame_stride,
+                                                                int lut_binarize, bbcu_stream_t stream)
+{
+    int rc = check_common(x, y, idx, W, node_size, frame_size, frame_stride);
+    if (rc) return rc;
+    BB200_REQUIRE_PTR(mean); BB200_REQUIRE_PTR(rstd); BB200_REQUIRE_PTR(rmean); BB200_REQUIRE_PTR(rvar);
+    BB200_REQUIRE(frame_size > 0 || node_size == 0, BBCU_ERR_BAD_SIZE);
+    BB200_REQUIRE((long long)frame_stride * 32 >= frame_size, BBCU_ERR_BAD_STRIDE);
+    if (node_size == 0) return BBCU_OK;
+    cudaStream_t st = as_stream(stream);
+    double *sums = static_cast<double *>(stream_scratch(st, sizeof(double) * 2 * (size_t)node_size));
+    BB200_REQUIRE(sums != nullptr, BBCU_ERR_NO_MEMORY);
+    BB200_CUDA(cudaMemsetAsync(sums, 0, sizeof(double) * 2 * (size_t)node_size, st));
+    FwdArgs a = {};
+    a.x = x; a.ybits = reinterpret_cast<uint32_t *>(y); a.idx = idx; a.W = W; a.sums = sums; a.bias = unbinarize_bias;
+    a.gamma = gamma; a.beta = beta;
+    a.O = node_size; a.F = frame_size; a.xs = frame_stride; a.ys = frame_stride; a.lut_binarize = lut_binarize; a.binary = 1;
+    rc = launch_forward<true, PH_STATS, true>(a, 2048, st);
+    if (rc) return rc;
+    rc = dl6_finalize_and_normalize(nullptr, sums, mean, rstd, rmean, rvar, gamma, beta, momentum, node_size, frame_size, frame_stride,
+                                    frame_size, 1, st);
+    if (rc) return rc;
+    a.mean = mean; a.rstd = rstd; a.stat_is_var = 0;
+    return launch_forward<true, PH_NORM, true>(a, 2048, st);
+}
+
+extern "C" int bbcu_fp32_DifferentiableLut6_ForwardInference(const float *x, float *y, const int *idx, const float *W, const float *rmean,
+                                                             const float *rvar, float gamma, float beta, float unbinarize_bias, int node_size,
+                                                             int frame_size, int frame_stride, int lut_binarize, int binary_mode,
+                                                             bbcu_stream_t stream)
+{
+    int rc = check_common(x, y, idx, W, node_size, frame_size, frame_stride);
+    if (rc) return rc;
+    BB200_REQUIRE_PTR(rmean); BB200_REQUIRE_PTR(rvar);
+    BB200_REQUIRE(frame_stride >= frame_size, BBCU_ERR_BAD_STRIDE);
+    FwdArgs a = {};
+    a.x = x; a.y = y; a.idx = idx; a.W = W; a.mean = rmean; a.rstd = rvar; a.stat_is_var = 1; a.bias = unbinarize_bias;
+    a.gamma = gamma; a.beta = beta;
+    a.O = node_size; a.F = frame_size; a.xs = frame_stride; a.ys = frame_stride; a.lut_binarize = lut_binarize; a.binary = binary_mode;
+    return launch_forward<false, PH_NORM, false>(a, 2048, as_stream(stream));
+}
+
+extern "C" int bbcu_bit_fp32_DifferentiableLut6_ForwardInference(const int *x, int *y, const int *idx, const float *W, const float *rmean,
+                                                                 const float *rvar, float gamma, float beta, float unbinarize_bias,
+                                                                 int node_size, int frame_size, int frame_stride, int lut_binarize,
+                                                                 bbcu_stream_t stream)
+{
+    int rc = check_common(x, y, idx, W, node_size, frame_size, frame_stride);
+    if (rc) return rc;
+    BB200_REQUIRE_PTR(rmean); BB200_REQUIRE_PTR(rvar);
+    BB200_REQUIRE((long long)frame_stride * 32 >= frame_size, BBCU_ERR_BAD_STRIDE);
+    FwdArgs a = {};
+    a.x = x; a.ybits = reinterpret_cast<uint32_t *>(y); a.idx = idx; a.W = W; a.mean = rmean; a.rstd = rvar; a.stat_is_var = 1;
+    a.bias = unbinarize_bias; a.gamma = gamma; a.beta = beta;
+    a.O = node_size; a.F = frame_size; a.xs = frame_stride; a.ys = frame_stride; a.lut_binarize = lut_binarize; a.binary = 1;
+    return launch_forward<true, PH_NORM, true>(a, 2048, as_stream(stream));
+}
+
+static int dl6_backward_args(BwdArgs &a, const void *x, const float *dy, float *dx, const int *idx, const float *W, float *dW,
+                             const float *mean, const float *rstd, float gamma, float beta, float bias, int I, int O, int F,
+                             long long xs, long long fs, int lut_binarize, int binary)
+{
+    int rc = check_common(x, dx, idx, W, O, F, fs);
+    if (rc) return rc;
+    BB200_REQUIRE_PTR(dy); BB200_REQUIRE_PTR(dW); BB200_REQUIRE_PTR(mean); BB200_REQUIRE_PTR(rstd);
+    BB200_REQUIRE(I >= 0, BBCU_ERR_BAD_SIZE);
+    BB200_REQUIRE(fs >= F, BBCU_ERR_BAD_STRIDE);
+    a = BwdArgs{};
+    a.x = x; a.dy = dy; a.dx = dx; a.idx = idx; a.W = W; a.dW = dW; a.mean = mean; a.rstd = rstd;
+    a.gamma = gamma; a.beta = beta; a.bias = bias;
+    a.O = O; a.F = F; a.xs = xs; a.dys = fs; a.dxs = fs; a.lut_binarize = lut_binarize; a.binary = binary;
+    return BBCU_OK;
+}
+
+extern "C" int bbcu_fp32_DifferentiableLut6_Backward(const float *x, const float *dy, float *dx, float *dx_tmp, const int *idx, const int *rev,
+                                                     const float *W, float *dW, const float *mean, const float *rstd, float *dmean_tmp,
+                                                     float *dvar_tmp, float gamma, float beta, float unbinarize_bias, int reverse_index_stride,
+                                                     int input_node_size, int output_node_size, int frame_size, int frame_stride,
+                                                     int tmp_frame_size, int tmp_frame_stride, int lut_binarize, int binary_mode,
+                                                     bbcu_stream_t stream)
+{
+    (void)dx_tmp; (void)rev; (void)reverse_index_stride; (void)tmp_frame_size; (void)tmp_frame_stride;
+    BB200_REQUIRE_PTR(dmean_tmp); BB200_REQUIRE_PTR(dvar_tmp);
+    BwdArgs a;
+    int rc = dl6_backward_args(a, x, dy, dx, idx, W, dW, mean, rstd, gamma, beta, unbinarize_bias, input_node_size, output_node_size, frame_size,
+                               frame_stride, frame_stride, lut_binarize, binary_mode);
+    if (rc) return rc;
+    return backward_common<false>(a, true, frame_size > 0 ? frame_size : 1, dmean_tmp, dvar_tmp, nullptr, input_node_size, as_stream(stream));
+}
+
+extern "C" int bbcu_bit_fp32_DifferentiableLut6_Backward(const int *x, const float *dy, float *dx, float *dx_tmp, const int *idx, const int *rev,
+                                                         const float *W, float *dW, const float *mean, const float *rstd, float *dmean_tmp,
+                                                         float *dvar_tmp, float gamma, float beta, float unbinarize_bias,
+                                                         int reverse_index_stride, int input_node_size, int output_node_size, int frame_size,
+                                                         int frame_stride, int x_frame_stride, int tmp_frame_size, int tmp_frame_stride,
+                                                         int lut_binarize, bbcu_stream_t stream)
+{
+    (void)dx_tmp; (void)rev; (void)reverse_index_stride; (void)tmp_frame_size; (void)tmp_frame_stride;
+    BB200_REQUIRE_PTR(dmean_tmp); BB200_REQUIRE_PTR(dvar_tmp);
+    BB200_REQUIRE((long long)x_frame_stride * 32 >= frame_size, BBCU_ERR_BAD_STRIDE);
+    BwdArgs a;
+    int rc = dl6_backward_args(a, x, dy, dx, idx, W, dW, mean, rstd, gamma, beta, unbinarize_bias, input_node_size, output_node_size, frame_size,
+                               x_frame_stride, frame_stride, lut_binarize, 1);
+    if (rc) return rc;
+    return backward_common<true>(a, true, frame_size > 0 ? frame_size : 1, dmean_tmp, dvar_tmp, nullptr, input_node_size, as_stream(stream));
+}
+
+extern "C" int bbcu_fp32_DifferentiableLut6_BackwardStats(const float *x, const float *dy, const int *idx, const float *W, const float *mean,
+                                                          const float *rstd, double *dev_sums, float gamma, float beta, float unbinarize_bias,
+                                                          int node_size, int frame_size, int frame_stride, int lut_binarize, int binary_mode,
+                                                          bbcu_stream_t stream)
+{
+    int rc = check_common(x, dev_sums, idx, W, node_size, frame_size, frame_stride);
+    if (rc) return rc;
+    BB200_REQUIRE_PTR(dy); BB200_REQUIRE_PTR(mean); BB200_REQUIRE_PTR(rstd);
+    BB200_REQUIRE(frame_stride >= frame_size, BBCU_ERR_BAD_STRIDE);
+    cudaStream_t st = as_stream(stream);
+    BB200_CUDA(cudaMemsetAsync(dev_sums, 0, sizeof(double) * 2 * (size_t)node_size, st));
+    if (node_size == 0 || frame_size == 0) return BBCU_OK;
+    BwdArgs a = {};
+    a.x = x; a.dy = dy; a.idx = idx; a.W = W; a.mean = mean; a.rstd = rstd; a.sums = dev_sums;
+    a.gamma = gamma; a.beta = beta; a.bias = unbinarize_bias;
+    a.O = node_size; a.F = frame_size; a.xs = frame_stride; a.dys = frame_stride; a.lut_binarize = lut_binarize; a.binary = binary_mode;
+    a.groups = (a.O + kWarpsPerCta - 1) / kWarpsPerCta;
+    a.T = frame_tile(6LL * a.O, 32, a.groups, a.F, 2048);
+    const long long blocks = (long long)((a.F + a.T - 1) / a.T) * a.groups;
+    BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+    k_lut6_backward_stats<false><<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(a);
+    return launch_status();
+}
+
+extern "C" int bbcu_fp32_DifferentiableLut6_BackwardApply(const float *x, const float *dy, float *dx, const int *idx, const float *W, float *dW,
+                                                          const float *mean, const float *rstd, const double *dev_sums, float *dmean_tmp,
+                                                          float *dvar_tmp, float gamma, float beta, float unbinarize_bias, int input_node_size,
+                                                          int output_node_size, int frame_size, int frame_stride, long long total_frame_size,
+                                                          int lut_binarize, int binary_mode, bbcu_stream_t stream)
+{
+    BB200_REQUIRE_PTR(dev_sums); BB200_REQUIRE_PTR(dmean_tmp); BB200_REQUIRE_PTR(dvar_tmp);
+    BB200_REQUIRE(total_frame_size >= frame_size && total_frame_size > 0, BBCU_ERR_BAD_SIZE);
+    BwdArgs a;
+    int rc = dl6_backward_args(a, x, dy, dx, idx, W, dW, mean, rstd, gamma, beta, unbinarize_bias, input_node_size, output_node_size, frame_size,
+                               frame_stride, frame_stride, lut_binarize, binary_mode);
+    if (rc) return rc;
+    return backward_common<false>(a, true, total_frame_size, dmean_tmp, dvar_tmp, dev_sums, input_node_size, as_stream(stream));
+}

@@ -1,0 +1,219 @@
+"""The bbcu_* operators on torch CUDA tensors.
+
+torch only provides device memory and the current stream here; every operator is one call through
+the C ABI (binarybrain_b200.abi).  Frame buffers are 2-D tensors ``[nodes, frame_stride]``: fp32
+buffers hold one float per frame, bit buffers (dtype int32) 32 frames per element, LSB first -- the
+FrameBuffer layout of the reference (include/bb/FrameBuffer.h:28-46).  ``frames`` is the number of
+valid frames; the stride is taken from the tensor.
+"""
+import torch
+
+from . import abi
+
+BIAS = 0.25   # unbinarize_bias of the reference's layers (include/bb/DifferentiableLutN.h:63)
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def _chk(t, dtype, name):
+    if not t.is_cuda:
+        raise ValueError(f"{name}: expected a CUDA tensor (the bbcu_* operators have no CPU path)")
+    if t.dtype != dtype:
+        raise ValueError(f"{name}: expected dtype {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name}: expected a contiguous tensor")
+    return t
+
+
+def fp32_stride(frames):
+    """Row stride in floats: rows padded to 32 bytes (include/bb/FrameBuffer.h:414-417)."""
+    return (frames + 7) // 8 * 8
+
+
+def bit_stride(frames):
+    """Row stride in 32-bit words: rows padded to 256 bits."""
+    return (frames + 255) // 256 * 8
+
+
+# ------------------------------------------------------------------------------------------ StochasticLut6
+def stochastic_lut6_forward(x, idx, W, frames, y=None, binary=False, lut_binarize=False, bias=BIAS, bit_output=False):
+    """fp32 or bit-packed x -> fp32 y (clip to [0,1]) or, with bit_output (bit x only), bit-packed y = lut > 0.5."""
+    O = idx.shape[0]
+    _chk(idx, torch.int32, "idx"); _chk(W, torch.float32, "W")
+    if x.dtype == torch.float32:
+        _chk(x, torch.float32, "x")
+        if y is None:
+            y = torch.empty((O, x.shape[1]), dtype=torch.float32, device=x.device)
+        abi.call("bbcu_fp32_StochasticLut6_Forward", _p(x), _p(y), _p(idx), _p(W), O, frames, x.shape[1], int(binary), int(lut_binarize),
+                 bias, _stream())
+    elif bit_output:
+        _chk(x, torch.int32, "x")
+        if y is None:
+            y = torch.zeros((O, x.shape[1]), dtype=torch.int32, device=x.device)
+        abi.call("bbcu_bit_bit_fp32_StochasticLut6_Forward", _p(x), _p(y), _p(idx), _p(W), O, frames, x.shape[1], int(lut_binarize), bias,
+                 _stream())
+    else:
+        _chk(x, torch.int32, "x")
+        if y is None:
+            y = torch.empty((O, fp32_stride(frames)), dtype=torch.float32, device=x.device)
+        abi.call("bbcu_bit_fp32_StochasticLut6_Forward", _p(x), _p(y), _p(idx), _p(W), O, frames, y.shape[1], x.shape[1], int(lut_binarize),
+                 bias, _stream())
+    return y
+
+
+def stochastic_lut6_backward(x, dy, idx, W, dW, n_in, frames, dx=None, binary=False, lut_binarize=False, bias=BIAS):
+    """dx is overwritten, dW accumulated into."""
+    O = idx.shape[0]
+    _chk(dy, torch.float32, "dy"); _chk(dW, torch.float32, "dW")
+    if dx is None:
+        dx = torch.empty((n_in, dy.shape[1]), dtype=torch.float32, device=dy.device)
+    if x.dtype == torch.float32:
+        assert x.shape[1] == dy.shape[1], "x, dy and dx share one frame stride"
+        abi.call("bbcu_fp32_StochasticLut6_Backward", _p(x), _p(dy), _p(dx), 0, _p(idx), 0, _p(W), _p(dW), 0, n_in, O, frames, dy.shape[1],
+                 0, 0, int(binary), int(lut_binarize), bias, _stream())
+    else:
+        _chk(x, torch.int32, "x")
+        abi.call("bbcu_bit_fp32_StochasticLut6_Backward", _p(x), _p(dy), _p(dx), 0, _p(idx), 0, _p(W), _p(dW), 0, n_in, O, frames,
+                 dy.shape[1], x.shape[1], 0, 0, int(lut_binarize), bias, _stream())
+    return dx
+
+
+# ------------------------------------------------------------------------------------------ DifferentiableLut6
+def differentiable_lut6_forward_training(x, idx, W, running_mean, running_var, frames, y=None, gamma=0.3, beta=0.5, momentum=0.9,
+                                         bias=BIAS, lut_binarize=False, binary=True):
+    """Returns (y, mean, rstd); running_mean / running_var are updated in place.  Bit x gives bit y."""
+    O = idx.shape[0]
+    dev = x.device
+    mean = torch.empty(O, dtype=torch.float32, device=dev)
+    rstd = torch.empty(O, dtype=torch.float32, device=dev)
+    if x.dtype == torch.float32:
+        if y is None:
+            y = torch.empty((O, x.shape[1]), dtype=torch.float32, device=dev)
+        abi.call("bbcu_fp32_DifferentiableLut6_ForwardTraining", _p(x), _p(y), _p(idx), _p(W), _p(mean), _p(rstd), _p(running_mean),
+                 _p(running_var), gamma, beta, momentum, bias, O, frames, x.shape[1], int(lut_binarize), int(binary), _stream())
+    else:
+        _chk(x, torch.int32, "x")
+        if y is None:
+            y = torch.zeros((O, x.shape[1]), dtype=torch.int32, device=dev)
+        abi.call("bbcu_bit_fp32_DifferentiableLut6_ForwardTraining", _p(x), _p(y), _p(idx), _p(W), _p(mean), _p(rstd), _p(running_mean),
+                 _p(running_var), gamma, beta, momentum, bias, O, frames, x.shape[1], int(lut_binarize), _stream())
+    return y, mean, rstd
+
+
+def differentiable_lut6_forward_inference(x, idx, W, running_mean, running_var, frames, y=None, gamma=0.3, beta=0.5, bias=BIAS,
+                                          lut_binarize=False, binary=True):
+    O = idx.shape[0]
+    if x.dtype == torch.float32:
+        if y is None:
+            y = torch.empty((O, x.shape[1]), dtype=torch.float32, device=x.device)
+        abi.call("bbcu_fp32_DifferentiableLut6_ForwardInference", _p(x), _p(y), _p(idx), _p(W), _p(running_mean), _p(running_var), gamma, beta,
+                 bias, O, frames, x.shape[1], int(lut_binarize), int(binary), _stream())
+    else:
+        if y is None:
+            y = torch.zeros((O, x.shape[1]), dtype=torch.int32, device=x.device)
+        abi.call("bbcu_bit_fp32_DifferentiableLut6_ForwardInference", _p(x), _p(y), _p(idx), _p(W), _p(running_mean), _p(running_var), gamma,
+                 beta, bias, O, frames, x.shape[1], int(lut_binarize), _stream())
+    return y
+
+
+def differentiable_lut6_backward(x, dy, idx, W, dW, mean, rstd, n_in, frames, dx=None, gamma=0.3, beta=0.5, bias=BIAS, lut_binarize=False,
+                                 binary=True):
+    O = idx.shape[0]
+    dev = dy.device
+    if dx is None:
+        dx = torch.empty((n_in, dy.shape[1]), dtype=torch.float32, device=dev)
+    dmean = torch.empty(O, dtype=torch.float32, device=dev)
+    dvar = torch.empty(O, dtype=torch.float32, device=dev)
+    if x.dtype == torch.float32:
+        assert x.shape[1] == dy.shape[1]
+        abi.call("bbcu_fp32_DifferentiableLut6_Backward", _p(x), _p(dy), _p(dx), 0, _p(idx), 0, _p(W), _p(dW), _p(mean), _p(rstd), _p(dmean),
+                 _p(dvar), gamma, beta, bias, 0, n_in, O, frames, dy.shape[1], 0, 0, int(lut_binarize), int(binary), _stream())
+    else:
+        abi.call("bbcu_bit_fp32_DifferentiableLut6_Backward", _p(x), _p(dy), _p(dx), 0, _p(idx), 0, _p(W), _p(dW), _p(mean), _p(rstd),
+                 _p(dmean), _p(dvar), gamma, beta, bias, 0, n_in, O, frames, dy.shape[1], x.shape[1], 0, 0, int(lut_binarize), _stream())
+    return dx
+
+
+# ------------------------------------------------------------------------------------------ StochasticBatchNormalization
+def stochastic_bn_forward_training(x, running_mean, running_var, frames, gamma=0.2, beta=0.5, momentum=0.9):
+    O = x.shape[0]
+    y = torch.empty_like(x)
+    mean = torch.empty(O, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(O, dtype=torch.float32, device=x.device)
+    abi.call("bbcu_fp32_StochasticBatchNormalization_ForwardTraining", _p(x), _p(y), _p(mean), _p(rstd), _p(running_mean), _p(running_var),
+             gamma, beta, momentum, O, frames, x.shape[1], _stream())
+    return y, mean, rstd
+
+
+def stochastic_bn_reforward(x, mean, rstd, frames, gamma=0.2, beta=0.5):
+    y = torch.empty_like(x)
+    abi.call("bbcu_fp32_StochasticBatchNormalization_ReForward", _p(x), _p(y), _p(mean), _p(rstd), gamma, beta, x.shape[0], frames, x.shape[1],
+             _stream())
+    return y
+
+
+def stochastic_bn_forward_inference(x, running_mean, running_var, frames, gamma=0.2, beta=0.5):
+    y = torch.empty_like(x)
+    abi.call("bbcu_fp32_StochasticBatchNormalization_ForwardInference", _p(x), _p(y), _p(running_mean), _p(running_var), gamma, beta,
+             x.shape[0], frames, x.shape[1], _stream())
+    return y
+
+
+def stochastic_bn_backward(x, dy, mean, rstd, frames, gamma=0.2):
+    dx = torch.empty_like(dy)
+    abi.call("bbcu_fp32_StochasticBatchNormalization_Backward", _p(x), _p(dy), _p(dx), _p(mean), _p(rstd), gamma, 1.0 / frames, dy.shape[0],
+             frames, dy.shape[1], x.shape[1], _stream())
+    return dx
+
+
+# ------------------------------------------------------------------------------------------ BinaryLut6
+def binary_lut6_forward(x, idx, table, frames, y=None):
+    """Bit-packed inference forward; ``table`` is [nodes, 2] int32 (64-entry truth table per node)."""
+    _chk(x, torch.int32, "x"); _chk(idx, torch.int32, "idx"); _chk(table, torch.int32, "table")
+    O = idx.shape[0]
+    if y is None:
+        y = torch.empty((O, x.shape[1]), dtype=torch.int32, device=x.device)
+    abi.call("bbcu_bit_BinaryLut6_Forward", _p(x), _p(y), _p(idx), _p(table), O, frames, x.shape[1], _stream())
+    return y
+
+
+# ------------------------------------------------------------------------------------------ per-step neighbours
+def clamp_(t, lo=0.0, hi=1.0):
+    abi.call("bbcu_fp32_Vector_clamp", _p(t), _p(t), lo, hi, t.numel(), _stream())
+    return t
+
+
+class Adam:
+    """bb::OptimizerAdam over a list of (param, grad) CUDA tensors (include/bb/OptimizerAdam.h:142-184)."""
+
+    def __init__(self, params, grads, lr=0.001, beta1=0.9, beta2=0.999):
+        self.params, self.grads = list(params), list(grads)
+        self.m = [torch.zeros_like(p) for p in self.params]
+        self.v = [torch.zeros_like(p) for p in self.params]
+        dev = self.params[0].device
+        self._sizes = torch.tensor([p.numel() for p in self.params], dtype=torch.int32, device=dev)
+        mk = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=dev)
+        self._tabs = [mk(self.params), mk(self.grads), mk(self.m), mk(self.v)]
+        self.lr, self.beta1, self.beta2 = lr, beta1, beta2
+        self.b1, self.b2 = beta1, beta2
+
+    def step(self):
+        lr_t = self.lr * (1.0 - self.b2) ** 0.5 / (1.0 - self.b1)
+        abi.call("bbcu_fp32_OptimizerAdam", len(self.params), _p(self._sizes), *[_p(t) for t in self._tabs], lr_t, self.beta1, self.beta2,
+                 _stream())
+        self.b1 *= self.beta1
+        self.b2 *= self.beta2
+
+    def zero_grad(self):
+        for g in self.grads:
+            g.zero_()
+
+    def update(self):          # Optimizer::Update = Step + ZeroGrad (include/bb/Optimizer.h:29-33)
+        self.step()
+        self.zero_grad()

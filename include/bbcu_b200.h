@@ -1,0 +1,202 @@
+/* bbcu_b200.h -- C ABI of the sm_100a implementation of BinaryBrain's LUT6 hot path.
+ *
+ * Every entry point replaces one operator of BinaryBrain's CUDA layer (include/bbcu/bbcu.h in
+ * ryuz/BinaryBrain v4.3.2; the citation beside each declaration is the prototype it replaces).
+ * The reference declares the LUT operators as C++ templates on the LUT width N; a C symbol cannot
+ * be a template, so N = 6 is folded into the name ("...Lut6_..."), the spelling the reference's own
+ * raw-kernel harness already uses (tests/cuda/StochasticLut6_Test.cpp:60,174).  Argument order and
+ * meaning are the reference's, with these fixed rules:
+ *
+ *   - every pointer is a DEVICE pointer on the current device unless its name starts with host_;
+ *   - fp32 frame buffers are node-major: element (frame f, node n) at buf[n*frame_stride + f];
+ *     bit buffers hold 32 frames per 32-bit word, frame f = bit (f & 31) of word n*stride + (f >> 5)
+ *     (include/bb/FrameBuffer.h:28-46, include/bb/DataType.h:612-647); strides are in ELEMENTS
+ *     (floats or 32-bit words), as the reference's callers pass them;
+ *   - input_index is [output_node][6] int32, W is [output_node][64] fp32, bit k of the table index
+ *     is input k;
+ *   - the last argument is the CUDA stream (a cudaStream_t passed as void*, NULL = default
+ *     stream).  All work is enqueued on that stream and nothing synchronises the host;
+ *   - return value: 0 on success, BBCU_ERR_* (< 0) for a rejected argument, a cudaError_t (> 0)
+ *     if the CUDA runtime reported one.  Nothing exits the process (the reference's macros call
+ *     exit(1), include/bbcu/bbcu_util.h:17-36).
+ *
+ * Results follow the reference's CPU branches (the header-only path in include/bb), which is what
+ * parity is measured against; where the reference's old CUDA kernels differ from its CPU code the
+ * CPU code wins.  dev_dx_tmp and dev_reverse_index of the backward operators are
+ * accepted for signature compatibility and are not read or written: dx is accumulated with
+ * vector reductions in L2 instead of a [nodes*6][frames] temporary.
+ */
+#ifndef BBCU_B200_H
+#define BBCU_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void *bbcu_stream_t;
+
+#define BBCU_OK                 0
+#define BBCU_ERR_NULL_POINTER  (-1)
+#define BBCU_ERR_BAD_SIZE      (-2)
+#define BBCU_ERR_BAD_STRIDE    (-3)
+#define BBCU_ERR_NO_DEVICE     (-4)
+#define BBCU_ERR_NO_MEMORY     (-5)
+#define BBCU_ERR_TOO_LARGE     (-6)
+
+/* Human-readable text for a return value of any function below. */
+const char *bbcu_b200_error_string(int status);
+/* ABI version of this library (bumped when a signature changes). */
+int bbcu_b200_abi_version(void);
+
+/* ------------------------------------------------------------------ Manager: include/bbcu/bbcu.h:49-55, cuda/Manager.cu:15-55 */
+int  bbcu_GetDeviceCount(void);
+int  bbcu_GetDevice(void);
+void bbcu_SetDevice(int device);
+void bbcu_SetHostOnly(int host_only);
+int  bbcu_IsHostOnly(void);
+int  bbcu_IsDeviceAvailable(void);
+
+/* ------------------------------------------------------------------ Device heap: include/bbcu/bbcu.h:63-67, cuda/LocalHeap.cu:13-201
+ * Caching allocator over cudaMalloc, one pool per device, thread-safe.  Malloc returns NULL when the device is out of
+ * memory even after the cache has been released (the reference asserts).  Free only returns the block to the cache. */
+void  *bbcu_LocalHeap_Malloc(size_t size);
+void   bbcu_LocalHeap_Free(void *ptr);
+size_t bbcu_LocalHeap_GetMaxAllocSize(void);
+size_t bbcu_LocalHeap_GetAllocatedSize(void);
+void   bbcu_LocalHeap_GarbageCollect(void);
+/* Additive: artificial cap on live+cached bytes (0 = none), used to exercise the out-of-memory path without exhausting a GPU. */
+void   bbcu_LocalHeap_SetByteLimit(size_t bytes);
+
+/* ------------------------------------------------------------------ StochasticLut6: include/bbcu/bbcu.h:667-761 */
+/* bbcu_fp32_StochasticLut_Forward<6>, include/bbcu/bbcu.h:667-681.  y = clip(lut(x), 0, 1). */
+int bbcu_fp32_StochasticLut6_Forward(const float *dev_x_buf, float *dev_y_buf, const int *dev_input_index, const float *dev_W,
+                                     int node_size, int frame_size, int frame_stride,
+                                     int input_binary, int lut_binarize, float unbinarize_bias, bbcu_stream_t stream);
+/* bbcu_bit_fp32_StochasticLut_Forward<6>, include/bbcu/bbcu.h:683-697.  Bit-packed x, fp32 y. */
+int bbcu_bit_fp32_StochasticLut6_Forward(const int *dev_x_buf, float *dev_y_buf, const int *dev_input_index, const float *dev_W,
+                                         int node_size, int frame_size, int frame_stride, int bin_frame_stride,
+                                         int lut_binarize, float unbinarize_bias, bbcu_stream_t stream);
+/* bbcu_bit_bit_fp32_StochasticLut_Forward<6>, include/bbcu/bbcu.h:699-712.  Bit-packed x and y (y = lut(x) > 0.5). */
+int bbcu_bit_bit_fp32_StochasticLut6_Forward(const int *dev_x_buf, int *dev_y_buf, const int *dev_input_index, const float *dev_W,
+                                             int node_size, int frame_size, int frame_stride,
+                                             int lut_binarize, float unbinarize_bias, bbcu_stream_t stream);
+/* bbcu_fp32_StochasticLut_Backward<6>, include/bbcu/bbcu.h:715-737.  dx overwritten, dW accumulated into. */
+int bbcu_fp32_StochasticLut6_Backward(const float *dev_x_buf, const float *dev_dy_buf, float *dev_dx_buf, float *dev_dx_tmp,
+                                      const int *dev_input_index, const int *dev_reverse_index, const float *dev_W, float *dev_dW,
+                                      int reverse_index_stride, int input_node_size, int output_node_size,
+                                      int frame_size, int frame_stride, int tmp_frame_size, int tmp_frame_stride,
+                                      int input_binary, int lut_binarize, float unbinarize_bias, bbcu_stream_t stream);
+/* bbcu_bit_fp32_StochasticLut_Backward<6>, include/bbcu/bbcu.h:739-761. */
+int bbcu_bit_fp32_StochasticLut6_Backward(const int *dev_x_buf, const float *dev_dy_buf, float *dev_dx_buf, float *dev_dx_tmp,
+                                          const int *dev_input_index, const int *dev_reverse_index, const float *dev_W, float *dev_dW,
+                                          int reverse_index_stride, int input_node_size, int output_node_size,
+                                          int frame_size, int frame_stride, int bin_frame_stride, int tmp_frame_size, int tmp_frame_stride,
+                                          int lut_binarize, float unbinarize_bias, bbcu_stream_t stream);
+
+/* ------------------------------------------------------------------ DifferentiableLut6: include/bbcu/bbcu.h:518-660 */
+/* bbcu_fp32_DifferentiableLutN_ForwardTraining<6>, include/bbcu/bbcu.h:518-539.
+ * Writes y, mean, rstd; updates running_mean / running_var with `momentum`. */
+int bbcu_fp32_DifferentiableLut6_ForwardTraining(const float *dev_x_buf, float *dev_y_buf, const int *dev_input_index, const float *dev_W,
+                                                 float *dev_mean_buf, float *dev_rstd_buf, float *dev_running_mean_buf, float *dev_running_var_buf,
+                                                 float gamma, float beta, float momentum, float unbinarize_bias,
+                                                 int node_size, int frame_size, int frame_stride, int lut_binarize, int binary_mode,
+                                                 bbcu_stream_t stream);
+/* bbcu_bit_fp32_DifferentiableLutN_ForwardTraining<6>, include/bbcu/bbcu.h:541-561.  frame_stride in 32-bit words (x and y). */
+int bbcu_bit_fp32_DifferentiableLut6_ForwardTraining(const int *dev_x_buf, int *dev_y_buf, const int *dev_input_index, const float *dev_W,
+                                                     float *dev_mean_buf, float *dev_rstd_buf, float *dev_running_mean_buf, float *dev_running_var_buf,
+                                                     float gamma, float beta, float momentum, float unbinarize_bias,
+                                                     int node_size, int frame_size, int frame_stride, int lut_binarize,
+                                                     bbcu_stream_t stream);
+/* bbcu_fp32_DifferentiableLutN_ForwardInference<6>, include/bbcu/bbcu.h:563-581. */
+int bbcu_fp32_DifferentiableLut6_ForwardInference(const float *dev_x_buf, float *dev_y_buf, const int *dev_input_index, const float *dev_W,
+                                                  const float *dev_running_mean_buf, const float *dev_running_var_buf,
+                                                  float gamma, float beta, float unbinarize_bias,
+                                                  int node_size, int frame_size, int frame_stride, int lut_binarize, int binary_mode,
+                                                  bbcu_stream_t stream);
+/* bbcu_bit_fp32_DifferentiableLutN_ForwardInference<6>, include/bbcu/bbcu.h:583-600. */
+int bbcu_bit_fp32_DifferentiableLut6_ForwardInference(const int *dev_x_buf, int *dev_y_buf, const int *dev_input_index, const float *dev_W,
+                                                      const float *dev_running_mean_buf, const float *dev_running_var_buf,
+                                                      float gamma, float beta, float unbinarize_bias,
+                                                      int node_size, int frame_size, int frame_stride, int lut_binarize,
+                                                      bbcu_stream_t stream);
+/* bbcu_fp32_DifferentiableLutN_Backward<6>, include/bbcu/bbcu.h:602-630.
+ * dev_dmean_tmp / dev_dvar_tmp ([output_node_size] fp32) receive the batch-norm mean / variance gradients. */
+int bbcu_fp32_DifferentiableLut6_Backward(const float *dev_x_buf, const float *dev_dy_buf, float *dev_dx_buf, float *dev_dx_tmp,
+                                          const int *dev_input_index, const int *dev_reverse_index, const float *dev_W, float *dev_dW,
+                                          const float *dev_mean_buf, const float *dev_rstd_buf, float *dev_dmean_tmp, float *dev_dvar_tmp,
+                                          float gamma, float beta, float unbinarize_bias,
+                                          int reverse_index_stride, int input_node_size, int output_node_size,
+                                          int frame_size, int frame_stride, int tmp_frame_size, int tmp_frame_stride,
+                                          int lut_binarize, int binary_mode, bbcu_stream_t stream);
+/* bbcu_bit_fp32_DifferentiableLutN_Backward<6>, include/bbcu/bbcu.h:632-660.  frame_stride: dy/dx floats; x_frame_stride: x words. */
+int bbcu_bit_fp32_DifferentiableLut6_Backward(const int *dev_x_buf, const float *dev_dy_buf, float *dev_dx_buf, float *dev_dx_tmp,
+                                              const int *dev_input_index, const int *dev_reverse_index, const float *dev_W, float *dev_dW,
+                                              const float *dev_mean_buf, const float *dev_rstd_buf, float *dev_dmean_tmp, float *dev_dvar_tmp,
+                                              float gamma, float beta, float unbinarize_bias,
+                                              int reverse_index_stride, int input_node_size, int output_node_size,
+                                              int frame_size, int frame_stride, int x_frame_stride, int tmp_frame_size, int tmp_frame_stride,
+                                              int lut_binarize, bbcu_stream_t stream);
+
+/* ------------------------------------------------------------------ StochasticBatchNormalization: include/bbcu/bbcu.h:883-942 */
+int bbcu_fp32_StochasticBatchNormalization_ForwardTraining(const float *dev_x_buf, float *dev_y_buf, float *dev_mean_buf, float *dev_rstd_buf,
+                                                           float *dev_running_mean_buf, float *dev_running_var_buf,
+                                                           float gamma, float beta, float momentum,
+                                                           int node_size, int frame_size, int frame_stride, bbcu_stream_t stream);
+int bbcu_fp32_StochasticBatchNormalization_ReForward(const float *dev_x_buf, float *dev_y_buf, const float *dev_mean_buf, const float *dev_rstd_buf,
+                                                     float gamma, float beta, int node_size, int frame_size, int frame_stride, bbcu_stream_t stream);
+int bbcu_fp32_StochasticBatchNormalization_ForwardInference(const float *dev_x_buf, float *dev_y_buf,
+                                                            const float *dev_running_mean_buf, const float *dev_running_var_buf,
+                                                            float gamma, float beta, int node_size, int frame_size, int frame_stride, bbcu_stream_t stream);
+int bbcu_fp32_StochasticBatchNormalization_Backward(const float *dev_x_buf, const float *dev_dy_buf, float *dev_dx_buf,
+                                                    const float *dev_mean_buf, const float *dev_rstd_buf, float gamma, float reciprocal_frame_size,
+                                                    int node_size, int frame_size, int frame_stride, int x_frame_stride, bbcu_stream_t stream);
+
+/* ------------------------------------------------------------------ BinaryLut6: include/bbcu/bbcu.h:285-295, cuda/BinaryLut6.cu:165-196
+ * dev_table is [node][2] int32: bit i of the 64-bit table is the output for input index i (include/bb/BinaryLutN.h:43-46).
+ * Unlike the reference (one block per node in grid.y, cuda/BinaryLut6.cu:179-180) any node_size up to INT_MAX works.
+ * The reference spells it "BinatyLut6"; both spellings are exported. */
+int bbcu_bit_BinaryLut6_Forward(const int *dev_x_buf, int *dev_y_buf, const int *dev_input_index, const int *dev_table,
+                                int node_size, int frame_size, int frame_stride, bbcu_stream_t stream);
+int bbcu_bit_BinatyLut6_Forward(const int *dev_x_buf, int *dev_y_buf, const int *dev_input_index, const int *dev_table,
+                                int node_size, int frame_size, int frame_stride, bbcu_stream_t stream);
+
+/* ------------------------------------------------------------------ Neighbours of the path that its callers need every step */
+/* bbcu_fp32_Vector_clamp, include/bbcu/bbcu.h:191-198 (the W clamp of DifferentiableLutN.h:605-608 / StochasticLutN.h:451). */
+int bbcu_fp32_Vector_clamp(float *dev_dst, const float *dev_src, float lo, float hi, int size, bbcu_stream_t stream);
+/* bbcu_fp32_Vector_set, include/bbcu/bbcu.h:89-94. */
+int bbcu_fp32_Vector_set(float *dev_dst, float a, int size, bbcu_stream_t stream);
+/* bbcu_fp32_OptimizerAdam, include/bbcu/bbcu.h:1560-1572, cuda/OptimizerAdam.cu:12-48.  The tables are DEVICE arrays of `size`
+ * entries.  m += (1-b1)(g-m); v += (1-b2)(g*g-v); p -= lr_t*m/(sqrt(v)+1e-7).  Gradients are left untouched. */
+int bbcu_fp32_OptimizerAdam(int size, const int *dev_size_table, float *const *dev_params_buf_table, float *const *dev_grads_buf_table,
+                            float *const *dev_m_buf_table, float *const *dev_v_buf_table, float lr_t, float beta1, float beta2,
+                            bbcu_stream_t stream);
+
+/* ------------------------------------------------------------------ Additive: frame-sharded (multi-GPU) building blocks.
+ * No counterpart in the reference (it has no multi-device path, include/bb/Memory.h:215-216).  A rank holds a contiguous frame
+ * shard; these split the batch-norm operators at the points where per-node sums over ALL frames are needed, so the caller can
+ * all-reduce `dev_sums` ([node_size][2] fp64) between the two halves.  total_frame_size is the global frame count. */
+int bbcu_fp32_DifferentiableLut6_ForwardStats(const float *dev_x_buf, float *dev_y_buf, const int *dev_input_index, const float *dev_W,
+                                              double *dev_sums, float unbinarize_bias, int node_size, int frame_size, int frame_stride,
+                                              int lut_binarize, int binary_mode, bbcu_stream_t stream);
+int bbcu_fp32_DifferentiableLut6_ForwardNormalize(float *dev_y_buf, const double *dev_sums, float *dev_mean_buf, float *dev_rstd_buf,
+                                                  float *dev_running_mean_buf, float *dev_running_var_buf,
+                                                  float gamma, float beta, float momentum, int node_size, int frame_size, int frame_stride,
+                                                  long long total_frame_size, int binary_mode, bbcu_stream_t stream);
+int bbcu_fp32_DifferentiableLut6_BackwardStats(const float *dev_x_buf, const float *dev_dy_buf, const int *dev_input_index, const float *dev_W,
+                                               const float *dev_mean_buf, const float *dev_rstd_buf, double *dev_sums,
+                                               float gamma, float beta, float unbinarize_bias, int node_size, int frame_size, int frame_stride,
+                                               int lut_binarize, int binary_mode, bbcu_stream_t stream);
+int bbcu_fp32_DifferentiableLut6_BackwardApply(const float *dev_x_buf, const float *dev_dy_buf, float *dev_dx_buf,
+                                               const int *dev_input_index, const float *dev_W, float *dev_dW,
+                                               const float *dev_mean_buf, const float *dev_rstd_buf, const double *dev_sums,
+                                               float *dev_dmean_tmp, float *dev_dvar_tmp,
+                                               float gamma, float beta, float unbinarize_bias, int input_node_size, int output_node_size,
+                                               int frame_size, int frame_stride, long long total_frame_size,
+                                               int lut_binarize, int binary_mode, bbcu_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BBCU_B200_H */

@@ -1,0 +1,402 @@
+"""GPU parity: every bbcu_* operator, called through the C ABI, against the CPU oracle.
+
+Tolerances (north-star): BinaryLut6 and gather indexing bit-exact; fp32 y / dx / dW within 1e-5 of the
+value range.  Two documented refinements where a decision threshold or the batch-norm condition number
+makes a literal 1e-5 meaningless:
+  * outputs that pass through a threshold (binarised y, the hard-tanh mask in dx) may differ from the
+    oracle only where the oracle's pre-threshold value is within 1e-4 of the threshold;
+  * batch-normalised fp32 outputs are compared with 1e-5 * max(1, gamma*rstd): the normalisation
+    multiplies the last-ulp difference between a lerp tree and the CPU's product form by gamma*rstd
+    (up to 95 when the variance sits at its 1e-5 floor).
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden_cases
+from oracle import port, pack_bits, unpack_bits
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-5
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from binarybrain_b200 import ops as o
+    return o
+
+
+def _flags(case):
+    d = {}
+    for p in case.split("_"):
+        if p[0] == "b" and p[1:].isdigit():
+            d["binary"] = int(p[1:])
+        if p[0] == "l" and p[1:].isdigit():
+            d["lut_binarize"] = int(p[1:])
+    return d
+
+
+# --------------------------------------------------------------------------------------------- StochasticLut6
+def _sl6_check(ops, x, idx, W, dy, dW0, fl, want, stride=None):
+    from gpu_util import dev_fp32, dev, host_fp32, err
+    I, F = x.shape
+    O = idx.shape[0]
+    xd = dev_fp32(x, stride)
+    y = ops.stochastic_lut6_forward(xd, dev(idx), dev(W), F, **fl)
+    assert err(host_fp32(y, F), want["y"]) <= TOL
+    dWd = dev(dW0.copy())
+    dx = ops.stochastic_lut6_backward(xd, dev_fp32(dy, stride), dev(idx), dev(W), dWd, I, F, **fl)
+    assert err(host_fp32(dx, F), want["dx"]) <= TOL
+    assert err(dWd.cpu().numpy(), want["dW"]) <= TOL
+
+
+@pytest.mark.parametrize("case", golden_cases("sl6"))
+def test_sl6_fp32_golden(ops, golden, case):
+    g = lambda n: golden[case + "_" + n]
+    _sl6_check(ops, g("x"), g("idx"), g("W"), g("dy"), g("dW0"), _flags(case), dict(y=g("y"), dx=g("dx"), dW=g("dW")))
+
+
+@pytest.mark.parametrize("I,O,F,stride", [(13, 17, 1529, None), (14, 1024, 8, None), (14, 1024, 3, 16), (300, 700, 2100, 2112),
+                                          (6, 1, 1, None), (2048, 4096, 640, None)])
+@pytest.mark.parametrize("binary,lut_binarize", [(0, 0), (1, 1)])
+def test_sl6_fp32_oracle(ops, I, O, F, stride, binary, lut_binarize):
+    from gpu_util import wiring
+    rng = np.random.default_rng(I * 7 + O + F)
+    idx = wiring(rng, I, O)
+    W = np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32)
+    x = (rng.random((I, F), dtype=np.float32) * 1.2 - 0.1).astype(np.float32)     # also exercises the [0,1] clip
+    dy = rng.random((O, F), dtype=np.float32)
+    dW0 = rng.random((O, 64), dtype=np.float32)
+    fl = dict(binary=binary, lut_binarize=lut_binarize)
+    y = port.sl6_forward(x, idx, W, **fl)
+    dx, dW = port.sl6_backward(x, dy, idx, W, I, dW=dW0, **fl)
+    _sl6_check(ops, x, idx, W, dy, dW0, fl, dict(y=y, dx=dx, dW=dW), stride)
+
+
+@pytest.mark.parametrize("case", golden_cases("sl6bit"))
+def test_sl6_bit_golden(ops, golden, case):
+    from gpu_util import dev_bits, dev_fp32, dev, host_fp32, host_bits, err
+    g = lambda n: golden[case + "_" + n]
+    fl = _flags(case)
+    F = g("dy").shape[1]
+    I = g("x").shape[0]
+    xd = dev_bits(g("x"), F)
+    y = ops.stochastic_lut6_forward(xd, dev(g("idx")), dev(g("W")), F, **fl)
+    assert err(host_fp32(y, F), g("y")) <= TOL
+    dWd = torch.zeros((g("idx").shape[0], 64), device="cuda")
+    dx = ops.stochastic_lut6_backward(xd, dev_fp32(g("dy")), dev(g("idx")), dev(g("W")), dWd, I, F, **fl)
+    assert err(host_fp32(dx, F), g("dx")) <= TOL and err(dWd.cpu().numpy(), g("dW")) <= TOL
+    # bit -> bit: y = lut > 0.5, compared where the oracle is not on the threshold
+    yb = ops.stochastic_lut6_forward(xd, dev(g("idx")), dev(g("W")), F, bit_output=True, **fl)
+    raw, want = port.sl6_forward(g("x"), g("idx"), g("W"), frames=F, want_bits=True, **fl)
+    bad = unpack_bits(host_bits(yb, F), F) != unpack_bits(want, F)
+    assert (np.abs(raw[bad] - 0.5) < 1e-4).all() and bad.mean() < 1e-3
+
+
+# --------------------------------------------------------------------------------------------- DifferentiableLut6
+def _dl6_fp32_check(ops, x, idx, W, dy, rm0, rv0, fl, stride=None):
+    from gpu_util import dev_fp32, dev, host_fp32, err
+    I, F = x.shape
+    O = idx.shape[0]
+    p = port.dl6_forward_train(x, idx, W, rm0, rv0, **fl)
+    xd = dev_fp32(x, stride)
+    rm, rv = dev(rm0.copy()), dev(rv0.copy())
+    y, mean, rstd = ops.differentiable_lut6_forward_training(xd, dev(idx), dev(W), rm, rv, F, **fl)
+    yh = host_fp32(y, F)
+    assert err(mean.cpu().numpy(), p["mean"]) <= TOL
+    amp = max(1.0, 0.3 * float(p["rstd"].max()))
+    assert np.abs(rstd.cpu().numpy() / p["rstd"] - 1).max() <= 1e-4
+    assert err(rm.cpu().numpy(), p["running_mean"]) <= TOL and err(rv.cpu().numpy(), p["running_var"]) <= TOL
+    if fl["binary"]:
+        bad = yh != p["y"]
+        assert (np.abs(p["y_pre"][bad] - 0.5) < 1e-4 * amp).all() and bad.mean() < 1e-2
+    else:
+        assert np.abs(yh - p["y"]).max() <= TOL * amp * 3
+    # backward with the oracle's own mean / rstd so that only this operator is under test
+    dx_w, dW_w = port.dl6_backward(x, dy, idx, W, p["mean"], p["rstd"], I, **fl)
+    dWd = torch.zeros((O, 64), device="cuda")
+    dx = ops.differentiable_lut6_backward(xd, dev_fp32(dy, stride), dev(idx), dev(W), dWd, dev(p["mean"]), dev(p["rstd"]), I, F, **fl)
+    dxh = host_fp32(dx, F)
+    # hard-tanh mask: a frame whose pre-activation sits on 0 or 1 may flip; allow those rows of evidence only
+    pre = p["y_pre"]
+    edge = (np.abs(pre) < 1e-4 * amp) | (np.abs(pre - 1) < 1e-4 * amp)
+    scale = max(1.0, float(np.abs(dx_w).max()))
+    if not edge.any():
+        assert np.abs(dxh - dx_w).max() <= 2e-5 * scale * amp
+        assert err(dWd.cpu().numpy(), dW_w) <= 2e-5 * amp
+    # inference
+    pi = port.dl6_forward_infer(x, idx, W, rm0, rv0, **fl)
+    yi = host_fp32(ops.differentiable_lut6_forward_inference(xd, dev(idx), dev(W), dev(rm0), dev(rv0), F, **fl), F)
+    if fl["binary"]:
+        bad = yi != pi["y"]
+        assert (np.abs(pi["y_pre"][bad] - 0.5) < 1e-4).all()
+    else:
+        assert np.abs(yi - pi["y"]).max() <= TOL * 3
+    return edge.any()
+
+
+@pytest.mark.parametrize("case", golden_cases("dl6"))
+def test_dl6_fp32_golden(ops, golden, case):
+    from gpu_util import dev_fp32, dev, host_fp32, err
+    g = lambda n: golden[case + "_" + n]
+    fl = _flags(case)
+    _dl6_fp32_check(ops, g("x"), g("idx"), g("W"), g("dy"), g("rm0"), g("rv0"), fl)
+    # and against the reference's own numbers
+    F = g("x").shape[1]
+    rm, rv = dev(g("rm0").copy()), dev(g("rv0").copy())
+    y, mean, rstd = ops.differentiable_lut6_forward_training(dev_fp32(g("x")), dev(g("idx")), dev(g("W")), rm, rv, F, **fl)
+    assert err(mean.cpu().numpy(), g("mean")) <= TOL and err(rm.cpu().numpy(), g("rm")) <= TOL
+    if not fl["binary"]:
+        assert np.abs(host_fp32(y, F) - g("y")).max() <= TOL * 3 * max(1.0, 0.3 * float(g("rstd").max()))
+
+
+@pytest.mark.parametrize("I,O,F,stride", [(16, 16, 131, None), (24, 1024, 64, None), (200, 300, 1100, 1104), (6, 2, 39, 64),
+                                          (1024, 2048, 512, None)])
+@pytest.mark.parametrize("binary,lut_binarize", [(0, 0), (1, 0), (1, 1), (0, 1)])
+def test_dl6_fp32_oracle(ops, I, O, F, stride, binary, lut_binarize):
+    from gpu_util import wiring
+    rng = np.random.default_rng(I + 31 * O + F)
+    idx = wiring(rng, I, O)
+    W = np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32)
+    x = rng.random((I, F), dtype=np.float32)
+    dy = rng.random((O, F), dtype=np.float32)
+    rm0 = rng.random(O, dtype=np.float32)
+    rv0 = rng.random(O, dtype=np.float32) + 0.5
+    _dl6_fp32_check(ops, x, idx, W, dy, rm0, rv0, dict(binary=binary, lut_binarize=lut_binarize), stride)
+
+
+def test_dl6_fp32_fresh_layer_tables(ops):
+    """Tables N(0.5, 0.01) as a new layer has them: variance at the 1e-5 floor, gamma*rstd = 95."""
+    from gpu_util import wiring
+    rng = np.random.default_rng(99)
+    I, O, F = 784, 1024, 512
+    idx = wiring(rng, I, O)
+    W = np.clip(rng.normal(0.5, 0.01, (O, 64)), 0, 1).astype(np.float32)
+    x = rng.random((I, F), dtype=np.float32)
+    dy = rng.random((O, F), dtype=np.float32)
+    _dl6_fp32_check(ops, x, idx, W, dy, np.zeros(O, np.float32), np.ones(O, np.float32), dict(binary=0, lut_binarize=0))
+
+
+@pytest.mark.parametrize("case", golden_cases("dl6bit"))
+def test_dl6_bit_golden(ops, golden, case):
+    from gpu_util import dev_bits, dev_fp32, dev, host_fp32, host_bits, err
+    g = lambda n: golden[case + "_" + n]
+    fl = _flags(case)
+    F = g("dy").shape[1]
+    I = g("x").shape[0]
+    O = g("idx").shape[0]
+    p = port.dl6_forward_train(g("x"), g("idx"), g("W"), np.zeros(O), np.ones(O), frames=F, **fl)
+    xd = dev_bits(g("x"), F)
+    rm, rv = torch.zeros(O, device="cuda"), torch.ones(O, device="cuda")
+    y, mean, rstd = ops.differentiable_lut6_forward_training(xd, dev(g("idx")), dev(g("W")), rm, rv, F, **fl)
+    assert err(mean.cpu().numpy(), g("mean")) <= TOL and np.abs(rstd.cpu().numpy() / g("rstd") - 1).max() <= 1e-4
+    assert err(rm.cpu().numpy(), g("rm")) <= TOL and err(rv.cpu().numpy(), g("rv")) <= TOL
+    amp = max(1.0, 0.3 * float(g("rstd").max()))
+    bad = unpack_bits(host_bits(y, F), F) != unpack_bits(g("y"), F)
+    assert (np.abs(p["y_pre"][bad] - 0.5) < 1e-4 * amp).all()
+    dWd = torch.zeros((O, 64), device="cuda")
+    dx = ops.differentiable_lut6_backward(xd, dev_fp32(g("dy")), dev(g("idx")), dev(g("W")), dWd, dev(g("mean")), dev(g("rstd")), I, F, **fl)
+    pre = p["y_pre"]
+    if not ((np.abs(pre) < 1e-4 * amp) | (np.abs(pre - 1) < 1e-4 * amp)).any():
+        assert err(host_fp32(dx, F), g("dx")) <= 2e-5 * amp and err(dWd.cpu().numpy(), g("dW")) <= 2e-5 * amp
+    yi = ops.differentiable_lut6_forward_inference(xd, dev(g("idx")), dev(g("W")), dev(g("rm")), dev(g("rv")), F, **fl)
+    pi = port.dl6_forward_infer(g("x"), g("idx"), g("W"), g("rm"), g("rv"), frames=F, **fl)
+    bad = unpack_bits(host_bits(yi, F), F) != unpack_bits(g("y_infer"), F)
+    assert (np.abs(pi["y_pre"][bad] - 0.5) < 1e-4).all()
+
+
+def test_dl6_bit_oracle_odd_sizes(ops):
+    from gpu_util import dev_bits, dev_fp32, dev, host_fp32, host_bits, err, wiring
+    rng = np.random.default_rng(5)
+    for (I, O, F) in [(40, 33, 1529), (512, 1024, 1024), (7, 3, 31)]:
+        idx = wiring(rng, I, O)
+        W = np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32)
+        xb = pack_bits(rng.random((I, F)) > 0.5)
+        dy = rng.random((O, F), dtype=np.float32)
+        p = port.dl6_forward_train(xb, idx, W, np.zeros(O), np.ones(O), frames=F)
+        xd = dev_bits(xb, F)
+        rm, rv = torch.zeros(O, device="cuda"), torch.ones(O, device="cuda")
+        y, mean, rstd = ops.differentiable_lut6_forward_training(xd, dev(idx), dev(W), rm, rv, F)
+        amp = max(1.0, 0.3 * float(p["rstd"].max()))
+        assert err(mean.cpu().numpy(), p["mean"]) <= TOL
+        bad = unpack_bits(host_bits(y, F), F) != unpack_bits(p["y_bits"], F)
+        assert (np.abs(p["y_pre"][bad] - 0.5) < 1e-4 * amp).all() and bad.mean() < 1e-3
+        dx_w, dW_w = port.dl6_backward(xb, dy, idx, W, p["mean"], p["rstd"], I)
+        dWd = torch.zeros((O, 64), device="cuda")
+        dx = ops.differentiable_lut6_backward(xd, dev_fp32(dy), dev(idx), dev(W), dWd, dev(p["mean"]), dev(p["rstd"]), I, F)
+        pre = p["y_pre"]
+        edge = (np.abs(pre) < 1e-4 * amp) | (np.abs(pre - 1) < 1e-4 * amp)
+        if not edge.any():
+            assert err(host_fp32(dx, F), dx_w) <= 2e-5 * amp and err(dWd.cpu().numpy(), dW_w) <= 2e-5 * amp
+
+
+# --------------------------------------------------------------------------------------------- StochasticBatchNormalization
+@pytest.mark.parametrize("O,F,stride", [(16, 39, None), (8, 200, None), (33, 10000, 10008), (5, 7, 16)])
+def test_sbn_oracle(ops, O, F, stride):
+    from gpu_util import dev_fp32, dev, host_fp32, err
+    rng = np.random.default_rng(O + F)
+    x = rng.random((O, F), dtype=np.float32)
+    dy = rng.random((O, F), dtype=np.float32)
+    rm0 = rng.random(O, dtype=np.float32)
+    rv0 = rng.random(O, dtype=np.float32) + 0.5
+    p = port.sbn_forward_train(x, rm0, rv0)
+    xd = dev_fp32(x, stride)
+    rm, rv = dev(rm0.copy()), dev(rv0.copy())
+    y, mean, rstd = ops.stochastic_bn_forward_training(xd, rm, rv, F)
+    assert err(host_fp32(y, F), p["y"]) <= 2e-5
+    assert err(mean.cpu().numpy(), p["mean"]) <= TOL and np.abs(rstd.cpu().numpy() / p["rstd"] - 1).max() <= 2e-5
+    assert err(rm.cpu().numpy(), p["running_mean"]) <= TOL and err(rv.cpu().numpy(), p["running_var"]) <= TOL
+    assert err(host_fp32(ops.stochastic_bn_reforward(xd, dev(p["mean"]), dev(p["rstd"]), F), F), port.sbn_reforward(x, p["mean"], p["rstd"])) <= TOL
+    assert err(host_fp32(ops.stochastic_bn_forward_inference(xd, dev(rm0), dev(rv0), F), F), port.sbn_forward_infer(x, rm0, rv0)) <= TOL
+    dx = ops.stochastic_bn_backward(xd, dev_fp32(dy, stride), dev(p["mean"]), dev(p["rstd"]), F)
+    assert err(host_fp32(dx, F), port.sbn_backward(x, dy, p["mean"], p["rstd"])) <= 2e-5
+
+
+# --------------------------------------------------------------------------------------------- BinaryLut6
+@pytest.mark.parametrize("case", golden_cases("bl6"))
+def test_binary_lut6_golden_bit_exact(ops, golden, case):
+    from gpu_util import dev_bits, dev, host_bits
+    g = lambda n: golden[case + "_" + n]
+    F = int(case.split("_")[-1])
+    y = ops.binary_lut6_forward(dev_bits(g("x"), F), dev(g("idx")), dev(g("table")), F)
+    assert (unpack_bits(host_bits(y, F), F) == unpack_bits(g("y"), F)).all()
+
+
+def test_binary_lut6_truth_tables(ops):
+    from gpu_util import dev_bits, dev, host_bits
+    frames = np.arange(64)
+    x = pack_bits(((frames[None, :] >> np.arange(6)[:, None]) & 1).astype(np.uint8))
+    idx = np.arange(6, dtype=np.int32)[None, :]
+    for t in (0x8000000000000000, 0xFFFFFFFFFFFFFFFE, 0x6996966996696996, 0x0123456789ABCDEF, 0, 2**64 - 1):
+        table = np.array([[t & 0xFFFFFFFF, t >> 32]], dtype=np.uint64).astype(np.uint32).view(np.int32)
+        y = unpack_bits(host_bits(ops.binary_lut6_forward(dev_bits(x, 64), dev(idx), dev(table), 64), 64), 64)[0]
+        assert (y == [(t >> i) & 1 for i in range(64)]).all()
+
+
+@pytest.mark.parametrize("I,O,F,stride", [(16, 16, 32, None), (40, 33, 300, None), (1000, 3000, 5000, None), (64, 70000, 64, None),
+                                          (50, 20, 100, 5), (1, 1, 1, None)])
+def test_binary_lut6_oracle_bit_exact(ops, I, O, F, stride):
+    from gpu_util import dev_bits, dev, host_bits, wiring
+    rng = np.random.default_rng(I + O + F)
+    idx = wiring(rng, I, O) if I >= 6 else np.zeros((O, 6), np.int32)
+    table = rng.integers(-2**31, 2**31, (O, 2)).astype(np.int32)
+    xb = pack_bits(rng.random((I, F)) > 0.5)
+    want = port.binary_lut6_forward(xb, idx, table, F)
+    y = ops.binary_lut6_forward(dev_bits(xb, F, stride), dev(idx), dev(table), F)
+    assert (unpack_bits(host_bits(y, F), F) == unpack_bits(want, F)).all()
+
+
+def test_binary_lut6_full_size_properties(ops):
+    """BASELINE config 1 shape (16384 -> 16384 nodes, 2^20 frames): properties that need no CPU pass.
+
+    (a) a table that projects input k reproduces that input row bit for bit (gather indexing);
+    (b) complementing the table complements the output; (c) a 4096-node x 8192-frame window agrees with the oracle."""
+    I = O = 16384
+    F = 1 << 20
+    S = F // 32
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randint(-2**31, 2**31 - 1, (I, S), dtype=torch.int32, device="cuda", generator=g)
+    idx = torch.stack([torch.randperm(I, device="cuda", generator=g)[:O] for _ in range(6)], dim=1).to(torch.int32).contiguous()
+    # (a) projection tables: node n projects input (n % 6)
+    proj = [0xAAAAAAAAAAAAAAAA, 0xCCCCCCCCCCCCCCCC, 0xF0F0F0F0F0F0F0F0, 0xFF00FF00FF00FF00, 0xFFFF0000FFFF0000, 0xFFFFFFFF00000000]
+    tab = np.array([[p & 0xFFFFFFFF, p >> 32] for p in proj], dtype=np.uint64).astype(np.uint32).view(np.int32)
+    k = torch.arange(O, device="cuda") % 6
+    table = torch.from_numpy(tab).cuda()[k].contiguous()
+    y = ops.binary_lut6_forward(x, idx, table, F)
+    src = idx.gather(1, k[:, None].to(torch.int64)).squeeze(1).to(torch.int64)
+    for lo in range(0, O, 2048):
+        assert torch.equal(y[lo:lo + 2048], x[src[lo:lo + 2048]])
+    # (b) complement
+    table = torch.randint(-2**31, 2**31 - 1, (O, 2), dtype=torch.int32, device="cuda", generator=g)
+    y1 = ops.binary_lut6_forward(x, idx, table, F)
+    y2 = ops.binary_lut6_forward(x, idx, ~table, F)
+    assert torch.equal(y1, ~y2)
+    # (c) window against the oracle
+    xs = np.ascontiguousarray(x[:, :256].cpu().numpy()).view(np.uint32)
+    want = port.binary_lut6_forward(xs, idx[:4096].cpu().numpy(), table[:4096].cpu().numpy(), 8192)
+    got = np.ascontiguousarray(y1[:4096, :256].cpu().numpy()).view(np.uint32)
+    assert (got == want).all()
+
+
+# --------------------------------------------------------------------------------------------- behaviour of the ABI
+def test_determinism_and_dw_accumulation(ops):
+    from gpu_util import dev_fp32, dev, wiring
+    rng = np.random.default_rng(3)
+    I, O, F = 256, 512, 777
+    idx, W = dev(wiring(rng, I, O)), dev(rng.random((O, 64), dtype=np.float32))
+    x, dy = dev_fp32(rng.random((I, F), dtype=np.float32)), dev_fp32(rng.random((O, F), dtype=np.float32))
+    y1 = ops.stochastic_lut6_forward(x, idx, W, F)
+    y2 = ops.stochastic_lut6_forward(x, idx, W, F)
+    assert torch.equal(y1[:, :F], y2[:, :F])
+    dW = torch.zeros((O, 64), device="cuda")
+    ops.stochastic_lut6_backward(x, dy, idx, W, dW, I, F)
+    once = dW.clone()
+    ops.stochastic_lut6_backward(x, dy, idx, W, dW, I, F)          # dW is accumulated into, dx overwritten
+    assert torch.allclose(dW, 2 * once, rtol=1e-5, atol=1e-5)
+
+
+def test_argument_errors_do_not_reach_the_gpu(ops):
+    from binarybrain_b200 import abi
+    L = abi.lib()
+    x = torch.zeros((8, 8), device="cuda")
+    idx = torch.zeros((4, 6), dtype=torch.int32, device="cuda")
+    W = torch.zeros((4, 64), device="cuda")
+    p = lambda t: t.data_ptr()
+    assert L.bbcu_fp32_StochasticLut6_Forward(0, p(x), p(idx), p(W), 4, 8, 8, 0, 0, 0.25, None) == -1
+    assert L.bbcu_fp32_StochasticLut6_Forward(p(x), p(x), p(idx), p(W), -1, 8, 8, 0, 0, 0.25, None) == -2
+    assert L.bbcu_fp32_StochasticLut6_Forward(p(x), p(x), p(idx), p(W), 4, 9, 8, 0, 0, 0.25, None) == -3
+    assert L.bbcu_bit_BinaryLut6_Forward(p(x), p(x), p(idx), 0, 4, 8, 8, None) == -1
+    assert b"stride" in L.bbcu_b200_error_string(-3)
+    with pytest.raises(abi.BbcuError):
+        abi.call("bbcu_fp32_StochasticLut6_Forward", 0, 0, 0, 0, 1, 1, 1, 0, 0, 0.25, None)
+    # empty inputs are a no-op, not an error
+    assert L.bbcu_fp32_StochasticLut6_Forward(p(x), p(x), p(idx), p(W), 0, 8, 8, 0, 0, 0.25, None) == 0
+    assert L.bbcu_bit_BinaryLut6_Forward(p(x), p(x), p(idx), p(idx), 4, 0, 8, None) == 0
+    torch.cuda.synchronize()
+
+
+def test_heap_cache_and_out_of_memory(ops):
+    from binarybrain_b200 import abi
+    L = abi.lib()
+    a = L.bbcu_LocalHeap_Malloc(1 << 20)
+    assert a and L.bbcu_LocalHeap_GetAllocatedSize() >= (1 << 20)
+    L.bbcu_LocalHeap_Free(a)
+    b = L.bbcu_LocalHeap_Malloc((1 << 20) - 4096)            # within 1.5x of the cached block: reused
+    assert b == a
+    L.bbcu_LocalHeap_Free(b)
+    L.bbcu_LocalHeap_GarbageCollect()
+    L.bbcu_LocalHeap_SetByteLimit(1 << 20)
+    try:
+        assert L.bbcu_LocalHeap_Malloc(1 << 22) is None       # refused on the host: no GPU memory is exhausted
+    finally:
+        L.bbcu_LocalHeap_SetByteLimit(0)
+    assert L.bbcu_IsDeviceAvailable() == 1 and L.bbcu_GetDeviceCount() >= 1
+
+
+def test_adam_100_steps(ops, golden):
+    """100 x (forward, backward, Adam update) of one DifferentiableLut6 layer on the GPU vs the reference run: |dW| <= 1e-4."""
+    from gpu_util import dev_fp32, dev, host_fp32
+    idx, x, dy = golden["adam_idx"], golden["adam_x"], golden["adam_dy"]
+    I, F = x.shape
+    O = idx.shape[0]
+    for key, bn in (("adam", True), ("adamnobn", False)):
+        W = dev(golden[key + "_W0"].copy())
+        dW = torch.zeros_like(W)
+        opt = ops.Adam([W], [dW])
+        xd, dyd, idxd = dev_fp32(x), dev_fp32(dy), dev(idx)
+        rm, rv = torch.zeros(O, device="cuda"), torch.ones(O, device="cuda")
+        for _ in range(100):
+            ops.clamp_(W)
+            if bn:
+                y, mean, rstd = ops.differentiable_lut6_forward_training(xd, idxd, W, rm, rv, F, binary=False)
+                ops.differentiable_lut6_backward(xd, dyd, idxd, W, dW, mean, rstd, I, F, binary=False)
+            else:
+                y = ops.stochastic_lut6_forward(xd, idxd, W, F)
+                ops.stochastic_lut6_backward(xd, dyd, idxd, W, dW, I, F)
+            opt.update()
+        assert np.abs(W.cpu().numpy() - golden[key + "_W100"]).max() <= 1e-4
+        if bn:
+            assert np.abs(rm.cpu().numpy() - golden["adam_rm100"]).max() <= 1e-4
