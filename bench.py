@@ -1,0 +1,309 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 LUT6 hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extras]
+
+Headline workload (BASELINE config 1): BinaryLut6 bit-packed inference forward, 16384 -> 16384 nodes,
+2^20 frames per GPU, Bernoulli(0.5) inputs, random 6-input wiring, random 64-bit tables.  One step is
+one forward over the whole batch.  `value` = node-frames/s with inputs resident in HBM; `e2e` = the same
+through the public operator with HOST buffers (pinned H2D of x, D2H of y inside the timed region).
+Frames shard across ranks with no collective (weak scaling: every rank holds 2^20 frames).
+
+The `fp32` object reports the other half of the metric -- StochasticLut6 / DifferentiableLut6 forward and
+backward on one 8192 -> 8192 layer slice of config 4 -- with the roofline that bounds each (FP32 pipe or HBM).
+
+`--impl reference` times the reference's own CPU implementation (oracle/_ref, the unmodified BinaryBrain
+headers, AVX2 + OpenMP on all host cores) on a bounded frame sample of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_IN = N_OUT = 16384
+FRAMES = 1 << 20
+CPU_SAMPLE_FRAMES = 1 << 18          # bounded sample for the CPU legs (the full batch needs 8 GiB of host copies)
+FALLBACK_HBM_GBS = 6650.0            # the pool's earlier measurement, used only when MEASURED_PEAKS.json is absent
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_binary_lut6 launch (ncu); see profiles/. None until captured.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured", d
+    return FALLBACK_HBM_GBS, "fallback", {}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.thread.join(timeout=2)
+        sm = [float(r[0]) for r in self.rows if len(r) >= 8 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 8 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 8 for i in range(4) if r[4 + i].lower().startswith("active")})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def make_inputs(torch, device, frames, seed):
+    g = torch.Generator(device=device).manual_seed(seed)
+    words = frames // 32
+    x = torch.randint(-2**31, 2**31 - 1, (N_IN, words), dtype=torch.int32, device=device, generator=g)       # Bernoulli(0.5) bits
+    key = torch.rand((N_OUT, N_IN), device=device, generator=g) if N_IN <= 4096 else None
+    if key is not None:
+        idx = key.topk(6, dim=1).indices.to(torch.int32).contiguous()
+    else:   # 6 distinct inputs per node: draw, then re-draw the few rows with a repeat
+        idx = torch.randint(0, N_IN, (N_OUT, 6), device=device, generator=g)
+        for _ in range(8):
+            s = idx.sort(dim=1).values
+            bad = (s[:, 1:] == s[:, :-1]).any(dim=1)
+            if not bool(bad.any()):
+                break
+            idx[bad] = torch.randint(0, N_IN, (int(bad.sum()), 6), device=device, generator=g)
+        idx = idx.to(torch.int32).contiguous()
+    table = torch.randint(-2**31, 2**31 - 1, (N_OUT, 2), dtype=torch.int32, device=device, generator=g)
+    return x, idx, table
+
+
+def cpu_reference_leg(steps, warmup, frames=CPU_SAMPLE_FRAMES):
+    """BinaryLutN<6,Bit>::Forward of the unmodified reference headers (AVX2 + OpenMP), or the C port when _ref is absent."""
+    import numpy as np
+    from oracle import port, ref
+    rng = np.random.default_rng(1)
+    words = frames // 32
+    x = rng.integers(0, 2**32, (N_IN, words), dtype=np.uint64).astype(np.uint32)
+    idx = rng.integers(0, N_IN, (N_OUT, 6)).astype(np.int32)
+    table = rng.integers(-2**31, 2**31, (N_OUT, 2)).astype(np.int32)
+    use_ref = ref.available()
+    times = []
+    for i in range(warmup + steps):
+        if use_ref:
+            t = ref.binary_lut6(x, idx, table, frames)["t_fwd"]
+        else:
+            t0 = time.perf_counter()
+            port.binary_lut6_forward(x, idx, table, frames)
+            t = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(t)
+    cores = ref.num_threads() if use_ref else (os.cpu_count() or 1)
+    per_step = sum(times) / len(times)
+    return {"value": N_OUT * frames / per_step, "unit": "node-frames/s", "cores": cores, "kind": "reference" if use_ref else "port",
+            "sample": f"BinaryLut6 {N_IN}->{N_OUT} nodes, {frames} of {FRAMES} frames per step, mean of {len(times)} steps, "
+                      f"{'bb::BinaryLutN<6,Bit>::Forward AVX2+OpenMP' if use_ref else 'C port, OpenMP'}"}, per_step
+
+
+def fp32_section(torch, ops, steps):
+    """SL6 / DL6 forward and backward on one 8192 -> 8192 node layer, 16384 frames (x, y, dy, dx: 512 MiB each, > L2)."""
+    I = O = 8192
+    F = 16384
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(2)
+    x = torch.rand((I, F), device=dev, generator=g)
+    dy = torch.rand((O, F), device=dev, generator=g)
+    idx = torch.randint(0, I, (O, 6), device=dev, generator=g).to(torch.int32)
+    W = (torch.randn((O, 64), device=dev, generator=g) * 0.01 + 0.5).clamp_(0, 1)
+    dW = torch.zeros((O, 64), device=dev)
+    rm, rv = torch.zeros(O, device=dev), torch.ones(O, device=dev)
+    y = torch.empty((O, F), device=dev)
+    dx = torch.empty((I, F), device=dev)
+    state = {}
+
+    def dl_fwd():
+        state["y"], state["mean"], state["rstd"] = ops.differentiable_lut6_forward_training(x, idx, W, rm, rv, F, y=y, binary=False)
+
+    cases = {
+        "sl6_forward":  (lambda: ops.stochastic_lut6_forward(x, idx, W, F, y=y), 126.0, 8.0),
+        "sl6_backward": (lambda: ops.stochastic_lut6_backward(x, dy, idx, W, dW, I, F, dx=dx), 505.0, 12.0),
+        "dl6_forward_training": (dl_fwd, 136.0, 16.0),
+        "dl6_backward": (lambda: ops.differentiable_lut6_backward(x, dy, idx, W, dW, state["mean"], state["rstd"], I, F, dx=dx, binary=False),
+                         525.0 + 126.0, 24.0),
+    }
+    props = torch.cuda.get_device_properties(0)
+    hbm, which, _ = measured_peaks()
+    out = {"layer": f"{I}->{O} nodes, {F} frames", "fp32_peak_note": "SMs*128 lanes*2*sm_clock at the max SM clock"}
+    fp32_peak = props.multi_processor_count * 128 * 2 * 1.965e9
+    for name, (fn, flops, bytes_) in cases.items():
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        sec = e0.elapsed_time(e1) / 1e3 / steps
+        nf = O * F / sec
+        t_fp, t_hbm = flops / fp32_peak, bytes_ / (hbm * 1e9)
+        out[name] = {"node_frames_per_s": nf, "ms": sec * 1e3, "bound": "fp32" if t_fp > t_hbm else "hbm",
+                     "frac_of_roofline": nf * max(t_fp, t_hbm), "fp32_frac": nf * t_fp, "hbm_frac": nf * t_hbm,
+                     "algorithmic_flops_per_nf": flops, "algorithmic_bytes_per_nf": bytes_}
+    out["hbm_peak"] = f"{hbm} GB/s of {which}"
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--frames", type=int, default=FRAMES, help="frames per GPU (default: the full 2^20 of config 1)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the fp32 section, the e2e leg and the CPU baseline")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    config = {"workload": f"config 1: BinaryLut6 forward {N_IN}->{N_OUT} nodes, 2^20 frames per GPU bit-packed (x, y 2 GiB each)",
+              "frames_per_gpu": args.frames, "sharding": "frames, no collective", "l2": "inputs (2 GiB) exceed L2 (126 MB); no flush"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        base, per_step = cpu_reference_leg(args.steps, args.warmup)
+        line = {"impl": "reference", "metric": "BinaryLut6 forward node-frames/s", "value": base["value"], "unit": "node-frames/s",
+                "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "u32 bit-packed", "data": "synthetic", "config": config,
+                "cpu_baseline": base, "e2e": {"value": base["value"], "unit": "node-frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return 0
+
+    import torch
+    from binarybrain_b200 import abi, ops          # raises if the CUDA library is missing: there is no CPU fallback
+    abi.lib()
+    assert torch.cuda.is_available(), "bench.py --impl ours needs a CUDA device"
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    W = max(args.warmup, 3)
+    frames = args.frames
+    x, idx, table = make_inputs(torch, "cuda", frames, seed=1 + rank)
+    y = torch.empty_like(x)
+
+    def step():
+        ops.binary_lut6_forward(x, idx, table, frames, y=y)
+
+    for _ in range(W):
+        step()
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    # keep the sampler alive long enough to have seen the loaded clocks at least a few times
+    t_keep = time.time()
+    while len(sampler.rows) < 3 and time.time() - t_keep < 1.0:
+        step()
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
+    if dist:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    sec_per_step = ms / 1e3 / args.steps
+    value = world * N_OUT * frames / sec_per_step
+
+    hbm, which, _ = measured_peaks()
+    algo_bytes = frames * (N_IN + N_OUT) / 8 + 32 * N_OUT            # x + y bit rows, wiring + table per node
+    achieved = algo_bytes / sec_per_step / 1e9
+    line = {"metric": "BinaryLut6 forward node-frames/s", "value": value, "unit": "node-frames/s", "n_gpus": world, "steps": args.steps,
+            "warmup": W, "ms_per_step": sec_per_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u32 bit-packed", "data": "synthetic", "config": config, "clocks": clocks, "gpu_launches": args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": f"of {which}", "kernel": "k_binary_lut6",
+                         "algorithmic_bytes_per_launch": algo_bytes}}
+
+    if not args.no_extras:
+        # end to end through the operator with host buffers: H2D of x, kernel, D2H of y, every step
+        hx = torch.empty(x.shape, dtype=torch.int32).pin_memory()
+        hy = torch.empty(y.shape, dtype=torch.int32).pin_memory()
+        hx.copy_(x)
+        torch.cuda.synchronize()
+        k = max(2, min(args.steps, 5))
+        for i in range(1 + k):
+            if i == 1:
+                torch.cuda.synchronize()
+                if dist:
+                    dist.barrier()
+                t0 = time.perf_counter()
+            x.copy_(hx, non_blocking=True)
+            step()
+            hy.copy_(y, non_blocking=True)
+            torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+        dt = time.perf_counter() - t0
+        if dist:
+            t = torch.tensor([dt], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        line["e2e"] = {"value": world * N_OUT * frames / (dt / k), "unit": "node-frames/s", "h2d_bytes_per_step": hx.numel() * 4,
+                       "d2h_bytes_per_step": hy.numel() * 4, "steps": k}
+        del hx, hy
+        if rank == 0:
+            del x, y
+            torch.cuda.empty_cache()
+            line["fp32"] = fp32_section(torch, ops, max(3, min(args.steps, 10)))
+            if world == 1:
+                line["cpu_baseline"], _ = cpu_reference_leg(3, 1)
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -108,7 +108,9 @@ def _dl6_fp32_check(ops, x, idx, W, dy, rm0, rv0, fl, stride=None):
     yh = host_fp32(y, F)
     assert err(mean.cpu().numpy(), p["mean"]) <= TOL
     amp = max(1.0, 0.3 * float(p["rstd"].max()))
-    assert np.abs(rstd.cpu().numpy() / p["rstd"] - 1).max() <= 1e-4
+    # rstd = 1/sqrt(var) with var = E[y^2] - mean^2 taken in fp32 by both sides: what can be held is the variance to a few
+    # ulps of E[y^2] ~ 0.25 (3e-8 each), whatever that is relative to a variance that may sit near its 1e-5 floor
+    assert np.abs(1.0 / rstd.cpu().numpy().astype(np.float64) ** 2 - 1.0 / p["rstd"].astype(np.float64) ** 2).max() <= 2e-7
     assert err(rm.cpu().numpy(), p["running_mean"]) <= TOL and err(rv.cpu().numpy(), p["running_var"]) <= TOL
     if fl["binary"]:
         bad = yh != p["y"]
