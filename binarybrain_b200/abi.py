@@ -51,6 +51,8 @@ SIGNATURES = {
     "bbcu_fp32_DifferentiableLut6_ForwardStats": (_i, [_vp] * 5 + [_f] + [_i] * 5 + [_vp]),
     "bbcu_fp32_DifferentiableLut6_ForwardNormalize": (_i, [_vp] * 6 + [_f] * 3 + [_i] * 3 + [_ll, _i, _vp]),
     "bbcu_fp32_DifferentiableLut6_BackwardStats": (_i, [_vp] * 7 + [_f] * 3 + [_i] * 5 + [_vp]),
+    "bbcu_fp32_DifferentiableLut6_ForwardTraining_NoAlloc": (_i, [_vp] * 8 + [_f] * 4 + [_i] * 5 + [_vp]),
+    "bbcu_fp32_DifferentiableLut6_ForwardTraining_NoAlloc_MaxNodes": (_i, []),
     "bbcu_fp32_DifferentiableLut6_BackwardApply": (_i, [_vp] * 11 + [_f] * 3 + [_i] * 4 + [_ll, _i, _i, _vp]),
 }
 

@@ -22,7 +22,7 @@
  *
  * Results follow the reference's CPU branches (the header-only path in include/bb), which is what
  * parity is measured against; where the reference's old CUDA kernels differ from its CPU code the
- * CPU code wins (see DESIGN.md).  dev_dx_tmp and dev_reverse_index of the backward operators are
+ * CPU code wins.  dev_dx_tmp and dev_reverse_index of the backward operators are
  * accepted for signature compatibility and are not read or written: dx is accumulated with
  * vector reductions in L2 instead of a [nodes*6][frames] temporary.
  */
@@ -195,6 +195,20 @@ int bbcu_fp32_DifferentiableLut6_BackwardApply(const float *dev_x_buf, const flo
                                                float gamma, float beta, float unbinarize_bias, int input_node_size, int output_node_size,
                                                int frame_size, int frame_stride, long long total_frame_size,
                                                int lut_binarize, int binary_mode, bbcu_stream_t stream);
+
+/* ------------------------------------------------------------------ Additive: a training forward that allocates nothing.
+ * No counterpart in the reference.  Same arguments and results as bbcu_fp32_DifferentiableLut6_ForwardTraining, for callers that
+ * cannot tolerate a cudaMalloc inside the call (a pre-planned device-memory budget, or a latency path that must not take
+ * cudaMalloc's implicit device synchronisation): the per-node fp64 sums live in a fixed 1 MiB array inside the library's device
+ * image instead of heap scratch.  node_size above ..._MaxNodes() (65536) returns BBCU_ERR_TOO_LARGE.  All calls on a device share
+ * that array: calls whose GPU work may overlap race, so keep them on one stream.  The first call on each device resolves the
+ * array's address and should be made outside of stream capture. */
+int bbcu_fp32_DifferentiableLut6_ForwardTraining_NoAlloc(const float *dev_x_buf, float *dev_y_buf, const int *dev_input_index, const float *dev_W,
+                                                         float *dev_mean_buf, float *dev_rstd_buf, float *dev_running_mean_buf,
+                                                         float *dev_running_var_buf, float gamma, float beta, float momentum,
+                                                         float unbinarize_bias, int node_size, int frame_size, int frame_stride,
+                                                         int lut_binarize, int binary_mode, bbcu_stream_t stream);
+int bbcu_fp32_DifferentiableLut6_ForwardTraining_NoAlloc_MaxNodes(void);
 
 #ifdef __cplusplus
 }
