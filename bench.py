@@ -188,6 +188,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--frames", type=int, default=FRAMES, help="frames per GPU (default: the full 2^20 of config 1)")
     ap.add_argument("--no-extras", action="store_true", help="skip the fp32 section, the e2e leg and the CPU baseline")
+    ap.add_argument("--fp32-only", action="store_true", help="run and print only the fp32 section (profiling aid)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -216,6 +217,9 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if args.fp32_only:
+        print(json.dumps({"fp32": fp32_section(torch, ops, max(1, args.steps))}))
+        return 0
     W = max(args.warmup, 3)
     frames = args.frames
     x, idx, table = make_inputs(torch, "cuda", frames, seed=1 + rank)

@@ -8,7 +8,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libbbcu_b200.so")
+LIB_PATH = os.environ.get("BBCU_B200_LIB") or os.path.join(_HERE, "lib", "libbbcu_b200.so")
 
 _vp, _i, _f, _ll, _sz = C.c_void_p, C.c_int, C.c_float, C.c_longlong, C.c_size_t
 

@@ -9,6 +9,8 @@
 // Mapping: one warp per output node, one 128-bit load per lane and input row, so a warp reads 512
 // contiguous bytes of each of its six rows per iteration; CTAs of consecutive node groups share a
 // word tile so the tile's input rows stay in L2 for the ~6 nodes that read each of them.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace bb200 {
@@ -90,6 +92,82 @@ k_binary_lut6(const BlArgs a)
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Two-pipe variant (the one the launcher uses for aligned rows).
+//   * Level 1 of the tree only ever produces one of {0, x0, ~x0, ~0}.  In two's complement that is
+//     x0 * a + b with (a, b) in {(0,0), (1,0), (-1,-1), (0,-1)}: an integer multiply-add, which issues to the
+//     FMA pipe and leaves the 31 selects of levels 2..6 to the INT/logic pipe, so the two pipes split the
+//     63 ops per 32 frames about evenly instead of the logic pipe taking all of them.
+//   * The 32 (a, b) pairs of a node are derived by 32 lanes in parallel (lane k does pair k) and exchanged
+//     through shared memory, instead of every lane deriving all 64 values.
+//   * Each lane carries 8 words (two 128-bit loads per input row) per iteration.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t lut6_word_imad(uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3, uint32_t x4, uint32_t x5,
+                                                   const int2 (&ab)[32])
+{
+    uint32_t v[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) v[k] = x0 * (uint32_t)ab[k].x + (uint32_t)ab[k].y;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) v[k] = (v[2 * k] & ~x1) | (v[2 * k + 1] & x1);
+#pragma unroll
+    for (int k = 0; k < 8; ++k)  v[k] = (v[2 * k] & ~x2) | (v[2 * k + 1] & x2);
+#pragma unroll
+    for (int k = 0; k < 4; ++k)  v[k] = (v[2 * k] & ~x3) | (v[2 * k + 1] & x3);
+#pragma unroll
+    for (int k = 0; k < 2; ++k)  v[k] = (v[2 * k] & ~x4) | (v[2 * k + 1] & x4);
+    return (v[0] & ~x5) | (v[1] & x5);
+}
+
+__global__ void __launch_bounds__(kBlWarps * 32)
+k_binary_lut6_2pipe(const BlArgs a)
+{
+    __shared__ int2 s_ab[kBlWarps][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x / a.groups;
+    const int node = (blockIdx.x % a.groups) * kBlWarps + warp;
+    if (node >= a.O) return;
+    {
+        // lane k: table bits 2k (x0 = 0) and 2k+1 (x0 = 1) -> (a, b)
+        const uint32_t t  = (uint32_t)__ldg(a.table + 2 * (size_t)node + (lane >> 4));
+        const uint32_t lo = (t >> ((2 * lane) & 31)) & 1u, hi = (t >> ((2 * lane + 1) & 31)) & 1u;
+        s_ab[warp][lane] = make_int2((int)hi - (int)lo, -(int)lo);
+        __syncwarp();
+    }
+    int2 ab[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) ab[k] = s_ab[warp][k];
+    const uint32_t *rows[6];
+#pragma unroll
+    for (int j = 0; j < 6; ++j) rows[j] = a.x + (size_t)__ldg(a.idx + (size_t)node * 6 + j) * a.stride;
+    uint32_t *yrow = a.y + (size_t)node * a.stride;
+
+    const int w_begin = tile * a.Tw;
+    const int w_end   = min(a.nwords, w_begin + a.Tw);
+    for (int w = w_begin + 4 * lane; w < w_end; w += 256) {
+        const bool second = (w + 128) < w_end;
+        uint4 lo[6], hi[6];
+#pragma unroll
+        for (int j = 0; j < 6; ++j) {
+            lo[j] = __ldg(reinterpret_cast<const uint4 *>(rows[j] + w));
+            hi[j] = second ? __ldg(reinterpret_cast<const uint4 *>(rows[j] + w + 128)) : make_uint4(0, 0, 0, 0);
+        }
+        uint4 o;
+        o.x = lut6_word_imad(lo[0].x, lo[1].x, lo[2].x, lo[3].x, lo[4].x, lo[5].x, ab);
+        o.y = lut6_word_imad(lo[0].y, lo[1].y, lo[2].y, lo[3].y, lo[4].y, lo[5].y, ab);
+        o.z = lut6_word_imad(lo[0].z, lo[1].z, lo[2].z, lo[3].z, lo[4].z, lo[5].z, ab);
+        o.w = lut6_word_imad(lo[0].w, lo[1].w, lo[2].w, lo[3].w, lo[4].w, lo[5].w, ab);
+        *reinterpret_cast<uint4 *>(yrow + w) = o;
+        if (second) {
+            o.x = lut6_word_imad(hi[0].x, hi[1].x, hi[2].x, hi[3].x, hi[4].x, hi[5].x, ab);
+            o.y = lut6_word_imad(hi[0].y, hi[1].y, hi[2].y, hi[3].y, hi[4].y, hi[5].y, ab);
+            o.z = lut6_word_imad(hi[0].z, hi[1].z, hi[2].z, hi[3].z, hi[4].z, hi[5].z, ab);
+            o.w = lut6_word_imad(hi[0].w, hi[1].w, hi[2].w, hi[3].w, hi[4].w, hi[5].w, ab);
+            *reinterpret_cast<uint4 *>(yrow + w + 128) = o;
+        }
+    }
+}
+
 }   // namespace bb200
 
 using namespace bb200;
@@ -115,8 +193,10 @@ extern "C" int bbcu_bit_BinaryLut6_Forward(const int *x, int *y, const int *idx,
     a.Tw = ((tf / 32 + 127) / 128) * 128;
     const long long blocks = (long long)((a.nwords + a.Tw - 1) / a.Tw) * a.groups;
     BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
-    if (vec) k_binary_lut6<true><<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
-    else     k_binary_lut6<false><<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
+    static const int variant = []() { const char *e = getenv("BB200_BL6_VARIANT"); return e ? atoi(e) : 1; }();
+    if (vec && variant == 1) k_binary_lut6_2pipe<<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
+    else if (vec)            k_binary_lut6<true><<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
+    else                     k_binary_lut6<false><<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
     return launch_status();
 }
 

@@ -42,7 +42,7 @@ __device__ __forceinline__ void stage_table(float2 *tab, const float *__restrict
 // binary mode maps x to 0.5 +/- bias by (x > 0.5), otherwise x is clipped to [0, 1].
 __device__ __forceinline__ float condition_x(float v, int binary, float bias)
 {
-    return binary ? (0.5f + (v > 0.5f ? bias : -bias)) : fminf(1.0f, fmaxf(0.0f, v));
+    return binary ? (0.5f + (v > 0.5f ? bias : -bias)) : __saturatef(v);     // one FADD.SAT: clip to [0, 1]
 }
 
 __device__ __forceinline__ float lut6_forward(const float2 *tab, const float (&x)[6])
