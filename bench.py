@@ -29,6 +29,8 @@ sys.path.insert(0, ROOT)
 
 N_IN = N_OUT = 16384
 FRAMES = 1 << 20
+TRAIN_NODES = 65536                  # config 4 layer width
+TRAIN_FRAMES = 4096                  # frames per GPU and step in the training section (6 saved activations of 1 GiB each)
 CPU_SAMPLE_FRAMES = 1 << 18          # bounded sample for the CPU legs (the full batch needs 8 GiB of host copies)
 FALLBACK_HBM_GBS = 6650.0            # the pool's earlier measurement, used only when MEASURED_PEAKS.json is absent
 # dram__bytes_read.sum + dram__bytes_write.sum of one k_binary_lut6 launch (ncu); see profiles/. None until captured.
@@ -180,6 +182,66 @@ def fp32_section(torch, ops, steps):
     return out
 
 
+def train_section(torch, ops, dist, world, rank, steps):
+    """Config-4 style training step, frame-sharded: 6 stacked DifferentiableLut6 layers of TRAIN_NODES nodes (fp32, batch norm on),
+    TRAIN_FRAMES frames per GPU (global batch = that x world), MSE loss on the last layer, backward with the per-layer dW all-reduce
+    overlapped with the next layer's backward, Adam.  Reports forward+backward node-frames/s over all ranks."""
+    from binarybrain_b200.dist import ShardedDifferentiableLut6
+    nodes, frames, layers_n = TRAIN_NODES, TRAIN_FRAMES, 6
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(3)          # same seed on every rank: replicated wiring and tables
+    layers = []
+    for _ in range(layers_n):
+        idx = torch.randint(0, nodes, (nodes, 6), device=dev, generator=g).to(torch.int32)
+        W = (torch.randn((nodes, 64), device=dev, generator=g) * 0.01 + 0.5).clamp_(0, 1)
+        layers.append(ShardedDifferentiableLut6(idx, W, nodes, binary=False))
+    opt = ops.Adam([l.W for l in layers], [l.dW for l in layers])
+    gd = torch.Generator(device=dev).manual_seed(100 + rank)  # each rank draws its own frame shard
+    x0 = torch.rand((nodes, frames), device=dev, generator=gd)
+    target = torch.rand((nodes, frames), device=dev, generator=gd)
+    total = frames * world
+    acts = [torch.empty((nodes, frames), device=dev) for _ in range(layers_n)]
+    grads = [torch.empty((nodes, frames), device=dev) for _ in range(2)]
+
+    def step():
+        h = x0
+        for l, a in zip(layers, acts):
+            ops.clamp_(l.W)
+            h = l.forward(h, frames, total, y=a)
+        dy = grads[0]
+        torch.sub(h, target, out=dy)
+        dy.mul_(2.0 / (total * nodes))                       # d/dy of the mean squared error over the GLOBAL batch
+        for k, l in enumerate(reversed(layers)):
+            dy = l.backward(dy, dx=grads[(k + 1) % 2])
+        for l in layers:
+            l.wait_grad()
+        opt.update()
+
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if dist:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    sec = ms / 1e3 / steps
+    return {"workload": f"config 4 (frame-sharded training): {layers_n} x DifferentiableLut6 {nodes}->{nodes}, {frames} frames per GPU "
+                        f"(global batch {total}), fp32, batch norm, MSE, Adam; dW all-reduce overlapped with backward",
+            "node_frames_per_s": layers_n * nodes * total / sec, "ms_per_step": sec * 1e3, "steps": steps, "n_gpus": world,
+            "allreduce_bytes_per_step": layers_n * (nodes * 64 * 4 + 2 * nodes * 2 * 8) if world > 1 else 0}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -294,9 +356,10 @@ def main():
             dt = float(t.item())
         line["e2e"] = {"value": world * N_OUT * frames / (dt / k), "unit": "node-frames/s", "h2d_bytes_per_step": hx.numel() * 4,
                        "d2h_bytes_per_step": hy.numel() * 4, "steps": k}
-        del hx, hy
+        del hx, hy, x, y
+        torch.cuda.empty_cache()
+        line["train"] = train_section(torch, ops, dist, world, rank, max(2, min(args.steps, 5)))
         if rank == 0:
-            del x, y
             torch.cuda.empty_cache()
             line["fp32"] = fp32_section(torch, ops, max(3, min(args.steps, 10)))
             if world == 1:

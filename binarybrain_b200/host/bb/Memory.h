@@ -1,0 +1,271 @@
+// bb::Memory / bb::Tensor_ / bb::FrameBuffer -- host-side containers in BinaryBrain's style over the
+// bbcu_* C ABI.
+//
+// Same roles and layout as the reference's include/bb/Memory.h:45-823, Tensor.h and FrameBuffer.h:269-1720:
+// a lazily mirrored host/device pair with dirty flags, fp32 / bit frame buffers that are node-major and
+// frame-contiguous with rows padded to 256 bits (FrameBuffer.h:28-46,414-417).  Differences by design:
+// device memory comes from the per-device caching heap of libbbcu_b200 (bbcu_LocalHeap_*), copies are
+// cudaMemcpyAsync on the layer stream followed by one stream sync when the HOST side needs the data, and
+// there are no ref-counted lock objects: Host()/Dev() return the pointer after making that side current.
+#pragma once
+
+#include <cuda_runtime_api.h>
+
+#include <cstdint>
+#include <cstring>
+#include <memory>
+#include <sstream>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "bbcu_b200.h"
+
+#define BB_TYPE_BIT   (0x0000 + 1)
+#define BB_TYPE_FP32  (0x0100 + 32)
+#define BB_TYPE_INT32 (0x0200 + 32)
+
+namespace bb {
+
+using index_t   = std::int64_t;
+using indices_t = std::vector<index_t>;
+
+struct Bit {};   // tag type: one bit per frame, 32 frames per 32-bit word, LSB first
+
+template <typename T> struct DataType;
+template <> struct DataType<float>        { static constexpr int type = BB_TYPE_FP32;  static const char *Name() { return "fp32"; } };
+template <> struct DataType<Bit>          { static constexpr int type = BB_TYPE_BIT;   static const char *Name() { return "bit"; } };
+template <> struct DataType<std::int32_t> { static constexpr int type = BB_TYPE_INT32; static const char *Name() { return "int32"; } };
+
+inline int DataType_GetBitSize(int type) { return type == BB_TYPE_BIT ? 1 : 32; }
+
+inline index_t CalcShapeSize(indices_t const &shape)
+{
+    index_t n = 1;
+    for (auto s : shape) n *= s;
+    return n;
+}
+
+// BinaryBrain's BB_ASSERT under BB_ASSERT_EXCEPTION (include/bb/Assert.h:24-42): a C++ exception, never exit().
+#define BB_ASSERT(cond) \
+    do { if (!(cond)) { std::ostringstream os_; os_ << "BB_ASSERT(" #cond ") failed at " << __FILE__ << ":" << __LINE__; \
+                        throw std::runtime_error(os_.str()); } } while (0)
+
+inline void bbcu_check(int status, char const *what)
+{
+    if (status != 0) {
+        throw std::runtime_error(std::string(what) + ": " + bbcu_b200_error_string(status));
+    }
+}
+#define BBCU_CHECK(call) ::bb::bbcu_check((call), #call)
+
+inline void cuda_check(cudaError_t e, char const *what)
+{
+    if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+}
+#define BB_CUDA_CHECK(call) ::bb::cuda_check((call), #call)
+
+
+class Manager
+{
+public:
+    static bool IsDeviceAvailable() { return bbcu_IsDeviceAvailable() != 0; }
+    static void SetHostOnly(bool h) { bbcu_SetHostOnly(h ? 1 : 0); }
+    static int  GetDeviceCount()    { return bbcu_GetDeviceCount(); }
+    static void SetDevice(int d)    { bbcu_SetDevice(d); }
+    // The stream every layer enqueues on (default stream unless a caller installs another one).
+    static cudaStream_t &Stream() { static cudaStream_t s = nullptr; return s; }
+};
+
+
+// Host/device mirrored byte buffer.
+class Memory
+{
+    std::size_t                 m_size = 0;
+    std::vector<std::uint8_t>   m_host;
+    void                       *m_dev = nullptr;
+    bool                        m_host_valid = true;    // host copy holds the current contents
+    bool                        m_dev_valid  = false;   // device copy holds the current contents
+
+public:
+    Memory() {}
+    explicit Memory(std::size_t size) { Resize(size); }
+    Memory(Memory const &) = delete;
+    Memory &operator=(Memory const &) = delete;
+    ~Memory() { if (m_dev) bbcu_LocalHeap_Free(m_dev); }
+
+    void Resize(std::size_t size)
+    {
+        if (m_dev) { bbcu_LocalHeap_Free(m_dev); m_dev = nullptr; }
+        m_size = size;
+        m_host.assign(size, 0);
+        m_host_valid = true;
+        m_dev_valid  = false;
+    }
+    std::size_t GetSize() const { return m_size; }
+
+    // new_buf: the caller overwrites everything, so nothing is copied (reference: Lock(true)).
+    void *Host(bool new_buf = false)
+    {
+        if (!m_host_valid && !new_buf && m_dev) {
+            BB_CUDA_CHECK(cudaMemcpyAsync(m_host.data(), m_dev, m_size, cudaMemcpyDeviceToHost, Manager::Stream()));
+            BB_CUDA_CHECK(cudaStreamSynchronize(Manager::Stream()));
+        }
+        m_host_valid = true;
+        m_dev_valid  = false;
+        return m_host.data();
+    }
+    void const *HostConst()
+    {
+        if (!m_host_valid && m_dev) {
+            BB_CUDA_CHECK(cudaMemcpyAsync(m_host.data(), m_dev, m_size, cudaMemcpyDeviceToHost, Manager::Stream()));
+            BB_CUDA_CHECK(cudaStreamSynchronize(Manager::Stream()));
+        }
+        m_host_valid = true;
+        return m_host.data();
+    }
+    void *Dev(bool new_buf = false)
+    {
+        DevConst(new_buf);
+        m_host_valid = false;
+        return m_dev;
+    }
+    void const *DevConst(bool new_buf = false)
+    {
+        BB_ASSERT(Manager::IsDeviceAvailable());     // no CPU fallback behind the operators
+        if (!m_dev) {
+            m_dev = bbcu_LocalHeap_Malloc(m_size);
+            if (!m_dev) throw std::runtime_error("bbcu_LocalHeap_Malloc: device memory exhausted");
+            m_dev_valid = false;
+        }
+        if (!m_dev_valid && !new_buf && m_size) {
+            // pageable host memory: the runtime stages the copy before returning, so m_host may change afterwards
+            BB_CUDA_CHECK(cudaMemcpyAsync(m_dev, m_host.data(), m_size, cudaMemcpyHostToDevice, Manager::Stream()));
+        }
+        m_dev_valid = true;
+        return m_dev;
+    }
+};
+
+
+// Dense typed tensor (parameters, statistics, tables).
+template <typename T>
+class Tensor_
+{
+    indices_t               m_shape;
+    std::shared_ptr<Memory> m_mem = std::make_shared<Memory>();
+
+public:
+    Tensor_() {}
+    explicit Tensor_(indices_t shape) { Resize(shape); }
+    void Resize(indices_t shape) { m_shape = shape; m_mem->Resize(sizeof(T) * (std::size_t)CalcShapeSize(shape)); }
+    void Resize(index_t n) { Resize(indices_t{n}); }
+    indices_t GetShape() const { return m_shape; }
+    index_t   GetSize()  const { return CalcShapeSize(m_shape); }
+    T       *Host(bool new_buf = false) { return static_cast<T *>(m_mem->Host(new_buf)); }
+    T const *HostConst() const          { return static_cast<T const *>(m_mem->HostConst()); }
+    T       *Dev(bool new_buf = false)  { return static_cast<T *>(m_mem->Dev(new_buf)); }
+    T const *DevConst() const           { return static_cast<T const *>(m_mem->DevConst()); }
+    void Fill(T v) { T *p = Host(true); for (index_t i = 0; i < GetSize(); ++i) p[i] = v; }
+    void FillZero() { std::memset(m_mem->Host(true), 0, m_mem->GetSize()); }
+    T  operator()(index_t i, index_t j) const { return HostConst()[i * m_shape.back() + j]; }
+    std::vector<T> ToVector() const { T const *p = HostConst(); return std::vector<T>(p, p + GetSize()); }
+    void FromVector(std::vector<T> const &v) { BB_ASSERT((index_t)v.size() == GetSize()); std::memcpy(Host(true), v.data(), sizeof(T) * v.size()); }
+};
+
+using Tensor = Tensor_<float>;
+
+
+// [node][frame] buffer of fp32 or bit frames.
+class FrameBuffer
+{
+    index_t                 m_frame_size = 0;
+    index_t                 m_frame_stride = 0;     // BYTES per node row (reference: GetFrameStride())
+    indices_t               m_shape;
+    int                     m_type = 0;
+    std::shared_ptr<Memory> m_mem;
+
+public:
+    FrameBuffer() {}
+    FrameBuffer(index_t frame_size, indices_t shape, int data_type, bool /*host_only*/ = false) { Resize(frame_size, shape, data_type); }
+
+    // rows are padded to 256 bits (include/bb/FrameBuffer.h:414-417)
+    static index_t CalcFrameStride(int data_type, index_t frame_size)
+    {
+        return ((frame_size * DataType_GetBitSize(data_type) + 255) / 256) * (256 / 8);
+    }
+
+    void Resize(index_t frame_size, indices_t shape, int data_type)
+    {
+        BB_ASSERT(data_type == BB_TYPE_FP32 || data_type == BB_TYPE_BIT);
+        m_frame_size   = frame_size;
+        m_frame_stride = CalcFrameStride(data_type, frame_size);
+        m_shape        = shape;
+        m_type         = data_type;
+        m_mem          = std::make_shared<Memory>((std::size_t)(m_frame_stride * CalcShapeSize(shape)));
+    }
+
+    bool      Empty()          const { return !m_mem; }
+    int       GetType()        const { return m_type; }
+    index_t   GetFrameSize()   const { return m_frame_size; }
+    index_t   GetFrameStride() const { return m_frame_stride; }
+    index_t   GetNodeSize()    const { return CalcShapeSize(m_shape); }
+    indices_t GetShape()       const { return m_shape; }
+    bool      IsDeviceAvailable() const { return Manager::IsDeviceAvailable(); }
+
+    void       *LockDeviceMemory(bool new_buf = false) { return m_mem->Dev(new_buf); }
+    void const *LockDeviceMemoryConst() const          { return m_mem->DevConst(); }
+    void       *LockMemory(bool new_buf = false)       { return m_mem->Host(new_buf); }
+    void const *LockMemoryConst() const                { return m_mem->HostConst(); }
+
+    void FillZero() { std::memset(m_mem->Host(true), 0, m_mem->GetSize()); }
+
+    // element access on the host mirror (slow path, as in the reference: FrameBuffer.h:1077-1146)
+    float GetFP32(index_t frame, index_t node) const
+    {
+        auto base = static_cast<std::uint8_t const *>(m_mem->HostConst()) + node * m_frame_stride;
+        if (m_type == BB_TYPE_FP32) return reinterpret_cast<float const *>(base)[frame];
+        return (float)((reinterpret_cast<std::uint32_t const *>(base)[frame >> 5] >> (frame & 31)) & 1u);
+    }
+    void SetFP32(index_t frame, index_t node, float v)
+    {
+        auto base = static_cast<std::uint8_t *>(m_mem->Host()) + node * m_frame_stride;
+        if (m_type == BB_TYPE_FP32) { reinterpret_cast<float *>(base)[frame] = v; return; }
+        auto &w = reinterpret_cast<std::uint32_t *>(base)[frame >> 5];
+        std::uint32_t m = 1u << (frame & 31);
+        if (v > 0.5f) w |= m; else w &= ~m;            // include/bb/DataType.h:612-647, LSB first
+    }
+
+    // dense [frame][node] host array -> buffer (what FromNumpy receives from Python: frames on axis 0)
+    void SetFrameMajor(float const *src)
+    {
+        index_t nodes = GetNodeSize();
+        auto base = static_cast<std::uint8_t *>(m_mem->Host(true));
+        std::memset(base, 0, m_mem->GetSize());
+        for (index_t n = 0; n < nodes; ++n) {
+            auto row = base + n * m_frame_stride;
+            if (m_type == BB_TYPE_FP32) {
+                for (index_t f = 0; f < m_frame_size; ++f) reinterpret_cast<float *>(row)[f] = src[f * nodes + n];
+            } else {
+                for (index_t f = 0; f < m_frame_size; ++f)
+                    if (src[f * nodes + n] > 0.5f) reinterpret_cast<std::uint32_t *>(row)[f >> 5] |= 1u << (f & 31);
+            }
+        }
+    }
+    void GetFrameMajor(float *dst) const
+    {
+        index_t nodes = GetNodeSize();
+        auto base = static_cast<std::uint8_t const *>(m_mem->HostConst());
+        for (index_t n = 0; n < nodes; ++n) {
+            auto row = base + n * m_frame_stride;
+            if (m_type == BB_TYPE_FP32) {
+                for (index_t f = 0; f < m_frame_size; ++f) dst[f * nodes + n] = reinterpret_cast<float const *>(row)[f];
+            } else {
+                for (index_t f = 0; f < m_frame_size; ++f)
+                    dst[f * nodes + n] = (float)((reinterpret_cast<std::uint32_t const *>(row)[f >> 5] >> (f & 31)) & 1u);
+            }
+        }
+    }
+};
+
+}   // namespace bb

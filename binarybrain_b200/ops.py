@@ -217,3 +217,31 @@ class Adam:
     def update(self):          # Optimizer::Update = Step + ZeroGrad (include/bb/Optimizer.h:29-33)
         self.step()
         self.zero_grad()
+
+
+# ------------------------------------------------------------------------------------------ frame-sharded halves
+def dl6_forward_stats(x, idx, W, frames, y, sums, bias=BIAS, lut_binarize=False, binary=True):
+    """Pass 1 of the training forward on this rank's frames: raw LUT values into y, per-node (sum y, sum y^2) into sums [O,2] fp64."""
+    abi.call("bbcu_fp32_DifferentiableLut6_ForwardStats", _p(x), _p(y), _p(idx), _p(W), _p(sums), bias, idx.shape[0], frames, x.shape[1],
+             int(lut_binarize), int(binary), _stream())
+
+
+def dl6_forward_normalize(y, sums, mean, rstd, running_mean, running_var, frames, total_frames, gamma=0.3, beta=0.5, momentum=0.9, binary=True):
+    """Pass 2: statistics from the (all-reduced) sums over total_frames, then normalise y in place."""
+    abi.call("bbcu_fp32_DifferentiableLut6_ForwardNormalize", _p(y), _p(sums), _p(mean), _p(rstd), _p(running_mean), _p(running_var), gamma, beta,
+             momentum, y.shape[0], frames, y.shape[1], int(total_frames), int(binary), _stream())
+
+
+def dl6_backward_stats(x, dy, idx, W, mean, rstd, frames, sums, gamma=0.3, beta=0.5, bias=BIAS, lut_binarize=False, binary=True):
+    abi.call("bbcu_fp32_DifferentiableLut6_BackwardStats", _p(x), _p(dy), _p(idx), _p(W), _p(mean), _p(rstd), _p(sums), gamma, beta, bias,
+             idx.shape[0], frames, x.shape[1], int(lut_binarize), int(binary), _stream())
+
+
+def dl6_backward_apply(x, dy, dx, idx, W, dW, mean, rstd, sums, n_in, frames, total_frames, gamma=0.3, beta=0.5, bias=BIAS, lut_binarize=False,
+                       binary=True):
+    O = idx.shape[0]
+    dmean = torch.empty(O, dtype=torch.float32, device=dy.device)
+    dvar = torch.empty(O, dtype=torch.float32, device=dy.device)
+    abi.call("bbcu_fp32_DifferentiableLut6_BackwardApply", _p(x), _p(dy), _p(dx), _p(idx), _p(W), _p(dW), _p(mean), _p(rstd), _p(sums), _p(dmean),
+             _p(dvar), gamma, beta, bias, n_in, O, frames, dy.shape[1], int(total_frames), int(lut_binarize), int(binary), _stream())
+    return dx

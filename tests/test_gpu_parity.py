@@ -402,3 +402,40 @@ def test_adam_100_steps(ops, golden):
         assert np.abs(W.cpu().numpy() - golden[key + "_W100"]).max() <= 1e-4
         if bn:
             assert np.abs(rm.cpu().numpy() - golden["adam_rm100"]).max() <= 1e-4
+
+
+def test_frame_sharded_halves_equal_the_whole(ops):
+    """ForwardStats|ForwardNormalize and BackwardStats|BackwardApply on two frame shards, with the [O,2] fp64 sums added by
+    hand (what the all-reduce does), against the unsharded operators on the same GPU."""
+    from gpu_util import dev, wiring
+    rng = np.random.default_rng(21)
+    I, O, F = 300, 500, 1024
+    idx, W = dev(wiring(rng, I, O)), dev(np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32))
+    x, dy = dev(rng.random((I, F), dtype=np.float32)), dev(rng.random((O, F), dtype=np.float32))
+    rm, rv = torch.zeros(O, device="cuda"), torch.ones(O, device="cuda")
+    y_w, mean_w, rstd_w = ops.differentiable_lut6_forward_training(x, idx, W, rm, rv, F, binary=False)
+    dW_w = torch.zeros((O, 64), device="cuda")
+    dx_w = ops.differentiable_lut6_backward(x, dy, idx, W, dW_w, mean_w, rstd_w, I, F, binary=False)
+    cuts = [(0, 384), (384, 1024)]
+    xs = [x[:, b:e].contiguous() for b, e in cuts]
+    dys = [dy[:, b:e].contiguous() for b, e in cuts]
+    ys = [torch.empty((O, e - b), device="cuda") for b, e in cuts]
+    sums = [torch.zeros((O, 2), dtype=torch.float64, device="cuda") for _ in cuts]
+    for k, (b, e) in enumerate(cuts):
+        ops.dl6_forward_stats(xs[k], idx, W, e - b, ys[k], sums[k], binary=False)
+    total = sums[0] + sums[1]
+    mean, rstd = torch.empty(O, device="cuda"), torch.empty(O, device="cuda")
+    for k, (b, e) in enumerate(cuts):
+        rm2, rv2 = torch.zeros(O, device="cuda"), torch.ones(O, device="cuda")
+        ops.dl6_forward_normalize(ys[k], total, mean, rstd, rm2, rv2, e - b, F, binary=False)
+    assert torch.allclose(mean, mean_w, atol=1e-6) and torch.allclose(rstd, rstd_w, rtol=1e-4)
+    assert torch.allclose(rm2, rm, atol=1e-6) and torch.allclose(rv2, rv, atol=1e-6)
+    assert torch.allclose(torch.cat(ys, 1), y_w, atol=2e-4)
+    for k, (b, e) in enumerate(cuts):
+        ops.dl6_backward_stats(xs[k], dys[k], idx, W, mean_w, rstd_w, e - b, sums[k], binary=False)
+    total = sums[0] + sums[1]
+    dW = torch.zeros((O, 64), device="cuda")
+    dxs = [ops.dl6_backward_apply(xs[k], dys[k], torch.empty((I, e - b), device="cuda"), idx, W, dW, mean_w, rstd_w, total, I, e - b, F, binary=False)
+           for k, (b, e) in enumerate(cuts)]
+    assert torch.allclose(torch.cat(dxs, 1), dx_w, rtol=1e-4, atol=1e-4 * float(dx_w.abs().max()))
+    assert torch.allclose(dW, dW_w, rtol=1e-4, atol=1e-4 * float(dW_w.abs().max()))

@@ -1,0 +1,206 @@
+"""Host side above the C ABI: the C++ bb:: classes behind the pybind11 module `binarybrain_b200.core`.
+
+CPU tests: library exports vs include/bbcu_b200.h, seeded wiring / table initialisation against the reference's
+own draws (golden), FrameBuffer layout.  GPU tests: the layer classes end to end against the oracle, the way
+the reference's tests drive them (create, set_input_shape, copy wiring and W, forward, backward, optimizer).
+"""
+import os
+import re
+
+import numpy as np
+import pytest
+
+from oracle import port, pack_bits
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def core():
+    from binarybrain_b200 import build
+    build.build_all()
+    import binarybrain_b200.core as c
+    return c
+
+
+def test_library_exports_every_declared_symbol():
+    """The C-ABI library loads and exports each function include/bbcu_b200.h declares (no compute call: works without a GPU)."""
+    import ctypes
+    from binarybrain_b200 import abi, build
+    lib = ctypes.CDLL(build.build_library())
+    text = open(os.path.join(ROOT, "include", "bbcu_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = set(re.findall(r"\b(bbcu_[A-Za-z0-9_]+)\s*\(", text))
+    assert len(names) >= 40
+    missing = [n for n in sorted(names) if not hasattr(lib, n)]
+    assert not missing, missing
+    assert set(abi.SIGNATURES) == names          # the ctypes table covers the header, no more, no less
+    assert lib.bbcu_b200_abi_version() == 1
+    lib.bbcu_b200_error_string.restype = ctypes.c_char_p
+    assert lib.bbcu_b200_error_string(-1).startswith(b"bbcu_b200")
+
+
+def test_missing_library_fails_loudly(tmp_path):
+    from binarybrain_b200 import abi
+    with pytest.raises(ImportError):
+        abi.load(str(tmp_path / "nope.so"))
+
+
+def test_seeded_wiring_and_tables_match_the_reference(core, golden):
+    lut = core.DifferentiableLut6_fp32_fp32.create([16], seed=1)
+    lut.set_input_shape([32])
+    assert (lut.get_connection() == golden["init_32_16_s1_idx"]).all()
+    assert np.array_equal(lut.W().numpy(), golden["init_32_16_s1_W"])
+    big = core.DifferentiableLut6_fp32_fp32.create([1024], seed=1)
+    big.set_input_shape([784])
+    idx = big.get_connection()
+    assert (idx[:8] == golden["init_784_1024_s1_idx_head"]).all()
+    assert int(idx.astype(np.int64).sum()) == int(golden["init_784_1024_s1_idx_sum"][0])
+    assert np.array_equal(big.W().numpy()[:2], golden["init_784_1024_s1_W_head"])
+    assert all(len(set(r)) == 6 for r in idx.tolist())            # six distinct inputs per node
+    # the stochastic layer draws the same way; a different seed gives a different table
+    sl = core.StochasticLut6_fp32_fp32.create([16], seed=1)
+    sl.set_input_shape([32])
+    assert (sl.get_connection() == golden["init_32_16_s1_idx"]).all()
+    other = core.DifferentiableLut6_fp32_fp32.create([16], seed=2)
+    other.set_input_shape([32])
+    assert (other.get_connection() != golden["init_32_16_s1_idx"]).any()
+
+
+def test_framebuffer_layout_and_numpy_round_trip(core):
+    rng = np.random.default_rng(0)
+    a = rng.random((39, 5), dtype=np.float32)                  # [frames, nodes]
+    fb = core.FrameBuffer.from_numpy_fp32(a, core.TYPE_FP32)
+    assert fb.get_frame_size() == 39 and fb.get_node_size() == 5
+    assert fb.get_frame_stride() == 160 == core.FrameBuffer.calc_frame_stride(core.TYPE_FP32, 39)     # 40 floats: rows padded to 32 bytes
+    assert np.array_equal(fb.numpy_fp32(), a)
+    assert fb.get_fp32(7, 3) == a[7, 3]
+    bits = (a > 0.5).astype(np.float32)
+    fbb = core.FrameBuffer.from_numpy_fp32(a, core.TYPE_BIT)
+    assert fbb.get_frame_stride() == 32 == core.FrameBuffer.calc_frame_stride(core.TYPE_BIT, 39)       # 256 bits
+    assert np.array_equal(fbb.numpy_fp32(), bits)
+    fbb.set_fp32(0, 0, 1.0 - bits[0, 0])
+    assert fbb.get_fp32(0, 0) == 1.0 - bits[0, 0]
+    shaped = core.FrameBuffer(8, [3, 4], core.TYPE_FP32)
+    assert shaped.get_node_shape() == [3, 4] and shaped.get_node_size() == 12
+
+
+def test_commands_and_defaults(core):
+    lut = core.DifferentiableLut6_fp32_fp32.create([4])
+    assert lut.get_model_name() == "DifferentiableLut6" and lut.get_gamma() == pytest.approx(0.3) and lut.get_beta() == 0.5
+    lut.send_command("binary false")
+    lut.send_command("lut_binarize true")
+    lut.send_command("momentum 0.5")
+    with pytest.raises(RuntimeError):
+        lut.send_command("host_only true")                      # no CPU branch in this build
+    with pytest.raises(RuntimeError):
+        lut.set_input_shape([8])
+        lut.set_node_connection_index(0, 0, 99)                 # out of range
+
+
+# ------------------------------------------------------------------------------------------------ GPU
+def _copy_layer(layer, idx, W):
+    layer.set_connection(idx)
+    layer.W().set_numpy(W)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("binary,lut_binarize", [(False, False), (True, True)])
+def test_differentiable_lut6_layer_against_oracle(core, binary, lut_binarize):
+    rng = np.random.default_rng(4)
+    I, O, F = 64, 48, 200
+    lut = core.DifferentiableLut6_fp32_fp32.create([O], momentum=0.9)
+    lut.send_command("binary " + ("true" if binary else "false"))
+    lut.send_command("lut_binarize " + ("true" if lut_binarize else "false"))
+    lut.set_input_shape([I])
+    idx = lut.get_connection()
+    W = np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32)
+    lut.W().set_numpy(W)
+    x = rng.random((F, I), dtype=np.float32)
+    dy = rng.random((F, O), dtype=np.float32)
+    y = lut.forward(core.FrameBuffer.from_numpy_fp32(x), True).numpy_fp32()
+    dx = lut.backward(core.FrameBuffer.from_numpy_fp32(dy)).numpy_fp32()
+    p = port.dl6_forward_train(x.T.copy(), idx, W, np.zeros(O), np.ones(O), binary=int(binary), lut_binarize=int(lut_binarize))
+    dx_w, dW_w = port.dl6_backward(x.T.copy(), dy.T.copy(), idx, W, p["mean"], p["rstd"], I, binary=int(binary), lut_binarize=int(lut_binarize))
+    amp = max(1.0, 0.3 * float(p["rstd"].max()))
+    if binary:
+        assert (y.T != p["y"]).mean() < 1e-3
+    else:
+        assert np.abs(y.T - p["y"]).max() <= 3e-5 * amp
+    assert np.abs(lut.get_mean().numpy() - p["running_mean"]).max() <= 1e-5
+    pre = p["y_pre"]
+    if not ((np.abs(pre) < 1e-4 * amp) | (np.abs(pre - 1) < 1e-4 * amp)).any():
+        assert np.abs(dx.T - dx_w).max() <= 1e-4 * amp * max(1.0, np.abs(dx_w).max())
+        assert np.abs(lut.dW().numpy() - dW_w).max() <= 1e-4 * amp * max(1.0, np.abs(dW_w).max())
+    # inference uses the running statistics
+    yi = lut.forward(core.FrameBuffer.from_numpy_fp32(x), False).numpy_fp32()
+    pi = port.dl6_forward_infer(x.T.copy(), idx, W, p["running_mean"], p["running_var"], binary=int(binary), lut_binarize=int(lut_binarize))
+    assert (np.abs(yi.T - pi["y"]) > 1e-4).mean() < 1e-3
+
+
+@pytest.mark.gpu
+def test_bit_layers_and_binary_lut_import(core):
+    rng = np.random.default_rng(6)
+    I, O, F = 40, 24, 333
+    x = (rng.random((F, I)) > 0.5).astype(np.float32)
+    xb = pack_bits(x.T)
+    dl = core.DifferentiableLut6_bit_fp32.create([O], momentum=0.9)
+    dl.set_input_shape([I])
+    W = np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32)
+    dl.W().set_numpy(W)
+    idx = dl.get_connection()
+    y = dl.forward(core.FrameBuffer.from_numpy_fp32(x, core.TYPE_BIT), True).numpy_fp32()
+    p = port.dl6_forward_train(xb, idx, W, np.zeros(O), np.ones(O), frames=F)
+    assert (y.T != p["y"]).mean() < 1e-3
+    dy = rng.random((F, O), dtype=np.float32)
+    dx = dl.backward(core.FrameBuffer.from_numpy_fp32(dy)).numpy_fp32()
+    dx_w, _ = port.dl6_backward(xb, dy.T.copy(), idx, W, p["mean"], p["rstd"], I)
+    assert np.abs(dx.T - dx_w).max() <= 1e-3 * max(1.0, np.abs(dx_w).max())
+    # StochasticLutN<6,Bit>: fp32 output
+    sl = core.StochasticLut6_bit_fp32.create([O])
+    sl.set_input_shape([I])
+    sl.send_command("lut_binarize false")
+    _copy_layer(sl, idx, W)
+    ys = sl.forward(core.FrameBuffer.from_numpy_fp32(x, core.TYPE_BIT), True).numpy_fp32()
+    assert np.abs(ys.T - port.sl6_forward(xb, idx, W, frames=F)).max() <= 1e-5
+    # freeze the trained layer into truth tables (table[i] = W[i] >= 0.5) and run the bit-packed inference layer
+    bl = core.BinaryLut6_bit_fp32.create([O])
+    bl.import_layer(dl)
+    table = np.zeros((O, 2), np.int32)
+    tb = (W >= 0.5)
+    for i in range(64):
+        table[:, i >> 5] |= (tb[:, i].astype(np.int64) << (i & 31)).astype(np.uint32).view(np.int32)
+        assert bl.get_lut_table(3, i) == bool(tb[3, i])
+    yb = bl.forward(core.FrameBuffer.from_numpy_fp32(x, core.TYPE_BIT), False).numpy_fp32()
+    want = port.binary_lut6_forward(xb, idx, table, F)
+    from oracle import unpack_bits
+    assert (yb.T == unpack_bits(want, F)).all()
+
+
+@pytest.mark.gpu
+def test_stochastic_layer_sbn_and_adam(core, golden):
+    rng = np.random.default_rng(8)
+    # StochasticLutN fp32 + OptimizerAdam: 100 steps against the reference's run (no batch norm, tables N(0.5, 0.01))
+    idx, x, dy = golden["adam_idx"], golden["adam_x"], golden["adam_dy"]
+    O = idx.shape[0]
+    sl = core.DifferentiableLut6_fp32_fp32.create([O], batch_norm=False, binary=False)
+    sl.set_input_shape([x.shape[0]])
+    _copy_layer(sl, idx, golden["adamnobn_W0"])
+    opt = core.OptimizerAdam_fp32.create()
+    opt.set_variables(sl.W(), sl.dW())
+    xb, dyb = core.FrameBuffer.from_numpy_fp32(x.T.copy()), core.FrameBuffer.from_numpy_fp32(dy.T.copy())
+    for _ in range(100):
+        sl.forward(xb, True)
+        sl.backward(dyb)
+        opt.update()
+    assert np.abs(sl.W().numpy() - golden["adamnobn_W100"]).max() <= 1e-4
+    # StochasticBatchNormalization
+    a = rng.random((200, 8), dtype=np.float32)
+    bn = core.StochasticBatchNormalization_fp32.create()
+    y = bn.forward(core.FrameBuffer.from_numpy_fp32(a), True).numpy_fp32()
+    p = port.sbn_forward_train(a.T.copy(), np.zeros(8), np.ones(8))
+    assert np.abs(y.T - p["y"]).max() <= 2e-5
+    g = rng.random((200, 8), dtype=np.float32)
+    dx = bn.backward(core.FrameBuffer.from_numpy_fp32(g)).numpy_fp32()
+    assert np.abs(dx.T - port.sbn_backward(a.T.copy(), g.T.copy(), p["mean"], p["rstd"])).max() <= 2e-5
+    assert np.abs(bn.get_mean().numpy() - p["running_mean"]).max() <= 1e-6
