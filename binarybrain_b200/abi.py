@@ -16,6 +16,7 @@ _vp, _i, _f, _ll, _sz = C.c_void_p, C.c_int, C.c_float, C.c_longlong, C.c_size_t
 SIGNATURES = {
     "bbcu_b200_error_string": (C.c_char_p, [_i]),
     "bbcu_b200_abi_version": (_i, []),
+    "bbcu_b200_device_fault": (_i, []),
     "bbcu_GetDeviceCount": (_i, []),
     "bbcu_GetDevice": (_i, []),
     "bbcu_SetDevice": (None, [_i]),

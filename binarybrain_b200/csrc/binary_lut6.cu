@@ -12,6 +12,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "async_copy.cuh"
 
 namespace bb200 {
 
@@ -102,8 +103,9 @@ k_binary_lut6(const BlArgs a)
 //     through shared memory, instead of every lane deriving all 64 values.
 //   * Each lane carries 8 words (two 128-bit loads per input row) per iteration.
 // ---------------------------------------------------------------------------------------------
+template <typename AB>     // AB: int2[32] in registers, or a pointer to the warp's 32 pairs in shared memory
 __device__ __forceinline__ uint32_t lut6_word_imad(uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3, uint32_t x4, uint32_t x5,
-                                                   const int2 (&ab)[32])
+                                                   const AB &ab)
 {
     uint32_t v[32];
 #pragma unroll
@@ -168,6 +170,141 @@ k_binary_lut6_2pipe(const BlArgs a)
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Persistent, bulk-copy-pipelined variant (aligned rows; the launcher's default).
+// Work item = (word tile of 256 words, group of 8 nodes); CTA c takes items c, c + gridDim, ... so the CTAs in
+// flight sweep the node groups of one tile together and the tile's rows stay in L2.  Each warp owns one node of
+// the group and runs its own two-stage pipeline: lane 0 starts six 1 KiB bulk copies (one per gathered row) for
+// item j+2 as soon as item j has been read out of shared memory into registers, then the warp computes item j
+// while the copies of j+1 and j+2 are in flight.  No warp ever waits on a load it has only just issued, and no
+// CTA-wide barrier exists after set-up.
+// ---------------------------------------------------------------------------------------------
+constexpr int kPipeWords  = 256;                      // words per row segment and item (1 KiB)
+constexpr int kPipeStages = 2;
+// dynamic shared memory layout: [rows: warp x stage x 6 x 256 words][barriers: warp x stage, padded to 128 B][level-1 pairs: warp x 32 x int2]
+constexpr int kPipeRowsBytes = kBlWarps * kPipeStages * 6 * kPipeWords * 4;
+constexpr int kPipeBarBytes  = 128;
+constexpr int kPipeAbBytes   = kBlWarps * 32 * 8;
+constexpr int kPipeSmem      = kPipeRowsBytes + kPipeBarBytes + kPipeAbBytes;
+static_assert(kBlWarps * kPipeStages * 8 <= kPipeBarBytes, "barrier block too small");
+
+struct PipeItem {
+    int node, w0, nw;     // node (clamped for loads), first word, words in this tile (multiple of 4)
+    bool store;
+};
+
+__device__ __forceinline__ bool pipe_item(const BlArgs &a, long long it, long long n_items, int warp, PipeItem &p)
+{
+    if (it >= n_items) return false;
+    const int tile  = (int)(it / a.groups);
+    const int group = (int)(it % a.groups);
+    const int node  = group * kBlWarps + warp;
+    p.store = node < a.O;
+    p.node  = p.store ? node : a.O - 1;
+    p.w0    = tile * kPipeWords;
+    p.nw    = min(kPipeWords, a.nwords - p.w0);
+    return true;
+}
+
+__device__ __forceinline__ void pipe_issue(const BlArgs &a, const PipeItem &p, uint32_t *stage, uint64_t *bar)
+{
+    const uint32_t bytes = (uint32_t)p.nw * 4u;
+    mbar_arrive_expect_tx(bar, 6u * bytes);
+#pragma unroll
+    for (int j = 0; j < 6; ++j) {
+        const uint32_t *src = a.x + (size_t)__ldg(a.idx + (size_t)p.node * 6 + j) * a.stride + p.w0;
+        bulk_copy_g2s(stage + j * kPipeWords, src, bytes, bar);
+    }
+}
+
+__global__ void __launch_bounds__(kBlWarps * 32, 2)
+k_binary_lut6_pipe(const BlArgs a, long long n_items, int *fault)
+{
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    uint32_t *s_rows = reinterpret_cast<uint32_t *>(smem_raw);                                   // [warp][stage][6][256]
+    uint64_t *s_bar  = reinterpret_cast<uint64_t *>(smem_raw + kPipeRowsBytes);                   // [warp][stage]
+    int2     *s_ab   = reinterpret_cast<int2 *>(smem_raw + kPipeRowsBytes + kPipeBarBytes);      // [warp][32]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint32_t *my_rows = s_rows + (size_t)warp * kPipeStages * 6 * kPipeWords;
+    uint64_t *my_bar  = s_bar + warp * kPipeStages;
+    int2     *my_ab   = s_ab + warp * 32;
+
+    if (lane == 0) {
+        for (int s = 0; s < kPipeStages; ++s) mbar_init(my_bar + s, 1);
+        mbar_init_fence();
+    }
+    __syncwarp();
+
+    // prologue: items 0 and 1 of this CTA
+    PipeItem cur, nxt;
+    long long it = blockIdx.x;
+    const long long step = gridDim.x;
+    if (lane == 0) {
+        PipeItem p;
+        if (pipe_item(a, it, n_items, warp, p))        pipe_issue(a, p, my_rows, my_bar);
+        if (pipe_item(a, it + step, n_items, warp, p)) pipe_issue(a, p, my_rows + 6 * kPipeWords, my_bar + 1);
+    }
+    uint32_t tword = 0;
+    if (pipe_item(a, it, n_items, warp, cur)) tword = (uint32_t)__ldg(a.table + 2 * (size_t)cur.node + (lane >> 4));
+
+    for (int k = 0; pipe_item(a, it, n_items, warp, cur); ++k, it += step) {
+        const int s = k & 1;
+        const uint32_t parity = (uint32_t)(k >> 1) & 1u;
+        uint32_t *stage = my_rows + s * 6 * kPipeWords;
+
+        // this node's level-1 (a, b) pairs; the table word of the NEXT item is fetched now and used next round
+        {
+            const uint32_t lo = (tword >> ((2 * lane) & 31)) & 1u, hi = (tword >> ((2 * lane + 1) & 31)) & 1u;
+            __syncwarp();
+            my_ab[lane] = make_int2((int)hi - (int)lo, -(int)lo);
+            __syncwarp();
+        }
+        const bool have_next = pipe_item(a, it + step, n_items, warp, nxt);
+        if (have_next) tword = (uint32_t)__ldg(a.table + 2 * (size_t)nxt.node + (lane >> 4));
+        const int2 *ab = my_ab;
+
+        if (!mbar_wait(my_bar + s, parity)) {          // bounded: record the fault, let the other stage's copies land, leave
+            if (lane == 0) atomicCAS(fault, 0, kFaultBarrierTimeout);
+            if (have_next) mbar_wait(my_bar + (s ^ 1), (uint32_t)((k + 1) >> 1) & 1u);
+            return;
+        }
+        const int w = 4 * lane;
+        uint4 lo[6], hi[6];
+#pragma unroll
+        for (int j = 0; j < 6; ++j) {
+            lo[j] = *reinterpret_cast<const uint4 *>(stage + j * kPipeWords + w);
+            hi[j] = *reinterpret_cast<const uint4 *>(stage + j * kPipeWords + w + 128);
+        }
+        __syncwarp();                                   // every lane has read the stage out
+        if (lane == 0) {
+            PipeItem p;
+            if (pipe_item(a, it + 2 * step, n_items, warp, p)) {
+                proxy_fence_async();                    // reads above (generic proxy) before the refill (async proxy)
+                pipe_issue(a, p, stage, my_bar + s);
+            }
+        }
+
+        uint32_t *yrow = a.y + (size_t)cur.node * a.stride + cur.w0;
+        if (cur.store && w < cur.nw) {
+            uint4 o;
+            o.x = lut6_word_imad(lo[0].x, lo[1].x, lo[2].x, lo[3].x, lo[4].x, lo[5].x, ab);
+            o.y = lut6_word_imad(lo[0].y, lo[1].y, lo[2].y, lo[3].y, lo[4].y, lo[5].y, ab);
+            o.z = lut6_word_imad(lo[0].z, lo[1].z, lo[2].z, lo[3].z, lo[4].z, lo[5].z, ab);
+            o.w = lut6_word_imad(lo[0].w, lo[1].w, lo[2].w, lo[3].w, lo[4].w, lo[5].w, ab);
+            *reinterpret_cast<uint4 *>(yrow + w) = o;
+        }
+        if (cur.store && w + 128 < cur.nw) {
+            uint4 o;
+            o.x = lut6_word_imad(hi[0].x, hi[1].x, hi[2].x, hi[3].x, hi[4].x, hi[5].x, ab);
+            o.y = lut6_word_imad(hi[0].y, hi[1].y, hi[2].y, hi[3].y, hi[4].y, hi[5].y, ab);
+            o.z = lut6_word_imad(hi[0].z, hi[1].z, hi[2].z, hi[3].z, hi[4].z, hi[5].z, ab);
+            o.w = lut6_word_imad(hi[0].w, hi[1].w, hi[2].w, hi[3].w, hi[4].w, hi[5].w, ab);
+            *reinterpret_cast<uint4 *>(yrow + w + 128) = o;
+        }
+    }
+}
+
 }   // namespace bb200
 
 using namespace bb200;
@@ -193,8 +330,27 @@ extern "C" int bbcu_bit_BinaryLut6_Forward(const int *x, int *y, const int *idx,
     a.Tw = ((tf / 32 + 127) / 128) * 128;
     const long long blocks = (long long)((a.nwords + a.Tw - 1) / a.Tw) * a.groups;
     BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
-    static const int variant = []() { const char *e = getenv("BB200_BL6_VARIANT"); return e ? atoi(e) : 1; }();
-    if (vec && variant == 1) k_binary_lut6_2pipe<<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
+    static const int variant = []() { const char *e = getenv("BB200_BL6_VARIANT"); return e ? atoi(e) : 2; }();
+    if (vec && variant == 2) {
+        // persistent pipeline: two CTAs per SM, each walking (tile, node group) items
+        static bool attr_done[64] = {};              // the opt-in to > 48 KB of dynamic shared memory is per device
+        const int dev_id = bbcu_GetDevice();
+        bool attr_ok = dev_id >= 0 && dev_id < 64 && attr_done[dev_id];
+        if (!attr_ok && dev_id >= 0 && dev_id < 64) {
+            attr_ok = cudaFuncSetAttribute(k_binary_lut6_pipe, cudaFuncAttributeMaxDynamicSharedMemorySize, kPipeSmem) == cudaSuccess;
+            attr_done[dev_id] = attr_ok;
+            if (!attr_ok) cudaGetLastError();
+        }
+        int *fault = fault_word();
+        if (attr_ok && fault != nullptr) {
+            const long long n_items = (long long)((a.nwords + kPipeWords - 1) / kPipeWords) * a.groups;
+            long long grid = 2LL * device_info().sm_count;
+            if (grid > n_items) grid = n_items;
+            k_binary_lut6_pipe<<<(unsigned)grid, kBlWarps * 32, kPipeSmem, as_stream(stream)>>>(a, n_items, fault);
+            return launch_status();
+        }
+    }
+    if (vec && variant >= 1) k_binary_lut6_2pipe<<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
     else if (vec)            k_binary_lut6<true><<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
     else                     k_binary_lut6<false><<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
     return launch_status();

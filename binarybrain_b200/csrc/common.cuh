@@ -36,6 +36,9 @@ void *stream_scratch(cudaStream_t stream, size_t bytes);
 // while that still leaves enough CTAs to fill the machine.
 int frame_tile(long long rows_touched, int bits_per_row_frame, int node_groups, int frame_size, int max_tile);
 
+// Per-device int in global memory (zero until a kernel records a fault); allocated once, never freed.
+int *fault_word();
+
 inline cudaStream_t as_stream(bbcu_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
 }   // namespace bb200

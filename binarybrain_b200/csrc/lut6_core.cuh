@@ -172,3 +172,65 @@ __device__ __forceinline__ double warp_sum(double v)
 }
 
 }   // namespace bb200
+
+// ---------------------------------------------------------------------------------------------------
+// Packed-pair arithmetic (sm_100 f32x2): one instruction does the same fp32 operation on two frames held in a
+// 64-bit register pair, so the 63-lerp tree of two frames costs 94 issue slots instead of 188.  Each lane carries
+// NP pairs; the tree is walked depth first (a node's value is produced and consumed before its sibling subtree is
+// started), which keeps about one live value per level and pair instead of 32.
+// ---------------------------------------------------------------------------------------------------
+namespace bb200 {
+
+typedef unsigned long long f32x2;
+
+__device__ __forceinline__ f32x2 pack2(float a, float b) { f32x2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ void unpack2(f32x2 v, float &a, float &b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) { f32x2 d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) { f32x2 d; asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { f32x2 d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) { f32x2 d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+
+// Per-node table for the packed path: 32 entries of (w, w, d, d), i.e. level 1 reads both packed operands with one 128-bit load.
+__device__ __forceinline__ void stage_table_x2(float4 *tab, const float *__restrict__ W, int node, int lane, int lut_binarize)
+{
+    __syncwarp();
+    float2 v = reinterpret_cast<const float2 *>(W + (size_t)node * 64)[lane];
+    if (lut_binarize) {
+        v.x = v.x > 0.5f ? 1.0f : 0.0f;
+        v.y = v.y > 0.5f ? 1.0f : 0.0f;
+    }
+    const float d = v.y - v.x;
+    tab[lane] = make_float4(v.x, v.x, d, d);
+    __syncwarp();
+}
+
+template <int L, int K, int NP>
+struct LerpTree {
+    // value of node K at level L for NP frame pairs; x[j][p] is input j of pair p
+    static __device__ __forceinline__ void eval(const float4 *tab, const f32x2 (&x)[6][NP], f32x2 (&out)[NP])
+    {
+        f32x2 a[NP], b[NP];
+        LerpTree<L - 1, 2 * K, NP>::eval(tab, x, a);
+        LerpTree<L - 1, 2 * K + 1, NP>::eval(tab, x, b);
+#pragma unroll
+        for (int p = 0; p < NP; ++p) out[p] = fma2(x[L - 1][p], sub2(b[p], a[p]), a[p]);
+    }
+};
+
+template <int K, int NP>
+struct LerpTree<1, K, NP> {
+    static __device__ __forceinline__ void eval(const float4 *tab, const f32x2 (&x)[6][NP], f32x2 (&out)[NP])
+    {
+        const ulonglong2 wd = *reinterpret_cast<const ulonglong2 *>(tab + K);     // .x = (w, w), .y = (d, d)
+#pragma unroll
+        for (int p = 0; p < NP; ++p) out[p] = fma2(x[0][p], wd.y, wd.x);
+    }
+};
+
+template <int NP>
+__device__ __forceinline__ void lut6_forward_x2(const float4 *tab, const f32x2 (&x)[6][NP], f32x2 (&y)[NP])
+{
+    LerpTree<6, 0, NP>::eval(tab, x, y);
+}
+
+}   // namespace bb200

@@ -9,7 +9,10 @@
 // Schedule: a CTA is 8 warps = 8 consecutive output nodes working on one frame tile; consecutive CTAs
 // walk the node groups of the SAME frame tile, so the input rows of that tile are fetched from HBM once
 // and then hit in L2 for the other ~5 nodes that read them.
+#include <type_traits>
+
 #include "common.cuh"
+#include "async_copy.cuh"
 #include "lut6_core.cuh"
 
 namespace bb200 {
@@ -72,14 +75,14 @@ template <bool XBIT, int PHASE, bool YBIT>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, BB200_FWD_CTAS)
 k_lut6_forward(const FwdArgs a)
 {
-    __shared__ float2 s_tab[kWarpsPerCta][32];
+    __shared__ float4 s_tab[kWarpsPerCta][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x / a.groups;
     const int node = (blockIdx.x % a.groups) * kWarpsPerCta + warp;
     if (node >= a.O) return;
 
-    float2 *tab = s_tab[warp];
-    stage_table(tab, a.W, node, lane, a.lut_binarize);
+    float4 *tab = s_tab[warp];
+    stage_table_x2(tab, a.W, node, lane, a.lut_binarize);
     int rows[6];
 #pragma unroll
     for (int j = 0; j < 6; ++j) rows[j] = __ldg(a.idx + (size_t)node * 6 + j);
@@ -98,15 +101,19 @@ k_lut6_forward(const FwdArgs a)
     for (int base = f_begin; base < f_end; base += kFramesPerIter) {
         float xv[4][6];
         gather_x<XBIT>(xv, a.x, a.xs, rows, base, lane, a.F, a.binary, a.bias);
+        // frames q = 0,1 and q = 2,3 of this lane travel as two packed pairs through one walk of the tree
+        f32x2 xp[6][2], yp[2];
+#pragma unroll
+        for (int j = 0; j < 6; ++j) { xp[j][0] = pack2(xv[0][j], xv[1][j]); xp[j][1] = pack2(xv[2][j], xv[3][j]); }
+        lut6_forward_x2<2>(tab, xp, yp);
+        float vq[4];
+        unpack2(yp[0], vq[0], vq[1]);
+        unpack2(yp[1], vq[2], vq[3]);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const int f = base + 32 * q + lane;
             const bool live = f < a.F;
-            float v = lut6_forward(tab, xv[q]);
-            // order the four frames' trees one after the other (an empty asm that makes the next frame's first input
-            // depend on this frame's result): interleaving them only multiplies the live registers, and occupancy is
-            // what hides the gather latency here
-            if (q < 3) asm volatile("" : "+f"(xv[q + 1][0]) : "f"(v));
+            float v = vq[q];
             if (PHASE == PH_STATS) {
                 if (live) { s1 += (double)v; s2 += (double)v * (double)v; }
                 if (!YBIT && live) a.y[(size_t)node * a.ys + f] = v;
@@ -120,7 +127,7 @@ k_lut6_forward(const FwdArgs a)
                     if (lane == 0 && base + 32 * q < a.F) a.ybits[(size_t)node * a.ys + ((base >> 5) + q)] = m;
                 } else if (live) {
                     if (PHASE == PH_NORM && a.binary) v = v > 0.5f ? 1.0f : 0.0f;
-                    else                              v = fmaxf(0.0f, fminf(1.0f, v));
+                    else                              v = __saturatef(v);
                     a.y[(size_t)node * a.ys + f] = v;
                 }
             }
@@ -132,6 +139,165 @@ k_lut6_forward(const FwdArgs a)
         if (lane == 0) {
             atomicAdd(a.sums + 2 * (size_t)node, s1);
             atomicAdd(a.sums + 2 * (size_t)node + 1, s2);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Persistent, bulk-copy-pipelined forward for fp32 inputs with 16-byte aligned rows (the launcher's default).
+// Work item = (frame tile of a.T = 128 or 256 frames, group of 8 nodes); CTA c takes items c, c + gridDim, ... so
+// the CTAs in flight sweep the node groups of one tile together and the tile's rows stay in L2.  Each warp owns one
+// node of the group and runs its own two-stage pipeline: lane 0 starts seven bulk copies (six gathered row
+// segments and the node's 64 table entries) for item j+2 once item j has been read out of shared memory, and the
+// warp computes item j while the copies of j+1 (and j+2) are in flight.
+// ---------------------------------------------------------------------------------------------
+constexpr int kFpMaxItemFrames = 256;
+constexpr int kFpStages        = 2;
+constexpr int kFpStageBytes    = 6 * kFpMaxItemFrames * 4 + 256;                       // six row segments + raw W[64]
+constexpr int kFpRowsBytes     = kWarpsPerCta * kFpStages * kFpStageBytes;
+constexpr int kFpBarBytes      = 128;
+constexpr int kFpTabBytes      = kWarpsPerCta * 32 * 16;
+constexpr int kFpSmem          = kFpRowsBytes + kFpBarBytes + kFpTabBytes;
+static_assert(kWarpsPerCta * kFpStages * 8 <= kFpBarBytes, "barrier block too small");
+
+struct FpItem {
+    int node, f0, nf, nc;     // node (clamped for loads), first frame, valid frames, floats to copy per row (multiple of 4)
+    bool store;
+};
+
+__device__ __forceinline__ bool fp_item(const FwdArgs &a, long long it, long long n_items, int warp, FpItem &p)
+{
+    if (it >= n_items) return false;
+    const int tile  = (int)(it / a.groups);
+    const int group = (int)(it % a.groups);
+    const int node  = group * kWarpsPerCta + warp;
+    p.store = node < a.O;
+    p.node  = p.store ? node : a.O - 1;
+    p.f0    = tile * a.T;
+    p.nf    = min(a.T, a.F - p.f0);
+    p.nc    = (int)min((long long)a.T, a.xs - p.f0);
+    return true;
+}
+
+__device__ __forceinline__ void fp_issue(const FwdArgs &a, const FpItem &p, unsigned char *stage, uint64_t *bar)
+{
+    const uint32_t bytes = (uint32_t)p.nc * 4u;
+    mbar_arrive_expect_tx(bar, 6u * bytes + 256u);
+    const float *xf = static_cast<const float *>(a.x);
+#pragma unroll
+    for (int j = 0; j < 6; ++j) {
+        const float *src = xf + (size_t)__ldg(a.idx + (size_t)p.node * 6 + j) * a.xs + p.f0;
+        bulk_copy_g2s(stage + j * (kFpMaxItemFrames * 4), src, bytes, bar);
+    }
+    bulk_copy_g2s(stage + 6 * kFpMaxItemFrames * 4, a.W + (size_t)p.node * 64, 256u, bar);
+}
+
+template <int PHASE>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, 2)
+k_lut6_forward_pipe(const FwdArgs a, long long n_items, int *fault)
+{
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned char *my_stages = smem_raw + (size_t)warp * kFpStages * kFpStageBytes;
+    uint64_t *my_bar = reinterpret_cast<uint64_t *>(smem_raw + kFpRowsBytes) + warp * kFpStages;
+    float4   *tab    = reinterpret_cast<float4 *>(smem_raw + kFpRowsBytes + kFpBarBytes) + warp * 32;
+
+    if (lane == 0) {
+        for (int s = 0; s < kFpStages; ++s) mbar_init(my_bar + s, 1);
+        mbar_init_fence();
+    }
+    __syncwarp();
+
+    long long it = blockIdx.x;
+    const long long step = gridDim.x;
+    FpItem cur, nxt;
+    if (lane == 0) {
+        FpItem p;
+        if (fp_item(a, it, n_items, warp, p))        fp_issue(a, p, my_stages, my_bar);
+        if (fp_item(a, it + step, n_items, warp, p)) fp_issue(a, p, my_stages + kFpStageBytes, my_bar + 1);
+    }
+    // per-node batch-norm constants travel one item ahead of their use
+    float mean_n = 0.0f, scale_n = 0.0f;
+    if (PHASE == PH_NORM && fp_item(a, it, n_items, warp, cur)) { mean_n = a.mean[cur.node]; scale_n = a.rstd[cur.node]; }
+
+    for (int k = 0; fp_item(a, it, n_items, warp, cur); ++k, it += step) {
+        const int s = k & 1;
+        const uint32_t parity = (uint32_t)(k >> 1) & 1u;
+        unsigned char *stage = my_stages + s * kFpStageBytes;
+        float mean = mean_n, scale = scale_n;
+        if (PHASE == PH_NORM && a.stat_is_var) scale = 1.0f / sqrtf(scale);        // DifferentiableLutN.h:866-868
+        const bool have_next = fp_item(a, it + step, n_items, warp, nxt);
+        if (PHASE == PH_NORM && have_next) { mean_n = a.mean[nxt.node]; scale_n = a.rstd[nxt.node]; }
+
+        if (!mbar_wait(my_bar + s, parity)) {          // bounded: record the fault, let the other stage's copies land, leave
+            if (lane == 0) atomicCAS(fault, 0, kFaultBarrierTimeout);
+            if (have_next) mbar_wait(my_bar + (s ^ 1), (uint32_t)((k + 1) >> 1) & 1u);
+            return;
+        }
+        {   // raw W[64] -> 32 x (w, w, d, d)
+            float2 v = reinterpret_cast<const float2 *>(stage + 6 * kFpMaxItemFrames * 4)[lane];
+            if (a.lut_binarize) { v.x = v.x > 0.5f ? 1.0f : 0.0f; v.y = v.y > 0.5f ? 1.0f : 0.0f; }
+            const float d = v.y - v.x;
+            __syncwarp();
+            tab[lane] = make_float4(v.x, v.x, d, d);
+            __syncwarp();
+        }
+        double s1 = 0.0, s2 = 0.0;
+        const float *xs0 = reinterpret_cast<const float *>(stage);
+        // one walk of the tree carries NP frame pairs per lane: 4 pairs (256 frames per warp) when the item is that wide
+        auto walk = [&](auto np_tag, int h) {
+            constexpr int NP = decltype(np_tag)::value;
+            f32x2 xp[6][NP], yp[NP];
+#pragma unroll
+            for (int j = 0; j < 6; ++j) {
+                const float *r = xs0 + j * kFpMaxItemFrames + h + lane;
+#pragma unroll
+                for (int p = 0; p < NP; ++p)
+                    xp[j][p] = pack2(condition_x(r[64 * p], a.binary, a.bias), condition_x(r[64 * p + 32], a.binary, a.bias));
+            }
+            if (h + 64 * NP >= cur.nf) {
+                // last read of this stage: hand it back to the copy engine for item k+2 before doing the math
+                __syncwarp();
+                if (lane == 0) {
+                    FpItem p;
+                    if (fp_item(a, it + 2 * step, n_items, warp, p)) {
+                        proxy_fence_async();
+                        fp_issue(a, p, stage, my_bar + s);
+                    }
+                }
+            }
+            lut6_forward_x2<NP>(tab, xp, yp);
+#pragma unroll
+            for (int p = 0; p < NP; ++p) {
+                float vq[2];
+                unpack2(yp[p], vq[0], vq[1]);
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int fl = h + 64 * p + 32 * e + lane;
+                    const bool live = cur.store && fl < cur.nf;
+                    float v = vq[e];
+                    if (PHASE == PH_STATS) {
+                        if (live) { s1 += (double)v; s2 += (double)v * (double)v; }
+                    } else if (PHASE == PH_NORM) {
+                        v = (v - mean) * scale;
+                        v = v * a.gamma + a.beta;
+                        v = a.binary ? (v > 0.5f ? 1.0f : 0.0f) : __saturatef(v);
+                    } else {
+                        v = __saturatef(v);
+                    }
+                    if (live) a.y[(size_t)cur.node * a.ys + cur.f0 + fl] = v;
+                }
+            }
+        };
+        if (cur.nf > kFramesPerIter) walk(std::integral_constant<int, 4>(), 0);
+        else                         walk(std::integral_constant<int, 2>(), 0);
+        if (PHASE == PH_STATS && cur.store) {
+            s1 = warp_sum(s1);
+            s2 = warp_sum(s2);
+            if (lane == 0) {
+                atomicAdd(a.sums + 2 * (size_t)cur.node, s1);
+                atomicAdd(a.sums + 2 * (size_t)cur.node + 1, s2);
+            }
         }
     }
 }
@@ -351,12 +517,34 @@ static int check_common(const void *x, const void *y, const int *idx, const floa
     return BBCU_OK;
 }
 
+// opt-in to more than 48 KB of dynamic shared memory (per kernel and device; the call is a host-side attribute write)
+template <typename K>
+static bool allow_big_smem(K kernel, int bytes)
+{
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) { cudaGetLastError(); return false; }
+    return true;
+}
+
 template <bool XBIT, int PHASE, bool YBIT>
 static int launch_forward(FwdArgs a, int max_tile, cudaStream_t st)
 {
     if (a.O == 0 || a.F == 0) return BBCU_OK;
     a.groups = (a.O + kWarpsPerCta - 1) / kWarpsPerCta;
-    a.T = frame_tile(3LL * a.O, XBIT ? 1 : 32, a.groups, a.F, max_tile);   // input count is not part of this ABI: between O (square layer) and 6*O rows are touched
+    // input count is not part of this ABI: between O (square layer) and 6*O rows are touched
+    a.T = frame_tile(3LL * a.O, XBIT ? 1 : 32, a.groups, a.F, max_tile);
+    if (!XBIT && !YBIT) {
+        // pipelined path: rows and tables must start on 16-byte boundaries for the bulk copies
+        const bool aligned = ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.W)) & 15) == 0 && (a.xs % 4) == 0;
+        int *fault = aligned ? fault_word() : nullptr;
+        if (aligned && fault != nullptr && allow_big_smem(k_lut6_forward_pipe<PHASE>, kFpSmem)) {
+            a.T = a.T >= kFpMaxItemFrames ? kFpMaxItemFrames : kFramesPerIter;
+            const long long n_items = (long long)((a.F + a.T - 1) / a.T) * a.groups;
+            long long grid = 2LL * device_info().sm_count;
+            if (grid > n_items) grid = n_items;
+            k_lut6_forward_pipe<PHASE><<<(unsigned)grid, kWarpsPerCta * 32, kFpSmem, st>>>(a, n_items, fault);
+            return launch_status();
+        }
+    }
     const long long tiles = (a.F + a.T - 1) / a.T;
     const long long blocks = tiles * a.groups;
     BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);

@@ -15,6 +15,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "async_copy.cuh"
 
 namespace bb200 {
 
@@ -86,6 +87,22 @@ int frame_tile(long long rows_touched, int bits_per_row_frame, int node_groups, 
     return (int)t;
 }
 
+int *fault_word()
+{
+    static std::mutex mu;
+    static std::map<int, int *> words;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> g(mu);
+    auto it = words.find(dev);
+    if (it == words.end()) {
+        void *p = nullptr;
+        if (cudaMalloc(&p, 256) != cudaSuccess || cudaMemset(p, 0, 256) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        it = words.emplace(dev, static_cast<int *>(p)).first;
+    }
+    return it->second;
+}
+
 void *stream_scratch(cudaStream_t stream, size_t bytes)
 {
     if (bytes == 0) bytes = 256;
@@ -135,6 +152,17 @@ extern "C" const char *bbcu_b200_error_string(int status)
 }
 
 extern "C" int bbcu_b200_abi_version(void) { return 1; }
+
+// Synchronises the device and returns the first fault code a kernel recorded (0 = none), clearing it.
+extern "C" int bbcu_b200_device_fault(void)
+{
+    int v = 0;
+    int *w = fault_word();
+    if (w == nullptr || cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpy(&v, w, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (v != 0) cudaMemset(w, 0, sizeof(int));
+    return v;
+}
 
 // ---------------------------------------------------------------------------------------------- manager
 extern "C" int bbcu_GetDeviceCount(void)

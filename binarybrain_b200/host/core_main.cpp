@@ -35,8 +35,8 @@ static void tensor_set_numpy(Tensor &t, py::array_t<float, py::array::c_style | 
 template <class L, class PyClass>
 static void def_sparse(PyClass &c)
 {
-    c.def("W", [](L &l) -> Tensor & { return l.W(); }, py::return_value_policy::reference_internal)
-     .def("dW", [](L &l) -> Tensor & { return l.dW(); }, py::return_value_policy::reference_internal)
+    c.def("W", [](L &l) { return l.GetParameters(); })
+     .def("dW", [](L &l) { return l.GetGradients(); })
      .def("get_node_connection_size", &L::GetNodeConnectionSize)
      .def("get_node_connection_index", &L::GetNodeConnectionIndex)
      .def("set_node_connection_index", &L::SetNodeConnectionIndex)

@@ -49,6 +49,10 @@ typedef void *bbcu_stream_t;
 const char *bbcu_b200_error_string(int status);
 /* ABI version of this library (bumped when a signature changes). */
 int bbcu_b200_abi_version(void);
+/* Synchronises the current device and returns the first fault code one of this library's kernels recorded since the last call
+ * (0 = none, 1 = a bounded wait on an asynchronous copy expired, -1 = the query itself failed).  Kernels never trap or spin
+ * forever: a wait that does not complete is abandoned, recorded here, and the kernel returns. */
+int bbcu_b200_device_fault(void);
 
 /* ------------------------------------------------------------------ Manager: include/bbcu/bbcu.h:49-55, cuda/Manager.cu:15-55 */
 int  bbcu_GetDeviceCount(void);

@@ -360,6 +360,18 @@ def test_argument_errors_do_not_reach_the_gpu(ops):
     torch.cuda.synchronize()
 
 
+def test_no_kernel_recorded_a_fault(ops):
+    """Kernels with bounded waits record a fault code instead of hanging; after a normal run it is still 0."""
+    from binarybrain_b200 import abi
+    from gpu_util import dev_bits, dev, wiring
+    rng = np.random.default_rng(2)
+    I, O, F = 512, 1000, 40000              # several pipeline rounds per warp, ragged last tile and last node group
+    xb = pack_bits(rng.random((I, F)) > 0.5)
+    y = ops.binary_lut6_forward(dev_bits(xb, F), dev(wiring(rng, I, O)), dev(rng.integers(-2**31, 2**31, (O, 2)).astype(np.int32)), F)
+    assert y.shape[0] == O
+    assert abi.lib().bbcu_b200_device_fault() == 0
+
+
 def test_heap_cache_and_out_of_memory(ops):
     from binarybrain_b200 import abi
     L = abi.lib()
