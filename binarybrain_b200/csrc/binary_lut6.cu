@@ -170,6 +170,31 @@ k_binary_lut6_2pipe(const BlArgs a)
     }
 }
 
+// Depth-first multiplexer tree over NW words at once.  A level-1 node costs one 64-bit shared-memory read of its
+// (a, b) pair, shared by all NW words; walking depth first keeps about one live value per level and word, so eight
+// words fit in registers and the pair reads amortise to four per word instead of thirty-two.
+template <int L, int K, int NW>
+struct MuxTree {
+    static __device__ __forceinline__ void eval(const int2 *ab, const uint32_t (&x)[6][NW], uint32_t (&out)[NW])
+    {
+        uint32_t lo[NW], hi[NW];
+        MuxTree<L - 1, 2 * K, NW>::eval(ab, x, lo);
+        MuxTree<L - 1, 2 * K + 1, NW>::eval(ab, x, hi);
+#pragma unroll
+        for (int w = 0; w < NW; ++w) out[w] = (lo[w] & ~x[L - 1][w]) | (hi[w] & x[L - 1][w]);
+    }
+};
+
+template <int K, int NW>
+struct MuxTree<1, K, NW> {
+    static __device__ __forceinline__ void eval(const int2 *ab, const uint32_t (&x)[6][NW], uint32_t (&out)[NW])
+    {
+        const int2 p = ab[K];
+#pragma unroll
+        for (int w = 0; w < NW; ++w) out[w] = x[0][w] * (uint32_t)p.x + (uint32_t)p.y;
+    }
+};
+
 // ---------------------------------------------------------------------------------------------
 // Persistent, bulk-copy-pipelined variant (aligned rows; the launcher's default).
 // Work item = (word tile of 256 words, group of 8 nodes); CTA c takes items c, c + gridDim, ... so the CTAs in
@@ -193,11 +218,11 @@ struct PipeItem {
     bool store;
 };
 
-__device__ __forceinline__ bool pipe_item(const BlArgs &a, long long it, long long n_items, int warp, PipeItem &p)
+__device__ __forceinline__ bool pipe_item(const BlArgs &a, int it, int n_items, int warp, PipeItem &p)
 {
     if (it >= n_items) return false;
-    const int tile  = (int)(it / a.groups);
-    const int group = (int)(it % a.groups);
+    const int tile  = it / a.groups;
+    const int group = it - tile * a.groups;
     const int node  = group * kBlWarps + warp;
     p.store = node < a.O;
     p.node  = p.store ? node : a.O - 1;
@@ -218,7 +243,7 @@ __device__ __forceinline__ void pipe_issue(const BlArgs &a, const PipeItem &p, u
 }
 
 __global__ void __launch_bounds__(kBlWarps * 32, 2)
-k_binary_lut6_pipe(const BlArgs a, long long n_items, int *fault)
+k_binary_lut6_pipe(const BlArgs a, int n_items, int *fault)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     uint32_t *s_rows = reinterpret_cast<uint32_t *>(smem_raw);                                   // [warp][stage][6][256]
@@ -238,8 +263,8 @@ k_binary_lut6_pipe(const BlArgs a, long long n_items, int *fault)
 
     // prologue: items 0 and 1 of this CTA
     PipeItem cur, nxt;
-    long long it = blockIdx.x;
-    const long long step = gridDim.x;
+    int it = (int)blockIdx.x;
+    const int step = (int)gridDim.x;
     if (lane == 0) {
         PipeItem p;
         if (pipe_item(a, it, n_items, warp, p))        pipe_issue(a, p, my_rows, my_bar);
@@ -270,11 +295,13 @@ k_binary_lut6_pipe(const BlArgs a, long long n_items, int *fault)
             return;
         }
         const int w = 4 * lane;
-        uint4 lo[6], hi[6];
+        uint32_t xw[6][8], o[8];
 #pragma unroll
         for (int j = 0; j < 6; ++j) {
-            lo[j] = *reinterpret_cast<const uint4 *>(stage + j * kPipeWords + w);
-            hi[j] = *reinterpret_cast<const uint4 *>(stage + j * kPipeWords + w + 128);
+            const uint4 lo = *reinterpret_cast<const uint4 *>(stage + j * kPipeWords + w);
+            const uint4 hi = *reinterpret_cast<const uint4 *>(stage + j * kPipeWords + w + 128);
+            xw[j][0] = lo.x; xw[j][1] = lo.y; xw[j][2] = lo.z; xw[j][3] = lo.w;
+            xw[j][4] = hi.x; xw[j][5] = hi.y; xw[j][6] = hi.z; xw[j][7] = hi.w;
         }
         __syncwarp();                                   // every lane has read the stage out
         if (lane == 0) {
@@ -284,24 +311,10 @@ k_binary_lut6_pipe(const BlArgs a, long long n_items, int *fault)
                 pipe_issue(a, p, stage, my_bar + s);
             }
         }
-
+        MuxTree<6, 0, 8>::eval(ab, xw, o);
         uint32_t *yrow = a.y + (size_t)cur.node * a.stride + cur.w0;
-        if (cur.store && w < cur.nw) {
-            uint4 o;
-            o.x = lut6_word_imad(lo[0].x, lo[1].x, lo[2].x, lo[3].x, lo[4].x, lo[5].x, ab);
-            o.y = lut6_word_imad(lo[0].y, lo[1].y, lo[2].y, lo[3].y, lo[4].y, lo[5].y, ab);
-            o.z = lut6_word_imad(lo[0].z, lo[1].z, lo[2].z, lo[3].z, lo[4].z, lo[5].z, ab);
-            o.w = lut6_word_imad(lo[0].w, lo[1].w, lo[2].w, lo[3].w, lo[4].w, lo[5].w, ab);
-            *reinterpret_cast<uint4 *>(yrow + w) = o;
-        }
-        if (cur.store && w + 128 < cur.nw) {
-            uint4 o;
-            o.x = lut6_word_imad(hi[0].x, hi[1].x, hi[2].x, hi[3].x, hi[4].x, hi[5].x, ab);
-            o.y = lut6_word_imad(hi[0].y, hi[1].y, hi[2].y, hi[3].y, hi[4].y, hi[5].y, ab);
-            o.z = lut6_word_imad(hi[0].z, hi[1].z, hi[2].z, hi[3].z, hi[4].z, hi[5].z, ab);
-            o.w = lut6_word_imad(hi[0].w, hi[1].w, hi[2].w, hi[3].w, hi[4].w, hi[5].w, ab);
-            *reinterpret_cast<uint4 *>(yrow + w + 128) = o;
-        }
+        if (cur.store && w < cur.nw)       *reinterpret_cast<uint4 *>(yrow + w)       = make_uint4(o[0], o[1], o[2], o[3]);
+        if (cur.store && w + 128 < cur.nw) *reinterpret_cast<uint4 *>(yrow + w + 128) = make_uint4(o[4], o[5], o[6], o[7]);
     }
 }
 
@@ -344,9 +357,10 @@ extern "C" int bbcu_bit_BinaryLut6_Forward(const int *x, int *y, const int *idx,
         int *fault = fault_word();
         if (attr_ok && fault != nullptr) {
             const long long n_items = (long long)((a.nwords + kPipeWords - 1) / kPipeWords) * a.groups;
+            BB200_REQUIRE(n_items < (1LL << 31) - 4096, BBCU_ERR_TOO_LARGE);      // 32-bit item arithmetic in the kernel
             long long grid = 2LL * device_info().sm_count;
             if (grid > n_items) grid = n_items;
-            k_binary_lut6_pipe<<<(unsigned)grid, kBlWarps * 32, kPipeSmem, as_stream(stream)>>>(a, n_items, fault);
+            k_binary_lut6_pipe<<<(unsigned)grid, kBlWarps * 32, kPipeSmem, as_stream(stream)>>>(a, (int)n_items, fault);
             return launch_status();
         }
     }

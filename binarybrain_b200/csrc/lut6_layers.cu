@@ -165,11 +165,11 @@ struct FpItem {
     bool store;
 };
 
-__device__ __forceinline__ bool fp_item(const FwdArgs &a, long long it, long long n_items, int warp, FpItem &p)
+__device__ __forceinline__ bool fp_item(const FwdArgs &a, int it, int n_items, int warp, FpItem &p)
 {
     if (it >= n_items) return false;
-    const int tile  = (int)(it / a.groups);
-    const int group = (int)(it % a.groups);
+    const int tile  = it / a.groups;
+    const int group = it - tile * a.groups;
     const int node  = group * kWarpsPerCta + warp;
     p.store = node < a.O;
     p.node  = p.store ? node : a.O - 1;
@@ -194,7 +194,7 @@ __device__ __forceinline__ void fp_issue(const FwdArgs &a, const FpItem &p, unsi
 
 template <int PHASE>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, 2)
-k_lut6_forward_pipe(const FwdArgs a, long long n_items, int *fault)
+k_lut6_forward_pipe(const FwdArgs a, int n_items, int *fault)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -208,8 +208,8 @@ k_lut6_forward_pipe(const FwdArgs a, long long n_items, int *fault)
     }
     __syncwarp();
 
-    long long it = blockIdx.x;
-    const long long step = gridDim.x;
+    int it = (int)blockIdx.x;
+    const int step = (int)gridDim.x;
     FpItem cur, nxt;
     if (lane == 0) {
         FpItem p;
@@ -539,9 +539,10 @@ static int launch_forward(FwdArgs a, int max_tile, cudaStream_t st)
         if (aligned && fault != nullptr && allow_big_smem(k_lut6_forward_pipe<PHASE>, kFpSmem)) {
             a.T = a.T >= kFpMaxItemFrames ? kFpMaxItemFrames : kFramesPerIter;
             const long long n_items = (long long)((a.F + a.T - 1) / a.T) * a.groups;
+            BB200_REQUIRE(n_items < (1LL << 31) - 4096, BBCU_ERR_TOO_LARGE);      // 32-bit item arithmetic in the kernel
             long long grid = 2LL * device_info().sm_count;
             if (grid > n_items) grid = n_items;
-            k_lut6_forward_pipe<PHASE><<<(unsigned)grid, kWarpsPerCta * 32, kFpSmem, st>>>(a, n_items, fault);
+            k_lut6_forward_pipe<PHASE><<<(unsigned)grid, kWarpsPerCta * 32, kFpSmem, st>>>(a, (int)n_items, fault);
             return launch_status();
         }
     }
@@ -575,7 +576,7 @@ static int backward_common(BwdArgs a, bool bn, long long total_frames, float *dm
     a.T = frame_tile(rows, (XBIT ? 1 : 32) + 32, a.groups, a.F, 1024);
     const long long tiles = (a.F + a.T - 1) / a.T;
     const long long blocks = tiles * a.groups;
-    BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+    BB200_REQUIRE(blocks < (1LL << 31) - 4096, BBCU_ERR_TOO_LARGE);
     a.rF = 1.0f / (float)total_frames;
     if (bn) {
         if (ext_sums == nullptr) {
