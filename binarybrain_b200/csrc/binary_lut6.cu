@@ -213,37 +213,36 @@ constexpr int kPipeAbBytes   = kBlWarps * 32 * 8;
 constexpr int kPipeSmem      = kPipeRowsBytes + kPipeBarBytes + kPipeAbBytes;
 static_assert(kBlWarps * kPipeStages * 8 <= kPipeBarBytes, "barrier block too small");
 
-struct PipeItem {
-    int node, w0, nw;     // node (clamped for loads), first word, words in this tile (multiple of 4)
-    bool store;
+// Position of a work item, advanced incrementally (item index + gridDim) so that no division runs per item.
+struct PipePos {
+    int tile, group;
 };
 
-__device__ __forceinline__ bool pipe_item(const BlArgs &a, int it, int n_items, int warp, PipeItem &p)
+__device__ __forceinline__ PipePos pipe_advance(PipePos p, int dt, int dg, int groups)
 {
-    if (it >= n_items) return false;
-    const int tile  = it / a.groups;
-    const int group = it - tile * a.groups;
-    const int node  = group * kBlWarps + warp;
-    p.store = node < a.O;
-    p.node  = p.store ? node : a.O - 1;
-    p.w0    = tile * kPipeWords;
-    p.nw    = min(kPipeWords, a.nwords - p.w0);
-    return true;
+    p.group += dg;
+    p.tile += dt;
+    if (p.group >= groups) { p.group -= groups; ++p.tile; }
+    return p;
 }
 
-__device__ __forceinline__ void pipe_issue(const BlArgs &a, const PipeItem &p, uint32_t *stage, uint64_t *bar)
+// Lanes 0..5 each start the bulk copy of one gathered row segment (one instruction issue covers all six); lane 0 has
+// armed the barrier with the byte count just before.
+__device__ __forceinline__ void pipe_issue(const BlArgs &a, PipePos pos, int warp, int lane, uint32_t *stage, uint64_t *bar)
 {
-    const uint32_t bytes = (uint32_t)p.nw * 4u;
-    mbar_arrive_expect_tx(bar, 6u * bytes);
-#pragma unroll
-    for (int j = 0; j < 6; ++j) {
-        const uint32_t *src = a.x + (size_t)__ldg(a.idx + (size_t)p.node * 6 + j) * a.stride + p.w0;
-        bulk_copy_g2s(stage + j * kPipeWords, src, bytes, bar);
+    const int node  = min(pos.group * kBlWarps + warp, a.O - 1);
+    const int w0    = pos.tile * kPipeWords;
+    const uint32_t bytes = (uint32_t)min(kPipeWords, a.nwords - w0) * 4u;
+    if (lane == 0) mbar_arrive_expect_tx(bar, 6u * bytes);
+    __syncwarp();
+    if (lane < 6) {
+        const uint32_t *src = a.x + (size_t)__ldg(a.idx + (size_t)node * 6 + lane) * a.stride + w0;
+        bulk_copy_g2s(stage + lane * kPipeWords, src, bytes, bar);
     }
 }
 
 __global__ void __launch_bounds__(kBlWarps * 32, 2)
-k_binary_lut6_pipe(const BlArgs a, int n_items, int *fault)
+k_binary_lut6_pipe(const BlArgs a, int n_tiles, int *fault)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     uint32_t *s_rows = reinterpret_cast<uint32_t *>(smem_raw);                                   // [warp][stage][6][256]
@@ -261,22 +260,28 @@ k_binary_lut6_pipe(const BlArgs a, int n_items, int *fault)
     }
     __syncwarp();
 
-    // prologue: items 0 and 1 of this CTA
-    PipeItem cur, nxt;
-    int it = (int)blockIdx.x;
+    // items blockIdx, blockIdx + gridDim, ...: position of the current item and of the next two
     const int step = (int)gridDim.x;
-    if (lane == 0) {
-        PipeItem p;
-        if (pipe_item(a, it, n_items, warp, p))        pipe_issue(a, p, my_rows, my_bar);
-        if (pipe_item(a, it + step, n_items, warp, p)) pipe_issue(a, p, my_rows + 6 * kPipeWords, my_bar + 1);
-    }
-    uint32_t tword = 0;
-    if (pipe_item(a, it, n_items, warp, cur)) tword = (uint32_t)__ldg(a.table + 2 * (size_t)cur.node + (lane >> 4));
+    const int dt = step / a.groups, dg = step - dt * a.groups;
+    PipePos p0;
+    p0.tile  = (int)blockIdx.x / a.groups;
+    p0.group = (int)blockIdx.x - p0.tile * a.groups;
+    PipePos p1 = pipe_advance(p0, dt, dg, a.groups);
+    PipePos p2 = pipe_advance(p1, dt, dg, a.groups);
 
-    for (int k = 0; pipe_item(a, it, n_items, warp, cur); ++k, it += step) {
+    if (p0.tile < n_tiles) pipe_issue(a, p0, warp, lane, my_rows, my_bar);
+    if (p1.tile < n_tiles) pipe_issue(a, p1, warp, lane, my_rows + 6 * kPipeWords, my_bar + 1);
+    uint32_t tword = 0;
+    if (p0.tile < n_tiles) tword = (uint32_t)__ldg(a.table + 2 * (size_t)min(p0.group * kBlWarps + warp, a.O - 1) + (lane >> 4));
+
+    for (int k = 0; p0.tile < n_tiles; ++k) {
         const int s = k & 1;
         const uint32_t parity = (uint32_t)(k >> 1) & 1u;
         uint32_t *stage = my_rows + s * 6 * kPipeWords;
+        const int node = p0.group * kBlWarps + warp;
+        const bool store = node < a.O;
+        const int w0 = p0.tile * kPipeWords;
+        const int nw = min(kPipeWords, a.nwords - w0);
 
         // this node's level-1 (a, b) pairs; the table word of the NEXT item is fetched now and used next round
         {
@@ -285,9 +290,8 @@ k_binary_lut6_pipe(const BlArgs a, int n_items, int *fault)
             my_ab[lane] = make_int2((int)hi - (int)lo, -(int)lo);
             __syncwarp();
         }
-        const bool have_next = pipe_item(a, it + step, n_items, warp, nxt);
-        if (have_next) tword = (uint32_t)__ldg(a.table + 2 * (size_t)nxt.node + (lane >> 4));
-        const int2 *ab = my_ab;
+        const bool have_next = p1.tile < n_tiles;
+        if (have_next) tword = (uint32_t)__ldg(a.table + 2 * (size_t)min(p1.group * kBlWarps + warp, a.O - 1) + (lane >> 4));
 
         if (!mbar_wait(my_bar + s, parity)) {          // bounded: record the fault, let the other stage's copies land, leave
             if (lane == 0) atomicCAS(fault, 0, kFaultBarrierTimeout);
@@ -304,17 +308,16 @@ k_binary_lut6_pipe(const BlArgs a, int n_items, int *fault)
             xw[j][4] = hi.x; xw[j][5] = hi.y; xw[j][6] = hi.z; xw[j][7] = hi.w;
         }
         __syncwarp();                                   // every lane has read the stage out
-        if (lane == 0) {
-            PipeItem p;
-            if (pipe_item(a, it + 2 * step, n_items, warp, p)) {
-                proxy_fence_async();                    // reads above (generic proxy) before the refill (async proxy)
-                pipe_issue(a, p, stage, my_bar + s);
-            }
+        if (p2.tile < n_tiles) {
+            proxy_fence_async();                        // reads above (generic proxy) before the refill (async proxy)
+            pipe_issue(a, p2, warp, lane, stage, my_bar + s);
         }
-        MuxTree<6, 0, 8>::eval(ab, xw, o);
-        uint32_t *yrow = a.y + (size_t)cur.node * a.stride + cur.w0;
-        if (cur.store && w < cur.nw)       *reinterpret_cast<uint4 *>(yrow + w)       = make_uint4(o[0], o[1], o[2], o[3]);
-        if (cur.store && w + 128 < cur.nw) *reinterpret_cast<uint4 *>(yrow + w + 128) = make_uint4(o[4], o[5], o[6], o[7]);
+        MuxTree<6, 0, 8>::eval(my_ab, xw, o);
+        uint32_t *yrow = a.y + (size_t)min(node, a.O - 1) * a.stride + w0;
+        if (store && w < nw)       *reinterpret_cast<uint4 *>(yrow + w)       = make_uint4(o[0], o[1], o[2], o[3]);
+        if (store && w + 128 < nw) *reinterpret_cast<uint4 *>(yrow + w + 128) = make_uint4(o[4], o[5], o[6], o[7]);
+
+        p0 = p1; p1 = p2; p2 = pipe_advance(p2, dt, dg, a.groups);
     }
 }
 
@@ -360,7 +363,7 @@ extern "C" int bbcu_bit_BinaryLut6_Forward(const int *x, int *y, const int *idx,
             BB200_REQUIRE(n_items < (1LL << 31) - 4096, BBCU_ERR_TOO_LARGE);      // 32-bit item arithmetic in the kernel
             long long grid = 2LL * device_info().sm_count;
             if (grid > n_items) grid = n_items;
-            k_binary_lut6_pipe<<<(unsigned)grid, kBlWarps * 32, kPipeSmem, as_stream(stream)>>>(a, (int)n_items, fault);
+            k_binary_lut6_pipe<<<(unsigned)grid, kBlWarps * 32, kPipeSmem, as_stream(stream)>>>(a, (a.nwords + kPipeWords - 1) / kPipeWords, fault);
             return launch_status();
         }
     }

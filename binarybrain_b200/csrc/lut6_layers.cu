@@ -160,41 +160,39 @@ constexpr int kFpTabBytes      = kWarpsPerCta * 32 * 16;
 constexpr int kFpSmem          = kFpRowsBytes + kFpBarBytes + kFpTabBytes;
 static_assert(kWarpsPerCta * kFpStages * 8 <= kFpBarBytes, "barrier block too small");
 
-struct FpItem {
-    int node, f0, nf, nc;     // node (clamped for loads), first frame, valid frames, floats to copy per row (multiple of 4)
-    bool store;
+// Position of a work item, advanced incrementally (item index + gridDim) so that no division runs per item.
+struct FpPos {
+    int tile, group;
 };
 
-__device__ __forceinline__ bool fp_item(const FwdArgs &a, int it, int n_items, int warp, FpItem &p)
+__device__ __forceinline__ FpPos fp_advance(FpPos p, int dt, int dg, int groups)
 {
-    if (it >= n_items) return false;
-    const int tile  = it / a.groups;
-    const int group = it - tile * a.groups;
-    const int node  = group * kWarpsPerCta + warp;
-    p.store = node < a.O;
-    p.node  = p.store ? node : a.O - 1;
-    p.f0    = tile * a.T;
-    p.nf    = min(a.T, a.F - p.f0);
-    p.nc    = (int)min((long long)a.T, a.xs - p.f0);
-    return true;
+    p.group += dg;
+    p.tile += dt;
+    if (p.group >= groups) { p.group -= groups; ++p.tile; }
+    return p;
 }
 
-__device__ __forceinline__ void fp_issue(const FwdArgs &a, const FpItem &p, unsigned char *stage, uint64_t *bar)
+// Lanes 0..5 each start the bulk copy of one gathered row segment and lane 6 that of the node's table (one
+// instruction issue covers all seven); lane 0 has armed the barrier with the byte count just before.
+__device__ __forceinline__ void fp_issue(const FwdArgs &a, FpPos pos, int warp, int lane, unsigned char *stage, uint64_t *bar)
 {
-    const uint32_t bytes = (uint32_t)p.nc * 4u;
-    mbar_arrive_expect_tx(bar, 6u * bytes + 256u);
-    const float *xf = static_cast<const float *>(a.x);
-#pragma unroll
-    for (int j = 0; j < 6; ++j) {
-        const float *src = xf + (size_t)__ldg(a.idx + (size_t)p.node * 6 + j) * a.xs + p.f0;
-        bulk_copy_g2s(stage + j * (kFpMaxItemFrames * 4), src, bytes, bar);
+    const int node = min(pos.group * kWarpsPerCta + warp, a.O - 1);
+    const int f0   = pos.tile * a.T;
+    const uint32_t bytes = (uint32_t)min((long long)a.T, a.xs - f0) * 4u;       // row stride is a multiple of 4 floats
+    if (lane == 0) mbar_arrive_expect_tx(bar, 6u * bytes + 256u);
+    __syncwarp();
+    if (lane < 6) {
+        const float *src = static_cast<const float *>(a.x) + (size_t)__ldg(a.idx + (size_t)node * 6 + lane) * a.xs + f0;
+        bulk_copy_g2s(stage + lane * (kFpMaxItemFrames * 4), src, bytes, bar);
+    } else if (lane == 6) {
+        bulk_copy_g2s(stage + 6 * kFpMaxItemFrames * 4, a.W + (size_t)node * 64, 256u, bar);
     }
-    bulk_copy_g2s(stage + 6 * kFpMaxItemFrames * 4, a.W + (size_t)p.node * 64, 256u, bar);
 }
 
 template <int PHASE>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, 2)
-k_lut6_forward_pipe(const FwdArgs a, int n_items, int *fault)
+k_lut6_forward_pipe(const FwdArgs a, int n_tiles, int *fault)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -208,26 +206,42 @@ k_lut6_forward_pipe(const FwdArgs a, int n_items, int *fault)
     }
     __syncwarp();
 
-    int it = (int)blockIdx.x;
+    // items blockIdx, blockIdx + gridDim, ...: position of the current item and of the next two
     const int step = (int)gridDim.x;
-    FpItem cur, nxt;
-    if (lane == 0) {
-        FpItem p;
-        if (fp_item(a, it, n_items, warp, p))        fp_issue(a, p, my_stages, my_bar);
-        if (fp_item(a, it + step, n_items, warp, p)) fp_issue(a, p, my_stages + kFpStageBytes, my_bar + 1);
-    }
+    const int dt = step / a.groups, dg = step - dt * a.groups;
+    FpPos p0;
+    p0.tile  = (int)blockIdx.x / a.groups;
+    p0.group = (int)blockIdx.x - p0.tile * a.groups;
+    FpPos p1 = fp_advance(p0, dt, dg, a.groups);
+    FpPos p2 = fp_advance(p1, dt, dg, a.groups);
+    if (p0.tile < n_tiles) fp_issue(a, p0, warp, lane, my_stages, my_bar);
+    if (p1.tile < n_tiles) fp_issue(a, p1, warp, lane, my_stages + kFpStageBytes, my_bar + 1);
+
     // per-node batch-norm constants travel one item ahead of their use
     float mean_n = 0.0f, scale_n = 0.0f;
-    if (PHASE == PH_NORM && fp_item(a, it, n_items, warp, cur)) { mean_n = a.mean[cur.node]; scale_n = a.rstd[cur.node]; }
+    if (PHASE == PH_NORM && p0.tile < n_tiles) {
+        const int n0 = min(p0.group * kWarpsPerCta + warp, a.O - 1);
+        mean_n = a.mean[n0];
+        scale_n = a.rstd[n0];
+    }
 
-    for (int k = 0; fp_item(a, it, n_items, warp, cur); ++k, it += step) {
+    for (int k = 0; p0.tile < n_tiles; ++k) {
         const int s = k & 1;
         const uint32_t parity = (uint32_t)(k >> 1) & 1u;
         unsigned char *stage = my_stages + s * kFpStageBytes;
+        const int node_raw = p0.group * kWarpsPerCta + warp;
+        const bool store = node_raw < a.O;
+        const int node = min(node_raw, a.O - 1);
+        const int f0 = p0.tile * a.T;
+        const int nf = min(a.T, a.F - f0);
         float mean = mean_n, scale = scale_n;
         if (PHASE == PH_NORM && a.stat_is_var) scale = 1.0f / sqrtf(scale);        // DifferentiableLutN.h:866-868
-        const bool have_next = fp_item(a, it + step, n_items, warp, nxt);
-        if (PHASE == PH_NORM && have_next) { mean_n = a.mean[nxt.node]; scale_n = a.rstd[nxt.node]; }
+        const bool have_next = p1.tile < n_tiles;
+        if (PHASE == PH_NORM && have_next) {
+            const int n1 = min(p1.group * kWarpsPerCta + warp, a.O - 1);
+            mean_n = a.mean[n1];
+            scale_n = a.rstd[n1];
+        }
 
         if (!mbar_wait(my_bar + s, parity)) {          // bounded: record the fault, let the other stage's copies land, leave
             if (lane == 0) atomicCAS(fault, 0, kFaultBarrierTimeout);
@@ -244,27 +258,23 @@ k_lut6_forward_pipe(const FwdArgs a, int n_items, int *fault)
         }
         double s1 = 0.0, s2 = 0.0;
         const float *xs0 = reinterpret_cast<const float *>(stage);
+        float *yrow = a.y + (size_t)node * a.ys + f0 + lane;
         // one walk of the tree carries NP frame pairs per lane: 4 pairs (256 frames per warp) when the item is that wide
-        auto walk = [&](auto np_tag, int h) {
+        auto walk = [&](auto np_tag) {
             constexpr int NP = decltype(np_tag)::value;
             f32x2 xp[6][NP], yp[NP];
 #pragma unroll
             for (int j = 0; j < 6; ++j) {
-                const float *r = xs0 + j * kFpMaxItemFrames + h + lane;
+                const float *r = xs0 + j * kFpMaxItemFrames + lane;
 #pragma unroll
                 for (int p = 0; p < NP; ++p)
                     xp[j][p] = pack2(condition_x(r[64 * p], a.binary, a.bias), condition_x(r[64 * p + 32], a.binary, a.bias));
             }
-            if (h + 64 * NP >= cur.nf) {
-                // last read of this stage: hand it back to the copy engine for item k+2 before doing the math
-                __syncwarp();
-                if (lane == 0) {
-                    FpItem p;
-                    if (fp_item(a, it + 2 * step, n_items, warp, p)) {
-                        proxy_fence_async();
-                        fp_issue(a, p, stage, my_bar + s);
-                    }
-                }
+            // the stage has been read out: hand it back to the copy engine for item k+2 before doing the math
+            __syncwarp();
+            if (p2.tile < n_tiles) {
+                proxy_fence_async();
+                fp_issue(a, p2, warp, lane, stage, my_bar + s);
             }
             lut6_forward_x2<NP>(tab, xp, yp);
 #pragma unroll
@@ -273,8 +283,8 @@ k_lut6_forward_pipe(const FwdArgs a, int n_items, int *fault)
                 unpack2(yp[p], vq[0], vq[1]);
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    const int fl = h + 64 * p + 32 * e + lane;
-                    const bool live = cur.store && fl < cur.nf;
+                    const int fl = 64 * p + 32 * e;
+                    const bool live = store && fl + lane < nf;
                     float v = vq[e];
                     if (PHASE == PH_STATS) {
                         if (live) { s1 += (double)v; s2 += (double)v * (double)v; }
@@ -285,20 +295,21 @@ k_lut6_forward_pipe(const FwdArgs a, int n_items, int *fault)
                     } else {
                         v = __saturatef(v);
                     }
-                    if (live) a.y[(size_t)cur.node * a.ys + cur.f0 + fl] = v;
+                    if (live) yrow[fl] = v;
                 }
             }
         };
-        if (cur.nf > kFramesPerIter) walk(std::integral_constant<int, 4>(), 0);
-        else                         walk(std::integral_constant<int, 2>(), 0);
-        if (PHASE == PH_STATS && cur.store) {
+        if (nf > kFramesPerIter) walk(std::integral_constant<int, 4>());
+        else                     walk(std::integral_constant<int, 2>());
+        if (PHASE == PH_STATS && store) {
             s1 = warp_sum(s1);
             s2 = warp_sum(s2);
             if (lane == 0) {
-                atomicAdd(a.sums + 2 * (size_t)cur.node, s1);
-                atomicAdd(a.sums + 2 * (size_t)cur.node + 1, s2);
+                atomicAdd(a.sums + 2 * (size_t)node, s1);
+                atomicAdd(a.sums + 2 * (size_t)node + 1, s2);
             }
         }
+        p0 = p1; p1 = p2; p2 = fp_advance(p2, dt, dg, a.groups);
     }
 }
 
@@ -542,7 +553,7 @@ static int launch_forward(FwdArgs a, int max_tile, cudaStream_t st)
             BB200_REQUIRE(n_items < (1LL << 31) - 4096, BBCU_ERR_TOO_LARGE);      // 32-bit item arithmetic in the kernel
             long long grid = 2LL * device_info().sm_count;
             if (grid > n_items) grid = n_items;
-            k_lut6_forward_pipe<PHASE><<<(unsigned)grid, kWarpsPerCta * 32, kFpSmem, st>>>(a, (int)n_items, fault);
+            k_lut6_forward_pipe<PHASE><<<(unsigned)grid, kWarpsPerCta * 32, kFpSmem, st>>>(a, (a.F + a.T - 1) / a.T, fault);
             return launch_status();
         }
     }
