@@ -54,6 +54,7 @@ SIGNATURES = {
     "bbcu_fp32_DifferentiableLut6_BackwardStats": (_i, [_vp] * 7 + [_f] * 3 + [_i] * 5 + [_vp]),
     "bbcu_fp32_DifferentiableLut6_ForwardTraining_NoAlloc": (_i, [_vp] * 8 + [_f] * 4 + [_i] * 5 + [_vp]),
     "bbcu_fp32_DifferentiableLut6_ForwardTraining_NoAlloc_MaxNodes": (_i, []),
+    "bbcu_fp32_DifferentiableLut6_BackwardStatsFromOutput": (_i, [_vp] * 4 + [_f] * 2 + [_i] * 4 + [_vp]),
     "bbcu_fp32_DifferentiableLut6_BackwardApply": (_i, [_vp] * 11 + [_f] * 3 + [_i] * 4 + [_ll, _i, _i, _vp]),
 }
 

@@ -437,6 +437,54 @@ k_lut6_backward_stats(const BwdArgs a)
     }
 }
 
+// Batch-norm statistics of the backward pass from the layer's own OUTPUT instead of a recomputed LUT value (non-binary
+// mode only).  y = clip((raw - mean) * rstd * gamma + beta, 0, 1): where y is strictly inside (0, 1) the hard-tanh passes
+// the gradient and (raw - mean) * rstd = (y - beta) / gamma, so  -(gamma*dy*(raw - mean)*rstd^2) = -dy*(y - beta)*rstd;
+// where y is 0 or 1 the gradient is masked (DifferentiableLutN.h:1204-1206).  An HBM-bound stream over y and dy
+// (8 bytes per node-frame) replaces a second evaluation of the LUT tree.
+__global__ void __launch_bounds__(256)
+k_dl6_backward_stats_from_y(const float *__restrict__ y, const float *__restrict__ dy, const float *__restrict__ rstd_buf, double *sums,
+                            float gamma, float beta, int F, long long ys, long long dys, int chunks)
+{
+    __shared__ double red[2][8];
+    const int node = blockIdx.x / chunks, chunk = blockIdx.x % chunks;
+    const float *yr = y + (size_t)node * ys;
+    const float *gr = dy + (size_t)node * dys;
+    const int f0 = chunk * 8192, f1 = min(F, f0 + 8192);
+    const float rstd = rstd_buf[node];
+    double dstd = 0.0, dmeanx = 0.0;
+    const bool vec = ((reinterpret_cast<uintptr_t>(yr) | reinterpret_cast<uintptr_t>(gr)) & 15) == 0;
+    auto one = [&](float yv, float g) {
+        if (yv <= 0.0f || yv >= 1.0f) g = 0.0f;
+        dstd   -= (double)(g * (yv - beta) * rstd);
+        dmeanx -= (double)((gamma * g) * rstd);
+    };
+    if (vec) {
+        int f = f0 + threadIdx.x * 4;
+        for (; f + 3 < f1; f += 1024) {
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(yr + f));
+            const float4 g = __ldg(reinterpret_cast<const float4 *>(gr + f));
+            one(a.x, g.x); one(a.y, g.y); one(a.z, g.z); one(a.w, g.w);
+        }
+        const int tail = f0 + ((f1 - f0) & ~3);          // the last 0..3 frames of the chunk
+        if ((int)threadIdx.x < f1 - tail) one(__ldg(yr + tail + threadIdx.x), __ldg(gr + tail + threadIdx.x));
+    } else {
+        for (int f = f0 + threadIdx.x; f < f1; f += 256) one(__ldg(yr + f), __ldg(gr + f));
+    }
+    // block reduction of the two sums
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) { dstd += __shfl_xor_sync(kFull, dstd, m); dmeanx += __shfl_xor_sync(kFull, dmeanx, m); }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { red[0][warp] = dstd; red[1][warp] = dmeanx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double a = 0.0, b = 0.0;
+        for (int w = 0; w < 8; ++w) { a += red[0][w]; b += red[1][w]; }
+        atomicAdd(sums + 2 * (size_t)node, a);
+        atomicAdd(sums + 2 * (size_t)node + 1, b);
+    }
+}
+
 __global__ void k_bn_backward_finalize(const double *__restrict__ sums, const float *__restrict__ mean_buf, const float *__restrict__ rstd_buf,
                                        float *dmean_out, float *dvar_out, int O, long long total_frames)
 {
@@ -883,6 +931,24 @@ extern "C" int bbcu_fp32_DifferentiableLut6_BackwardStats(const float *x, const 
     const long long blocks = (long long)((a.F + a.T - 1) / a.T) * a.groups;
     BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
     k_lut6_backward_stats<false><<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(a);
+    return launch_status();
+}
+
+extern "C" int bbcu_fp32_DifferentiableLut6_BackwardStatsFromOutput(const float *y, const float *dy, const float *rstd, double *dev_sums,
+                                                                    float gamma, float beta, int node_size, int frame_size,
+                                                                    int frame_stride, int binary_mode, bbcu_stream_t stream)
+{
+    BB200_REQUIRE_PTR(y); BB200_REQUIRE_PTR(dy); BB200_REQUIRE_PTR(rstd); BB200_REQUIRE_PTR(dev_sums);
+    BB200_REQUIRE(node_size >= 0 && frame_size >= 0, BBCU_ERR_BAD_SIZE);
+    BB200_REQUIRE(binary_mode == 0, BBCU_ERR_BAD_SIZE);          // a binarised output does not carry the pre-activation value
+    BB200_REQUIRE(frame_stride >= frame_size, BBCU_ERR_BAD_STRIDE);
+    cudaStream_t st = as_stream(stream);
+    BB200_CUDA(cudaMemsetAsync(dev_sums, 0, sizeof(double) * 2 * (size_t)node_size, st));
+    if (node_size == 0 || frame_size == 0) return BBCU_OK;
+    const int chunks = (frame_size + 8191) / 8192;
+    BB200_REQUIRE((long long)node_size * chunks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+    k_dl6_backward_stats_from_y<<<node_size * chunks, 256, 0, st>>>(y, dy, rstd, dev_sums, gamma, beta, frame_size, frame_stride, frame_stride,
+                                                                    chunks);
     return launch_status();
 }
 

@@ -47,7 +47,7 @@ class ShardedDifferentiableLut6:
         self.rstd = torch.empty(self.n_out, dtype=torch.float32, device=dev)
         self.sums = torch.zeros((self.n_out, 2), dtype=torch.float64, device=dev)
         self.gamma, self.beta, self.momentum, self.binary, self.lut_binarize = gamma, beta, momentum, binary, lut_binarize
-        self._x = None
+        self._x = self._y = None
         self._pending = None
 
     @property
@@ -68,6 +68,9 @@ class ShardedDifferentiableLut6:
         self.ops.dl6_forward_normalize(y, self.sums, self.mean, self.rstd, self.running_mean, self.running_var, frames, total_frames,
                                        gamma=self.gamma, beta=self.beta, momentum=self.momentum, binary=self.binary)
         self._x, self._frames, self._total = x, frames, total_frames
+        # the output doubles as the saved pre-activation (non-binary mode): in a stack of layers it is the next layer's input
+        # and stays alive until that layer's backward, i.e. past this layer's
+        self._y = y if (not self.binary and hasattr(self.ops, "dl6_backward_stats_from_output")) else None
         return y
 
     def backward(self, dy, dx=None):
@@ -76,11 +79,14 @@ class ShardedDifferentiableLut6:
         if dx is None:
             dx = torch.empty((self.n_in, dy.shape[1]), dtype=torch.float32, device=dy.device)
         kw = dict(gamma=self.gamma, beta=self.beta, lut_binarize=self.lut_binarize, binary=self.binary)
-        self.ops.dl6_backward_stats(x, dy, self.idx, self.W, self.mean, self.rstd, frames, self.sums, **kw)
+        if self._y is not None and self._y.shape[1] == dy.shape[1]:
+            self.ops.dl6_backward_stats_from_output(self._y, dy, self.rstd, frames, self.sums, gamma=self.gamma, beta=self.beta)
+        else:
+            self.ops.dl6_backward_stats(x, dy, self.idx, self.W, self.mean, self.rstd, frames, self.sums, **kw)
         self._allreduce(self.sums)
         self.ops.dl6_backward_apply(x, dy, dx, self.idx, self.W, self.dW, self.mean, self.rstd, self.sums, self.n_in, frames, total, **kw)
         self._pending = self._allreduce(self.dW, async_op=True)
-        self._x = None
+        self._x = self._y = None
         return dx
 
     def wait_grad(self):

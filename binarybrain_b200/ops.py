@@ -237,6 +237,12 @@ def dl6_backward_stats(x, dy, idx, W, mean, rstd, frames, sums, gamma=0.3, beta=
              idx.shape[0], frames, x.shape[1], int(lut_binarize), int(binary), _stream())
 
 
+def dl6_backward_stats_from_output(y, dy, rstd, frames, sums, gamma=0.3, beta=0.5):
+    """The sums of dl6_backward_stats from the layer's training output y (non-binary mode): no second LUT evaluation."""
+    abi.call("bbcu_fp32_DifferentiableLut6_BackwardStatsFromOutput", _p(y), _p(dy), _p(rstd), _p(sums), gamma, beta, y.shape[0], frames,
+             y.shape[1], 0, _stream())
+
+
 def dl6_backward_apply(x, dy, dx, idx, W, dW, mean, rstd, sums, n_in, frames, total_frames, gamma=0.3, beta=0.5, bias=BIAS, lut_binarize=False,
                        binary=True):
     O = idx.shape[0]

@@ -192,6 +192,12 @@ int bbcu_fp32_DifferentiableLut6_BackwardStats(const float *dev_x_buf, const flo
                                                const float *dev_mean_buf, const float *dev_rstd_buf, double *dev_sums,
                                                float gamma, float beta, float unbinarize_bias, int node_size, int frame_size, int frame_stride,
                                                int lut_binarize, int binary_mode, bbcu_stream_t stream);
+/* Same sums as ..._BackwardStats, taken from the layer's own training OUTPUT y instead of re-evaluating the LUT (non-binary mode
+ * only; binary_mode != 0 is rejected): where 0 < y < 1 the pre-activation value is (y - beta) / gamma, elsewhere the gradient is
+ * masked.  A stream over y and dy (8 bytes per node-frame). */
+int bbcu_fp32_DifferentiableLut6_BackwardStatsFromOutput(const float *dev_y_buf, const float *dev_dy_buf, const float *dev_rstd_buf,
+                                                         double *dev_sums, float gamma, float beta, int node_size, int frame_size,
+                                                         int frame_stride, int binary_mode, bbcu_stream_t stream);
 int bbcu_fp32_DifferentiableLut6_BackwardApply(const float *dev_x_buf, const float *dev_dy_buf, float *dev_dx_buf,
                                                const int *dev_input_index, const float *dev_W, float *dev_dW,
                                                const float *dev_mean_buf, const float *dev_rstd_buf, const double *dev_sums,

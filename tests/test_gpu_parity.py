@@ -446,6 +446,11 @@ def test_frame_sharded_halves_equal_the_whole(ops):
     for k, (b, e) in enumerate(cuts):
         ops.dl6_backward_stats(xs[k], dys[k], idx, W, mean_w, rstd_w, e - b, sums[k], binary=False)
     total = sums[0] + sums[1]
+    # the same sums from the layer's output instead of a second LUT evaluation
+    from_y = torch.zeros((O, 2), dtype=torch.float64, device="cuda")
+    ops.dl6_backward_stats_from_output(y_w, dy, rstd_w, F, from_y)
+    scale = float(total.abs().max())
+    assert torch.allclose(from_y, total, rtol=1e-4, atol=1e-5 * scale)
     dW = torch.zeros((O, 64), device="cuda")
     dxs = [ops.dl6_backward_apply(xs[k], dys[k], torch.empty((I, e - b), device="cuda"), idx, W, dW, mean_w, rstd_w, total, I, e - b, F, binary=False)
            for k, (b, e) in enumerate(cuts)]
