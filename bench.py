@@ -33,8 +33,9 @@ TRAIN_NODES = 65536                  # config 4 layer width
 TRAIN_FRAMES = 4096                  # frames per GPU and step in the training section (6 saved activations of 1 GiB each)
 CPU_SAMPLE_FRAMES = 1 << 18          # bounded sample for the CPU legs (the full batch needs 8 GiB of host copies)
 FALLBACK_HBM_GBS = 6650.0            # the pool's earlier measurement, used only when MEASURED_PEAKS.json is absent
-# dram__bytes_read.sum + dram__bytes_write.sum of one k_binary_lut6 launch (ncu); see profiles/. None until captured.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_binary_lut6_pipe launch: ncu on a 131072-frame launch gave
+# 436.2 MB + 244.2 MB (profiles/binary_lut6_16384x16384_131072frames.md); traffic grows with frames, so x8 for 2^20 frames.
+NCU_TRAFFIC_BYTES_PER_FRAME = (436.2e6 + 244.2e6) / 131072
 
 
 def measured_peaks():
@@ -329,7 +330,7 @@ def main():
             "warmup": W, "ms_per_step": sec_per_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "u32 bit-packed", "data": "synthetic", "config": config, "clocks": clocks, "gpu_launches": args.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": f"of {which}", "kernel": "k_binary_lut6",
+                         "traffic": NCU_TRAFFIC_BYTES_PER_FRAME * frames, "peak_source": f"of {which}", "kernel": "k_binary_lut6",
                          "algorithmic_bytes_per_launch": algo_bytes}}
 
     if not args.no_extras:
