@@ -340,16 +340,15 @@ def main():
         hx.copy_(x)
         torch.cuda.synchronize()
         k = max(2, min(args.steps, 5))
+        hidx, htab = idx.cpu(), table.cpu()
         for i in range(1 + k):
             if i == 1:
                 torch.cuda.synchronize()
                 if dist:
                     dist.barrier()
                 t0 = time.perf_counter()
-            x.copy_(hx, non_blocking=True)
-            step()
-            hy.copy_(y, non_blocking=True)
-            torch.cuda.synchronize()
+            # one call through the C ABI with HOST buffers: upload of x, kernel and download of y happen inside (chunk-pipelined)
+            ops.binary_lut6_forward_host(hx, hidx, htab, frames, y=hy)
         if dist:
             dist.barrier()
         dt = time.perf_counter() - t0

@@ -46,6 +46,9 @@ SIGNATURES = {
     "bbcu_fp32_StochasticBatchNormalization_Backward": (_i, [_vp] * 5 + [_f] * 2 + [_i] * 4 + [_vp]),
     "bbcu_bit_BinaryLut6_Forward": (_i, [_vp] * 4 + [_i] * 3 + [_vp]),
     "bbcu_bit_BinatyLut6_Forward": (_i, [_vp] * 4 + [_i] * 3 + [_vp]),
+    "bbcu_host_bit_BinaryLut6_Forward": (_i, [_vp] * 4 + [_i] * 4),
+    "bbcu_b200_host_alloc": (_vp, [_sz]),
+    "bbcu_b200_host_free": (None, [_vp]),
     "bbcu_fp32_Vector_clamp": (_i, [_vp, _vp, _f, _f, _i, _vp]),
     "bbcu_fp32_Vector_set": (_i, [_vp, _f, _i, _vp]),
     "bbcu_fp32_OptimizerAdam": (_i, [_i] + [_vp] * 5 + [_f] * 3 + [_vp]),

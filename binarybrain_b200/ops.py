@@ -183,6 +183,18 @@ def binary_lut6_forward(x, idx, table, frames, y=None):
     return y
 
 
+def binary_lut6_forward_host(x, idx, table, frames, y=None):
+    """BinaryLut6 forward on HOST tensors (int32, ideally pinned): chunked upload / kernel / download overlapped inside the library."""
+    for t, n in ((x, "x"), (idx, "idx"), (table, "table")):
+        if t.is_cuda or t.dtype != torch.int32 or not t.is_contiguous():
+            raise ValueError(f"{n}: expected a contiguous int32 host tensor")
+    O = idx.shape[0]
+    if y is None:
+        y = torch.empty((O, x.shape[1]), dtype=torch.int32).pin_memory()
+    abi.call("bbcu_host_bit_BinaryLut6_Forward", _p(x), _p(y), _p(idx), _p(table), x.shape[0], O, frames, x.shape[1])
+    return y
+
+
 # ------------------------------------------------------------------------------------------ per-step neighbours
 def clamp_(t, lo=0.0, hi=1.0):
     abi.call("bbcu_fp32_Vector_clamp", _p(t), _p(t), lo, hi, t.numel(), _stream())

@@ -166,6 +166,15 @@ int bbcu_bit_BinaryLut6_Forward(const int *dev_x_buf, int *dev_y_buf, const int 
 int bbcu_bit_BinatyLut6_Forward(const int *dev_x_buf, int *dev_y_buf, const int *dev_input_index, const int *dev_table,
                                 int node_size, int frame_size, int frame_stride, bbcu_stream_t stream);
 
+/* Additive: the same operator on HOST frame buffers (what a caller does that keeps its FrameBuffers in host memory,
+ * include/bb/Memory.h:524-662).  Uploads x in frame chunks, runs the kernel per chunk and downloads y, with upload, kernel and
+ * download of neighbouring chunks overlapped on three internal streams; returns when y is complete.  frame_stride is the HOST row
+ * stride in 32-bit words.  Use page-locked buffers (bbcu_b200_host_alloc) for full PCIe overlap.  One such call at a time per process. */
+int bbcu_host_bit_BinaryLut6_Forward(const int *host_x_buf, int *host_y_buf, const int *host_input_index, const int *host_table,
+                                     int input_node_size, int node_size, int frame_size, int frame_stride);
+void *bbcu_b200_host_alloc(size_t bytes);
+void  bbcu_b200_host_free(void *ptr);
+
 /* ------------------------------------------------------------------ Neighbours of the path that its callers need every step */
 /* bbcu_fp32_Vector_clamp, include/bbcu/bbcu.h:191-198 (the W clamp of DifferentiableLutN.h:605-608 / StochasticLutN.h:451). */
 int bbcu_fp32_Vector_clamp(float *dev_dst, const float *dev_src, float lo, float hi, int size, bbcu_stream_t stream);

@@ -291,6 +291,24 @@ def test_binary_lut6_oracle_bit_exact(ops, I, O, F, stride):
     assert (unpack_bits(host_bits(y, F), F) == unpack_bits(want, F)).all()
 
 
+def test_binary_lut6_host_buffers_bit_exact(ops):
+    """The host-buffer entry point (chunked upload / kernel / download) against the oracle; ragged last chunk and last word."""
+    from gpu_util import wiring
+    rng = np.random.default_rng(77)
+    for (I, O, F, pinned) in [(300, 200, 32 * 4096 * 2 + 1000, True), (64, 48, 999, False)]:
+        idx = wiring(rng, I, O)
+        table = rng.integers(-2**31, 2**31, (O, 2)).astype(np.int32)
+        xb = pack_bits(rng.random((I, F)) > 0.5)
+        hx = torch.from_numpy(xb.view(np.int32))
+        hy = torch.zeros((O, xb.shape[1]), dtype=torch.int32)
+        if pinned:
+            hx, hy = hx.pin_memory(), hy.pin_memory()
+        ops.binary_lut6_forward_host(hx, torch.from_numpy(idx), torch.from_numpy(table), F, y=hy)
+        want = port.binary_lut6_forward(xb, idx, table, F)
+        got = np.ascontiguousarray(hy.numpy()).view(np.uint32)
+        assert (unpack_bits(got, F) == unpack_bits(want, F)).all()
+
+
 def test_binary_lut6_full_size_properties(ops):
     """BASELINE config 1 shape (16384 -> 16384 nodes, 2^20 frames): properties that need no CPU pass.
 
