@@ -203,15 +203,14 @@ def train_section(torch, ops, dist, world, rank, steps):
     total = frames * world
     acts = [torch.empty((nodes, frames), device=dev) for _ in range(layers_n)]
     grads = [torch.empty((nodes, frames), device=dev) for _ in range(2)]
+    loss_buf = torch.zeros(1024, dtype=torch.float64, device=dev)
 
     def step():
         h = x0
         for l, a in zip(layers, acts):
             ops.clamp_(l.W)
             h = l.forward(h, frames, total, y=a)
-        dy = grads[0]
-        torch.sub(h, target, out=dy)
-        dy.mul_(2.0 / (total * nodes))                       # d/dy of the mean squared error over the GLOBAL batch
+        dy, _ = ops.mean_squared_error(h, target, frames, batch_size=total, loss_buf=loss_buf, dy=grads[0])   # mean over the GLOBAL batch
         for k, l in enumerate(reversed(layers)):
             dy = l.backward(dy, dx=grads[(k + 1) % 2])
         for l in layers:

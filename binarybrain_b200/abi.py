@@ -52,6 +52,10 @@ SIGNATURES = {
     "bbcu_fp32_Vector_clamp": (_i, [_vp, _vp, _f, _f, _i, _vp]),
     "bbcu_fp32_Vector_set": (_i, [_vp, _f, _i, _vp]),
     "bbcu_fp32_OptimizerAdam": (_i, [_i] + [_vp] * 5 + [_f] * 3 + [_vp]),
+    "bbcu_fp32_LossSoftmaxCrossEntropy": (_i, [_vp] * 4 + [_f] + [_i] * 4 + [_vp]),
+    "bbcu_fp32_LossMeanSquaredError": (_i, [_vp] * 4 + [_i] * 4 + [_f, C.c_double, _vp]),
+    "bbcu_fp32_Reduce_Forward": (_i, [_vp] * 2 + [_i] * 5 + [_vp]),
+    "bbcu_fp32_Reduce_Backward": (_i, [_vp] * 2 + [_i] * 5 + [_vp]),
     "bbcu_fp32_DifferentiableLut6_ForwardStats": (_i, [_vp] * 5 + [_f] + [_i] * 5 + [_vp]),
     "bbcu_fp32_DifferentiableLut6_ForwardNormalize": (_i, [_vp] * 6 + [_f] * 3 + [_i] * 3 + [_ll, _i, _vp]),
     "bbcu_fp32_DifferentiableLut6_BackwardStats": (_i, [_vp] * 7 + [_f] * 3 + [_i] * 5 + [_vp]),

@@ -201,6 +201,44 @@ def clamp_(t, lo=0.0, hi=1.0):
     return t
 
 
+def softmax_cross_entropy(y, t, frames, pix_size=1):
+    """bb::LossSoftmaxCrossEntropy::CalculateLoss: returns (dy, loss) with loss = -sum(loss_buf) / t_sum (the mean over frames)."""
+    dy = torch.empty_like(y)
+    loss_buf = torch.zeros(frames, dtype=torch.float64, device=y.device)
+    t_sum = float(t[:, :frames].sum().item())
+    abi.call("bbcu_fp32_LossSoftmaxCrossEntropy", _p(y), _p(t), _p(dy), _p(loss_buf), t_sum, pix_size, y.shape[0] // pix_size, frames, y.shape[1],
+             _stream())
+    return dy, (-loss_buf.sum() / t_sum)
+
+
+def mean_squared_error(y, t, frames, batch_size=None, loss_buf=None, dy=None):
+    """bb::LossMeanSquaredError::CalculateLoss (mean reduction): returns (dy, loss_buf); loss = loss_buf.sum() / frames seen."""
+    nodes = y.shape[0]
+    batch_size = frames if batch_size is None else batch_size
+    if dy is None:
+        dy = torch.empty_like(y)
+    if loss_buf is None:
+        loss_buf = torch.zeros(1024, dtype=torch.float64, device=y.device)
+    abi.call("bbcu_fp32_LossMeanSquaredError", _p(y), _p(t), _p(dy), _p(loss_buf), loss_buf.numel(), nodes, frames, y.shape[1],
+             2.0 / (nodes * batch_size), 1.0 / nodes, _stream())
+    return dy, loss_buf
+
+
+def reduce_forward(x, out_nodes, frames, y=None):
+    """bb::Reduce forward: y[o] = mean_i x[out_nodes * i + o]."""
+    if y is None:
+        y = torch.empty((out_nodes, x.shape[1]), dtype=torch.float32, device=x.device)
+    abi.call("bbcu_fp32_Reduce_Forward", _p(x), _p(y), x.shape[0], out_nodes, frames, x.shape[1], y.shape[1], _stream())
+    return y
+
+
+def reduce_backward(dy, in_nodes, frames, dx=None):
+    if dx is None:
+        dx = torch.empty((in_nodes, dy.shape[1]), dtype=torch.float32, device=dy.device)
+    abi.call("bbcu_fp32_Reduce_Backward", _p(dy), _p(dx), in_nodes, dy.shape[0], frames, dy.shape[1], dx.shape[1], _stream())
+    return dx
+
+
 class Adam:
     """bb::OptimizerAdam over a list of (param, grad) CUDA tensors (include/bb/OptimizerAdam.h:142-184)."""
 

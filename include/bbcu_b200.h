@@ -186,6 +186,21 @@ int bbcu_fp32_OptimizerAdam(int size, const int *dev_size_table, float *const *d
                             float *const *dev_m_buf_table, float *const *dev_v_buf_table, float lr_t, float beta1, float beta2,
                             bbcu_stream_t stream);
 
+/* bbcu_LossSoftmaxCrossEntropy<float>, include/bbcu/bbcu.h:1507-1519: per frame and pixel a softmax over the ch_size channel rows
+ * (node = ch * pix_size + pix); dy = (t_weight * softmax - t) / t_sum; dev_loss_buf[frame] = sum log(softmax + 1e-7) * t_weight. */
+int bbcu_fp32_LossSoftmaxCrossEntropy(const float *dev_y_buf, const float *dev_t_buf, float *dev_dy_buf, double *dev_loss_buf, float t_sum,
+                                      int pix_size, int ch_size, int frame_size, int frame_stride, bbcu_stream_t stream);
+/* bbcu_fp32_LossMeanSquaredError, include/bbcu/bbcu.h:1487-1500: dy = grad_reduction * (y - t); the squared errors times loss_reduction
+ * are ADDED into dev_loss_buf[0 .. loss_buf_size) (the caller sums the buffer). */
+int bbcu_fp32_LossMeanSquaredError(const float *dev_y_buf, const float *dev_t_buf, float *dev_dy_buf, double *dev_loss_buf, int loss_buf_size,
+                                   int node_size, int frame_size, int frame_stride, float grad_reduction, double loss_reduction,
+                                   bbcu_stream_t stream);
+/* Additive (the reference's bb::Reduce has only a CPU branch, include/bb/Reduce.h:200-268): y[o] = mean_i x[output_node_size * i + o]. */
+int bbcu_fp32_Reduce_Forward(const float *dev_x_buf, float *dev_y_buf, int input_node_size, int output_node_size, int frame_size,
+                             int x_frame_stride, int y_frame_stride, bbcu_stream_t stream);
+int bbcu_fp32_Reduce_Backward(const float *dev_dy_buf, float *dev_dx_buf, int input_node_size, int output_node_size, int frame_size,
+                              int dy_frame_stride, int dx_frame_stride, bbcu_stream_t stream);
+
 /* ------------------------------------------------------------------ Additive: frame-sharded (multi-GPU) building blocks.
  * No counterpart in the reference (it has no multi-device path, include/bb/Memory.h:215-216).  A rank holds a contiguous frame
  * shard; these split the batch-norm operators at the points where per-node sums over ALL frames are needed, so the caller can

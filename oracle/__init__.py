@@ -52,6 +52,23 @@ def unpack_bits(words, frames):
     return b[:, :frames].copy()
 
 
+def det_uniform(shape, seed):
+    """Deterministic uniform[0,1) float32 array from integer hashing only (splitmix64 of the element index): the same values on
+    every numpy version, so large test inputs need not be stored with the golden outputs."""
+    n = int(np.prod(shape))
+    z = np.arange(n, dtype=np.uint64) + np.uint64(((int(seed) + 1) * 0x9E3779B97F4A7C15) & 0xFFFFFFFFFFFFFFFF)
+    z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+    z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+    z = z ^ (z >> np.uint64(31))
+    return ((z >> np.uint64(40)).astype(np.float32) / np.float32(1 << 24)).reshape(shape)
+
+
+def det_wiring(n_in, n_out, seed):
+    """Deterministic [n_out, 6] wiring with six distinct inputs per node (argsort of hashed keys, row by row)."""
+    keys = det_uniform((n_out, n_in), seed)
+    return np.argsort(keys, axis=1, kind="stable")[:, :6].astype(np.int32)
+
+
 class _Port:
     """oracle/lut6_oracle.c"""
 
@@ -196,6 +213,36 @@ class _Port:
                                             C.c_int(O), C.c_int(frames))
         return y
 
+    # -- Reduce and losses ----------------------------------------------------------------------
+    def reduce_forward(self, x, out_nodes):
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.zeros((out_nodes, x.shape[1]), np.float32)
+        self.lib.oracle_reduce_forward(_vp(x), _vp(y), C.c_int(x.shape[0]), C.c_int(out_nodes), C.c_int(x.shape[1]))
+        return y
+
+    def reduce_backward(self, dy, in_nodes):
+        dy = np.ascontiguousarray(dy, np.float32)
+        dx = np.zeros((in_nodes, dy.shape[1]), np.float32)
+        self.lib.oracle_reduce_backward(_vp(dy), _vp(dx), C.c_int(in_nodes), C.c_int(dy.shape[0]), C.c_int(dy.shape[1]))
+        return dx
+
+    def softmax_cross_entropy(self, y, t):
+        y = np.ascontiguousarray(y, np.float32)
+        t = np.ascontiguousarray(t, np.float32)
+        dy = np.zeros_like(y)
+        self.lib.oracle_softmax_cross_entropy.restype = C.c_double
+        loss = self.lib.oracle_softmax_cross_entropy(_vp(y), _vp(t), _vp(dy), C.c_int(y.shape[0]), C.c_int(y.shape[1]))
+        return dy, float(loss)
+
+    def mean_squared_error(self, y, t, batch_size=None):
+        y = np.ascontiguousarray(y, np.float32)
+        t = np.ascontiguousarray(t, np.float32)
+        dy = np.zeros_like(y)
+        self.lib.oracle_mean_squared_error.restype = C.c_double
+        loss = self.lib.oracle_mean_squared_error(_vp(y), _vp(t), _vp(dy), C.c_int(y.shape[0]), C.c_int(y.shape[1]),
+                                                  C.c_int(y.shape[1] if batch_size is None else batch_size))
+        return dy, float(loss)
+
     # -- Adam ---------------------------------------------------------------------------------
     def adam_update(self, p, g, m, v, state, lr=0.001, beta1=0.9, beta2=0.999):
         """In place on float32 arrays p, g, m, v; ``state`` is a 2-element float32 array [b1^t, b2^t] starting at 1."""
@@ -310,6 +357,29 @@ class _Ref:
             C.c_int(batch_norm), C.c_int(binary), C.c_int(lut_binarize), C.c_float(gamma), C.c_float(beta), C.c_float(momentum),
             _vp(dy), C.c_int(steps), C.c_float(lr), C.c_float(beta1), C.c_float(beta2), _vp(y), _vp(rm), _vp(rv))
         return dict(W=Wo, y=y, running_mean=rm, running_var=rv)
+
+
+    def _lut_mlp_step(self, x, t, widths, classes, idx_list, W_list, use_mse, lr):
+        x = np.ascontiguousarray(x, np.float32)
+        t = np.ascontiguousarray(t, np.float32)
+        F = x.shape[1]
+        idx = np.ascontiguousarray(np.concatenate([np.asarray(i, np.int32).reshape(-1) for i in idx_list]))
+        W = np.ascontiguousarray(np.concatenate([np.asarray(w, np.float32).reshape(-1) for w in W_list]))
+        wd = np.ascontiguousarray(widths, np.int32)
+        y = np.zeros((classes, F), np.float32)
+        dx = np.zeros((widths[0], F), np.float32)
+        loss = C.c_double(0)
+        self.lib.bbref_lut_mlp_step(_vp(x), _vp(t), C.c_int(F), C.c_int(len(widths) - 1), _vp(wd), C.c_int(classes), _vp(idx), _vp(W),
+                                    C.c_int(use_mse), C.c_float(lr), _vp(y), C.byref(loss), _vp(dx))
+        out, o = [], 0
+        for n in widths[1:]:
+            out.append(W[o:o + n * 64].reshape(n, 64).copy())
+            o += n * 64
+        return dict(y=y, loss=loss.value, dx=dx, W=out)
+
+    def lut_mlp_step(self, x, t, widths, classes, idx_list, W_list, use_mse=False, lr=0.001):
+        """One training step (forward, loss, backward, Adam) of stacked DifferentiableLut6 layers + Reduce through the reference's Sequential."""
+        return self._lut_mlp_step(x, t, list(widths), classes, idx_list, W_list, int(use_mse), lr)
 
 
 port = _Port()

@@ -359,3 +359,66 @@ void oracle_adam_update(float *p, float *g, float *mbuf, float *vbuf, size_t n, 
         g[i] = 0.0f;
     }
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Neighbours used by whole-step parity (config 0 / config 4): bb::Reduce, the two losses.
+ * Reduce                  include/bb/Reduce.h:200-220 (forward), :250-268 (backward)
+ * LossSoftmaxCrossEntropy include/bb/LossSoftmaxCrossEntropy.h:151-205 (pix_size = 1 form)
+ * LossMeanSquaredError    include/bb/LossMeanSquaredError.h:153-172 (mean reduction)
+ * ------------------------------------------------------------------------------------------ */
+void oracle_reduce_forward(float const *x, float *y, int in_nodes, int out_nodes, int F)
+{
+    int mux = in_nodes / out_nodes;
+    for (int o = 0; o < out_nodes; ++o)
+        for (int f = 0; f < F; ++f) {
+            float sum = 0;
+            for (int i = 0; i < mux; ++i) sum += x[(size_t)(out_nodes * i + o) * F + f];
+            y[(size_t)o * F + f] = sum / (float)mux;
+        }
+}
+
+void oracle_reduce_backward(float const *dy, float *dx, int in_nodes, int out_nodes, int F)
+{
+    int mux = in_nodes / out_nodes;
+    for (int o = 0; o < out_nodes; ++o)
+        for (int f = 0; f < F; ++f) {
+            float g = dy[(size_t)o * F + f] / (float)mux;
+            for (int i = 0; i < mux; ++i) dx[(size_t)(out_nodes * i + o) * F + f] = g;
+        }
+}
+
+double oracle_softmax_cross_entropy(float const *y, float const *t, float *dy, int nodes, int F)
+{
+    float eps = 1.0e-7f, t_sum = 0;
+    for (int f = 0; f < F; ++f) for (int n = 0; n < nodes; ++n) t_sum += t[(size_t)n * F + f];
+    double loss_sum = 0;
+    for (int f = 0; f < F; ++f) {
+        float c = -3.402823466e+38f;
+        for (int n = 0; n < nodes; ++n) c = fmaxf(c, y[(size_t)n * F + f]);
+        float y_sum = 0, t_max = 0;
+        for (int n = 0; n < nodes; ++n) { y_sum += expf(y[(size_t)n * F + f] - c); t_max += t[(size_t)n * F + f]; }
+        if (y_sum <= eps) y_sum = eps;
+        float lf = 0;
+        for (int n = 0; n < nodes; ++n) {
+            float softmax = expf(y[(size_t)n * F + f] - c) / y_sum, tv = t[(size_t)n * F + f];
+            if (tv > 0) lf += logf(softmax + eps) * t_max;
+            dy[(size_t)n * F + f] = (t_max * softmax - tv) / t_sum;
+        }
+        loss_sum += lf;
+    }
+    return -loss_sum / t_sum;
+}
+
+double oracle_mean_squared_error(float const *y, float const *t, float *dy, int nodes, int F, int batch_size)
+{
+    float grad_reduction = 1.0f / (float)(nodes * batch_size);
+    double loss = 0;
+    for (int f = 0; f < F; ++f)
+        for (int n = 0; n < nodes; ++n) {
+            float g = y[(size_t)n * F + f] - t[(size_t)n * F + f];
+            dy[(size_t)n * F + f] = 2 * g * grad_reduction;
+            float e = g * g;
+            if (!isnan(e)) loss += e * (1.0 / nodes);
+        }
+    return loss / F;
+}

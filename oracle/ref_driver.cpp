@@ -29,6 +29,10 @@
 #include "bb/BinaryLutN.h"
 #include "bb/StochasticBatchNormalization.h"
 #include "bb/OptimizerAdam.h"
+#include "bb/Sequential.h"
+#include "bb/Reduce.h"
+#include "bb/LossSoftmaxCrossEntropy.h"
+#include "bb/LossMeanSquaredError.h"
 
 namespace {
 
@@ -372,6 +376,67 @@ int bbref_differentiable_lut6_adam(float const *x, int I, int O, int F, int cons
         auto m = lut->lock_mean_const();
         auto v = lut->lock_var_const();
         for (int n = 0; n < O; ++n) { running_mean[n] = m[n]; running_var[n] = v[n]; }
+    }
+    return 0;
+}
+
+// One training step of a stack of DifferentiableLutN<6,float> layers (fp32, batch norm on, non-binary) followed by bb::Reduce to
+// `classes` outputs, LossSoftmaxCrossEntropy (use_mse = 0) or LossMeanSquaredError (use_mse = 1) and OptimizerAdam:
+// forward(train) -> loss -> backward -> Update.  idx / W are the concatenated wiring and tables of the layers (in: initial, out:
+// W after the step); widths[0] is the input width, widths[1..layers] the layer widths.  classes == widths[layers] skips the Reduce.
+int bbref_lut_mlp_step(float const *x, float const *t, int frames, int layers, int const *widths, int classes, int const *idx, float *W,
+                       int use_mse, float lr, float *y_out, double *loss_out, float *dx_out)
+{
+    auto net = bb::Sequential::Create();
+    std::vector<std::shared_ptr<bb::DifferentiableLutN<6, float, float>>> luts;
+    for (int l = 0; l < layers; ++l) {
+        bb::DifferentiableLutN<6, float, float>::create_t c;
+        c.output_shape = {widths[l + 1]};
+        c.binary = false;
+        auto lut = bb::DifferentiableLutN<6, float, float>::Create(c);
+        lut->SendCommand("host_only true");
+        luts.push_back(lut);
+        net->Add(lut);
+    }
+    if (classes != widths[layers]) net->Add(bb::Reduce<float, float>::Create(bb::indices_t({classes})));
+    net->SetInputShape({widths[0]});
+    size_t io = 0, wo = 0;
+    for (int l = 0; l < layers; ++l) {
+        set_wiring(luts[l], idx + io, widths[l + 1]);
+        set_W(luts[l], W + wo, widths[l + 1]);
+        io += (size_t)widths[l + 1] * 6;
+        wo += (size_t)widths[l + 1] * 64;
+    }
+    bb::FrameBuffer x_buf(frames, {widths[0]}, BB_TYPE_FP32, true);
+    put_fp32(x_buf, x, widths[0], frames);
+    bb::FrameBuffer t_buf(frames, {classes}, BB_TYPE_FP32, true);
+    put_fp32(t_buf, t, classes, frames);
+
+    bb::OptimizerAdam<float>::create_t oc;
+    oc.learning_rate = lr;
+    auto opt = bb::OptimizerAdam<float>::Create(oc);
+    opt->SetVariables(net->GetParameters(), net->GetGradients());
+
+    auto y_buf = net->Forward(x_buf, true);
+    bb::FrameBuffer dy_buf;
+    if (use_mse) {
+        auto loss = bb::LossMeanSquaredError<float>::Create();
+        dy_buf = loss->CalculateLoss(y_buf, t_buf, frames);
+        if (loss_out) *loss_out = loss->GetLoss();
+    } else {
+        auto loss = bb::LossSoftmaxCrossEntropy<float>::Create();
+        dy_buf = loss->CalculateLoss(y_buf, t_buf, frames);
+        if (loss_out) *loss_out = loss->GetLoss();
+    }
+    auto dx_buf = net->Backward(dy_buf);
+    opt->Update();
+    if (y_out) get_fp32(y_buf, y_out, classes, frames);
+    if (dx_out) get_fp32(dx_buf, dx_out, widths[0], frames);
+    wo = 0;
+    for (int l = 0; l < layers; ++l) {
+        auto p = luts[l]->lock_W_const();
+        for (int n = 0; n < widths[l + 1]; ++n) for (int i = 0; i < 64; ++i) W[wo + (size_t)n * 64 + i] = p(n, i);
+        wo += (size_t)widths[l + 1] * 64;
     }
     return 0;
 }

@@ -16,7 +16,7 @@ import sys
 import numpy as np
 
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", ".."))
-from oracle import ref, pack_bits  # noqa: E402
+from oracle import ref, pack_bits, det_uniform, det_wiring  # noqa: E402
 
 OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lut6_golden.npz")
 
@@ -154,6 +154,28 @@ def main():
     W = np.clip(rng.normal(0.5, 0.01, (O, 64)), 0, 1).astype(np.float32)
     r = ref.differentiable_lut6_adam(x, idx, W, dy, 100, batch_norm=False, binary=False)
     g.update({"adamnobn_W0": W, "adamnobn_W100": r["W"], "adamnobn_y100": r["y"]})
+
+    # One whole training step of BASELINE config 0: 784 -> 1024 -> 420 -> 70 DifferentiableLut6 (fp32, batch norm, non-binary),
+    # Reduce to 10 classes, softmax cross-entropy, Adam, 512 frames.  Inputs come from integer hashing (oracle.det_uniform), so only
+    # the results are stored: logits, loss, dx and W checksums plus a few rows.
+    widths, classes, F = [784, 1024, 420, 70], 10, 512
+    x = det_uniform((widths[0], F), 101)
+    labels = (det_uniform((F,), 102) * classes).astype(np.int64)
+    t = np.zeros((classes, F), np.float32)
+    t[labels, np.arange(F)] = 1.0
+    idx_l = [det_wiring(widths[l], widths[l + 1], 110 + l) for l in range(3)]
+    W_l = [np.clip(0.5 + 0.25 * (det_uniform((widths[l + 1], 64), 120 + l) - 0.5) * 3.46, 0, 1).astype(np.float32) for l in range(3)]
+    r = ref.lut_mlp_step(x, t, widths, classes, idx_l, W_l)
+    g.update({"cfg0_y": r["y"], "cfg0_loss": np.array([r["loss"]]), "cfg0_dx_rows": r["dx"][:4], "cfg0_dx_abs_sum": np.array([np.abs(r["dx"]).sum(dtype=np.float64)])})
+    for l in range(3):
+        g.update({f"cfg0_W{l}_rows": r["W"][l][:4], f"cfg0_W{l}_sum": np.array([r["W"][l].sum(dtype=np.float64)]),
+                  f"cfg0_dWstep{l}_abs_sum": np.array([np.abs(r["W"][l] - W_l[l]).sum(dtype=np.float64)])})
+    # the losses and Reduce on their own
+    yl = det_uniform((10, 40), 130) * 4 - 2
+    tl = np.zeros((10, 40), np.float32)
+    tl[(det_uniform((40,), 131) * 10).astype(np.int64), np.arange(40)] = 1.0
+    import ctypes as C  # noqa: E402
+    g.update({"loss_y": yl, "loss_t": tl})
 
     np.savez_compressed(OUT, **g)
     print("wrote", OUT, os.path.getsize(OUT), "bytes,", len(g), "arrays")
