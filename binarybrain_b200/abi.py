@@ -56,6 +56,10 @@ SIGNATURES = {
     "bbcu_fp32_LossMeanSquaredError": (_i, [_vp] * 4 + [_i] * 4 + [_f, C.c_double, _vp]),
     "bbcu_fp32_Reduce_Forward": (_i, [_vp] * 2 + [_i] * 5 + [_vp]),
     "bbcu_fp32_Reduce_Backward": (_i, [_vp] * 2 + [_i] * 5 + [_vp]),
+    "bbcu_bit_fp32_RealToBinary_Forward": (_i, [_vp, _vp, _vp, _i, C.c_uint, C.c_uint, _f, _f] + [C.c_uint] * 5 + [_vp]),
+    "bbcu_bit_fp32_BinaryToReal_Forward": (_i, [_vp, _vp] + [_i] * 6 + [_vp]),
+    "bbcu_fp32_BinaryToReal_Forward": (_i, [_vp, _vp] + [_i] * 6 + [_vp]),
+    "bbcu_fp32_BinaryToReal_Backward": (_i, [_vp, _vp] + [_i] * 6 + [_vp]),
     "bbcu_fp32_DifferentiableLut6_ForwardStats": (_i, [_vp] * 5 + [_f] + [_i] * 5 + [_vp]),
     "bbcu_fp32_DifferentiableLut6_ForwardNormalize": (_i, [_vp] * 6 + [_f] * 3 + [_i] * 3 + [_ll, _i, _vp]),
     "bbcu_fp32_DifferentiableLut6_BackwardStats": (_i, [_vp] * 7 + [_f] * 3 + [_i] * 5 + [_vp]),

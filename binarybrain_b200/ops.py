@@ -239,6 +239,34 @@ def reduce_backward(dy, in_nodes, frames, dx=None):
     return dx
 
 
+def real_to_binary(x, frames, frame_mod=1, depth_mod=1, lo=0.0, hi=1.0, thresholds=None, point_size=None):
+    """bb::RealToBinary forward to bit frames: [nodes, frames] fp32 -> [nodes * depth_mod, frames * frame_mod] bits.
+    thresholds: optional fp32 [nodes, >= frames * frame_mod] (what a seeded value generator supplies in the reference)."""
+    nodes = x.shape[0]
+    point_size = nodes if point_size is None else point_size
+    out_frames = frames * frame_mod
+    y = torch.zeros((nodes * depth_mod, bit_stride(out_frames)), dtype=torch.int32, device=x.device)
+    abi.call("bbcu_bit_fp32_RealToBinary_Forward", _p(x), _p(y), _p(thresholds), 0 if thresholds is None else thresholds.shape[1], depth_mod,
+             frame_mod, lo, hi, point_size, nodes // point_size, frames, x.shape[1], y.shape[1], _stream())
+    return y
+
+
+def binary_to_real(x, x_nodes, y_nodes, y_frames, frame_mux=1):
+    """bb::BinaryToReal forward: bit (int32) or fp32 frames -> fp32 [y_nodes, y_frames], averaging node_mux x frame_mux inputs."""
+    y = torch.empty((y_nodes, fp32_stride(y_frames)), dtype=torch.float32, device=x.device)
+    name = "bbcu_bit_fp32_BinaryToReal_Forward" if x.dtype == torch.int32 else "bbcu_fp32_BinaryToReal_Forward"
+    abi.call(name, _p(x), _p(y), x_nodes // y_nodes, frame_mux, y_nodes, x.shape[1], y_frames, y.shape[1], _stream())
+    return y
+
+
+def binary_to_real_backward(dy, x_nodes, y_frames, frame_mux=1):
+    y_nodes = dy.shape[0]
+    dx = torch.empty((x_nodes, fp32_stride(y_frames * frame_mux)), dtype=torch.float32, device=dy.device)
+    abi.call("bbcu_fp32_BinaryToReal_Backward", _p(dy), _p(dx), x_nodes // y_nodes, frame_mux, y_nodes, dx.shape[1], y_frames, dy.shape[1],
+             _stream())
+    return dx
+
+
 class Adam:
     """bb::OptimizerAdam over a list of (param, grad) CUDA tensors (include/bb/OptimizerAdam.h:142-184)."""
 

@@ -201,6 +201,22 @@ int bbcu_fp32_Reduce_Forward(const float *dev_x_buf, float *dev_y_buf, int input
 int bbcu_fp32_Reduce_Backward(const float *dev_dy_buf, float *dev_dx_buf, int input_node_size, int output_node_size, int frame_size,
                               int dy_frame_stride, int dx_frame_stride, bbcu_stream_t stream);
 
+/* bbcu_bit_RealToBinary_Forward<float>, include/bbcu/bbcu.h:1355-1369, with one added argument pair: dev_thresholds == NULL gives the
+ * deterministic modulation of the reference's operator (include/bb/RealToBinary.h:309-345, binary mode); otherwise it is an fp32 frame
+ * buffer [input node][output frame] (row stride threshold_frame_stride) and bit = modulated x > threshold, the form the reference
+ * evaluates on the host with a value generator (:352-398).  Output frames = x_frame_size * frame_modulation_size, bit-packed. */
+int bbcu_bit_fp32_RealToBinary_Forward(const float *dev_x_buf, int *dev_y_buf, const float *dev_thresholds, int threshold_frame_stride,
+                                       unsigned depth_modulation_size, unsigned frame_modulation_size, float input_range_lo,
+                                       float input_range_hi, unsigned point_size, unsigned x_depth_size, unsigned x_frame_size,
+                                       unsigned x_frame_stride, unsigned y_frame_stride, bbcu_stream_t stream);
+/* bbcu_bit_fp32_BinaryToReal_Forward / bbcu_fp32_BinaryToReal_Forward / bbcu_fp32_BinaryToReal_Backward, include/bbcu/bbcu.h:1376-1413. */
+int bbcu_bit_fp32_BinaryToReal_Forward(const int *dev_x_buf, float *dev_y_buf, int node_mux_size, int frame_mux_size, int y_node_size,
+                                       int x_frame_stride, int y_frame_size, int y_frame_stride, bbcu_stream_t stream);
+int bbcu_fp32_BinaryToReal_Forward(const float *dev_x_buf, float *dev_y_buf, int node_mux_size, int frame_mux_size, int y_node_size,
+                                   int x_frame_stride, int y_frame_size, int y_frame_stride, bbcu_stream_t stream);
+int bbcu_fp32_BinaryToReal_Backward(const float *dev_dy_buf, float *dev_dx_buf, int node_mux_size, int frame_mux_size, int y_node_size,
+                                    int x_frame_stride, int y_frame_size, int y_frame_stride, bbcu_stream_t stream);
+
 /* ------------------------------------------------------------------ Additive: frame-sharded (multi-GPU) building blocks.
  * No counterpart in the reference (it has no multi-device path, include/bb/Memory.h:215-216).  A rank holds a contiguous frame
  * shard; these split the batch-norm operators at the points where per-node sums over ALL frames are needed, so the caller can

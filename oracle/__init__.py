@@ -243,6 +243,30 @@ class _Port:
                                                   C.c_int(y.shape[1] if batch_size is None else batch_size))
         return dy, float(loss)
 
+    # -- binary modulation -------------------------------------------------------------------------
+    def real_to_binary(self, x, frame_mod=1, depth_mod=1, thresholds=None, lo=0.0, hi=1.0, point_size=1):
+        x = np.ascontiguousarray(x, np.float32)
+        nodes, frames = x.shape
+        words = (frames * frame_mod + 31) // 32
+        y = np.zeros((nodes * depth_mod, words), np.uint32)
+        th = None if thresholds is None else np.ascontiguousarray(thresholds, np.float32)
+        self.lib.oracle_real_to_binary(_vp(x), _vp(y), C.c_size_t(words), _vp(th), C.c_int(nodes // point_size), C.c_int(point_size),
+                                       C.c_int(frames), C.c_int(frame_mod), C.c_int(depth_mod), C.c_float(lo), C.c_float(hi))
+        return y
+
+    def binary_to_real(self, x_words, y_nodes, y_frames, frame_mux=1):
+        x_words = np.ascontiguousarray(x_words, np.uint32)
+        y = np.zeros((y_nodes, y_frames), np.float32)
+        self.lib.oracle_binary_to_real_forward(_vp(x_words), C.c_size_t(x_words.shape[1]), _vp(y), C.c_int(x_words.shape[0]), C.c_int(y_nodes),
+                                               C.c_int(y_frames), C.c_int(frame_mux))
+        return y
+
+    def binary_to_real_backward(self, dy, x_nodes, frame_mux=1):
+        dy = np.ascontiguousarray(dy, np.float32)
+        dx = np.zeros((x_nodes, dy.shape[1] * frame_mux), np.float32)
+        self.lib.oracle_binary_to_real_backward(_vp(dy), _vp(dx), C.c_int(x_nodes), C.c_int(dy.shape[0]), C.c_int(dy.shape[1]), C.c_int(frame_mux))
+        return dx
+
     # -- Adam ---------------------------------------------------------------------------------
     def adam_update(self, p, g, m, v, state, lr=0.001, beta1=0.9, beta2=0.999):
         """In place on float32 arrays p, g, m, v; ``state`` is a 2-element float32 array [b1^t, b2^t] starting at 1."""
@@ -358,6 +382,27 @@ class _Ref:
             _vp(dy), C.c_int(steps), C.c_float(lr), C.c_float(beta1), C.c_float(beta2), _vp(y), _vp(rm), _vp(rv))
         return dict(W=Wo, y=y, running_mean=rm, running_var=rv)
 
+
+    def real_to_binary(self, x, frame_mod=1, depth_mod=1, seed=0, point_size=1):
+        x = np.ascontiguousarray(x, np.float32)
+        nodes, frames = x.shape
+        of = frames * frame_mod
+        y = np.zeros((nodes * depth_mod, (of + 31) // 32), np.uint32)
+        th = np.zeros((nodes, of), np.float32)
+        self.lib.bbref_real_to_binary(_vp(x), C.c_int(nodes // point_size), C.c_int(point_size), C.c_int(frames), C.c_int(frame_mod),
+                                      C.c_int(depth_mod), C.c_uint64(seed), _vp(y), _vp(th))
+        return y, (th if seed else None)
+
+    def binary_to_real(self, x_words, y_nodes, y_frames, frame_mux=1, dy=None):
+        x_words = np.ascontiguousarray(x_words, np.uint32)
+        x_nodes = x_words.shape[0]
+        y = np.zeros((y_nodes, y_frames), np.float32)
+        dx = None
+        if dy is not None:
+            dy = np.ascontiguousarray(dy, np.float32)
+            dx = np.zeros((x_nodes, y_frames * frame_mux), np.float32)
+        self.lib.bbref_binary_to_real(_vp(x_words), C.c_int(x_nodes), C.c_int(y_nodes), C.c_int(y_frames), C.c_int(frame_mux), _vp(y), _vp(dy), _vp(dx))
+        return y, dx
 
     def _lut_mlp_step(self, x, t, widths, classes, idx_list, W_list, use_mse, lr):
         x = np.ascontiguousarray(x, np.float32)

@@ -422,3 +422,58 @@ double oracle_mean_squared_error(float const *y, float const *t, float *dy, int 
         }
     return loss / F;
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Binary modulation (config 2 neighbours)
+ * RealToBinary  include/bb/RealToBinary.h:309-345 (th == NULL: deterministic) and :352-398 (th[node][out_frame] given)
+ * BinaryToReal  include/bb/BinaryToReal.h:247-276 (forward), :312-330 (backward)
+ * Layout: x [x_depth * point_size][frames] fp32, y bit rows of `ys` words; output node = (depth * depth_mod + d) * point_size + p.
+ * ------------------------------------------------------------------------------------------ */
+void oracle_real_to_binary(float const *x, uint32_t *y, size_t ys, float const *th, int x_depth, int point_size, int frames, int frame_mod,
+                           int depth_mod, float lo, float hi)
+{
+    float frame_step = 1.0f / (float)frame_mod, depth_step = 1.0f / (float)depth_mod, scale = 1.0f / (hi - lo);
+    int out_frames = frames * frame_mod, nodes = x_depth * point_size;
+    for (int n = 0; n < nodes * depth_mod; ++n) memset(y + (size_t)n * ys, 0, sizeof(uint32_t) * ((out_frames + 31) / 32));
+    for (int fi = 0; fi < frames; ++fi)
+        for (int f = 0; f < frame_mod; ++f) {
+            int of = fi * frame_mod + f;
+            for (int depth = 0; depth < x_depth; ++depth)
+                for (int p = 0; p < point_size; ++p) {
+                    int in_node = depth * point_size + p;
+                    float xv = (x[(size_t)in_node * frames + fi] - lo) * scale;
+                    for (int d = 0; d < depth_mod; ++d) {
+                        int on = (depth * depth_mod + d) * point_size + p;
+                        float v = (xv - (float)(d * depth_step)) * (float)depth_mod;
+                        int bit;
+                        if (th) bit = v > th[(size_t)in_node * out_frames + of];
+                        else {
+                            v = (v - (float)(f * frame_step)) * (float)frame_mod;
+                            v = fmaxf(0.0f, fminf(1.0f, v));
+                            bit = v > 0.5f;
+                        }
+                        if (bit) y[(size_t)on * ys + (of >> 5)] |= 1u << (of & 31);
+                    }
+                }
+        }
+}
+
+void oracle_binary_to_real_forward(uint32_t const *x, size_t xs, float *y, int x_nodes, int y_nodes, int y_frames, int frame_mux)
+{
+    for (int f = 0; f < y_frames; ++f)
+        for (int n = 0; n < y_nodes; ++n) {
+            float v = 0; int cnt = 0;
+            for (int xn = n; xn < x_nodes; xn += y_nodes)
+                for (int i = 0; i < frame_mux; ++i) { v += (float)get_bit(x + (size_t)xn * xs, f * frame_mux + i); ++cnt; }
+            y[(size_t)n * y_frames + f] = v / (float)cnt;
+        }
+}
+
+void oracle_binary_to_real_backward(float const *dy, float *dx, int x_nodes, int y_nodes, int y_frames, int frame_mux)
+{
+    float gain = (float)y_nodes / ((float)x_nodes * (float)frame_mux);
+    for (int n = 0; n < x_nodes; ++n)
+        for (int f = 0; f < y_frames; ++f)
+            for (int i = 0; i < frame_mux; ++i)
+                dx[(size_t)n * y_frames * frame_mux + f * frame_mux + i] = dy[(size_t)(n % y_nodes) * y_frames + f] * gain;
+}

@@ -33,6 +33,9 @@
 #include "bb/Reduce.h"
 #include "bb/LossSoftmaxCrossEntropy.h"
 #include "bb/LossMeanSquaredError.h"
+#include "bb/RealToBinary.h"
+#include "bb/BinaryToReal.h"
+#include "bb/UniformDistributionGenerator.h"
 
 namespace {
 
@@ -437,6 +440,53 @@ int bbref_lut_mlp_step(float const *x, float const *t, int frames, int layers, i
         auto p = luts[l]->lock_W_const();
         for (int n = 0; n < widths[l + 1]; ++n) for (int i = 0; i < 64; ++i) W[wo + (size_t)n * 64 + i] = p(n, i);
         wo += (size_t)widths[l + 1] * 64;
+    }
+    return 0;
+}
+
+// bb::RealToBinary<bb::Bit,float>::Forward on an input of node shape {depth, point_size}.  seed == 0: deterministic modulation;
+// otherwise thresholds come from UniformDistributionGenerator<float>(0, 1, seed), data-wise, and th_out [node][out_frame]
+// receives the threshold each comparison used (the same generator is replayed in the draw order of RealToBinary.h:360-392).
+int bbref_real_to_binary(float const *x, int depth, int point_size, int frames, int frame_mod, int depth_mod, std::uint64_t seed,
+                         std::uint32_t *y_bits, float *th_out)
+{
+    std::shared_ptr<bb::ValueGenerator<float>> gen;
+    if (seed) gen = bb::UniformDistributionGenerator<float>::Create(0.0f, 1.0f, seed);
+    auto r2b = bb::RealToBinary<bb::Bit, float>::Create(frame_mod, depth_mod, gen, false);
+    r2b->SendCommand("host_only true");
+    const int nodes = depth * point_size;
+    bb::FrameBuffer x_buf(frames, {depth, point_size}, BB_TYPE_FP32, true);
+    put_fp32(x_buf, x, nodes, frames);
+    auto y_buf = r2b->Forward(x_buf, true);
+    get_bit(y_buf, y_bits, nodes * depth_mod, frames * frame_mod);
+    if (seed && th_out) {
+        auto replay = bb::UniformDistributionGenerator<float>::Create(0.0f, 1.0f, seed);
+        int out_frames = frames * frame_mod;
+        for (int of = 0; of < out_frames; ++of) {
+            float th = replay->GetValue();
+            for (int n = 0; n < nodes; ++n) {
+                th_out[(size_t)n * out_frames + of] = th;
+                th = replay->GetValue();
+            }
+        }
+    }
+    return 0;
+}
+
+// bb::BinaryToReal<bb::Bit,float>: forward of bit frames [x_nodes][y_frames * frame_mux] to fp32 [y_nodes][y_frames], then backward of dy.
+int bbref_binary_to_real(std::uint32_t const *x_bits, int x_nodes, int y_nodes, int y_frames, int frame_mux, float *y, float const *dy, float *dx)
+{
+    auto b2r = bb::BinaryToReal<bb::Bit, float>::Create(frame_mux, bb::indices_t({y_nodes}));
+    b2r->SendCommand("host_only true");
+    bb::FrameBuffer x_buf(y_frames * frame_mux, {x_nodes}, BB_TYPE_BIT, true);
+    put_bit(x_buf, x_bits, x_nodes, y_frames * frame_mux);
+    auto y_buf = b2r->Forward(x_buf, true);
+    if (y) get_fp32(y_buf, y, y_nodes, y_frames);
+    if (dy && dx) {
+        bb::FrameBuffer dy_buf(y_frames, {y_nodes}, BB_TYPE_FP32, true);
+        put_fp32(dy_buf, dy, y_nodes, y_frames);
+        auto dx_buf = b2r->Backward(dy_buf);
+        get_fp32(dx_buf, dx, x_nodes, y_frames * frame_mux);
     }
     return 0;
 }

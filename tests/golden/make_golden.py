@@ -177,6 +177,19 @@ def main():
     import ctypes as C  # noqa: E402
     g.update({"loss_y": yl, "loss_t": tl})
 
+    # Binary modulation (config 2 neighbours): RealToBinary with frame modulation 7 (deterministic and with seeded thresholds from
+    # the reference's UniformDistributionGenerator), BinaryToReal integration back to 10 outputs with its backward.
+    xm = det_uniform((12, 9), 140)
+    for ps in (1, 4):
+        yb, _ = ref.real_to_binary(xm, frame_mod=7, depth_mod=2, seed=0, point_size=ps)
+        ys, th = ref.real_to_binary(xm, frame_mod=7, depth_mod=2, seed=7, point_size=ps)
+        g.update({f"r2b_p{ps}_det": yb, f"r2b_p{ps}_seeded": ys, f"r2b_p{ps}_th": th})
+    g["r2b_x"] = xm
+    xb, _ = ref.real_to_binary(det_uniform((60, 8), 141), frame_mod=7, seed=3)
+    dyb = det_uniform((10, 8), 142)
+    yb2r, dxb2r = ref.binary_to_real(xb, 10, 8, 7, dy=dyb)
+    g.update({"b2r_x": xb, "b2r_dy": dyb, "b2r_y": yb2r, "b2r_dx": dxb2r})
+
     np.savez_compressed(OUT, **g)
     print("wrote", OUT, os.path.getsize(OUT), "bytes,", len(g), "arrays")
 
