@@ -27,8 +27,16 @@ const DeviceInfo &device_info();
 
 // Scratch memory private to (device, stream): grows on demand through the device heap, is reused by
 // later calls on the same stream and is released by bbcu_LocalHeap_GarbageCollect().  Stream order
-// makes back-to-back calls on one stream safe; different streams get different blocks.
-void *stream_scratch(cudaStream_t stream, size_t bytes);
+// makes back-to-back calls on one stream safe; different streams get different blocks.  A stream has
+// kScratchSlots independent blocks, for callers whose scratch is alive at the same time (slot 0: batch-norm
+// sums, slot 1: per-node coefficient tables of the pipelined forward).
+constexpr int kScratchSlots = 2;
+void *stream_scratch(cudaStream_t stream, size_t bytes, int slot = 0);
+
+// Pass 1 of the DifferentiableLut6 training forward (raw LUT values into y, fp64 sums per node); with may_allocate = false
+// it takes nothing from the heap or the stream scratch.
+int dl6_forward_stats(const float *x, float *y, const int *idx, const float *W, double *dev_sums, float unbinarize_bias, int node_size,
+                      int frame_size, int frame_stride, int lut_binarize, int binary_mode, bool may_allocate, cudaStream_t st);
 
 // Frames handled by one CTA pass.  The gathered input rows of a frame tile (and, in the backward
 // pass, the dx rows it reduces into) have to stay resident in L2 while every output node of the

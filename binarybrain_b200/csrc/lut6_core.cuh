@@ -1,14 +1,22 @@
-// Device-side core of the 6-input stochastic LUT: the 63-lerp multilinear tree, its reverse
+// Device-side core of the 6-input stochastic LUT: the 63-node multilinear tree, its reverse
 // pass, and the warp-level reduction of the 64 per-table-entry gradients.
 //
 // A LUT6 node computes  y = sum_{i<64} W[i] * prod_{j<6} (bit_j(i) ? x_j : 1 - x_j)
-// (BinaryBrain include/bb/StochasticOperation.h:95-114).  That multilinear form is evaluated as a
-// binary tree of 63 linear interpolations, one level per input:
-//     level 1: t1[k] = W[2k] + x0 * (W[2k+1] - W[2k])            k < 32
-//     level 2: t2[k] = t1[2k] + x1 * (t1[2k+1] - t1[2k])         k < 16   ... down to y at level 6.
-// The reverse pass walks the same tree: the gradient arriving at a lerp node splits into g*t and
-// g - g*t for its children and contributes g * (b - a) to that level's input gradient; the 32
-// gradients that reach level 1 are the table-entry gradients (times x0 / 1 - x0).
+// (BinaryBrain include/bb/StochasticOperation.h:95-114).  Written as a binary tree of linear interpolations, one
+// level per input, a node is  a (1 - x) + b x  =  (a + b)/2 + (x - 1/2) (b - a).  Pushing that rewrite down to the table
+// turns the multilinear form into a polynomial in the centred inputs u_j = x_j - 1/2,
+//     y = sum_S c[S] prod_{j in S} u_j,
+// whose 64 coefficients come from the table by one butterfly per input, (a, b) -> ((a + b)/2, b - a).  In that basis a
+// tree node is ONE fma (a + u * b) instead of a subtract and an fma: 63 operations per value instead of 94, same walk,
+// same registers:
+//     level 1: t1[k] = c[2k] + u0 * c[2k+1]                      k < 32
+//     level 2: t2[k] = t1[2k] + u1 * t1[2k+1]                    k < 16   ... down to y at level 6.
+// The centred form is also the well-conditioned one: every |u_j| <= 1/2 balances the factor 2 a difference can gain per
+// level, and the table gradients come back from the coefficient gradients without the 64-fold cancellation the
+// uncentred polynomial (in x_j) would have.
+// The reverse pass walks the same tree: the gradient g arriving at a node a + u * b goes on to a unchanged and to b as
+// g * u, and adds g * b to that level's input gradient; the 64 gradients that reach level 1 are the coefficient
+// gradients, summed over frames and only then mapped back to table-entry gradients by the adjoint butterfly.
 //
 // Work mapping used by every LUT kernel: one warp owns one output node for a run of frames; in one
 // iteration a warp covers 128 frames and lane l handles frames  base + 32*q + l,  q = 0..3, so every
@@ -25,7 +33,39 @@ constexpr int kWarpsPerCta   = 8;     // one output node per warp
 constexpr int kFramesPerIter = 128;   // 32 lanes x 4 frames
 constexpr unsigned kFull     = 0xffffffffu;
 
-// Per-node table staged in shared memory as 32 (w, d) pairs: level 1 is t1[k] = fma(x0, d, w).
+// Table -> polynomial coefficients, done by a whole warp: lane l passes table entries 2l and 2l + 1 and gets
+// coefficients 2l and 2l + 1 back (input 0 inside the lane, inputs 1..5 across lanes).
+__device__ __forceinline__ float2 table_to_coeffs(float2 v, int lane)
+{
+    v = make_float2(0.5f * (v.x + v.y), v.y - v.x);
+#pragma unroll
+    for (int b = 0; b < 5; ++b) {
+        const float tx = __shfl_xor_sync(kFull, v.x, 1 << b);
+        const float ty = __shfl_xor_sync(kFull, v.y, 1 << b);
+        const bool upper = (lane >> b) & 1;
+        v.x = upper ? v.x - tx : 0.5f * (v.x + tx);
+        v.y = upper ? v.y - ty : 0.5f * (v.y + ty);
+    }
+    return v;
+}
+
+// The adjoint map: gradients of the coefficients -> gradients of the table entries (same lane layout).
+// For one butterfly (a, b) -> (m, d) = ((a + b)/2, b - a):  da = dm/2 - dd,  db = dm/2 + dd.
+__device__ __forceinline__ float2 coeff_grads_to_table(float2 g, int lane)
+{
+    g = make_float2(0.5f * g.x - g.y, 0.5f * g.x + g.y);
+#pragma unroll
+    for (int b = 0; b < 5; ++b) {
+        const float tx = __shfl_xor_sync(kFull, g.x, 1 << b);
+        const float ty = __shfl_xor_sync(kFull, g.y, 1 << b);
+        const bool upper = (lane >> b) & 1;                  // the upper lane holds dd and receives dm, the lower one the reverse
+        g.x = upper ? fmaf(0.5f, tx, g.x) : fmaf(0.5f, g.x, -tx);
+        g.y = upper ? fmaf(0.5f, ty, g.y) : fmaf(0.5f, g.y, -ty);
+    }
+    return g;
+}
+
+// Per-node coefficients staged in shared memory as 32 (c[2k], c[2k+1]) pairs: level 1 is t1[k] = fma(u0, c[2k+1], c[2k]).
 __device__ __forceinline__ void stage_table(float2 *tab, const float *__restrict__ W, int node, int lane, int lut_binarize)
 {
     __syncwarp();
@@ -34,68 +74,68 @@ __device__ __forceinline__ void stage_table(float2 *tab, const float *__restrict
         v.x = v.x > 0.5f ? 1.0f : 0.0f;
         v.y = v.y > 0.5f ? 1.0f : 0.0f;
     }
-    tab[lane] = make_float2(v.x, v.y - v.x);
+    tab[lane] = table_to_coeffs(v, lane);
     __syncwarp();
 }
 
-// Input conditioning of the reference's CPU path (include/bb/DifferentiableLutN.h:779-786):
-// binary mode maps x to 0.5 +/- bias by (x > 0.5), otherwise x is clipped to [0, 1].
-__device__ __forceinline__ float condition_x(float v, int binary, float bias)
+// Input conditioning of the reference's CPU path (include/bb/DifferentiableLutN.h:779-786), returning the centred
+// input u = x - 1/2: binary mode maps x to 0.5 +/- bias by (x > 0.5), otherwise x is clipped to [0, 1].
+__device__ __forceinline__ float condition_u(float v, int binary, float bias)
 {
-    return binary ? (0.5f + (v > 0.5f ? bias : -bias)) : __saturatef(v);     // one FADD.SAT: clip to [0, 1]
+    return binary ? (v > 0.5f ? bias : -bias) : __saturatef(v) - 0.5f;
 }
 
-__device__ __forceinline__ float lut6_forward(const float2 *tab, const float (&x)[6])
+__device__ __forceinline__ float lut6_forward(const float2 *tab, const float (&u)[6])
 {
     float t[32];
 #pragma unroll
-    for (int k = 0; k < 32; ++k) { float2 wd = tab[k]; t[k] = fmaf(x[0], wd.y, wd.x); }
+    for (int k = 0; k < 32; ++k) { float2 c = tab[k]; t[k] = fmaf(u[0], c.y, c.x); }
 #pragma unroll
-    for (int k = 0; k < 16; ++k) t[k] = fmaf(x[1], t[2 * k + 1] - t[2 * k], t[2 * k]);
+    for (int k = 0; k < 16; ++k) t[k] = fmaf(u[1], t[2 * k + 1], t[2 * k]);
 #pragma unroll
-    for (int k = 0; k < 8; ++k)  t[k] = fmaf(x[2], t[2 * k + 1] - t[2 * k], t[2 * k]);
+    for (int k = 0; k < 8; ++k)  t[k] = fmaf(u[2], t[2 * k + 1], t[2 * k]);
 #pragma unroll
-    for (int k = 0; k < 4; ++k)  t[k] = fmaf(x[3], t[2 * k + 1] - t[2 * k], t[2 * k]);
+    for (int k = 0; k < 4; ++k)  t[k] = fmaf(u[3], t[2 * k + 1], t[2 * k]);
 #pragma unroll
-    for (int k = 0; k < 2; ++k)  t[k] = fmaf(x[4], t[2 * k + 1] - t[2 * k], t[2 * k]);
-    return fmaf(x[5], t[1] - t[0], t[0]);
+    for (int k = 0; k < 2; ++k)  t[k] = fmaf(u[4], t[2 * k + 1], t[2 * k]);
+    return fmaf(u[5], t[1], t[0]);
 }
 
-// The (b - a) differences of levels 2..6, kept between the forward and the reverse pass.
-struct LerpDiffs {
+// The odd ("b") operands of levels 2..6, kept between the forward and the reverse pass.
+struct KeptOperands {
     float d2[16], d3[8], d4[4], d5[2], d6;
 };
 
-__device__ __forceinline__ float lut6_forward_keep(const float2 *tab, const float (&x)[6], LerpDiffs &D)
+__device__ __forceinline__ float lut6_forward_keep(const float2 *tab, const float (&u)[6], KeptOperands &D)
 {
     float t[32];
 #pragma unroll
-    for (int k = 0; k < 32; ++k) { float2 wd = tab[k]; t[k] = fmaf(x[0], wd.y, wd.x); }
+    for (int k = 0; k < 32; ++k) { float2 c = tab[k]; t[k] = fmaf(u[0], c.y, c.x); }
 #pragma unroll
-    for (int k = 0; k < 16; ++k) { D.d2[k] = t[2 * k + 1] - t[2 * k]; t[k] = fmaf(x[1], D.d2[k], t[2 * k]); }
+    for (int k = 0; k < 16; ++k) { D.d2[k] = t[2 * k + 1]; t[k] = fmaf(u[1], D.d2[k], t[2 * k]); }
 #pragma unroll
-    for (int k = 0; k < 8; ++k)  { D.d3[k] = t[2 * k + 1] - t[2 * k]; t[k] = fmaf(x[2], D.d3[k], t[2 * k]); }
+    for (int k = 0; k < 8; ++k)  { D.d3[k] = t[2 * k + 1]; t[k] = fmaf(u[2], D.d3[k], t[2 * k]); }
 #pragma unroll
-    for (int k = 0; k < 4; ++k)  { D.d4[k] = t[2 * k + 1] - t[2 * k]; t[k] = fmaf(x[3], D.d4[k], t[2 * k]); }
+    for (int k = 0; k < 4; ++k)  { D.d4[k] = t[2 * k + 1]; t[k] = fmaf(u[3], D.d4[k], t[2 * k]); }
 #pragma unroll
-    for (int k = 0; k < 2; ++k)  { D.d5[k] = t[2 * k + 1] - t[2 * k]; t[k] = fmaf(x[4], D.d5[k], t[2 * k]); }
-    D.d6 = t[1] - t[0];
-    return fmaf(x[5], D.d6, t[0]);
+    for (int k = 0; k < 2; ++k)  { D.d5[k] = t[2 * k + 1]; t[k] = fmaf(u[4], D.d5[k], t[2 * k]); }
+    D.d6 = t[1];
+    return fmaf(u[5], D.d6, t[0]);
 }
 
-// Reverse pass for one frame: g is the gradient arriving at y.  Adds the 64 table-entry gradients
-// into acc (acc[i] belongs to W[i]) and returns the six input gradients in dx.
-__device__ __forceinline__ void lut6_reverse(const float2 *tab, const float (&x)[6], const LerpDiffs &D, float g,
+// Reverse pass for one frame: g is the gradient arriving at y.  Adds the 64 coefficient gradients
+// into acc (acc[i] belongs to c[i]) and returns the six input gradients in dx.
+__device__ __forceinline__ void lut6_reverse(const float2 *tab, const float (&u)[6], const KeptOperands &D, float g,
                                              float (&acc)[64], float (&dx)[6])
 {
     float gt[32];
     dx[5] = g * D.d6;
-    gt[1] = g * x[5];
-    gt[0] = g - gt[1];
+    gt[0] = g;
+    gt[1] = g * u[5];
 
     dx[4] = fmaf(gt[1], D.d5[1], gt[0] * D.d5[0]);
 #pragma unroll
-    for (int k = 1; k >= 0; --k) { float hi = gt[k] * x[4]; gt[2 * k] = gt[k] - hi; gt[2 * k + 1] = hi; }
+    for (int k = 1; k >= 0; --k) { gt[2 * k + 1] = gt[k] * u[4]; gt[2 * k] = gt[k]; }
 
     {
         float s = 0.0f;
@@ -104,7 +144,7 @@ __device__ __forceinline__ void lut6_reverse(const float2 *tab, const float (&x)
         dx[3] = s;
     }
 #pragma unroll
-    for (int k = 3; k >= 0; --k) { float hi = gt[k] * x[3]; gt[2 * k] = gt[k] - hi; gt[2 * k + 1] = hi; }
+    for (int k = 3; k >= 0; --k) { gt[2 * k + 1] = gt[k] * u[3]; gt[2 * k] = gt[k]; }
 
     {
         float s0 = 0.0f, s1 = 0.0f;
@@ -113,7 +153,7 @@ __device__ __forceinline__ void lut6_reverse(const float2 *tab, const float (&x)
         dx[2] = s0 + s1;
     }
 #pragma unroll
-    for (int k = 7; k >= 0; --k) { float hi = gt[k] * x[2]; gt[2 * k] = gt[k] - hi; gt[2 * k + 1] = hi; }
+    for (int k = 7; k >= 0; --k) { gt[2 * k + 1] = gt[k] * u[2]; gt[2 * k] = gt[k]; }
 
     {
         float s0 = 0.0f, s1 = 0.0f;
@@ -122,11 +162,10 @@ __device__ __forceinline__ void lut6_reverse(const float2 *tab, const float (&x)
         dx[1] = s0 + s1;
     }
 #pragma unroll
-    for (int k = 15; k >= 0; --k) { float hi = gt[k] * x[1]; gt[2 * k] = gt[k] - hi; gt[2 * k + 1] = hi; }
+    for (int k = 15; k >= 0; --k) { gt[2 * k + 1] = gt[k] * u[1]; gt[2 * k] = gt[k]; }
 
     {
         float s0 = 0.0f, s1 = 0.0f;
-        const float nx0 = 1.0f - x[0];
 #pragma unroll
         for (int k = 0; k < 32; k += 2) {
             s0 = fmaf(gt[k], tab[k].y, s0);
@@ -134,8 +173,8 @@ __device__ __forceinline__ void lut6_reverse(const float2 *tab, const float (&x)
         }
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
-            acc[2 * k]     = fmaf(gt[k], nx0, acc[2 * k]);
-            acc[2 * k + 1] = fmaf(gt[k], x[0], acc[2 * k + 1]);
+            acc[2 * k]    += gt[k];
+            acc[2 * k + 1] = fmaf(gt[k], u[0], acc[2 * k + 1]);
         }
         dx[0] = s0 + s1;
     }
@@ -175,7 +214,7 @@ __device__ __forceinline__ double warp_sum(double v)
 
 // ---------------------------------------------------------------------------------------------------
 // Packed-pair arithmetic (sm_100 f32x2): one instruction does the same fp32 operation on two frames held in a
-// 64-bit register pair, so the 63-lerp tree of two frames costs 94 issue slots instead of 188.  Each lane carries
+// 64-bit register pair, so the 63-node tree of two frames costs 63 issue slots instead of 126.  Each lane carries
 // NP pairs; the tree is walked depth first (a node's value is produced and consumed before its sibling subtree is
 // started), which keeps about one live value per level and pair instead of 32.
 // ---------------------------------------------------------------------------------------------------
@@ -190,7 +229,8 @@ __device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) { f32x2 d; asm("sub.rn.f
 __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { f32x2 d; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
 __device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) { f32x2 d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
 
-// Per-node table for the packed path: 32 entries of (w, w, d, d), i.e. level 1 reads both packed operands with one 128-bit load.
+// Per-node table for the packed path: 32 entries of (c0, c0, c1, c1), the coefficient pair of a level-1 node duplicated for
+// both halves of a packed operand, so that level 1 reads both operands with one 128-bit load.
 __device__ __forceinline__ void stage_table_x2(float4 *tab, const float *__restrict__ W, int node, int lane, int lut_binarize)
 {
     __syncwarp();
@@ -199,8 +239,8 @@ __device__ __forceinline__ void stage_table_x2(float4 *tab, const float *__restr
         v.x = v.x > 0.5f ? 1.0f : 0.0f;
         v.y = v.y > 0.5f ? 1.0f : 0.0f;
     }
-    const float d = v.y - v.x;
-    tab[lane] = make_float4(v.x, v.x, d, d);
+    v = table_to_coeffs(v, lane);
+    tab[lane] = make_float4(v.x, v.x, v.y, v.y);
     __syncwarp();
 }
 
@@ -213,7 +253,7 @@ struct LerpTree {
         LerpTree<L - 1, 2 * K, NP>::eval(tab, x, a);
         LerpTree<L - 1, 2 * K + 1, NP>::eval(tab, x, b);
 #pragma unroll
-        for (int p = 0; p < NP; ++p) out[p] = fma2(x[L - 1][p], sub2(b[p], a[p]), a[p]);
+        for (int p = 0; p < NP; ++p) out[p] = fma2(x[L - 1][p], b[p], a[p]);
     }
 };
 
@@ -221,7 +261,7 @@ template <int K, int NP>
 struct LerpTree<1, K, NP> {
     static __device__ __forceinline__ void eval(const float4 *tab, const f32x2 (&x)[6][NP], f32x2 (&out)[NP])
     {
-        const ulonglong2 wd = *reinterpret_cast<const ulonglong2 *>(tab + K);     // .x = (w, w), .y = (d, d)
+        const ulonglong2 wd = *reinterpret_cast<const ulonglong2 *>(tab + K);     // .x = (c0, c0), .y = (c1, c1)
 #pragma unroll
         for (int p = 0; p < NP; ++p) out[p] = fma2(x[0][p], wd.y, wd.x);
     }

@@ -36,8 +36,11 @@ struct FwdArgs {
     int O, F, T;
     long long xs, ys;       // row strides in elements (floats / words)
     int lut_binarize, binary, stat_is_var, groups;
+    const float4 *coef;     // pipelined kernel only: per-node tables already in packed-operand form, or nullptr
+    int no_scratch;         // launcher: do not take the coefficient table from the stream's scratch (which may allocate)
 };
 
+// Centred, conditioned inputs u = x - 1/2 of the lane's four frames of one 128-frame iteration.
 template <bool XBIT>
 __device__ __forceinline__ void gather_x(float (&xv)[4][6], const void *x, long long xs, const int (&rows)[6], int base, int lane, int F,
                                          int binary, float bias)
@@ -50,7 +53,7 @@ __device__ __forceinline__ void gather_x(float (&xv)[4][6], const void *x, long 
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 uint32_t w = (base + 32 * q < F) ? __ldg(row + q) : 0u;
-                xv[q][j] = 0.5f + (((w >> lane) & 1u) ? bias : -bias);
+                xv[q][j] = ((w >> lane) & 1u) ? bias : -bias;
             }
         }
     } else {
@@ -61,7 +64,7 @@ __device__ __forceinline__ void gather_x(float (&xv)[4][6], const void *x, long 
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 float v = (base + 32 * q + lane < F) ? __ldg(row + 32 * q) : 0.0f;
-                xv[q][j] = condition_x(v, binary, bias);
+                xv[q][j] = condition_u(v, binary, bias);
             }
         }
     }
@@ -147,18 +150,26 @@ k_lut6_forward(const FwdArgs a)
 // Persistent, bulk-copy-pipelined forward for fp32 inputs with 16-byte aligned rows (the launcher's default).
 // Work item = (frame tile of a.T = 128 or 256 frames, group of 8 nodes); CTA c takes items c, c + gridDim, ... so
 // the CTAs in flight sweep the node groups of one tile together and the tile's rows stay in L2.  Each warp owns one
-// node of the group and runs its own two-stage pipeline: lane 0 starts seven bulk copies (six gathered row
-// segments and the node's 64 table entries) for item j+2 once item j has been read out of shared memory, and the
+// node of the group and runs its own two-stage pipeline: seven lanes start one bulk copy each (six gathered row
+// segments and the node's table) for item j+2 once item j has been read out of shared memory, and the
 // warp computes item j while the copies of j+1 (and j+2) are in flight.
+// The table normally arrives ready to use: a small kernel in front (k_table_coeffs) has turned every node's 64 entries
+// into the 32 x (c0, c0, c1, c1) packed-operand form once per launch, so no warp repeats that butterfly (ten shuffles
+// in a dependent chain) for every item.  Tables have a ring of three slots per warp because the table of item j is
+// still being read while the copies of item j+2 are started.  Without the scratch table (a.coef == nullptr) the raw
+// entries are copied instead and converted in place.
 // ---------------------------------------------------------------------------------------------
 constexpr int kFpMaxItemFrames = 256;
 constexpr int kFpStages        = 2;
-constexpr int kFpStageBytes    = 6 * kFpMaxItemFrames * 4 + 256;                       // six row segments + raw W[64]
+constexpr int kFpStageBytes    = 6 * kFpMaxItemFrames * 4;                             // six row segments
 constexpr int kFpRowsBytes     = kWarpsPerCta * kFpStages * kFpStageBytes;
 constexpr int kFpBarBytes      = 128;
-constexpr int kFpTabBytes      = kWarpsPerCta * 32 * 16;
+constexpr int kFpTabSlots      = 3;
+constexpr int kFpTabSlotBytes  = 32 * 16;
+constexpr int kFpTabBytes      = kWarpsPerCta * kFpTabSlots * kFpTabSlotBytes;
 constexpr int kFpSmem          = kFpRowsBytes + kFpBarBytes + kFpTabBytes;
 static_assert(kWarpsPerCta * kFpStages * 8 <= kFpBarBytes, "barrier block too small");
+static_assert(2 * (kFpSmem + 1024) <= 227 * 1024, "two CTAs per SM must fit");
 
 // Position of a work item, advanced incrementally (item index + gridDim) so that no division runs per item.
 struct FpPos {
@@ -175,22 +186,38 @@ __device__ __forceinline__ FpPos fp_advance(FpPos p, int dt, int dg, int groups)
 
 // Lanes 0..5 each start the bulk copy of one gathered row segment and lane 6 that of the node's table (one
 // instruction issue covers all seven); lane 0 has armed the barrier with the byte count just before.
-__device__ __forceinline__ void fp_issue(const FwdArgs &a, FpPos pos, int warp, int lane, unsigned char *stage, uint64_t *bar)
+__device__ __forceinline__ void fp_issue(const FwdArgs &a, FpPos pos, int warp, int lane, unsigned char *stage, unsigned char *tab_slot,
+                                         uint64_t *bar)
 {
     const int node = min(pos.group * kWarpsPerCta + warp, a.O - 1);
     const int f0   = pos.tile * a.T;
     const uint32_t bytes = (uint32_t)min((long long)a.T, a.xs - f0) * 4u;       // row stride is a multiple of 4 floats
-    if (lane == 0) mbar_arrive_expect_tx(bar, 6u * bytes + 256u);
+    const uint32_t tab_bytes = a.coef ? (uint32_t)kFpTabSlotBytes : 256u;
+    if (lane == 0) mbar_arrive_expect_tx(bar, 6u * bytes + tab_bytes);
     __syncwarp();
     if (lane < 6) {
         const float *src = static_cast<const float *>(a.x) + (size_t)__ldg(a.idx + (size_t)node * 6 + lane) * a.xs + f0;
         bulk_copy_g2s(stage + lane * (kFpMaxItemFrames * 4), src, bytes, bar);
     } else if (lane == 6) {
-        bulk_copy_g2s(stage + 6 * kFpMaxItemFrames * 4, a.W + (size_t)node * 64, 256u, bar);
+        if (a.coef) bulk_copy_g2s(tab_slot, a.coef + (size_t)node * 32, tab_bytes, bar);
+        else        bulk_copy_g2s(tab_slot, a.W + (size_t)node * 64, tab_bytes, bar);
     }
 }
 
-template <int PHASE>
+// Every node's table as 32 x (c0, c0, c1, c1): the polynomial coefficients, each duplicated for the two halves of a packed operand.
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+k_table_coeffs(const float *__restrict__ W, float4 *__restrict__ coef, int O, int lut_binarize)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int node = blockIdx.x * kWarpsPerCta + warp;
+    if (node >= O) return;
+    float2 v = reinterpret_cast<const float2 *>(W + (size_t)node * 64)[lane];
+    if (lut_binarize) { v.x = v.x > 0.5f ? 1.0f : 0.0f; v.y = v.y > 0.5f ? 1.0f : 0.0f; }
+    v = table_to_coeffs(v, lane);
+    coef[(size_t)node * 32 + lane] = make_float4(v.x, v.x, v.y, v.y);
+}
+
+template <int PHASE, bool BINARY>            // BINARY: the layer's binary mode, compiled in so that input conditioning is one instruction
 __global__ void __launch_bounds__(kWarpsPerCta * 32, 2)
 k_lut6_forward_pipe(const FwdArgs a, int n_tiles, int *fault)
 {
@@ -198,7 +225,7 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles, int *fault)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned char *my_stages = smem_raw + (size_t)warp * kFpStages * kFpStageBytes;
     uint64_t *my_bar = reinterpret_cast<uint64_t *>(smem_raw + kFpRowsBytes) + warp * kFpStages;
-    float4   *tab    = reinterpret_cast<float4 *>(smem_raw + kFpRowsBytes + kFpBarBytes) + warp * 32;
+    unsigned char *my_tabs = smem_raw + kFpRowsBytes + kFpBarBytes + (size_t)warp * kFpTabSlots * kFpTabSlotBytes;
 
     if (lane == 0) {
         for (int s = 0; s < kFpStages; ++s) mbar_init(my_bar + s, 1);
@@ -214,8 +241,9 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles, int *fault)
     p0.group = (int)blockIdx.x - p0.tile * a.groups;
     FpPos p1 = fp_advance(p0, dt, dg, a.groups);
     FpPos p2 = fp_advance(p1, dt, dg, a.groups);
-    if (p0.tile < n_tiles) fp_issue(a, p0, warp, lane, my_stages, my_bar);
-    if (p1.tile < n_tiles) fp_issue(a, p1, warp, lane, my_stages + kFpStageBytes, my_bar + 1);
+    if (p0.tile < n_tiles) fp_issue(a, p0, warp, lane, my_stages, my_tabs, my_bar);
+    if (p1.tile < n_tiles) fp_issue(a, p1, warp, lane, my_stages + kFpStageBytes, my_tabs + kFpTabSlotBytes, my_bar + 1);
+    int ts = 0;                                   // table slot of the current item: k mod 3
 
     // per-node batch-norm constants travel one item ahead of their use
     float mean_n = 0.0f, scale_n = 0.0f;
@@ -248,55 +276,59 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles, int *fault)
             if (have_next) mbar_wait(my_bar + (s ^ 1), (uint32_t)((k + 1) >> 1) & 1u);
             return;
         }
-        {   // raw W[64] -> 32 x (w, w, d, d)
-            float2 v = reinterpret_cast<const float2 *>(stage + 6 * kFpMaxItemFrames * 4)[lane];
+        float4 *tab = reinterpret_cast<float4 *>(my_tabs + ts * kFpTabSlotBytes);
+        unsigned char *tab_refill = my_tabs + (ts == 0 ? 2 : ts - 1) * kFpTabSlotBytes;      // slot (k + 2) mod 3, last read by item k - 1
+        ts = ts == 2 ? 0 : ts + 1;
+        if (a.coef == nullptr) {   // raw W[64] arrived: convert in place to 32 x (c0, c0, c1, c1)
+            float2 v = reinterpret_cast<const float2 *>(tab)[lane];
             if (a.lut_binarize) { v.x = v.x > 0.5f ? 1.0f : 0.0f; v.y = v.y > 0.5f ? 1.0f : 0.0f; }
-            const float d = v.y - v.x;
+            v = table_to_coeffs(v, lane);
             __syncwarp();
-            tab[lane] = make_float4(v.x, v.x, d, d);
+            tab[lane] = make_float4(v.x, v.x, v.y, v.y);
             __syncwarp();
         }
         double s1 = 0.0, s2 = 0.0;
         const float *xs0 = reinterpret_cast<const float *>(stage);
         float *yrow = a.y + (size_t)node * a.ys + f0 + lane;
-        // one walk of the tree carries NP frame pairs per lane: 4 pairs (256 frames per warp) when the item is that wide
+        // One walk of the tree carries NP frame pairs per lane (frames 32q + lane; pair p = frames q = 2p, 2p + 1): 4 pairs when the
+        // item is 256 frames wide, 2 pairs for a 128-frame item.
         auto walk = [&](auto np_tag) {
             constexpr int NP = decltype(np_tag)::value;
-            f32x2 xp[6][NP], yp[NP];
+            f32x2 up[6][NP], yp[NP];
 #pragma unroll
             for (int j = 0; j < 6; ++j) {
                 const float *r = xs0 + j * kFpMaxItemFrames + lane;
 #pragma unroll
-                for (int p = 0; p < NP; ++p)
-                    xp[j][p] = pack2(condition_x(r[64 * p], a.binary, a.bias), condition_x(r[64 * p + 32], a.binary, a.bias));
+                for (int p = 0; p < NP; ++p) {
+                    // the same values as condition_u()
+                    if (BINARY) up[j][p] = pack2(r[64 * p] > 0.5f ? a.bias : -a.bias, r[64 * p + 32] > 0.5f ? a.bias : -a.bias);
+                    else        up[j][p] = pack2(__saturatef(r[64 * p]) - 0.5f, __saturatef(r[64 * p + 32]) - 0.5f);
+                }
             }
             // the stage has been read out: hand it back to the copy engine for item k+2 before doing the math
             __syncwarp();
             if (p2.tile < n_tiles) {
                 proxy_fence_async();
-                fp_issue(a, p2, warp, lane, stage, my_bar + s);
+                fp_issue(a, p2, warp, lane, stage, tab_refill, my_bar + s);
             }
-            lut6_forward_x2<NP>(tab, xp, yp);
+            lut6_forward_x2<NP>(tab, up, yp);
 #pragma unroll
-            for (int p = 0; p < NP; ++p) {
-                float vq[2];
-                unpack2(yp[p], vq[0], vq[1]);
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int fl = 64 * p + 32 * e;
-                    const bool live = store && fl + lane < nf;
-                    float v = vq[e];
-                    if (PHASE == PH_STATS) {
-                        if (live) { s1 += (double)v; s2 += (double)v * (double)v; }
-                    } else if (PHASE == PH_NORM) {
-                        v = (v - mean) * scale;
-                        v = v * a.gamma + a.beta;
-                        v = a.binary ? (v > 0.5f ? 1.0f : 0.0f) : __saturatef(v);
-                    } else {
-                        v = __saturatef(v);
-                    }
-                    if (live) yrow[fl] = v;
+            for (int q = 0; q < 2 * NP; ++q) {
+                const int fl = 32 * q;
+                const bool live = store && fl + lane < nf;
+                float v0, v1;
+                unpack2(yp[q >> 1], v0, v1);
+                float v = (q & 1) ? v1 : v0;
+                if (PHASE == PH_STATS) {
+                    if (live) { s1 += (double)v; s2 += (double)v * (double)v; }
+                } else if (PHASE == PH_NORM) {
+                    v = (v - mean) * scale;
+                    v = v * a.gamma + a.beta;
+                    v = BINARY ? (v > 0.5f ? 1.0f : 0.0f) : __saturatef(v);
+                } else {
+                    v = __saturatef(v);
                 }
+                if (live) yrow[fl] = v;
             }
         };
         if (nf > kFramesPerIter) walk(std::integral_constant<int, 4>());
@@ -540,7 +572,7 @@ k_lut6_backward(const BwdArgs a)
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const int f = base + 32 * q + lane;
-            LerpDiffs D;
+            KeptOperands D;
             float v = lut6_forward_keep(tab, xv[q], D);
             float g = dyv[q];
             if (BN) {
@@ -559,9 +591,10 @@ k_lut6_backward(const BwdArgs a)
         }
     }
     warp_reduce_scatter64(acc, lane);
+    const float2 gw = coeff_grads_to_table(make_float2(acc[0], acc[1]), lane);
     float *dst = a.dW + (size_t)node * 64 + 2 * lane;
-    atomicAdd(dst, acc[0]);
-    atomicAdd(dst + 1, acc[1]);
+    atomicAdd(dst, gw.x);
+    atomicAdd(dst + 1, gw.y);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -595,7 +628,8 @@ static int launch_forward(FwdArgs a, int max_tile, cudaStream_t st)
         // pipelined path: rows and tables must start on 16-byte boundaries for the bulk copies
         const bool aligned = ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.W)) & 15) == 0 && (a.xs % 4) == 0;
         int *fault = aligned ? fault_word() : nullptr;
-        if (aligned && fault != nullptr && allow_big_smem(k_lut6_forward_pipe<PHASE>, kFpSmem)) {
+        auto kern = a.binary ? k_lut6_forward_pipe<PHASE, true> : k_lut6_forward_pipe<PHASE, false>;
+        if (aligned && fault != nullptr && allow_big_smem(kern, kFpSmem)) {
             // 256-frame items whenever there are that many frames: four frame pairs per lane share every table read and the
             // per-item costs halve.  Measured on B200: 65536 -> 65536 nodes x 4096 frames 1.89 ms (128) vs 1.49 ms (256), although
             // the 256-frame tile of such a layer (64 MiB of gathered rows) no longer fits a fifth of L2.
@@ -604,7 +638,16 @@ static int launch_forward(FwdArgs a, int max_tile, cudaStream_t st)
             BB200_REQUIRE(n_items < (1LL << 31) - 4096, BBCU_ERR_TOO_LARGE);      // 32-bit item arithmetic in the kernel
             long long grid = 2LL * device_info().sm_count;
             if (grid > n_items) grid = n_items;
-            k_lut6_forward_pipe<PHASE><<<(unsigned)grid, kWarpsPerCta * 32, kFpSmem, st>>>(a, (a.F + a.T - 1) / a.T, fault);
+            if (!a.no_scratch) {
+                // slot 1 of the stream's scratch: slot 0 may hold the caller's batch-norm sums at the same time
+                float4 *coef = static_cast<float4 *>(stream_scratch(st, (size_t)a.O * kFpTabSlotBytes, 1));
+                if (coef != nullptr) {
+                    k_table_coeffs<<<a.groups, kWarpsPerCta * 32, 0, st>>>(a.W, coef, a.O, a.lut_binarize);
+                    BB200_CUDA(cudaPeekAtLastError());
+                    a.coef = coef;
+                }
+            }
+            kern<<<(unsigned)grid, kWarpsPerCta * 32, kFpSmem, st>>>(a, (a.F + a.T - 1) / a.T, fault);
             return launch_status();
         }
     }
@@ -755,20 +798,29 @@ static int dl6_finalize_and_normalize(float *y, const double *sums, float *mean,
     return launch_status();
 }
 
-extern "C" int bbcu_fp32_DifferentiableLut6_ForwardStats(const float *x, float *y, const int *idx, const float *W, double *dev_sums,
-                                                         float unbinarize_bias, int node_size, int frame_size, int frame_stride,
-                                                         int lut_binarize, int binary_mode, bbcu_stream_t stream)
+namespace bb200 {
+int dl6_forward_stats(const float *x, float *y, const int *idx, const float *W, double *dev_sums, float unbinarize_bias, int node_size,
+                      int frame_size, int frame_stride, int lut_binarize, int binary_mode, bool may_allocate, cudaStream_t st)
 {
     int rc = check_common(x, y, idx, W, node_size, frame_size, frame_stride);
     if (rc) return rc;
     BB200_REQUIRE_PTR(dev_sums);
     BB200_REQUIRE(frame_stride >= frame_size, BBCU_ERR_BAD_STRIDE);
-    cudaStream_t st = as_stream(stream);
     BB200_CUDA(cudaMemsetAsync(dev_sums, 0, sizeof(double) * 2 * (size_t)node_size, st));
     FwdArgs a = {};
     a.x = x; a.y = y; a.idx = idx; a.W = W; a.sums = dev_sums; a.bias = unbinarize_bias;
     a.O = node_size; a.F = frame_size; a.xs = frame_stride; a.ys = frame_stride; a.lut_binarize = lut_binarize; a.binary = binary_mode;
+    a.no_scratch = may_allocate ? 0 : 1;
     return launch_forward<false, PH_STATS, false>(a, 2048, st);
+}
+}   // namespace bb200
+
+extern "C" int bbcu_fp32_DifferentiableLut6_ForwardStats(const float *x, float *y, const int *idx, const float *W, double *dev_sums,
+                                                         float unbinarize_bias, int node_size, int frame_size, int frame_stride,
+                                                         int lut_binarize, int binary_mode, bbcu_stream_t stream)
+{
+    return dl6_forward_stats(x, y, idx, W, dev_sums, unbinarize_bias, node_size, frame_size, frame_stride, lut_binarize, binary_mode, true,
+                             as_stream(stream));
 }
 
 extern "C" int bbcu_fp32_DifferentiableLut6_ForwardNormalize(float *y, const double *dev_sums, float *mean, float *rstd, float *rmean,

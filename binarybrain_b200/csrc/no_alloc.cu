@@ -69,8 +69,9 @@ extern "C" int bbcu_fp32_DifferentiableLut6_ForwardTraining_NoAlloc(const float 
     if (rc) return rc;
     // pass 1 clears `sums` on the stream, stores the raw LUT values in y and accumulates the per-node sums;
     // pass 2 turns the sums into mean / rstd / running statistics and normalises y in place
-    rc = bbcu_fp32_DifferentiableLut6_ForwardStats(dev_x_buf, dev_y_buf, dev_input_index, dev_W, sums, unbinarize_bias, node_size, frame_size,
-                                                   frame_stride, lut_binarize, binary_mode, stream);
+    // (may_allocate = false: the kernel then converts each node's table itself instead of reading a converted copy from heap scratch)
+    rc = bb200::dl6_forward_stats(dev_x_buf, dev_y_buf, dev_input_index, dev_W, sums, unbinarize_bias, node_size, frame_size, frame_stride,
+                           lut_binarize, binary_mode, false, bb200::as_stream(stream));
     if (rc) return rc;
     return bbcu_fp32_DifferentiableLut6_ForwardNormalize(dev_y_buf, sums, dev_mean_buf, dev_rstd_buf, dev_running_mean_buf, dev_running_var_buf,
                                                          gamma, beta, momentum, node_size, frame_size, frame_stride, frame_size, binary_mode,

@@ -26,7 +26,7 @@ struct Pool {
     std::unordered_map<void *, size_t> live;          // ptr -> block size
     std::multimap<size_t, void *> cached;             // block size -> ptr
     size_t live_bytes = 0, cached_bytes = 0, max_alloc = 0, byte_limit = 0;
-    std::map<cudaStream_t, std::pair<void *, size_t>> scratch;
+    std::map<std::pair<cudaStream_t, int>, std::pair<void *, size_t>> scratch;     // (stream, slot) -> block
 };
 
 std::mutex g_pools_mu;
@@ -103,13 +103,15 @@ int *fault_word()
     return it->second;
 }
 
-void *stream_scratch(cudaStream_t stream, size_t bytes)
+void *stream_scratch(cudaStream_t stream, size_t bytes, int slot)
 {
+    if (slot < 0 || slot >= kScratchSlots) return nullptr;
+    const std::pair<cudaStream_t, int> key(stream, slot);
     if (bytes == 0) bytes = 256;
     Pool &p = pool_of_current_device();
     {
         std::lock_guard<std::mutex> g(p.mu);
-        auto it = p.scratch.find(stream);
+        auto it = p.scratch.find(key);
         if (it != p.scratch.end() && it->second.second >= bytes) return it->second.first;
     }
     // grow: the old block goes back to the heap cache (work already enqueued on it is stream-ordered
@@ -120,9 +122,9 @@ void *stream_scratch(cudaStream_t stream, size_t bytes)
     void *old = nullptr;
     {
         std::lock_guard<std::mutex> g(p.mu);
-        auto it = p.scratch.find(stream);
+        auto it = p.scratch.find(key);
         if (it != p.scratch.end()) old = it->second.first;
-        p.scratch[stream] = std::make_pair(fresh, bytes);
+        p.scratch[key] = std::make_pair(fresh, bytes);
     }
     if (old) {
         cudaStreamSynchronize(stream);
