@@ -228,17 +228,20 @@ __device__ __forceinline__ PipePos pipe_advance(PipePos p, int dt, int dg, int g
 
 // Lanes 0..5 each start the bulk copy of one gathered row segment (one instruction issue covers all six); lane 0 has
 // armed the barrier with the byte count just before.
-__device__ __forceinline__ void pipe_issue(const BlArgs &a, PipePos pos, int warp, int lane, uint32_t *stage, uint64_t *bar)
+// `row` is the lane's input row of the item's node (pipe_row), fetched an item earlier so that the copy does not wait for it.
+__device__ __forceinline__ void pipe_issue(const BlArgs &a, PipePos pos, int row, int lane, uint32_t *stage, uint64_t *bar)
 {
-    const int node  = min(pos.group * kBlWarps + warp, a.O - 1);
     const int w0    = pos.tile * kPipeWords;
     const uint32_t bytes = (uint32_t)min(kPipeWords, a.nwords - w0) * 4u;
     if (lane == 0) mbar_arrive_expect_tx(bar, 6u * bytes);
     __syncwarp();
-    if (lane < 6) {
-        const uint32_t *src = a.x + (size_t)__ldg(a.idx + (size_t)node * 6 + lane) * a.stride + w0;
-        bulk_copy_g2s(stage + lane * kPipeWords, src, bytes, bar);
-    }
+    if (lane < 6) bulk_copy_g2s(stage + lane * kPipeWords, a.x + (size_t)row * a.stride + w0, bytes, bar);
+}
+
+__device__ __forceinline__ int pipe_row(const BlArgs &a, PipePos pos, int warp, int lane)
+{
+    const int node = min(pos.group * kBlWarps + warp, a.O - 1);
+    return lane < 6 ? __ldg(a.idx + (size_t)node * 6 + lane) : 0;
 }
 
 __global__ void __launch_bounds__(kBlWarps * 32, 2)
@@ -269,8 +272,9 @@ k_binary_lut6_pipe(const BlArgs a, int n_tiles, int *fault)
     PipePos p1 = pipe_advance(p0, dt, dg, a.groups);
     PipePos p2 = pipe_advance(p1, dt, dg, a.groups);
 
-    if (p0.tile < n_tiles) pipe_issue(a, p0, warp, lane, my_rows, my_bar);
-    if (p1.tile < n_tiles) pipe_issue(a, p1, warp, lane, my_rows + 6 * kPipeWords, my_bar + 1);
+    if (p0.tile < n_tiles) pipe_issue(a, p0, pipe_row(a, p0, warp, lane), lane, my_rows, my_bar);
+    if (p1.tile < n_tiles) pipe_issue(a, p1, pipe_row(a, p1, warp, lane), lane, my_rows + 6 * kPipeWords, my_bar + 1);
+    int row2 = p2.tile < n_tiles ? pipe_row(a, p2, warp, lane) : 0;          // input rows of item k+2, one item ahead of their use
     uint32_t tword = 0;
     if (p0.tile < n_tiles) tword = (uint32_t)__ldg(a.table + 2 * (size_t)min(p0.group * kBlWarps + warp, a.O - 1) + (lane >> 4));
 
@@ -310,14 +314,16 @@ k_binary_lut6_pipe(const BlArgs a, int n_tiles, int *fault)
         __syncwarp();                                   // every lane has read the stage out
         if (p2.tile < n_tiles) {
             proxy_fence_async();                        // reads above (generic proxy) before the refill (async proxy)
-            pipe_issue(a, p2, warp, lane, stage, my_bar + s);
+            pipe_issue(a, p2, row2, lane, stage, my_bar + s);
         }
+        const PipePos p3 = pipe_advance(p2, dt, dg, a.groups);
+        if (p3.tile < n_tiles) row2 = pipe_row(a, p3, warp, lane);
         MuxTree<6, 0, 8>::eval(my_ab, xw, o);
         uint32_t *yrow = a.y + (size_t)min(node, a.O - 1) * a.stride + w0;
         if (store && w < nw)       *reinterpret_cast<uint4 *>(yrow + w)       = make_uint4(o[0], o[1], o[2], o[3]);
         if (store && w + 128 < nw) *reinterpret_cast<uint4 *>(yrow + w + 128) = make_uint4(o[4], o[5], o[6], o[7]);
 
-        p0 = p1; p1 = p2; p2 = pipe_advance(p2, dt, dg, a.groups);
+        p0 = p1; p1 = p2; p2 = p3;
     }
 }
 

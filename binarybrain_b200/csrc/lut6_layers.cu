@@ -186,7 +186,14 @@ __device__ __forceinline__ FpPos fp_advance(FpPos p, int dt, int dg, int groups)
 
 // Lanes 0..5 each start the bulk copy of one gathered row segment and lane 6 that of the node's table (one
 // instruction issue covers all seven); lane 0 has armed the barrier with the byte count just before.
-__device__ __forceinline__ void fp_issue(const FwdArgs &a, FpPos pos, int warp, int lane, unsigned char *stage, unsigned char *tab_slot,
+// `row` is the lane's input row of the item's node (fp_row), fetched an item earlier so that the copy does not wait for it.
+__device__ __forceinline__ int fp_row(const FwdArgs &a, FpPos pos, int warp, int lane)
+{
+    const int node = min(pos.group * kWarpsPerCta + warp, a.O - 1);
+    return lane < 6 ? __ldg(a.idx + (size_t)node * 6 + lane) : 0;
+}
+
+__device__ __forceinline__ void fp_issue(const FwdArgs &a, FpPos pos, int row, int warp, int lane, unsigned char *stage, unsigned char *tab_slot,
                                          uint64_t *bar)
 {
     const int node = min(pos.group * kWarpsPerCta + warp, a.O - 1);
@@ -196,7 +203,7 @@ __device__ __forceinline__ void fp_issue(const FwdArgs &a, FpPos pos, int warp, 
     if (lane == 0) mbar_arrive_expect_tx(bar, 6u * bytes + tab_bytes);
     __syncwarp();
     if (lane < 6) {
-        const float *src = static_cast<const float *>(a.x) + (size_t)__ldg(a.idx + (size_t)node * 6 + lane) * a.xs + f0;
+        const float *src = static_cast<const float *>(a.x) + (size_t)row * a.xs + f0;
         bulk_copy_g2s(stage + lane * (kFpMaxItemFrames * 4), src, bytes, bar);
     } else if (lane == 6) {
         if (a.coef) bulk_copy_g2s(tab_slot, a.coef + (size_t)node * 32, tab_bytes, bar);
@@ -241,8 +248,9 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles, int *fault)
     p0.group = (int)blockIdx.x - p0.tile * a.groups;
     FpPos p1 = fp_advance(p0, dt, dg, a.groups);
     FpPos p2 = fp_advance(p1, dt, dg, a.groups);
-    if (p0.tile < n_tiles) fp_issue(a, p0, warp, lane, my_stages, my_tabs, my_bar);
-    if (p1.tile < n_tiles) fp_issue(a, p1, warp, lane, my_stages + kFpStageBytes, my_tabs + kFpTabSlotBytes, my_bar + 1);
+    if (p0.tile < n_tiles) fp_issue(a, p0, fp_row(a, p0, warp, lane), warp, lane, my_stages, my_tabs, my_bar);
+    if (p1.tile < n_tiles) fp_issue(a, p1, fp_row(a, p1, warp, lane), warp, lane, my_stages + kFpStageBytes, my_tabs + kFpTabSlotBytes, my_bar + 1);
+    int row2 = p2.tile < n_tiles ? fp_row(a, p2, warp, lane) : 0;            // input rows of item k+2, one item ahead of their use
     int ts = 0;                                   // table slot of the current item: k mod 3
 
     // per-node batch-norm constants travel one item ahead of their use
@@ -289,46 +297,64 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles, int *fault)
         }
         double s1 = 0.0, s2 = 0.0;
         const float *xs0 = reinterpret_cast<const float *>(stage);
-        float *yrow = a.y + (size_t)node * a.ys + f0 + lane;
-        // One walk of the tree carries NP frame pairs per lane (frames 32q + lane; pair p = frames q = 2p, 2p + 1): 4 pairs when the
-        // item is 256 frames wide, 2 pairs for a 128-frame item.
+        float *yrow = a.y + (size_t)node * a.ys + f0 + 4 * lane;
+        // One walk of the tree carries NP frame pairs per lane.  A lane owns four consecutive frames of every 128 (frames 128h + 4 lane
+        // + 0..3, h < NP/2; pairs (0, 1) and (2, 3)), so its inputs come out of shared memory with one 128-bit load per row and half and
+        // its outputs leave with one 128-bit store per half: 4 pairs when the item is 256 frames wide, 2 pairs for a 128-frame item.
+        const FpPos p3 = fp_advance(p2, dt, dg, a.groups);
         auto walk = [&](auto np_tag) {
             constexpr int NP = decltype(np_tag)::value;
             f32x2 up[6][NP], yp[NP];
 #pragma unroll
             for (int j = 0; j < 6; ++j) {
-                const float *r = xs0 + j * kFpMaxItemFrames + lane;
 #pragma unroll
-                for (int p = 0; p < NP; ++p) {
+                for (int h = 0; h < NP / 2; ++h) {
+                    const float4 r = *reinterpret_cast<const float4 *>(xs0 + j * kFpMaxItemFrames + 128 * h + 4 * lane);
                     // the same values as condition_u()
-                    if (BINARY) up[j][p] = pack2(r[64 * p] > 0.5f ? a.bias : -a.bias, r[64 * p + 32] > 0.5f ? a.bias : -a.bias);
-                    else        up[j][p] = pack2(__saturatef(r[64 * p]) - 0.5f, __saturatef(r[64 * p + 32]) - 0.5f);
+                    if (BINARY) {
+                        up[j][2 * h]     = pack2(r.x > 0.5f ? a.bias : -a.bias, r.y > 0.5f ? a.bias : -a.bias);
+                        up[j][2 * h + 1] = pack2(r.z > 0.5f ? a.bias : -a.bias, r.w > 0.5f ? a.bias : -a.bias);
+                    } else {
+                        up[j][2 * h]     = pack2(__saturatef(r.x) - 0.5f, __saturatef(r.y) - 0.5f);
+                        up[j][2 * h + 1] = pack2(__saturatef(r.z) - 0.5f, __saturatef(r.w) - 0.5f);
+                    }
                 }
             }
             // the stage has been read out: hand it back to the copy engine for item k+2 before doing the math
             __syncwarp();
             if (p2.tile < n_tiles) {
                 proxy_fence_async();
-                fp_issue(a, p2, warp, lane, stage, tab_refill, my_bar + s);
+                fp_issue(a, p2, row2, warp, lane, stage, tab_refill, my_bar + s);
             }
+            if (p3.tile < n_tiles) row2 = fp_row(a, p3, warp, lane);
             lut6_forward_x2<NP>(tab, up, yp);
 #pragma unroll
-            for (int q = 0; q < 2 * NP; ++q) {
-                const int fl = 32 * q;
-                const bool live = store && fl + lane < nf;
-                float v0, v1;
-                unpack2(yp[q >> 1], v0, v1);
-                float v = (q & 1) ? v1 : v0;
-                if (PHASE == PH_STATS) {
-                    if (live) { s1 += (double)v; s2 += (double)v * (double)v; }
-                } else if (PHASE == PH_NORM) {
-                    v = (v - mean) * scale;
-                    v = v * a.gamma + a.beta;
-                    v = BINARY ? (v > 0.5f ? 1.0f : 0.0f) : __saturatef(v);
-                } else {
-                    v = __saturatef(v);
+            for (int h = 0; h < NP / 2; ++h) {
+                float v[4];
+                unpack2(yp[2 * h], v[0], v[1]);
+                unpack2(yp[2 * h + 1], v[2], v[3]);
+                const int fl = 128 * h + 4 * lane;                 // first of the lane's four frames, relative to the item
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (PHASE == PH_STATS) {
+                        if (store && fl + i < nf) { s1 += (double)v[i]; s2 += (double)v[i] * (double)v[i]; }
+                    } else if (PHASE == PH_NORM) {
+                        v[i] = (v[i] - mean) * scale;
+                        v[i] = v[i] * a.gamma + a.beta;
+                        v[i] = BINARY ? (v[i] > 0.5f ? 1.0f : 0.0f) : __saturatef(v[i]);
+                    } else {
+                        v[i] = __saturatef(v[i]);
+                    }
                 }
-                if (live) yrow[fl] = v;
+                if (store) {
+                    if (fl + 3 < nf) {
+                        *reinterpret_cast<float4 *>(yrow + 128 * h) = make_float4(v[0], v[1], v[2], v[3]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 3; ++i)
+                            if (fl + i < nf) yrow[128 * h + i] = v[i];
+                    }
+                }
             }
         };
         if (nf > kFramesPerIter) walk(std::integral_constant<int, 4>());
@@ -341,7 +367,7 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles, int *fault)
                 atomicAdd(a.sums + 2 * (size_t)node + 1, s2);
             }
         }
-        p0 = p1; p1 = p2; p2 = fp_advance(p2, dt, dg, a.groups);
+        p0 = p1; p1 = p2; p2 = p3;
     }
 }
 
@@ -625,8 +651,9 @@ static int launch_forward(FwdArgs a, int max_tile, cudaStream_t st)
     // input count is not part of this ABI: between O (square layer) and 6*O rows are touched
     a.T = frame_tile(3LL * a.O, XBIT ? 1 : 32, a.groups, a.F, max_tile);
     if (!XBIT && !YBIT) {
-        // pipelined path: rows and tables must start on 16-byte boundaries for the bulk copies
-        const bool aligned = ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.W)) & 15) == 0 && (a.xs % 4) == 0;
+        // pipelined path: rows and tables must start on 16-byte boundaries for the bulk copies and the 128-bit stores
+        const bool aligned = ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.W) | reinterpret_cast<uintptr_t>(a.y)) & 15) == 0 &&
+                             (a.xs % 4) == 0 && (a.ys % 4) == 0;
         int *fault = aligned ? fault_word() : nullptr;
         auto kern = a.binary ? k_lut6_forward_pipe<PHASE, true> : k_lut6_forward_pipe<PHASE, false>;
         if (aligned && fault != nullptr && allow_big_smem(kern, kFpSmem)) {
