@@ -60,6 +60,16 @@ SIGNATURES = {
     "bbcu_bit_fp32_BinaryToReal_Forward": (_i, [_vp, _vp] + [_i] * 6 + [_vp]),
     "bbcu_fp32_BinaryToReal_Forward": (_i, [_vp, _vp] + [_i] * 6 + [_vp]),
     "bbcu_fp32_BinaryToReal_Backward": (_i, [_vp, _vp] + [_i] * 6 + [_vp]),
+    "bbcu_fp32_Im2Col_Forward": (_i, [_vp, _vp] + [_i] * 15 + [_f, _vp]),
+    "bbcu_bit_Im2Col_Forward": (_i, [_vp, _vp] + [_i] * 15 + [_vp]),
+    "bbcu_fp32_Im2Col_Backward": (_i, [_vp, _vp] + [_i] * 14 + [_vp]),
+    "bbcu_fp32_Col2Im_Forward": (_i, [_vp, _vp] + [_i] * 6 + [_vp]),
+    "bbcu_bit_Col2Im_Forward": (_i, [_vp, _vp] + [_i] * 6 + [_vp]),
+    "bbcu_fp32_Col2Im_Backward": (_i, [_vp, _vp] + [_i] * 6 + [_vp]),
+    "bbcu_fp32_MaxPooling_Forward": (_i, [_vp] * 3 + [_i] * 9 + [_vp]),
+    "bbcu_bit_MaxPooling_Forward": (_i, [_vp] * 2 + [_i] * 9 + [_vp]),
+    "bbcu_fp32_MaxPooling_Backward": (_i, [_vp] * 3 + [_i] * 9 + [_vp]),
+    "bbcu_bit_fp32_MaxPooling_Backward": (_i, [_vp] * 3 + [_i] * 10 + [_vp]),
     "bbcu_fp32_DifferentiableLut6_ForwardStats": (_i, [_vp] * 5 + [_f] + [_i] * 5 + [_vp]),
     "bbcu_fp32_DifferentiableLut6_ForwardNormalize": (_i, [_vp] * 6 + [_f] * 3 + [_i] * 3 + [_ll, _i, _vp]),
     "bbcu_fp32_DifferentiableLut6_BackwardStats": (_i, [_vp] * 7 + [_f] * 3 + [_i] * 5 + [_vp]),

@@ -204,7 +204,14 @@ struct MuxTree<1, K, NW> {
 // while the copies of j+1 and j+2 are in flight.  No warp ever waits on a load it has only just issued, and no
 // CTA-wide barrier exists after set-up.
 // ---------------------------------------------------------------------------------------------
-constexpr int kPipeWords  = 256;                      // words per row segment and item (1 KiB)
+#ifndef BB200_BL6_NW
+#define BB200_BL6_NW 8
+#endif
+#ifndef BB200_BL6_CTAS
+#define BB200_BL6_CTAS 2
+#endif
+constexpr int kPipeNW     = BB200_BL6_NW;             // words per lane and item
+constexpr int kPipeWords  = 32 * kPipeNW;             // words per row segment and item (1 KiB)
 constexpr int kPipeStages = 2;
 // dynamic shared memory layout: [rows: warp x stage x 6 x 256 words][barriers: warp x stage, padded to 128 B][level-1 pairs: warp x 32 x int2]
 constexpr int kPipeRowsBytes = kBlWarps * kPipeStages * 6 * kPipeWords * 4;
@@ -244,7 +251,7 @@ __device__ __forceinline__ int pipe_row(const BlArgs &a, PipePos pos, int warp, 
     return lane < 6 ? __ldg(a.idx + (size_t)node * 6 + lane) : 0;
 }
 
-__global__ void __launch_bounds__(kBlWarps * 32, 2)
+__global__ void __launch_bounds__(kBlWarps * 32, BB200_BL6_CTAS)
 k_binary_lut6_pipe(const BlArgs a, int n_tiles, int *fault)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -303,13 +310,14 @@ k_binary_lut6_pipe(const BlArgs a, int n_tiles, int *fault)
             return;
         }
         const int w = 4 * lane;
-        uint32_t xw[6][8], o[8];
+        uint32_t xw[6][kPipeNW], o[kPipeNW];
 #pragma unroll
         for (int j = 0; j < 6; ++j) {
-            const uint4 lo = *reinterpret_cast<const uint4 *>(stage + j * kPipeWords + w);
-            const uint4 hi = *reinterpret_cast<const uint4 *>(stage + j * kPipeWords + w + 128);
-            xw[j][0] = lo.x; xw[j][1] = lo.y; xw[j][2] = lo.z; xw[j][3] = lo.w;
-            xw[j][4] = hi.x; xw[j][5] = hi.y; xw[j][6] = hi.z; xw[j][7] = hi.w;
+#pragma unroll
+            for (int h = 0; h < kPipeNW / 4; ++h) {
+                const uint4 v = *reinterpret_cast<const uint4 *>(stage + j * kPipeWords + w + 128 * h);
+                xw[j][4 * h] = v.x; xw[j][4 * h + 1] = v.y; xw[j][4 * h + 2] = v.z; xw[j][4 * h + 3] = v.w;
+            }
         }
         __syncwarp();                                   // every lane has read the stage out
         if (p2.tile < n_tiles) {
@@ -318,10 +326,11 @@ k_binary_lut6_pipe(const BlArgs a, int n_tiles, int *fault)
         }
         const PipePos p3 = pipe_advance(p2, dt, dg, a.groups);
         if (p3.tile < n_tiles) row2 = pipe_row(a, p3, warp, lane);
-        MuxTree<6, 0, 8>::eval(my_ab, xw, o);
+        MuxTree<6, 0, kPipeNW>::eval(my_ab, xw, o);
         uint32_t *yrow = a.y + (size_t)min(node, a.O - 1) * a.stride + w0;
-        if (store && w < nw)       *reinterpret_cast<uint4 *>(yrow + w)       = make_uint4(o[0], o[1], o[2], o[3]);
-        if (store && w + 128 < nw) *reinterpret_cast<uint4 *>(yrow + w + 128) = make_uint4(o[4], o[5], o[6], o[7]);
+#pragma unroll
+        for (int h = 0; h < kPipeNW / 4; ++h)
+            if (store && w + 128 * h < nw) *reinterpret_cast<uint4 *>(yrow + w + 128 * h) = make_uint4(o[4 * h], o[4 * h + 1], o[4 * h + 2], o[4 * h + 3]);
 
         p0 = p1; p1 = p2; p2 = p3;
     }
@@ -367,7 +376,7 @@ extern "C" int bbcu_bit_BinaryLut6_Forward(const int *x, int *y, const int *idx,
         if (attr_ok && fault != nullptr) {
             const long long n_items = (long long)((a.nwords + kPipeWords - 1) / kPipeWords) * a.groups;
             BB200_REQUIRE(n_items < (1LL << 31) - 4096, BBCU_ERR_TOO_LARGE);      // 32-bit item arithmetic in the kernel
-            long long grid = 2LL * device_info().sm_count;
+            long long grid = (long long)BB200_BL6_CTAS * device_info().sm_count;
             if (grid > n_items) grid = n_items;
             k_binary_lut6_pipe<<<(unsigned)grid, kBlWarps * 32, kPipeSmem, as_stream(stream)>>>(a, (a.nwords + kPipeWords - 1) / kPipeWords, fault);
             return launch_status();

@@ -1,0 +1,617 @@
+// Convolution lowering around the per-pixel LUT layers of a LUT-CNN: Im2Col, Col2Im and MaxPooling.
+//
+// FrameBuffers are node-major and frame-contiguous, and lowering multiplies the frame axis by the output pixels:
+// output frame  fo = fi * P + p  (fi = input frame, p = oy * OW + ox, P = OH * OW).  Every operator here is pure
+// data movement, so the only thing to get right is that both the reads and the writes are made of full lines:
+//   * Im2Col / Col2Im exchange the roles of "pixel" and "frame" (pixels are nodes on one side and part of the frame
+//     index on the other), i.e. they are 32 x 32 tile transposes through shared memory (fp32) or 32 x 32 bit-matrix
+//     transposes by warp ballot (bit frames);
+//   * MaxPooling keeps the frame axis and is a straight per-frame window scan.
+//
+// Semantics follow the reference's CPU branches:
+//   Im2Col      include/bb/ConvolutionIm2Col.h:361-396 (forward, border modes :253-288), :439-482 (backward: only
+//               positions inside the image receive gradient; replicated / reflected border copies send none back)
+//   Col2Im      include/bb/ConvolutionCol2Im.h:205-221 (forward), :283-299 (backward)
+//   MaxPooling  include/bb/MaxPooling.h:286-322 (fp32 forward: first maximum wins, argmax counts in-range window
+//               positions), :369-394 (bit forward: OR), :600-629 (backward by argmax), :681-708 (bit layer backward:
+//               the first set input bit takes the gradient)
+#include "common.cuh"
+
+namespace bb200 {
+
+namespace {
+
+enum { kBorderConstant = 0, kBorderReflect = 1, kBorderReflect101 = 2, kBorderReplicate = 3, kBorderWrap = 4 };
+
+struct Im2ColGeom {
+    int x_stride, y_stride, x_offset, y_offset;
+    int in_w, in_h, in_c, out_w, out_h, filter_w, filter_h, border_mode;
+    int in_frames;
+    long long in_fs, out_fs;          // frame strides in elements (floats / words)
+};
+
+__device__ __forceinline__ bool border_remap(int mode, int &x, int &y, int w, int h)
+{
+    switch (mode) {
+    case kBorderReflect:
+        if (x < 0) x = -x - 1;
+        if (y < 0) y = -y - 1;
+        if (x >= w) x = (w - 1) - (x - w);
+        if (y >= h) y = (h - 1) - (y - h);
+        return true;
+    case kBorderReflect101:
+        if (x < 0) x = -x;
+        if (y < 0) y = -y;
+        if (x >= w) x = (w - 2) - (x - w);
+        if (y >= h) y = (h - 2) - (y - h);
+        return true;
+    case kBorderReplicate:
+        if (x < 0) x = 0;
+        if (y < 0) y = 0;
+        if (x >= w) x = w - 1;
+        if (y >= h) y = h - 1;
+        return true;
+    case kBorderWrap:
+        if (x < 0) x += w;
+        if (y < 0) y += h;
+        if (x >= w) x -= w;
+        if (y >= h) y -= h;
+        return true;
+    default:
+        return false;
+    }
+}
+
+// Input node read by output pixel p of output node (c, fy, fx), or -1 for the border value.
+__device__ __forceinline__ int im2col_source(const Im2ColGeom &g, int c, int fy, int fx, int p)
+{
+    int iy = (p / g.out_w) * g.y_stride - g.y_offset + fy;
+    int ix = (p % g.out_w) * g.x_stride - g.x_offset + fx;
+    if (iy >= 0 && iy < g.in_h && ix >= 0 && ix < g.in_w) return (c * g.in_h + iy) * g.in_w + ix;
+    if (border_remap(g.border_mode, ix, iy, g.in_w, g.in_h)) {
+        // a remap that still misses the image (filter wider than the image) reads nothing
+        if (iy >= 0 && iy < g.in_h && ix >= 0 && ix < g.in_w) return (c * g.in_h + iy) * g.in_w + ix;
+    }
+    return -1;
+}
+
+// --------------------------------------------------------------------------------------------- Im2Col fp32
+// Block = one output node x 32 input frames x 32 output pixels.  Reads run along input frames, writes along pixels.
+__global__ void __launch_bounds__(256)
+k_im2col_forward_f32(const float *__restrict__ x, float *__restrict__ y, Im2ColGeom g, float border_value, int p_tiles, int f_tiles)
+{
+    __shared__ float tile[32][33];
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    int b = blockIdx.x;
+    const int pt = b % p_tiles; b /= p_tiles;
+    const int ft = b % f_tiles; b /= f_tiles;
+    const int on = b;                                             // (c * filter_h + fy) * filter_w + fx
+    const int fx = on % g.filter_w, fy = (on / g.filter_w) % g.filter_h, c = on / (g.filter_w * g.filter_h);
+    const int P = g.out_w * g.out_h;
+    const int p0 = pt * 32, f0 = ft * 32;
+#pragma unroll
+    for (int r = ty; r < 32; r += 8) {
+        const int p = p0 + r, fi = f0 + tx;
+        float v = border_value;
+        if (p < P && fi < g.in_frames) {
+            const int in = im2col_source(g, c, fy, fx, p);
+            if (in >= 0) v = x[(size_t)in * g.in_fs + fi];
+        }
+        tile[r][tx] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = ty; r < 32; r += 8) {
+        const int fi = f0 + r, p = p0 + tx;
+        if (p < P && fi < g.in_frames) y[(size_t)on * g.out_fs + (size_t)fi * P + p] = tile[tx][r];
+    }
+}
+
+// Block = one channel x 32 input frames x 32 input pixels (q = y * W + x).  For every filter tap the threads of a warp read
+// consecutive output pixels of one output frame row; the sums are turned through shared memory and written along frames.
+__global__ void __launch_bounds__(256)
+k_im2col_backward_f32(const float *__restrict__ dy, float *__restrict__ dx, Im2ColGeom g, int q_tiles, int f_tiles)
+{
+    __shared__ float tile[32][33];
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    int b = blockIdx.x;
+    const int qt = b % q_tiles; b /= q_tiles;
+    const int ft = b % f_tiles; b /= f_tiles;
+    const int c = b;
+    const int Q = g.in_w * g.in_h, P = g.out_w * g.out_h;
+    const int q = qt * 32 + tx;
+    const int iy_limit = (g.out_h - 1) * g.y_stride, ix_limit = (g.out_w - 1) * g.x_stride;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (q < Q) {
+        const int yy = q / g.in_w, xx = q % g.in_w;
+        for (int fy = yy % g.y_stride; fy < g.filter_h; fy += g.y_stride) {
+            const int iy = yy - fy + g.y_offset;
+            if (iy < 0 || iy > iy_limit) continue;
+            for (int fx = xx % g.x_stride; fx < g.filter_w; fx += g.x_stride) {
+                const int ix = xx - fx + g.x_offset;
+                if (ix < 0 || ix > ix_limit) continue;
+                const int p  = (iy / g.y_stride) * g.out_w + ix / g.x_stride;
+                const int on = (c * g.filter_h + fy) * g.filter_w + fx;
+                const float *row = dy + (size_t)on * g.out_fs + p;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int fi = ft * 32 + ty + 8 * k;
+                    if (fi < g.in_frames) acc[k] += row[(size_t)fi * P];
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) tile[ty + 8 * k][tx] = acc[k];            // [frame][pixel]
+    __syncthreads();
+#pragma unroll
+    for (int r = ty; r < 32; r += 8) {
+        const int qq = qt * 32 + r, fi = ft * 32 + tx;
+        if (qq < Q && fi < g.in_frames) dx[(size_t)(c * Q + qq) * g.in_fs + fi] = tile[tx][r];
+    }
+}
+
+// 32 x 32 bit-matrix transpose across a warp: lane k holds row k; afterwards lane j holds column j (bit k of the result =
+// bit j of lane k's word).
+__device__ __forceinline__ uint32_t warp_bit_transpose(uint32_t row, int lane)
+{
+    uint32_t mine = 0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const uint32_t col = __ballot_sync(0xffffffffu, (row >> j) & 1u);
+        if (lane == j) mine = col;
+    }
+    return mine;
+}
+
+// --------------------------------------------------------------------------------------------- Im2Col bit
+// P % 32 == 0: an output word is 32 consecutive pixels of one input frame.  A warp takes one input word column (32 input
+// frames) and one group of 32 pixels: lane k reads the word of pixel k, the ballot transpose gives lane j the output word of
+// input frame j.  A block covers up to 32 consecutive pixel groups, so each frame's words leave as one contiguous run.
+__global__ void __launch_bounds__(256)
+k_im2col_forward_bit(const uint32_t *__restrict__ x, uint32_t *__restrict__ y, Im2ColGeom g, int groups, int g_tiles, int in_words)
+{
+    __shared__ uint32_t tile[32][33];                             // [input frame j][pixel group]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int b = blockIdx.x;
+    const int gt = b % g_tiles; b /= g_tiles;
+    const int wi = b % in_words; b /= in_words;
+    const int on = b;
+    const int fx = on % g.filter_w, fy = (on / g.filter_w) % g.filter_h, c = on / (g.filter_w * g.filter_h);
+    const int g0 = gt * 32, gn = min(32, groups - g0);
+    for (int gl = warp; gl < gn; gl += 8) {
+        const int in = im2col_source(g, c, fy, fx, (g0 + gl) * 32 + lane);
+        const uint32_t row = in >= 0 ? x[(size_t)in * g.in_fs + wi] : 0u;
+        tile[lane][gl] = warp_bit_transpose(row, lane);
+    }
+    __syncthreads();
+    for (int j = warp; j < 32; j += 8) {
+        const int fi = wi * 32 + j;
+        if (fi < g.in_frames && lane < gn) y[(size_t)on * g.out_fs + (size_t)fi * groups + g0 + lane] = tile[j][lane];
+    }
+}
+
+// Any P: one thread per output word gathers its 32 bits one by one.
+__global__ void __launch_bounds__(256)
+k_im2col_forward_bit_any(const uint32_t *__restrict__ x, uint32_t *__restrict__ y, Im2ColGeom g, int out_words, int out_nodes)
+{
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long long)out_words * out_nodes) return;
+    const int on = (int)(t / out_words), wo = (int)(t % out_words);
+    const int fx = on % g.filter_w, fy = (on / g.filter_w) % g.filter_h, c = on / (g.filter_w * g.filter_h);
+    const int P = g.out_w * g.out_h;
+    const long long out_frames = (long long)g.in_frames * P;
+    uint32_t word = 0;
+    for (int k = 0; k < 32; ++k) {
+        const long long fo = (long long)wo * 32 + k;
+        if (fo >= out_frames) break;
+        const int fi = (int)(fo / P), p = (int)(fo % P);
+        const int in = im2col_source(g, c, fy, fx, p);
+        if (in >= 0) word |= ((x[(size_t)in * g.in_fs + (fi >> 5)] >> (fi & 31)) & 1u) << k;
+    }
+    y[(size_t)on * g.out_fs + wo] = word;
+}
+
+// --------------------------------------------------------------------------------------------- Col2Im
+// FORWARD: y[c * hw + xy][fo] = x[c][fo * hw + xy];  otherwise dx[c][fo * hw + xy] = dy[c * hw + xy][fo].
+// Block = one channel x 32 pixels x 32 output frames; the image-side array is walked along frames, the column-side one along pixels.
+template <bool FORWARD>
+__global__ void __launch_bounds__(256)
+k_col2im_f32(const float *__restrict__ src, float *__restrict__ dst, int hw, int out_frames, long long col_fs, long long img_fs, int xy_tiles,
+             int f_tiles)
+{
+    __shared__ float tile[32][33];
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    int b = blockIdx.x;
+    const int xt = b % xy_tiles; b /= xy_tiles;
+    const int ft = b % f_tiles; b /= f_tiles;
+    const int c = b;
+    const int xy0 = xt * 32, f0 = ft * 32;
+    if (FORWARD) {
+#pragma unroll
+        for (int r = ty; r < 32; r += 8) {                        // r = frame, tx = pixel
+            const int fo = f0 + r, xy = xy0 + tx;
+            tile[r][tx] = (fo < out_frames && xy < hw) ? src[(size_t)c * col_fs + (size_t)fo * hw + xy] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = ty; r < 32; r += 8) {                        // r = pixel, tx = frame
+            const int xy = xy0 + r, fo = f0 + tx;
+            if (fo < out_frames && xy < hw) dst[(size_t)(c * hw + xy) * img_fs + fo] = tile[tx][r];
+        }
+    } else {
+#pragma unroll
+        for (int r = ty; r < 32; r += 8) {                        // r = pixel, tx = frame
+            const int xy = xy0 + r, fo = f0 + tx;
+            tile[r][tx] = (fo < out_frames && xy < hw) ? src[(size_t)(c * hw + xy) * img_fs + fo] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = ty; r < 32; r += 8) {                        // r = frame, tx = pixel
+            const int fo = f0 + r, xy = xy0 + tx;
+            if (fo < out_frames && xy < hw) dst[(size_t)c * col_fs + (size_t)fo * hw + xy] = tile[tx][r];
+        }
+    }
+}
+
+// hw % 32 == 0: warp = (channel, output word wo, pixel group); lane j reads the input word of output frame 32 wo + j that
+// holds the group's 32 pixels, the transpose gives lane k the output word of pixel k.  A block takes 32 consecutive output
+// words of the same pixel group, so every pixel's row receives one contiguous run.
+__global__ void __launch_bounds__(256)
+k_col2im_forward_bit(const uint32_t *__restrict__ x, uint32_t *__restrict__ y, int hw, int out_frames, long long in_fs, long long out_fs,
+                     int groups, int w_tiles, int out_words)
+{
+    __shared__ uint32_t tile[32][33];                             // [pixel k][output word]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int b = blockIdx.x;
+    const int wt = b % w_tiles; b /= w_tiles;
+    const int gp = b % groups; b /= groups;
+    const int c = b;
+    const int w0 = wt * 32, wn = min(32, out_words - w0);
+    for (int wl = warp; wl < wn; wl += 8) {
+        const long long fo = (long long)(w0 + wl) * 32 + lane;
+        const uint32_t row = fo < out_frames ? x[(size_t)c * in_fs + (size_t)fo * groups + gp] : 0u;
+        tile[lane][wl] = warp_bit_transpose(row, lane);
+    }
+    __syncthreads();
+    for (int k = warp; k < 32; k += 8)
+        if (lane < wn) y[(size_t)(c * hw + gp * 32 + k) * out_fs + w0 + lane] = tile[k][lane];
+}
+
+__global__ void __launch_bounds__(256)
+k_col2im_forward_bit_any(const uint32_t *__restrict__ x, uint32_t *__restrict__ y, int hw, int out_frames, long long in_fs, long long out_fs,
+                         int out_words, int out_nodes)
+{
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long long)out_words * out_nodes) return;
+    const int on = (int)(t / out_words), wo = (int)(t % out_words);
+    const int c = on / hw, xy = on % hw;
+    uint32_t word = 0;
+    for (int k = 0; k < 32; ++k) {
+        const long long fo = (long long)wo * 32 + k;
+        if (fo >= out_frames) break;
+        const long long fi = fo * hw + xy;
+        word |= ((x[(size_t)c * in_fs + (fi >> 5)] >> (fi & 31)) & 1u) << k;
+    }
+    y[(size_t)on * out_fs + wo] = word;
+}
+
+// --------------------------------------------------------------------------------------------- MaxPooling
+struct PoolGeom {
+    int filter_h, filter_w, in_w, in_h, out_w, out_h, c_size, frames;
+};
+
+// One thread per (output node, frame); grid.y walks the output nodes.
+__global__ void __launch_bounds__(256)
+k_maxpool_forward_f32(const float *__restrict__ x, float *__restrict__ y, int *__restrict__ argmax, PoolGeom g, long long fs)
+{
+    const int f = blockIdx.x * blockDim.x + threadIdx.x;
+    if (f >= g.frames) return;
+    for (int on = blockIdx.y; on < g.c_size * g.out_h * g.out_w; on += gridDim.y) {
+        const int ox = on % g.out_w, oy = (on / g.out_w) % g.out_h, c = on / (g.out_w * g.out_h);
+        float best = -3.402823466e+38f;                           // std::numeric_limits<float>::lowest()
+        int am = 0, arg = 0;
+        for (int fy = 0; fy < g.filter_h; ++fy) {
+            const int iy = oy * g.filter_h + fy;
+            if (iy >= g.in_h) break;
+            for (int fx = 0; fx < g.filter_w; ++fx) {
+                const int ix = ox * g.filter_w + fx;
+                if (ix >= g.in_w) break;
+                const float v = x[(size_t)((c * g.in_h + iy) * g.in_w + ix) * fs + f];
+                if (v > best) { best = v; am = arg; }
+                ++arg;
+            }
+        }
+        y[(size_t)on * fs + f] = best;
+        if (argmax) argmax[(size_t)on * fs + f] = am;
+    }
+}
+
+__global__ void __launch_bounds__(256)
+k_maxpool_forward_bit(const uint32_t *__restrict__ x, uint32_t *__restrict__ y, PoolGeom g, long long fs, int words)
+{
+    const int w = blockIdx.x * blockDim.x + threadIdx.x;
+    if (w >= words) return;
+    for (int on = blockIdx.y; on < g.c_size * g.out_h * g.out_w; on += gridDim.y) {
+        const int ox = on % g.out_w, oy = (on / g.out_w) % g.out_h, c = on / (g.out_w * g.out_h);
+        uint32_t m = 0;
+        for (int fy = 0; fy < g.filter_h; ++fy) {
+            const int iy = oy * g.filter_h + fy;
+            if (iy >= g.in_h) break;
+            for (int fx = 0; fx < g.filter_w; ++fx) {
+                const int ix = ox * g.filter_w + fx;
+                if (ix >= g.in_w) break;
+                m |= x[(size_t)((c * g.in_h + iy) * g.in_w + ix) * fs + w];
+            }
+        }
+        y[(size_t)on * fs + w] = m;
+    }
+}
+
+// XBITS = false: routed by argmax; XBITS = true: the first set input bit of the window takes the gradient.
+template <bool XBITS>
+__global__ void __launch_bounds__(256)
+k_maxpool_backward(const void *__restrict__ sel, const float *__restrict__ dy, float *__restrict__ dx, PoolGeom g, long long sel_fs, long long fs)
+{
+    const int f = blockIdx.x * blockDim.x + threadIdx.x;
+    if (f >= g.frames) return;
+    for (int on = blockIdx.y; on < g.c_size * g.out_h * g.out_w; on += gridDim.y) {
+        const int ox = on % g.out_w, oy = (on / g.out_w) % g.out_h, c = on / (g.out_w * g.out_h);
+        float grad = dy[(size_t)on * fs + f];
+        const int am = XBITS ? 0 : static_cast<const int *>(sel)[(size_t)on * sel_fs + f];
+        int arg = 0;
+        for (int fy = 0; fy < g.filter_h; ++fy) {
+            const int iy = oy * g.filter_h + fy;
+            if (iy >= g.in_h) break;
+            for (int fx = 0; fx < g.filter_w; ++fx) {
+                const int ix = ox * g.filter_w + fx;
+                if (ix >= g.in_w) break;
+                const size_t in = (size_t)((c * g.in_h + iy) * g.in_w + ix);
+                if (XBITS) {
+                    const bool bit = (static_cast<const uint32_t *>(sel)[in * sel_fs + (f >> 5)] >> (f & 31)) & 1u;
+                    dx[in * fs + f] = bit ? grad : 0.0f;
+                    if (bit) grad = 0.0f;
+                } else {
+                    dx[in * fs + f] = (arg == am) ? grad : 0.0f;
+                    ++arg;
+                }
+            }
+        }
+    }
+}
+
+int check_im2col(const void *a, const void *b, int x_stride, int y_stride, int in_frames, long long in_fs, int in_w, int in_h, int in_c, int out_w,
+                 int out_h, long long out_fs, int filter_w, int filter_h, int frames_per_unit_in, int frames_per_unit_out)
+{
+    BB200_REQUIRE_PTR(a); BB200_REQUIRE_PTR(b);
+    BB200_REQUIRE(x_stride >= 1 && y_stride >= 1 && in_frames >= 0 && in_w >= 1 && in_h >= 1 && in_c >= 0 && out_w >= 0 && out_h >= 0 &&
+                  filter_w >= 1 && filter_h >= 1, BBCU_ERR_BAD_SIZE);
+    const long long out_frames = (long long)in_frames * out_w * out_h;
+    BB200_REQUIRE(out_frames < (1LL << 31) && (long long)in_c * in_h * in_w < (1LL << 31) && (long long)in_c * filter_h * filter_w < (1LL << 31),
+                  BBCU_ERR_TOO_LARGE);
+    BB200_REQUIRE(in_fs * frames_per_unit_in >= in_frames && out_fs * frames_per_unit_out >= out_frames, BBCU_ERR_BAD_STRIDE);
+    return BBCU_OK;
+}
+
+Im2ColGeom make_geom(int x_stride, int y_stride, int x_offset, int y_offset, int in_frames, long long in_fs, int in_w, int in_h, int in_c, int out_w,
+                     int out_h, long long out_fs, int filter_w, int filter_h, int border_mode)
+{
+    Im2ColGeom g;
+    g.x_stride = x_stride; g.y_stride = y_stride; g.x_offset = x_offset; g.y_offset = y_offset;
+    g.in_w = in_w; g.in_h = in_h; g.in_c = in_c; g.out_w = out_w; g.out_h = out_h; g.filter_w = filter_w; g.filter_h = filter_h;
+    g.border_mode = border_mode; g.in_frames = in_frames; g.in_fs = in_fs; g.out_fs = out_fs;
+    return g;
+}
+
+int check_pool(const void *a, const void *b, int fh, int fw, int in_w, int in_h, int out_w, int out_h, int c_size, int frames)
+{
+    BB200_REQUIRE_PTR(a); BB200_REQUIRE_PTR(b);
+    BB200_REQUIRE(fh >= 1 && fw >= 1 && in_w >= 1 && in_h >= 1 && c_size >= 0 && frames >= 0, BBCU_ERR_BAD_SIZE);
+    BB200_REQUIRE(out_w == (in_w + fw - 1) / fw && out_h == (in_h + fh - 1) / fh, BBCU_ERR_BAD_SIZE);
+    BB200_REQUIRE((long long)c_size * in_h * in_w < (1LL << 31), BBCU_ERR_TOO_LARGE);
+    return BBCU_OK;
+}
+
+PoolGeom make_pool(int fh, int fw, int in_w, int in_h, int out_w, int out_h, int c_size, int frames)
+{
+    PoolGeom g;
+    g.filter_h = fh; g.filter_w = fw; g.in_w = in_w; g.in_h = in_h; g.out_w = out_w; g.out_h = out_h; g.c_size = c_size; g.frames = frames;
+    return g;
+}
+
+inline unsigned grid_y(long long nodes) { return (unsigned)(nodes < 65535 ? (nodes > 0 ? nodes : 1) : 65535); }
+
+}   // namespace
+}   // namespace bb200
+
+using namespace bb200;
+
+// ----------------------------------------------------------------------------------------------------- Im2Col
+extern "C" int bbcu_fp32_Im2Col_Forward(const float *dev_x_buf, float *dev_y_buf, int x_stride, int y_stride, int x_offset, int y_offset,
+                                        int input_frame_size, int input_frame_stride, int input_w_size, int input_h_size, int input_c_size,
+                                        int output_w_size, int output_h_size, int output_frame_stride, int filter_w_size, int filter_h_size,
+                                        int border_mode, float border_value, bbcu_stream_t stream)
+{
+    int rc = check_im2col(dev_x_buf, dev_y_buf, x_stride, y_stride, input_frame_size, input_frame_stride, input_w_size, input_h_size, input_c_size,
+                          output_w_size, output_h_size, output_frame_stride, filter_w_size, filter_h_size, 1, 1);
+    if (rc) return rc;
+    const long long P = (long long)output_w_size * output_h_size, out_nodes = (long long)input_c_size * filter_h_size * filter_w_size;
+    if (P == 0 || input_frame_size == 0 || out_nodes == 0) return BBCU_OK;
+    const Im2ColGeom g = make_geom(x_stride, y_stride, x_offset, y_offset, input_frame_size, input_frame_stride, input_w_size, input_h_size,
+                                   input_c_size, output_w_size, output_h_size, output_frame_stride, filter_w_size, filter_h_size, border_mode);
+    const int p_tiles = (int)((P + 31) / 32), f_tiles = (input_frame_size + 31) / 32;
+    const long long blocks = out_nodes * p_tiles * f_tiles;
+    BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+    k_im2col_forward_f32<<<(unsigned)blocks, dim3(32, 8), 0, as_stream(stream)>>>(dev_x_buf, dev_y_buf, g, border_value, p_tiles, f_tiles);
+    return launch_status();
+}
+
+extern "C" int bbcu_bit_Im2Col_Forward(const int *dev_x_buf, int *dev_y_buf, int x_stride, int y_stride, int x_offset, int y_offset,
+                                       int input_frame_size, int input_frame_stride, int input_w_size, int input_h_size, int input_c_size,
+                                       int output_w_size, int output_h_size, int output_frame_stride, int filter_w_size, int filter_h_size,
+                                       int border_mode, bbcu_stream_t stream)
+{
+    int rc = check_im2col(dev_x_buf, dev_y_buf, x_stride, y_stride, input_frame_size, input_frame_stride, input_w_size, input_h_size, input_c_size,
+                          output_w_size, output_h_size, output_frame_stride, filter_w_size, filter_h_size, 32, 32);
+    if (rc) return rc;
+    const long long P = (long long)output_w_size * output_h_size, out_nodes = (long long)input_c_size * filter_h_size * filter_w_size;
+    if (P == 0 || input_frame_size == 0 || out_nodes == 0) return BBCU_OK;
+    const Im2ColGeom g = make_geom(x_stride, y_stride, x_offset, y_offset, input_frame_size, input_frame_stride, input_w_size, input_h_size,
+                                   input_c_size, output_w_size, output_h_size, output_frame_stride, filter_w_size, filter_h_size, border_mode);
+    const uint32_t *x = reinterpret_cast<const uint32_t *>(dev_x_buf);
+    uint32_t *y = reinterpret_cast<uint32_t *>(dev_y_buf);
+    if (P % 32 == 0) {
+        const int groups = (int)(P / 32), g_tiles = (groups + 31) / 32, in_words = (input_frame_size + 31) / 32;
+        const long long blocks = out_nodes * in_words * g_tiles;
+        BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+        k_im2col_forward_bit<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(x, y, g, groups, g_tiles, in_words);
+    } else {
+        const long long out_words = ((long long)input_frame_size * P + 31) / 32;
+        const long long blocks = (out_words * out_nodes + 255) / 256;
+        BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+        k_im2col_forward_bit_any<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(x, y, g, (int)out_words, (int)out_nodes);
+    }
+    return launch_status();
+}
+
+extern "C" int bbcu_fp32_Im2Col_Backward(const float *dev_dy_buf, float *dev_dx_buf, int x_stride, int y_stride, int x_offset, int y_offset,
+                                         int input_frame_size, int input_frame_stride, int input_w_size, int input_h_size, int input_c_size,
+                                         int output_w_size, int output_h_size, int output_frame_stride, int filter_w_size, int filter_h_size,
+                                         bbcu_stream_t stream)
+{
+    int rc = check_im2col(dev_dy_buf, dev_dx_buf, x_stride, y_stride, input_frame_size, input_frame_stride, input_w_size, input_h_size,
+                          input_c_size, output_w_size, output_h_size, output_frame_stride, filter_w_size, filter_h_size, 1, 1);
+    if (rc) return rc;
+    if (input_c_size == 0 || input_frame_size == 0) return BBCU_OK;
+    const Im2ColGeom g = make_geom(x_stride, y_stride, x_offset, y_offset, input_frame_size, input_frame_stride, input_w_size, input_h_size,
+                                   input_c_size, output_w_size, output_h_size, output_frame_stride, filter_w_size, filter_h_size, kBorderConstant);
+    const int q_tiles = (input_w_size * input_h_size + 31) / 32, f_tiles = (input_frame_size + 31) / 32;
+    const long long blocks = (long long)input_c_size * q_tiles * f_tiles;
+    BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+    k_im2col_backward_f32<<<(unsigned)blocks, dim3(32, 8), 0, as_stream(stream)>>>(dev_dy_buf, dev_dx_buf, g, q_tiles, f_tiles);
+    return launch_status();
+}
+
+// ----------------------------------------------------------------------------------------------------- Col2Im
+static int check_col2im(const void *a, const void *b, int w, int h, int c, long long col_fs, int out_frames, long long img_fs, int unit)
+{
+    BB200_REQUIRE_PTR(a); BB200_REQUIRE_PTR(b);
+    BB200_REQUIRE(w >= 1 && h >= 1 && c >= 0 && out_frames >= 0, BBCU_ERR_BAD_SIZE);
+    BB200_REQUIRE((long long)out_frames * w * h < (1LL << 31) && (long long)c * w * h < (1LL << 31), BBCU_ERR_TOO_LARGE);
+    BB200_REQUIRE(col_fs * unit >= (long long)out_frames * w * h && img_fs * unit >= out_frames, BBCU_ERR_BAD_STRIDE);
+    return BBCU_OK;
+}
+
+template <bool FORWARD>
+static int col2im_f32(const float *src, float *dst, int w, int h, int c, int col_fs, int out_frames, int img_fs, cudaStream_t st)
+{
+    int rc = check_col2im(src, dst, w, h, c, col_fs, out_frames, img_fs, 1);
+    if (rc) return rc;
+    if (c == 0 || out_frames == 0) return BBCU_OK;
+    const int hw = w * h, xy_tiles = (hw + 31) / 32, f_tiles = (out_frames + 31) / 32;
+    const long long blocks = (long long)c * xy_tiles * f_tiles;
+    BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+    k_col2im_f32<FORWARD><<<(unsigned)blocks, dim3(32, 8), 0, st>>>(src, dst, hw, out_frames, col_fs, img_fs, xy_tiles, f_tiles);
+    return launch_status();
+}
+
+extern "C" int bbcu_fp32_Col2Im_Forward(const float *dev_x_buf, float *dev_y_buf, int w_size, int h_size, int c_size, int input_frame_stride,
+                                        int output_frame_size, int output_frame_stride, bbcu_stream_t stream)
+{
+    return col2im_f32<true>(dev_x_buf, dev_y_buf, w_size, h_size, c_size, input_frame_stride, output_frame_size, output_frame_stride,
+                            as_stream(stream));
+}
+
+extern "C" int bbcu_fp32_Col2Im_Backward(const float *dev_dy_buf, float *dev_dx_buf, int w_size, int h_size, int c_size, int input_frame_stride,
+                                         int output_frame_size, int output_frame_stride, bbcu_stream_t stream)
+{
+    return col2im_f32<false>(dev_dy_buf, dev_dx_buf, w_size, h_size, c_size, input_frame_stride, output_frame_size, output_frame_stride,
+                             as_stream(stream));
+}
+
+extern "C" int bbcu_bit_Col2Im_Forward(const int *dev_x_buf, int *dev_y_buf, int w_size, int h_size, int c_size, int input_frame_stride,
+                                       int output_frame_size, int output_frame_stride, bbcu_stream_t stream)
+{
+    int rc = check_col2im(dev_x_buf, dev_y_buf, w_size, h_size, c_size, input_frame_stride, output_frame_size, output_frame_stride, 32);
+    if (rc) return rc;
+    if (c_size == 0 || output_frame_size == 0) return BBCU_OK;
+    const uint32_t *x = reinterpret_cast<const uint32_t *>(dev_x_buf);
+    uint32_t *y = reinterpret_cast<uint32_t *>(dev_y_buf);
+    const int hw = w_size * h_size, out_words = (output_frame_size + 31) / 32;
+    if (hw % 32 == 0) {
+        const int groups = hw / 32, w_tiles = (out_words + 31) / 32;
+        const long long blocks = (long long)c_size * groups * w_tiles;
+        BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+        k_col2im_forward_bit<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(x, y, hw, output_frame_size, input_frame_stride, output_frame_stride,
+                                                                             groups, w_tiles, out_words);
+    } else {
+        const long long out_nodes = (long long)c_size * hw;
+        const long long blocks = (out_nodes * out_words + 255) / 256;
+        BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+        k_col2im_forward_bit_any<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(x, y, hw, output_frame_size, input_frame_stride,
+                                                                                 output_frame_stride, out_words, (int)out_nodes);
+    }
+    return launch_status();
+}
+
+// ----------------------------------------------------------------------------------------------------- MaxPooling
+extern "C" int bbcu_fp32_MaxPooling_Forward(const float *dev_x_buf, float *dev_y_buf, int *dev_argmax_buf, int filter_h_size, int filter_w_size,
+                                            int input_w_size, int input_h_size, int output_w_size, int output_h_size, int c_size, int frame_size,
+                                            int frame_stride, bbcu_stream_t stream)
+{
+    int rc = check_pool(dev_x_buf, dev_y_buf, filter_h_size, filter_w_size, input_w_size, input_h_size, output_w_size, output_h_size, c_size, frame_size);
+    if (rc) return rc;
+    BB200_REQUIRE(frame_stride >= frame_size, BBCU_ERR_BAD_STRIDE);
+    if (c_size == 0 || frame_size == 0) return BBCU_OK;
+    const PoolGeom g = make_pool(filter_h_size, filter_w_size, input_w_size, input_h_size, output_w_size, output_h_size, c_size, frame_size);
+    dim3 grid((frame_size + 255) / 256, grid_y((long long)c_size * output_h_size * output_w_size));
+    k_maxpool_forward_f32<<<grid, 256, 0, as_stream(stream)>>>(dev_x_buf, dev_y_buf, dev_argmax_buf, g, frame_stride);
+    return launch_status();
+}
+
+extern "C" int bbcu_bit_MaxPooling_Forward(const int *dev_x_buf, int *dev_y_buf, int filter_h_size, int filter_w_size, int input_w_size,
+                                           int input_h_size, int output_w_size, int output_h_size, int c_size, int frame_size, int frame_stride,
+                                           bbcu_stream_t stream)
+{
+    int rc = check_pool(dev_x_buf, dev_y_buf, filter_h_size, filter_w_size, input_w_size, input_h_size, output_w_size, output_h_size, c_size, frame_size);
+    if (rc) return rc;
+    BB200_REQUIRE((long long)frame_stride * 32 >= frame_size, BBCU_ERR_BAD_STRIDE);
+    if (c_size == 0 || frame_size == 0) return BBCU_OK;
+    const PoolGeom g = make_pool(filter_h_size, filter_w_size, input_w_size, input_h_size, output_w_size, output_h_size, c_size, frame_size);
+    const int words = (frame_size + 31) / 32;
+    dim3 grid((words + 255) / 256, grid_y((long long)c_size * output_h_size * output_w_size));
+    k_maxpool_forward_bit<<<grid, 256, 0, as_stream(stream)>>>(reinterpret_cast<const uint32_t *>(dev_x_buf), reinterpret_cast<uint32_t *>(dev_y_buf), g,
+                                                              frame_stride, words);
+    return launch_status();
+}
+
+extern "C" int bbcu_fp32_MaxPooling_Backward(const int *dev_argmax_buf, const float *dev_dy_buf, float *dev_dx_buf, int filter_h_size,
+                                             int filter_w_size, int input_w_size, int input_h_size, int output_w_size, int output_h_size, int c_size,
+                                             int frame_size, int frame_stride, bbcu_stream_t stream)
+{
+    BB200_REQUIRE_PTR(dev_argmax_buf);
+    int rc = check_pool(dev_dy_buf, dev_dx_buf, filter_h_size, filter_w_size, input_w_size, input_h_size, output_w_size, output_h_size, c_size, frame_size);
+    if (rc) return rc;
+    BB200_REQUIRE(frame_stride >= frame_size, BBCU_ERR_BAD_STRIDE);
+    if (c_size == 0 || frame_size == 0) return BBCU_OK;
+    const PoolGeom g = make_pool(filter_h_size, filter_w_size, input_w_size, input_h_size, output_w_size, output_h_size, c_size, frame_size);
+    dim3 grid((frame_size + 255) / 256, grid_y((long long)c_size * output_h_size * output_w_size));
+    k_maxpool_backward<false><<<grid, 256, 0, as_stream(stream)>>>(dev_argmax_buf, dev_dy_buf, dev_dx_buf, g, frame_stride, frame_stride);
+    return launch_status();
+}
+
+extern "C" int bbcu_bit_fp32_MaxPooling_Backward(const int *dev_x_buf, const float *dev_dy_buf, float *dev_dx_buf, int filter_h_size,
+                                                 int filter_w_size, int input_w_size, int input_h_size, int output_w_size, int output_h_size,
+                                                 int c_size, int frame_size, int forward_frame_stride, int backward_frame_stride,
+                                                 bbcu_stream_t stream)
+{
+    BB200_REQUIRE_PTR(dev_x_buf);
+    int rc = check_pool(dev_dy_buf, dev_dx_buf, filter_h_size, filter_w_size, input_w_size, input_h_size, output_w_size, output_h_size, c_size, frame_size);
+    if (rc) return rc;
+    BB200_REQUIRE(backward_frame_stride >= frame_size && (long long)forward_frame_stride * 32 >= frame_size, BBCU_ERR_BAD_STRIDE);
+    if (c_size == 0 || frame_size == 0) return BBCU_OK;
+    const PoolGeom g = make_pool(filter_h_size, filter_w_size, input_w_size, input_h_size, output_w_size, output_h_size, c_size, frame_size);
+    dim3 grid((frame_size + 255) / 256, grid_y((long long)c_size * output_h_size * output_w_size));
+    k_maxpool_backward<true><<<grid, 256, 0, as_stream(stream)>>>(dev_x_buf, dev_dy_buf, dev_dx_buf, g, forward_frame_stride, backward_frame_stride);
+    return launch_status();
+}

@@ -267,6 +267,82 @@ def binary_to_real_backward(dy, x_nodes, y_frames, frame_mux=1):
     return dx
 
 
+BORDER_MODES = {"constant": 0, "reflect": 1, "reflect_101": 2, "replicate": 3, "wrap": 4}
+
+
+def im2col_geometry(h, w, fh, fw, y_stride=1, x_stride=1, padding="valid"):
+    """(out_h, out_w, y_offset, x_offset) of bb::ConvolutionIm2Col (include/bb/ConvolutionIm2Col.h:200-215)."""
+    if padding == "valid":
+        return ((h - fh + 1) + (y_stride - 1)) // y_stride, ((w - fw + 1) + (x_stride - 1)) // x_stride, 0, 0
+    if padding == "same":
+        return (h + y_stride - 1) // y_stride, (w + x_stride - 1) // x_stride, (fh - 1) // 2, (fw - 1) // 2
+    raise ValueError(f"unknown padding {padding!r}")
+
+
+def im2col_forward(x, frames, c, h, w, fh, fw, y_stride=1, x_stride=1, padding="valid", border_mode="reflect_101", border_value=0.0):
+    """bb::ConvolutionIm2Col forward: [c*h*w, frames] (fp32, or int32 bit words) -> [c*fh*fw, frames*oh*ow]."""
+    oh, ow, yo, xo = im2col_geometry(h, w, fh, fw, y_stride, x_stride, padding)
+    of = frames * oh * ow
+    if x.dtype == torch.int32:
+        y = torch.zeros((c * fh * fw, bit_stride(of)), dtype=torch.int32, device=x.device)
+        abi.call("bbcu_bit_Im2Col_Forward", _p(x), _p(y), x_stride, y_stride, xo, yo, frames, x.shape[1], w, h, c, ow, oh, y.shape[1], fw, fh,
+                 BORDER_MODES[border_mode], _stream())
+    else:
+        y = torch.empty((c * fh * fw, fp32_stride(of)), dtype=torch.float32, device=x.device)
+        abi.call("bbcu_fp32_Im2Col_Forward", _p(x), _p(y), x_stride, y_stride, xo, yo, frames, x.shape[1], w, h, c, ow, oh, y.shape[1], fw, fh,
+                 BORDER_MODES[border_mode], border_value, _stream())
+    return y
+
+
+def im2col_backward(dy, frames, c, h, w, fh, fw, y_stride=1, x_stride=1, padding="valid"):
+    oh, ow, yo, xo = im2col_geometry(h, w, fh, fw, y_stride, x_stride, padding)
+    dx = torch.empty((c * h * w, fp32_stride(frames)), dtype=torch.float32, device=dy.device)
+    abi.call("bbcu_fp32_Im2Col_Backward", _p(dy), _p(dx), x_stride, y_stride, xo, yo, frames, dx.shape[1], w, h, c, ow, oh, dy.shape[1], fw, fh,
+             _stream())
+    return dx
+
+
+def col2im_forward(x, c, h, w, out_frames):
+    """bb::ConvolutionCol2Im forward: [c, out_frames*h*w] -> [c*h*w, out_frames] (fp32, or int32 bit words)."""
+    if x.dtype == torch.int32:
+        y = torch.zeros((c * h * w, bit_stride(out_frames)), dtype=torch.int32, device=x.device)
+        abi.call("bbcu_bit_Col2Im_Forward", _p(x), _p(y), w, h, c, x.shape[1], out_frames, y.shape[1], _stream())
+    else:
+        y = torch.empty((c * h * w, fp32_stride(out_frames)), dtype=torch.float32, device=x.device)
+        abi.call("bbcu_fp32_Col2Im_Forward", _p(x), _p(y), w, h, c, x.shape[1], out_frames, y.shape[1], _stream())
+    return y
+
+
+def col2im_backward(dy, c, h, w, out_frames):
+    dx = torch.empty((c, fp32_stride(out_frames * h * w)), dtype=torch.float32, device=dy.device)
+    abi.call("bbcu_fp32_Col2Im_Backward", _p(dy), _p(dx), w, h, c, dx.shape[1], out_frames, dy.shape[1], _stream())
+    return dx
+
+
+def maxpool_forward(x, frames, c, h, w, fh, fw, want_argmax=True):
+    """bb::MaxPooling forward.  fp32: returns (y, argmax or None); int32 bit words: returns y."""
+    oh, ow = (h + fh - 1) // fh, (w + fw - 1) // fw
+    if x.dtype == torch.int32:
+        y = torch.zeros((c * oh * ow, x.shape[1]), dtype=torch.int32, device=x.device)
+        abi.call("bbcu_bit_MaxPooling_Forward", _p(x), _p(y), fh, fw, w, h, ow, oh, c, frames, x.shape[1], _stream())
+        return y
+    y = torch.empty((c * oh * ow, x.shape[1]), dtype=torch.float32, device=x.device)
+    am = torch.empty((c * oh * ow, x.shape[1]), dtype=torch.int32, device=x.device) if want_argmax else None
+    abi.call("bbcu_fp32_MaxPooling_Forward", _p(x), _p(y), _p(am), fh, fw, w, h, ow, oh, c, frames, x.shape[1], _stream())
+    return y, am
+
+
+def maxpool_backward(sel, dy, frames, c, h, w, fh, fw, bit_input=False):
+    """sel: the forward's argmax (fp32 layer) or, with bit_input=True, the forward's bit-packed input."""
+    oh, ow = (h + fh - 1) // fh, (w + fw - 1) // fw
+    dx = torch.empty((c * h * w, dy.shape[1]), dtype=torch.float32, device=dy.device)
+    if bit_input:
+        abi.call("bbcu_bit_fp32_MaxPooling_Backward", _p(sel), _p(dy), _p(dx), fh, fw, w, h, ow, oh, c, frames, sel.shape[1], dy.shape[1], _stream())
+    else:
+        abi.call("bbcu_fp32_MaxPooling_Backward", _p(sel), _p(dy), _p(dx), fh, fw, w, h, ow, oh, c, frames, dy.shape[1], _stream())
+    return dx
+
+
 class Adam:
     """bb::OptimizerAdam over a list of (param, grad) CUDA tensors (include/bb/OptimizerAdam.h:142-184)."""
 

@@ -217,6 +217,55 @@ int bbcu_fp32_BinaryToReal_Forward(const float *dev_x_buf, float *dev_y_buf, int
 int bbcu_fp32_BinaryToReal_Backward(const float *dev_dy_buf, float *dev_dx_buf, int node_mux_size, int frame_mux_size, int y_node_size,
                                     int x_frame_stride, int y_frame_size, int y_frame_stride, bbcu_stream_t stream);
 
+/* ------------------------------------------------------------------ Convolution lowering (include/bbcu/bbcu.h:949-1186).
+ * Lowering multiplies the frame axis by the output pixels: output frame = input frame * (output_h * output_w) + oy * output_w + ox.
+ * border_mode: 0 constant (border_value; 0 for bit frames), 1 reflect, 2 reflect_101, 3 replicate, 4 wrap
+ * (include/bb/ConvolutionIm2Col.h:253-288).  Results follow the reference's CPU branches; strides are in elements
+ * (floats / 32-frame words). */
+/* bbcu_fp32_Im2Col_Forward, bbcu.h:1076-1097: y[(c*fh + fy)*fw + fx][fo] = x[(c*ih + iy)*iw + ix][fi]. */
+int bbcu_fp32_Im2Col_Forward(const float *dev_x_buf, float *dev_y_buf, int x_stride, int y_stride, int x_offset, int y_offset,
+                             int input_frame_size, int input_frame_stride, int input_w_size, int input_h_size, int input_c_size,
+                             int output_w_size, int output_h_size, int output_frame_stride, int filter_w_size, int filter_h_size,
+                             int border_mode, float border_value, bbcu_stream_t stream);
+/* bbcu_bit_Im2Col_Forward, bbcu.h:1099-1119. */
+int bbcu_bit_Im2Col_Forward(const int *dev_x_buf, int *dev_y_buf, int x_stride, int y_stride, int x_offset, int y_offset,
+                            int input_frame_size, int input_frame_stride, int input_w_size, int input_h_size, int input_c_size,
+                            int output_w_size, int output_h_size, int output_frame_stride, int filter_w_size, int filter_h_size,
+                            int border_mode, bbcu_stream_t stream);
+/* bbcu_fp32_Im2Col_Backward, bbcu.h:1122-1141: dx overwritten; only in-image positions receive gradient
+ * (include/bb/ConvolutionIm2Col.h:439-482). */
+int bbcu_fp32_Im2Col_Backward(const float *dev_dy_buf, float *dev_dx_buf, int x_stride, int y_stride, int x_offset, int y_offset,
+                              int input_frame_size, int input_frame_stride, int input_w_size, int input_h_size, int input_c_size,
+                              int output_w_size, int output_h_size, int output_frame_stride, int filter_w_size, int filter_h_size,
+                              bbcu_stream_t stream);
+/* bbcu_fp32_Col2Im_Forward / bbcu_bit_Col2Im_Forward / bbcu_fp32_Col2Im_Backward, bbcu.h:1148-1186:
+ * y[c*h*w + xy][fo] = x[c][fo*h*w + xy]; input_frame_stride belongs to the [c][...] side in all three. */
+int bbcu_fp32_Col2Im_Forward(const float *dev_x_buf, float *dev_y_buf, int w_size, int h_size, int c_size, int input_frame_stride,
+                             int output_frame_size, int output_frame_stride, bbcu_stream_t stream);
+int bbcu_bit_Col2Im_Forward(const int *dev_x_buf, int *dev_y_buf, int w_size, int h_size, int c_size, int input_frame_stride,
+                            int output_frame_size, int output_frame_stride, bbcu_stream_t stream);
+int bbcu_fp32_Col2Im_Backward(const float *dev_dy_buf, float *dev_dx_buf, int w_size, int h_size, int c_size, int input_frame_stride,
+                              int output_frame_size, int output_frame_stride, bbcu_stream_t stream);
+/* bbcu_fp32_MaxPooling_Forward, bbcu.h:949-964: windows of filter_h x filter_w with the same stride, output size rounded up;
+ * the first maximum wins; dev_argmax_buf (may be NULL) receives the winner's ordinal among the window's in-image positions
+ * (include/bb/MaxPooling.h:286-322). */
+int bbcu_fp32_MaxPooling_Forward(const float *dev_x_buf, float *dev_y_buf, int *dev_argmax_buf, int filter_h_size, int filter_w_size,
+                                 int input_w_size, int input_h_size, int output_w_size, int output_h_size, int c_size, int frame_size,
+                                 int frame_stride, bbcu_stream_t stream);
+/* bbcu_bit_MaxPooling_Forward, bbcu.h:966-980: OR of the window. */
+int bbcu_bit_MaxPooling_Forward(const int *dev_x_buf, int *dev_y_buf, int filter_h_size, int filter_w_size, int input_w_size,
+                                int input_h_size, int output_w_size, int output_h_size, int c_size, int frame_size, int frame_stride,
+                                bbcu_stream_t stream);
+/* bbcu_fp32_MaxPooling_Backward, bbcu.h:983-998: dx = dy at the argmax position, 0 elsewhere. */
+int bbcu_fp32_MaxPooling_Backward(const int *dev_argmax_buf, const float *dev_dy_buf, float *dev_dx_buf, int filter_h_size, int filter_w_size,
+                                  int input_w_size, int input_h_size, int output_w_size, int output_h_size, int c_size, int frame_size,
+                                  int frame_stride, bbcu_stream_t stream);
+/* bbcu_bit_fp32_MaxPooling_Backward, bbcu.h:1000-1016: dev_x_buf is the bit layer's forward INPUT; the first set bit of a window
+ * takes the gradient (include/bb/MaxPooling.h:681-708). */
+int bbcu_bit_fp32_MaxPooling_Backward(const int *dev_x_buf, const float *dev_dy_buf, float *dev_dx_buf, int filter_h_size, int filter_w_size,
+                                      int input_w_size, int input_h_size, int output_w_size, int output_h_size, int c_size, int frame_size,
+                                      int forward_frame_stride, int backward_frame_stride, bbcu_stream_t stream);
+
 /* ------------------------------------------------------------------ Additive: frame-sharded (multi-GPU) building blocks.
  * No counterpart in the reference (it has no multi-device path, include/bb/Memory.h:215-216).  A rank holds a contiguous frame
  * shard; these split the batch-norm operators at the points where per-node sums over ALL frames are needed, so the caller can

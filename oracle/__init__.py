@@ -267,6 +267,97 @@ class _Port:
         self.lib.oracle_binary_to_real_backward(_vp(dy), _vp(dx), C.c_int(x_nodes), C.c_int(dy.shape[0]), C.c_int(dy.shape[1]), C.c_int(frame_mux))
         return dx
 
+    # -- convolution lowering -------------------------------------------------------------------
+    BORDER = {"constant": 0, "reflect": 1, "reflect_101": 2, "replicate": 3, "wrap": 4}
+
+    @staticmethod
+    def im2col_geometry(h, w, fh, fw, y_stride=1, x_stride=1, padding="valid"):
+        """(out_h, out_w, y_offset, x_offset) of ConvolutionIm2Col (include/bb/ConvolutionIm2Col.h:200-215)."""
+        if padding == "valid":
+            return ((h - fh + 1) + (y_stride - 1)) // y_stride, ((w - fw + 1) + (x_stride - 1)) // x_stride, 0, 0
+        if padding == "same":
+            return (h + y_stride - 1) // y_stride, (w + x_stride - 1) // x_stride, (fh - 1) // 2, (fw - 1) // 2
+        raise ValueError(padding)
+
+    def im2col_forward(self, x, c, h, w, fh, fw, y_stride=1, x_stride=1, padding="valid", border_mode="reflect_101", border_value=0.0,
+                       frames=None):
+        """x: float32 [c*h*w][frames] or uint32 words [c*h*w][words] (then pass ``frames``)."""
+        oh, ow, yo, xo = self.im2col_geometry(h, w, fh, fw, y_stride, x_stride, padding)
+        bm = self.BORDER[border_mode]
+        if x.dtype == np.uint32:
+            x = np.ascontiguousarray(x)
+            of = frames * oh * ow
+            y = np.zeros((c * fh * fw, (of + 31) // 32), np.uint32)
+            self.lib.oracle_im2col_forward_bit(_vp(x), C.c_size_t(x.shape[1]), _vp(y), C.c_size_t(y.shape[1]), C.c_int(x_stride), C.c_int(y_stride),
+                                               C.c_int(xo), C.c_int(yo), C.c_int(frames), C.c_int(w), C.c_int(h), C.c_int(c), C.c_int(ow),
+                                               C.c_int(oh), C.c_int(fw), C.c_int(fh), C.c_int(bm))
+            return y
+        x = np.ascontiguousarray(x, np.float32)
+        frames = x.shape[1]
+        y = np.zeros((c * fh * fw, frames * oh * ow), np.float32)
+        self.lib.oracle_im2col_forward_f32(_vp(x), _vp(y), C.c_int(x_stride), C.c_int(y_stride), C.c_int(xo), C.c_int(yo), C.c_int(frames),
+                                           C.c_int(w), C.c_int(h), C.c_int(c), C.c_int(ow), C.c_int(oh), C.c_int(fw), C.c_int(fh), C.c_int(bm),
+                                           C.c_float(border_value))
+        return y
+
+    def im2col_backward(self, dy, c, h, w, fh, fw, y_stride=1, x_stride=1, padding="valid"):
+        oh, ow, yo, xo = self.im2col_geometry(h, w, fh, fw, y_stride, x_stride, padding)
+        dy = np.ascontiguousarray(dy, np.float32)
+        frames = dy.shape[1] // (oh * ow)
+        dx = np.zeros((c * h * w, frames), np.float32)
+        self.lib.oracle_im2col_backward_f32(_vp(dy), _vp(dx), C.c_int(x_stride), C.c_int(y_stride), C.c_int(xo), C.c_int(yo), C.c_int(frames),
+                                            C.c_int(w), C.c_int(h), C.c_int(c), C.c_int(ow), C.c_int(oh), C.c_int(fw), C.c_int(fh))
+        return dx
+
+    def col2im_forward(self, x, c, h, w, out_frames):
+        if x.dtype == np.uint32:
+            x = np.ascontiguousarray(x)
+            y = np.zeros((c * h * w, (out_frames + 31) // 32), np.uint32)
+            self.lib.oracle_col2im_forward_bit(_vp(x), C.c_size_t(x.shape[1]), _vp(y), C.c_size_t(y.shape[1]), C.c_int(w), C.c_int(h), C.c_int(c),
+                                               C.c_int(out_frames))
+            return y
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.zeros((c * h * w, out_frames), np.float32)
+        self.lib.oracle_col2im_forward_f32(_vp(x), _vp(y), C.c_int(w), C.c_int(h), C.c_int(c), C.c_int(out_frames))
+        return y
+
+    def col2im_backward(self, dy, c, h, w):
+        dy = np.ascontiguousarray(dy, np.float32)
+        out_frames = dy.shape[1]
+        dx = np.zeros((c, out_frames * h * w), np.float32)
+        self.lib.oracle_col2im_backward_f32(_vp(dy), _vp(dx), C.c_int(w), C.c_int(h), C.c_int(c), C.c_int(out_frames))
+        return dx
+
+    def maxpool_forward(self, x, c, h, w, fh, fw, frames=None):
+        """float32: returns (y, argmax); uint32 words: returns y."""
+        oh, ow = (h + fh - 1) // fh, (w + fw - 1) // fw
+        if x.dtype == np.uint32:
+            x = np.ascontiguousarray(x)
+            y = np.zeros((c * oh * ow, x.shape[1]), np.uint32)
+            self.lib.oracle_maxpool_forward_bit(_vp(x), _vp(y), C.c_size_t(x.shape[1]), C.c_int(fh), C.c_int(fw), C.c_int(w), C.c_int(h), C.c_int(c),
+                                                C.c_int(frames))
+            return y
+        x = np.ascontiguousarray(x, np.float32)
+        frames = x.shape[1]
+        y = np.zeros((c * oh * ow, frames), np.float32)
+        am = np.zeros((c * oh * ow, frames), np.int32)
+        self.lib.oracle_maxpool_forward_f32(_vp(x), _vp(y), _vp(am), C.c_int(fh), C.c_int(fw), C.c_int(w), C.c_int(h), C.c_int(c), C.c_int(frames))
+        return y, am
+
+    def maxpool_backward(self, argmax_or_xbits, dy, c, h, w, fh, fw):
+        """argmax int32 [c*oh*ow][frames] (fp32 layer) or the forward input as uint32 words (bit layer)."""
+        dy = np.ascontiguousarray(dy, np.float32)
+        frames = dy.shape[1]
+        dx = np.zeros((c * h * w, frames), np.float32)
+        a = np.ascontiguousarray(argmax_or_xbits)
+        if a.dtype == np.uint32:
+            self.lib.oracle_maxpool_backward_bit_f32(_vp(a), C.c_size_t(a.shape[1]), _vp(dy), _vp(dx), C.c_int(fh), C.c_int(fw), C.c_int(w),
+                                                     C.c_int(h), C.c_int(c), C.c_int(frames))
+        else:
+            self.lib.oracle_maxpool_backward_f32(_vp(a.astype(np.int32)), _vp(dy), _vp(dx), C.c_int(fh), C.c_int(fw), C.c_int(w), C.c_int(h),
+                                                 C.c_int(c), C.c_int(frames))
+        return dx
+
     # -- Adam ---------------------------------------------------------------------------------
     def adam_update(self, p, g, m, v, state, lr=0.001, beta1=0.9, beta2=0.999):
         """In place on float32 arrays p, g, m, v; ``state`` is a 2-element float32 array [b1^t, b2^t] starting at 1."""
@@ -402,6 +493,50 @@ class _Ref:
             dy = np.ascontiguousarray(dy, np.float32)
             dx = np.zeros((x_nodes, y_frames * frame_mux), np.float32)
         self.lib.bbref_binary_to_real(_vp(x_words), C.c_int(x_nodes), C.c_int(y_nodes), C.c_int(y_frames), C.c_int(frame_mux), _vp(y), _vp(dy), _vp(dx))
+        return y, dx
+
+    def im2col(self, x, c, h, w, fh, fw, y_stride=1, x_stride=1, padding="valid", border_mode="reflect_101", dy=None, frames=None):
+        """Returns (y, dx); x float32 [c*h*w][frames] or uint32 words (then pass ``frames``; forward only)."""
+        bit = x.dtype == np.uint32
+        x = np.ascontiguousarray(x) if bit else np.ascontiguousarray(x, np.float32)
+        frames = frames if bit else x.shape[1]
+        hw = C.c_int(0)
+        args = lambda y, dyv, dxv: self.lib.bbref_im2col(C.c_int(int(bit)), _vp(x), C.c_int(c), C.c_int(h), C.c_int(w), C.c_int(frames), C.c_int(fh),
+                                                         C.c_int(fw), C.c_int(y_stride), C.c_int(x_stride), padding.encode(), border_mode.encode(),
+                                                         _vp(y), _vp(dyv), _vp(dxv), C.byref(hw))
+        args(None, None, None)                       # first pass: output geometry
+        of = frames * hw.value
+        y = np.zeros((c * fh * fw, (of + 31) // 32), np.uint32) if bit else np.zeros((c * fh * fw, of), np.float32)
+        dx = None
+        if dy is not None and not bit:
+            dy = np.ascontiguousarray(dy, np.float32)
+            dx = np.zeros((c * h * w, frames), np.float32)
+        args(y, dy, dx)
+        return y, dx
+
+    def col2im(self, x, c, h, w, out_frames, dy=None):
+        bit = x.dtype == np.uint32
+        x = np.ascontiguousarray(x) if bit else np.ascontiguousarray(x, np.float32)
+        y = np.zeros((c * h * w, (out_frames + 31) // 32), np.uint32) if bit else np.zeros((c * h * w, out_frames), np.float32)
+        dx = None
+        if dy is not None and not bit:
+            dy = np.ascontiguousarray(dy, np.float32)
+            dx = np.zeros((c, out_frames * h * w), np.float32)
+        self.lib.bbref_col2im(C.c_int(int(bit)), _vp(x), C.c_int(c), C.c_int(h), C.c_int(w), C.c_int(out_frames), _vp(y), _vp(dy), _vp(dx))
+        return y, dx
+
+    def maxpool(self, x, c, h, w, fh, fw, dy=None, frames=None):
+        bit = x.dtype == np.uint32
+        x = np.ascontiguousarray(x) if bit else np.ascontiguousarray(x, np.float32)
+        frames = frames if bit else x.shape[1]
+        oh, ow = (h + fh - 1) // fh, (w + fw - 1) // fw
+        y = np.zeros((c * oh * ow, (frames + 31) // 32), np.uint32) if bit else np.zeros((c * oh * ow, frames), np.float32)
+        dx = None
+        if dy is not None:
+            dy = np.ascontiguousarray(dy, np.float32)
+            dx = np.zeros((c * h * w, frames), np.float32)
+        self.lib.bbref_maxpool(C.c_int(int(bit)), _vp(x), C.c_int(c), C.c_int(h), C.c_int(w), C.c_int(frames), C.c_int(fh), C.c_int(fw), _vp(y),
+                               _vp(dy), _vp(dx))
         return y, dx
 
     def _lut_mlp_step(self, x, t, widths, classes, idx_list, W_list, use_mse, lr):

@@ -20,6 +20,7 @@
 #include <stddef.h>
 #include <string.h>
 #include <math.h>
+#include <float.h>
 
 typedef struct {
     int   binary;        /* x -> 0.5 +/- bias by (x > 0.5)  (fp32 input only; bit input always is) */
@@ -476,4 +477,253 @@ void oracle_binary_to_real_backward(float const *dy, float *dx, int x_nodes, int
         for (int f = 0; f < y_frames; ++f)
             for (int i = 0; i < frame_mux; ++i)
                 dx[(size_t)n * y_frames * frame_mux + f * frame_mux + i] = dy[(size_t)(n % y_nodes) * y_frames + f] * gain;
+}
+
+/* ------------------------------------------------------------------------------------------------
+ * Convolution lowering: Im2Col, Col2Im, MaxPooling (CPU paths of the reference).
+ * Dense arrays: fp32 [node][frames], bits [node][words] with an explicit word stride.
+ * ---------------------------------------------------------------------------------------------- */
+
+enum { ORACLE_BORDER_CONSTANT = 0, ORACLE_BORDER_REFLECT = 1, ORACLE_BORDER_REFLECT_101 = 2, ORACLE_BORDER_REPLICATE = 3, ORACLE_BORDER_WRAP = 4 };
+
+/* include/bb/ConvolutionIm2Col.h:253-288 */
+static int im2col_border(int mode, int *x, int *y, int w, int h)
+{
+    switch (mode) {
+    case ORACLE_BORDER_REFLECT:
+        if (*x < 0) *x = -*x - 1;
+        if (*y < 0) *y = -*y - 1;
+        if (*x >= w) *x = (w - 1) - (*x - w);
+        if (*y >= h) *y = (h - 1) - (*y - h);
+        return 1;
+    case ORACLE_BORDER_REFLECT_101:
+        if (*x < 0) *x = -*x;
+        if (*y < 0) *y = -*y;
+        if (*x >= w) *x = (w - 2) - (*x - w);
+        if (*y >= h) *y = (h - 2) - (*y - h);
+        return 1;
+    case ORACLE_BORDER_REPLICATE:
+        if (*x < 0) *x = 0;
+        if (*y < 0) *y = 0;
+        if (*x >= w) *x = w - 1;
+        if (*y >= h) *y = h - 1;
+        return 1;
+    case ORACLE_BORDER_WRAP:
+        if (*x < 0) *x += w;
+        if (*y < 0) *y += h;
+        if (*x >= w) *x -= w;
+        if (*y >= h) *y -= h;
+        return 1;
+    default:
+        return 0;
+    }
+}
+
+/* Source of output element (output_frame, node (c, fy, fx)): returns the input node or -1 for the border value.
+ * include/bb/ConvolutionIm2Col.h:368-391 */
+static int im2col_source(int output_frame, int c, int fy, int fx, int x_stride, int y_stride, int x_offset, int y_offset, int in_w, int in_h,
+                         int out_w, int out_h, int border_mode, int *input_frame)
+{
+    int output_size = out_w * out_h;
+    int f = output_frame % output_size;
+    *input_frame = output_frame / output_size;
+    int iy = (f / out_w) * y_stride - y_offset + fy;
+    int ix = (f % out_w) * x_stride - x_offset + fx;
+    if (iy >= 0 && iy < in_h && ix >= 0 && ix < in_w) return (c * in_h + iy) * in_w + ix;
+    if (im2col_border(border_mode, &ix, &iy, in_w, in_h)) return (c * in_h + iy) * in_w + ix;
+    return -1;
+}
+
+void oracle_im2col_forward_f32(float const *x, float *y, int x_stride, int y_stride, int x_offset, int y_offset, int in_frames, int in_w, int in_h,
+                               int in_c, int out_w, int out_h, int filter_w, int filter_h, int border_mode, float border_value)
+{
+    int out_frames = in_frames * out_w * out_h;
+    for (int c = 0; c < in_c; ++c)
+        for (int fy = 0; fy < filter_h; ++fy)
+            for (int fx = 0; fx < filter_w; ++fx) {
+                int on = (c * filter_h + fy) * filter_w + fx;
+                for (int of = 0; of < out_frames; ++of) {
+                    int fi, in = im2col_source(of, c, fy, fx, x_stride, y_stride, x_offset, y_offset, in_w, in_h, out_w, out_h, border_mode, &fi);
+                    y[(size_t)on * out_frames + of] = in < 0 ? border_value : x[(size_t)in * in_frames + fi];
+                }
+            }
+}
+
+/* Bit frames: the border value of the Bit specialisation is 0. */
+void oracle_im2col_forward_bit(uint32_t const *x, size_t xs, uint32_t *y, size_t ys, int x_stride, int y_stride, int x_offset, int y_offset,
+                               int in_frames, int in_w, int in_h, int in_c, int out_w, int out_h, int filter_w, int filter_h, int border_mode)
+{
+    int out_frames = in_frames * out_w * out_h;
+    for (int c = 0; c < in_c; ++c)
+        for (int fy = 0; fy < filter_h; ++fy)
+            for (int fx = 0; fx < filter_w; ++fx) {
+                int on = (c * filter_h + fy) * filter_w + fx;
+                memset(y + (size_t)on * ys, 0, sizeof(uint32_t) * ((out_frames + 31) / 32));
+                for (int of = 0; of < out_frames; ++of) {
+                    int fi, in = im2col_source(of, c, fy, fx, x_stride, y_stride, x_offset, y_offset, in_w, in_h, out_w, out_h, border_mode, &fi);
+                    if (in >= 0 && ((x[(size_t)in * xs + (fi >> 5)] >> (fi & 31)) & 1u)) y[(size_t)on * ys + (of >> 5)] |= 1u << (of & 31);
+                }
+            }
+}
+
+/* include/bb/ConvolutionIm2Col.h:439-482: only positions inside the image receive gradient (border copies send none back). */
+void oracle_im2col_backward_f32(float const *dy, float *dx, int x_stride, int y_stride, int x_offset, int y_offset, int in_frames, int in_w, int in_h,
+                                int in_c, int out_w, int out_h, int filter_w, int filter_h)
+{
+    int out_frames = in_frames * out_w * out_h;
+    int iy_limit = (out_h - 1) * y_stride, ix_limit = (out_w - 1) * x_stride;
+    for (int c = 0; c < in_c; ++c)
+        for (int y = 0; y < in_h; ++y)
+            for (int x = 0; x < in_w; ++x) {
+                int in = (c * in_h + y) * in_w + x;
+                int x_align = x % x_stride, y_align = y % y_stride;
+                for (int fi = 0; fi < in_frames; ++fi) {
+                    float g = 0;
+                    for (int fy = y_align; fy < filter_h; fy += y_stride) {
+                        int iy = y - fy + y_offset;
+                        if (iy < 0 || iy > iy_limit) continue;
+                        for (int fx = x_align; fx < filter_w; fx += x_stride) {
+                            int ix = x - fx + x_offset;
+                            if (ix < 0 || ix > ix_limit) continue;
+                            int of = (fi * out_h + iy / y_stride) * out_w + ix / x_stride;
+                            int on = (c * filter_h + fy) * filter_w + fx;
+                            g += dy[(size_t)on * out_frames + of];
+                        }
+                    }
+                    dx[(size_t)in * in_frames + fi] = 0.0f + g;
+                }
+            }
+}
+
+/* include/bb/ConvolutionCol2Im.h:205-221: y[c*hw + xy][fo] = x[c][fo*hw + xy] */
+void oracle_col2im_forward_f32(float const *x, float *y, int w, int h, int c_size, int out_frames)
+{
+    int hw = w * h, in_frames = out_frames * hw;
+    for (int c = 0; c < c_size; ++c)
+        for (int xy = 0; xy < hw; ++xy)
+            for (int fo = 0; fo < out_frames; ++fo) y[(size_t)(c * hw + xy) * out_frames + fo] = x[(size_t)c * in_frames + (size_t)fo * hw + xy];
+}
+
+void oracle_col2im_forward_bit(uint32_t const *x, size_t xs, uint32_t *y, size_t ys, int w, int h, int c_size, int out_frames)
+{
+    int hw = w * h;
+    for (int c = 0; c < c_size; ++c)
+        for (int xy = 0; xy < hw; ++xy) {
+            uint32_t *row = y + (size_t)(c * hw + xy) * ys;
+            memset(row, 0, sizeof(uint32_t) * ((out_frames + 31) / 32));
+            for (int fo = 0; fo < out_frames; ++fo) {
+                size_t fi = (size_t)fo * hw + xy;
+                if ((x[(size_t)c * xs + (fi >> 5)] >> (fi & 31)) & 1u) row[fo >> 5] |= 1u << (fo & 31);
+            }
+        }
+}
+
+/* include/bb/ConvolutionCol2Im.h:283-299 */
+void oracle_col2im_backward_f32(float const *dy, float *dx, int w, int h, int c_size, int out_frames)
+{
+    int hw = w * h, in_frames = out_frames * hw;
+    for (int c = 0; c < c_size; ++c)
+        for (int xy = 0; xy < hw; ++xy)
+            for (int fo = 0; fo < out_frames; ++fo) dx[(size_t)c * in_frames + (size_t)fo * hw + xy] = dy[(size_t)(c * hw + xy) * out_frames + fo];
+}
+
+/* include/bb/MaxPooling.h:286-322: strict '>' from the lowest float, so the first maximum wins; argmax counts the in-range
+ * positions of the window in scan order. */
+void oracle_maxpool_forward_f32(float const *x, float *y, int32_t *argmax, int filter_h, int filter_w, int in_w, int in_h, int c_size, int frames)
+{
+    int out_w = (in_w + filter_w - 1) / filter_w, out_h = (in_h + filter_h - 1) / filter_h;
+    for (int c = 0; c < c_size; ++c)
+        for (int oy = 0; oy < out_h; ++oy)
+            for (int ox = 0; ox < out_w; ++ox) {
+                size_t on = ((size_t)c * out_h + oy) * out_w + ox;
+                for (int f = 0; f < frames; ++f) {
+                    float best = -FLT_MAX;
+                    int32_t am = 0, arg = 0;
+                    for (int fy = 0; fy < filter_h; ++fy) {
+                        int iy = oy * filter_h + fy;
+                        if (iy >= in_h) continue;
+                        for (int fx = 0; fx < filter_w; ++fx) {
+                            int ix = ox * filter_w + fx;
+                            if (ix >= in_w) continue;
+                            float v = x[(((size_t)c * in_h + iy) * in_w + ix) * frames + f];
+                            if (v > best) { best = v; am = arg; }
+                            ++arg;
+                        }
+                    }
+                    y[on * frames + f] = best;
+                    if (argmax) argmax[on * frames + f] = am;
+                }
+            }
+}
+
+/* include/bb/MaxPooling.h:369-394: OR of the window */
+void oracle_maxpool_forward_bit(uint32_t const *x, uint32_t *y, size_t stride, int filter_h, int filter_w, int in_w, int in_h, int c_size, int frames)
+{
+    int out_w = (in_w + filter_w - 1) / filter_w, out_h = (in_h + filter_h - 1) / filter_h, words = (frames + 31) / 32;
+    for (int c = 0; c < c_size; ++c)
+        for (int oy = 0; oy < out_h; ++oy)
+            for (int ox = 0; ox < out_w; ++ox) {
+                uint32_t *row = y + (((size_t)c * out_h + oy) * out_w + ox) * stride;
+                for (int wd = 0; wd < words; ++wd) {
+                    uint32_t m = 0;
+                    for (int fy = 0; fy < filter_h; ++fy)
+                        for (int fx = 0; fx < filter_w; ++fx) {
+                            int iy = oy * filter_h + fy, ix = ox * filter_w + fx;
+                            if (iy < in_h && ix < in_w) m |= x[(((size_t)c * in_h + iy) * in_w + ix) * stride + wd];
+                        }
+                    row[wd] = m;
+                }
+            }
+}
+
+/* include/bb/MaxPooling.h:600-629 */
+void oracle_maxpool_backward_f32(int32_t const *argmax, float const *dy, float *dx, int filter_h, int filter_w, int in_w, int in_h, int c_size, int frames)
+{
+    int out_w = (in_w + filter_w - 1) / filter_w, out_h = (in_h + filter_h - 1) / filter_h;
+    for (int c = 0; c < c_size; ++c)
+        for (int oy = 0; oy < out_h; ++oy)
+            for (int ox = 0; ox < out_w; ++ox) {
+                size_t on = ((size_t)c * out_h + oy) * out_w + ox;
+                for (int f = 0; f < frames; ++f) {
+                    int32_t arg = 0, am = argmax[on * frames + f];
+                    float g = dy[on * frames + f];
+                    for (int fy = 0; fy < filter_h; ++fy) {
+                        int iy = oy * filter_h + fy;
+                        if (iy >= in_h) continue;
+                        for (int fx = 0; fx < filter_w; ++fx) {
+                            int ix = ox * filter_w + fx;
+                            if (ix >= in_w) continue;
+                            dx[(((size_t)c * in_h + iy) * in_w + ix) * frames + f] = (arg == am) ? g : 0.0f;
+                            ++arg;
+                        }
+                    }
+                }
+            }
+}
+
+/* include/bb/MaxPooling.h:681-708: the first set input bit of the window takes the gradient */
+void oracle_maxpool_backward_bit_f32(uint32_t const *x, size_t xs, float const *dy, float *dx, int filter_h, int filter_w, int in_w, int in_h,
+                                     int c_size, int frames)
+{
+    int out_w = (in_w + filter_w - 1) / filter_w, out_h = (in_h + filter_h - 1) / filter_h;
+    for (int c = 0; c < c_size; ++c)
+        for (int oy = 0; oy < out_h; ++oy)
+            for (int ox = 0; ox < out_w; ++ox) {
+                size_t on = ((size_t)c * out_h + oy) * out_w + ox;
+                for (int f = 0; f < frames; ++f) {
+                    float g = dy[on * frames + f];
+                    for (int fy = 0; fy < filter_h; ++fy) {
+                        int iy = oy * filter_h + fy;
+                        if (iy >= in_h) continue;
+                        for (int fx = 0; fx < filter_w; ++fx) {
+                            int ix = ox * filter_w + fx;
+                            if (ix >= in_w) continue;
+                            size_t in = ((size_t)c * in_h + iy) * in_w + ix;
+                            int bit = (x[in * xs + (f >> 5)] >> (f & 31)) & 1u;
+                            dx[in * frames + f] = bit ? g : 0.0f;
+                            if (bit) g = 0.0f;
+                        }
+                    }
+                }
+            }
 }

@@ -36,6 +36,9 @@
 #include "bb/RealToBinary.h"
 #include "bb/BinaryToReal.h"
 #include "bb/UniformDistributionGenerator.h"
+#include "bb/ConvolutionIm2Col.h"
+#include "bb/ConvolutionCol2Im.h"
+#include "bb/MaxPooling.h"
 
 namespace {
 
@@ -488,6 +491,99 @@ int bbref_binary_to_real(std::uint32_t const *x_bits, int x_nodes, int y_nodes, 
         auto dx_buf = b2r->Backward(dy_buf);
         get_fp32(dx_buf, dx, x_nodes, y_frames * frame_mux);
     }
+    return 0;
+}
+
+// bb::ConvolutionIm2Col: forward of x [c*h*w][frames] to y [c*fh*fw][frames*oh*ow], then (fp32 only) backward of dy.
+// bit != 0 runs the <bb::Bit, float> instantiation on packed words (forward only).
+int bbref_im2col(int bit, void const *x, int c, int h, int w, int frames, int fh, int fw, int y_stride, int x_stride, char const *padding,
+                 char const *border_mode, void *y, float const *dy, float *dx, int *out_hw)
+{
+    const int in_nodes = c * h * w, out_nodes = c * fh * fw;
+    if (bit) {
+        auto layer = bb::ConvolutionIm2Col<bb::Bit, float>::Create(fh, fw, y_stride, x_stride, padding, border_mode);
+        layer->SendCommand("host_only true");
+        bb::FrameBuffer x_buf(frames, {c, h, w}, BB_TYPE_BIT, true);
+        put_bit(x_buf, (std::uint32_t const *)x, in_nodes, frames);
+        auto y_buf = layer->Forward(x_buf, true);
+        if (out_hw) *out_hw = (int)(y_buf.GetFrameSize() / frames);
+        if (y) get_bit(y_buf, (std::uint32_t *)y, out_nodes, (int)y_buf.GetFrameSize());
+        return 0;
+    }
+    auto layer = bb::ConvolutionIm2Col<float, float>::Create(fh, fw, y_stride, x_stride, padding, border_mode);
+    layer->SendCommand("host_only true");
+    bb::FrameBuffer x_buf(frames, {c, h, w}, BB_TYPE_FP32, true);
+    put_fp32(x_buf, (float const *)x, in_nodes, frames);
+    auto y_buf = layer->Forward(x_buf, true);
+    const int out_frames = (int)y_buf.GetFrameSize();
+    if (out_hw) *out_hw = out_frames / frames;
+    if (y) get_fp32(y_buf, (float *)y, out_nodes, out_frames);
+    if (dy && dx) {
+        bb::FrameBuffer dy_buf(out_frames, {c, fh, fw}, BB_TYPE_FP32, true);
+        put_fp32(dy_buf, dy, out_nodes, out_frames);
+        auto dx_buf = layer->Backward(dy_buf);
+        get_fp32(dx_buf, dx, in_nodes, frames);
+    }
+    return 0;
+}
+
+// bb::ConvolutionCol2Im: x [c][out_frames*h*w] to y [c*h*w][out_frames]; (fp32 only) backward of dy.
+int bbref_col2im(int bit, void const *x, int c, int h, int w, int out_frames, void *y, float const *dy, float *dx)
+{
+    const int in_frames = out_frames * h * w, out_nodes = c * h * w;
+    if (bit) {
+        auto layer = bb::ConvolutionCol2Im<bb::Bit, float>::Create(h, w);
+        layer->SendCommand("host_only true");
+        layer->SetInputShape({c});                       // Forward() does not derive the channel count itself
+        bb::FrameBuffer x_buf(in_frames, {c}, BB_TYPE_BIT, true);
+        put_bit(x_buf, (std::uint32_t const *)x, c, in_frames);
+        auto y_buf = layer->Forward(x_buf, true);
+        if (y) get_bit(y_buf, (std::uint32_t *)y, out_nodes, out_frames);
+        return 0;
+    }
+    auto layer = bb::ConvolutionCol2Im<float, float>::Create(h, w);
+    layer->SendCommand("host_only true");
+    layer->SetInputShape({c});
+    bb::FrameBuffer x_buf(in_frames, {c}, BB_TYPE_FP32, true);
+    put_fp32(x_buf, (float const *)x, c, in_frames);
+    auto y_buf = layer->Forward(x_buf, true);
+    if (y) get_fp32(y_buf, (float *)y, out_nodes, out_frames);
+    if (dy && dx) {
+        bb::FrameBuffer dy_buf(out_frames, {c, h, w}, BB_TYPE_FP32, true);
+        put_fp32(dy_buf, dy, out_nodes, out_frames);
+        auto dx_buf = layer->Backward(dy_buf);
+        get_fp32(dx_buf, dx, c, in_frames);
+    }
+    return 0;
+}
+
+// bb::MaxPooling: forward of x [c*h*w][frames] to y [c*oh*ow][frames] and backward of dy.
+int bbref_maxpool(int bit, void const *x, int c, int h, int w, int frames, int fh, int fw, void *y, float const *dy, float *dx)
+{
+    const int oh = (h + fh - 1) / fh, ow = (w + fw - 1) / fw;
+    const int in_nodes = c * h * w, out_nodes = c * oh * ow;
+    bb::FrameBuffer dy_buf;
+    if (dy) {
+        dy_buf = bb::FrameBuffer(frames, {c, oh, ow}, BB_TYPE_FP32, true);
+        put_fp32(dy_buf, dy, out_nodes, frames);
+    }
+    if (bit) {
+        auto layer = bb::MaxPooling<bb::Bit, float>::Create(fh, fw);
+        layer->SendCommand("host_only true");
+        bb::FrameBuffer x_buf(frames, {c, h, w}, BB_TYPE_BIT, true);
+        put_bit(x_buf, (std::uint32_t const *)x, in_nodes, frames);
+        auto y_buf = layer->Forward(x_buf, true);
+        if (y) get_bit(y_buf, (std::uint32_t *)y, out_nodes, frames);
+        if (dy && dx) get_fp32(layer->Backward(dy_buf), dx, in_nodes, frames);
+        return 0;
+    }
+    auto layer = bb::MaxPooling<float, float>::Create(fh, fw);
+    layer->SendCommand("host_only true");
+    bb::FrameBuffer x_buf(frames, {c, h, w}, BB_TYPE_FP32, true);
+    put_fp32(x_buf, (float const *)x, in_nodes, frames);
+    auto y_buf = layer->Forward(x_buf, true);
+    if (y) get_fp32(y_buf, (float *)y, out_nodes, frames);
+    if (dy && dx) get_fp32(layer->Backward(dy_buf), dx, in_nodes, frames);
     return 0;
 }
 

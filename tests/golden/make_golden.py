@@ -16,7 +16,7 @@ import sys
 import numpy as np
 
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", ".."))
-from oracle import ref, pack_bits, det_uniform, det_wiring  # noqa: E402
+from oracle import ref, port, pack_bits, det_uniform, det_wiring  # noqa: E402
 
 OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lut6_golden.npz")
 
@@ -189,6 +189,39 @@ def main():
     dyb = det_uniform((10, 8), 142)
     yb2r, dxb2r = ref.binary_to_real(xb, 10, 8, 7, dy=dyb)
     g.update({"b2r_x": xb, "b2r_dy": dyb, "b2r_y": yb2r, "b2r_dx": dxb2r})
+
+    # Convolution lowering (config 3 neighbours): ConvolutionIm2Col / ConvolutionCol2Im / MaxPooling of the reference, fp32 and bit
+    # frames, forward and backward.  Inputs are det_uniform(seed) and are regenerated by the tests; the case tables are stored.
+    PADS, BORDERS = ["valid", "same"], ["constant", "reflect", "reflect_101", "replicate", "wrap"]
+    im2col_cases = [  # c, h, w, fh, fw, y_stride, x_stride, padding, border, frames
+        (3, 8, 8, 3, 3, 1, 1, 1, 2, 5), (2, 7, 9, 3, 3, 1, 1, 0, 0, 4), (2, 8, 8, 3, 3, 2, 2, 1, 3, 3), (1, 6, 5, 5, 3, 1, 2, 1, 4, 2),
+        (2, 6, 6, 3, 3, 1, 1, 1, 1, 3), (2, 9, 7, 2, 2, 2, 1, 0, 2, 3), (2, 8, 8, 3, 3, 1, 1, 1, 0, 40), (3, 8, 4, 3, 3, 1, 1, 1, 2, 37)]
+    for k, (c, h, w, fh, fw, ys, xs, pad, bm, F) in enumerate(im2col_cases):
+        x = det_uniform((c * h * w, F), 300 + k)
+        oh, ow, _, _ = port.im2col_geometry(h, w, fh, fw, ys, xs, PADS[pad])
+        dy = det_uniform((c * fh * fw, F * oh * ow), 320 + k)
+        y, dx = ref.im2col(x, c, h, w, fh, fw, ys, xs, PADS[pad], BORDERS[bm], dy=dy)
+        yb, _ = ref.im2col(pack_bits(x > 0.5), c, h, w, fh, fw, ys, xs, PADS[pad], BORDERS[bm], frames=F)
+        g.update({f"im2col{k}_y": y, f"im2col{k}_dx": dx, f"im2col{k}_ybits": yb})
+    g["im2col_cases"] = np.array(im2col_cases, np.int32)
+    col2im_cases = [(3, 4, 5, 7), (2, 8, 8, 33), (5, 1, 1, 9), (2, 4, 8, 70)]      # c, h, w, output frames
+    for k, (c, h, w, Fo) in enumerate(col2im_cases):
+        x = det_uniform((c, Fo * h * w), 340 + k)
+        dy = det_uniform((c * h * w, Fo), 350 + k)
+        y, dx = ref.col2im(x, c, h, w, Fo, dy=dy)
+        yb, _ = ref.col2im(pack_bits(x > 0.5), c, h, w, Fo)
+        g.update({f"col2im{k}_y": y, f"col2im{k}_dx": dx, f"col2im{k}_ybits": yb})
+    g["col2im_cases"] = np.array(col2im_cases, np.int32)
+    pool_cases = [(3, 8, 8, 2, 2, 9), (2, 7, 5, 2, 2, 33), (2, 9, 9, 3, 3, 5), (1, 4, 6, 2, 3, 70)]   # c, h, w, fh, fw, frames
+    for k, (c, h, w, fh, fw, F) in enumerate(pool_cases):
+        x = np.floor(det_uniform((c * h * w, F), 360 + k) * 4).astype(np.float32) / 4          # few distinct values: ties on purpose
+        oh, ow = (h + fh - 1) // fh, (w + fw - 1) // fw
+        dy = det_uniform((c * oh * ow, F), 370 + k)
+        y, dx = ref.maxpool(x, c, h, w, fh, fw, dy=dy)
+        xb = pack_bits(det_uniform((c * h * w, F), 380 + k) > 0.7)
+        yb, dxb = ref.maxpool(xb, c, h, w, fh, fw, dy=dy, frames=F)
+        g.update({f"pool{k}_y": y, f"pool{k}_dx": dx, f"pool{k}_ybits": yb, f"pool{k}_dxbits": dxb})
+    g["pool_cases"] = np.array(pool_cases, np.int32)
 
     np.savez_compressed(OUT, **g)
     print("wrote", OUT, os.path.getsize(OUT), "bytes,", len(g), "arrays")

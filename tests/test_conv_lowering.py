@@ -1,0 +1,150 @@
+"""Convolution lowering around the per-pixel LUT layers of BASELINE config 3: ConvolutionIm2Col, ConvolutionCol2Im, MaxPooling,
+fp32 and bit frames, forward and backward.  Golden values come from the reference's own classes (tests/golden/make_golden.py);
+these operators only move or select values, so every comparison is exact (fp32 gradients of Im2Col, which add up to
+filter_h * filter_w terms, to 1e-6)."""
+import numpy as np
+import pytest
+
+from oracle import port, pack_bits, det_uniform
+
+PADS, BORDERS = ["valid", "same"], ["constant", "reflect", "reflect_101", "replicate", "wrap"]
+
+
+def _im2col_inputs(k, case):
+    c, h, w, fh, fw, ys, xs, pad, bm, F = (int(v) for v in case)
+    x = det_uniform((c * h * w, F), 300 + k)
+    oh, ow, _, _ = port.im2col_geometry(h, w, fh, fw, ys, xs, PADS[pad])
+    dy = det_uniform((c * fh * fw, F * oh * ow), 320 + k)
+    return (c, h, w, fh, fw, ys, xs, PADS[pad], BORDERS[bm], F, oh, ow), x, dy
+
+
+def _pool_inputs(k, case):
+    c, h, w, fh, fw, F = (int(v) for v in case)
+    x = np.floor(det_uniform((c * h * w, F), 360 + k) * 4).astype(np.float32) / 4
+    oh, ow = (h + fh - 1) // fh, (w + fw - 1) // fw
+    dy = det_uniform((c * oh * ow, F), 370 + k)
+    xb = pack_bits(det_uniform((c * h * w, F), 380 + k) > 0.7)
+    return (c, h, w, fh, fw, F), x, dy, xb
+
+
+def test_conv_lowering_oracle_against_reference(golden):
+    for k, case in enumerate(golden["im2col_cases"]):
+        (c, h, w, fh, fw, ys, xs, pad, bm, F, oh, ow), x, dy = _im2col_inputs(k, case)
+        assert np.array_equal(port.im2col_forward(x, c, h, w, fh, fw, ys, xs, pad, bm), golden[f"im2col{k}_y"])
+        assert np.array_equal(port.im2col_forward(pack_bits(x > 0.5), c, h, w, fh, fw, ys, xs, pad, bm, frames=F), golden[f"im2col{k}_ybits"])
+        assert np.array_equal(port.im2col_backward(dy, c, h, w, fh, fw, ys, xs, pad), golden[f"im2col{k}_dx"])
+    for k, (c, h, w, Fo) in enumerate(golden["col2im_cases"].tolist()):
+        x, dy = det_uniform((c, Fo * h * w), 340 + k), det_uniform((c * h * w, Fo), 350 + k)
+        assert np.array_equal(port.col2im_forward(x, c, h, w, Fo), golden[f"col2im{k}_y"])
+        assert np.array_equal(port.col2im_forward(pack_bits(x > 0.5), c, h, w, Fo), golden[f"col2im{k}_ybits"])
+        assert np.array_equal(port.col2im_backward(dy, c, h, w), golden[f"col2im{k}_dx"])
+    for k, case in enumerate(golden["pool_cases"]):
+        (c, h, w, fh, fw, F), x, dy, xb = _pool_inputs(k, case)
+        y, am = port.maxpool_forward(x, c, h, w, fh, fw)
+        assert np.array_equal(y, golden[f"pool{k}_y"])
+        assert np.array_equal(port.maxpool_backward(am, dy, c, h, w, fh, fw), golden[f"pool{k}_dx"])
+        assert np.array_equal(port.maxpool_forward(xb, c, h, w, fh, fw, frames=F), golden[f"pool{k}_ybits"])
+        assert np.array_equal(port.maxpool_backward(xb, dy, c, h, w, fh, fw), golden[f"pool{k}_dxbits"])
+
+
+def test_im2col_col2im_round_trip_oracle():
+    """A 1x1 'same' Im2Col followed by Col2Im is the identity on [c*h*w][frames] (the pair brackets the per-pixel LUT layers)."""
+    c, h, w, F = 3, 5, 4, 6
+    x = det_uniform((c * h * w, F), 390)
+    cols = port.im2col_forward(x, c, h, w, 1, 1, padding="same")
+    assert cols.shape == (c, F * h * w)
+    assert np.array_equal(port.col2im_forward(cols, c, h, w, F), x)
+
+
+@pytest.mark.gpu
+def test_conv_lowering_gpu_against_golden(golden):
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from binarybrain_b200 import ops
+    from gpu_util import dev_fp32, dev_bits, host_fp32, host_bits, dev
+    for k, case in enumerate(golden["im2col_cases"]):
+        (c, h, w, fh, fw, ys, xs, pad, bm, F, oh, ow), x, dy = _im2col_inputs(k, case)
+        Fo = F * oh * ow
+        y = ops.im2col_forward(dev_fp32(x), F, c, h, w, fh, fw, ys, xs, pad, bm)
+        assert np.array_equal(host_fp32(y, Fo), golden[f"im2col{k}_y"]), k
+        yb = ops.im2col_forward(dev_bits(pack_bits(x > 0.5), F), F, c, h, w, fh, fw, ys, xs, pad, bm)
+        assert np.array_equal(host_bits(yb, Fo), golden[f"im2col{k}_ybits"]), k
+        dx = ops.im2col_backward(dev_fp32(dy), F, c, h, w, fh, fw, ys, xs, pad)
+        assert np.abs(host_fp32(dx, F) - golden[f"im2col{k}_dx"]).max() <= 1e-6, k
+    for k, (c, h, w, Fo) in enumerate(golden["col2im_cases"].tolist()):
+        x, dy = det_uniform((c, Fo * h * w), 340 + k), det_uniform((c * h * w, Fo), 350 + k)
+        assert np.array_equal(host_fp32(ops.col2im_forward(dev_fp32(x), c, h, w, Fo), Fo), golden[f"col2im{k}_y"]), k
+        yb = ops.col2im_forward(dev_bits(pack_bits(x > 0.5), Fo * h * w), c, h, w, Fo)
+        assert np.array_equal(host_bits(yb, Fo), golden[f"col2im{k}_ybits"]), k
+        assert np.array_equal(host_fp32(ops.col2im_backward(dev_fp32(dy), c, h, w, Fo), Fo * h * w), golden[f"col2im{k}_dx"]), k
+    for k, case in enumerate(golden["pool_cases"]):
+        (c, h, w, fh, fw, F), x, dy, xb = _pool_inputs(k, case)
+        y, am = ops.maxpool_forward(dev_fp32(x), F, c, h, w, fh, fw)
+        assert np.array_equal(host_fp32(y, F), golden[f"pool{k}_y"]), k
+        dx = ops.maxpool_backward(am, dev_fp32(dy), F, c, h, w, fh, fw)
+        assert np.array_equal(host_fp32(dx, F), golden[f"pool{k}_dx"]), k
+        xbd = dev_bits(xb, F)
+        assert np.array_equal(host_bits(ops.maxpool_forward(xbd, F, c, h, w, fh, fw), F), golden[f"pool{k}_ybits"]), k
+        dxb = ops.maxpool_backward(xbd, dev_fp32(dy), F, c, h, w, fh, fw, bit_input=True)
+        assert np.array_equal(host_fp32(dxb, F), golden[f"pool{k}_dxbits"]), k
+
+
+@pytest.mark.gpu
+def test_config3_block_shapes_gpu_against_oracle():
+    """The lowering of BASELINE config 3's first conv block at full size: 3x32x32 images, batch 256, 3x3 'same' Im2Col (frames
+    x1024, the bit-frame fast path with 32 pixel groups), Col2Im back from 32 channels and 2x2 MaxPooling, fp32 and bit frames."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from binarybrain_b200 import ops
+    from gpu_util import dev_fp32, dev_bits, host_fp32, host_bits
+    c, h, w, B = 3, 32, 32, 256
+    x = det_uniform((c * h * w, B), 400)
+    cols = ops.im2col_forward(dev_fp32(x), B, c, h, w, 3, 3, padding="same")
+    want = port.im2col_forward(x, c, h, w, 3, 3, padding="same")
+    assert np.array_equal(host_fp32(cols, B * h * w), want)
+    xb = pack_bits(x > 0.5)
+    colsb = ops.im2col_forward(dev_bits(xb, B), B, c, h, w, 3, 3, padding="same")
+    assert np.array_equal(host_bits(colsb, B * h * w), port.im2col_forward(xb, c, h, w, 3, 3, padding="same", frames=B))
+    dy = det_uniform((c * 9, B * h * w), 401)
+    dx = ops.im2col_backward(dev_fp32(dy), B, c, h, w, 3, 3, padding="same")
+    assert np.abs(host_fp32(dx, B) - port.im2col_backward(dy, c, h, w, 3, 3, padding="same")).max() <= 2e-6
+    # the LUT tree's 32 output channels, still one pixel per frame, go back to images
+    ch = 32
+    z = det_uniform((ch, B * h * w), 402)
+    img = ops.col2im_forward(dev_fp32(z), ch, h, w, B)
+    img_w = port.col2im_forward(z, ch, h, w, B)
+    assert np.array_equal(host_fp32(img, B), img_w)
+    zb = pack_bits(z > 0.5)
+    imgb = ops.col2im_forward(dev_bits(zb, B * h * w), ch, h, w, B)
+    imgb_w = port.col2im_forward(zb, ch, h, w, B)
+    assert np.array_equal(host_bits(imgb, B), imgb_w)
+    g = det_uniform((ch * h * w, B), 403)
+    assert np.array_equal(host_fp32(ops.col2im_backward(dev_fp32(g), ch, h, w, B), B * h * w), port.col2im_backward(g, ch, h, w))
+    # 2x2 pooling to 16x16
+    y, am = ops.maxpool_forward(img, B, ch, h, w, 2, 2)
+    y_w, am_w = port.maxpool_forward(img_w, ch, h, w, 2, 2)
+    assert np.array_equal(host_fp32(y, B), y_w) and np.array_equal(am[:, :B].cpu().numpy(), am_w)
+    gp = det_uniform((ch * 16 * 16, B), 404)
+    assert np.array_equal(host_fp32(ops.maxpool_backward(am, dev_fp32(gp), B, ch, h, w, 2, 2), B), port.maxpool_backward(am_w, gp, ch, h, w, 2, 2))
+    yb = ops.maxpool_forward(imgb, B, ch, h, w, 2, 2)
+    assert np.array_equal(host_bits(yb, B), port.maxpool_forward(imgb_w, ch, h, w, 2, 2, frames=B))
+    dxb = ops.maxpool_backward(imgb, dev_fp32(gp), B, ch, h, w, 2, 2, bit_input=True)
+    assert np.array_equal(host_fp32(dxb, B), port.maxpool_backward(imgb_w, gp, ch, h, w, 2, 2))
+
+
+@pytest.mark.gpu
+def test_conv_lowering_rejects_bad_arguments():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from binarybrain_b200 import abi
+    x = torch.zeros((48, 8), device="cuda")
+    y = torch.zeros((27, 8), device="cuda")
+    p = lambda t: t.data_ptr()
+    # output frame stride smaller than frames * oh * ow
+    assert abi.lib().bbcu_fp32_Im2Col_Forward(p(x), p(y), 1, 1, 1, 1, 8, 8, 4, 4, 3, 4, 4, 8, 3, 3, 2, 0.0, None) == -3
+    assert abi.lib().bbcu_fp32_Im2Col_Forward(None, p(y), 1, 1, 1, 1, 8, 8, 4, 4, 3, 4, 4, 128, 3, 3, 2, 0.0, None) == -1
+    # pooling output size must be the rounded-up quotient
+    assert abi.lib().bbcu_fp32_MaxPooling_Forward(p(x), p(y), None, 2, 2, 4, 4, 3, 2, 3, 8, 8, None) == -2
