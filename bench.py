@@ -242,6 +242,59 @@ def train_section(torch, ops, dist, world, rank, steps):
             "allreduce_bytes_per_step": layers_n * (nodes * 64 * 4 + 2 * nodes * 2 * 8) if world > 1 else 0}
 
 
+def build_config3_network(dev, seed=5, ops=None):
+    """BASELINE config 3, the LUT-CNN, from the host-side classes: two conv blocks (each two bb::Convolution2d of per-pixel
+    DifferentiableLut6 layers with 3x3 'same' lowering, then 2x2 MaxPooling) and a dense head 4096 -> 1024 -> 420 -> 70 -> 10.
+    Random 6-distinct wiring, tables N(0.5, 0.01), fp32, batch norm on."""
+    import torch
+    from binarybrain_b200.conv import Convolution2d, MaxPooling, Sequential
+    from binarybrain_b200.dist import ShardedDifferentiableLut6
+    g = torch.Generator(device=dev).manual_seed(seed)
+
+    def lut(n_in, n_out):
+        idx = torch.rand((n_out, n_in), device=dev, generator=g).argsort(dim=1)[:, :6].to(torch.int32).contiguous()
+        W = (torch.randn((n_out, 64), device=dev, generator=g) * 0.01 + 0.5).clamp_(0, 1)
+        return ShardedDifferentiableLut6(idx, W, n_in, ops=ops, binary=False)
+
+    def conv(c, hw, widths):
+        return Convolution2d([lut(a, b) for a, b in zip(widths[:-1], widths[1:])], c, hw, hw, 3, 3, padding="same", ops=ops)
+
+    return Sequential([
+        conv(3, 32, [27, 216, 36, 32]), conv(32, 32, [288, 216, 36, 32]), MaxPooling(32, 32, 32, 2, 2, ops=ops),
+        conv(32, 16, [288, 384, 64]), conv(64, 16, [576, 384, 64]), MaxPooling(64, 16, 16, 2, 2, ops=ops),
+        lut(4096, 1024), lut(1024, 420), lut(420, 70), lut(70, 10)])
+
+
+def cnn_section(torch, ops, steps):
+    """Config 3: LUT-CNN forward + backward on 256 synthetic 3x32x32 images (one GPU).  Node-frames count the LUT evaluations of
+    one forward pass (per-pixel layers run on 256 * oh * ow frames)."""
+    B = 256
+    net = build_config3_network(torch.device("cuda"))
+    x = torch.rand((3 * 32 * 32, B), device="cuda")
+    dy = torch.rand((10, ops.fp32_stride(B)), device="cuda")
+
+    def step():
+        for l in net.lut_layers():
+            ops.clamp_(l.W)
+        net.forward(x, B)
+        net.backward(dy)
+
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    sec = e0.elapsed_time(e1) / 1e3 / steps
+    nf = B * (1024 * (216 + 36 + 32) * 2 + 256 * (384 + 64) * 2 + (1024 + 420 + 70 + 10))
+    return {"workload": "config 3 (LUT-CNN): 3x32x32 images, batch 256, 2 conv blocks of per-pixel DifferentiableLut6 trees with 3x3 Im2Col / "
+                        "Col2Im and 2x2 MaxPooling, dense head 4096->1024->420->70->10, fp32, batch norm; forward + backward",
+            "node_frames_per_s": nf / sec, "ms_per_step": sec * 1e3, "steps": steps, "n_gpus": 1}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -363,6 +416,8 @@ def main():
         if rank == 0:
             torch.cuda.empty_cache()
             line["fp32"] = fp32_section(torch, ops, max(3, min(args.steps, 10)))
+            torch.cuda.empty_cache()
+            line["cnn"] = cnn_section(torch, ops, max(2, min(args.steps, 5)))
             if world == 1:
                 line["cpu_baseline"], _ = cpu_reference_leg(3, 1)
     if dist:

@@ -148,3 +148,70 @@ def test_conv_lowering_rejects_bad_arguments():
     assert abi.lib().bbcu_fp32_Im2Col_Forward(None, p(y), 1, 1, 1, 1, 8, 8, 4, 4, 3, 4, 4, 128, 3, 3, 2, 0.0, None) == -1
     # pooling output size must be the rounded-up quotient
     assert abi.lib().bbcu_fp32_MaxPooling_Forward(p(x), p(y), None, 2, 2, 4, 4, 3, 2, 3, 8, 8, None) == -2
+
+
+def _tables(shape, seed):
+    """Well-spread tables (std ~0.25): batch norm then amplifies rounding differences by ~10 per layer instead of ~100."""
+    return np.clip(0.5 + 0.25 * (det_uniform(shape, seed) - 0.5) * 3.46, 0, 1).astype(np.float32)
+
+
+@pytest.mark.gpu
+def test_convolution2d_layer_gpu_against_oracle():
+    """bb::Convolution2d of two DifferentiableLut6 layers (27 -> 48 -> 16 per pixel) on 3x8x8 images, then 2x2 MaxPooling:
+    forward and backward through the host-side classes against the same composition of oracle operators."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from binarybrain_b200.conv import Convolution2d, MaxPooling, Sequential
+    from binarybrain_b200.dist import ShardedDifferentiableLut6
+    from oracle import det_wiring
+    from gpu_util import dev, dev_fp32, host_fp32, err
+    c, h, w, B = 3, 8, 8, 6
+    P = h * w
+    widths = [27, 48, 16]
+    idx = [det_wiring(widths[l], widths[l + 1], 410 + l) for l in range(2)]
+    W = [_tables((widths[l + 1], 64), 420 + l) for l in range(2)]
+    x = det_uniform((c * h * w, B), 430)
+    dy = det_uniform((16 * 4 * 4, B), 431)
+    # oracle composition
+    cols = port.im2col_forward(x, c, h, w, 3, 3, padding="same")
+    f1 = port.dl6_forward_train(cols, idx[0], W[0], np.zeros(48), np.ones(48), binary=False)
+    f2 = port.dl6_forward_train(f1["y"], idx[1], W[1], np.zeros(16), np.ones(16), binary=False)
+    img = port.col2im_forward(f2["y"], 16, h, w, B)
+    y_w, am = port.maxpool_forward(img, 16, h, w, 2, 2)
+    g = port.maxpool_backward(am, dy, 16, h, w, 2, 2)
+    g = port.col2im_backward(g, 16, h, w)
+    g1, dW1 = port.dl6_backward(f1["y"], g, idx[1], W[1], f2["mean"], f2["rstd"], 48, binary=False)
+    g0, dW0 = port.dl6_backward(cols, g1, idx[0], W[0], f1["mean"], f1["rstd"], 27, binary=False)
+    dx_w = port.im2col_backward(g0, c, h, w, 3, 3, padding="same")
+    # device
+    luts = [ShardedDifferentiableLut6(dev(idx[l]), dev(W[l]), widths[l]) for l in range(2)]
+    net = Sequential([Convolution2d(luts, c, h, w, 3, 3, padding="same"), MaxPooling(16, h, w, 2, 2)])
+    y = net.forward(dev_fp32(x), B)
+    amp = max(1.0, 0.3 * float(f1["rstd"].max())) * max(1.0, 0.3 * float(f2["rstd"].max()))       # batch-norm gain of the two layers
+    assert err(host_fp32(y, B), y_w) <= 1e-5 * amp
+    dx = net.backward(dev_fp32(dy))
+    assert err(host_fp32(dx, B), dx_w) <= 1e-4 * amp
+    assert err(luts[1].dW.cpu().numpy(), dW1) <= 1e-4 * amp and err(luts[0].dW.cpu().numpy(), dW0) <= 1e-4 * amp
+
+
+@pytest.mark.gpu
+def test_config3_network_runs_at_full_shape():
+    """BASELINE config 3 assembled from the host-side classes (two conv blocks with pooling and the dense head), batch 32:
+    one forward and backward; shapes, finiteness, value range and that every table received gradient."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import bench
+    B = 32
+    net = bench.build_config3_network(torch.device("cuda"), seed=5)
+    x = torch.rand((3 * 32 * 32, B), device="cuda")
+    y = net.forward(x, B)
+    assert y.shape[0] == 10 and y.shape[1] >= B
+    assert torch.isfinite(y[:, :B]).all() and float(y[:, :B].min()) >= 0.0 and float(y[:, :B].max()) <= 1.0
+    dx = net.backward(torch.rand_like(y))
+    assert dx.shape[0] == 3 * 32 * 32 and torch.isfinite(dx[:, :B]).all()
+    luts = net.lut_layers()
+    assert len(luts) == 14
+    for layer in luts:
+        assert torch.isfinite(layer.dW).all() and float(layer.dW.abs().sum()) > 0.0
