@@ -273,4 +273,117 @@ __device__ __forceinline__ void lut6_forward_x2(const float4 *tab, const f32x2 (
     LerpTree<6, 0, NP>::eval(tab, x, y);
 }
 
+// ---------------------------------------------------------------------------------------------------
+// One frame, both halves of the tree at once.  The coefficients with input 5 clear (c[0..31]) and set (c[32..63]) form
+// two 5-input polynomials in the same variables u0..u4; carried in the two halves of packed operands they cost 31
+// packed FMAs together, and y = half0 + u5 * half1.  The reverse pass has the same shape (the gradient of half 1 is
+// g * u5), and the 64 accumulators become 32 packed ones: acc2[i] = (dC[i], dC[i + 32]).  This halves the issue slots
+// of the backward pass without adding a single live register, unlike packing two FRAMES, which doubles the kept state.
+// The arithmetic per half is the scalar tree's, operation for operation, so values agree bit for bit with lut6_forward().
+// ---------------------------------------------------------------------------------------------------
+
+// Table for this form: 16 entries of (c[2k], c[2k+32], c[2k+1], c[2k+33]).
+__device__ __forceinline__ void stage_table_halves(float4 *tab2, const float *__restrict__ W, int node, int lane, int lut_binarize)
+{
+    __syncwarp();
+    float2 v = reinterpret_cast<const float2 *>(W + (size_t)node * 64)[lane];
+    if (lut_binarize) {
+        v.x = v.x > 0.5f ? 1.0f : 0.0f;
+        v.y = v.y > 0.5f ? 1.0f : 0.0f;
+    }
+    v = table_to_coeffs(v, lane);
+    const float hx = __shfl_down_sync(kFull, v.x, 16), hy = __shfl_down_sync(kFull, v.y, 16);
+    if (lane < 16) tab2[lane] = make_float4(v.x, hx, v.y, hy);
+    __syncwarp();
+}
+
+// The odd operands of levels 2..5 (both halves) and of level 6, kept between the forward and the reverse pass.
+struct KeptHalves {
+    f32x2 d2[8], d3[4], d4[2], d5;
+    float d6;
+};
+
+__device__ __forceinline__ float lut6_forward_keep_halves(const float4 *tab2, const float (&u)[6], KeptHalves &D)
+{
+    f32x2 U[5];
+#pragma unroll
+    for (int j = 0; j < 5; ++j) U[j] = pack2(u[j], u[j]);
+    f32x2 t[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+        const ulonglong2 c = *reinterpret_cast<const ulonglong2 *>(tab2 + k);       // .x = even pair, .y = odd pair
+        t[k] = fma2(U[0], c.y, c.x);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { D.d2[k] = t[2 * k + 1]; t[k] = fma2(U[1], D.d2[k], t[2 * k]); }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { D.d3[k] = t[2 * k + 1]; t[k] = fma2(U[2], D.d3[k], t[2 * k]); }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) { D.d4[k] = t[2 * k + 1]; t[k] = fma2(U[3], D.d4[k], t[2 * k]); }
+    D.d5 = t[1];
+    const f32x2 top = fma2(U[4], D.d5, t[0]);
+    float a, b;
+    unpack2(top, a, b);
+    D.d6 = b;
+    return fmaf(u[5], b, a);
+}
+
+// Reverse pass for one frame; acc2[i] collects (dC[i], dC[i + 32]).
+__device__ __forceinline__ void lut6_reverse_halves(const float4 *tab2, const float (&u)[6], const KeptHalves &D, float g,
+                                                    f32x2 (&acc2)[32], float (&dx)[6])
+{
+    f32x2 U[5];
+#pragma unroll
+    for (int j = 0; j < 5; ++j) U[j] = pack2(u[j], u[j]);
+    f32x2 gt[16], s[5];
+    dx[5] = g * D.d6;
+    gt[0] = pack2(g, g * u[5]);
+
+    s[4] = mul2(gt[0], D.d5);
+    gt[1] = mul2(gt[0], U[4]);
+
+    s[3] = fma2(gt[1], D.d4[1], mul2(gt[0], D.d4[0]));
+#pragma unroll
+    for (int k = 1; k >= 0; --k) { gt[2 * k + 1] = mul2(gt[k], U[3]); gt[2 * k] = gt[k]; }
+
+    {
+        f32x2 a = mul2(gt[0], D.d3[0]), b = mul2(gt[1], D.d3[1]);
+        a = fma2(gt[2], D.d3[2], a);
+        b = fma2(gt[3], D.d3[3], b);
+        s[2] = add2(a, b);
+    }
+#pragma unroll
+    for (int k = 3; k >= 0; --k) { gt[2 * k + 1] = mul2(gt[k], U[2]); gt[2 * k] = gt[k]; }
+
+    {
+        f32x2 a = mul2(gt[0], D.d2[0]), b = mul2(gt[1], D.d2[1]);
+#pragma unroll
+        for (int k = 2; k < 8; k += 2) { a = fma2(gt[k], D.d2[k], a); b = fma2(gt[k + 1], D.d2[k + 1], b); }
+        s[1] = add2(a, b);
+    }
+#pragma unroll
+    for (int k = 7; k >= 0; --k) { gt[2 * k + 1] = mul2(gt[k], U[1]); gt[2 * k] = gt[k]; }
+
+    {
+        f32x2 a = 0ull, b = 0ull;
+#pragma unroll
+        for (int k = 0; k < 16; k += 2) {
+            a = fma2(gt[k], reinterpret_cast<const ulonglong2 *>(tab2 + k)->y, a);
+            b = fma2(gt[k + 1], reinterpret_cast<const ulonglong2 *>(tab2 + k + 1)->y, b);
+        }
+        s[0] = add2(a, b);
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            acc2[2 * k]     = add2(acc2[2 * k], gt[k]);
+            acc2[2 * k + 1] = fma2(gt[k], U[0], acc2[2 * k + 1]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 5; ++j) {
+        float lo, hi;
+        unpack2(s[j], lo, hi);
+        dx[j] = lo + hi;
+    }
+}
+
 }   // namespace bb200

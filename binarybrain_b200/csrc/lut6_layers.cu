@@ -562,13 +562,13 @@ template <bool XBIT, bool BN>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, 1)
 k_lut6_backward(const BwdArgs a)
 {
-    __shared__ float2 s_tab[kWarpsPerCta][32];
+    __shared__ float4 s_tab[kWarpsPerCta][16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x / a.groups;
     const int node = (blockIdx.x % a.groups) * kWarpsPerCta + warp;
     if (node >= a.O) return;
-    float2 *tab = s_tab[warp];
-    stage_table(tab, a.W, node, lane, a.lut_binarize);
+    float4 *tab = s_tab[warp];
+    stage_table_halves(tab, a.W, node, lane, a.lut_binarize);
     int rows[6];
 #pragma unroll
     for (int j = 0; j < 6; ++j) rows[j] = __ldg(a.idx + (size_t)node * 6 + j);
@@ -580,9 +580,9 @@ k_lut6_backward(const BwdArgs a)
         dmean = a.dmean[node];
         dvar_rF = a.dvar[node];
     }
-    float acc[64];
+    f32x2 acc2[32];                       // (dC[i], dC[i + 32]): both halves of the tree travel in one packed operand
 #pragma unroll
-    for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+    for (int i = 0; i < 32; ++i) acc2[i] = 0ull;
 
     const int f_begin = tile * a.T;
     const int f_end   = min(a.F, f_begin + a.T);
@@ -598,8 +598,8 @@ k_lut6_backward(const BwdArgs a)
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const int f = base + 32 * q + lane;
-            KeptOperands D;
-            float v = lut6_forward_keep(tab, xv[q], D);
+            KeptHalves D;
+            float v = lut6_forward_keep_halves(tab, xv[q], D);
             float g = dyv[q];
             if (BN) {
                 float tanh_x = ((v - mean) * rstd) * a.gamma + a.beta;
@@ -609,13 +609,16 @@ k_lut6_backward(const BwdArgs a)
                 if (f >= a.F) g = 0.0f;
             }
             float dxv[6];
-            lut6_reverse(tab, xv[q], D, g, acc, dxv);
+            lut6_reverse_halves(tab, xv[q], D, g, acc2, dxv);
             if (f < a.F) {
 #pragma unroll
                 for (int j = 0; j < 6; ++j) atomicAdd(a.dx + (size_t)rows[j] * a.dxs + f, dxv[j]);
             }
         }
     }
+    float acc[64];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) unpack2(acc2[i], acc[i], acc[i + 32]);
     warp_reduce_scatter64(acc, lane);
     const float2 gw = coeff_grads_to_table(make_float2(acc[0], acc[1]), lane);
     float *dst = a.dW + (size_t)node * 64 + 2 * lane;
