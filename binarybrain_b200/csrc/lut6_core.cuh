@@ -65,119 +65,11 @@ __device__ __forceinline__ float2 coeff_grads_to_table(float2 g, int lane)
     return g;
 }
 
-// Per-node coefficients staged in shared memory as 32 (c[2k], c[2k+1]) pairs: level 1 is t1[k] = fma(u0, c[2k+1], c[2k]).
-__device__ __forceinline__ void stage_table(float2 *tab, const float *__restrict__ W, int node, int lane, int lut_binarize)
-{
-    __syncwarp();
-    float2 v = reinterpret_cast<const float2 *>(W + (size_t)node * 64)[lane];
-    if (lut_binarize) {
-        v.x = v.x > 0.5f ? 1.0f : 0.0f;
-        v.y = v.y > 0.5f ? 1.0f : 0.0f;
-    }
-    tab[lane] = table_to_coeffs(v, lane);
-    __syncwarp();
-}
-
 // Input conditioning of the reference's CPU path (include/bb/DifferentiableLutN.h:779-786), returning the centred
 // input u = x - 1/2: binary mode maps x to 0.5 +/- bias by (x > 0.5), otherwise x is clipped to [0, 1].
 __device__ __forceinline__ float condition_u(float v, int binary, float bias)
 {
     return binary ? (v > 0.5f ? bias : -bias) : __saturatef(v) - 0.5f;
-}
-
-__device__ __forceinline__ float lut6_forward(const float2 *tab, const float (&u)[6])
-{
-    float t[32];
-#pragma unroll
-    for (int k = 0; k < 32; ++k) { float2 c = tab[k]; t[k] = fmaf(u[0], c.y, c.x); }
-#pragma unroll
-    for (int k = 0; k < 16; ++k) t[k] = fmaf(u[1], t[2 * k + 1], t[2 * k]);
-#pragma unroll
-    for (int k = 0; k < 8; ++k)  t[k] = fmaf(u[2], t[2 * k + 1], t[2 * k]);
-#pragma unroll
-    for (int k = 0; k < 4; ++k)  t[k] = fmaf(u[3], t[2 * k + 1], t[2 * k]);
-#pragma unroll
-    for (int k = 0; k < 2; ++k)  t[k] = fmaf(u[4], t[2 * k + 1], t[2 * k]);
-    return fmaf(u[5], t[1], t[0]);
-}
-
-// The odd ("b") operands of levels 2..6, kept between the forward and the reverse pass.
-struct KeptOperands {
-    float d2[16], d3[8], d4[4], d5[2], d6;
-};
-
-__device__ __forceinline__ float lut6_forward_keep(const float2 *tab, const float (&u)[6], KeptOperands &D)
-{
-    float t[32];
-#pragma unroll
-    for (int k = 0; k < 32; ++k) { float2 c = tab[k]; t[k] = fmaf(u[0], c.y, c.x); }
-#pragma unroll
-    for (int k = 0; k < 16; ++k) { D.d2[k] = t[2 * k + 1]; t[k] = fmaf(u[1], D.d2[k], t[2 * k]); }
-#pragma unroll
-    for (int k = 0; k < 8; ++k)  { D.d3[k] = t[2 * k + 1]; t[k] = fmaf(u[2], D.d3[k], t[2 * k]); }
-#pragma unroll
-    for (int k = 0; k < 4; ++k)  { D.d4[k] = t[2 * k + 1]; t[k] = fmaf(u[3], D.d4[k], t[2 * k]); }
-#pragma unroll
-    for (int k = 0; k < 2; ++k)  { D.d5[k] = t[2 * k + 1]; t[k] = fmaf(u[4], D.d5[k], t[2 * k]); }
-    D.d6 = t[1];
-    return fmaf(u[5], D.d6, t[0]);
-}
-
-// Reverse pass for one frame: g is the gradient arriving at y.  Adds the 64 coefficient gradients
-// into acc (acc[i] belongs to c[i]) and returns the six input gradients in dx.
-__device__ __forceinline__ void lut6_reverse(const float2 *tab, const float (&u)[6], const KeptOperands &D, float g,
-                                             float (&acc)[64], float (&dx)[6])
-{
-    float gt[32];
-    dx[5] = g * D.d6;
-    gt[0] = g;
-    gt[1] = g * u[5];
-
-    dx[4] = fmaf(gt[1], D.d5[1], gt[0] * D.d5[0]);
-#pragma unroll
-    for (int k = 1; k >= 0; --k) { gt[2 * k + 1] = gt[k] * u[4]; gt[2 * k] = gt[k]; }
-
-    {
-        float s = 0.0f;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) s = fmaf(gt[k], D.d4[k], s);
-        dx[3] = s;
-    }
-#pragma unroll
-    for (int k = 3; k >= 0; --k) { gt[2 * k + 1] = gt[k] * u[3]; gt[2 * k] = gt[k]; }
-
-    {
-        float s0 = 0.0f, s1 = 0.0f;
-#pragma unroll
-        for (int k = 0; k < 8; k += 2) { s0 = fmaf(gt[k], D.d3[k], s0); s1 = fmaf(gt[k + 1], D.d3[k + 1], s1); }
-        dx[2] = s0 + s1;
-    }
-#pragma unroll
-    for (int k = 7; k >= 0; --k) { gt[2 * k + 1] = gt[k] * u[2]; gt[2 * k] = gt[k]; }
-
-    {
-        float s0 = 0.0f, s1 = 0.0f;
-#pragma unroll
-        for (int k = 0; k < 16; k += 2) { s0 = fmaf(gt[k], D.d2[k], s0); s1 = fmaf(gt[k + 1], D.d2[k + 1], s1); }
-        dx[1] = s0 + s1;
-    }
-#pragma unroll
-    for (int k = 15; k >= 0; --k) { gt[2 * k + 1] = gt[k] * u[1]; gt[2 * k] = gt[k]; }
-
-    {
-        float s0 = 0.0f, s1 = 0.0f;
-#pragma unroll
-        for (int k = 0; k < 32; k += 2) {
-            s0 = fmaf(gt[k], tab[k].y, s0);
-            s1 = fmaf(gt[k + 1], tab[k + 1].y, s1);
-        }
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-            acc[2 * k]    += gt[k];
-            acc[2 * k + 1] = fmaf(gt[k], u[0], acc[2 * k + 1]);
-        }
-        dx[0] = s0 + s1;
-    }
 }
 
 // Sums acc[i] over the 32 lanes of a warp with a halving butterfly (62 shuffles instead of 64 x 5):
@@ -279,7 +171,8 @@ __device__ __forceinline__ void lut6_forward_x2(const float4 *tab, const f32x2 (
 // packed FMAs together, and y = half0 + u5 * half1.  The reverse pass has the same shape (the gradient of half 1 is
 // g * u5), and the 64 accumulators become 32 packed ones: acc2[i] = (dC[i], dC[i + 32]).  This halves the issue slots
 // of the backward pass without adding a single live register, unlike packing two FRAMES, which doubles the kept state.
-// The arithmetic per half is the scalar tree's, operation for operation, so values agree bit for bit with lut6_forward().
+// The arithmetic per half is that of the frame-pair walk (LerpTree), operation for operation, so the forward and the backward
+// kernels see bit-identical LUT values.
 // ---------------------------------------------------------------------------------------------------
 
 // Table for this form: 16 entries of (c[2k], c[2k+32], c[2k+1], c[2k+33]).
@@ -325,6 +218,29 @@ __device__ __forceinline__ float lut6_forward_keep_halves(const float4 *tab2, co
     float a, b;
     unpack2(top, a, b);
     D.d6 = b;
+    return fmaf(u[5], b, a);
+}
+
+// Forward only (no kept operands): 31 packed FMAs and one scalar.
+__device__ __forceinline__ float lut6_forward_halves(const float4 *tab2, const float (&u)[6])
+{
+    f32x2 t[16];
+    {
+        const f32x2 U0 = pack2(u[0], u[0]);
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            const ulonglong2 c = *reinterpret_cast<const ulonglong2 *>(tab2 + k);
+            t[k] = fma2(U0, c.y, c.x);
+        }
+    }
+#pragma unroll
+    for (int L = 1; L < 5; ++L) {
+        const f32x2 U = pack2(u[L], u[L]);
+#pragma unroll
+        for (int k = 0; k < (16 >> L); ++k) t[k] = fma2(U, t[2 * k + 1], t[2 * k]);
+    }
+    float a, b;
+    unpack2(t[0], a, b);
     return fmaf(u[5], b, a);
 }
 

@@ -70,6 +70,35 @@ __device__ __forceinline__ void gather_x(float (&xv)[4][6], const void *x, long 
     }
 }
 
+// The same gather split in two: the raw loads (fp32 bit patterns or 32-frame words) and, later, their conditioning.  Keeping the two
+// apart lets a kernel issue the loads of its next iteration early and touch the values only when it needs them.
+template <bool XBIT>
+__device__ __forceinline__ void gather_raw(uint32_t (&raw)[4][6], const void *x, long long xs, const int (&rows)[6], int base, int lane, int F)
+{
+#pragma unroll
+    for (int j = 0; j < 6; ++j) {
+        if (XBIT) {
+            const uint32_t *row = static_cast<const uint32_t *>(x) + (size_t)rows[j] * xs + (base >> 5);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) raw[q][j] = (base + 32 * q < F) ? __ldg(row + q) : 0u;
+        } else {
+            const uint32_t *row = static_cast<const uint32_t *>(x) + (size_t)rows[j] * xs + base + lane;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) raw[q][j] = (base + 32 * q + lane < F) ? __ldg(row + 32 * q) : 0u;
+        }
+    }
+}
+
+template <bool XBIT>
+__device__ __forceinline__ void condition_raw(float (&xv)[4][6], const uint32_t (&raw)[4][6], int lane, int binary, float bias)
+{
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int j = 0; j < 6; ++j)
+            xv[q][j] = XBIT ? (((raw[q][j] >> lane) & 1u) ? bias : -bias) : condition_u(__uint_as_float(raw[q][j]), binary, bias);
+}
+
 #ifndef BB200_FWD_CTAS
 #define BB200_FWD_CTAS 2      // resident CTAs per SM the forward kernels are compiled for (register cap 65536 / (256 * n))
 #endif
@@ -455,13 +484,13 @@ template <bool XBIT>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, 3)
 k_lut6_backward_stats(const BwdArgs a)
 {
-    __shared__ float2 s_tab[kWarpsPerCta][32];
+    __shared__ float4 s_tab[kWarpsPerCta][16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x / a.groups;
     const int node = (blockIdx.x % a.groups) * kWarpsPerCta + warp;
     if (node >= a.O) return;
-    float2 *tab = s_tab[warp];
-    stage_table(tab, a.W, node, lane, a.lut_binarize);
+    float4 *tab = s_tab[warp];
+    stage_table_halves(tab, a.W, node, lane, a.lut_binarize);
     int rows[6];
 #pragma unroll
     for (int j = 0; j < 6; ++j) rows[j] = __ldg(a.idx + (size_t)node * 6 + j);
@@ -477,7 +506,7 @@ k_lut6_backward_stats(const BwdArgs a)
         for (int q = 0; q < 4; ++q) {
             const int f = base + 32 * q + lane;
             if (f < a.F) {
-                float v = lut6_forward(tab, xv[q]);
+                float v = lut6_forward_halves(tab, xv[q]);
                 float tanh_x = ((v - mean) * rstd) * a.gamma + a.beta;
                 float g = __ldg(a.dy + (size_t)node * a.dys + f);
                 if (tanh_x <= 0.0f || tanh_x >= 1.0f) g = 0.0f;
@@ -586,14 +615,28 @@ k_lut6_backward(const BwdArgs a)
 
     const int f_begin = tile * a.T;
     const int f_end   = min(a.F, f_begin + a.T);
-    for (int base = f_begin; base < f_end; base += kFramesPerIter) {
-        float xv[4][6];
-        gather_x<XBIT>(xv, a.x, a.xs, rows, base, lane, a.F, a.binary, a.bias);
-        float dyv[4];
+    // The loads of iteration i + 1 are issued before the arithmetic of iteration i (about 1000 instructions), so their latency is
+    // covered by this warp's own work: with ~240 registers per thread only two warps share a scheduler and cannot cover it for each other.
+    uint32_t xn[4][6];
+    float dyn[4];
+    gather_raw<XBIT>(xn, a.x, a.xs, rows, f_begin, lane, a.F);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const int f = base + 32 * q + lane;
-            dyv[q] = (f < a.F) ? __ldg(a.dy + (size_t)node * a.dys + f) : 0.0f;
+    for (int q = 0; q < 4; ++q) {
+        const int f = f_begin + 32 * q + lane;
+        dyn[q] = (f < a.F) ? __ldg(a.dy + (size_t)node * a.dys + f) : 0.0f;
+    }
+    for (int base = f_begin; base < f_end; base += kFramesPerIter) {
+        float xv[4][6], dyv[4];
+        condition_raw<XBIT>(xv, xn, lane, a.binary, a.bias);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) dyv[q] = dyn[q];
+        if (base + kFramesPerIter < f_end) {
+            gather_raw<XBIT>(xn, a.x, a.xs, rows, base + kFramesPerIter, lane, a.F);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int f = base + kFramesPerIter + 32 * q + lane;
+                dyn[q] = (f < a.F) ? __ldg(a.dy + (size_t)node * a.dys + f) : 0.0f;
+            }
         }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
