@@ -89,6 +89,17 @@ __device__ __forceinline__ void gather_raw(uint32_t (&raw)[4][6], const void *x,
     }
 }
 
+// fp32 rows addressed by ready-made element offsets (row * stride), so that the per-access address is one 64-bit add
+__device__ __forceinline__ void gather_raw_off(uint32_t (&raw)[4][6], const float *x, const long long (&off)[6], int base, int lane, int F)
+{
+#pragma unroll
+    for (int j = 0; j < 6; ++j) {
+        const uint32_t *row = reinterpret_cast<const uint32_t *>(x + off[j]) + base + lane;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) raw[q][j] = (base + 32 * q + lane < F) ? __ldg(row + 32 * q) : 0u;
+    }
+}
+
 template <bool XBIT>
 __device__ __forceinline__ void condition_raw(float (&xv)[4][6], const uint32_t (&raw)[4][6], int lane, int binary, float bias)
 {
@@ -598,9 +609,15 @@ k_lut6_backward(const BwdArgs a)
     if (node >= a.O) return;
     float4 *tab = s_tab[warp];
     stage_table_halves(tab, a.W, node, lane, a.lut_binarize);
+    // fp32 inputs: x and dx rows share one stride, so one 64-bit element offset per input serves both and an access costs a single
+    // 64-bit add; bit inputs keep the row numbers for the (word-strided) x rows as well
     int rows[6];
+    long long off[6];
 #pragma unroll
-    for (int j = 0; j < 6; ++j) rows[j] = __ldg(a.idx + (size_t)node * 6 + j);
+    for (int j = 0; j < 6; ++j) {
+        rows[j] = __ldg(a.idx + (size_t)node * 6 + j);
+        off[j] = (long long)rows[j] * a.dxs;
+    }
 
     float mean = 0.0f, rstd = 0.0f, dmean = 0.0f, dvar_rF = 0.0f;
     if (BN) {
@@ -619,7 +636,8 @@ k_lut6_backward(const BwdArgs a)
     // covered by this warp's own work: with ~240 registers per thread only two warps share a scheduler and cannot cover it for each other.
     uint32_t xn[4][6];
     float dyn[4];
-    gather_raw<XBIT>(xn, a.x, a.xs, rows, f_begin, lane, a.F);
+    if (XBIT) gather_raw<true>(xn, a.x, a.xs, rows, f_begin, lane, a.F);
+    else      gather_raw_off(xn, static_cast<const float *>(a.x), off, f_begin, lane, a.F);
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
         const int f = f_begin + 32 * q + lane;
@@ -631,7 +649,8 @@ k_lut6_backward(const BwdArgs a)
 #pragma unroll
         for (int q = 0; q < 4; ++q) dyv[q] = dyn[q];
         if (base + kFramesPerIter < f_end) {
-            gather_raw<XBIT>(xn, a.x, a.xs, rows, base + kFramesPerIter, lane, a.F);
+            if (XBIT) gather_raw<true>(xn, a.x, a.xs, rows, base + kFramesPerIter, lane, a.F);
+            else      gather_raw_off(xn, static_cast<const float *>(a.x), off, base + kFramesPerIter, lane, a.F);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const int f = base + kFramesPerIter + 32 * q + lane;
@@ -654,8 +673,9 @@ k_lut6_backward(const BwdArgs a)
             float dxv[6];
             lut6_reverse_halves(tab, xv[q], D, g, acc2, dxv);
             if (f < a.F) {
+                float *dxf = a.dx + f;
 #pragma unroll
-                for (int j = 0; j < 6; ++j) atomicAdd(a.dx + (size_t)rows[j] * a.dxs + f, dxv[j]);
+                for (int j = 0; j < 6; ++j) atomicAdd(dxf + off[j], dxv[j]);
             }
         }
     }
