@@ -295,6 +295,86 @@ def cnn_section(torch, ops, steps):
             "node_frames_per_s": nf / sec, "ms_per_step": sec * 1e3, "steps": steps, "n_gpus": 1}
 
 
+def operators_section(torch, ops, steps):
+    """Every other operator of the path on the same 8192 -> 8192 x 16384-frame layer (bit inputs: same node counts, 16384 frames), each with
+    its algorithmic bytes / flops per node-frame and the fraction of max(HBM, FP32) roofline time, plus the lowering operators at a config-3
+    block shape and Adam.  One launch sequence per operator call, timed with CUDA events over `steps` calls after 3 warm-ups."""
+    I = O = 8192
+    F = 16384
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(4)
+    idx = torch.rand((O, I), device=dev, generator=g).argsort(dim=1)[:, :6].to(torch.int32).contiguous()
+    W = (torch.randn((O, 64), device=dev, generator=g) * 0.01 + 0.5).clamp_(0, 1)
+    dW = torch.zeros((O, 64), device=dev)
+    xb = torch.randint(-2**31, 2**31 - 1, (I, ops.bit_stride(F)), device=dev, generator=g, dtype=torch.int32)
+    xf = torch.rand((I, F), device=dev, generator=g)
+    dy = torch.rand((O, F), device=dev, generator=g)
+    rm, rv = torch.zeros(O, device=dev), torch.ones(O, device=dev)
+    yf = torch.empty((O, F), device=dev)
+    ybit = torch.zeros((O, ops.bit_stride(F)), dtype=torch.int32, device=dev)
+    dx = torch.empty((I, F), device=dev)
+    st = {}
+
+    def dl_bit_fwd():
+        _, st["mean"], st["rstd"] = ops.differentiable_lut6_forward_training(xb, idx, W, rm, rv, F, y=ybit)
+
+    def sbn_fwd():
+        st["sy"], st["smean"], st["srstd"] = ops.stochastic_bn_forward_training(xf, rm, rv, F)
+
+    adam = ops.Adam([W], [dW])
+    # lowering at the first conv block of config 3: 32 channels, 32x32, batch 256
+    c, hw, B = 32, 32, 256
+    img = torch.rand((c * hw * hw, B), device=dev, generator=g)
+    cols = ops.im2col_forward(img, B, c, hw, hw, 3, 3, padding="same")
+    colsb_in = torch.randint(-2**31, 2**31 - 1, (c * hw * hw, ops.bit_stride(B)), device=dev, generator=g, dtype=torch.int32)
+    z = torch.rand((c, B * hw * hw), device=dev, generator=g)
+    pooled, am = ops.maxpool_forward(img, B, c, hw, hw, 2, 2)
+    gp = torch.rand_like(pooled)
+    nf = float(O) * F
+    px = float(c) * hw * hw * B                       # image elements
+    cases = {   # name: (callable, units per call, algorithmic bytes per unit, algorithmic flops per unit)
+        "sl6_forward_bit_fp32": (lambda: ops.stochastic_lut6_forward(xb, idx, W, F, y=yf), nf, 4.125, 126.0),
+        "sl6_forward_bit_bit": (lambda: ops.stochastic_lut6_forward(xb, idx, W, F, y=ybit, bit_output=True), nf, 0.25, 126.0),
+        "sl6_backward_bit": (lambda: ops.stochastic_lut6_backward(xb, dy, idx, W, dW, I, F, dx=dx), nf, 8.125, 505.0),
+        "dl6_forward_training_bit": (dl_bit_fwd, nf, 0.375, 262.0),
+        "dl6_forward_inference_bit": (lambda: ops.differentiable_lut6_forward_inference(xb, idx, W, rm, rv, F, y=ybit), nf, 0.25, 136.0),
+        "dl6_forward_inference_fp32": (lambda: ops.differentiable_lut6_forward_inference(xf, idx, W, rm, rv, F, y=yf, binary=False), nf, 8.0, 136.0),
+        "dl6_backward_bit": (lambda: ops.differentiable_lut6_backward(xb, dy, idx, W, dW, st["mean"], st["rstd"], I, F, dx=dx), nf, 12.125, 651.0),
+        "sbn_forward_training": (sbn_fwd, nf, 12.0, 8.0),
+        "sbn_backward": (lambda: ops.stochastic_bn_backward(xf, dy, st["smean"], st["srstd"], F), nf, 20.0, 12.0),
+        "adam_update": (lambda: adam.update(), float(W.numel()), 28.0, 12.0),
+        "im2col_forward_fp32": (lambda: ops.im2col_forward(img, B, c, hw, hw, 3, 3, padding="same"), px * 9, 4.0 + 4.0 / 9, 0.0),
+        "im2col_forward_bit": (lambda: ops.im2col_forward(colsb_in, B, c, hw, hw, 3, 3, padding="same"), px * 9, (1 + 1.0 / 9) / 8, 0.0),
+        "im2col_backward_fp32": (lambda: ops.im2col_backward(cols, B, c, hw, hw, 3, 3, padding="same"), px * 9, 4.0 + 4.0 / 9, 1.0),
+        "col2im_forward_fp32": (lambda: ops.col2im_forward(z, c, hw, hw, B), px, 8.0, 0.0),
+        "col2im_backward_fp32": (lambda: ops.col2im_backward(img, c, hw, hw, B), px, 8.0, 0.0),
+        "maxpool_forward_fp32": (lambda: ops.maxpool_forward(img, B, c, hw, hw, 2, 2), px, 4.0 + 2.0, 1.0),
+        "maxpool_backward_fp32": (lambda: ops.maxpool_backward(am, gp, B, c, hw, hw, 2, 2), px, 4.0 + 2.0, 0.0),
+    }
+    props = torch.cuda.get_device_properties(0)
+    hbm, which, _ = measured_peaks()
+    fp32_peak = props.multi_processor_count * 128 * 2 * 1.965e9
+    out = {"layer": f"{I}->{O} nodes, {F} frames (bit inputs: same frames, 32 per word); lowering: {c} channels {hw}x{hw}, batch {B}, 3x3 same / 2x2 pool",
+           "unit": "node-frames (LUT, SBN), table entries (Adam), output elements (lowering: Im2Col counts the 9x expanded buffer)",
+           "hbm_peak": f"{hbm} GB/s of {which}"}
+    for name, (fn, units, bytes_, flops) in cases.items():
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        sec = e0.elapsed_time(e1) / 1e3 / steps
+        t_fp, t_hbm = flops / fp32_peak, bytes_ / (hbm * 1e9)
+        out[name] = {"units_per_s": units / sec, "ms": sec * 1e3, "bound": "fp32" if t_fp > t_hbm else "hbm",
+                     "frac_of_roofline": units / sec * max(t_fp, t_hbm), "algorithmic_bytes_per_unit": round(bytes_, 4),
+                     "algorithmic_flops_per_unit": flops}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -418,6 +498,8 @@ def main():
             line["fp32"] = fp32_section(torch, ops, max(3, min(args.steps, 10)))
             torch.cuda.empty_cache()
             line["cnn"] = cnn_section(torch, ops, max(2, min(args.steps, 5)))
+            torch.cuda.empty_cache()
+            line["operators"] = operators_section(torch, ops, max(3, min(args.steps, 10)))
             if world == 1:
                 line["cpu_baseline"], _ = cpu_reference_leg(3, 1)
     if dist:

@@ -76,11 +76,14 @@ __device__ __forceinline__ int im2col_source(const Im2ColGeom &g, int c, int fy,
 }
 
 // --------------------------------------------------------------------------------------------- Im2Col fp32
-// Block = one output node x 32 input frames x 32 output pixels.  Reads run along input frames, writes along pixels.
+// Block = one output node x 32 input frames x 128 output pixels (four 32 x 32 tiles, so that every thread has 16 independent
+// loads in flight before the barrier).  Reads run along input frames, writes along pixels.
+constexpr int kIm2ColTiles = 4;
+
 __global__ void __launch_bounds__(256)
 k_im2col_forward_f32(const float *__restrict__ x, float *__restrict__ y, Im2ColGeom g, float border_value, int p_tiles, int f_tiles)
 {
-    __shared__ float tile[32][33];
+    __shared__ float tile[kIm2ColTiles][32][33];
     const int tx = threadIdx.x, ty = threadIdx.y;
     int b = blockIdx.x;
     const int pt = b % p_tiles; b /= p_tiles;
@@ -88,23 +91,34 @@ k_im2col_forward_f32(const float *__restrict__ x, float *__restrict__ y, Im2ColG
     const int on = b;                                             // (c * filter_h + fy) * filter_w + fx
     const int fx = on % g.filter_w, fy = (on / g.filter_w) % g.filter_h, c = on / (g.filter_w * g.filter_h);
     const int P = g.out_w * g.out_h;
-    const int p0 = pt * 32, f0 = ft * 32;
-#pragma unroll
-    for (int r = ty; r < 32; r += 8) {
-        const int p = p0 + r, fi = f0 + tx;
-        float v = border_value;
-        if (p < P && fi < g.in_frames) {
-            const int in = im2col_source(g, c, fy, fx, p);
-            if (in >= 0) v = x[(size_t)in * g.in_fs + fi];
-        }
-        tile[r][tx] = v;
+    const int p0 = pt * 32 * kIm2ColTiles, f0 = ft * 32;
+    const int fi_r = f0 + tx;
+    // the source node depends on the pixel only: one warp per tile works it out for 32 pixels (two integer divisions and the
+    // border logic each), the loads below read it back as a broadcast
+    __shared__ int s_src[kIm2ColTiles][32];
+    if (ty < kIm2ColTiles) {
+        const int p = p0 + 32 * ty + tx;
+        s_src[ty][tx] = p < P ? im2col_source(g, c, fy, fx, p) : -2;
     }
     __syncthreads();
 #pragma unroll
-    for (int r = ty; r < 32; r += 8) {
-        const int fi = f0 + r, p = p0 + tx;
-        if (p < P && fi < g.in_frames) y[(size_t)on * g.out_fs + (size_t)fi * P + p] = tile[tx][r];
-    }
+    for (int t = 0; t < kIm2ColTiles; ++t)
+#pragma unroll
+        for (int r = ty; r < 32; r += 8) {
+            const int in = s_src[t][r];
+            float v = border_value;
+            if (in >= 0 && fi_r < g.in_frames) v = x[(size_t)in * g.in_fs + fi_r];
+            tile[t][r][tx] = v;
+        }
+    __syncthreads();
+    float *yrow = y + (size_t)on * g.out_fs;
+#pragma unroll
+    for (int t = 0; t < kIm2ColTiles; ++t)
+#pragma unroll
+        for (int r = ty; r < 32; r += 8) {
+            const int fi = f0 + r, p = p0 + 32 * t + tx;
+            if (p < P && fi < g.in_frames) yrow[(size_t)fi * P + p] = tile[t][tx][r];
+        }
 }
 
 // Block = one channel x 32 input frames x 32 input pixels (q = y * W + x).  For every filter tap the threads of a warp read
@@ -439,7 +453,7 @@ extern "C" int bbcu_fp32_Im2Col_Forward(const float *dev_x_buf, float *dev_y_buf
     if (P == 0 || input_frame_size == 0 || out_nodes == 0) return BBCU_OK;
     const Im2ColGeom g = make_geom(x_stride, y_stride, x_offset, y_offset, input_frame_size, input_frame_stride, input_w_size, input_h_size,
                                    input_c_size, output_w_size, output_h_size, output_frame_stride, filter_w_size, filter_h_size, border_mode);
-    const int p_tiles = (int)((P + 31) / 32), f_tiles = (input_frame_size + 31) / 32;
+    const int p_tiles = (int)((P + 32 * kIm2ColTiles - 1) / (32 * kIm2ColTiles)), f_tiles = (input_frame_size + 31) / 32;
     const long long blocks = out_nodes * p_tiles * f_tiles;
     BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
     k_im2col_forward_f32<<<(unsigned)blocks, dim3(32, 8), 0, as_stream(stream)>>>(dev_x_buf, dev_y_buf, g, border_value, p_tiles, f_tiles);
