@@ -9,7 +9,6 @@
 // Mapping: one warp per output node, one 128-bit load per lane and input row, so a warp reads 512
 // contiguous bytes of each of its six rows per iteration; CTAs of consecutive node groups share a
 // word tile so the tile's input rows stay in L2 for the ~6 nodes that read each of them.
-#include <cstdlib>
 
 #include "common.cuh"
 #include "async_copy.cuh"
@@ -361,8 +360,7 @@ extern "C" int bbcu_bit_BinaryLut6_Forward(const int *x, int *y, const int *idx,
     a.Tw = ((tf / 32 + 127) / 128) * 128;
     const long long blocks = (long long)((a.nwords + a.Tw - 1) / a.Tw) * a.groups;
     BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
-    static const int variant = []() { const char *e = getenv("BB200_BL6_VARIANT"); return e ? atoi(e) : 2; }();
-    if (vec && variant == 2) {
+    if (vec) {
         // persistent pipeline: two CTAs per SM, each walking (tile, node group) items
         static bool attr_done[64] = {};              // the opt-in to > 48 KB of dynamic shared memory is per device
         const int dev_id = bbcu_GetDevice();
@@ -382,9 +380,9 @@ extern "C" int bbcu_bit_BinaryLut6_Forward(const int *x, int *y, const int *idx,
             return launch_status();
         }
     }
-    if (vec && variant >= 1) k_binary_lut6_2pipe<<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
-    else if (vec)            k_binary_lut6<true><<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
-    else                     k_binary_lut6<false><<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
+    // aligned rows without the shared-memory opt-in (or without a fault word): the non-pipelined 128-bit kernel; otherwise word loads
+    if (vec) k_binary_lut6_2pipe<<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
+    else     k_binary_lut6<false><<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
     return launch_status();
 }
 
