@@ -334,10 +334,11 @@ def operators_section(torch, ops, steps):
     px = float(c) * hw * hw * B                       # image elements
     cases = {   # name: (callable, units per call, algorithmic bytes per unit, algorithmic flops per unit)
         "sl6_forward_bit_fp32": (lambda: ops.stochastic_lut6_forward(xb, idx, W, F, y=yf), nf, 4.125, 126.0),
-        "sl6_forward_bit_bit": (lambda: ops.stochastic_lut6_forward(xb, idx, W, F, y=ybit, bit_output=True), nf, 0.25, 126.0),
+        # bit in, bit out: evaluated as a BinaryLut6 forward with a per-node truth table (no per-frame fp32 tree), so the bound is HBM
+        "sl6_forward_bit_bit": (lambda: ops.stochastic_lut6_forward(xb, idx, W, F, y=ybit, bit_output=True), nf, 0.25, 0.0),
         "sl6_backward_bit": (lambda: ops.stochastic_lut6_backward(xb, dy, idx, W, dW, I, F, dx=dx), nf, 8.125, 505.0),
-        "dl6_forward_training_bit": (dl_bit_fwd, nf, 0.375, 262.0),
-        "dl6_forward_inference_bit": (lambda: ops.differentiable_lut6_forward_inference(xb, idx, W, rm, rv, F, y=ybit), nf, 0.25, 136.0),
+        "dl6_forward_training_bit": (dl_bit_fwd, nf, 0.375, 0.0),       # x read twice (pattern histogram, then the table forward)
+        "dl6_forward_inference_bit": (lambda: ops.differentiable_lut6_forward_inference(xb, idx, W, rm, rv, F, y=ybit), nf, 0.25, 0.0),
         "dl6_forward_inference_fp32": (lambda: ops.differentiable_lut6_forward_inference(xf, idx, W, rm, rv, F, y=yf, binary=False), nf, 8.0, 136.0),
         "dl6_backward_bit": (lambda: ops.differentiable_lut6_backward(xb, dy, idx, W, dW, st["mean"], st["rstd"], I, F, dx=dx), nf, 12.125, 651.0),
         "sbn_forward_training": (sbn_fwd, nf, 12.0, 8.0),

@@ -1,0 +1,238 @@
+// Bit-input LUT layers by pattern table.
+//
+// With bit-packed inputs every input of a node is one of two values (0.5 - bias, 0.5 + bias), so a node's LUT value over a
+// frame depends only on the frame's 6-bit input pattern p: y = Y[p], 64 values per node.  Everything a bit-in / bit-out
+// layer produces then follows from Y and from how often each pattern occurs:
+//
+//   * bit output (y > 0.5 after the optional batch-norm affine map) is a 64-bit truth table B[p] per node, and the layer's
+//     forward IS a BinaryLut6 forward with that table: 63 word-wide integer operations per 32 frames instead of a 63-node
+//     fp32 tree per frame;
+//   * the batch statistics of the training forward are  sum_p H[p] Y[p]  and  sum_p H[p] Y[p]^2  with H the per-node
+//     histogram of the patterns over the frames (minterm masks and population counts on whole words).
+//
+// Y[p] is evaluated by the same tree walk, on the same conditioned inputs (+-bias), as the per-frame kernels, so the
+// values -- and every threshold decision taken on them -- are bit-identical to evaluating the tree frame by frame.
+//
+// Reference semantics: the bit-input branches of include/bb/StochasticLutN.h:432-560 and include/bb/DifferentiableLutN.h:
+// 747-905 (CPU), operators bbcu_bit_bit_fp32_StochasticLut_Forward, bbcu_bit_fp32_DifferentiableLutN_ForwardTraining /
+// _ForwardInference (include/bbcu/bbcu.h:540-560, 600-618, 712-727).
+#include "common.cuh"
+#include "lut6_core.cuh"
+
+namespace bb200 {
+
+namespace {
+
+enum { kTableRaw = 0, kTableNorm = 1, kTableNone = 2 };
+
+// One warp per node: lane l evaluates patterns l and l + 32 as one packed pair (they differ in input 5 only).
+// MODE kTableRaw : B[p] = Y[p] > 0.5                                   (StochasticLut6, bit -> bit)
+//      kTableNorm: B[p] = ((Y[p] - mean) * scale) * gamma + beta > 0.5 (DifferentiableLut6 inference; scale = 1/sqrt(var))
+//      kTableNone: Y only (training: the statistics come first)
+template <int MODE>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+k_pattern_values(const float *__restrict__ W, float *__restrict__ Y, int *__restrict__ table, const float *__restrict__ mean_buf,
+                 const float *__restrict__ var_buf, float gamma, float beta, float bias, int O, int lut_binarize)
+{
+    __shared__ float4 s_tab[kWarpsPerCta][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int node = blockIdx.x * kWarpsPerCta + warp;
+    if (node >= O) return;
+    float4 *tab = s_tab[warp];
+    stage_table_x2(tab, W, node, lane, lut_binarize);
+    f32x2 up[6][1], yp[1];
+#pragma unroll
+    for (int j = 0; j < 5; ++j) {
+        const float u = ((lane >> j) & 1) ? bias : -bias;
+        up[j][0] = pack2(u, u);
+    }
+    up[5][0] = pack2(-bias, bias);
+    lut6_forward_x2<1>(tab, up, yp);
+    float lo, hi;
+    unpack2(yp[0], lo, hi);
+    if (Y != nullptr) {
+        Y[(size_t)node * 64 + lane] = lo;
+        Y[(size_t)node * 64 + 32 + lane] = hi;
+    }
+    if (MODE != kTableNone) {
+        if (MODE == kTableNorm) {
+            const float mean = mean_buf[node], scale = 1.0f / sqrtf(var_buf[node]);       // DifferentiableLutN.h:866-868
+            lo = (lo - mean) * scale; lo = lo * gamma + beta;
+            hi = (hi - mean) * scale; hi = hi * gamma + beta;
+        }
+        const unsigned w_lo = __ballot_sync(kFull, lo > 0.5f), w_hi = __ballot_sync(kFull, hi > 0.5f);
+        if (lane == 0) { table[2 * (size_t)node] = (int)w_lo; table[2 * (size_t)node + 1] = (int)w_hi; }
+    }
+}
+
+// Minterm masks of 6 input words, depth first: at the leaves the population counts of the 64 patterns.
+template <int L>
+struct Minterms {
+    static __device__ __forceinline__ void count(uint32_t m, const uint32_t (&x)[6], uint32_t (&cnt)[64], int base)
+    {
+        Minterms<L - 1>::count(m & ~x[L - 1], x, cnt, base);
+        Minterms<L - 1>::count(m & x[L - 1], x, cnt, base + (1 << (L - 1)));
+    }
+};
+template <>
+struct Minterms<0> {
+    static __device__ __forceinline__ void count(uint32_t m, const uint32_t (&)[6], uint32_t (&cnt)[64], int base) { cnt[base] += __popc(m); }
+};
+
+template <int N, int MASK>
+__device__ __forceinline__ void butterfly_step_u32(uint32_t (&a)[64], int lane)
+{
+    const bool upper = (lane & MASK) != 0;
+#pragma unroll
+    for (int i = 0; i < N / 2; ++i) {
+        const uint32_t send = upper ? a[i] : a[i + N / 2];
+        const uint32_t keep = upper ? a[i + N / 2] : a[i];
+        a[i] = keep + __shfl_xor_sync(kFull, send, MASK);
+    }
+}
+
+// Per-node histogram of the input patterns.  Warp = one node for a tile of words; each lane takes whole words (32 frames).
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+k_pattern_histogram(const uint32_t *__restrict__ x, const int *__restrict__ idx, uint32_t *__restrict__ hist, int O, int F, long long xs, int groups,
+                    int tile_words)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x / groups;
+    const int node = (blockIdx.x % groups) * kWarpsPerCta + warp;
+    if (node >= O) return;
+    const uint32_t *rows[6];
+#pragma unroll
+    for (int j = 0; j < 6; ++j) rows[j] = x + (size_t)__ldg(idx + (size_t)node * 6 + j) * xs;
+    uint32_t cnt[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) cnt[i] = 0;
+    const int words = (F + 31) >> 5;
+    const int w_end = min(words, (tile + 1) * tile_words);
+    for (int w = tile * tile_words + lane; w < w_end; w += 32) {
+        uint32_t xw[6];
+#pragma unroll
+        for (int j = 0; j < 6; ++j) xw[j] = __ldg(rows[j] + w);
+        const int valid = F - w * 32;                                   // frames in this word
+        const uint32_t live = valid >= 32 ? 0xffffffffu : ((1u << valid) - 1u);
+        Minterms<6>::count(live, xw, cnt, 0);
+    }
+    butterfly_step_u32<64, 16>(cnt, lane);
+    butterfly_step_u32<32, 8>(cnt, lane);
+    butterfly_step_u32<16, 4>(cnt, lane);
+    butterfly_step_u32<8, 2>(cnt, lane);
+    butterfly_step_u32<4, 1>(cnt, lane);
+    atomicAdd(hist + (size_t)node * 64 + 2 * lane, cnt[0]);
+    atomicAdd(hist + (size_t)node * 64 + 2 * lane + 1, cnt[1]);
+}
+
+// Training statistics and the truth table from Y and the histogram (include/bb/DifferentiableLutN.h:804-812 for the statistics).
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+k_dl6_bit_train_finalize(const float *__restrict__ Y, const uint32_t *__restrict__ hist, int *__restrict__ table, float *mean_out, float *rstd_out,
+                         float *running_mean, float *running_var, float gamma, float beta, float momentum, int O, int F)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int node = blockIdx.x * kWarpsPerCta + warp;
+    if (node >= O) return;
+    const float y0 = Y[(size_t)node * 64 + lane], y1 = Y[(size_t)node * 64 + 32 + lane];
+    const double h0 = (double)hist[(size_t)node * 64 + lane], h1 = (double)hist[(size_t)node * 64 + 32 + lane];
+    double s1 = h0 * (double)y0 + h1 * (double)y1;
+    double s2 = h0 * ((double)y0 * (double)y0) + h1 * ((double)y1 * (double)y1);
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    const float rF   = 1.0f / (float)F;
+    const float mean = (float)s1 * rF;
+    const float var  = fmaxf(1.0e-5f, fmaf((float)s2, rF, -(mean * mean)));
+    const float rstd = 1.0f / sqrtf(var);
+    float lo = (y0 - mean) * rstd, hi = (y1 - mean) * rstd;
+    lo = lo * gamma + beta;
+    hi = hi * gamma + beta;
+    const unsigned w_lo = __ballot_sync(kFull, lo > 0.5f), w_hi = __ballot_sync(kFull, hi > 0.5f);
+    if (lane == 0) {
+        table[2 * (size_t)node] = (int)w_lo;
+        table[2 * (size_t)node + 1] = (int)w_hi;
+        running_mean[node] = running_mean[node] * momentum + mean * (1.0f - momentum);
+        running_var[node]  = running_var[node]  * momentum + var  * (1.0f - momentum);
+        mean_out[node] = mean;
+        rstd_out[node] = rstd;
+    }
+}
+
+// BinaryLut6 leaves the bits past the last frame as its inputs make them; these layers clear them.
+__global__ void k_clear_tail_bits(uint32_t *y, int O, int F, long long ys)
+{
+    const int node = blockIdx.x * blockDim.x + threadIdx.x;
+    if (node >= O) return;
+    y[(size_t)node * ys + (F >> 5)] &= (1u << (F & 31)) - 1u;
+}
+
+struct Scratch {
+    float    *Y;        // [O][64]
+    uint32_t *hist;     // [O][64]
+    int      *table;    // [O][2]
+};
+
+bool carve(Scratch &s, int O, cudaStream_t st)
+{
+    const size_t per_node = 64 * 4 + 64 * 4 + 8;
+    unsigned char *base = static_cast<unsigned char *>(stream_scratch(st, per_node * (size_t)O, 1));
+    if (base == nullptr) return false;
+    s.Y = reinterpret_cast<float *>(base);
+    s.hist = reinterpret_cast<uint32_t *>(base + (size_t)O * 256);
+    s.table = reinterpret_cast<int *>(base + (size_t)O * 512);
+    return true;
+}
+
+int run_binary_lut(const int *x, int *y, const int *idx, const int *table, int O, int F, int stride, cudaStream_t st)
+{
+    int rc = bbcu_bit_BinaryLut6_Forward(x, y, idx, table, O, F, stride, reinterpret_cast<bbcu_stream_t>(st));
+    if (rc) return rc;
+    if (F & 31) {
+        k_clear_tail_bits<<<(O + 255) / 256, 256, 0, st>>>(reinterpret_cast<uint32_t *>(y), O, F, stride);
+        return launch_status();
+    }
+    return BBCU_OK;
+}
+
+}   // namespace
+
+// StochasticLut6 bit -> bit (with_bn = false) and DifferentiableLut6 bit inference (with_bn = true).  Returns
+// BBCU_ERR_NO_MEMORY when the scratch cannot be had; the caller then falls back to the per-frame kernel.
+int bit_forward_by_table(bool with_bn, const int *x, int *y, const int *idx, const float *W, const float *rmean, const float *rvar, float gamma,
+                         float beta, float bias, int O, int F, int stride, int lut_binarize, cudaStream_t st)
+{
+    if (O == 0 || F == 0) return BBCU_OK;
+    Scratch s;
+    if (!carve(s, O, st)) return BBCU_ERR_NO_MEMORY;
+    const int blocks = (O + kWarpsPerCta - 1) / kWarpsPerCta;
+    if (with_bn) k_pattern_values<kTableNorm><<<blocks, kWarpsPerCta * 32, 0, st>>>(W, nullptr, s.table, rmean, rvar, gamma, beta, bias, O, lut_binarize);
+    else         k_pattern_values<kTableRaw><<<blocks, kWarpsPerCta * 32, 0, st>>>(W, nullptr, s.table, nullptr, nullptr, 0.0f, 0.0f, bias, O, lut_binarize);
+    BB200_CUDA(cudaPeekAtLastError());
+    return run_binary_lut(x, y, idx, s.table, O, F, stride, st);
+}
+
+int dl6_bit_forward_training_by_table(const int *x, int *y, const int *idx, const float *W, float *mean, float *rstd, float *rmean, float *rvar,
+                                      float gamma, float beta, float momentum, float bias, int O, int F, int stride, int lut_binarize,
+                                      cudaStream_t st)
+{
+    if (O == 0 || F == 0) return BBCU_OK;
+    Scratch s;
+    if (!carve(s, O, st)) return BBCU_ERR_NO_MEMORY;
+    const int groups = (O + kWarpsPerCta - 1) / kWarpsPerCta;
+    k_pattern_values<kTableNone><<<groups, kWarpsPerCta * 32, 0, st>>>(W, s.Y, nullptr, nullptr, nullptr, 0.0f, 0.0f, bias, O, lut_binarize);
+    BB200_CUDA(cudaPeekAtLastError());
+    BB200_CUDA(cudaMemsetAsync(s.hist, 0, (size_t)O * 256, st));
+    // word tiles: wide enough to amortise the 64-counter reduction (about 400 instructions per warp), narrow enough to fill the GPU
+    const int words = (F + 31) / 32;
+    int tile_words = 4096;
+    while (tile_words > 32 && (long long)groups * ((words + tile_words - 1) / tile_words) < 2LL * device_info().sm_count) tile_words /= 2;
+    const long long blocks = (long long)groups * ((words + tile_words - 1) / tile_words);
+    BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+    k_pattern_histogram<<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(reinterpret_cast<const uint32_t *>(x), idx, s.hist, O, F, stride, groups,
+                                                                       tile_words);
+    BB200_CUDA(cudaPeekAtLastError());
+    k_dl6_bit_train_finalize<<<groups, kWarpsPerCta * 32, 0, st>>>(s.Y, s.hist, s.table, mean, rstd, rmean, rvar, gamma, beta, momentum, O, F);
+    BB200_CUDA(cudaPeekAtLastError());
+    return run_binary_lut(x, y, idx, s.table, O, F, stride, st);
+}
+
+}   // namespace bb200

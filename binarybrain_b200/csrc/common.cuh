@@ -44,6 +44,14 @@ int dl6_forward_stats(const float *x, float *y, const int *idx, const float *W, 
 // while that still leaves enough CTAs to fill the machine.
 int frame_tile(long long rows_touched, int bits_per_row_frame, int node_groups, int frame_size, int max_tile);
 
+// Bit-in / bit-out LUT layers evaluated through a per-node pattern table and the BinaryLut6 kernel (binary_mode.cu).  Both return
+// BBCU_ERR_NO_MEMORY when their scratch cannot be had, in which case the caller runs the per-frame kernels instead.
+int bit_forward_by_table(bool with_bn, const int *x, int *y, const int *idx, const float *W, const float *rmean, const float *rvar, float gamma,
+                         float beta, float bias, int O, int F, int stride, int lut_binarize, cudaStream_t st);
+int dl6_bit_forward_training_by_table(const int *x, int *y, const int *idx, const float *W, float *mean, float *rstd, float *rmean, float *rvar,
+                                      float gamma, float beta, float momentum, float bias, int O, int F, int stride, int lut_binarize,
+                                      cudaStream_t st);
+
 // Per-device int in global memory (zero until a kernel records a fault); allocated once, never freed.
 int *fault_word();
 

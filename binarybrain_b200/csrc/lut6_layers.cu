@@ -833,6 +833,10 @@ extern "C" int bbcu_bit_bit_fp32_StochasticLut6_Forward(const int *x, int *y, co
     int rc = check_common(x, y, idx, W, node_size, frame_size, frame_stride);
     if (rc) return rc;
     BB200_REQUIRE((long long)frame_stride * 32 >= frame_size, BBCU_ERR_BAD_STRIDE);
+    // bit in, bit out: the layer is a BinaryLut6 forward with the truth table (LUT value of each input pattern > 0.5)
+    rc = bit_forward_by_table(false, x, y, idx, W, nullptr, nullptr, 0.0f, 0.0f, unbinarize_bias, node_size, frame_size, frame_stride,
+                              lut_binarize, as_stream(stream));
+    if (rc != BBCU_ERR_NO_MEMORY) return rc;
     return forward_plain<true>(x, nullptr, reinterpret_cast<uint32_t *>(y), idx, W, node_size, frame_size, frame_stride, frame_stride, 1,
                                lut_binarize, unbinarize_bias, as_stream(stream));
 }
@@ -958,6 +962,10 @@ extern "C" int bbcu_bit_fp32_DifferentiableLut6_ForwardTraining(const int *x, in
     BB200_REQUIRE((long long)frame_stride * 32 >= frame_size, BBCU_ERR_BAD_STRIDE);
     if (node_size == 0) return BBCU_OK;
     cudaStream_t st = as_stream(stream);
+    // bit in, bit out: statistics from the per-node histogram of input patterns, output by a BinaryLut6 forward with the truth table
+    rc = dl6_bit_forward_training_by_table(x, y, idx, W, mean, rstd, rmean, rvar, gamma, beta, momentum, unbinarize_bias, node_size, frame_size,
+                                           frame_stride, lut_binarize, st);
+    if (rc != BBCU_ERR_NO_MEMORY) return rc;
     double *sums = static_cast<double *>(stream_scratch(st, sizeof(double) * 2 * (size_t)node_size));
     BB200_REQUIRE(sums != nullptr, BBCU_ERR_NO_MEMORY);
     BB200_CUDA(cudaMemsetAsync(sums, 0, sizeof(double) * 2 * (size_t)node_size, st));
@@ -999,6 +1007,9 @@ extern "C" int bbcu_bit_fp32_DifferentiableLut6_ForwardInference(const int *x, i
     if (rc) return rc;
     BB200_REQUIRE_PTR(rmean); BB200_REQUIRE_PTR(rvar);
     BB200_REQUIRE((long long)frame_stride * 32 >= frame_size, BBCU_ERR_BAD_STRIDE);
+    rc = bit_forward_by_table(true, x, y, idx, W, rmean, rvar, gamma, beta, unbinarize_bias, node_size, frame_size, frame_stride, lut_binarize,
+                              as_stream(stream));
+    if (rc != BBCU_ERR_NO_MEMORY) return rc;
     FwdArgs a = {};
     a.x = x; a.ybits = reinterpret_cast<uint32_t *>(y); a.idx = idx; a.W = W; a.mean = rmean; a.rstd = rvar; a.stat_is_var = 1;
     a.bias = unbinarize_bias; a.gamma = gamma; a.beta = beta;
