@@ -333,7 +333,7 @@ def operators_section(torch, ops, steps):
     nf = float(O) * F
     px = float(c) * hw * hw * B                       # image elements
     cases = {   # name: (callable, units per call, algorithmic bytes per unit, algorithmic flops per unit)
-        "sl6_forward_bit_fp32": (lambda: ops.stochastic_lut6_forward(xb, idx, W, F, y=yf), nf, 4.125, 126.0),
+        "sl6_forward_bit_fp32": (lambda: ops.stochastic_lut6_forward(xb, idx, W, F, y=yf), nf, 4.125, 0.0),       # per-pattern value lookup
         # bit in, bit out: evaluated as a BinaryLut6 forward with a per-node truth table (no per-frame fp32 tree), so the bound is HBM
         "sl6_forward_bit_bit": (lambda: ops.stochastic_lut6_forward(xb, idx, W, F, y=ybit, bit_output=True), nf, 0.25, 0.0),
         "sl6_backward_bit": (lambda: ops.stochastic_lut6_backward(xb, dy, idx, W, dW, I, F, dx=dx), nf, 8.125, 505.0),

@@ -165,6 +165,44 @@ __global__ void k_clear_tail_bits(uint32_t *y, int O, int F, long long ys)
     y[(size_t)node * ys + (F >> 5)] &= (1u << (F & 31)) - 1u;
 }
 
+// StochasticLut6 bit -> fp32: y[f] = clip(Y[p(f)], 0, 1).  Warp = one node for a tile of words.  Each lane loads one word of each of
+// the six rows (32 words per row and step, coalesced), then the warp walks the 32 words: word k is broadcast by shuffle, lane l
+// takes frame l of it, looks its pattern up in the node's 64 clipped values (shared memory) and the warp stores 32 consecutive
+// frames.
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+k_bit_gather_forward(const uint32_t *__restrict__ x, float *__restrict__ y, const int *__restrict__ idx, const float *__restrict__ Y, int O, int F,
+                     long long xs, long long ys, int groups, int tile_words)
+{
+    __shared__ float s_val[kWarpsPerCta][64];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x / groups;
+    const int node = (blockIdx.x % groups) * kWarpsPerCta + warp;
+    if (node >= O) return;
+    float *val = s_val[warp];
+    val[lane] = __saturatef(Y[(size_t)node * 64 + lane]);
+    val[lane + 32] = __saturatef(Y[(size_t)node * 64 + 32 + lane]);
+    __syncwarp();
+    const uint32_t *rows[6];
+#pragma unroll
+    for (int j = 0; j < 6; ++j) rows[j] = x + (size_t)__ldg(idx + (size_t)node * 6 + j) * xs;
+    const int words = (F + 31) >> 5;
+    const int w_end = min(words, (tile + 1) * tile_words);
+    float *yrow = y + (size_t)node * ys;
+    for (int w0 = tile * tile_words; w0 < w_end; w0 += 32) {
+        uint32_t xw[6];
+#pragma unroll
+        for (int j = 0; j < 6; ++j) xw[j] = (w0 + lane < w_end) ? __ldg(rows[j] + w0 + lane) : 0u;
+        const int kn = min(32, w_end - w0);
+        for (int k = 0; k < kn; ++k) {
+            uint32_t p = 0;
+#pragma unroll
+            for (int j = 5; j >= 0; --j) p = (p << 1) | ((__shfl_sync(kFull, xw[j], k) >> lane) & 1u);
+            const long long f = (long long)(w0 + k) * 32 + lane;
+            if (f < F) yrow[f] = val[p];
+        }
+    }
+}
+
 struct Scratch {
     float    *Y;        // [O][64]
     uint32_t *hist;     // [O][64]
@@ -233,6 +271,26 @@ int dl6_bit_forward_training_by_table(const int *x, int *y, const int *idx, cons
     k_dl6_bit_train_finalize<<<groups, kWarpsPerCta * 32, 0, st>>>(s.Y, s.hist, s.table, mean, rstd, rmean, rvar, gamma, beta, momentum, O, F);
     BB200_CUDA(cudaPeekAtLastError());
     return run_binary_lut(x, y, idx, s.table, O, F, stride, st);
+}
+
+// StochasticLut6 bit -> fp32 forward.
+int bit_fp32_forward_by_table(const int *x, float *y, const int *idx, const float *W, float bias, int O, int F, long long xs, long long ys,
+                              int lut_binarize, cudaStream_t st)
+{
+    if (O == 0 || F == 0) return BBCU_OK;
+    Scratch s;
+    if (!carve(s, O, st)) return BBCU_ERR_NO_MEMORY;
+    const int groups = (O + kWarpsPerCta - 1) / kWarpsPerCta;
+    k_pattern_values<kTableNone><<<groups, kWarpsPerCta * 32, 0, st>>>(W, s.Y, nullptr, nullptr, nullptr, 0.0f, 0.0f, bias, O, lut_binarize);
+    BB200_CUDA(cudaPeekAtLastError());
+    // frame tiles as in the other LUT kernels: the tile's input rows stay in L2 while all nodes consume them
+    const int tf = frame_tile(3LL * O, 1, groups, F, 1 << 20);
+    const int tile_words = ((tf + 1023) / 1024) * 32;
+    const long long blocks = (long long)groups * (((F + 31) / 32 + tile_words - 1) / tile_words);
+    BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+    k_bit_gather_forward<<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(reinterpret_cast<const uint32_t *>(x), y, idx, s.Y, O, F, xs, ys, groups,
+                                                                        tile_words);
+    return launch_status();
 }
 
 }   // namespace bb200

@@ -52,6 +52,9 @@ int dl6_bit_forward_training_by_table(const int *x, int *y, const int *idx, cons
                                       float gamma, float beta, float momentum, float bias, int O, int F, int stride, int lut_binarize,
                                       cudaStream_t st);
 
+int bit_fp32_forward_by_table(const int *x, float *y, const int *idx, const float *W, float bias, int O, int F, long long xs, long long ys,
+                              int lut_binarize, cudaStream_t st);
+
 // Per-device int in global memory (zero until a kernel records a fault); allocated once, never freed.
 int *fault_word();
 

@@ -823,6 +823,10 @@ extern "C" int bbcu_bit_fp32_StochasticLut6_Forward(const int *x, float *y, cons
     int rc = check_common(x, y, idx, W, node_size, frame_size, frame_stride);
     if (rc) return rc;
     BB200_REQUIRE(frame_stride >= frame_size && (long long)bin_frame_stride * 32 >= frame_size, BBCU_ERR_BAD_STRIDE);
+    // bit inputs: the node's value is one of 64 per-pattern values, looked up per frame
+    rc = bit_fp32_forward_by_table(x, y, idx, W, unbinarize_bias, node_size, frame_size, bin_frame_stride, frame_stride, lut_binarize,
+                                   as_stream(stream));
+    if (rc != BBCU_ERR_NO_MEMORY) return rc;
     return forward_plain<true>(x, y, nullptr, idx, W, node_size, frame_size, bin_frame_stride, frame_stride, 1, lut_binarize,
                                unbinarize_bias, as_stream(stream));
 }
