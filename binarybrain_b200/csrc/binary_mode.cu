@@ -203,6 +203,162 @@ k_bit_gather_forward(const uint32_t *__restrict__ x, float *__restrict__ y, cons
     }
 }
 
+// --------------------------------------------------------------------------------------------- backward of bit-input layers
+// With bit inputs the backward pass also factors through the pattern p of a frame:
+//   dx_j(f) = g(f) * D_j[p(f)]          D_j[p] = dy/du_j at pattern p, six values per pattern and node
+//   dW      = K^T Hg                    Hg[p] = sum of g over the frames with pattern p; K[i][p] = prod_j k(bit_j(i), bit_j(p)),
+//                                        k = 0.5 + bias where the bits agree, 0.5 - bias where they differ (one butterfly per input)
+// and for the batch-norm form g(f) = mask[p] dy(f) gamma rstd + dmean + Y[p] dvar / F, so Hg and the two batch sums
+// (include/bb/DifferentiableLutN.h:1190-1258) follow from Hdy[p] = sum of dy per pattern and the pattern counts H[p].
+// Per frame that leaves: the pattern (6 shuffles, ~18 integer ops), 6 table reads, 6 multiplies and the 6 dx reductions.
+
+enum { kBwdPlainAll = 0, kBwdHistOnly = 1, kBwdNormDx = 2 };
+
+struct BitBwdArgs {
+    const uint32_t *x;
+    const float *dy;
+    float *dx;
+    const int *idx;
+    const float *W;
+    float *hdy;                         // [O][64] per-pattern sums of dy (added to)
+    const float *mean, *rstd, *dmean, *dvar;
+    float gamma, beta, bias, rF;
+    int O, F, groups, tile_words, lut_binarize;
+    long long xs, fs;                   // word stride of x, float stride of dy / dx
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+k_bit_backward_frames(const BitBwdArgs a)
+{
+    __shared__ float4 s_tab[kWarpsPerCta][16];
+    __shared__ float s_D[kWarpsPerCta][6][64];
+    __shared__ float s_A[kWarpsPerCta][64], s_B[kWarpsPerCta][64], s_H[kWarpsPerCta][64];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x / a.groups;
+    const int node = (blockIdx.x % a.groups) * kWarpsPerCta + warp;
+    if (node >= a.O) return;
+    // the node's per-pattern tables: this lane works out patterns `lane` and `lane + 32`
+    stage_table_halves(s_tab[warp], a.W, node, lane, a.lut_binarize);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int p = lane + 32 * half;
+        float u[6];
+#pragma unroll
+        for (int j = 0; j < 6; ++j) u[j] = ((p >> j) & 1) ? a.bias : -a.bias;
+        KeptHalves K;
+        const float v = lut6_forward_keep_halves(s_tab[warp], u, K);
+        if (MODE != kBwdHistOnly) {
+            f32x2 unused[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) unused[i] = 0ull;
+            float d[6];
+            lut6_reverse_halves(s_tab[warp], u, K, 1.0f, unused, d);
+#pragma unroll
+            for (int j = 0; j < 6; ++j) s_D[warp][j][p] = d[j];
+        }
+        if (MODE == kBwdNormDx) {
+            const float mean = a.mean[node], rstd = a.rstd[node];
+            const float tanh_x = ((v - mean) * rstd) * a.gamma + a.beta;
+            s_A[warp][p] = (tanh_x <= 0.0f || tanh_x >= 1.0f) ? 0.0f : 1.0f;              // hard-tanh mask of the pattern
+            s_B[warp][p] = a.dmean[node] + (v * a.dvar[node] * a.rF);
+        }
+        if (MODE != kBwdNormDx) s_H[warp][p] = 0.0f;
+    }
+    __syncwarp();
+    const float grstd_gamma = a.gamma, rstd_n = (MODE == kBwdNormDx) ? a.rstd[node] : 0.0f;
+
+    const uint32_t *rows[6];
+    long long off[6];
+#pragma unroll
+    for (int j = 0; j < 6; ++j) {
+        const int r = __ldg(a.idx + (size_t)node * 6 + j);
+        rows[j] = a.x + (size_t)r * a.xs;
+        off[j] = (long long)r * a.fs;
+    }
+    const int words = (a.F + 31) >> 5;
+    const int w_end = min(words, (tile + 1) * a.tile_words);
+    const float *dyrow = a.dy + (size_t)node * a.fs;
+    for (int w0 = tile * a.tile_words; w0 < w_end; w0 += 32) {
+        uint32_t xw[6];
+#pragma unroll
+        for (int j = 0; j < 6; ++j) xw[j] = (w0 + lane < w_end) ? __ldg(rows[j] + w0 + lane) : 0u;
+        const int kn = min(32, w_end - w0);
+        for (int k = 0; k < kn; ++k) {
+            uint32_t p = 0;
+#pragma unroll
+            for (int j = 5; j >= 0; --j) p = (p << 1) | ((__shfl_sync(kFull, xw[j], k) >> lane) & 1u);
+            const long long f = (long long)(w0 + k) * 32 + lane;
+            if (f < a.F) {
+                const float dyv = __ldg(dyrow + f);
+                if (MODE != kBwdNormDx) atomicAdd(&s_H[warp][p], dyv);
+                if (MODE != kBwdHistOnly) {
+                    float g = dyv;
+                    if (MODE == kBwdNormDx) g = ((dyv * s_A[warp][p]) * grstd_gamma) * rstd_n + s_B[warp][p];
+                    float *dxf = a.dx + f;
+#pragma unroll
+                    for (int j = 0; j < 6; ++j) atomicAdd(dxf + off[j], g * s_D[warp][j][p]);
+                }
+            }
+        }
+    }
+    if (MODE != kBwdNormDx) {
+        __syncwarp();
+        atomicAdd(a.hdy + (size_t)node * 64 + lane, s_H[warp][lane]);
+        atomicAdd(a.hdy + (size_t)node * 64 + 32 + lane, s_H[warp][lane + 32]);
+    }
+}
+
+// Per-pattern gradient sums -> table-entry gradients: for every input, (a, b) -> (a hi + b lo, a lo + b hi) with hi = 0.5 + bias,
+// lo = 0.5 - bias.  Lane l holds patterns 2l and 2l + 1 on entry and table entries 2l and 2l + 1 on return.
+__device__ __forceinline__ float2 pattern_sums_to_table_grads(float2 v, int lane, float bias)
+{
+    const float hi = 0.5f + bias, lo = 0.5f - bias;
+    v = make_float2(v.x * hi + v.y * lo, v.x * lo + v.y * hi);
+#pragma unroll
+    for (int b = 0; b < 5; ++b) {
+        const float tx = __shfl_xor_sync(kFull, v.x, 1 << b), ty = __shfl_xor_sync(kFull, v.y, 1 << b);
+        v.x = v.x * hi + tx * lo;
+        v.y = v.y * hi + ty * lo;
+    }
+    return v;
+}
+
+// One warp per node.  BN = false: dW += K^T Hdy.  BN = true: the batch sums, dmean / dvar, then dW += K^T Hg with
+// Hg[p] = mask[p] gamma rstd Hdy[p] + (dmean + Y[p] dvar / F) H[p].
+template <bool BN>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+k_bit_backward_finalize(const float *__restrict__ hdy, const uint32_t *__restrict__ hist, const float *__restrict__ Y, float *dW,
+                        const float *__restrict__ mean_buf, const float *__restrict__ rstd_buf, float *dmean_out, float *dvar_out, float gamma,
+                        float beta, float bias, int O, int F)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int node = blockIdx.x * kWarpsPerCta + warp;
+    if (node >= O) return;
+    float2 hg = reinterpret_cast<const float2 *>(hdy + (size_t)node * 64)[lane];             // patterns 2l, 2l + 1
+    if (BN) {
+        const float2 y = reinterpret_cast<const float2 *>(Y + (size_t)node * 64)[lane];
+        const uint2 h = reinterpret_cast<const uint2 *>(hist + (size_t)node * 64)[lane];
+        const float mean = mean_buf[node], rstd = rstd_buf[node], rstd2 = rstd * rstd, rF = 1.0f / (float)F;
+        const float t0 = ((y.x - mean) * rstd) * gamma + beta, t1 = ((y.y - mean) * rstd) * gamma + beta;
+        const float m0 = (t0 <= 0.0f || t0 >= 1.0f) ? 0.0f : 1.0f, m1 = (t1 <= 0.0f || t1 >= 1.0f) ? 0.0f : 1.0f;
+        const float dxn0 = gamma * (m0 * hg.x), dxn1 = gamma * (m1 * hg.y);                   // sum over the pattern's frames of gamma * masked dy
+        double dstd = -((double)(dxn0 * (y.x - mean) * rstd2) + (double)(dxn1 * (y.y - mean) * rstd2));
+        double dmeanx = -((double)(dxn0 * rstd) + (double)(dxn1 * rstd));
+        dstd = warp_sum(dstd);
+        dmeanx = warp_sum(dmeanx);
+        const float dvar = (float)dstd * rstd;
+        const float dmean = ((float)dmeanx - (mean * dvar)) * rF;
+        if (lane == 0) { dvar_out[node] = dvar; dmean_out[node] = dmean; }
+        hg.x = (dxn0 * rstd) + (dmean + (y.x * dvar * rF)) * (float)h.x;
+        hg.y = (dxn1 * rstd) + (dmean + (y.y * dvar * rF)) * (float)h.y;
+    }
+    const float2 gw = pattern_sums_to_table_grads(hg, lane, bias);
+    float *dst = dW + (size_t)node * 64 + 2 * lane;
+    dst[0] += gw.x;
+    dst[1] += gw.y;
+}
+
 struct Scratch {
     float    *Y;        // [O][64]
     uint32_t *hist;     // [O][64]
@@ -211,12 +367,12 @@ struct Scratch {
 
 bool carve(Scratch &s, int O, cudaStream_t st)
 {
-    const size_t per_node = 64 * 4 + 64 * 4 + 8;
+    const size_t per_node = 64 * 4 + 64 * 4 + 8 + 64 * 4;        // Y, pattern counts, truth table, per-pattern dy sums
     unsigned char *base = static_cast<unsigned char *>(stream_scratch(st, per_node * (size_t)O, 1));
     if (base == nullptr) return false;
     s.Y = reinterpret_cast<float *>(base);
     s.hist = reinterpret_cast<uint32_t *>(base + (size_t)O * 256);
-    s.table = reinterpret_cast<int *>(base + (size_t)O * 512);
+    s.table = reinterpret_cast<int *>(base + (size_t)O * 768);
     return true;
 }
 
@@ -290,6 +446,53 @@ int bit_fp32_forward_by_table(const int *x, float *y, const int *idx, const floa
     BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
     k_bit_gather_forward<<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(reinterpret_cast<const uint32_t *>(x), y, idx, s.Y, O, F, xs, ys, groups,
                                                                         tile_words);
+    return launch_status();
+}
+
+// Backward of the bit-input layers (StochasticLut6: bn = false; DifferentiableLut6: bn = true).  dx must be zero on entry.
+int bit_backward_by_table(bool bn, const int *x, const float *dy, float *dx, const int *idx, const float *W, float *dW, const float *mean,
+                          const float *rstd, float *dmean_out, float *dvar_out, float gamma, float beta, float bias, int O, int F, long long xs,
+                          long long fs, int lut_binarize, cudaStream_t st)
+{
+    if (O == 0 || F == 0) return BBCU_OK;
+    Scratch s;
+    if (!carve(s, O, st)) return BBCU_ERR_NO_MEMORY;
+    float *hdy = reinterpret_cast<float *>(s.hist) + (size_t)O * 64;       // the block between the pattern counts and the truth tables
+    BitBwdArgs a = {};
+    a.x = reinterpret_cast<const uint32_t *>(x); a.dy = dy; a.dx = dx; a.idx = idx; a.W = W; a.hdy = hdy;
+    a.mean = mean; a.rstd = rstd; a.dmean = dmean_out; a.dvar = dvar_out;
+    a.gamma = gamma; a.beta = beta; a.bias = bias; a.rF = 1.0f / (float)F;
+    a.O = O; a.F = F; a.xs = xs; a.fs = fs; a.lut_binarize = lut_binarize;
+    a.groups = (O + kWarpsPerCta - 1) / kWarpsPerCta;
+    const int words = (F + 31) / 32;
+    // tiles of 4096 frames unless that leaves the GPU short of CTAs (each warp pays ~1000 instructions of table set-up per tile)
+    a.tile_words = 128;
+    while (a.tile_words > 32 && (long long)a.groups * ((words + a.tile_words - 1) / a.tile_words) < 2LL * device_info().sm_count) a.tile_words /= 2;
+    const long long blocks = (long long)a.groups * ((words + a.tile_words - 1) / a.tile_words);
+    BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+    BB200_CUDA(cudaMemsetAsync(hdy, 0, (size_t)O * 256, st));
+    const unsigned nb = (unsigned)blocks, threads = kWarpsPerCta * 32;
+    if (!bn) {
+        k_bit_backward_frames<kBwdPlainAll><<<nb, threads, 0, st>>>(a);
+        BB200_CUDA(cudaPeekAtLastError());
+        k_bit_backward_finalize<false><<<a.groups, threads, 0, st>>>(hdy, nullptr, nullptr, dW, nullptr, nullptr, nullptr, nullptr, 0.0f, 0.0f, bias, O, F);
+        return launch_status();
+    }
+    k_pattern_values<kTableNone><<<a.groups, threads, 0, st>>>(W, s.Y, nullptr, nullptr, nullptr, 0.0f, 0.0f, bias, O, lut_binarize);
+    BB200_CUDA(cudaPeekAtLastError());
+    BB200_CUDA(cudaMemsetAsync(s.hist, 0, (size_t)O * 256, st));
+    {
+        int tw = 4096;
+        while (tw > 32 && (long long)a.groups * ((words + tw - 1) / tw) < 2LL * device_info().sm_count) tw /= 2;
+        const long long hb = (long long)a.groups * ((words + tw - 1) / tw);
+        k_pattern_histogram<<<(unsigned)hb, threads, 0, st>>>(a.x, idx, s.hist, O, F, xs, a.groups, tw);
+        BB200_CUDA(cudaPeekAtLastError());
+    }
+    k_bit_backward_frames<kBwdHistOnly><<<nb, threads, 0, st>>>(a);
+    BB200_CUDA(cudaPeekAtLastError());
+    k_bit_backward_finalize<true><<<a.groups, threads, 0, st>>>(hdy, s.hist, s.Y, dW, mean, rstd, dmean_out, dvar_out, gamma, beta, bias, O, F);
+    BB200_CUDA(cudaPeekAtLastError());
+    k_bit_backward_frames<kBwdNormDx><<<nb, threads, 0, st>>>(a);
     return launch_status();
 }
 

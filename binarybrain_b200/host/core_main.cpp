@@ -6,6 +6,7 @@
 #include <pybind11/stl.h>
 
 #include "bb/LutModels.h"
+#include "bb/ConvModels.h"
 
 namespace py = pybind11;
 using namespace bb;
@@ -17,6 +18,14 @@ using StochasticLut6_bit_fp32      = StochasticLutN<6, Bit, float>;
 using BinaryLut6_bit_fp32          = BinaryLutN<6, Bit, float>;
 using StochasticBatchNormalization_fp32 = StochasticBatchNormalization<float>;
 using OptimizerAdam_fp32           = OptimizerAdam<float>;
+using ConvolutionIm2Col_fp32_fp32   = ConvolutionIm2Col<float, float>;
+using ConvolutionIm2Col_bit_fp32    = ConvolutionIm2Col<Bit, float>;
+using ConvolutionCol2Im_fp32_fp32   = ConvolutionCol2Im<float, float>;
+using ConvolutionCol2Im_bit_fp32    = ConvolutionCol2Im<Bit, float>;
+using MaxPooling_fp32_fp32          = MaxPooling<float, float>;
+using MaxPooling_bit_fp32           = MaxPooling<Bit, float>;
+using Convolution2d_fp32_fp32       = Convolution2d<float, float>;
+using Convolution2d_bit_fp32        = Convolution2d<Bit, float>;
 
 static py::array_t<float> tensor_numpy(Tensor &t)
 {
@@ -164,6 +173,33 @@ PYBIND11_MODULE(core, m)
         .def("reforward", &StochasticBatchNormalization_fp32::ReForward)
         .def("get_mean", [](StochasticBatchNormalization_fp32 &l) -> Tensor & { return l.running_mean(); }, py::return_value_policy::reference_internal)
         .def("get_var", [](StochasticBatchNormalization_fp32 &l) -> Tensor & { return l.running_var(); }, py::return_value_policy::reference_internal);
+
+    // convolution lowering (python/binarybrain/src/core_main.cpp of the reference registers the same names)
+    py::class_<Sequential, Model, std::shared_ptr<Sequential>>(m, "Sequential")
+        .def_static("create", &Sequential::Create)
+        .def("add", &Sequential::Add)
+        .def("get_size", &Sequential::GetSize)
+        .def("get", &Sequential::Get);
+#define BB200_DEF_CONV(FT)                                                                                                                      \
+    py::class_<ConvolutionIm2Col_##FT, Model, std::shared_ptr<ConvolutionIm2Col_##FT>>(m, "ConvolutionIm2Col_" #FT)                              \
+        .def_static("create", [](index_t fh, index_t fw, index_t ys, index_t xs, std::string padding, std::string border) {                     \
+            return ConvolutionIm2Col_##FT::Create(fh, fw, ys, xs, padding, border); },                                                          \
+            py::arg("filter_h_size"), py::arg("filter_w_size"), py::arg("y_stride") = 1, py::arg("x_stride") = 1,                               \
+            py::arg("padding") = "valid", py::arg("border_mode") = "reflect_101");                                                              \
+    py::class_<ConvolutionCol2Im_##FT, Model, std::shared_ptr<ConvolutionCol2Im_##FT>>(m, "ConvolutionCol2Im_" #FT)                              \
+        .def_static("create", [](index_t h, index_t w) { return ConvolutionCol2Im_##FT::Create(h, w); }, py::arg("h_size"), py::arg("w_size")); \
+    py::class_<MaxPooling_##FT, Model, std::shared_ptr<MaxPooling_##FT>>(m, "MaxPooling_" #FT)                                                   \
+        .def_static("create", [](index_t fh, index_t fw) { return MaxPooling_##FT::Create(fh, fw); }, py::arg("filter_h_size"),                 \
+                    py::arg("filter_w_size"));                                                                                                  \
+    py::class_<Convolution2d_##FT, Model, std::shared_ptr<Convolution2d_##FT>>(m, "Convolution2d_" #FT)                                          \
+        .def_static("create", [](std::shared_ptr<Model> layer, index_t fh, index_t fw, index_t ys, index_t xs, std::string padding,             \
+                                 std::string border) { return Convolution2d_##FT::Create(layer, fh, fw, ys, xs, padding, border); },            \
+            py::arg("layer"), py::arg("filter_h_size"), py::arg("filter_w_size"), py::arg("y_stride") = 1, py::arg("x_stride") = 1,             \
+            py::arg("padding") = "valid", py::arg("border_mode") = "reflect_101")                                                               \
+        .def("get_layer", &Convolution2d_##FT::GetLayer);
+    BB200_DEF_CONV(fp32_fp32)
+    BB200_DEF_CONV(bit_fp32)
+#undef BB200_DEF_CONV
 
     py::class_<OptimizerAdam_fp32, std::shared_ptr<OptimizerAdam_fp32>>(m, "OptimizerAdam_fp32")
         .def_static("create", &OptimizerAdam_fp32::Create, py::arg("learning_rate") = 0.001f, py::arg("beta1") = 0.9f, py::arg("beta2") = 0.999f)

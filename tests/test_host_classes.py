@@ -204,3 +204,50 @@ def test_stochastic_layer_sbn_and_adam(core, golden):
     dx = bn.backward(core.FrameBuffer.from_numpy_fp32(g)).numpy_fp32()
     assert np.abs(dx.T - port.sbn_backward(a.T.copy(), g.T.copy(), p["mean"], p["rstd"])).max() <= 2e-5
     assert np.abs(bn.get_mean().numpy() - p["running_mean"]).max() <= 1e-6
+
+
+@pytest.mark.gpu
+def test_convolution2d_and_maxpooling_classes_against_oracle(core):
+    """bb::Convolution2d (Im2Col -> Sequential of two StochasticLut6 layers -> Col2Im) followed by bb::MaxPooling, through the C++
+    host classes; the oracle composes the same operators.  StochasticLut6 (no batch norm) keeps the comparison well conditioned."""
+    from oracle import unpack_bits
+    rng = np.random.default_rng(9)
+    c, h, w, B = 3, 8, 8, 5
+    seq = core.Sequential.create()
+    l1 = core.StochasticLut6_fp32_fp32.create([24])
+    l2 = core.StochasticLut6_fp32_fp32.create([8])
+    for layer in (l1, l2):
+        layer.send_command("lut_binarize false")
+        seq.add(layer)
+    conv = core.Convolution2d_fp32_fp32.create(seq, 3, 3, padding="same")
+    pool = core.MaxPooling_fp32_fp32.create(2, 2)
+    assert conv.set_input_shape([c, h, w]) == [8, h, w]
+    assert pool.set_input_shape([8, h, w]) == [8, 4, 4]
+    W1 = np.clip(rng.normal(0.5, 0.25, (24, 64)), 0, 1).astype(np.float32)
+    W2 = np.clip(rng.normal(0.5, 0.25, (8, 64)), 0, 1).astype(np.float32)
+    l1.W().set_numpy(W1)
+    l2.W().set_numpy(W2)
+    idx1, idx2 = l1.get_connection(), l2.get_connection()
+    x = rng.random((B, c * h * w), dtype=np.float32)
+    y = pool.forward(conv.forward(core.FrameBuffer.from_numpy_fp32(x.reshape(B, c, h, w)), True), True).numpy_fp32()
+    cols = port.im2col_forward(x.T.copy(), c, h, w, 3, 3, padding="same")
+    h1 = port.sl6_forward(cols, idx1, W1)
+    h2 = port.sl6_forward(h1, idx2, W2)
+    img = port.col2im_forward(h2, 8, h, w, B)
+    y_w, am = port.maxpool_forward(img, 8, h, w, 2, 2)
+    assert np.abs(y.reshape(B, -1).T - y_w).max() <= 1e-5
+    dy = rng.random((B, 8 * 4 * 4), dtype=np.float32)
+    dx = conv.backward(pool.backward(core.FrameBuffer.from_numpy_fp32(dy.reshape(B, 8, 4, 4)))).numpy_fp32()
+    g = port.col2im_backward(port.maxpool_backward(am, dy.T.copy(), 8, h, w, 2, 2), 8, h, w)
+    g1, dW2 = port.sl6_backward(h1, g, idx2, W2, 24)
+    g0, dW1 = port.sl6_backward(cols, g1, idx1, W1, 27)
+    dx_w = port.im2col_backward(g0, c, h, w, 3, 3, padding="same")
+    assert np.abs(dx.reshape(B, -1).T - dx_w).max() <= 1e-5 * max(1.0, np.abs(dx_w).max())
+    assert np.abs(l1.dW().numpy() - dW1).max() <= 1e-5 * max(1.0, np.abs(dW1).max())
+    assert np.abs(l2.dW().numpy() - dW2).max() <= 1e-5 * max(1.0, np.abs(dW2).max())
+    # bit frames: 2x2 pooling is an OR
+    xb = (rng.random((B, c * h * w)) > 0.7).astype(np.float32)
+    pb = core.MaxPooling_bit_fp32.create(2, 2)
+    yb = pb.forward(core.FrameBuffer.from_numpy_fp32(xb.reshape(B, c, h, w), core.TYPE_BIT), True).numpy_fp32()
+    want = unpack_bits(port.maxpool_forward(pack_bits(xb.T), c, h, w, 2, 2, frames=B), B)
+    assert np.array_equal(yb.reshape(B, -1).T > 0.5, want.astype(bool))
