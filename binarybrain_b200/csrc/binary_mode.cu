@@ -227,8 +227,10 @@ struct BitBwdArgs {
     long long xs, fs;                   // word stride of x, float stride of dy / dx
 };
 
+// Four CTAs per SM (64 registers): the frame loop needs few registers and hides its load latency with warps; the table set-up at the
+// top, which would like ~130, runs once per tile and may spill.
 template <int MODE>
-__global__ void __launch_bounds__(kWarpsPerCta * 32)
+__global__ void __launch_bounds__(kWarpsPerCta * 32, 4)
 k_bit_backward_frames(const BitBwdArgs a)
 {
     __shared__ float4 s_tab[kWarpsPerCta][16];
@@ -284,13 +286,16 @@ k_bit_backward_frames(const BitBwdArgs a)
 #pragma unroll
         for (int j = 0; j < 6; ++j) xw[j] = (w0 + lane < w_end) ? __ldg(rows[j] + w0 + lane) : 0u;
         const int kn = min(32, w_end - w0);
-        for (int k = 0; k < kn; ++k) {
+        // dy of the next word is fetched while this one is processed
+        long long f = (long long)w0 * 32 + lane;
+        float dy_next = f < a.F ? __ldg(dyrow + f) : 0.0f;
+        for (int k = 0; k < kn; ++k, f += 32) {
             uint32_t p = 0;
 #pragma unroll
             for (int j = 5; j >= 0; --j) p = (p << 1) | ((__shfl_sync(kFull, xw[j], k) >> lane) & 1u);
-            const long long f = (long long)(w0 + k) * 32 + lane;
+            const float dyv = dy_next;
+            if (k + 1 < kn && f + 32 < a.F) dy_next = __ldg(dyrow + f + 32);
             if (f < a.F) {
-                const float dyv = __ldg(dyrow + f);
                 if (MODE != kBwdNormDx) atomicAdd(&s_H[warp][p], dyv);
                 if (MODE != kBwdHistOnly) {
                     float g = dyv;
