@@ -442,10 +442,18 @@ k_bn_normalize_inplace(float *y, const float *__restrict__ mean_buf, const float
     const int f1 = min(F, f0 + 4096);
     const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15) == 0);
     if (vec) {
-        for (int f = f0 + threadIdx.x * 4; f < f1; f += 1024) {
+        // all four 128-bit loads of a thread are in flight before the first store (16 KiB per CTA)
+        float4 v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int f = f0 + threadIdx.x * 4 + 1024 * k;
+            if (f + 3 < f1) v[k] = *reinterpret_cast<const float4 *>(row + f);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int f = f0 + threadIdx.x * 4 + 1024 * k;
             if (f + 3 < f1) {
-                float4 v = *reinterpret_cast<float4 *>(row + f);
-                float o[4] = {v.x, v.y, v.z, v.w};
+                float o[4] = {v[k].x, v[k].y, v[k].z, v[k].w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     float t = (o[i] - mean) * rstd;
