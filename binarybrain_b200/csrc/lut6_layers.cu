@@ -199,7 +199,11 @@ k_lut6_forward(const FwdArgs a)
 // still being read while the copies of item j+2 are started.  Without the scratch table (a.coef == nullptr) the raw
 // entries are copied instead and converted in place.
 // ---------------------------------------------------------------------------------------------
-constexpr int kFpMaxItemFrames = 256;
+#ifndef BB200_FWD_ITEM
+#define BB200_FWD_ITEM 256
+#endif
+constexpr int kFpMaxItemFrames = BB200_FWD_ITEM;
+constexpr int kFpCtas          = BB200_FWD_ITEM == 128 ? 3 : 2;
 constexpr int kFpStages        = 2;
 constexpr int kFpStageBytes    = 6 * kFpMaxItemFrames * 4;                             // six row segments
 constexpr int kFpRowsBytes     = kWarpsPerCta * kFpStages * kFpStageBytes;
@@ -209,7 +213,7 @@ constexpr int kFpTabSlotBytes  = 32 * 16;
 constexpr int kFpTabBytes      = kWarpsPerCta * kFpTabSlots * kFpTabSlotBytes;
 constexpr int kFpSmem          = kFpRowsBytes + kFpBarBytes + kFpTabBytes;
 static_assert(kWarpsPerCta * kFpStages * 8 <= kFpBarBytes, "barrier block too small");
-static_assert(2 * (kFpSmem + 1024) <= 227 * 1024, "two CTAs per SM must fit");
+static_assert(kFpCtas * (kFpSmem + 1024) <= 227 * 1024, "the CTAs of one SM must fit");
 
 // Position of a work item, advanced incrementally (item index + gridDim) so that no division runs per item.
 struct FpPos {
@@ -265,7 +269,7 @@ k_table_coeffs(const float *__restrict__ W, float4 *__restrict__ coef, int O, in
 }
 
 template <int PHASE, bool BINARY>            // BINARY: the layer's binary mode, compiled in so that input conditioning is one instruction
-__global__ void __launch_bounds__(kWarpsPerCta * 32, 2)
+__global__ void __launch_bounds__(kWarpsPerCta * 32, kFpCtas)
 k_lut6_forward_pipe(const FwdArgs a, int n_tiles, int *fault)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -397,8 +401,8 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles, int *fault)
                 }
             }
         };
-        if (nf > kFramesPerIter) walk(std::integral_constant<int, 4>());
-        else                     walk(std::integral_constant<int, 2>());
+        if (kFpMaxItemFrames > kFramesPerIter && nf > kFramesPerIter) walk(std::integral_constant<int, kFpMaxItemFrames / 64>());
+        else                                                          walk(std::integral_constant<int, 2>());
         if (PHASE == PH_STATS && store) {
             s1 = warp_sum(s1);
             s2 = warp_sum(s2);
@@ -737,7 +741,7 @@ static int launch_forward(FwdArgs a, int max_tile, cudaStream_t st)
             a.T = a.F > kFramesPerIter ? kFpMaxItemFrames : kFramesPerIter;
             const long long n_items = (long long)((a.F + a.T - 1) / a.T) * a.groups;
             BB200_REQUIRE(n_items < (1LL << 31) - 4096, BBCU_ERR_TOO_LARGE);      // 32-bit item arithmetic in the kernel
-            long long grid = 2LL * device_info().sm_count;
+            long long grid = (long long)kFpCtas * device_info().sm_count;
             if (grid > n_items) grid = n_items;
             if (!a.no_scratch) {
                 // slot 1 of the stream's scratch: slot 0 may hold the caller's batch-norm sums at the same time
