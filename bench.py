@@ -34,8 +34,8 @@ TRAIN_FRAMES = 4096                  # frames per GPU and step in the training s
 CPU_SAMPLE_FRAMES = 1 << 18          # bounded sample for the CPU legs (the full batch needs 8 GiB of host copies)
 FALLBACK_HBM_GBS = 6650.0            # the pool's earlier measurement, used only when MEASURED_PEAKS.json is absent
 # dram__bytes_read.sum + dram__bytes_write.sum of one k_binary_lut6_pipe launch: ncu on a 131072-frame launch gave
-# 436.2 MB + 244.2 MB (profiles/binary_lut6_16384x16384_131072frames.md); traffic grows with frames, so x8 for 2^20 frames.
-NCU_TRAFFIC_BYTES_PER_FRAME = (436.2e6 + 244.2e6) / 131072
+# 449.7 MB + 244.6 MB (profiles/binary_lut6_16384x16384_131072frames.md); traffic grows with frames, so x8 for 2^20 frames.
+NCU_TRAFFIC_BYTES_PER_FRAME = (449.7e6 + 244.6e6) / 131072
 
 
 def measured_peaks():
