@@ -254,7 +254,7 @@ def build_config3_network(dev, seed=5, ops=None):
     def lut(n_in, n_out):
         idx = torch.rand((n_out, n_in), device=dev, generator=g).argsort(dim=1)[:, :6].to(torch.int32).contiguous()
         W = (torch.randn((n_out, 64), device=dev, generator=g) * 0.01 + 0.5).clamp_(0, 1)
-        return ShardedDifferentiableLut6(idx, W, n_in, ops=ops, binary=False)
+        return ShardedDifferentiableLut6(idx, W, n_in, ops=ops, binary=False, sharded=False)       # runs on one rank only: no collectives
 
     def conv(c, hw, widths):
         return Convolution2d([lut(a, b) for a, b in zip(widths[:-1], widths[1:])], c, hw, hw, 3, 3, padding="same", ops=ops)

@@ -32,11 +32,12 @@ def frame_shard(total_frames, rank, world, align=32):
 class ShardedDifferentiableLut6:
     """One DifferentiableLut6 layer (fp32, batch norm on) whose frames are sharded over the ranks of `group`."""
 
-    def __init__(self, idx, W, n_in, ops=None, group=None, gamma=0.3, beta=0.5, momentum=0.9, binary=False, lut_binarize=False):
+    def __init__(self, idx, W, n_in, ops=None, group=None, gamma=0.3, beta=0.5, momentum=0.9, binary=False, lut_binarize=False, sharded=True):
         if ops is None:
             from . import ops as cuda_ops          # the CUDA operators; there is no CPU fallback behind them
             ops = cuda_ops
         self.ops, self.group = ops, group
+        self.sharded = sharded          # False: a purely local layer that never enters a collective, whatever process group exists
         self.idx, self.W, self.n_in = idx, W, n_in
         self.n_out = idx.shape[0]
         dev = W.device
@@ -52,6 +53,8 @@ class ShardedDifferentiableLut6:
 
     @property
     def world(self):
+        if not self.sharded:
+            return 1
         return dist.get_world_size(self.group) if dist.is_available() and dist.is_initialized() else 1
 
     def _allreduce(self, t, async_op=False):

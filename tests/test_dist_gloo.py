@@ -132,3 +132,32 @@ def test_two_ranks_equal_one_rank(tmp_path):
         assert np.abs(r["dW"] - dW_w).max() <= 1e-4 * amp * max(1.0, np.abs(dW_w).max())
     assert np.abs(y - p["y"]).max() <= 1e-4 * amp
     assert np.abs(dx - dx_w).max() <= 1e-4 * amp * max(1.0, np.abs(dx_w).max())
+
+
+def _local_worker(rank, world, port_no, out):
+    """Rank 0 alone runs a layer marked sharded=False while a 2-rank group exists; rank 1 goes straight to the barrier.  A layer
+    that entered a collective here would leave rank 0 waiting for a partner that never comes (the group's timeout is 20 s)."""
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port_no)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    from binarybrain_b200.dist import ShardedDifferentiableLut6
+    if rank == 0:
+        I, O, F, idx, W, x, dy = _case()
+        layer = ShardedDifferentiableLut6(torch.from_numpy(idx), torch.from_numpy(W), I, ops=HostOps(), binary=False, sharded=False)
+        assert layer.world == 1
+        y = layer.forward(torch.from_numpy(x.copy()), F, F)
+        layer.backward(torch.from_numpy(dy.copy()))
+        np.savez(out.format(rank), y=y.numpy(), dW=layer.wait_grad().numpy())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_unsharded_layer_on_one_rank_enters_no_collective(tmp_path):
+    from oracle import port
+    I, O, F, idx, W, x, dy = _case()
+    out = str(tmp_path / "l{}.npz")
+    mp.spawn(_local_worker, args=(2, 31000 + os.getpid() % 2000, out), nprocs=2, join=True)
+    p = port.dl6_forward_train(x, idx, W, np.zeros(O), np.ones(O), binary=0)
+    r = np.load(out.format(0))
+    assert np.abs(r["y"] - p["y"]).max() <= 1e-4 * max(1.0, 0.3 * float(p["rstd"].max()))
