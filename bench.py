@@ -414,7 +414,9 @@ def main():
         if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
             os.environ["NCCL_DEBUG"] = "WARN"          # keep NCCL's version banner off stdout: stdout carries exactly one JSON line
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import datetime
+        # a collective that is not matched on every rank fails after three minutes instead of holding the GPUs for NCCL's default ten
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=180))
     if args.fp32_only:
         print(json.dumps({"fp32": fp32_section(torch, ops, max(1, args.steps))}))
         return 0
