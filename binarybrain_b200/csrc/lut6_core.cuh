@@ -137,20 +137,20 @@ __device__ __forceinline__ void stage_table_x2(float4 *tab, const float *__restr
 }
 
 template <int L, int K, int NP>
-struct LerpTree {
+struct PolyTree {
     // value of node K at level L for NP frame pairs; x[j][p] is input j of pair p
     static __device__ __forceinline__ void eval(const float4 *tab, const f32x2 (&x)[6][NP], f32x2 (&out)[NP])
     {
         f32x2 a[NP], b[NP];
-        LerpTree<L - 1, 2 * K, NP>::eval(tab, x, a);
-        LerpTree<L - 1, 2 * K + 1, NP>::eval(tab, x, b);
+        PolyTree<L - 1, 2 * K, NP>::eval(tab, x, a);
+        PolyTree<L - 1, 2 * K + 1, NP>::eval(tab, x, b);
 #pragma unroll
         for (int p = 0; p < NP; ++p) out[p] = fma2(x[L - 1][p], b[p], a[p]);
     }
 };
 
 template <int K, int NP>
-struct LerpTree<1, K, NP> {
+struct PolyTree<1, K, NP> {
     static __device__ __forceinline__ void eval(const float4 *tab, const f32x2 (&x)[6][NP], f32x2 (&out)[NP])
     {
         const ulonglong2 wd = *reinterpret_cast<const ulonglong2 *>(tab + K);     // .x = (c0, c0), .y = (c1, c1)
@@ -162,7 +162,7 @@ struct LerpTree<1, K, NP> {
 template <int NP>
 __device__ __forceinline__ void lut6_forward_x2(const float4 *tab, const f32x2 (&x)[6][NP], f32x2 (&y)[NP])
 {
-    LerpTree<6, 0, NP>::eval(tab, x, y);
+    PolyTree<6, 0, NP>::eval(tab, x, y);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -171,7 +171,7 @@ __device__ __forceinline__ void lut6_forward_x2(const float4 *tab, const f32x2 (
 // packed FMAs together, and y = half0 + u5 * half1.  The reverse pass has the same shape (the gradient of half 1 is
 // g * u5), and the 64 accumulators become 32 packed ones: acc2[i] = (dC[i], dC[i + 32]).  This halves the issue slots
 // of the backward pass without adding a single live register, unlike packing two FRAMES, which doubles the kept state.
-// The arithmetic per half is that of the frame-pair walk (LerpTree), operation for operation, so the forward and the backward
+// The arithmetic per half is that of the frame-pair walk (PolyTree), operation for operation, so the forward and the backward
 // kernels see bit-identical LUT values.
 // ---------------------------------------------------------------------------------------------------
 
