@@ -133,6 +133,32 @@ def cpu_reference_leg(steps, warmup, frames=CPU_SAMPLE_FRAMES):
                       f"{'bb::BinaryLutN<6,Bit>::Forward AVX2+OpenMP' if use_ref else 'C port, OpenMP'}"}, per_step
 
 
+def fp32_cpu_reference(nodes=8192):
+    """The reference's own CPU code (oracle/_ref: AVX2 + OpenMP StochasticLutN, scalar DifferentiableLutN whose backward is serial) on
+    the fp32 operators, same node count, at a reduced frame count (stated in the result; never extrapolated)."""
+    import numpy as np
+    import oracle
+    ref = oracle.ref
+    if not ref.available():
+        return None
+    rng = np.random.default_rng(7)
+    idx = np.stack([rng.permutation(nodes)[:6] for _ in range(nodes)]).astype(np.int32)
+    W = np.clip(rng.normal(0.5, 0.01, (nodes, 64)), 0, 1).astype(np.float32)
+    out = {"cores": ref.num_threads(), "kind": "reference", "unit": "node-frames/s"}
+    F = 1024
+    x, dy = rng.random((nodes, F), dtype=np.float32), rng.random((nodes, F), dtype=np.float32)
+    r = ref.stochastic_lut6(x, idx, W, dy=dy)                        # warm-up (first-touch of the buffers, OpenMP team start)
+    r = ref.stochastic_lut6(x, idx, W, dy=dy)
+    out["sl6_forward"] = {"value": nodes * F / r["t_fwd"], "frames": F}
+    out["sl6_backward"] = {"value": nodes * F / r["t_bwd"], "frames": F}
+    F = 256                                                           # DifferentiableLutN's CPU backward is a serial loop over nodes
+    x, dy = rng.random((nodes, F), dtype=np.float32), rng.random((nodes, F), dtype=np.float32)
+    r = ref.differentiable_lut6(x, idx, W, binary=False, dy=dy)
+    out["dl6_forward_training"] = {"value": nodes * F / r["t_fwd"], "frames": F}
+    out["dl6_backward"] = {"value": nodes * F / r["t_bwd"], "frames": F}
+    return out
+
+
 def fp32_section(torch, ops, steps):
     """SL6 / DL6 forward and backward on one 8192 -> 8192 node layer, 16384 frames (x, y, dy, dx: 512 MiB each, > L2)."""
     I = O = 8192
@@ -505,6 +531,7 @@ def main():
             line["operators"] = operators_section(torch, ops, max(3, min(args.steps, 10)))
             if world == 1:
                 line["cpu_baseline"], _ = cpu_reference_leg(3, 1)
+                line["fp32"]["cpu_baseline"] = fp32_cpu_reference()
     if dist:
         dist.barrier()
         dist.destroy_process_group()
