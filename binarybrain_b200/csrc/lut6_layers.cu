@@ -7,8 +7,9 @@
 // which the reference's old CUDA kernels do (cuda/StochasticLut.cuh:191-193,430-470) and its CPU code does not.
 //
 // Schedule: a CTA is 8 warps = 8 consecutive output nodes working on one frame tile; consecutive CTAs
-// walk the node groups of the SAME frame tile, so the input rows of that tile are fetched from HBM once
-// and then hit in L2 for the other ~5 nodes that read them.
+// walk the node groups of the SAME frame tile, so in the forward kernels the input rows of that tile are fetched
+// from HBM once or twice and otherwise hit in L2 for the other nodes that read them.
+// Bit-input operators go through per-node pattern tables instead (binary_mode.cu); the kernels here are their fallback.
 #include <type_traits>
 
 #include "common.cuh"
@@ -605,8 +606,9 @@ __global__ void k_bn_backward_finalize(const double *__restrict__ sums, const fl
 }
 
 // dW / dx.  BN = true folds the batch-norm backward (DifferentiableLutN.h:1225-1258) in front of the LUT's.
-// dx rows must be zero on entry: every node adds its six input gradients with red.global.add.f32, which
-// resolve in L2 where the tile's dx rows are resident.
+// dx rows must be zero on entry: every node adds its six input gradients with red.global.add.f32.  With the wide (4096-frame)
+// tiles used for the sake of the dW accumulators the tile's dx rows no longer all stay in L2 (ncu: 20 % hit rate), which measured
+// cheaper than reducing the 64 accumulators more often.
 template <bool XBIT, bool BN>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, 1)
 k_lut6_backward(const BwdArgs a)
