@@ -13,6 +13,7 @@
 #include <string>
 
 #include "Memory.h"
+#include "Serialize.h"
 
 namespace bb {
 
@@ -92,6 +93,32 @@ public:
     }
     std::int32_t const *LockDeviceMemConst_InputTable() const { return m_table.DevConst(); }
     Tensor_<std::int32_t> &Table() { return m_table; }
+
+    // include/bb/FixedSizeConnectionTable.h:50-61 over include/bb/ConnectionTable.h (shapes) over Object
+    void DumpObject(std::ostream &os, indices_t const &in_shape, indices_t const &out_shape) const
+    {
+        serial::WriteHeader(os, "FixedSizeConnectionTable" + std::to_string(N) + "_int32");
+        serial::Save(os, (std::int64_t)1);
+        serial::Save(os, (std::int64_t)1);
+        serial::Save(os, (std::int64_t)0);
+        serial::SaveShape(os, in_shape);
+        serial::SaveShape(os, out_shape);
+        serial::DumpTypedTensor(os, m_table);
+    }
+    void LoadObject(std::istream &is)
+    {
+        serial::ReadHeader(is, "FixedSizeConnectionTable" + std::to_string(N) + "_int32");
+        serial::ExpectVersion(is, 1, "FixedSizeConnectionTable");
+        serial::ExpectVersion(is, 1, "ConnectionTable");
+        serial::ExpectVersion(is, 0, "Object");
+        indices_t in_shape = serial::LoadShape(is), out_shape = serial::LoadShape(is);
+        m_in = CalcShapeSize(in_shape); m_out = CalcShapeSize(out_shape);
+        serial::LoadTypedTensor(is, m_table);
+        if (m_table.GetShape() != indices_t({m_out, (index_t)N})) throw std::runtime_error("LoadObject: connection table shape");
+        std::int32_t const *t = m_table.HostConst();
+        for (index_t i = 0; i < m_out * N; ++i)
+            if (t[i] < 0 || t[i] >= m_in) throw std::runtime_error("LoadObject: connection index out of range");
+    }
 };
 
 
@@ -103,6 +130,7 @@ class Model
 protected:
     std::vector<FrameBuffer> m_stack;
     bool m_parameter_lock = false;
+    std::string m_name;
 
     static bool EvalBool(std::string const &s) { return s == "true" || s == "True" || s == "TRUE" || s == "1"; }
     virtual void CommandProc(std::vector<std::string> const &args)
@@ -115,6 +143,17 @@ protected:
 public:
     virtual ~Model() {}
     virtual std::string GetModelName() const = 0;
+    virtual std::string GetObjectName() const { return GetModelName(); }
+    void SetName(std::string const &name) { m_name = name; }
+    std::string GetName() const { return m_name.empty() ? GetModelName() : m_name; }
+
+    // Serialisation in the reference's object format (include/bb/Object.h:38-58): layers dumped by BinaryBrain load here and back.
+    virtual void DumpObjectData(std::ostream &) const { throw std::runtime_error(GetModelName() + ": DumpObject is not provided"); }
+    virtual void LoadObjectData(std::istream &)       { throw std::runtime_error(GetModelName() + ": LoadObject is not provided"); }
+    void DumpObject(std::ostream &os) const { serial::WriteHeader(os, GetObjectName()); DumpObjectData(os); }
+    void LoadObject(std::istream &is)       { serial::ReadHeader(is, GetObjectName()); LoadObjectData(is); }
+    std::string DumpObjectBytes() const { std::ostringstream os(std::ios::binary); DumpObject(os); return os.str(); }
+    void LoadObjectBytes(std::string const &bytes) { std::istringstream is(bytes, std::ios::binary); LoadObject(is); }
     virtual indices_t SetInputShape(indices_t shape) = 0;
     virtual indices_t GetInputShape() const = 0;
     virtual indices_t GetOutputShape() const = 0;
@@ -234,7 +273,7 @@ public:
     }
 
     std::string GetModelName() const override { return "DifferentiableLut" + std::to_string(N); }
-    std::string GetObjectName() const { return GetModelName() + "_" + DataType<BinType>::Name() + "_" + DataType<RealType>::Name(); }
+    std::string GetObjectName() const override { return GetModelName() + "_" + DataType<BinType>::Name() + "_" + DataType<RealType>::Name(); }
 
     Tensor &running_mean() { return m_running_mean; }
     Tensor &running_var()  { return m_running_var; }
@@ -242,6 +281,55 @@ public:
     Tensor &tmp_rstd()     { return m_rstd; }
     float GetGamma() const { return m_gamma; }
     float GetBeta()  const { return m_beta; }
+
+    // include/bb/DifferentiableLutN.h:264-330
+    void DumpObjectData(std::ostream &os) const override
+    {
+        serial::Save(os, (std::int64_t)1);
+        serial::SaveModelBase(os, this->m_name);
+        serial::SaveBool(os, false);                         // host_only: there is no host branch here
+        serial::SaveBool(os, this->m_lut_binarize);
+        serial::SaveBool(os, this->m_binary_mode);
+        serial::SaveBool(os, m_batch_norm);
+        serial::SaveBool(os, m_flagClamp);
+        serial::SaveShape(os, this->m_input_shape);
+        serial::SaveShape(os, this->m_output_shape);
+        this->m_connection_table.DumpObject(os, this->m_input_shape, this->m_output_shape);
+        serial::DumpTensor(os, *this->m_W);
+        serial::Save(os, this->m_unbinarize_bias);
+        serial::Save(os, m_momentum);
+        serial::Save(os, m_gamma);
+        serial::Save(os, m_beta);
+        serial::DumpTypedTensor(os, m_running_mean);
+        serial::DumpTypedTensor(os, m_running_var);
+    }
+    void LoadObjectData(std::istream &is) override
+    {
+        serial::ExpectVersion(is, 1, "DifferentiableLutN");
+        this->m_name = serial::LoadModelBase(is);
+        (void)serial::LoadBool(is);                          // host_only
+        this->m_lut_binarize = serial::LoadBool(is);
+        this->m_binary_mode  = serial::LoadBool(is) || kBit;
+        m_batch_norm = serial::LoadBool(is);
+        m_flagClamp  = serial::LoadBool(is);
+        this->m_input_shape  = serial::LoadShape(is);
+        this->m_output_shape = serial::LoadShape(is);
+        this->m_connection_table.LoadObject(is);
+        serial::LoadTensor(is, *this->m_W);
+        serial::Load(is, this->m_unbinarize_bias);
+        serial::Load(is, m_momentum);
+        serial::Load(is, m_gamma);
+        serial::Load(is, m_beta);
+        serial::LoadTypedTensor(is, m_running_mean);
+        serial::LoadTypedTensor(is, m_running_var);
+        index_t O = CalcShapeSize(this->m_output_shape);
+        if (this->m_W->GetShape() != indices_t({O, (index_t)_super::NN}) || m_running_mean.GetSize() != O || m_running_var.GetSize() != O ||
+            this->m_connection_table.GetOutputNodeSize() != O || this->m_connection_table.GetInputNodeSize() != CalcShapeSize(this->m_input_shape))
+            throw std::runtime_error("LoadObject: inconsistent layer shapes");
+        this->m_dW->Resize(this->m_W->GetShape());
+        this->m_dW->FillZero();
+        m_mean.Resize(O); m_rstd.Resize(O);
+    }
 
     indices_t SetInputShape(indices_t shape) override
     {
@@ -386,6 +474,49 @@ public:
         return Create(c);
     }
     std::string GetModelName() const override { return "StochasticLut" + std::to_string(N); }
+    std::string GetObjectName() const override { return GetModelName() + "_" + DataType<BinType>::Name() + "_" + DataType<RealType>::Name(); }
+
+    // include/bb/StochasticLutN.h:170-230
+    void DumpObjectData(std::ostream &os) const override
+    {
+        serial::Save(os, (std::int64_t)1);
+        serial::SaveModelBase(os, this->m_name);
+        serial::SaveBool(os, false);                         // host_only
+        serial::SaveBool(os, true);                          // host_simd (the reference's default; no host branch here)
+        serial::SaveBool(os, this->m_binary_mode);
+        serial::SaveBool(os, this->m_lut_binarize);
+        serial::SaveBool(os, false);                         // y_binarize
+        serial::Save(os, (std::int64_t)(256 * 1024 * 1024)); // max_tmp_mem_size (unused: no dx temporary)
+        serial::SaveString(os, this->m_connection);
+        serial::Save(os, this->m_unbinarize_bias);
+        serial::SaveShape(os, this->m_input_shape);
+        serial::SaveShape(os, this->m_output_shape);
+        this->m_connection_table.DumpObject(os, this->m_input_shape, this->m_output_shape);
+        serial::DumpTensor(os, *this->m_W);
+    }
+    void LoadObjectData(std::istream &is) override
+    {
+        serial::ExpectVersion(is, 1, "StochasticLutN");
+        this->m_name = serial::LoadModelBase(is);
+        (void)serial::LoadBool(is);
+        (void)serial::LoadBool(is);
+        this->m_binary_mode  = serial::LoadBool(is) || kBit;
+        this->m_lut_binarize = serial::LoadBool(is);
+        if (serial::LoadBool(is)) throw std::runtime_error("LoadObject: y_binarize layers are not provided");
+        std::int64_t tmp; serial::Load(is, tmp);
+        this->m_connection = serial::LoadString(is);
+        serial::Load(is, this->m_unbinarize_bias);
+        this->m_input_shape  = serial::LoadShape(is);
+        this->m_output_shape = serial::LoadShape(is);
+        this->m_connection_table.LoadObject(is);
+        serial::LoadTensor(is, *this->m_W);
+        index_t O = CalcShapeSize(this->m_output_shape);
+        if (this->m_W->GetShape() != indices_t({O, (index_t)SparseLutBase<N>::NN}) || this->m_connection_table.GetOutputNodeSize() != O ||
+            this->m_connection_table.GetInputNodeSize() != CalcShapeSize(this->m_input_shape))
+            throw std::runtime_error("LoadObject: inconsistent layer shapes");
+        this->m_dW->Resize(this->m_W->GetShape());
+        this->m_dW->FillZero();
+    }
 
     indices_t SetInputShape(indices_t shape) override
     {
@@ -455,6 +586,7 @@ class BinaryLutN : public Model
     indices_t             m_input_shape, m_output_shape;
     Tensor_<std::int32_t> m_table;          // [node][2]: 64-entry truth table (BinaryLutN.h:43-46)
     Tensor_<std::int32_t> m_input_index;    // [node][6]
+    std::string           m_connection;
     std::mt19937_64       m_mt;
 
 public:
@@ -463,7 +595,7 @@ public:
         std::string   connection;
         std::uint64_t seed = 1;
     };
-    explicit BinaryLutN(create_t const &c) { m_output_shape = c.output_shape; m_mt.seed(c.seed); }
+    explicit BinaryLutN(create_t const &c) { m_output_shape = c.output_shape; m_connection = c.connection; m_mt.seed(c.seed); }
     static std::shared_ptr<BinaryLutN> Create(create_t const &c) { return std::make_shared<BinaryLutN>(c); }
     static std::shared_ptr<BinaryLutN> Create(index_t out, std::uint64_t seed = 1) { create_t c; c.output_shape = {out}; c.seed = seed; return Create(c); }
     static std::shared_ptr<BinaryLutN> CreatePy(indices_t output_shape, std::string connection = "", std::uint64_t seed = 1)
@@ -472,6 +604,38 @@ public:
         return Create(c);
     }
     std::string GetModelName() const override { return "BinaryLut" + std::to_string(N); }
+    std::string GetObjectName() const override { return GetModelName() + "_" + DataType<FT>::Name() + "_" + DataType<BT>::Name(); }
+
+    // include/bb/BinaryLutN.h:481-520
+    void DumpObjectData(std::ostream &os) const override
+    {
+        serial::Save(os, (std::int64_t)1);
+        serial::SaveModelBase(os, this->m_name);
+        serial::SaveBool(os, false);                         // host_only
+        serial::SaveBool(os, true);                          // host_simd
+        serial::SaveString(os, m_connection);
+        serial::SaveShape(os, m_input_shape);
+        serial::SaveShape(os, m_output_shape);
+        serial::DumpTypedTensor(os, m_table);
+        serial::DumpTypedTensor(os, m_input_index);
+    }
+    void LoadObjectData(std::istream &is) override
+    {
+        serial::ExpectVersion(is, 1, "BinaryLutN");
+        this->m_name = serial::LoadModelBase(is);
+        (void)serial::LoadBool(is);
+        (void)serial::LoadBool(is);
+        m_connection = serial::LoadString(is);
+        m_input_shape  = serial::LoadShape(is);
+        m_output_shape = serial::LoadShape(is);
+        serial::LoadTypedTensor(is, m_table);
+        serial::LoadTypedTensor(is, m_input_index);
+        index_t I = CalcShapeSize(m_input_shape), O = CalcShapeSize(m_output_shape);
+        if (m_table.GetShape() != indices_t({O, 2}) || m_input_index.GetShape() != indices_t({O, (index_t)N})) throw std::runtime_error("LoadObject: inconsistent layer shapes");
+        std::int32_t const *t = m_input_index.HostConst();
+        for (index_t i = 0; i < O * N; ++i)
+            if (t[i] < 0 || t[i] >= I) throw std::runtime_error("LoadObject: connection index out of range");
+    }
     indices_t GetInputShape()  const override { return m_input_shape; }
     indices_t GetOutputShape() const override { return m_output_shape; }
 

@@ -119,6 +119,11 @@ PYBIND11_MODULE(core, m)
 
     py::class_<Model, std::shared_ptr<Model>>(m, "Model")
         .def("get_model_name", &Model::GetModelName)
+        .def("get_object_name", &Model::GetObjectName)
+        .def("set_name", &Model::SetName)
+        .def("get_name", &Model::GetName)
+        .def("dump_bytes", [](Model &m) { return py::bytes(m.DumpObjectBytes()); })
+        .def("load_bytes", [](Model &m, py::bytes b) { m.LoadObjectBytes(std::string(b)); })
         .def("send_command", &Model::SendCommand, py::arg("command"))
         .def("get_input_shape", &Model::GetInputShape)
         .def("set_input_shape", &Model::SetInputShape)

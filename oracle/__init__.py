@@ -539,6 +539,49 @@ class _Ref:
                                _vp(dy), _vp(dx))
         return y, dx
 
+    LAYER_KINDS = {"dl6_fp32": 0, "dl6_bit": 1, "sl6_fp32": 2, "binary_lut6": 3}
+
+    def layer_dump(self, kind, n_in, idx, tables, running_mean=None, running_var=None, batch_norm=True, binary=True, lut_binarize=False,
+                   gamma=0.3, beta=0.5, momentum=0.9):
+        """DumpObject bytes (uint8 array) of a reference layer holding the given wiring and tables."""
+        k = self.LAYER_KINDS[kind]
+        idx = np.ascontiguousarray(idx, np.int32)
+        O = idx.shape[0]
+        tables = np.ascontiguousarray(tables, np.int32 if k == 3 else np.float32)
+        rm = np.zeros(O, np.float32) if running_mean is None else np.ascontiguousarray(running_mean, np.float32)
+        rv = np.ones(O, np.float32) if running_var is None else np.ascontiguousarray(running_var, np.float32)
+        buf = np.zeros(4096 + O * 1024, np.uint8)
+        self.lib.bbref_layer_dump.restype = C.c_longlong
+        n = self.lib.bbref_layer_dump(C.c_int(k), C.c_int(n_in), C.c_int(O), _vp(idx), _vp(tables), _vp(rm), _vp(rv), C.c_int(batch_norm),
+                                      C.c_int(binary), C.c_int(lut_binarize), C.c_float(gamma), C.c_float(beta), C.c_float(momentum), _vp(buf),
+                                      C.c_longlong(buf.size))
+        assert n > 0, n
+        return buf[:n].copy()
+
+    def layer_load(self, kind, data, n_in, n_out):
+        """LoadObject `data` into a reference layer and read its state back: dict(idx, tables, running_mean, running_var, flags, params)."""
+        k = self.LAYER_KINDS[kind]
+        data = np.ascontiguousarray(data, np.uint8)
+        idx = np.zeros((n_out, 6), np.int32)
+        tables = np.zeros((n_out, 2), np.int32) if k == 3 else np.zeros((n_out, 64), np.float32)
+        rm, rv = np.zeros(n_out, np.float32), np.zeros(n_out, np.float32)
+        flags, params = np.zeros(3, np.int32), np.zeros(3, np.float32)
+        rc = self.lib.bbref_layer_load(C.c_int(k), _vp(data), C.c_longlong(data.size), C.c_int(n_in), C.c_int(n_out), _vp(idx), _vp(tables),
+                                       _vp(rm), _vp(rv), _vp(flags), _vp(params))
+        assert rc == 0, rc
+        return dict(idx=idx, tables=tables, running_mean=rm, running_var=rv, lut_binarize=bool(flags[0]), binary=bool(flags[1]),
+                    batch_norm=bool(flags[2]), gamma=float(params[0]), beta=float(params[1]))
+
+    def layer_redump(self, kind, data, n_out):
+        """LoadObject then DumpObject through the reference: the bytes it writes back."""
+        data = np.ascontiguousarray(data, np.uint8)
+        out = np.zeros(data.size + 4096, np.uint8)
+        self.lib.bbref_layer_redump.restype = C.c_longlong
+        n = self.lib.bbref_layer_redump(C.c_int(self.LAYER_KINDS[kind]), _vp(data), C.c_longlong(data.size), C.c_int(n_out), _vp(out),
+                                        C.c_longlong(out.size))
+        assert n > 0, n
+        return out[:n].copy()
+
     def _lut_mlp_step(self, x, t, widths, classes, idx_list, W_list, use_mse, lr):
         x = np.ascontiguousarray(x, np.float32)
         t = np.ascontiguousarray(t, np.float32)

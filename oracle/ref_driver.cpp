@@ -20,6 +20,8 @@
 #include <cstring>
 #include <chrono>
 #include <vector>
+#include <sstream>
+#include <string>
 #ifdef _OPENMP
 #include <omp.h>
 #endif
@@ -227,6 +229,32 @@ int run_differentiable(void const *x, int I, int O, int F, int const *idx, float
 
 }   // namespace
 
+
+namespace {
+template <class L> void fill_sparse(L &lut, int I, int O, int const *idx, float const *W)
+{
+    lut->SetInputShape({I});
+    set_wiring(lut, idx, O);
+    set_W(lut, W, O);
+}
+template <class L> long long dump_to(L &lut, unsigned char *buf, long long cap)
+{
+    std::ostringstream os(std::ios::binary);
+    lut->DumpObject(os);
+    std::string bytes = os.str();
+    if ((long long)bytes.size() > cap) return -(long long)bytes.size();
+    std::memcpy(buf, bytes.data(), bytes.size());
+    return (long long)bytes.size();
+}
+template <class L> void read_sparse(L &lut, int O, int *idx, float *W)
+{
+    for (int n = 0; n < O; ++n)
+        for (int k = 0; k < 6; ++k) idx[n * 6 + k] = (int)lut->GetNodeConnectionIndex(n, k);
+    auto Wp = lut->lock_W_const();
+    for (int n = 0; n < O; ++n)
+        for (int i = 0; i < 64; ++i) W[n * 64 + i] = Wp(n, i);
+}
+}   // namespace
 
 extern "C" {
 
@@ -585,6 +613,101 @@ int bbref_maxpool(int bit, void const *x, int c, int h, int w, int frames, int f
     if (y) get_fp32(y_buf, (float *)y, out_nodes, frames);
     if (dy && dx) get_fp32(layer->Backward(dy_buf), dx, in_nodes, frames);
     return 0;
+}
+
+// Serialisation.  kind: 0 DifferentiableLutN<6,float>, 1 DifferentiableLutN<6,Bit>, 2 StochasticLutN<6,float>, 3 BinaryLutN<6,Bit>.
+// dump: build a layer with the given state (tables: W [O][64] fp32, or [O][2] int32 truth tables for kind 3) and write its DumpObject
+// bytes into buf (returns the byte count, negated when cap is too small).  load: LoadObject from bytes, read the state back out.
+long long bbref_layer_dump(int kind, int I, int O, int const *idx, void const *tables, float const *rmean, float const *rvar, int batch_norm,
+                           int binary, int lut_binarize, float gamma, float beta, float momentum, unsigned char *buf, long long cap)
+{
+    if (kind == 0 || kind == 1) {
+        auto make = [&](auto tag) {
+            using L = bb::DifferentiableLutN<6, decltype(tag)>;
+            typename L::create_t c;
+            c.output_shape = {O};
+            c.batch_norm = batch_norm != 0; c.binary = binary != 0;
+            c.momentum = momentum; c.gamma = gamma; c.beta = beta;
+            auto lut = L::Create(c);
+            lut->SendCommand(lut_binarize ? "lut_binarize true" : "lut_binarize false");
+            fill_sparse(lut, I, O, idx, (float const *)tables);
+            auto m = lut->lock_mean(); auto v = lut->lock_var();
+            for (int n = 0; n < O; ++n) { m[n] = rmean[n]; v[n] = rvar[n]; }
+            return dump_to(lut, buf, cap);
+        };
+        return kind == 0 ? make(float()) : make(bb::Bit());
+    }
+    if (kind == 2) {
+        auto lut = bb::StochasticLutN<6, float>::Create(O);
+        lut->SendCommand(binary ? "binary true" : "binary false");
+        lut->SendCommand(lut_binarize ? "lut_binarize true" : "lut_binarize false");
+        fill_sparse(lut, I, O, idx, (float const *)tables);
+        return dump_to(lut, buf, cap);
+    }
+    auto lut = bb::BinaryLutN<6, bb::Bit>::Create(O);
+    lut->SetInputShape({I});
+    std::int32_t const *t = (std::int32_t const *)tables;
+    for (int n = 0; n < O; ++n) {
+        for (int k = 0; k < 6; ++k) lut->SetNodeConnectionIndex(n, k, idx[n * 6 + k]);
+        for (int i = 0; i < 64; ++i) lut->SetLutTable(n, i, (t[n * 2 + (i >> 5)] >> (i & 31)) & 1);
+    }
+    return dump_to(lut, buf, cap);
+}
+
+// flags_out: [lut_binarize, binary, batch_norm]; params_out: [gamma, beta, momentum]
+int bbref_layer_load(int kind, unsigned char const *buf, long long size, int I, int O, int *idx, void *tables, float *rmean, float *rvar,
+                     int *flags_out, float *params_out)
+{
+    std::istringstream is(std::string((char const *)buf, (size_t)size), std::ios::binary);
+    if (kind == 0 || kind == 1) {
+        auto run = [&](auto tag) {
+            using L = bb::DifferentiableLutN<6, decltype(tag)>;
+            auto lut = L::Create(O);
+            lut->LoadObject(is);
+            if ((int)lut->GetInputNodeSize() != I || (int)lut->GetOutputNodeSize() != O) return 1;
+            read_sparse(lut, O, idx, (float *)tables);
+            auto m = lut->lock_mean_const(); auto v = lut->lock_var_const();
+            for (int n = 0; n < O; ++n) { rmean[n] = m[n]; rvar[n] = v[n]; }
+            std::ostringstream info;
+            lut->PrintInfo(1, info);                // the flags are only exposed through the printed summary
+            std::string txt = info.str();
+            flags_out[0] = txt.find("lut_binarize : 1") != std::string::npos;
+            flags_out[1] = txt.find("binary : 1") != std::string::npos;
+            flags_out[2] = txt.find("batch_norm : 1") != std::string::npos;
+            params_out[0] = (float)lut->GetGamma(); params_out[1] = (float)lut->GetBeta(); params_out[2] = 0.0f;
+            return 0;
+        };
+        return kind == 0 ? run(float()) : run(bb::Bit());
+    }
+    if (kind == 2) {
+        auto lut = bb::StochasticLutN<6, float>::Create(O);
+        lut->LoadObject(is);
+        if ((int)lut->GetInputNodeSize() != I || (int)lut->GetOutputNodeSize() != O) return 1;
+        read_sparse(lut, O, idx, (float *)tables);
+        return 0;
+    }
+    auto lut = bb::BinaryLutN<6, bb::Bit>::Create(O);
+    lut->LoadObject(is);
+    if ((int)lut->GetInputNodeSize() != I || (int)lut->GetOutputNodeSize() != O) return 1;
+    std::int32_t *t = (std::int32_t *)tables;
+    for (int n = 0; n < O; ++n) {
+        t[n * 2] = t[n * 2 + 1] = 0;
+        for (int k = 0; k < 6; ++k) idx[n * 6 + k] = (int)lut->GetNodeConnectionIndex(n, k);
+        for (int i = 0; i < 64; ++i) if (lut->GetLutTable(n, i)) t[n * 2 + (i >> 5)] |= (std::int32_t)(1u << (i & 31));
+    }
+    return 0;
+}
+
+// LoadObject `buf` into a fresh reference layer of the kind and DumpObject it again: equal bytes mean the reference read every field.
+long long bbref_layer_redump(int kind, unsigned char const *buf, long long size, int O, unsigned char *out, long long cap)
+{
+    std::istringstream is(std::string((char const *)buf, (size_t)size), std::ios::binary);
+    if (kind == 0) { auto l = bb::DifferentiableLutN<6, float>::Create(O);   l->LoadObject(is); return dump_to(l, out, cap); }
+    if (kind == 1) { auto l = bb::DifferentiableLutN<6, bb::Bit>::Create(O); l->LoadObject(is); return dump_to(l, out, cap); }
+    if (kind == 2) { auto l = bb::StochasticLutN<6, float>::Create(O);       l->LoadObject(is); return dump_to(l, out, cap); }
+    auto l = bb::BinaryLutN<6, bb::Bit>::Create(O);
+    l->LoadObject(is);
+    return dump_to(l, out, cap);
 }
 
 int bbref_num_threads(void)

@@ -223,6 +223,14 @@ def main():
         g.update({f"pool{k}_y": y, f"pool{k}_dx": dx, f"pool{k}_ybits": yb, f"pool{k}_dxbits": dxb})
     g["pool_cases"] = np.array(pool_cases, np.int32)
 
+    # Serialised layers: DumpObject bytes written by the reference's own classes (wiring det_wiring(10, 3, 500), tables det_uniform 501).
+    ser_idx, ser_W = det_wiring(10, 3, 500), det_uniform((3, 64), 501)
+    g["ser_dl6_fp32"] = ref.layer_dump("dl6_fp32", 10, ser_idx, ser_W, running_mean=[0.1, 0.2, 0.3], running_var=[1.5, 2.5, 3.5], lut_binarize=True,
+                                       binary=False, gamma=0.25, beta=0.4, momentum=0.8)
+    g["ser_dl6_bit"] = ref.layer_dump("dl6_bit", 10, ser_idx, ser_W)
+    g["ser_sl6_fp32"] = ref.layer_dump("sl6_fp32", 10, ser_idx, ser_W, binary=False, lut_binarize=True)
+    g["ser_binary_lut6"] = ref.layer_dump("binary_lut6", 10, ser_idx, np.array([[1, 2], [3, 4], [5, -6]], np.int32))
+
     np.savez_compressed(OUT, **g)
     print("wrote", OUT, os.path.getsize(OUT), "bytes,", len(g), "arrays")
 

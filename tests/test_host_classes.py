@@ -251,3 +251,56 @@ def test_convolution2d_and_maxpooling_classes_against_oracle(core):
     yb = pb.forward(core.FrameBuffer.from_numpy_fp32(xb.reshape(B, c, h, w), core.TYPE_BIT), True).numpy_fp32()
     want = unpack_bits(port.maxpool_forward(pack_bits(xb.T), c, h, w, 2, 2, frames=B), B)
     assert np.array_equal(yb.reshape(B, -1).T > 0.5, want.astype(bool))
+
+
+# ------------------------------------------------------------------------------------------------ serialisation (CPU)
+def _ser_state():
+    from oracle import det_wiring, det_uniform
+    return det_wiring(10, 3, 500), det_uniform((3, 64), 501)
+
+
+def test_layers_load_the_reference_dumps_and_write_them_back(core, golden):
+    """DumpObject bytes written by BinaryBrain's own classes (golden) load into the host classes here, every field arrives, and
+    dumping again gives the same bytes."""
+    idx, W = _ser_state()
+    lut = core.DifferentiableLut6_fp32_fp32.create([3])
+    data = golden["ser_dl6_fp32"].tobytes()
+    lut.load_bytes(data)
+    assert lut.get_input_shape() == [10] and lut.get_output_shape() == [3] and lut.get_object_name() == "DifferentiableLut6_fp32_fp32"
+    assert np.array_equal(lut.W().numpy(), W) and np.array_equal(lut.get_connection(), idx)
+    assert np.allclose(lut.get_mean().numpy(), [0.1, 0.2, 0.3]) and np.allclose(lut.get_var().numpy(), [1.5, 2.5, 3.5])
+    assert lut.dump_bytes() == data
+    for cls, key in ((core.DifferentiableLut6_bit_fp32, "ser_dl6_bit"), (core.StochasticLut6_fp32_fp32, "ser_sl6_fp32"),
+                     (core.BinaryLut6_bit_fp32, "ser_binary_lut6")):
+        layer = cls.create([3])
+        layer.load_bytes(golden[key].tobytes())
+        assert layer.dump_bytes() == golden[key].tobytes(), key
+        assert [[layer.get_node_connection_index(n, k) for k in range(6)] for n in range(3)] == idx.tolist()
+    bl = core.BinaryLut6_bit_fp32.create([3])
+    bl.load_bytes(golden["ser_binary_lut6"].tobytes())
+    assert [bl.get_lut_table(0, i) for i in range(3)] == [True, False, False] and bl.get_lut_table(0, 33) and bl.get_lut_table(2, 63)
+
+
+def test_load_rejects_foreign_and_truncated_data(core, golden):
+    data = golden["ser_dl6_fp32"].tobytes()
+    lut = core.DifferentiableLut6_fp32_fp32.create([3])
+    with pytest.raises(RuntimeError):
+        lut.load_bytes(data[:200])                                            # truncated
+    with pytest.raises(RuntimeError):
+        lut.load_bytes(golden["ser_sl6_fp32"].tobytes())                      # another class's object
+    with pytest.raises(RuntimeError):
+        lut.load_bytes(b"not an object at all")
+
+
+def test_reference_loads_what_the_host_classes_dump(core):
+    """The other direction, where the reference build is present: a freshly initialised layer here, dumped, is read by BinaryBrain's
+    LoadObject and written back unchanged."""
+    from oracle import ref
+    if not ref.available():
+        pytest.skip("oracle/_ref not built")
+    for cls, kind in ((core.DifferentiableLut6_fp32_fp32, "dl6_fp32"), (core.StochasticLut6_fp32_fp32, "sl6_fp32"),
+                      (core.BinaryLut6_bit_fp32, "binary_lut6")):
+        layer = cls.create([5])
+        layer.set_input_shape([12])
+        mine = np.frombuffer(layer.dump_bytes(), np.uint8)
+        assert np.array_equal(ref.layer_redump(kind, mine, 5), mine), kind
