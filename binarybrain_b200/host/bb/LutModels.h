@@ -282,6 +282,36 @@ public:
     float GetGamma() const { return m_gamma; }
     float GetBeta()  const { return m_beta; }
 
+    // One node on the host, with the running statistics (include/bb/DifferentiableLutN.h:527-586): the value a frozen node takes for
+    // six given inputs -- what the reference uses when it exports a trained network to a truth table.  Same product form as
+    // StochasticOperation_Lut_Forward (include/bb/StochasticOperation.h:95-114).
+    std::vector<double> ForwardNode(index_t node, std::vector<double> input_value) const
+    {
+        BB_ASSERT((int)input_value.size() == N && node >= 0 && node < CalcShapeSize(this->m_output_shape));
+        float const *Wp = this->m_W->HostConst() + node * _super::NN;
+        float x[N];
+        for (int i = 0; i < N; ++i) {
+            x[i] = (float)input_value[i];
+            if (this->m_binary_mode) x[i] = 0.5f + ((x[i] > 0.5f) ? +this->m_unbinarize_bias : -this->m_unbinarize_bias);
+            else                     x[i] = std::min(1.0f, std::max(0.0f, x[i]));
+        }
+        float y = 0.0f;
+        for (int i = 0; i < _super::NN; ++i) {
+            float w = std::min(1.0f, std::max(0.0f, Wp[i]));                      // the clamp Forward applies to the parameters
+            if (this->m_lut_binarize) w = w > 0.5f ? 1.0f : 0.0f;
+            for (int j = 0; j < N; ++j) w *= ((i >> j) & 1) ? x[j] : (1.0f - x[j]);
+            y += w;
+        }
+        if (m_batch_norm) {
+            float rstd = 1.0f / std::sqrt(m_running_var.HostConst()[node]);
+            y = (y - m_running_mean.HostConst()[node]) * rstd;
+            y = y * m_gamma + m_beta;
+        }
+        if (this->m_binary_mode) y = y > 0.5f ? 1.0f : 0.0f;
+        else                     y = std::max(std::min(y, 1.0f), 0.0f);
+        return std::vector<double>{(double)y};
+    }
+
     // include/bb/DifferentiableLutN.h:264-330
     void DumpObjectData(std::ostream &os) const override
     {

@@ -141,7 +141,8 @@ PYBIND11_MODULE(core, m)
          .def("get_mean", [](DifferentiableLut6_fp32_fp32 &l) -> Tensor & { return l.running_mean(); }, py::return_value_policy::reference_internal)
          .def("get_var", [](DifferentiableLut6_fp32_fp32 &l) -> Tensor & { return l.running_var(); }, py::return_value_policy::reference_internal)
          .def("get_gamma", &DifferentiableLut6_fp32_fp32::GetGamma)
-         .def("get_beta", &DifferentiableLut6_fp32_fp32::GetBeta);
+         .def("get_beta", &DifferentiableLut6_fp32_fp32::GetBeta)
+         .def("forward_node", &DifferentiableLut6_fp32_fp32::ForwardNode, py::arg("node"), py::arg("input_value"));
         def_sparse<DifferentiableLut6_fp32_fp32>(c);
     }
     {
@@ -149,7 +150,8 @@ PYBIND11_MODULE(core, m)
         c.def_static("create", &DifferentiableLut6_bit_fp32::CreatePy, py::arg("output_shape"), py::arg("batch_norm") = true, py::arg("binary") = true,
                      py::arg("connection") = "", py::arg("momentum") = 0.0, py::arg("gamma") = 0.3, py::arg("beta") = 0.5, py::arg("seed") = 1)
          .def("get_mean", [](DifferentiableLut6_bit_fp32 &l) -> Tensor & { return l.running_mean(); }, py::return_value_policy::reference_internal)
-         .def("get_var", [](DifferentiableLut6_bit_fp32 &l) -> Tensor & { return l.running_var(); }, py::return_value_policy::reference_internal);
+         .def("get_var", [](DifferentiableLut6_bit_fp32 &l) -> Tensor & { return l.running_var(); }, py::return_value_policy::reference_internal)
+         .def("forward_node", &DifferentiableLut6_bit_fp32::ForwardNode, py::arg("node"), py::arg("input_value"));
         def_sparse<DifferentiableLut6_bit_fp32>(c);
     }
     {

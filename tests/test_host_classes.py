@@ -304,3 +304,25 @@ def test_reference_loads_what_the_host_classes_dump(core):
         layer.set_input_shape([12])
         mine = np.frombuffer(layer.dump_bytes(), np.uint8)
         assert np.array_equal(ref.layer_redump(kind, mine, 5), mine), kind
+
+
+def test_forward_node_against_oracle_inference(core):
+    """ForwardNode (one node on the host, running statistics) equals the oracle's inference forward on the same six inputs."""
+    rng = np.random.default_rng(11)
+    I, O = 12, 7
+    for binary in (True, False):
+        lut = core.DifferentiableLut6_fp32_fp32.create([O], binary=binary)
+        lut.set_input_shape([I])
+        W = np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32)
+        lut.W().set_numpy(W)
+        rm, rv = rng.normal(0.5, 0.05, O).astype(np.float32), rng.uniform(0.01, 0.1, O).astype(np.float32)
+        lut.get_mean().set_numpy(rm)
+        lut.get_var().set_numpy(rv)
+        idx = lut.get_connection()
+        x = rng.random((I, 9), dtype=np.float32)
+        want = port.dl6_forward_infer(x, idx, W, rm, rv, binary=int(binary))
+        for node in range(O):
+            for f in range(9):
+                got = lut.forward_node(node, [float(x[idx[node, k], f]) for k in range(6)])[0]
+                if abs(want["y_pre"][node, f] - 0.5) > 1e-4 or not binary:
+                    assert abs(got - want["y"][node, f]) <= 1e-5, (binary, node, f)
