@@ -474,3 +474,28 @@ def test_frame_sharded_halves_equal_the_whole(ops):
            for k, (b, e) in enumerate(cuts)]
     assert torch.allclose(torch.cat(dxs, 1), dx_w, rtol=1e-4, atol=1e-4 * float(dx_w.abs().max()))
     assert torch.allclose(dW, dW_w, rtol=1e-4, atol=1e-4 * float(dW_w.abs().max()))
+
+
+@pytest.mark.parametrize("I,O,F", [(14, 16, 8), (14, 1024, 1024), (13, 17, 1529)])
+def test_fp32_binary_layer_equals_bit_layer(ops, I, O, F):
+    """The reference's cross-check (tests/gtest/StochasticLutNTest.cpp:253-449): a StochasticLut6 layer in binary mode on fp32 frames
+    holding 0/1 and the bit-packed layer on the same Bernoulli inputs give the same forward values and the same gradients, although
+    they run through different kernels here (the pipelined fp32 tree and the per-pattern tables)."""
+    from gpu_util import dev, dev_fp32, dev_bits, host_fp32, wiring
+    from oracle import pack_bits
+    rng = np.random.default_rng(31)
+    idx = wiring(rng, I, O)
+    W = np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32)
+    bits = rng.random((I, F)) > 0.5
+    dy = rng.random((O, F), dtype=np.float32)
+    for lut_binarize in (True, False):
+        y_f = ops.stochastic_lut6_forward(dev_fp32(bits.astype(np.float32)), dev(idx), dev(W), F, binary=True, lut_binarize=lut_binarize)
+        y_b = ops.stochastic_lut6_forward(dev_bits(pack_bits(bits), F), dev(idx), dev(W), F, lut_binarize=lut_binarize)
+        assert np.array_equal(host_fp32(y_f, F), host_fp32(y_b, F))
+        dW_f, dW_b = torch.zeros((O, 64), device="cuda"), torch.zeros((O, 64), device="cuda")
+        dx_f = ops.stochastic_lut6_backward(dev_fp32(bits.astype(np.float32)), dev_fp32(dy), dev(idx), dev(W), dW_f, I, F, binary=True,
+                                            lut_binarize=lut_binarize)
+        dx_b = ops.stochastic_lut6_backward(dev_bits(pack_bits(bits), F), dev_fp32(dy), dev(idx), dev(W), dW_b, I, F, lut_binarize=lut_binarize)
+        scale = max(1.0, float(dx_f[:, :F].abs().max()))
+        assert float((dx_f[:, :F] - dx_b[:, :F]).abs().max()) <= 1e-5 * scale
+        assert float((dW_f - dW_b).abs().max()) <= 1e-5 * max(1.0, float(dW_f.abs().max()))
