@@ -156,7 +156,7 @@ def test_dl6_fp32_golden(ops, golden, case):
 
 
 @pytest.mark.parametrize("I,O,F,stride", [(16, 16, 131, None), (24, 1024, 64, None), (200, 300, 1100, 1104), (6, 2, 39, 64),
-                                          (1024, 2048, 512, None)])
+                                          (1024, 2048, 512, None), (6, 1, 1, None), (16, 16, 1024, None)])
 @pytest.mark.parametrize("binary,lut_binarize", [(0, 0), (1, 0), (1, 1), (0, 1)])
 def test_dl6_fp32_oracle(ops, I, O, F, stride, binary, lut_binarize):
     from gpu_util import wiring
@@ -213,7 +213,7 @@ def test_dl6_bit_golden(ops, golden, case):
 def test_dl6_bit_oracle_odd_sizes(ops):
     from gpu_util import dev_bits, dev_fp32, dev, host_fp32, host_bits, err, wiring
     rng = np.random.default_rng(5)
-    for (I, O, F) in [(40, 33, 1529), (512, 1024, 1024), (7, 3, 31)]:
+    for (I, O, F) in [(40, 33, 1529), (512, 1024, 1024), (7, 3, 31), (6, 1, 1), (16, 2, 39)]:
         idx = wiring(rng, I, O)
         W = np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32)
         xb = pack_bits(rng.random((I, F)) > 0.5)
