@@ -344,6 +344,9 @@ def operators_section(torch, ops, steps):
     def dl_bit_fwd():
         _, st["mean"], st["rstd"] = ops.differentiable_lut6_forward_training(xb, idx, W, rm, rv, F, y=ybit)
 
+    def dl_binary_fwd():
+        _, st["bmean"], st["brstd"] = ops.differentiable_lut6_forward_training(xf, idx, W, rm, rv, F, y=yf, binary=True)
+
     def sbn_fwd():
         st["sy"], st["smean"], st["srstd"] = ops.stochastic_bn_forward_training(xf, rm, rv, F)
 
@@ -367,6 +370,11 @@ def operators_section(torch, ops, steps):
         "dl6_forward_inference_bit": (lambda: ops.differentiable_lut6_forward_inference(xb, idx, W, rm, rv, F, y=ybit), nf, 0.25, 0.0),
         "dl6_forward_inference_fp32": (lambda: ops.differentiable_lut6_forward_inference(xf, idx, W, rm, rv, F, y=yf, binary=False), nf, 8.0, 136.0),
         "dl6_backward_bit": (lambda: ops.differentiable_lut6_backward(xb, dy, idx, W, dW, st["mean"], st["rstd"], I, F, dx=dx), nf, 12.125, 651.0),
+        # binary mode on fp32 frames (the reference's default mode): forward by the fp32 tree, backward through the per-pattern tables
+        "dl6_forward_training_fp32_binary": (dl_binary_fwd, nf, 16.0, 136.0),
+        "dl6_backward_fp32_binary": (lambda: ops.differentiable_lut6_backward(xf, dy, idx, W, dW, st["bmean"], st["brstd"], I, F, dx=dx, binary=True),
+                                     nf, 24.0, 651.0),
+        "sl6_backward_fp32_binary": (lambda: ops.stochastic_lut6_backward(xf, dy, idx, W, dW, I, F, dx=dx, binary=True), nf, 12.0, 505.0),
         "sbn_forward_training": (sbn_fwd, nf, 12.0, 8.0),
         "sbn_backward": (lambda: ops.stochastic_bn_backward(xf, dy, st["smean"], st["srstd"], F), nf, 20.0, 12.0),
         "adam_update": (lambda: adam.update(), float(W.numel()), 28.0, 12.0),

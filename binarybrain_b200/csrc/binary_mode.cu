@@ -215,7 +215,8 @@ k_bit_gather_forward(const uint32_t *__restrict__ x, float *__restrict__ y, cons
 enum { kBwdPlainAll = 0, kBwdHistOnly = 1, kBwdNormDx = 2 };
 
 struct BitBwdArgs {
-    const uint32_t *x;
+    const uint32_t *x;                  // bit-packed rows, or (XF32 kernels) fp32 rows reinterpreted: an input is "set" where x > 0.5
+    uint32_t *hist;                     // XF32 only: [O][64] pattern counts (added to by the histogram pass)
     const float *dy;
     float *dx;
     const int *idx;
@@ -229,13 +230,16 @@ struct BitBwdArgs {
 
 // Four CTAs per SM (64 registers): the frame loop needs few registers and hides its load latency with warps; the table set-up at the
 // top, which would like ~130, runs once per tile and may spill.
-template <int MODE>
+// XF32: the layer is in binary mode on fp32 frames (include/bb/DifferentiableLutN.h:779-786 maps x to 0.5 +- bias by x > 0.5), so the
+// pattern of a frame comes from six compares instead of six bits, and the histogram pass also counts the patterns.
+template <int MODE, bool XF32>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, 4)
 k_bit_backward_frames(const BitBwdArgs a)
 {
     __shared__ float4 s_tab[kWarpsPerCta][16];
     __shared__ float s_D[kWarpsPerCta][6][64];
     __shared__ float s_A[kWarpsPerCta][64], s_B[kWarpsPerCta][64], s_H[kWarpsPerCta][64];
+    __shared__ unsigned s_C[XF32 ? kWarpsPerCta : 1][64];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x / a.groups;
     const int node = (blockIdx.x % a.groups) * kWarpsPerCta + warp;
@@ -266,6 +270,7 @@ k_bit_backward_frames(const BitBwdArgs a)
             s_B[warp][p] = a.dmean[node] + (v * a.dvar[node] * a.rF);
         }
         if (MODE != kBwdNormDx) s_H[warp][p] = 0.0f;
+        if (XF32 && MODE == kBwdHistOnly) s_C[warp][p] = 0u;
     }
     __syncwarp();
     const float grstd_gamma = a.gamma, rstd_n = (MODE == kBwdNormDx) ? a.rstd[node] : 0.0f;
@@ -283,20 +288,39 @@ k_bit_backward_frames(const BitBwdArgs a)
     const float *dyrow = a.dy + (size_t)node * a.fs;
     for (int w0 = tile * a.tile_words; w0 < w_end; w0 += 32) {
         uint32_t xw[6];
+        if (!XF32) {
 #pragma unroll
-        for (int j = 0; j < 6; ++j) xw[j] = (w0 + lane < w_end) ? __ldg(rows[j] + w0 + lane) : 0u;
+            for (int j = 0; j < 6; ++j) xw[j] = (w0 + lane < w_end) ? __ldg(rows[j] + w0 + lane) : 0u;
+        }
         const int kn = min(32, w_end - w0);
         // dy of the next word is fetched while this one is processed
         long long f = (long long)w0 * 32 + lane;
         float dy_next = f < a.F ? __ldg(dyrow + f) : 0.0f;
+        float x_next[XF32 ? 6 : 1];
+        if (XF32) {
+#pragma unroll
+            for (int j = 0; j < 6; ++j) x_next[j] = f < a.F ? __ldg(reinterpret_cast<const float *>(a.x) + f + off[j]) : 0.0f;
+        }
         for (int k = 0; k < kn; ++k, f += 32) {
             uint32_t p = 0;
+            if (XF32) {
+                // this frame's inputs were fetched during the previous step; the next frame's are fetched now
 #pragma unroll
-            for (int j = 5; j >= 0; --j) p = (p << 1) | ((__shfl_sync(kFull, xw[j], k) >> lane) & 1u);
+                for (int j = 5; j >= 0; --j) p = (p << 1) | (x_next[j] > 0.5f ? 1u : 0u);
+                if (k + 1 < kn && f + 32 < a.F) {
+                    const float *xf = reinterpret_cast<const float *>(a.x) + f + 32;
+#pragma unroll
+                    for (int j = 0; j < 6; ++j) x_next[j] = __ldg(xf + off[j]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 5; j >= 0; --j) p = (p << 1) | ((__shfl_sync(kFull, xw[j], k) >> lane) & 1u);
+            }
             const float dyv = dy_next;
             if (k + 1 < kn && f + 32 < a.F) dy_next = __ldg(dyrow + f + 32);
             if (f < a.F) {
                 if (MODE != kBwdNormDx) atomicAdd(&s_H[warp][p], dyv);
+                if (XF32 && MODE == kBwdHistOnly) atomicAdd(&s_C[warp][p], 1u);
                 if (MODE != kBwdHistOnly) {
                     float g = dyv;
                     if (MODE == kBwdNormDx) g = ((dyv * s_A[warp][p]) * grstd_gamma) * rstd_n + s_B[warp][p];
@@ -311,6 +335,10 @@ k_bit_backward_frames(const BitBwdArgs a)
         __syncwarp();
         atomicAdd(a.hdy + (size_t)node * 64 + lane, s_H[warp][lane]);
         atomicAdd(a.hdy + (size_t)node * 64 + 32 + lane, s_H[warp][lane + 32]);
+        if (XF32 && MODE == kBwdHistOnly) {
+            atomicAdd(a.hist + (size_t)node * 64 + lane, s_C[warp][lane]);
+            atomicAdd(a.hist + (size_t)node * 64 + 32 + lane, s_C[warp][lane + 32]);
+        }
     }
 }
 
@@ -455,16 +483,17 @@ int bit_fp32_forward_by_table(const int *x, float *y, const int *idx, const floa
 }
 
 // Backward of the bit-input layers (StochasticLut6: bn = false; DifferentiableLut6: bn = true).  dx must be zero on entry.
-int bit_backward_by_table(bool bn, const int *x, const float *dy, float *dx, const int *idx, const float *W, float *dW, const float *mean,
-                          const float *rstd, float *dmean_out, float *dvar_out, float gamma, float beta, float bias, int O, int F, long long xs,
-                          long long fs, int lut_binarize, cudaStream_t st)
+int bit_backward_by_table(bool bn, bool x_is_fp32, const void *x, const float *dy, float *dx, const int *idx, const float *W, float *dW,
+                          const float *mean, const float *rstd, float *dmean_out, float *dvar_out, float gamma, float beta, float bias, int O, int F,
+                          long long xs, long long fs, int lut_binarize, cudaStream_t st)
 {
+    if (x_is_fp32 && xs != fs) return BBCU_ERR_NO_MEMORY;          // fp32 x shares the stride of dy / dx in every caller; otherwise decline
     if (O == 0 || F == 0) return BBCU_OK;
     Scratch s;
     if (!carve(s, O, st)) return BBCU_ERR_NO_MEMORY;
     float *hdy = reinterpret_cast<float *>(s.hist) + (size_t)O * 64;       // the block between the pattern counts and the truth tables
     BitBwdArgs a = {};
-    a.x = reinterpret_cast<const uint32_t *>(x); a.dy = dy; a.dx = dx; a.idx = idx; a.W = W; a.hdy = hdy;
+    a.x = static_cast<const uint32_t *>(x); a.dy = dy; a.dx = dx; a.idx = idx; a.W = W; a.hdy = hdy; a.hist = s.hist;
     a.mean = mean; a.rstd = rstd; a.dmean = dmean_out; a.dvar = dvar_out;
     a.gamma = gamma; a.beta = beta; a.bias = bias; a.rF = 1.0f / (float)F;
     a.O = O; a.F = F; a.xs = xs; a.fs = fs; a.lut_binarize = lut_binarize;
@@ -478,7 +507,8 @@ int bit_backward_by_table(bool bn, const int *x, const float *dy, float *dx, con
     BB200_CUDA(cudaMemsetAsync(hdy, 0, (size_t)O * 256, st));
     const unsigned nb = (unsigned)blocks, threads = kWarpsPerCta * 32;
     if (!bn) {
-        k_bit_backward_frames<kBwdPlainAll><<<nb, threads, 0, st>>>(a);
+        if (x_is_fp32) k_bit_backward_frames<kBwdPlainAll, true><<<nb, threads, 0, st>>>(a);
+        else           k_bit_backward_frames<kBwdPlainAll, false><<<nb, threads, 0, st>>>(a);
         BB200_CUDA(cudaPeekAtLastError());
         k_bit_backward_finalize<false><<<a.groups, threads, 0, st>>>(hdy, nullptr, nullptr, dW, nullptr, nullptr, nullptr, nullptr, 0.0f, 0.0f, bias, O, F);
         return launch_status();
@@ -486,18 +516,20 @@ int bit_backward_by_table(bool bn, const int *x, const float *dy, float *dx, con
     k_pattern_values<kTableNone><<<a.groups, threads, 0, st>>>(W, s.Y, nullptr, nullptr, nullptr, 0.0f, 0.0f, bias, O, lut_binarize);
     BB200_CUDA(cudaPeekAtLastError());
     BB200_CUDA(cudaMemsetAsync(s.hist, 0, (size_t)O * 256, st));
-    {
+    if (!x_is_fp32) {                                   // fp32 frames: the histogram pass below counts the patterns itself
         int tw = 4096;
         while (tw > 32 && (long long)a.groups * ((words + tw - 1) / tw) < 2LL * device_info().sm_count) tw /= 2;
         const long long hb = (long long)a.groups * ((words + tw - 1) / tw);
         k_pattern_histogram<<<(unsigned)hb, threads, 0, st>>>(a.x, idx, s.hist, O, F, xs, a.groups, tw);
         BB200_CUDA(cudaPeekAtLastError());
     }
-    k_bit_backward_frames<kBwdHistOnly><<<nb, threads, 0, st>>>(a);
+    if (x_is_fp32) k_bit_backward_frames<kBwdHistOnly, true><<<nb, threads, 0, st>>>(a);
+    else           k_bit_backward_frames<kBwdHistOnly, false><<<nb, threads, 0, st>>>(a);
     BB200_CUDA(cudaPeekAtLastError());
     k_bit_backward_finalize<true><<<a.groups, threads, 0, st>>>(hdy, s.hist, s.Y, dW, mean, rstd, dmean_out, dvar_out, gamma, beta, bias, O, F);
     BB200_CUDA(cudaPeekAtLastError());
-    k_bit_backward_frames<kBwdNormDx><<<nb, threads, 0, st>>>(a);
+    if (x_is_fp32) k_bit_backward_frames<kBwdNormDx, true><<<nb, threads, 0, st>>>(a);
+    else           k_bit_backward_frames<kBwdNormDx, false><<<nb, threads, 0, st>>>(a);
     return launch_status();
 }
 

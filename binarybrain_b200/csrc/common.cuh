@@ -55,9 +55,9 @@ int dl6_bit_forward_training_by_table(const int *x, int *y, const int *idx, cons
 int bit_fp32_forward_by_table(const int *x, float *y, const int *idx, const float *W, float bias, int O, int F, long long xs, long long ys,
                               int lut_binarize, cudaStream_t st);
 
-int bit_backward_by_table(bool bn, const int *x, const float *dy, float *dx, const int *idx, const float *W, float *dW, const float *mean,
-                          const float *rstd, float *dmean_out, float *dvar_out, float gamma, float beta, float bias, int O, int F, long long xs,
-                          long long fs, int lut_binarize, cudaStream_t st);
+int bit_backward_by_table(bool bn, bool x_is_fp32, const void *x, const float *dy, float *dx, const int *idx, const float *W, float *dW,
+                          const float *mean, const float *rstd, float *dmean_out, float *dvar_out, float gamma, float beta, float bias, int O, int F,
+                          long long xs, long long fs, int lut_binarize, cudaStream_t st);
 
 // Per-device int in global memory (zero until a kernel records a fault); allocated once, never freed.
 int *fault_word();

@@ -780,10 +780,11 @@ static int backward_common(BwdArgs a, bool bn, long long total_frames, float *dm
     // dx starts from zero (the reference's CPU path: dx_buf.FillZero(), DifferentiableLutN.h:1159)
     if (I > 0 && a.dxs > 0) BB200_CUDA(cudaMemsetAsync(a.dx, 0, sizeof(float) * (size_t)I * a.dxs, st));
     if (a.O == 0 || a.F == 0) return BBCU_OK;
-    if (XBIT && ext_sums == nullptr && a.dys == a.dxs && total_frames == a.F) {
-        // bit inputs: everything factors through the 6-bit input pattern of a frame (binary_mode.cu)
-        const int rc = bit_backward_by_table(bn, static_cast<const int *>(a.x), a.dy, a.dx, a.idx, a.W, a.dW, a.mean, a.rstd, dmean_out, dvar_out,
-                                             a.gamma, a.beta, a.bias, a.O, a.F, a.xs, a.dxs, a.lut_binarize, st);
+    if ((XBIT || a.binary) && ext_sums == nullptr && a.dys == a.dxs && total_frames == a.F) {
+        // two-valued inputs (bit frames, or fp32 frames in binary mode): everything factors through the 6-bit input pattern of a
+        // frame (binary_mode.cu)
+        const int rc = bit_backward_by_table(bn, !XBIT, a.x, a.dy, a.dx, a.idx, a.W, a.dW, a.mean, a.rstd, dmean_out, dvar_out, a.gamma, a.beta,
+                                             a.bias, a.O, a.F, a.xs, a.dxs, a.lut_binarize, st);
         if (rc != BBCU_ERR_NO_MEMORY) return rc;
     }
     a.groups = (a.O + kWarpsPerCta - 1) / kWarpsPerCta;
