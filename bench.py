@@ -371,7 +371,8 @@ def operators_section(torch, ops, steps):
         "dl6_forward_inference_fp32": (lambda: ops.differentiable_lut6_forward_inference(xf, idx, W, rm, rv, F, y=yf, binary=False), nf, 8.0, 136.0),
         "dl6_backward_bit": (lambda: ops.differentiable_lut6_backward(xb, dy, idx, W, dW, st["mean"], st["rstd"], I, F, dx=dx), nf, 12.125, 651.0),
         # binary mode on fp32 frames (the reference's default mode): forward by the fp32 tree, backward through the per-pattern tables
-        "dl6_forward_training_fp32_binary": (dl_binary_fwd, nf, 16.0, 136.0),
+        "dl6_forward_training_fp32_binary": (dl_binary_fwd, nf, 13.0, 0.0),     # x read, pattern byte written and read, y written
+        "sl6_forward_fp32_binary": (lambda: ops.stochastic_lut6_forward(xf, idx, W, F, y=yf, binary=True), nf, 8.0, 0.0),
         "dl6_backward_fp32_binary": (lambda: ops.differentiable_lut6_backward(xf, dy, idx, W, dW, st["bmean"], st["brstd"], I, F, dx=dx, binary=True),
                                      nf, 24.0, 651.0),
         "sl6_backward_fp32_binary": (lambda: ops.stochastic_lut6_backward(xf, dy, idx, W, dW, I, F, dx=dx, binary=True), nf, 12.0, 505.0),

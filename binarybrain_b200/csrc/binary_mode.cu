@@ -392,17 +392,105 @@ k_bit_backward_finalize(const float *__restrict__ hdy, const uint32_t *__restric
     dst[1] += gw.y;
 }
 
+// --------------------------------------------------------------------------------------------- binary mode on fp32 frames, forward
+// Inputs are conditioned to 0.5 +- bias by x > 0.5 (include/bb/DifferentiableLutN.h:779-786), so the same per-pattern values apply;
+// the pattern of a frame comes from six compares.  A lane owns four consecutive frames of every 128 (one 128-bit load per input row).
+//   PASS_COUNT : pattern counts per node (shared-memory integer atomics, added to `hist` per tile) and the four patterns of the lane
+//                as one 32-bit word into `pat` ([node][frame] bytes) for the output pass of the training forward;
+//   PASS_OUTPUT: y[f] = val[p(f)], the patterns read back from `pat`;
+//   PASS_DIRECT: both in one go, y[f] = val[p(f)] straight from x (StochasticLut6 forward, inference).
+// val[p]: clip(Y[p]) (StochasticLut6), or the truth-table bit as 0 / 1 (DifferentiableLut6 in binary mode).
+enum { kPassCount = 0, kPassOutput = 1, kPassDirect = 2 };
+
+struct F32BinArgs {
+    const float *x;
+    float *y;
+    const int *idx;
+    const float *Y;          // [O][64] per-pattern values (kPassDirect without a table)
+    const int *table;        // [O][2] truth tables, or nullptr: val = clip(Y)
+    uint32_t *hist;          // [O][64]
+    unsigned char *pat;      // [O][fs] pattern bytes
+    int O, F, groups, tile_frames;
+    long long fs;            // frame stride of x, y and pat (elements); a multiple of 4
+};
+
+template <int PASS>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+k_f32_binary_forward(const F32BinArgs a)
+{
+    __shared__ float    s_val[kWarpsPerCta][64];
+    __shared__ unsigned s_cnt[kWarpsPerCta][64];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x / a.groups;
+    const int node = (blockIdx.x % a.groups) * kWarpsPerCta + warp;
+    if (node >= a.O) return;
+    if (PASS == kPassCount) {
+        s_cnt[warp][lane] = 0u;
+        s_cnt[warp][lane + 32] = 0u;
+    } else if (a.table != nullptr) {
+        const uint32_t lo = (uint32_t)a.table[2 * (size_t)node], hi = (uint32_t)a.table[2 * (size_t)node + 1];
+        s_val[warp][lane] = ((lo >> lane) & 1u) ? 1.0f : 0.0f;
+        s_val[warp][lane + 32] = ((hi >> lane) & 1u) ? 1.0f : 0.0f;
+    } else {
+        s_val[warp][lane] = __saturatef(a.Y[(size_t)node * 64 + lane]);
+        s_val[warp][lane + 32] = __saturatef(a.Y[(size_t)node * 64 + 32 + lane]);
+    }
+    __syncwarp();
+    long long off[6];
+    if (PASS != kPassOutput) {
+#pragma unroll
+        for (int j = 0; j < 6; ++j) off[j] = (long long)__ldg(a.idx + (size_t)node * 6 + j) * a.fs;
+    }
+    const int f_begin = tile * a.tile_frames, f_end = min(a.F, f_begin + a.tile_frames);
+    unsigned char *prow = a.pat ? a.pat + (size_t)node * a.fs : nullptr;
+    float *yrow = a.y ? a.y + (size_t)node * a.fs : nullptr;
+    for (int f = f_begin + 4 * lane; f < f_end; f += 128) {
+        uint32_t p4 = 0;                                           // the patterns of frames f .. f+3, one per byte
+        if (PASS == kPassOutput) {
+            p4 = *reinterpret_cast<const uint32_t *>(prow + f);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 6; ++j) {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(a.x + off[j] + f));
+                p4 |= ((v.x > 0.5f ? 1u : 0u) | (v.y > 0.5f ? 0x100u : 0u) | (v.z > 0.5f ? 0x10000u : 0u) | (v.w > 0.5f ? 0x1000000u : 0u)) << j;
+            }
+        }
+        if (PASS == kPassCount) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (f + i < a.F) atomicAdd(&s_cnt[warp][(p4 >> (8 * i)) & 63u], 1u);
+            *reinterpret_cast<uint32_t *>(prow + f) = p4;
+        } else {
+            const float4 o = make_float4(s_val[warp][p4 & 63u], s_val[warp][(p4 >> 8) & 63u], s_val[warp][(p4 >> 16) & 63u], s_val[warp][(p4 >> 24) & 63u]);
+            if (f + 3 < a.F) {
+                *reinterpret_cast<float4 *>(yrow + f) = o;
+            } else {
+                const float ov[4] = {o.x, o.y, o.z, o.w};
+                for (int i = 0; i < 4 && f + i < a.F; ++i) yrow[f + i] = ov[i];
+            }
+        }
+    }
+    if (PASS == kPassCount) {
+        __syncwarp();
+        atomicAdd(a.hist + (size_t)node * 64 + lane, s_cnt[warp][lane]);
+        atomicAdd(a.hist + (size_t)node * 64 + 32 + lane, s_cnt[warp][lane + 32]);
+    }
+}
+
 struct Scratch {
     float    *Y;        // [O][64]
     uint32_t *hist;     // [O][64]
     int      *table;    // [O][2]
+    unsigned char *pat; // extra bytes asked for by the caller (pattern bytes of the fp32 binary-mode training forward)
 };
 
-bool carve(Scratch &s, int O, cudaStream_t st)
+bool carve(Scratch &s, int O, cudaStream_t st, size_t extra = 0)
 {
     const size_t per_node = 64 * 4 + 64 * 4 + 8 + 64 * 4;        // Y, pattern counts, truth table, per-pattern dy sums
-    unsigned char *base = static_cast<unsigned char *>(stream_scratch(st, per_node * (size_t)O, 1));
+    const size_t fixed = (per_node * (size_t)O + 255) & ~(size_t)255;
+    unsigned char *base = static_cast<unsigned char *>(stream_scratch(st, fixed + extra, 1));
     if (base == nullptr) return false;
+    s.pat = base + fixed;
     s.Y = reinterpret_cast<float *>(base);
     s.hist = reinterpret_cast<uint32_t *>(base + (size_t)O * 256);
     s.table = reinterpret_cast<int *>(base + (size_t)O * 768);
@@ -479,6 +567,55 @@ int bit_fp32_forward_by_table(const int *x, float *y, const int *idx, const floa
     BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
     k_bit_gather_forward<<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(reinterpret_cast<const uint32_t *>(x), y, idx, s.Y, O, F, xs, ys, groups,
                                                                         tile_words);
+    return launch_status();
+}
+
+// Binary mode on fp32 frames.  mode 0: StochasticLut6 forward (y = clip of the per-pattern value); 1: DifferentiableLut6 inference
+// (running statistics); 2: DifferentiableLut6 training forward (batch statistics from the pattern counts).  Declines (NO_MEMORY) when the
+// rows are not 16-byte aligned or the pattern bytes of the training forward would not be a reasonable scratch.
+int f32_binary_forward_by_table(int mode, const float *x, float *y, const int *idx, const float *W, float *mean, float *rstd, float *rmean,
+                                float *rvar, float gamma, float beta, float momentum, float bias, int O, int F, long long fs, int lut_binarize,
+                                cudaStream_t st)
+{
+    if (O == 0 || F == 0) return BBCU_OK;
+    if (((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) != 0 || (fs % 4) != 0) return BBCU_ERR_NO_MEMORY;
+    const size_t pat_bytes = mode == 2 ? (size_t)O * (size_t)fs : 0;
+    if (pat_bytes > ((size_t)1 << 30)) return BBCU_ERR_NO_MEMORY;
+    Scratch s;
+    if (!carve(s, O, st, pat_bytes)) return BBCU_ERR_NO_MEMORY;
+    F32BinArgs a = {};
+    a.x = x; a.y = y; a.idx = idx; a.Y = s.Y; a.hist = s.hist; a.O = O; a.F = F; a.fs = fs;
+    a.groups = (O + kWarpsPerCta - 1) / kWarpsPerCta;
+    const unsigned threads = kWarpsPerCta * 32;
+    // frame tiles narrow enough for the tile's input rows to stay in L2 while every node reads them
+    const int tf = frame_tile(3LL * O, 32, a.groups, F, 1 << 20);
+    a.tile_frames = ((tf + 127) / 128) * 128;
+    if (a.tile_frames < 1024) a.tile_frames = 1024;               // at least eight steps per warp and tile: set-up and the 64 count atomics amortise
+    const long long blocks = (long long)a.groups * ((F + a.tile_frames - 1) / a.tile_frames);
+    BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+    if (mode == 0) {
+        k_pattern_values<kTableNone><<<a.groups, threads, 0, st>>>(W, s.Y, nullptr, nullptr, nullptr, 0.0f, 0.0f, bias, O, lut_binarize);
+        BB200_CUDA(cudaPeekAtLastError());
+        k_f32_binary_forward<kPassDirect><<<(unsigned)blocks, threads, 0, st>>>(a);
+        return launch_status();
+    }
+    if (mode == 1) {
+        k_pattern_values<kTableNorm><<<a.groups, threads, 0, st>>>(W, nullptr, s.table, rmean, rvar, gamma, beta, bias, O, lut_binarize);
+        BB200_CUDA(cudaPeekAtLastError());
+        a.table = s.table;
+        k_f32_binary_forward<kPassDirect><<<(unsigned)blocks, threads, 0, st>>>(a);
+        return launch_status();
+    }
+    k_pattern_values<kTableNone><<<a.groups, threads, 0, st>>>(W, s.Y, nullptr, nullptr, nullptr, 0.0f, 0.0f, bias, O, lut_binarize);
+    BB200_CUDA(cudaPeekAtLastError());
+    BB200_CUDA(cudaMemsetAsync(s.hist, 0, (size_t)O * 256, st));
+    a.pat = s.pat;
+    k_f32_binary_forward<kPassCount><<<(unsigned)blocks, threads, 0, st>>>(a);
+    BB200_CUDA(cudaPeekAtLastError());
+    k_dl6_bit_train_finalize<<<a.groups, threads, 0, st>>>(s.Y, s.hist, s.table, mean, rstd, rmean, rvar, gamma, beta, momentum, O, F);
+    BB200_CUDA(cudaPeekAtLastError());
+    a.table = s.table;
+    k_f32_binary_forward<kPassOutput><<<(unsigned)blocks, threads, 0, st>>>(a);
     return launch_status();
 }
 

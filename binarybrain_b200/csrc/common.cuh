@@ -59,6 +59,10 @@ int bit_backward_by_table(bool bn, bool x_is_fp32, const void *x, const float *d
                           const float *mean, const float *rstd, float *dmean_out, float *dvar_out, float gamma, float beta, float bias, int O, int F,
                           long long xs, long long fs, int lut_binarize, cudaStream_t st);
 
+int f32_binary_forward_by_table(int mode, const float *x, float *y, const int *idx, const float *W, float *mean, float *rstd, float *rmean,
+                                float *rvar, float gamma, float beta, float momentum, float bias, int O, int F, long long fs, int lut_binarize,
+                                cudaStream_t st);
+
 // Per-device int in global memory (zero until a kernel records a fault); allocated once, never freed.
 int *fault_word();
 

@@ -830,6 +830,11 @@ extern "C" int bbcu_fp32_StochasticLut6_Forward(const float *x, float *y, const 
     int rc = check_common(x, y, idx, W, node_size, frame_size, frame_stride);
     if (rc) return rc;
     BB200_REQUIRE(frame_stride >= frame_size, BBCU_ERR_BAD_STRIDE);
+    if (input_binary) {       // two-valued inputs: per-pattern values, looked up per frame (binary_mode.cu)
+        rc = f32_binary_forward_by_table(0, x, y, idx, W, nullptr, nullptr, nullptr, nullptr, 0.0f, 0.0f, 0.0f, unbinarize_bias, node_size, frame_size,
+                                         frame_stride, lut_binarize, as_stream(stream));
+        if (rc != BBCU_ERR_NO_MEMORY) return rc;
+    }
     return forward_plain<false>(x, y, nullptr, idx, W, node_size, frame_size, frame_stride, frame_stride, input_binary, lut_binarize,
                                 unbinarize_bias, as_stream(stream));
 }
@@ -963,6 +968,14 @@ extern "C" int bbcu_fp32_DifferentiableLut6_ForwardTraining(const float *x, floa
     BB200_REQUIRE(frame_size > 0 || node_size == 0, BBCU_ERR_BAD_SIZE);
     if (node_size == 0) return BBCU_OK;
     cudaStream_t st = as_stream(stream);
+    if (binary_mode) {        // two-valued inputs, binarised output: statistics from the pattern counts, output from the truth table
+        int rcb = check_common(x, y, idx, W, node_size, frame_size, frame_stride);
+        if (rcb) return rcb;
+        BB200_REQUIRE(frame_stride >= frame_size, BBCU_ERR_BAD_STRIDE);
+        rcb = f32_binary_forward_by_table(2, x, y, idx, W, mean, rstd, rmean, rvar, gamma, beta, momentum, unbinarize_bias, node_size, frame_size,
+                                          frame_stride, lut_binarize, st);
+        if (rcb != BBCU_ERR_NO_MEMORY) return rcb;
+    }
     double *sums = static_cast<double *>(stream_scratch(st, sizeof(double) * 2 * (size_t)(node_size > 0 ? node_size : 0)));
     BB200_REQUIRE(sums != nullptr, BBCU_ERR_NO_MEMORY);
     int rc = bbcu_fp32_DifferentiableLut6_ForwardStats(x, y, idx, W, sums, unbinarize_bias, node_size, frame_size, frame_stride, lut_binarize,
@@ -1013,6 +1026,11 @@ extern "C" int bbcu_fp32_DifferentiableLut6_ForwardInference(const float *x, flo
     if (rc) return rc;
     BB200_REQUIRE_PTR(rmean); BB200_REQUIRE_PTR(rvar);
     BB200_REQUIRE(frame_stride >= frame_size, BBCU_ERR_BAD_STRIDE);
+    if (binary_mode) {
+        rc = f32_binary_forward_by_table(1, x, y, idx, W, nullptr, nullptr, const_cast<float *>(rmean), const_cast<float *>(rvar), gamma, beta, 0.0f,
+                                         unbinarize_bias, node_size, frame_size, frame_stride, lut_binarize, as_stream(stream));
+        if (rc != BBCU_ERR_NO_MEMORY) return rc;
+    }
     FwdArgs a = {};
     a.x = x; a.y = y; a.idx = idx; a.W = W; a.mean = rmean; a.rstd = rvar; a.stat_is_var = 1; a.bias = unbinarize_bias;
     a.gamma = gamma; a.beta = beta;
