@@ -165,6 +165,16 @@ __global__ void k_clear_tail_bits(uint32_t *y, int O, int F, long long ys)
     y[(size_t)node * ys + (F >> 5)] &= (1u << (F & 31)) - 1u;
 }
 
+// Pattern of lane l's frame from six 32-frame words: bit l of word j has to land on bit j.  One rotation (funnel shift by (l - j) mod 32)
+// and one masked OR per input.
+__device__ __forceinline__ uint32_t lane_pattern(const uint32_t (&w)[6], int lane)
+{
+    uint32_t p = 0;
+#pragma unroll
+    for (int j = 0; j < 6; ++j) p |= __funnelshift_r(w[j], w[j], (lane - j) & 31) & (1u << j);
+    return p;
+}
+
 // StochasticLut6 bit -> fp32: y[f] = clip(Y[p(f)], 0, 1).  Warp = one node for a tile of words.  Each lane loads one word of each of
 // the six rows (32 words per row and step, coalesced), then the warp walks the 32 words: word k is broadcast by shuffle, lane l
 // takes frame l of it, looks its pattern up in the node's 64 clipped values (shared memory) and the warp stores 32 consecutive
@@ -194,9 +204,10 @@ k_bit_gather_forward(const uint32_t *__restrict__ x, float *__restrict__ y, cons
         for (int j = 0; j < 6; ++j) xw[j] = (w0 + lane < w_end) ? __ldg(rows[j] + w0 + lane) : 0u;
         const int kn = min(32, w_end - w0);
         for (int k = 0; k < kn; ++k) {
-            uint32_t p = 0;
+            uint32_t wk[6];
 #pragma unroll
-            for (int j = 5; j >= 0; --j) p = (p << 1) | ((__shfl_sync(kFull, xw[j], k) >> lane) & 1u);
+            for (int j = 0; j < 6; ++j) wk[j] = __shfl_sync(kFull, xw[j], k);
+            const uint32_t p = lane_pattern(wk, lane);
             const long long f = (long long)(w0 + k) * 32 + lane;
             if (f < F) yrow[f] = val[p];
         }
@@ -313,8 +324,10 @@ k_bit_backward_frames(const BitBwdArgs a)
                     for (int j = 0; j < 6; ++j) x_next[j] = __ldg(xf + off[j]);
                 }
             } else {
+                uint32_t wk[6];
 #pragma unroll
-                for (int j = 5; j >= 0; --j) p = (p << 1) | ((__shfl_sync(kFull, xw[j], k) >> lane) & 1u);
+                for (int j = 0; j < 6; ++j) wk[j] = __shfl_sync(kFull, xw[j], k);
+                p = lane_pattern(wk, lane);
             }
             const float dyv = dy_next;
             if (k + 1 < kn && f + 32 < a.F) dy_next = __ldg(dyrow + f + 32);
