@@ -457,17 +457,28 @@ k_f32_binary_forward(const F32BinArgs a)
     const int f_begin = tile * a.tile_frames, f_end = min(a.F, f_begin + a.tile_frames);
     unsigned char *prow = a.pat ? a.pat + (size_t)node * a.fs : nullptr;
     float *yrow = a.y ? a.y + (size_t)node * a.fs : nullptr;
-    for (int f = f_begin + 4 * lane; f < f_end; f += 128) {
-        uint32_t p4 = 0;                                           // the patterns of frames f .. f+3, one per byte
+    // the loads of step i + 1 are issued before step i is processed (the loop body is short and would otherwise wait on every load)
+    float4 xq[PASS == kPassOutput ? 1 : 6];
+    uint32_t pq = 0;
+    auto fetch = [&](int f) {
         if (PASS == kPassOutput) {
-            p4 = *reinterpret_cast<const uint32_t *>(prow + f);
+            pq = *reinterpret_cast<const uint32_t *>(prow + f);
         } else {
 #pragma unroll
-            for (int j = 0; j < 6; ++j) {
-                const float4 v = __ldg(reinterpret_cast<const float4 *>(a.x + off[j] + f));
-                p4 |= ((v.x > 0.5f ? 1u : 0u) | (v.y > 0.5f ? 0x100u : 0u) | (v.z > 0.5f ? 0x10000u : 0u) | (v.w > 0.5f ? 0x1000000u : 0u)) << j;
-            }
+            for (int j = 0; j < 6; ++j) xq[j] = __ldg(reinterpret_cast<const float4 *>(a.x + off[j] + f));
         }
+    };
+    int f = f_begin + 4 * lane;
+    if (f < f_end) fetch(f);
+    for (; f < f_end; f += 128) {
+        uint32_t p4 = pq;                                          // the patterns of frames f .. f+3, one per byte
+        if (PASS != kPassOutput) {
+            p4 = 0;
+#pragma unroll
+            for (int j = 0; j < 6; ++j)
+                p4 |= ((xq[j].x > 0.5f ? 1u : 0u) | (xq[j].y > 0.5f ? 0x100u : 0u) | (xq[j].z > 0.5f ? 0x10000u : 0u) | (xq[j].w > 0.5f ? 0x1000000u : 0u)) << j;
+        }
+        if (f + 128 < f_end) fetch(f + 128);
         if (PASS == kPassCount) {
 #pragma unroll
             for (int i = 0; i < 4; ++i)
