@@ -209,7 +209,7 @@ def fp32_section(torch, ops, steps):
     return out
 
 
-def train_section(torch, ops, dist, world, rank, steps):
+def train_section(torch, ops, dist, world, rank, steps, binary=False):
     """Config-4 style training step, frame-sharded: 6 stacked DifferentiableLut6 layers of TRAIN_NODES nodes (fp32, batch norm on),
     TRAIN_FRAMES frames per GPU (global batch = that x world), MSE loss on the last layer, backward with the per-layer dW all-reduce
     overlapped with the next layer's backward, Adam.  Reports forward+backward node-frames/s over all ranks."""
@@ -221,7 +221,7 @@ def train_section(torch, ops, dist, world, rank, steps):
     for _ in range(layers_n):
         idx = torch.randint(0, nodes, (nodes, 6), device=dev, generator=g).to(torch.int32)
         W = (torch.randn((nodes, 64), device=dev, generator=g) * 0.01 + 0.5).clamp_(0, 1)
-        layers.append(ShardedDifferentiableLut6(idx, W, nodes, binary=False))
+        layers.append(ShardedDifferentiableLut6(idx, W, nodes, binary=binary))
     opt = ops.Adam([l.W for l in layers], [l.dW for l in layers])
     gd = torch.Generator(device=dev).manual_seed(100 + rank)  # each rank draws its own frame shard
     x0 = torch.rand((nodes, frames), device=dev, generator=gd)
@@ -263,7 +263,7 @@ def train_section(torch, ops, dist, world, rank, steps):
         ms = float(t.item())
     sec = ms / 1e3 / steps
     return {"workload": f"config 4 (frame-sharded training): {layers_n} x DifferentiableLut6 {nodes}->{nodes}, {frames} frames per GPU "
-                        f"(global batch {total}), fp32, batch norm, MSE, Adam; dW all-reduce overlapped with backward",
+                        f"(global batch {total}), fp32{', binary mode' if binary else ''}, batch norm, MSE, Adam; dW all-reduce overlapped with backward",
             "node_frames_per_s": layers_n * nodes * total / sec, "ms_per_step": sec * 1e3, "steps": steps, "n_gpus": world,
             "allreduce_bytes_per_step": layers_n * (nodes * 64 * 4 + 2 * nodes * 2 * 8) if world > 1 else 0}
 
@@ -531,6 +531,9 @@ def main():
         del hx, hy, x, y
         torch.cuda.empty_cache()
         line["train"] = train_section(torch, ops, dist, world, rank, max(2, min(args.steps, 5)))
+        torch.cuda.empty_cache()
+        # the same step in the reference's default binary mode (inputs 0.5 +- bias by x > 0.5, outputs binarised)
+        line["train_binary"] = train_section(torch, ops, dist, world, rank, max(2, min(args.steps, 5)), binary=True)
         if rank == 0:
             torch.cuda.empty_cache()
             line["fp32"] = fp32_section(torch, ops, max(3, min(args.steps, 10)))

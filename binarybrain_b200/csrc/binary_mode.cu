@@ -228,6 +228,7 @@ enum { kBwdPlainAll = 0, kBwdHistOnly = 1, kBwdNormDx = 2 };
 struct BitBwdArgs {
     const uint32_t *x;                  // bit-packed rows, or (XF32 kernels) fp32 rows reinterpreted: an input is "set" where x > 0.5
     uint32_t *hist;                     // XF32 only: [O][64] pattern counts (added to by the histogram pass)
+    unsigned char *pat;                 // XF32 with batch norm: [O][fs] pattern bytes, written by the histogram pass, read by the dx pass
     const float *dy;
     float *dx;
     const int *idx;
@@ -307,15 +308,24 @@ k_bit_backward_frames(const BitBwdArgs a)
         // dy of the next word is fetched while this one is processed
         long long f = (long long)w0 * 32 + lane;
         float dy_next = f < a.F ? __ldg(dyrow + f) : 0.0f;
-        float x_next[XF32 ? 6 : 1];
-        if (XF32) {
+        // fp32 frames: this step's inputs were fetched during the previous step.  With batch norm the histogram pass leaves one pattern
+        // byte per frame behind and the dx pass reads that instead of gathering the six rows a second time.
+        constexpr bool kFromBytes = XF32 && MODE == kBwdNormDx;
+        float x_next[(XF32 && !kFromBytes) ? 6 : 1];
+        unsigned char p_next = 0;
+        const unsigned char *prow = XF32 && a.pat != nullptr ? a.pat + (size_t)node * a.fs : nullptr;
+        if (kFromBytes) {
+            p_next = f < a.F ? prow[f] : (unsigned char)0;
+        } else if (XF32) {
 #pragma unroll
             for (int j = 0; j < 6; ++j) x_next[j] = f < a.F ? __ldg(reinterpret_cast<const float *>(a.x) + f + off[j]) : 0.0f;
         }
         for (int k = 0; k < kn; ++k, f += 32) {
             uint32_t p = 0;
-            if (XF32) {
-                // this frame's inputs were fetched during the previous step; the next frame's are fetched now
+            if (kFromBytes) {
+                p = p_next;
+                if (k + 1 < kn && f + 32 < a.F) p_next = prow[f + 32];
+            } else if (XF32) {
 #pragma unroll
                 for (int j = 5; j >= 0; --j) p = (p << 1) | (x_next[j] > 0.5f ? 1u : 0u);
                 if (k + 1 < kn && f + 32 < a.F) {
@@ -323,6 +333,7 @@ k_bit_backward_frames(const BitBwdArgs a)
 #pragma unroll
                     for (int j = 0; j < 6; ++j) x_next[j] = __ldg(xf + off[j]);
                 }
+                if (MODE == kBwdHistOnly && f < a.F) const_cast<unsigned char *>(prow)[f] = (unsigned char)p;
             } else {
                 uint32_t wk[6];
 #pragma unroll
@@ -650,11 +661,13 @@ int bit_backward_by_table(bool bn, bool x_is_fp32, const void *x, const float *d
 {
     if (x_is_fp32 && xs != fs) return BBCU_ERR_NO_MEMORY;          // fp32 x shares the stride of dy / dx in every caller; otherwise decline
     if (O == 0 || F == 0) return BBCU_OK;
+    const size_t pat_bytes = (x_is_fp32 && bn) ? (size_t)O * (size_t)fs : 0;      // pattern bytes handed from the histogram pass to the dx pass
+    if (pat_bytes > ((size_t)1 << 30)) return BBCU_ERR_NO_MEMORY;
     Scratch s;
-    if (!carve(s, O, st)) return BBCU_ERR_NO_MEMORY;
+    if (!carve(s, O, st, pat_bytes)) return BBCU_ERR_NO_MEMORY;
     float *hdy = reinterpret_cast<float *>(s.hist) + (size_t)O * 64;       // the block between the pattern counts and the truth tables
     BitBwdArgs a = {};
-    a.x = static_cast<const uint32_t *>(x); a.dy = dy; a.dx = dx; a.idx = idx; a.W = W; a.hdy = hdy; a.hist = s.hist;
+    a.x = static_cast<const uint32_t *>(x); a.dy = dy; a.dx = dx; a.idx = idx; a.W = W; a.hdy = hdy; a.hist = s.hist; a.pat = pat_bytes ? s.pat : nullptr;
     a.mean = mean; a.rstd = rstd; a.dmean = dmean_out; a.dvar = dvar_out;
     a.gamma = gamma; a.beta = beta; a.bias = bias; a.rF = 1.0f / (float)F;
     a.O = O; a.F = F; a.xs = xs; a.fs = fs; a.lut_binarize = lut_binarize;

@@ -66,6 +66,15 @@ class ShardedDifferentiableLut6:
         """x: this rank's [n_in, stride] shard with `frames` valid frames; total_frames: frames of the whole step."""
         if y is None:
             y = torch.empty((self.n_out, x.shape[1]), dtype=torch.float32, device=x.device)
+        self._fused = self.world == 1 and self.binary and hasattr(self.ops, "differentiable_lut6_forward_training")
+        if self._fused:
+            # one rank, binary mode: the unsplit operators, which take the per-pattern table route (no exchange point is needed)
+            _, mean, rstd = self.ops.differentiable_lut6_forward_training(x, self.idx, self.W, self.running_mean, self.running_var, frames, y=y,
+                                                                         gamma=self.gamma, beta=self.beta, momentum=self.momentum,
+                                                                         lut_binarize=self.lut_binarize, binary=True)
+            self.mean, self.rstd = mean, rstd
+            self._x, self._frames, self._total, self._y = x, frames, total_frames, None
+            return y
         self.ops.dl6_forward_stats(x, self.idx, self.W, frames, y, self.sums, lut_binarize=self.lut_binarize, binary=self.binary)
         self._allreduce(self.sums)
         self.ops.dl6_forward_normalize(y, self.sums, self.mean, self.rstd, self.running_mean, self.running_var, frames, total_frames,
@@ -82,6 +91,10 @@ class ShardedDifferentiableLut6:
         if dx is None:
             dx = torch.empty((self.n_in, dy.shape[1]), dtype=torch.float32, device=dy.device)
         kw = dict(gamma=self.gamma, beta=self.beta, lut_binarize=self.lut_binarize, binary=self.binary)
+        if getattr(self, "_fused", False):
+            self.ops.differentiable_lut6_backward(x, dy, self.idx, self.W, self.dW, self.mean, self.rstd, self.n_in, frames, dx=dx, **kw)
+            self._x = None
+            return dx
         if self._y is not None and self._y.shape[1] == dy.shape[1]:
             self.ops.dl6_backward_stats_from_output(self._y, dy, self.rstd, frames, self.sums, gamma=self.gamma, beta=self.beta)
         else:

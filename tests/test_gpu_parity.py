@@ -499,3 +499,35 @@ def test_fp32_binary_layer_equals_bit_layer(ops, I, O, F):
         scale = max(1.0, float(dx_f[:, :F].abs().max()))
         assert float((dx_f[:, :F] - dx_b[:, :F]).abs().max()) <= 1e-5 * scale
         assert float((dW_f - dW_b).abs().max()) <= 1e-5 * max(1.0, float(dW_f.abs().max()))
+
+
+def test_single_rank_binary_layer_uses_the_unsplit_operators(ops):
+    """On one rank a binary-mode layer of binarybrain_b200.dist runs the unsplit operators (per-pattern table route); its results equal
+    the split halves (tree kernels) that the sharded path uses: outputs except next to the threshold, gradients to 1e-4."""
+    from binarybrain_b200.dist import ShardedDifferentiableLut6
+    from gpu_util import dev, wiring
+    rng = np.random.default_rng(41)
+    I, O, F = 200, 300, 1024
+    idx, W = dev(wiring(rng, I, O)), dev(np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32))
+    x, dy = dev(rng.random((I, F), dtype=np.float32)), dev(rng.random((O, F), dtype=np.float32))
+    layer = ShardedDifferentiableLut6(idx, W.clone(), I, binary=True)
+    y = layer.forward(x, F, F)
+    assert layer._fused
+    dx = layer.backward(dy)
+    dW = layer.wait_grad()
+    # the halves, by hand
+    y_h = torch.empty((O, F), device="cuda")
+    sums = torch.zeros((O, 2), dtype=torch.float64, device="cuda")
+    mean, rstd = torch.empty(O, device="cuda"), torch.empty(O, device="cuda")
+    rm, rv = torch.zeros(O, device="cuda"), torch.ones(O, device="cuda")
+    ops.dl6_forward_stats(x, idx, W, F, y_h, sums, binary=True)
+    ops.dl6_forward_normalize(y_h, sums, mean, rstd, rm, rv, F, F, binary=True)
+    assert float((y != y_h).float().mean()) < 1e-3
+    assert torch.allclose(layer.mean, mean, atol=1e-6) and torch.allclose(layer.rstd, rstd, rtol=1e-4)
+    ops.dl6_backward_stats(x, dy, idx, W, mean, rstd, F, sums, binary=True)
+    dW_h = torch.zeros((O, 64), device="cuda")
+    dx_h = torch.empty((I, F), device="cuda")
+    ops.dl6_backward_apply(x, dy, dx_h, idx, W, dW_h, mean, rstd, sums, I, F, F, binary=True)
+    amp = max(1.0, 0.3 * float(rstd.max()))
+    assert float((dx - dx_h).abs().max()) <= 1e-4 * amp * max(1.0, float(dx_h.abs().max()))
+    assert float((dW - dW_h).abs().max()) <= 1e-4 * amp * max(1.0, float(dW_h.abs().max()))
