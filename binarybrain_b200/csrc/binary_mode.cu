@@ -422,9 +422,11 @@ k_bit_backward_finalize(const float *__restrict__ hdy, const uint32_t *__restric
 //   PASS_COUNT : pattern counts per node (shared-memory integer atomics, added to `hist` per tile) and the four patterns of the lane
 //                as one 32-bit word into `pat` ([node][frame] bytes) for the output pass of the training forward;
 //   PASS_OUTPUT: y[f] = val[p(f)], the patterns read back from `pat`;
-//   PASS_DIRECT: both in one go, y[f] = val[p(f)] straight from x (StochasticLut6 forward, inference).
+//   PASS_DIRECT: both in one go, y[f] = val[p(f)] straight from x (StochasticLut6 forward, inference);
+//   PASS_STATS : the first half of a frame-sharded training forward: pattern counts, and y[f] = Y[p(f)] unclipped (the raw LUT value the
+//                normalise half works on).
 // val[p]: clip(Y[p]) (StochasticLut6), or the truth-table bit as 0 / 1 (DifferentiableLut6 in binary mode).
-enum { kPassCount = 0, kPassOutput = 1, kPassDirect = 2 };
+enum { kPassCount = 0, kPassOutput = 1, kPassDirect = 2, kPassStats = 3 };
 
 struct F32BinArgs {
     const float *x;
@@ -448,9 +450,15 @@ k_f32_binary_forward(const F32BinArgs a)
     const int tile = blockIdx.x / a.groups;
     const int node = (blockIdx.x % a.groups) * kWarpsPerCta + warp;
     if (node >= a.O) return;
-    if (PASS == kPassCount) {
+    constexpr bool kCounts = PASS == kPassCount || PASS == kPassStats;
+    if (kCounts) {
         s_cnt[warp][lane] = 0u;
         s_cnt[warp][lane + 32] = 0u;
+    }
+    if (PASS == kPassStats) {
+        s_val[warp][lane] = a.Y[(size_t)node * 64 + lane];
+        s_val[warp][lane + 32] = a.Y[(size_t)node * 64 + 32 + lane];
+    } else if (PASS == kPassCount) {
     } else if (a.table != nullptr) {
         const uint32_t lo = (uint32_t)a.table[2 * (size_t)node], hi = (uint32_t)a.table[2 * (size_t)node + 1];
         s_val[warp][lane] = ((lo >> lane) & 1u) ? 1.0f : 0.0f;
@@ -490,12 +498,13 @@ k_f32_binary_forward(const F32BinArgs a)
                 p4 |= ((xq[j].x > 0.5f ? 1u : 0u) | (xq[j].y > 0.5f ? 0x100u : 0u) | (xq[j].z > 0.5f ? 0x10000u : 0u) | (xq[j].w > 0.5f ? 0x1000000u : 0u)) << j;
         }
         if (f + 128 < f_end) fetch(f + 128);
-        if (PASS == kPassCount) {
+        if (kCounts) {
 #pragma unroll
             for (int i = 0; i < 4; ++i)
                 if (f + i < a.F) atomicAdd(&s_cnt[warp][(p4 >> (8 * i)) & 63u], 1u);
-            *reinterpret_cast<uint32_t *>(prow + f) = p4;
-        } else {
+            if (PASS == kPassCount) *reinterpret_cast<uint32_t *>(prow + f) = p4;
+        }
+        if (PASS != kPassCount) {
             const float4 o = make_float4(s_val[warp][p4 & 63u], s_val[warp][(p4 >> 8) & 63u], s_val[warp][(p4 >> 16) & 63u], s_val[warp][(p4 >> 24) & 63u]);
             if (f + 3 < a.F) {
                 *reinterpret_cast<float4 *>(yrow + f) = o;
@@ -505,11 +514,24 @@ k_f32_binary_forward(const F32BinArgs a)
             }
         }
     }
-    if (PASS == kPassCount) {
+    if (kCounts) {
         __syncwarp();
         atomicAdd(a.hist + (size_t)node * 64 + lane, s_cnt[warp][lane]);
         atomicAdd(a.hist + (size_t)node * 64 + 32 + lane, s_cnt[warp][lane + 32]);
     }
+}
+
+// Per-node (sum y, sum y^2) over this rank's frames from the pattern counts: sums[node] = (sum_p H[p] Y[p], sum_p H[p] Y[p]^2).
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+k_counts_to_sums(const float *__restrict__ Y, const uint32_t *__restrict__ hist, double *__restrict__ sums, int O)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int node = blockIdx.x * kWarpsPerCta + warp;
+    if (node >= O) return;
+    const double y0 = (double)Y[(size_t)node * 64 + lane], y1 = (double)Y[(size_t)node * 64 + 32 + lane];
+    const double h0 = (double)hist[(size_t)node * 64 + lane], h1 = (double)hist[(size_t)node * 64 + 32 + lane];
+    const double s1 = warp_sum(h0 * y0 + h1 * y1), s2 = warp_sum(h0 * (y0 * y0) + h1 * (y1 * y1));
+    if (lane == 0) { sums[2 * (size_t)node] = s1; sums[2 * (size_t)node + 1] = s2; }
 }
 
 struct Scratch {
@@ -606,7 +628,8 @@ int bit_fp32_forward_by_table(const int *x, float *y, const int *idx, const floa
 }
 
 // Binary mode on fp32 frames.  mode 0: StochasticLut6 forward (y = clip of the per-pattern value); 1: DifferentiableLut6 inference
-// (running statistics); 2: DifferentiableLut6 training forward (batch statistics from the pattern counts).  Declines (NO_MEMORY) when the
+// (running statistics); 2: DifferentiableLut6 training forward (batch statistics from the pattern counts); 3: the statistics half of a
+// frame-sharded training forward (raw per-pattern values into y, this rank's fp64 sums [O][2] through the `mean` argument).  Declines (NO_MEMORY) when the
 // rows are not 16-byte aligned or the pattern bytes of the training forward would not be a reasonable scratch.
 int f32_binary_forward_by_table(int mode, const float *x, float *y, const int *idx, const float *W, float *mean, float *rstd, float *rmean,
                                 float *rvar, float gamma, float beta, float momentum, float bias, int O, int F, long long fs, int lut_binarize,
@@ -632,6 +655,15 @@ int f32_binary_forward_by_table(int mode, const float *x, float *y, const int *i
         k_pattern_values<kTableNone><<<a.groups, threads, 0, st>>>(W, s.Y, nullptr, nullptr, nullptr, 0.0f, 0.0f, bias, O, lut_binarize);
         BB200_CUDA(cudaPeekAtLastError());
         k_f32_binary_forward<kPassDirect><<<(unsigned)blocks, threads, 0, st>>>(a);
+        return launch_status();
+    }
+    if (mode == 3) {          // first half of a sharded training forward: raw values into y, per-rank sums (mean doubles as the sums pointer)
+        k_pattern_values<kTableNone><<<a.groups, threads, 0, st>>>(W, s.Y, nullptr, nullptr, nullptr, 0.0f, 0.0f, bias, O, lut_binarize);
+        BB200_CUDA(cudaPeekAtLastError());
+        BB200_CUDA(cudaMemsetAsync(s.hist, 0, (size_t)O * 256, st));
+        k_f32_binary_forward<kPassStats><<<(unsigned)blocks, threads, 0, st>>>(a);
+        BB200_CUDA(cudaPeekAtLastError());
+        k_counts_to_sums<<<a.groups, threads, 0, st>>>(s.Y, s.hist, reinterpret_cast<double *>(mean), O);
         return launch_status();
     }
     if (mode == 1) {

@@ -930,6 +930,11 @@ int dl6_forward_stats(const float *x, float *y, const int *idx, const float *W, 
     if (rc) return rc;
     BB200_REQUIRE_PTR(dev_sums);
     BB200_REQUIRE(frame_stride >= frame_size, BBCU_ERR_BAD_STRIDE);
+    if (binary_mode && may_allocate) {       // two-valued inputs: raw values by per-pattern lookup, sums from the pattern counts
+        rc = f32_binary_forward_by_table(3, x, y, idx, W, reinterpret_cast<float *>(dev_sums), nullptr, nullptr, nullptr, 0.0f, 0.0f, 0.0f,
+                                         unbinarize_bias, node_size, frame_size, frame_stride, lut_binarize, st);
+        if (rc != BBCU_ERR_NO_MEMORY) return rc;
+    }
     BB200_CUDA(cudaMemsetAsync(dev_sums, 0, sizeof(double) * 2 * (size_t)node_size, st));
     FwdArgs a = {};
     a.x = x; a.y = y; a.idx = idx; a.W = W; a.sums = dev_sums; a.bias = unbinarize_bias;
