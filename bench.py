@@ -10,7 +10,11 @@ through the public operator with HOST buffers (pinned H2D of x, D2H of y inside 
 Frames shard across ranks with no collective (weak scaling: every rank holds 2^20 frames).
 
 The `fp32` object reports the other half of the metric -- StochasticLut6 / DifferentiableLut6 forward and
-backward on one 8192 -> 8192 layer slice of config 4 -- with the roofline that bounds each (FP32 pipe or HBM).
+backward on one 8192 -> 8192 layer slice of config 4 -- with the roofline that bounds each (FP32 pipe or HBM) and, at one
+GPU, the reference's CPU code on the same operators.  Further objects: `train` / `train_binary` (the frame-sharded config-4
+training step, in probability mode and in the reference's default binary mode), `cnn` (the config-3 LUT-CNN step) and
+`operators` (every other operator of the path: bit-input variants, binary mode, StochasticBatchNormalization, Adam, the
+convolution lowering), each with its time and roofline fraction.
 
 `--impl reference` times the reference's own CPU implementation (oracle/_ref, the unmodified BinaryBrain
 headers, AVX2 + OpenMP on all host cores) on a bounded frame sample of the same workload.
