@@ -19,9 +19,11 @@
  *   - return value: 0 on success, BBCU_ERR_* (< 0) for a rejected argument, a cudaError_t (> 0)
  *     if the CUDA runtime reported one.  Nothing exits the process (the reference's macros call
  *     exit(1), include/bbcu/bbcu_util.h:17-36);
- *   - scratch: the LUT operators keep small per-stream work areas (per-node sums, coefficient and pattern tables: at most
- *     ~1 KiB per output node) in the device heap below; the first call on a stream allocates them, later calls reuse them, and
- *     bbcu_LocalHeap_GarbageCollect releases them.  ..._ForwardTraining_NoAlloc is the variant that never allocates.
+ *   - scratch: the LUT operators keep per-stream work areas in the device heap below: per-node sums, coefficient and pattern
+ *     tables (at most ~1 KiB per output node) and, for DifferentiableLut6 in binary mode on fp32 frames, one pattern byte per
+ *     node-frame (node_size * frame_stride bytes; above 1 GiB the operator runs its scratch-free kernels instead).  The first
+ *     call on a stream allocates them, later calls reuse them, and bbcu_LocalHeap_GarbageCollect releases them.
+ *     ..._ForwardTraining_NoAlloc is the variant that never allocates.
  *
  * Results follow the reference's CPU branches (the header-only path in include/bb), which is what
  * parity is measured against; where the reference's old CUDA kernels differ from its CPU code the
