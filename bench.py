@@ -1,23 +1,26 @@
 #!/usr/bin/env python
 """Benchmark of the B200 LUT6 hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extras]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extras] [--only SECTION]
 
-Headline workload (BASELINE config 1): BinaryLut6 bit-packed inference forward, 16384 -> 16384 nodes,
-2^20 frames per GPU, Bernoulli(0.5) inputs, random 6-input wiring, random 64-bit tables.  One step is
-one forward over the whole batch.  `value` = node-frames/s with inputs resident in HBM; `e2e` = the same
-through the public operator with HOST buffers (pinned H2D of x, D2H of y inside the timed region).
-Frames shard across ranks with no collective (weak scaling: every rank holds 2^20 frames).
+Headline workload: the frame-sharded training step on six stacked DifferentiableLut6 layers of 65536 nodes (fp32, batch norm
+fused, MSE loss on the last layer, Adam), at a FIXED global batch of 32768 frames per step whatever the number of GPUs
+(strong scaling; one GPU holds ten 8 GiB frame buffers).  Rank r owns the frames [r G/N, (r+1) G/N).  Per layer and step the ranks
+exchange the batch-norm sums of the forward and of the backward pass (two blocking all-reduces of [65536, 2] fp64) and the
+table gradients ([65536, 64] fp32, all-reduced asynchronously under the next layer's backward).  One step is forward +
+backward + Adam over the whole global batch; `value` = layers x nodes x G / step time (node-frames/s, each counted once for
+its forward and backward together) with the inputs resident in HBM; `e2e` = the same step with this rank's input and target
+shards uploaded from pinned host memory every step (double-buffered on a copy stream) and the loss read back.
+`roofline` is that of the kernel that dominates the step, the fused batch-norm + LUT backward (k_lut6_backward_vec), timed
+with CUDA events around every one of its launches inside the timed steps.
 
-The `fp32` object reports the other half of the metric -- StochasticLut6 / DifferentiableLut6 forward and
-backward on one 8192 -> 8192 layer slice of config 4 -- with the roofline that bounds each (FP32 pipe or HBM) and, at one
-GPU, the reference's CPU code on the same operators.  Further objects: `train` / `train_binary` (the frame-sharded config-4
-training step, in probability mode and in the reference's default binary mode), `cnn` (the config-3 LUT-CNN step) and
-`operators` (every other operator of the path: bit-input variants, binary mode, StochasticBatchNormalization, Adam, the
-convolution lowering), each with its time and roofline fraction.
+Sub-objects: `binary_lut6` (BinaryLut6 bit-packed inference forward, 16384 -> 16384 nodes, 2^20 frames per GPU, with its own
+roofline, host-buffer e2e and CPU baseline), `fp32` (StochasticLut6 / DifferentiableLut6 forward and backward on one 65536 -> 65536
+x 4096-frame layer, each against the roofline that bounds it), `train_binary` (the same six layers in the reference's binary
+mode, 4096 frames per GPU), `cnn` (the LUT-CNN step) and `operators` (every other operator of the path).
 
-`--impl reference` times the reference's own CPU implementation (oracle/_ref, the unmodified BinaryBrain
-headers, AVX2 + OpenMP on all host cores) on a bounded frame sample of the same workload.
+`--impl reference` times the reference's own CPU implementation (oracle/_ref, the unmodified BinaryBrain headers, OpenMP on all
+host cores) on a bounded sample of the headline workload.
 """
 import argparse
 import json
@@ -31,15 +34,24 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-N_IN = N_OUT = 16384
-FRAMES = 1 << 20
-TRAIN_NODES = 65536                  # config 4 layer width
-TRAIN_FRAMES = 4096                  # frames per GPU and step in the training section (6 saved activations of 1 GiB each)
-CPU_SAMPLE_FRAMES = 1 << 18          # bounded sample for the CPU legs (the full batch needs 8 GiB of host copies)
+TRAIN_NODES = 65536                  # layer width of the training workload
+TRAIN_LAYERS = 6
+TRAIN_GLOBAL_BATCH = 32768           # frames per step over all GPUs (8 GiB per fp32 frame buffer on one GPU)
+CPU_TRAIN_SAMPLE_FRAMES = 8          # the reference's DifferentiableLutN backward is a serial loop over nodes (~2e5 node-frames/s)
+BL6_NODES = 16384
+BL6_FRAMES = 1 << 20
 FALLBACK_HBM_GBS = 6650.0            # the pool's earlier measurement, used only when MEASURED_PEAKS.json is absent
-# dram__bytes_read.sum + dram__bytes_write.sum of one k_binary_lut6_pipe launch: ncu on a 131072-frame launch gave
-# 449.7 MB + 244.6 MB (profiles/binary_lut6_16384x16384_131072frames.md); traffic grows with frames, so x8 for 2^20 frames.
-NCU_TRAFFIC_BYTES_PER_FRAME = (449.7e6 + 244.6e6) / 131072
+SM_CLOCK_HZ = 1.965e9                # clocks.max.sm of the B200s of this pool
+# Algorithmic work per node-frame (one LUT evaluation) of the kernels the rooflines are quoted on, counted for the 63-interpolation
+# tree: forward 126 flops; backward 126 (recomputed forward) + 63 x 5 (reverse pass) + 64 (table-gradient sums) = 505.
+FLOPS_FWD, FLOPS_BWD = 126.0, 505.0
+# what the centred-polynomial kernels issue instead: 63 FMA forward; backward 31 + 1 FMA forward halves, 41 packed FMA + 40 packed
+# mul/add + 7 scalar operations in the reverse pass, 12 for input conditioning
+FLOPS_FWD_EXECUTED, FLOPS_BWD_EXECUTED = 126.0 + 12.0, 379.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_binary_lut6_pipe launch: ncu on a 131072-frame launch; traffic grows with frames
+NCU_BL6_TRAFFIC_BYTES_PER_FRAME = (449.7e6 + 244.6e6) / 131072
+# the same for one k_lut6_backward_vec<BN> launch on a 65536 -> 65536 x 4096-frame layer (bytes per node-frame), or None until captured
+NCU_BWD_TRAFFIC_BYTES_PER_NF = None
 
 
 def measured_peaks():
@@ -90,36 +102,228 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def make_inputs(torch, device, frames, seed):
+def fp32_peak_flops(torch):
+    return torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count * 128 * 2 * SM_CLOCK_HZ
+
+
+class TimedOps:
+    """The operator module with CUDA events around every call of one operator (on the current stream, where it launches)."""
+
+    def __init__(self, ops, torch, name):
+        self._ops, self._torch, self._name, self.pairs, self.enabled = ops, torch, name, [], False
+
+    def __getattr__(self, attr):
+        fn = getattr(self._ops, attr)
+        if attr != self._name:
+            return fn
+
+        def timed(*a, **k):
+            if not self.enabled:
+                return fn(*a, **k)
+            e0, e1 = self._torch.cuda.Event(enable_timing=True), self._torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = fn(*a, **k)
+            e1.record()
+            self.pairs.append((e0, e1))
+            return r
+        return timed
+
+    def mean_ms(self):
+        return sum(a.elapsed_time(b) for a, b in self.pairs) / max(1, len(self.pairs))
+
+
+# ------------------------------------------------------------------------------------------------ the training step
+class TrainingWorkload:
+    """Six stacked DifferentiableLut6 layers, frame-sharded; replicated wiring / tables / Adam state, one frame shard per rank."""
+
+    def __init__(self, torch, ops, world, rank, frames_per_gpu, total_frames, binary=False, timed=None):
+        from binarybrain_b200.dist import ShardedDifferentiableLut6
+        self.torch, self.ops, self.world, self.frames, self.total = torch, ops, world, frames_per_gpu, total_frames
+        nodes, dev = TRAIN_NODES, "cuda"
+        g = torch.Generator(device=dev).manual_seed(3)          # same seed on every rank: replicated wiring and tables
+        self.layers = []
+        for _ in range(TRAIN_LAYERS):
+            idx = torch.randint(0, nodes, (nodes, 6), device=dev, generator=g).to(torch.int32)
+            W = (torch.randn((nodes, 64), device=dev, generator=g) * 0.01 + 0.5).clamp_(0, 1)
+            self.layers.append(ShardedDifferentiableLut6(idx, W, nodes, ops=timed if timed is not None else ops, binary=binary))
+        self.opt = ops.Adam([l.W for l in self.layers], [l.dW for l in self.layers])
+        gd = torch.Generator(device=dev).manual_seed(100 + rank)  # each rank draws its own frame shard
+        self.x0 = torch.rand((nodes, frames_per_gpu), device=dev, generator=gd)
+        self.target = torch.rand((nodes, frames_per_gpu), device=dev, generator=gd)
+        self.acts = [torch.empty((nodes, frames_per_gpu), device=dev) for _ in range(TRAIN_LAYERS)]
+        self.grads = [torch.empty((nodes, frames_per_gpu), device=dev) for _ in range(2)]
+        self.loss_buf = torch.zeros(1024, dtype=torch.float64, device=dev)
+
+    def step(self, x=None, target=None):
+        ops = self.ops
+        h = self.x0 if x is None else x
+        for l, a in zip(self.layers, self.acts):
+            ops.clamp_(l.W)
+            h = l.forward(h, self.frames, self.total, y=a)
+        dy, _ = ops.mean_squared_error(h, self.target if target is None else target, self.frames, batch_size=self.total,
+                                       loss_buf=self.loss_buf, dy=self.grads[0])         # mean over the GLOBAL batch
+        for k, l in enumerate(reversed(self.layers)):
+            dy = l.backward(dy, dx=self.grads[(k + 1) % 2])
+        for l in self.layers:
+            l.wait_grad()
+        self.opt.update()
+
+    # our kernels per step: per layer clamp, table conversion, statistics forward, finalize, normalise; the loss; per layer the
+    # backward statistics, finalize, table conversion, the backward kernel, the table-gradient kernel; Adam
+    LAUNCHES_PER_STEP = TRAIN_LAYERS * 5 + 1 + TRAIN_LAYERS * 5 + 1
+
+    def allreduce_bytes(self):
+        return TRAIN_LAYERS * (TRAIN_NODES * 64 * 4 + 2 * TRAIN_NODES * 2 * 8) if self.world > 1 else 0
+
+
+def timed_steps(torch, dist, fn, steps, warmup, sampler=None):
+    """`warmup` untimed calls, then exactly `steps` calls between barrier + synchronize, timed with CUDA events; max over ranks."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    if sampler:
+        sampler.start()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if dist:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms / 1e3 / steps
+
+
+def train_e2e(torch, dist, wl, steps):
+    """The training step fed from pinned host memory: every step uploads this rank's input and target shards (on a copy stream,
+    into the spare one of two device buffers, while the previous step computes) and reads the loss back."""
+    nbytes = wl.x0.numel() * 4
+    try:
+        with open("/proc/meminfo") as f:
+            avail = next(int(l.split()[1]) * 1024 for l in f if l.startswith("MemAvailable"))
+        local_ranks = int(os.environ.get("LOCAL_WORLD_SIZE", "1"))
+        if avail < 3 * 2 * nbytes * local_ranks:
+            return {"value": None, "unavailable": f"host memory: {avail >> 30} GiB available, {2 * nbytes * local_ranks >> 30} GiB of pinned buffers needed"}
+        hx = torch.empty(wl.x0.shape, dtype=torch.float32, pin_memory=True)
+        ht = torch.empty(wl.target.shape, dtype=torch.float32, pin_memory=True)
+    except (RuntimeError, OSError, StopIteration) as e:
+        return {"value": None, "unavailable": f"pinned host buffers: {e}"}
+    hx.copy_(wl.x0)
+    ht.copy_(wl.target)
+    bufs = [(wl.x0, wl.target), (torch.empty_like(wl.x0), torch.empty_like(wl.target))]
+    copy_stream = torch.cuda.Stream()
+    main = torch.cuda.current_stream()
+    ready = [torch.cuda.Event(), torch.cuda.Event()]          # upload into buffer b complete
+    freed = [torch.cuda.Event(), torch.cuda.Event()]          # the step that read buffer b has finished
+    for e in freed:
+        e.record(main)
+
+    def upload(b):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(freed[b])
+            bufs[b][0].copy_(hx, non_blocking=True)
+            bufs[b][1].copy_(ht, non_blocking=True)
+            ready[b].record(copy_stream)
+
+    losses = []
+    torch.cuda.synchronize()
+    upload(0)
+    t0 = None
+    for i in range(1 + steps):                                 # the first step is the warm-up of the pipeline
+        if i == 1:
+            torch.cuda.synchronize()
+            if dist:
+                dist.barrier()
+            t0 = time.perf_counter()
+        b = i & 1
+        if i < steps:
+            upload(b ^ 1)                                      # next step's inputs travel while this step computes
+        main.wait_event(ready[b])
+        wl.step(bufs[b][0], bufs[b][1])
+        freed[b].record(main)
+        losses.append(float(wl.loss_buf.sum().item()) / wl.total)          # device -> host read of the step's result
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    dt = time.perf_counter() - t0
+    if dist:
+        t = torch.tensor([dt], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t.item())
+    del hx, ht, bufs
+    return {"value": TRAIN_LAYERS * TRAIN_NODES * wl.total / (dt / steps), "unit": "node-frames/s", "h2d_bytes_per_step": 2 * nbytes,
+            "d2h_bytes_per_step": wl.loss_buf.numel() * 8, "steps": steps, "ms_per_step": dt / steps * 1e3,
+            "note": "per rank: input + target shard from pinned host memory each step, double-buffered on a copy stream; loss read back",
+            "last_loss": losses[-1]}
+
+
+def cpu_train_reference(steps, warmup):
+    """The reference's own DifferentiableLutN<6> (oracle/_ref: unmodified headers) forward + backward on one 65536-node layer of the
+    training workload at a reduced frame count; the C restatement when _ref is absent.  Returns (cpu_baseline object, seconds per step)."""
+    import numpy as np
+    import oracle
+    ref, port = oracle.ref, oracle.port
+    nodes, F = TRAIN_NODES, CPU_TRAIN_SAMPLE_FRAMES
+    rng = np.random.default_rng(7)
+    idx = rng.integers(0, nodes, (nodes, 6)).astype(np.int32)
+    W = np.clip(rng.normal(0.5, 0.01, (nodes, 64)), 0, 1).astype(np.float32)
+    x, dy = rng.random((nodes, F), dtype=np.float32), rng.random((nodes, F), dtype=np.float32)
+    use_ref = ref.available()
+    cores = ref.use_all_cores() if use_ref else (os.cpu_count() or 1)
+    times = []
+    for i in range(warmup + steps):
+        if use_ref:
+            r = ref.differentiable_lut6(x, idx, W, binary=False, dy=dy)
+            t = r["t_fwd"] + r["t_bwd"]
+        else:
+            t0 = time.perf_counter()
+            p = port.dl6_forward_train(x, idx, W, np.zeros(nodes, np.float32), np.ones(nodes, np.float32), binary=False)
+            port.dl6_backward(x, dy, idx, W, p["mean"], p["rstd"], nodes, binary=False)
+            t = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(t)
+    per_step = sum(times) / len(times)
+    return {"value": nodes * F / per_step, "unit": "node-frames/s", "cores": cores, "kind": "reference" if use_ref else "port",
+            "sample": f"one DifferentiableLut6 layer {nodes}->{nodes} of the six, {F} of {TRAIN_GLOBAL_BATCH} frames, forward + backward, mean of "
+                      f"{len(times)} steps; {'bb::DifferentiableLutN<6,float> (forward OpenMP over nodes, backward a serial loop)' if use_ref else 'C port, OpenMP'}"}, per_step
+
+
+# ------------------------------------------------------------------------------------------------ BinaryLut6
+def bl6_inputs(torch, device, frames, seed):
     g = torch.Generator(device=device).manual_seed(seed)
     words = frames // 32
-    x = torch.randint(-2**31, 2**31 - 1, (N_IN, words), dtype=torch.int32, device=device, generator=g)       # Bernoulli(0.5) bits
-    key = torch.rand((N_OUT, N_IN), device=device, generator=g) if N_IN <= 4096 else None
-    if key is not None:
-        idx = key.topk(6, dim=1).indices.to(torch.int32).contiguous()
-    else:   # 6 distinct inputs per node: draw, then re-draw the few rows with a repeat
-        idx = torch.randint(0, N_IN, (N_OUT, 6), device=device, generator=g)
-        for _ in range(8):
-            s = idx.sort(dim=1).values
-            bad = (s[:, 1:] == s[:, :-1]).any(dim=1)
-            if not bool(bad.any()):
-                break
-            idx[bad] = torch.randint(0, N_IN, (int(bad.sum()), 6), device=device, generator=g)
-        idx = idx.to(torch.int32).contiguous()
-    table = torch.randint(-2**31, 2**31 - 1, (N_OUT, 2), dtype=torch.int32, device=device, generator=g)
+    x = torch.randint(-2**31, 2**31 - 1, (BL6_NODES, words), dtype=torch.int32, device=device, generator=g)       # Bernoulli(0.5) bits
+    idx = torch.randint(0, BL6_NODES, (BL6_NODES, 6), device=device, generator=g)
+    for _ in range(8):   # 6 distinct inputs per node: re-draw the few rows with a repeat
+        s = idx.sort(dim=1).values
+        bad = (s[:, 1:] == s[:, :-1]).any(dim=1)
+        if not bool(bad.any()):
+            break
+        idx[bad] = torch.randint(0, BL6_NODES, (int(bad.sum()), 6), device=device, generator=g)
+    idx = idx.to(torch.int32).contiguous()
+    table = torch.randint(-2**31, 2**31 - 1, (BL6_NODES, 2), dtype=torch.int32, device=device, generator=g)
     return x, idx, table
 
 
-def cpu_reference_leg(steps, warmup, frames=CPU_SAMPLE_FRAMES):
+def bl6_cpu_reference(steps, warmup, frames):
     """BinaryLutN<6,Bit>::Forward of the unmodified reference headers (AVX2 + OpenMP), or the C port when _ref is absent."""
     import numpy as np
     from oracle import port, ref
     rng = np.random.default_rng(1)
     words = frames // 32
-    x = rng.integers(0, 2**32, (N_IN, words), dtype=np.uint64).astype(np.uint32)
-    idx = rng.integers(0, N_IN, (N_OUT, 6)).astype(np.int32)
-    table = rng.integers(-2**31, 2**31, (N_OUT, 2)).astype(np.int32)
+    x = rng.integers(0, 2**32, (BL6_NODES, words), dtype=np.uint64).astype(np.uint32)
+    idx = rng.integers(0, BL6_NODES, (BL6_NODES, 6)).astype(np.int32)
+    table = rng.integers(-2**31, 2**31, (BL6_NODES, 2)).astype(np.int32)
     use_ref = ref.available()
+    cores = ref.use_all_cores() if use_ref else (os.cpu_count() or 1)
     times = []
     for i in range(warmup + steps):
         if use_ref:
@@ -130,16 +334,64 @@ def cpu_reference_leg(steps, warmup, frames=CPU_SAMPLE_FRAMES):
             t = time.perf_counter() - t0
         if i >= warmup:
             times.append(t)
-    cores = ref.num_threads() if use_ref else (os.cpu_count() or 1)
     per_step = sum(times) / len(times)
-    return {"value": N_OUT * frames / per_step, "unit": "node-frames/s", "cores": cores, "kind": "reference" if use_ref else "port",
-            "sample": f"BinaryLut6 {N_IN}->{N_OUT} nodes, {frames} of {FRAMES} frames per step, mean of {len(times)} steps, "
-                      f"{'bb::BinaryLutN<6,Bit>::Forward AVX2+OpenMP' if use_ref else 'C port, OpenMP'}"}, per_step
+    return {"value": BL6_NODES * frames / per_step, "unit": "node-frames/s", "cores": cores, "kind": "reference" if use_ref else "port",
+            "sample": f"BinaryLut6 {BL6_NODES}->{BL6_NODES} nodes, {frames} of {BL6_FRAMES} frames per step, mean of {len(times)} steps, "
+                      f"{'bb::BinaryLutN<6,Bit>::Forward AVX2+OpenMP' if use_ref else 'C port, OpenMP'}"}
+
+
+def binary_lut6_section(torch, ops, dist, world, rank, steps, warmup, frames, extras):
+    """BinaryLut6 bit-packed inference forward, 16384 -> 16384 nodes, `frames` frames per GPU (frames shard with no collective)."""
+    x, idx, table = bl6_inputs(torch, "cuda", frames, seed=1 + rank)
+    y = torch.empty_like(x)
+    sec = timed_steps(torch, dist, lambda: ops.binary_lut6_forward(x, idx, table, frames, y=y), steps, warmup)
+    hbm, which, _ = measured_peaks()
+    algo_bytes = frames * (BL6_NODES + BL6_NODES) / 8 + 32 * BL6_NODES            # x + y bit rows, wiring + table per node
+    achieved = algo_bytes / sec / 1e9
+    out = {"workload": f"BinaryLut6 forward {BL6_NODES}->{BL6_NODES} nodes, {frames} frames per GPU bit-packed (x, y {frames * BL6_NODES // 8 >> 20} MiB each; "
+                       "inputs exceed L2, no flush)", "metric": "BinaryLut6 forward node-frames/s", "value": world * BL6_NODES * frames / sec,
+           "unit": "node-frames/s", "ms_per_step": sec * 1e3, "steps": steps, "scaling": "weak", "dtype": "u32 bit-packed", "gpu_launches": steps,
+           "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                        "traffic": NCU_BL6_TRAFFIC_BYTES_PER_FRAME * frames, "peak_source": f"of {which}", "kernel": "k_binary_lut6_pipe",
+                        "algorithmic_bytes_per_launch": algo_bytes}}
+    if extras and world == 1:
+        # end to end through the operator with host buffers: H2D of x, kernel, D2H of y, every step (chunk-pipelined inside the call)
+        hx = torch.empty(x.shape, dtype=torch.int32).pin_memory()
+        hy = torch.empty(y.shape, dtype=torch.int32).pin_memory()
+        hx.copy_(x)
+        torch.cuda.synchronize()
+        k = max(2, min(steps, 5))
+        hidx, htab = idx.cpu(), table.cpu()
+        for i in range(1 + k):
+            if i == 1:
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+            ops.binary_lut6_forward_host(hx, hidx, htab, frames, y=hy)
+        dt = time.perf_counter() - t0
+        out["e2e"] = {"value": BL6_NODES * frames / (dt / k), "unit": "node-frames/s", "h2d_bytes_per_step": hx.numel() * 4,
+                      "d2h_bytes_per_step": hy.numel() * 4, "steps": k}
+        del hx, hy
+        out["cpu_baseline"] = bl6_cpu_reference(3, 1, frames)
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ single operators
+def time_op(torch, fn, steps):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / 1e3 / steps
 
 
 def fp32_cpu_reference(nodes=8192):
     """The reference's own CPU code (oracle/_ref: AVX2 + OpenMP StochasticLutN, scalar DifferentiableLutN whose backward is serial) on
-    the fp32 operators, same node count, at a reduced frame count (stated in the result; never extrapolated)."""
+    the fp32 operators at a reduced size (stated in the result; never extrapolated)."""
     import numpy as np
     import oracle
     ref = oracle.ref
@@ -148,7 +400,7 @@ def fp32_cpu_reference(nodes=8192):
     rng = np.random.default_rng(7)
     idx = np.stack([rng.permutation(nodes)[:6] for _ in range(nodes)]).astype(np.int32)
     W = np.clip(rng.normal(0.5, 0.01, (nodes, 64)), 0, 1).astype(np.float32)
-    out = {"cores": ref.num_threads(), "kind": "reference", "unit": "node-frames/s"}
+    out = {"cores": ref.use_all_cores(), "kind": "reference", "unit": "node-frames/s", "nodes": nodes}
     F = 1024
     x, dy = rng.random((nodes, F), dtype=np.float32), rng.random((nodes, F), dtype=np.float32)
     r = ref.stochastic_lut6(x, idx, W, dy=dy)                        # warm-up (first-touch of the buffers, OpenMP team start)
@@ -163,10 +415,12 @@ def fp32_cpu_reference(nodes=8192):
     return out
 
 
-def fp32_section(torch, ops, steps):
-    """SL6 / DL6 forward and backward on one 8192 -> 8192 node layer, 16384 frames (x, y, dy, dx: 512 MiB each, > L2)."""
-    I = O = 8192
-    F = 16384
+def fp32_section(torch, ops, steps, nodes=TRAIN_NODES, frames=4096):
+    """SL6 / DL6 forward and backward on the layer the training step runs per GPU at eight GPUs: 65536 -> 65536 nodes, 4096 frames
+    (x, y, dy, dx: 1 GiB each, larger than L2).  Fractions: `frac_of_roofline` on the algorithmic flops / bytes of the 63-interpolation
+    formulation, `executed_fp32_frac` on the flops the centred-polynomial kernels really issue."""
+    I = O = nodes
+    F = frames
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(2)
     x = torch.rand((I, F), device=dev, generator=g)
@@ -182,100 +436,33 @@ def fp32_section(torch, ops, steps):
     def dl_fwd():
         state["y"], state["mean"], state["rstd"] = ops.differentiable_lut6_forward_training(x, idx, W, rm, rv, F, y=y, binary=False)
 
-    cases = {
-        "sl6_forward":  (lambda: ops.stochastic_lut6_forward(x, idx, W, F, y=y), 126.0, 8.0),
-        "sl6_backward": (lambda: ops.stochastic_lut6_backward(x, dy, idx, W, dW, I, F, dx=dx), 505.0, 12.0),
-        "dl6_forward_training": (dl_fwd, 136.0, 16.0),
+    cases = {   # name: (callable, algorithmic flops, algorithmic bytes, executed flops) per node-frame
+        "sl6_forward":  (lambda: ops.stochastic_lut6_forward(x, idx, W, F, y=y), FLOPS_FWD, 8.0, FLOPS_FWD_EXECUTED),
+        "sl6_backward": (lambda: ops.stochastic_lut6_backward(x, dy, idx, W, dW, I, F, dx=dx), FLOPS_BWD, 12.0, FLOPS_BWD_EXECUTED),
+        "dl6_forward_training": (dl_fwd, FLOPS_FWD + 10.0, 16.0, FLOPS_FWD_EXECUTED + 10.0),
+        # statistics pass (a second evaluation of the tree) + apply pass
         "dl6_backward": (lambda: ops.differentiable_lut6_backward(x, dy, idx, W, dW, state["mean"], state["rstd"], I, F, dx=dx, binary=False),
-                         525.0 + 126.0, 24.0),
+                         525.0 + FLOPS_FWD, 24.0, FLOPS_BWD_EXECUTED + 10.0 + FLOPS_FWD_EXECUTED + 10.0),
     }
-    props = torch.cuda.get_device_properties(0)
     hbm, which, _ = measured_peaks()
-    out = {"layer": f"{I}->{O} nodes, {F} frames", "fp32_peak_note": "SMs*128 lanes*2*sm_clock at the max SM clock"}
-    fp32_peak = props.multi_processor_count * 128 * 2 * 1.965e9
-    for name, (fn, flops, bytes_) in cases.items():
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        sec = e0.elapsed_time(e1) / 1e3 / steps
+    fp32_peak = fp32_peak_flops(torch)
+    out = {"layer": f"{I}->{O} nodes, {F} frames", "fp32_peak_tflops": fp32_peak / 1e12,
+           "fp32_peak_note": "SMs * 128 lanes * 2 * 1.965 GHz (clocks.max.sm)", "hbm_peak": f"{hbm} GB/s of {which}"}
+    for name, (fn, flops, bytes_, flops_exec) in cases.items():
+        sec = time_op(torch, fn, steps)
         nf = O * F / sec
         t_fp, t_hbm = flops / fp32_peak, bytes_ / (hbm * 1e9)
         out[name] = {"node_frames_per_s": nf, "ms": sec * 1e3, "bound": "fp32" if t_fp > t_hbm else "hbm",
                      "frac_of_roofline": nf * max(t_fp, t_hbm), "fp32_frac": nf * t_fp, "hbm_frac": nf * t_hbm,
-                     "algorithmic_flops_per_nf": flops, "algorithmic_bytes_per_nf": bytes_}
-    out["hbm_peak"] = f"{hbm} GB/s of {which}"
+                     "executed_fp32_frac": nf * flops_exec / fp32_peak,
+                     "algorithmic_flops_per_nf": flops, "algorithmic_bytes_per_nf": bytes_, "executed_flops_per_nf": flops_exec}
     return out
 
 
-def train_section(torch, ops, dist, world, rank, steps, binary=False):
-    """Config-4 style training step, frame-sharded: 6 stacked DifferentiableLut6 layers of TRAIN_NODES nodes (fp32, batch norm on),
-    TRAIN_FRAMES frames per GPU (global batch = that x world), MSE loss on the last layer, backward with the per-layer dW all-reduce
-    overlapped with the next layer's backward, Adam.  Reports forward+backward node-frames/s over all ranks."""
-    from binarybrain_b200.dist import ShardedDifferentiableLut6
-    nodes, frames, layers_n = TRAIN_NODES, TRAIN_FRAMES, 6
-    dev = "cuda"
-    g = torch.Generator(device=dev).manual_seed(3)          # same seed on every rank: replicated wiring and tables
-    layers = []
-    for _ in range(layers_n):
-        idx = torch.randint(0, nodes, (nodes, 6), device=dev, generator=g).to(torch.int32)
-        W = (torch.randn((nodes, 64), device=dev, generator=g) * 0.01 + 0.5).clamp_(0, 1)
-        layers.append(ShardedDifferentiableLut6(idx, W, nodes, binary=binary))
-    opt = ops.Adam([l.W for l in layers], [l.dW for l in layers])
-    gd = torch.Generator(device=dev).manual_seed(100 + rank)  # each rank draws its own frame shard
-    x0 = torch.rand((nodes, frames), device=dev, generator=gd)
-    target = torch.rand((nodes, frames), device=dev, generator=gd)
-    total = frames * world
-    acts = [torch.empty((nodes, frames), device=dev) for _ in range(layers_n)]
-    grads = [torch.empty((nodes, frames), device=dev) for _ in range(2)]
-    loss_buf = torch.zeros(1024, dtype=torch.float64, device=dev)
-
-    def step():
-        h = x0
-        for l, a in zip(layers, acts):
-            ops.clamp_(l.W)
-            h = l.forward(h, frames, total, y=a)
-        dy, _ = ops.mean_squared_error(h, target, frames, batch_size=total, loss_buf=loss_buf, dy=grads[0])   # mean over the GLOBAL batch
-        for k, l in enumerate(reversed(layers)):
-            dy = l.backward(dy, dx=grads[(k + 1) % 2])
-        for l in layers:
-            l.wait_grad()
-        opt.update()
-
-    for _ in range(2):
-        step()
-    torch.cuda.synchronize()
-    if dist:
-        dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    if dist:
-        dist.barrier()
-    ms = e0.elapsed_time(e1)
-    if dist:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    sec = ms / 1e3 / steps
-    return {"workload": f"config 4 (frame-sharded training): {layers_n} x DifferentiableLut6 {nodes}->{nodes}, {frames} frames per GPU "
-                        f"(global batch {total}), fp32{', binary mode' if binary else ''}, batch norm, MSE, Adam; dW all-reduce overlapped with backward",
-            "node_frames_per_s": layers_n * nodes * total / sec, "ms_per_step": sec * 1e3, "steps": steps, "n_gpus": world,
-            "allreduce_bytes_per_step": layers_n * (nodes * 64 * 4 + 2 * nodes * 2 * 8) if world > 1 else 0}
-
-
-def build_config3_network(dev, seed=5, ops=None):
-    """BASELINE config 3, the LUT-CNN, from the host-side classes: two conv blocks (each two bb::Convolution2d of per-pixel
-    DifferentiableLut6 layers with 3x3 'same' lowering, then 2x2 MaxPooling) and a dense head 4096 -> 1024 -> 420 -> 70 -> 10.
-    Random 6-distinct wiring, tables N(0.5, 0.01), fp32, batch norm on."""
+def build_lut_cnn(dev, seed=5, ops=None):
+    """The LUT-CNN from the host-side classes: two conv blocks (each two Convolution2d of per-pixel DifferentiableLut6 layers with 3x3
+    'same' lowering, then 2x2 MaxPooling) and a dense head 4096 -> 1024 -> 420 -> 70 -> 10.  Random 6-distinct wiring, tables
+    N(0.5, 0.01), fp32, batch norm on."""
     import torch
     from binarybrain_b200.conv import Convolution2d, MaxPooling, Sequential
     from binarybrain_b200.dist import ShardedDifferentiableLut6
@@ -296,10 +483,10 @@ def build_config3_network(dev, seed=5, ops=None):
 
 
 def cnn_section(torch, ops, steps):
-    """Config 3: LUT-CNN forward + backward on 256 synthetic 3x32x32 images (one GPU).  Node-frames count the LUT evaluations of
-    one forward pass (per-pixel layers run on 256 * oh * ow frames)."""
+    """LUT-CNN forward + backward on 256 synthetic 3x32x32 images (one GPU).  Node-frames count the LUT evaluations of one forward
+    pass (per-pixel layers run on 256 * oh * ow frames)."""
     B = 256
-    net = build_config3_network(torch.device("cuda"))
+    net = build_lut_cnn(torch.device("cuda"))
     x = torch.rand((3 * 32 * 32, B), device="cuda")
     dy = torch.rand((10, ops.fp32_stride(B)), device="cuda")
 
@@ -309,26 +496,17 @@ def cnn_section(torch, ops, steps):
         net.forward(x, B)
         net.backward(dy)
 
-    for _ in range(2):
-        step()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    sec = e0.elapsed_time(e1) / 1e3 / steps
+    sec = time_op(torch, step, steps)
     nf = B * (1024 * (216 + 36 + 32) * 2 + 256 * (384 + 64) * 2 + (1024 + 420 + 70 + 10))
-    return {"workload": "config 3 (LUT-CNN): 3x32x32 images, batch 256, 2 conv blocks of per-pixel DifferentiableLut6 trees with 3x3 Im2Col / "
+    return {"workload": "LUT-CNN: 3x32x32 images, batch 256, 2 conv blocks of per-pixel DifferentiableLut6 trees with 3x3 Im2Col / "
                         "Col2Im and 2x2 MaxPooling, dense head 4096->1024->420->70->10, fp32, batch norm; forward + backward",
             "node_frames_per_s": nf / sec, "ms_per_step": sec * 1e3, "steps": steps, "n_gpus": 1}
 
 
 def operators_section(torch, ops, steps):
-    """Every other operator of the path on the same 8192 -> 8192 x 16384-frame layer (bit inputs: same node counts, 16384 frames), each with
-    its algorithmic bytes / flops per node-frame and the fraction of max(HBM, FP32) roofline time, plus the lowering operators at a config-3
-    block shape and Adam.  One launch sequence per operator call, timed with CUDA events over `steps` calls after 3 warm-ups."""
+    """Every other operator of the path on an 8192 -> 8192 x 16384-frame layer (bit inputs: same node counts, 16384 frames), each with
+    its algorithmic bytes / flops per node-frame and the fraction of max(HBM, FP32) roofline time, plus the lowering operators at the
+    LUT-CNN's first conv block shape and Adam.  One launch sequence per operator call, timed with CUDA events over `steps` calls."""
     I = O = 8192
     F = 16384
     dev = "cuda"
@@ -355,7 +533,7 @@ def operators_section(torch, ops, steps):
         st["sy"], st["smean"], st["srstd"] = ops.stochastic_bn_forward_training(xf, rm, rv, F)
 
     adam = ops.Adam([W], [dW])
-    # lowering at the first conv block of config 3: 32 channels, 32x32, batch 256
+    # lowering at the first conv block of the LUT-CNN: 32 channels, 32x32, batch 256
     c, hw, B = 32, 32, 256
     img = torch.rand((c * hw * hw, B), device=dev, generator=g)
     cols = ops.im2col_forward(img, B, c, hw, hw, 3, 3, padding="same")
@@ -391,23 +569,13 @@ def operators_section(torch, ops, steps):
         "maxpool_forward_fp32": (lambda: ops.maxpool_forward(img, B, c, hw, hw, 2, 2), px, 4.0 + 2.0, 1.0),
         "maxpool_backward_fp32": (lambda: ops.maxpool_backward(am, gp, B, c, hw, hw, 2, 2), px, 4.0 + 2.0, 0.0),
     }
-    props = torch.cuda.get_device_properties(0)
     hbm, which, _ = measured_peaks()
-    fp32_peak = props.multi_processor_count * 128 * 2 * 1.965e9
+    fp32_peak = fp32_peak_flops(torch)
     out = {"layer": f"{I}->{O} nodes, {F} frames (bit inputs: same frames, 32 per word); lowering: {c} channels {hw}x{hw}, batch {B}, 3x3 same / 2x2 pool",
            "unit": "node-frames (LUT, SBN), table entries (Adam), output elements (lowering: Im2Col counts the 9x expanded buffer)",
            "hbm_peak": f"{hbm} GB/s of {which}"}
     for name, (fn, units, bytes_, flops) in cases.items():
-        for _ in range(3):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        sec = e0.elapsed_time(e1) / 1e3 / steps
+        sec = time_op(torch, fn, steps)
         t_fp, t_hbm = flops / fp32_peak, bytes_ / (hbm * 1e9)
         out[name] = {"units_per_s": units / sec, "ms": sec * 1e3, "bound": "fp32" if t_fp > t_hbm else "hbm",
                      "frac_of_roofline": units / sec * max(t_fp, t_hbm), "algorithmic_bytes_per_unit": round(bytes_, 4),
@@ -415,29 +583,46 @@ def operators_section(torch, ops, steps):
     return out
 
 
+METRIC = "LUT6 node-frames/s, training step forward+backward fp32 (DifferentiableLut6 x6, 65536 nodes)"
+
+
+def train_config(world, frames):
+    return {"workload": f"frame-sharded training step: {TRAIN_LAYERS} x DifferentiableLut6 {TRAIN_NODES}->{TRAIN_NODES}, fp32, batch norm, MSE, Adam; "
+                        f"global batch G = {frames * world} frames per step at every GPU count (strong scaling), {frames} frames per GPU",
+            "global_batch": frames * world, "frames_per_gpu": frames, "sharding": "frames; all-reduce of batch-norm sums (2 per layer, blocking) and of "
+            "the table gradients (1 per layer, overlapped with the next layer's backward)",
+            "l2": f"every frame buffer ({TRAIN_NODES * frames * 4 >> 20} MiB) exceeds L2 (126 MB); no flush"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--frames", type=int, default=FRAMES, help="frames per GPU (default: the full 2^20 of config 1)")
-    ap.add_argument("--no-extras", action="store_true", help="skip the fp32 section, the e2e leg and the CPU baseline")
-    ap.add_argument("--fp32-only", action="store_true", help="run and print only the fp32 section (profiling aid)")
+    ap.add_argument("--global-batch", type=int, default=TRAIN_GLOBAL_BATCH, help="frames per step over all GPUs (default: 32768)")
+    ap.add_argument("--bl6-frames", type=int, default=BL6_FRAMES, help="frames per GPU of the BinaryLut6 section (default: 2^20)")
+    ap.add_argument("--no-extras", action="store_true", help="headline only: no e2e leg, no sub-sections, no CPU baseline")
+    ap.add_argument("--only", default=None, choices=["train", "binary_lut6", "fp32"], help="run and print one section (profiling aid)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    config = {"workload": f"config 1: BinaryLut6 forward {N_IN}->{N_OUT} nodes, 2^20 frames per GPU bit-packed (x, y 2 GiB each)",
-              "frames_per_gpu": args.frames, "sharding": "frames, no collective", "l2": "inputs (2 GiB) exceed L2 (126 MB); no flush"}
+    if args.global_batch % (32 * world) != 0:
+        raise SystemExit("--global-batch must be a multiple of 32 frames per GPU")
+    frames = args.global_batch // world
+    config = train_config(world, frames)
 
     if args.impl == "reference":
         if rank != 0:
             return 0
-        base, per_step = cpu_reference_leg(args.steps, args.warmup)
-        line = {"impl": "reference", "metric": "BinaryLut6 forward node-frames/s", "value": base["value"], "unit": "node-frames/s",
+        # a launcher may have exported OMP_NUM_THREADS=1 (torch.distributed.run does): the CPU arm uses every core it may run on
+        ncores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+        os.environ["OMP_NUM_THREADS"] = str(ncores)
+        base, per_step = cpu_train_reference(args.steps, args.warmup)
+        line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": "node-frames/s",
                 "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "u32 bit-packed", "data": "synthetic", "config": config,
+                "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
                 "cpu_baseline": base, "e2e": {"value": base["value"], "unit": "node-frames/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
         print(json.dumps(line))
@@ -456,98 +641,79 @@ def main():
         import datetime
         # a collective that is not matched on every rank fails after three minutes instead of holding the GPUs for NCCL's default ten
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=180))
-    if args.fp32_only:
+    W = max(args.warmup, 3)
+    if args.only == "fp32":
         print(json.dumps({"fp32": fp32_section(torch, ops, max(1, args.steps))}))
         return 0
-    W = max(args.warmup, 3)
-    frames = args.frames
-    x, idx, table = make_inputs(torch, "cuda", frames, seed=1 + rank)
-    y = torch.empty_like(x)
+    if args.only == "binary_lut6":
+        print(json.dumps({"binary_lut6": binary_lut6_section(torch, ops, dist, world, rank, args.steps, W, args.bl6_frames, False)}))
+        return 0
 
-    def step():
-        ops.binary_lut6_forward(x, idx, table, frames, y=y)
-
+    # ---- headline: the training step
+    timed = TimedOps(ops, torch, "dl6_backward_apply")
+    wl = TrainingWorkload(torch, ops, world, rank, frames, frames * world, timed=timed)
     for _ in range(W):
-        step()
-    torch.cuda.synchronize()
-    if dist:
-        dist.barrier()
+        wl.step()
+    timed.enabled = True
     sampler = ClockSampler(local_rank)
-    sampler.start()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    if dist:
-        dist.barrier()
-    ms = e0.elapsed_time(e1)
-    # keep the sampler alive long enough to have seen the loaded clocks at least a few times
+    sec = timed_steps(torch, dist, wl.step, args.steps, 0, sampler)
+    timed.enabled = False
     t_keep = time.time()
-    while len(sampler.rows) < 3 and time.time() - t_keep < 1.0:
-        step()
+    while len(sampler.rows) < 3 and time.time() - t_keep < 1.5:      # let the sampler see the loaded clocks at least a few times
+        wl.step()
         torch.cuda.synchronize()
     clocks = sampler.stop()
-    if dist:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    sec_per_step = ms / 1e3 / args.steps
-    value = world * N_OUT * frames / sec_per_step
-
+    value = TRAIN_LAYERS * TRAIN_NODES * frames * world / sec
     hbm, which, _ = measured_peaks()
-    algo_bytes = frames * (N_IN + N_OUT) / 8 + 32 * N_OUT            # x + y bit rows, wiring + table per node
-    achieved = algo_bytes / sec_per_step / 1e9
-    line = {"metric": "BinaryLut6 forward node-frames/s", "value": value, "unit": "node-frames/s", "n_gpus": world, "steps": args.steps,
-            "warmup": W, "ms_per_step": sec_per_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "u32 bit-packed", "data": "synthetic", "config": config, "clocks": clocks, "gpu_launches": args.steps,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_FRAME * frames, "peak_source": f"of {which}", "kernel": "k_binary_lut6",
-                         "algorithmic_bytes_per_launch": algo_bytes}}
+    fp32_peak = fp32_peak_flops(torch)
+    k_ms = timed.mean_ms()                                           # one backward operator call: dx clear, finalize, table conversion, the kernel, dW
+    k_nf = TRAIN_NODES * frames
+    achieved_tf = FLOPS_BWD * k_nf / (k_ms / 1e3) / 1e12
+    line = {"metric": METRIC, "value": value, "unit": "node-frames/s", "n_gpus": world, "steps": args.steps, "warmup": W,
+            "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config, "clocks": clocks, "gpu_launches": args.steps * TrainingWorkload.LAUNCHES_PER_STEP,
+            "allreduce_bytes_per_step": wl.allreduce_bytes(),
+            "roofline": {"bound": "fp32", "kernel": "k_lut6_backward_vec<BN> (bbcu_fp32_DifferentiableLut6_BackwardApply)",
+                         "achieved": achieved_tf, "peak": fp32_peak / 1e12, "unit": "TFLOP/s", "frac": achieved_tf * 1e12 / fp32_peak,
+                         "executed_frac": (FLOPS_BWD_EXECUTED + 10.0) * k_nf / (k_ms / 1e3) / fp32_peak,
+                         "peak_source": "FP32 CUDA-core peak = SMs * 128 lanes * 2 * 1.965 GHz; the path has no tensor-core work",
+                         "ms_per_launch": k_ms, "launches_timed": len(timed.pairs), "node_frames_per_launch": k_nf,
+                         "algorithmic_flops_per_nf": FLOPS_BWD, "algorithmic_bytes_per_nf": 12.0,
+                         "hbm_achieved_gbs": 12.0 * k_nf / (k_ms / 1e3) / 1e9, "hbm_peak_gbs": hbm, "hbm_frac": 12.0 * k_nf / (k_ms / 1e3) / 1e9 / hbm,
+                         "hbm_peak_source": f"of {which}",
+                         "traffic": None if NCU_BWD_TRAFFIC_BYTES_PER_NF is None else NCU_BWD_TRAFFIC_BYTES_PER_NF * k_nf}}
 
     if not args.no_extras:
-        # end to end through the operator with host buffers: H2D of x, kernel, D2H of y, every step
-        hx = torch.empty(x.shape, dtype=torch.int32).pin_memory()
-        hy = torch.empty(y.shape, dtype=torch.int32).pin_memory()
-        hx.copy_(x)
-        torch.cuda.synchronize()
-        k = max(2, min(args.steps, 5))
-        hidx, htab = idx.cpu(), table.cpu()
-        for i in range(1 + k):
-            if i == 1:
-                torch.cuda.synchronize()
-                if dist:
-                    dist.barrier()
-                t0 = time.perf_counter()
-            # one call through the C ABI with HOST buffers: upload of x, kernel and download of y happen inside (chunk-pipelined)
-            ops.binary_lut6_forward_host(hx, hidx, htab, frames, y=hy)
+        line["e2e"] = train_e2e(torch, dist, wl, max(2, min(args.steps, 5)))
+    del wl
+    torch.cuda.empty_cache()
+    if args.only == "train" or args.no_extras:
         if dist:
             dist.barrier()
-        dt = time.perf_counter() - t0
-        if dist:
-            t = torch.tensor([dt], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            dt = float(t.item())
-        line["e2e"] = {"value": world * N_OUT * frames / (dt / k), "unit": "node-frames/s", "h2d_bytes_per_step": hx.numel() * 4,
-                       "d2h_bytes_per_step": hy.numel() * 4, "steps": k}
-        del hx, hy, x, y
-        torch.cuda.empty_cache()
-        line["train"] = train_section(torch, ops, dist, world, rank, max(2, min(args.steps, 5)))
-        torch.cuda.empty_cache()
-        # the same step in the reference's default binary mode (inputs 0.5 +- bias by x > 0.5, outputs binarised)
-        line["train_binary"] = train_section(torch, ops, dist, world, rank, max(2, min(args.steps, 5)), binary=True)
+            dist.destroy_process_group()
         if rank == 0:
-            torch.cuda.empty_cache()
-            line["fp32"] = fp32_section(torch, ops, max(3, min(args.steps, 10)))
-            torch.cuda.empty_cache()
-            line["cnn"] = cnn_section(torch, ops, max(2, min(args.steps, 5)))
-            torch.cuda.empty_cache()
-            line["operators"] = operators_section(torch, ops, max(3, min(args.steps, 10)))
-            if world == 1:
-                line["cpu_baseline"], _ = cpu_reference_leg(3, 1)
-                line["fp32"]["cpu_baseline"] = fp32_cpu_reference()
+            print(json.dumps(line))
+        return 0
+
+    k = max(2, min(args.steps, 5))
+    line["binary_lut6"] = binary_lut6_section(torch, ops, dist, world, rank, max(3, min(args.steps, 10)), 3, args.bl6_frames, True)
+    torch.cuda.empty_cache()
+    # the same six layers in the reference's binary mode (inputs 0.5 +- bias by x > 0.5, outputs binarised), 4096 frames per GPU
+    wb = TrainingWorkload(torch, ops, world, rank, 4096, 4096 * world, binary=True)
+    sec_b = timed_steps(torch, dist, wb.step, k, 2)
+    line["train_binary"] = {"workload": f"{TRAIN_LAYERS} x DifferentiableLut6 {TRAIN_NODES}->{TRAIN_NODES}, binary mode, 4096 frames per GPU (weak scaling)",
+                            "node_frames_per_s": TRAIN_LAYERS * TRAIN_NODES * 4096 * world / sec_b, "ms_per_step": sec_b * 1e3, "steps": k, "n_gpus": world}
+    del wb
+    torch.cuda.empty_cache()
+    if rank == 0:
+        line["fp32"] = fp32_section(torch, ops, max(3, min(args.steps, 10)))
+        torch.cuda.empty_cache()
+        line["cnn"] = cnn_section(torch, ops, k)
+        torch.cuda.empty_cache()
+        line["operators"] = operators_section(torch, ops, max(3, min(args.steps, 10)))
+        if world == 1:
+            line["cpu_baseline"], _ = cpu_train_reference(2, 1)
+            line["fp32"]["cpu_baseline"] = fp32_cpu_reference()
     if dist:
         dist.barrier()
         dist.destroy_process_group()

@@ -57,3 +57,35 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
 __device__ __forceinline__ void proxy_fence_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 }   // namespace bb200
+
+// ---------------------------------------------------------------------------------------------------
+// Per-thread 16-byte asynchronous copies (global -> shared, bypassing L1) with commit / wait groups.  A lane that copies only
+// bytes it will read back itself needs no barrier: cp_async_wait<N>() makes its own groups (all but the N newest) visible to it.
+// `valid` false writes 16 zero bytes without reading the source.
+// ---------------------------------------------------------------------------------------------------
+namespace bb200 {
+
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src, bool valid)
+{
+    const uint32_t src_bytes = valid ? 16u : 0u;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(smem_dst)), "l"(__cvta_generic_to_global(gmem_src)), "r"(src_bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Vector reductions into global memory (resolved in L2): 16 / 8 bytes per lane, address aligned to the vector size.
+__device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float c, float d)
+{
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(__cvta_generic_to_global(addr)), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__device__ __forceinline__ void red_add_v2(float *addr, float a, float b)
+{
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(__cvta_generic_to_global(addr)), "f"(a), "f"(b) : "memory");
+}
+
+}   // namespace bb200

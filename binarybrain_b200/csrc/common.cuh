@@ -12,11 +12,12 @@ namespace bb200 {
 
 #define BB200_REQUIRE_PTR(p)   do { if ((p) == nullptr) return BBCU_ERR_NULL_POINTER; } while (0)
 #define BB200_REQUIRE(cond, e) do { if (!(cond)) return (e); } while (0)
-#define BB200_CUDA(call)       do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return (int)e_; } while (0)
+#define BB200_CUDA(call)       do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { cudaGetLastError(); return (int)e_; } } while (0)
 
 constexpr int kFramesPerIterHost = 128;   // frames one warp covers per iteration (32 lanes x 4)
 
-inline int launch_status() { return (int)cudaPeekAtLastError(); }
+// Status of the launches just made: a launch error is reported once and cleared, so it cannot resurface in a later call.
+inline int launch_status() { return (int)cudaGetLastError(); }
 
 // Device properties read once per device.
 struct DeviceInfo {
@@ -63,7 +64,7 @@ int f32_binary_forward_by_table(int mode, const float *x, float *y, const int *i
                                 float *rvar, float gamma, float beta, float momentum, float bias, int O, int F, long long fs, int lut_binarize,
                                 cudaStream_t st);
 
-// Per-device int in global memory (zero until a kernel records a fault); allocated once, never freed.
+// Per-device int in the library's device image (zero until a kernel records a fault); nothing is allocated for it.
 int *fault_word();
 
 inline cudaStream_t as_stream(bbcu_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }

@@ -10,6 +10,7 @@
 // walk the node groups of the SAME frame tile, so in the forward kernels the input rows of that tile are fetched
 // from HBM once or twice and otherwise hit in L2 for the other nodes that read them.
 // Bit-input operators go through per-node pattern tables instead (binary_mode.cu); the kernels here are their fallback.
+#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -701,6 +702,244 @@ k_lut6_backward(const BwdArgs a)
 }
 
 // ---------------------------------------------------------------------------------------------
+// Persistent, vectorised backward for fp32 frames whose rows start on 16-byte boundaries (the launcher's default).
+//
+// Work item = (frame tile of a.T frames, group of 8 nodes), walked in tile-major order by one CTA per SM, so the CTAs in flight
+// sweep the node groups of one tile together: the tile's x rows come from HBM once, the other consumers of a row hit L2, and the
+// dx reductions of a row meet in L2 too.  The tile is therefore sized for L2, and what a wide tile used to amortise is made cheap
+// instead:
+//   * the per-node table arrives ready to use (k_table_halves has converted every table once per launch);
+//   * a warp streams its item in 128-frame chunks through a three-stage ring in shared memory: every lane copies, with 16-byte
+//     cp.async, the four consecutive frames of each of the six input rows and of dy that it will itself use, two chunks ahead
+//     of the arithmetic, so no lane ever waits for a barrier or for another lane, and the prefetch costs no registers;
+//   * a lane's four frames leave as one 128-bit reduction per input row (red.global.add.v4.f32);
+//   * at the end of an item the 64 per-lane gradient sums are added across lanes through a padded transpose in shared memory
+//     (16 stores, 32 loads and 32 packed adds per lane instead of 62 shuffles with two selects each) and leave as one 8-byte
+//     reduction per lane into the coefficient-gradient scratch dC, which k_coeff_grads_to_dw maps to table gradients once per
+//     launch.
+// dx rows must be zero on entry.
+// ---------------------------------------------------------------------------------------------
+constexpr int kBvStages     = 3;
+constexpr int kBvRowBytes   = kFramesPerIter * 4;                 // one row segment of a chunk
+constexpr int kBvStageBytes = 7 * kBvRowBytes;                    // six input rows and dy
+constexpr int kBvTabSlots   = 3;                                  // the copy side runs at most two items ahead of the arithmetic
+constexpr int kBvTabBytes   = 16 * 16;
+constexpr int kBvTrStride   = 68;                                 // floats per lane row of the transpose: 64 + 4 keeps 128-bit stores and
+constexpr int kBvTrBytes    = 32 * kBvTrStride * 4;               // 64-bit loads free of bank conflicts
+constexpr int kBvWarpBytes  = kBvStages * kBvStageBytes + kBvTabSlots * kBvTabBytes + kBvTrBytes;
+constexpr int kBvSmem       = kWarpsPerCta * kBvWarpBytes;
+static_assert(kBvSmem <= 227 * 1024, "one CTA per SM must fit");
+
+// Every node's table in the half-packed form of lut6_forward_keep_halves: 16 x (c[2k], c[2k+32], c[2k+1], c[2k+33]).
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+k_table_halves(const float *__restrict__ W, float4 *__restrict__ coef, int O, int lut_binarize)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int node = blockIdx.x * kWarpsPerCta + warp;
+    if (node >= O) return;
+    float2 v = reinterpret_cast<const float2 *>(W + (size_t)node * 64)[lane];
+    if (lut_binarize) { v.x = v.x > 0.5f ? 1.0f : 0.0f; v.y = v.y > 0.5f ? 1.0f : 0.0f; }
+    v = table_to_coeffs(v, lane);
+    const float hx = __shfl_down_sync(kFull, v.x, 16), hy = __shfl_down_sync(kFull, v.y, 16);
+    if (lane < 16) coef[(size_t)node * 16 + lane] = make_float4(v.x, hx, v.y, hy);
+}
+
+// dW += adjoint butterfly of the coefficient gradients (dC in the half-packed layout of k_table_halves); one warp per node.
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+k_coeff_grads_to_dw(const float4 *__restrict__ dC, float *__restrict__ dW, int O)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int node = blockIdx.x * kWarpsPerCta + warp;
+    if (node >= O) return;
+    const float4 e = dC[(size_t)node * 16 + (lane & 15)];
+    const float2 g = lane < 16 ? make_float2(e.x, e.z) : make_float2(e.y, e.w);        // coefficients 2 lane, 2 lane + 1
+    const float2 gw = coeff_grads_to_table(g, lane);
+    float2 *dst = reinterpret_cast<float2 *>(dW + (size_t)node * 64) + lane;
+    float2 cur = *dst;
+    cur.x += gw.x; cur.y += gw.y;
+    *dst = cur;
+}
+
+#ifdef BB200_TUNING
+__constant__ int g_bv_dbg;          // tuning builds only: bit 0 skips the dx reductions, bit 1 the per-item flush, bit 2 the reverse pass
+#define BV_DBG(bit) ((g_bv_dbg >> (bit)) & 1)
+#else
+#define BV_DBG(bit) 0
+#endif
+
+// Position of a 128-frame chunk in a warp's sequence: item (tile, group), chunk c of the item's n, table slot of the item.
+struct BvCursor {
+    int tile, group, c, n, slot;
+};
+
+template <bool BN, bool BINARY>
+__global__ void __launch_bounds__(kWarpsPerCta * 32, 1)
+k_lut6_backward_vec(const BwdArgs a, const float4 *__restrict__ coef, float *__restrict__ dC, int n_tiles, int n_full, int n_last)
+{
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned char *my = smem_raw + (size_t)warp * kBvWarpBytes;
+    unsigned char *my_tabs = my + kBvStages * kBvStageBytes;
+    float *tr = reinterpret_cast<float *>(my_tabs + kBvTabSlots * kBvTabBytes);
+
+    const int step = (int)gridDim.x;
+    const int dt = step / a.groups, dg = step - dt * a.groups;
+    auto next_item = [&](BvCursor &p) {
+        p.group += dg;
+        p.tile += dt;
+        if (p.group >= a.groups) { p.group -= a.groups; ++p.tile; }
+        p.c = 0;
+        p.n = p.tile == n_tiles - 1 ? n_last : n_full;
+        p.slot = p.slot == kBvTabSlots - 1 ? 0 : p.slot + 1;
+    };
+    auto node_of = [&](const BvCursor &p) { return min(p.group * kWarpsPerCta + warp, a.O - 1); };      // a ragged last group repeats the last node
+    auto row_of = [&](const BvCursor &p) { return (p.tile < n_tiles && lane < 6) ? __ldg(a.idx + (size_t)node_of(p) * 6 + lane) : 0; };
+
+    // ---- copy side: runs two chunks ahead of the arithmetic
+    BvCursor ic;
+    ic.tile = (int)blockIdx.x / a.groups;
+    ic.group = (int)blockIdx.x - ic.tile * a.groups;
+    ic.c = 0;
+    ic.n = ic.tile == n_tiles - 1 ? n_last : n_full;
+    ic.slot = 0;
+    BvCursor cc = ic;                              // arithmetic side
+    int ist = 0;                                   // ring stage the next copy fills
+    int row_i = row_of(ic), row_in;                // lanes 0..5: input rows of the copy side's item and of the item after it
+    {
+        BvCursor t = ic;
+        next_item(t);
+        row_in = row_of(t);
+    }
+    const float *xf = static_cast<const float *>(a.x);
+    auto issue = [&]() {
+        if (ic.tile < n_tiles) {
+            const int f = ic.tile * a.T + ic.c * kFramesPerIter + 4 * lane;          // first of this lane's four frames
+            const bool in_row = f < a.xs;
+            unsigned char *st = my + ist * kBvStageBytes + lane * 16;
+#pragma unroll
+            for (int j = 0; j < 6; ++j) {
+                const int r = __shfl_sync(kFull, row_i, j);
+                cp_async16(st + j * kBvRowBytes, xf + (size_t)r * a.xs + (in_row ? f : 0), in_row);
+            }
+            const int node = node_of(ic);
+            cp_async16(st + 6 * kBvRowBytes, a.dy + (size_t)node * a.dys + (f < a.dys ? f : 0), f < a.dys);
+            if (ic.c == 0 && lane < 16) cp_async16(my_tabs + ic.slot * kBvTabBytes + lane * 16, coef + (size_t)node * 16 + lane, true);
+            if (++ic.c == ic.n) {
+                next_item(ic);
+                row_i = row_in;
+                BvCursor t = ic;
+                next_item(t);
+                row_in = row_of(t);
+            }
+        }
+        cp_async_commit();                          // always: the group count per chunk stays uniform
+        ist = ist == kBvStages - 1 ? 0 : ist + 1;
+    };
+    issue();
+    issue();
+
+    int cst = 0;                                    // ring stage of the chunk being computed
+    int row_c = row_of(cc), row_cn;
+    float mean_n = 0.0f, rstd_n = 0.0f, dmean_n = 0.0f, dvar_n = 0.0f;
+    if (BN && cc.tile < n_tiles) {
+        const int n0 = node_of(cc);
+        mean_n = a.mean[n0]; rstd_n = a.rstd[n0]; dmean_n = a.dmean[n0]; dvar_n = a.dvar[n0];
+    }
+    f32x2 acc2[32];
+    while (cc.tile < n_tiles) {
+        const int node_raw = cc.group * kWarpsPerCta + warp;
+        const bool live_node = node_raw < a.O;
+        const int node = min(node_raw, a.O - 1);
+        const float mean = mean_n, rstd = rstd_n, dmean = dmean_n, dvar = dvar_n;
+        {   // the next item's rows and batch-norm constants travel one item ahead of their use
+            BvCursor t = cc;
+            next_item(t);
+            row_cn = row_of(t);
+            if (BN && t.tile < n_tiles) {
+                const int n1 = node_of(t);
+                mean_n = a.mean[n1]; rstd_n = a.rstd[n1]; dmean_n = a.dmean[n1]; dvar_n = a.dvar[n1];
+            }
+        }
+        const float4 *tab = reinterpret_cast<const float4 *>(my_tabs + cc.slot * kBvTabBytes);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc2[i] = 0ull;
+        const int f_tile = cc.tile * a.T;
+        for (; cc.c < cc.n; ++cc.c) {
+            issue();                                 // chunk k + 2 goes into the stage chunk k - 1 was read from
+            cp_async_wait<2>();                      // chunk k (and this item's table) has landed
+            const unsigned char *st = my + cst * kBvStageBytes + lane * 16;
+            cst = cst == kBvStages - 1 ? 0 : cst + 1;
+            float4 xq[6];
+#pragma unroll
+            for (int j = 0; j < 6; ++j) xq[j] = *reinterpret_cast<const float4 *>(st + j * kBvRowBytes);
+            const float4 dyq = *reinterpret_cast<const float4 *>(st + 6 * kBvRowBytes);
+            const int f0 = f_tile + cc.c * kFramesPerIter + 4 * lane;
+            float dxq[6][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float u[6];
+#pragma unroll
+                for (int j = 0; j < 6; ++j) {
+                    const float v = i == 0 ? xq[j].x : i == 1 ? xq[j].y : i == 2 ? xq[j].z : xq[j].w;
+                    u[j] = BINARY ? (v > 0.5f ? a.bias : -a.bias) : __saturatef(v) - 0.5f;           // the same values as condition_u()
+                }
+                KeptHalves D;
+                const float v = lut6_forward_keep_halves(tab, u, D);
+                float g = i == 0 ? dyq.x : i == 1 ? dyq.y : i == 2 ? dyq.z : dyq.w;
+                if (BN) {
+                    const float tanh_x = ((v - mean) * rstd) * a.gamma + a.beta;
+                    if (tanh_x <= 0.0f || tanh_x >= 1.0f) g = 0.0f;
+                    const float dxc = (g * a.gamma) * rstd;
+                    g = dxc + dmean + (v * dvar * a.rF);
+                }
+                if (f0 + i >= a.F || !live_node) g = 0.0f;
+                float dxv[6];
+                if (BV_DBG(2)) {
+#pragma unroll
+                    for (int j = 0; j < 6; ++j) dxv[j] = g * u[j] + v;
+                    acc2[i] = add2(acc2[i], pack2(v, g));
+                } else
+                lut6_reverse_halves(tab, u, D, g, acc2, dxv);
+#pragma unroll
+                for (int j = 0; j < 6; ++j) dxq[j][i] = dxv[j];
+            }
+            const bool write = f0 < a.F && live_node;
+#pragma unroll
+            for (int j = 0; j < 6; ++j) {
+                const int r = __shfl_sync(kFull, row_c, j);          // every lane takes part in the shuffle
+                if (write && !BV_DBG(0)) red_add_v4(a.dx + (size_t)r * a.dxs + f0, dxq[j][0], dxq[j][1], dxq[j][2], dxq[j][3]);
+            }
+        }
+        // ---- item done: sum the 64 accumulators over the lanes.  Lane l stores its 64 values as row l (16 x float4 in the table's
+        // half-packed order), then adds up columns 2l, 2l + 1 of all 32 rows.
+        if (BV_DBG(1)) { next_item(cc); row_c = row_cn; if (acc2[5] == 0x12345ull) dC[0] = 1.0f; continue; }
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            float4 v;
+            unpack2(acc2[2 * k], v.x, v.y);
+            unpack2(acc2[2 * k + 1], v.z, v.w);
+            *reinterpret_cast<float4 *>(tr + lane * kBvTrStride + 4 * k) = v;
+        }
+        __syncwarp();
+        f32x2 s0 = 0ull, s1 = 0ull, s2 = 0ull, s3 = 0ull;
+#pragma unroll
+        for (int r = 0; r < 32; r += 4) {
+            s0 = add2(s0, *reinterpret_cast<const f32x2 *>(tr + (r + 0) * kBvTrStride + 2 * lane));
+            s1 = add2(s1, *reinterpret_cast<const f32x2 *>(tr + (r + 1) * kBvTrStride + 2 * lane));
+            s2 = add2(s2, *reinterpret_cast<const f32x2 *>(tr + (r + 2) * kBvTrStride + 2 * lane));
+            s3 = add2(s3, *reinterpret_cast<const f32x2 *>(tr + (r + 3) * kBvTrStride + 2 * lane));
+        }
+        float lo, hi;
+        unpack2(add2(add2(s0, s1), add2(s2, s3)), lo, hi);
+        if (live_node) red_add_v2(dC + (size_t)node * 64 + 2 * lane, lo, hi);
+        next_item(cc);
+        row_c = row_cn;
+    }
+    cp_async_wait<0>();
+}
+
+// ---------------------------------------------------------------------------------------------
 // launchers
 // ---------------------------------------------------------------------------------------------
 static int check_common(const void *x, const void *y, const int *idx, const float *W, int O, int F, long long stride)
@@ -773,9 +1012,257 @@ static int forward_plain(const void *x, float *y, uint32_t *ybits, const int *id
     return launch_forward<XBIT, PH_PLAIN, false>(a, 2048, st);
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same persistent backward with BOTH sides staged through shared memory, so that the mapping of frames to lanes in the
+// arithmetic is independent of the mapping used for global memory:
+//   * global -> shared: every lane copies 16 bytes (four consecutive frames) of each of the seven rows of a chunk with cp.async,
+//     STAGES - 1 chunks ahead;
+//   * arithmetic: lane l takes frames 32 q + l, q = 0..3, of the chunk, one conflict-free 32-bit shared load per row and frame --
+//     no frame quads are held in registers, which takes 50 registers of operand staging out of the kernel;
+//   * the six input gradients of a frame go to a staging area in shared memory (conflict-free 32-bit stores), and after the
+//     chunk's four frames every lane adds its four consecutive frames of each row to dx with one 128-bit reduction.
+// NW warps (= nodes per group) per CTA, one CTA per SM.
+// ---------------------------------------------------------------------------------------------
+template <int NW, int STAGES>
+struct BsLayout {
+    static constexpr int kStage = 7 * kBvRowBytes;
+    static constexpr int kTabs  = kBvTabSlots * kBvTabBytes;
+    static constexpr int kWarp  = STAGES * kStage + kTabs + kBvTrBytes;       // the transpose buffer doubles as the dx staging area (6 x 512 bytes)
+    static constexpr int kSmem  = NW * kWarp;
+    static_assert(kSmem <= 227 * 1024, "one CTA per SM must fit");
+    static_assert(6 * kBvRowBytes <= kBvTrBytes, "dx staging fits the transpose buffer");
+};
+
+template <bool BN, bool BINARY, int NW, int STAGES>
+__global__ void __launch_bounds__(NW * 32, 1)
+k_lut6_backward_stg(const BwdArgs a, const float4 *__restrict__ coef, float *__restrict__ dC, int n_tiles, int n_full, int n_last)
+{
+    using L = BsLayout<NW, STAGES>;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned char *my = smem_raw + (size_t)warp * L::kWarp;
+    unsigned char *my_tabs = my + STAGES * L::kStage;
+    float *tr = reinterpret_cast<float *>(my_tabs + L::kTabs);
+
+    const int step = (int)gridDim.x;
+    const int dt = step / a.groups, dg = step - dt * a.groups;
+    auto next_item = [&](BvCursor &p) {
+        p.group += dg;
+        p.tile += dt;
+        if (p.group >= a.groups) { p.group -= a.groups; ++p.tile; }
+        p.c = 0;
+        p.n = p.tile == n_tiles - 1 ? n_last : n_full;
+        p.slot = p.slot == kBvTabSlots - 1 ? 0 : p.slot + 1;
+    };
+    auto node_of = [&](const BvCursor &p) { return min(p.group * NW + warp, a.O - 1); };      // a ragged last group repeats the last node
+    auto row_of = [&](const BvCursor &p) { return (p.tile < n_tiles && lane < 6) ? __ldg(a.idx + (size_t)node_of(p) * 6 + lane) : 0; };
+
+    BvCursor ic;
+    ic.tile = (int)blockIdx.x / a.groups;
+    ic.group = (int)blockIdx.x - ic.tile * a.groups;
+    ic.c = 0;
+    ic.n = ic.tile == n_tiles - 1 ? n_last : n_full;
+    ic.slot = 0;
+    BvCursor cc = ic;
+    int ist = 0;
+    int row_i = row_of(ic), row_in;
+    {
+        BvCursor t = ic;
+        next_item(t);
+        row_in = row_of(t);
+    }
+    const float *xf = static_cast<const float *>(a.x);
+    auto issue = [&]() {
+        if (ic.tile < n_tiles) {
+            const int f = ic.tile * a.T + ic.c * kFramesPerIter + 4 * lane;
+            const bool in_row = f < a.xs;
+            unsigned char *st = my + ist * L::kStage + lane * 16;
+#pragma unroll
+            for (int j = 0; j < 6; ++j) {
+                const int r = __shfl_sync(kFull, row_i, j);
+                cp_async16(st + j * kBvRowBytes, xf + (size_t)r * a.xs + (in_row ? f : 0), in_row);
+            }
+            const int node = node_of(ic);
+            cp_async16(st + 6 * kBvRowBytes, a.dy + (size_t)node * a.dys + (f < a.dys ? f : 0), f < a.dys);
+            if (ic.c == 0 && lane < 16) cp_async16(my_tabs + ic.slot * kBvTabBytes + lane * 16, coef + (size_t)node * 16 + lane, true);
+            if (++ic.c == ic.n) {
+                next_item(ic);
+                row_i = row_in;
+                BvCursor t = ic;
+                next_item(t);
+                row_in = row_of(t);
+            }
+        }
+        cp_async_commit();
+        ist = ist == STAGES - 1 ? 0 : ist + 1;
+    };
+#pragma unroll
+    for (int k = 0; k < STAGES - 1; ++k) issue();
+
+    int cst = 0;
+    int row_c = row_of(cc), row_cn;
+    float mean_n = 0.0f, rstd_n = 0.0f, dmean_n = 0.0f, dvar_n = 0.0f;
+    if (BN && cc.tile < n_tiles) {
+        const int n0 = node_of(cc);
+        mean_n = a.mean[n0]; rstd_n = a.rstd[n0]; dmean_n = a.dmean[n0]; dvar_n = a.dvar[n0];
+    }
+    f32x2 acc2[32];
+    while (cc.tile < n_tiles) {
+        const int node_raw = cc.group * NW + warp;
+        const bool live_node = node_raw < a.O;
+        const int node = min(node_raw, a.O - 1);
+        const float mean = mean_n, rstd = rstd_n, dmean = dmean_n, dvar = dvar_n;
+        {
+            BvCursor t = cc;
+            next_item(t);
+            row_cn = row_of(t);
+            if (BN && t.tile < n_tiles) {
+                const int n1 = node_of(t);
+                mean_n = a.mean[n1]; rstd_n = a.rstd[n1]; dmean_n = a.dmean[n1]; dvar_n = a.dvar[n1];
+            }
+        }
+        const float4 *tab = reinterpret_cast<const float4 *>(my_tabs + cc.slot * kBvTabBytes);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc2[i] = 0ull;
+        const int f_tile = cc.tile * a.T;
+        for (; cc.c < cc.n; ++cc.c) {
+            issue();                                 // refills the stage read STAGES - 1 chunks ago (all lanes are past the barrier below)
+            cp_async_wait<STAGES - 1>();
+            __syncwarp();                            // every lane's part of chunk k (and of this item's table) has landed
+            const float *st = reinterpret_cast<const float *>(my + cst * L::kStage) + lane;
+            cst = cst == STAGES - 1 ? 0 : cst + 1;
+            const int f0 = f_tile + cc.c * kFramesPerIter;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float u[6];
+#pragma unroll
+                for (int j = 0; j < 6; ++j) {
+                    const float v = st[j * kFramesPerIter + 32 * q];
+                    u[j] = BINARY ? (v > 0.5f ? a.bias : -a.bias) : __saturatef(v) - 0.5f;           // the same values as condition_u()
+                }
+                KeptHalves D;
+                const float v = lut6_forward_keep_halves(tab, u, D);
+                float g = st[6 * kFramesPerIter + 32 * q];
+                if (BN) {
+                    const float tanh_x = ((v - mean) * rstd) * a.gamma + a.beta;
+                    if (tanh_x <= 0.0f || tanh_x >= 1.0f) g = 0.0f;
+                    const float dxc = (g * a.gamma) * rstd;
+                    g = dxc + dmean + (v * dvar * a.rF);
+                }
+                if (f0 + 32 * q + lane >= a.F || !live_node) g = 0.0f;
+                float dxv[6];
+                lut6_reverse_halves(tab, u, D, g, acc2, dxv);
+#pragma unroll
+                for (int j = 0; j < 6; ++j) tr[j * kFramesPerIter + 32 * q + lane] = dxv[j];
+            }
+            __syncwarp();
+            const bool write = f0 + 4 * lane < a.F && live_node;
+#pragma unroll
+            for (int j = 0; j < 6; ++j) {
+                const int r = __shfl_sync(kFull, row_c, j);
+                const float4 d = *reinterpret_cast<const float4 *>(tr + j * kFramesPerIter + 4 * lane);
+                if (write) red_add_v4(a.dx + (size_t)r * a.dxs + f0 + 4 * lane, d.x, d.y, d.z, d.w);
+            }
+        }
+        // ---- item done: sum the 64 accumulators over the lanes through the (padded) transpose
+        __syncwarp();
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            float4 v;
+            unpack2(acc2[2 * k], v.x, v.y);
+            unpack2(acc2[2 * k + 1], v.z, v.w);
+            *reinterpret_cast<float4 *>(tr + lane * kBvTrStride + 4 * k) = v;
+        }
+        __syncwarp();
+        f32x2 s0 = 0ull, s1 = 0ull, s2 = 0ull, s3 = 0ull;
+#pragma unroll
+        for (int r = 0; r < 32; r += 4) {
+            s0 = add2(s0, *reinterpret_cast<const f32x2 *>(tr + (r + 0) * kBvTrStride + 2 * lane));
+            s1 = add2(s1, *reinterpret_cast<const f32x2 *>(tr + (r + 1) * kBvTrStride + 2 * lane));
+            s2 = add2(s2, *reinterpret_cast<const f32x2 *>(tr + (r + 2) * kBvTrStride + 2 * lane));
+            s3 = add2(s3, *reinterpret_cast<const f32x2 *>(tr + (r + 3) * kBvTrStride + 2 * lane));
+        }
+        float lo, hi;
+        unpack2(add2(add2(s0, s1), add2(s2, s3)), lo, hi);
+        if (live_node) red_add_v2(dC + (size_t)node * 64 + 2 * lane, lo, hi);
+        __syncwarp();                                // the transpose buffer is the next chunk's dx staging area
+        next_item(cc);
+        row_c = row_cn;
+    }
+    cp_async_wait<0>();
+}
+
+// Frames per tile of the persistent backward: the tile's x rows and dx rows (8 bytes per row and frame) get half of L2.
+static int backward_vec_tile(long long rows, int groups, int F)
+{
+    const DeviceInfo &di = device_info();
+    long long t = (long long)(di.l2_bytes / 2) / (8 * (rows > 0 ? rows : 1));
+    t = (t / kFramesPerIter) * kFramesPerIter;
+    if (t > 2048) t = 2048;
+    if (t < kFramesPerIter) t = kFramesPerIter;
+#ifdef BB200_TUNING
+    if (const char *e = getenv("BB200_BWD_TILE")) t = atoi(e);
+#endif
+    // small layers: narrow the tile until every SM has a couple of items
+    while (t > kFramesPerIter && (long long)groups * ((F + t - 1) / t) < 2LL * di.sm_count) t -= kFramesPerIter;
+    return (int)t;
+}
+
+// The persistent vectorised backward (k_lut6_backward_vec); BBCU_ERR_NO_MEMORY when its scratch (512 bytes per node) cannot be had.
+// `tmp` / `tmp_bytes`: scratch handed in by the caller (the reference's dev_dx_tmp), used when it is large enough and 16-byte aligned.
+static int launch_backward_vec(BwdArgs a, bool bn, int I, void *tmp, size_t tmp_bytes, cudaStream_t st)
+{
+    const size_t need = (size_t)a.O * 512;
+    unsigned char *scratch = nullptr;
+    if (tmp != nullptr && tmp_bytes >= need && (reinterpret_cast<uintptr_t>(tmp) & 15) == 0) scratch = static_cast<unsigned char *>(tmp);
+    else scratch = static_cast<unsigned char *>(stream_scratch(st, need, 1));
+    if (scratch == nullptr) return BBCU_ERR_NO_MEMORY;
+    float4 *coef = reinterpret_cast<float4 *>(scratch);
+    float *dC = reinterpret_cast<float *>(scratch + (size_t)a.O * 256);
+    auto kern = bn ? (a.binary ? k_lut6_backward_vec<true, true> : k_lut6_backward_vec<true, false>)
+                   : (a.binary ? k_lut6_backward_vec<false, true> : k_lut6_backward_vec<false, false>);
+    int smem = kBvSmem, nw = kWarpsPerCta;
+#ifdef BB200_TUNING
+    if (const char *e = getenv("BB200_BWD_KERNEL")) {
+        if (atoi(e) == 8) {
+            kern = bn ? (a.binary ? k_lut6_backward_stg<true, true, 8, 3> : k_lut6_backward_stg<true, false, 8, 3>)
+                      : (a.binary ? k_lut6_backward_stg<false, true, 8, 3> : k_lut6_backward_stg<false, false, 8, 3>);
+            smem = BsLayout<8, 3>::kSmem;
+        } else if (atoi(e) == 12) {
+            kern = bn ? (a.binary ? k_lut6_backward_stg<true, true, 12, 2> : k_lut6_backward_stg<true, false, 12, 2>)
+                      : (a.binary ? k_lut6_backward_stg<false, true, 12, 2> : k_lut6_backward_stg<false, false, 12, 2>);
+            smem = BsLayout<12, 2>::kSmem;
+            nw = 12;
+            a.groups = (a.O + 11) / 12;
+        }
+    }
+#endif
+    if (!allow_big_smem(kern, smem)) return BBCU_ERR_NO_MEMORY;
+    const long long rows = (long long)(I < 6LL * a.O ? I : 6LL * a.O);
+    a.T = backward_vec_tile(rows, a.groups, a.F);
+    const int n_tiles = (a.F + a.T - 1) / a.T;
+    const long long n_items = (long long)n_tiles * a.groups;
+    BB200_REQUIRE(n_items < (1LL << 31) - 4096, BBCU_ERR_TOO_LARGE);          // 32-bit item arithmetic in the kernel
+    const int n_full = a.T / kFramesPerIter;
+    const int n_last = (a.F - (n_tiles - 1) * a.T + kFramesPerIter - 1) / kFramesPerIter;
+    long long grid = device_info().sm_count;
+    if (grid > n_items) grid = n_items;
+#ifdef BB200_TUNING
+    { int dbg = getenv("BB200_BV_DBG") ? atoi(getenv("BB200_BV_DBG")) : 0; cudaMemcpyToSymbolAsync(g_bv_dbg, &dbg, sizeof(int), 0, cudaMemcpyHostToDevice, st); }
+#endif
+    const int groups8 = (a.O + kWarpsPerCta - 1) / kWarpsPerCta;
+    k_table_halves<<<groups8, kWarpsPerCta * 32, 0, st>>>(a.W, coef, a.O, a.lut_binarize);
+    BB200_CUDA(cudaPeekAtLastError());
+    BB200_CUDA(cudaMemsetAsync(dC, 0, (size_t)a.O * 256, st));
+    kern<<<(unsigned)grid, nw * 32, smem, st>>>(a, coef, dC, n_tiles, n_full, n_last);
+    BB200_CUDA(cudaPeekAtLastError());
+    k_coeff_grads_to_dw<<<groups8, kWarpsPerCta * 32, 0, st>>>(reinterpret_cast<const float4 *>(dC), a.dW, a.O);
+    return launch_status();
+}
+
 template <bool XBIT>
 static int backward_common(BwdArgs a, bool bn, long long total_frames, float *dmean_out, float *dvar_out, const double *ext_sums,
-                           int I, cudaStream_t st)
+                           int I, cudaStream_t st, void *tmp = nullptr, size_t tmp_bytes = 0)
 {
     // dx starts from zero (the reference's CPU path: dx_buf.FillZero(), DifferentiableLutN.h:1159)
     if (I > 0 && a.dxs > 0) BB200_CUDA(cudaMemsetAsync(a.dx, 0, sizeof(float) * (size_t)I * a.dxs, st));
@@ -812,16 +1299,38 @@ static int backward_common(BwdArgs a, bool bn, long long total_frames, float *dm
         k_bn_backward_finalize<<<(a.O + 255) / 256, 256, 0, st>>>(ext_sums, a.mean, a.rstd, dmean_out, dvar_out, a.O, total_frames);
         BB200_CUDA(cudaPeekAtLastError());
         a.dmean = dmean_out; a.dvar = dvar_out;
-        k_lut6_backward<XBIT, true><<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(a);
-    } else {
-        k_lut6_backward<XBIT, false><<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(a);
     }
+    if (!XBIT) {
+        // rows on 16-byte boundaries (the FrameBuffer layout gives them): the persistent vectorised kernel
+        const bool aligned = ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.dy) | reinterpret_cast<uintptr_t>(a.dx) |
+                               reinterpret_cast<uintptr_t>(a.dW)) & 15) == 0 && (a.xs % 4) == 0 && (a.dys % 4) == 0 && (a.dxs % 4) == 0;
+#ifdef BB200_TUNING
+        if (getenv("BB200_BWD_OLD")) goto old_kernel;
+#endif
+        if (aligned) {
+            const int rc = launch_backward_vec(a, bn, I, tmp, tmp_bytes, st);
+            if (rc != BBCU_ERR_NO_MEMORY) return rc;
+        }
+    }
+#ifdef BB200_TUNING
+old_kernel:
+#endif
+    if (bn) k_lut6_backward<XBIT, true><<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(a);
+    else    k_lut6_backward<XBIT, false><<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(a);
     return launch_status();
 }
 
 }   // namespace bb200
 
 using namespace bb200;
+
+// Bytes of the caller's dx_tmp buffer: the reference allocates it as output_node_size * 6 rows of tmp_frame_stride floats
+// (include/bb/DifferentiableLutN.h:1038-1042).
+static size_t dx_tmp_bytes(const void *dx_tmp, int output_node_size, int tmp_frame_stride)
+{
+    if (dx_tmp == nullptr || output_node_size <= 0 || tmp_frame_stride <= 0) return 0;
+    return (size_t)output_node_size * 6 * (size_t)tmp_frame_stride * sizeof(float);
+}
 
 // ------------------------------------------------------------------------------------------- StochasticLut6
 extern "C" int bbcu_fp32_StochasticLut6_Forward(const float *x, float *y, const int *idx, const float *W, int node_size, int frame_size,
@@ -873,7 +1382,7 @@ extern "C" int bbcu_fp32_StochasticLut6_Backward(const float *x, const float *dy
                                                  int frame_size, int frame_stride, int tmp_frame_size, int tmp_frame_stride,
                                                  int input_binary, int lut_binarize, float unbinarize_bias, bbcu_stream_t stream)
 {
-    (void)dx_tmp; (void)rev; (void)reverse_index_stride; (void)tmp_frame_size; (void)tmp_frame_stride;
+    (void)rev; (void)reverse_index_stride; (void)tmp_frame_size;
     int rc = check_common(x, dx, idx, W, output_node_size, frame_size, frame_stride);
     if (rc) return rc;
     BB200_REQUIRE_PTR(dy); BB200_REQUIRE_PTR(dW);
@@ -883,7 +1392,8 @@ extern "C" int bbcu_fp32_StochasticLut6_Backward(const float *x, const float *dy
     a.x = x; a.dy = dy; a.dx = dx; a.idx = idx; a.W = W; a.dW = dW; a.bias = unbinarize_bias;
     a.O = output_node_size; a.F = frame_size; a.xs = frame_stride; a.dys = frame_stride; a.dxs = frame_stride;
     a.lut_binarize = lut_binarize; a.binary = input_binary;
-    return backward_common<false>(a, false, frame_size > 0 ? frame_size : 1, nullptr, nullptr, nullptr, input_node_size, as_stream(stream));
+    return backward_common<false>(a, false, frame_size > 0 ? frame_size : 1, nullptr, nullptr, nullptr, input_node_size, as_stream(stream),
+                                  dx_tmp, dx_tmp_bytes(dx_tmp, output_node_size, tmp_frame_stride));
 }
 
 extern "C" int bbcu_bit_fp32_StochasticLut6_Backward(const int *x, const float *dy, float *dx, float *dx_tmp, const int *idx, const int *rev,
@@ -1085,13 +1595,14 @@ extern "C" int bbcu_fp32_DifferentiableLut6_Backward(const float *x, const float
                                                      int tmp_frame_size, int tmp_frame_stride, int lut_binarize, int binary_mode,
                                                      bbcu_stream_t stream)
 {
-    (void)dx_tmp; (void)rev; (void)reverse_index_stride; (void)tmp_frame_size; (void)tmp_frame_stride;
+    (void)rev; (void)reverse_index_stride; (void)tmp_frame_size;
     BB200_REQUIRE_PTR(dmean_tmp); BB200_REQUIRE_PTR(dvar_tmp);
     BwdArgs a;
     int rc = dl6_backward_args(a, x, dy, dx, idx, W, dW, mean, rstd, gamma, beta, unbinarize_bias, input_node_size, output_node_size, frame_size,
                                frame_stride, frame_stride, lut_binarize, binary_mode);
     if (rc) return rc;
-    return backward_common<false>(a, true, frame_size > 0 ? frame_size : 1, dmean_tmp, dvar_tmp, nullptr, input_node_size, as_stream(stream));
+    return backward_common<false>(a, true, frame_size > 0 ? frame_size : 1, dmean_tmp, dvar_tmp, nullptr, input_node_size, as_stream(stream),
+                                  dx_tmp, dx_tmp_bytes(dx_tmp, output_node_size, tmp_frame_stride));
 }
 
 extern "C" int bbcu_bit_fp32_DifferentiableLut6_Backward(const int *x, const float *dy, float *dx, float *dx_tmp, const int *idx, const int *rev,

@@ -1,4 +1,4 @@
-// Binary modulation around a LUT network (BASELINE config 2): RealToBinary turns one fp32 frame into frame_mod
+// Binary modulation around a LUT network: RealToBinary turns one fp32 frame into frame_mod
 // bit frames by comparing against a threshold per output frame, BinaryToReal integrates bit frames back into fp32.
 //
 // Semantics follow the reference's CPU branches:

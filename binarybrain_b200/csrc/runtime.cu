@@ -87,6 +87,10 @@ int frame_tile(long long rows_touched, int bits_per_row_frame, int node_groups, 
     return (int)t;
 }
 
+// The fault word lives in the library's device image (zero until a kernel records a fault), so that no launch path ever has to
+// allocate it: in host code the symbol below is only a handle, its device address is looked up once per device.
+static __device__ __align__(256) int g_fault_word[64];
+
 int *fault_word()
 {
     static std::mutex mu;
@@ -97,7 +101,7 @@ int *fault_word()
     auto it = words.find(dev);
     if (it == words.end()) {
         void *p = nullptr;
-        if (cudaMalloc(&p, 256) != cudaSuccess || cudaMemset(p, 0, 256) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        if (cudaGetSymbolAddress(&p, g_fault_word) != cudaSuccess || p == nullptr) { cudaGetLastError(); return nullptr; }
         it = words.emplace(dev, static_cast<int *>(p)).first;
     }
     return it->second;

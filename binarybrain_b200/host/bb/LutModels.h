@@ -70,21 +70,98 @@ public:
     index_t GetInputNodeSize()  const { return m_in; }
     index_t GetOutputNodeSize() const { return m_out; }
 
-    void InitializeConnection(std::uint64_t seed, std::string const &rule = "")
+    // The reference's wiring rules (include/bb/ConnectionTable.h:150-284), selected by the first word of `rule`:
+    //   "" / "random"  N distinct inputs per node dealt from one deck over all inputs;
+    //   "serial"       inputs 0, 1, 2, ... in order, wrapping around;
+    //   "pointwise"    shapes {c, h, w} with equal h, w: a node at (c, y, x) reads N channels of the same pixel (one deck per pixel);
+    //   "depthwise"    equal channel counts: a node of channel c reads N pixels of channel c (one deck per channel);
+    //   "gauss"        inputs drawn around the node's own (scaled) position with a normal distribution per axis, no repeats.
+    // Node index of a position: row-major over the shape, last axis fastest.  The per-pixel / per-channel decks are seeded
+    // from std::mt19937_64(seed) in visiting order, so libstdc++ builds give the reference's tables for the same seed.
+    void InitializeConnection(std::uint64_t seed, std::string const &rule, indices_t const &in_shape, indices_t const &out_shape)
     {
+        BB_ASSERT(CalcShapeSize(in_shape) == m_in && CalcShapeSize(out_shape) == m_out);
         auto t = m_table.Host(true);
-        if (rule == "serial") {                                   // ConnectionTable.h:255-266
+        const std::string kind = rule.substr(0, rule.find(' '));
+        auto flat = [](indices_t const &pos, indices_t const &shape) {
+            index_t k = 0;
+            for (std::size_t a = 0; a < shape.size(); ++a) k = k * shape[a] + pos[a];
+            return k;
+        };
+        if (kind == "serial") {                                   // ConnectionTable.h:255-266
             index_t k = 0;
             for (index_t o = 0; o < m_out; ++o) for (int i = 0; i < N; ++i) t[o * N + i] = (std::int32_t)(k++ % m_in);
             return;
         }
-        BB_ASSERT(rule.empty() || rule == "random");              // pointwise / depthwise / gauss rules are not provided
-        ShuffleDeck deck(m_in, seed);
+        if (kind == "pointwise") {                                // ConnectionTable.h:160-181
+            BB_ASSERT(in_shape.size() == 3 && out_shape.size() == 3 && in_shape[1] == out_shape[1] && in_shape[2] == out_shape[2]);
+            std::mt19937_64 mt(seed);
+            for (index_t y = 0; y < out_shape[1]; ++y)
+                for (index_t x = 0; x < out_shape[2]; ++x) {
+                    ShuffleDeck deck(in_shape[0], mt());
+                    for (index_t c = 0; c < out_shape[0]; ++c) {
+                        auto hand = deck.Deal(N);
+                        const index_t o = flat({c, y, x}, out_shape);
+                        for (int i = 0; i < N; ++i) t[o * N + i] = (std::int32_t)flat({hand[i], y, x}, in_shape);
+                    }
+                }
+            return;
+        }
+        if (kind == "depthwise") {                                // ConnectionTable.h:183-210
+            BB_ASSERT(in_shape.size() == 3 && out_shape.size() == 3 && in_shape[0] == out_shape[0]);
+            std::mt19937_64 mt(seed);
+            for (index_t c = 0; c < out_shape[0]; ++c) {
+                ShuffleDeck deck(in_shape[1] * in_shape[2], mt());
+                for (index_t y = 0; y < out_shape[1]; ++y)
+                    for (index_t x = 0; x < out_shape[2]; ++x) {
+                        auto hand = deck.Deal(N);
+                        const index_t o = flat({c, y, x}, out_shape);
+                        for (int i = 0; i < N; ++i) t[o * N + i] = (std::int32_t)flat({c, hand[i] / in_shape[2], hand[i] % in_shape[2]}, in_shape);
+                    }
+            }
+            return;
+        }
+        if (kind == "gauss") {                                    // ConnectionTable.h:212-253
+            const int n = (int)in_shape.size();
+            BB_ASSERT((int)out_shape.size() == n);
+            std::vector<double> step(n), sigma(n);
+            for (int a = 0; a < n; ++a) {
+                step[a]  = (double)(in_shape[a] - 1) / (double)(out_shape[a] - 1);      // 0/0 for an axis of one node on both sides, as in the reference
+                sigma[a] = (double)in_shape[a] / (double)out_shape[a];
+            }
+            std::mt19937_64 mt(seed);
+            std::normal_distribution<double> norm(0.0, 1.0);
+            indices_t pos((std::size_t)n, 0);
+            for (index_t o = 0; o < m_out; ++o) {                 // row-major visiting order = the node index
+                std::vector<index_t> taken;
+                for (int i = 0; i < N; ++i) {
+                    for (;;) {
+                        indices_t src((std::size_t)n);
+                        for (int a = 0; a < n; ++a) {
+                            double p = (double)pos[a] * step[a] + norm(mt) * sigma[a];
+                            while (p < 0) p += (double)in_shape[a];                     // wrap negative positions, then truncate and wrap
+                            src[a] = (index_t)p % in_shape[a];
+                        }
+                        const index_t in_node = flat(src, in_shape);
+                        if (std::find(taken.begin(), taken.end(), in_node) == taken.end()) {
+                            t[o * N + i] = (std::int32_t)in_node;
+                            taken.push_back(in_node);
+                            break;
+                        }
+                    }
+                }
+                for (int a = n - 1; a >= 0; --a) { if (++pos[a] < out_shape[a]) break; pos[a] = 0; }
+            }
+            return;
+        }
+        if (!(kind.empty() || kind == "random")) throw std::runtime_error("unknown connection rule : \"" + kind + "\"");
+        ShuffleDeck deck(m_in, seed);                             // ConnectionTable.h:268-280
         for (index_t o = 0; o < m_out; ++o) {
             auto hand = deck.Deal(N);
             for (int i = 0; i < N; ++i) t[o * N + i] = (std::int32_t)hand[i];
         }
     }
+    void InitializeConnection(std::uint64_t seed, std::string const &rule = "") { InitializeConnection(seed, rule, indices_t({m_in}), indices_t({m_out})); }
     index_t GetInputConnection(index_t node, int i) const { return m_table.HostConst()[node * N + i]; }
     void    SetInputConnection(index_t node, int i, index_t in_node)
     {
@@ -194,7 +271,7 @@ protected:
     {
         m_input_shape = shape;
         m_connection_table.SetShape(CalcShapeSize(m_input_shape), CalcShapeSize(m_output_shape));
-        m_connection_table.InitializeConnection(m_mt(), m_connection);
+        m_connection_table.InitializeConnection(m_mt(), m_connection, m_input_shape, m_output_shape);
         // W ~ N(0.5, 0.01) drawn in double and narrowed (include/bb/Tensor.h:555-565, DifferentiableLutN.h:495)
         m_W->Resize({CalcShapeSize(m_output_shape), NN});
         {

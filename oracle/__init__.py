@@ -383,6 +383,13 @@ class _Ref:
     def num_threads(self):
         return int(self.lib.bbref_num_threads())
 
+    def use_all_cores(self):
+        """OpenMP team = every core this process may run on, whatever OMP_NUM_THREADS the launcher exported; returns the count."""
+        n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+        if hasattr(self.lib, "bbref_set_num_threads"):
+            self.lib.bbref_set_num_threads(C.c_int(n))
+        return self.num_threads()
+
     def stochastic_lut6(self, x, idx, W, frames=None, binary=False, lut_binarize=False, host_simd=True, dy=None, dW=None):
         bit_in = x.dtype == np.uint32
         x = np.ascontiguousarray(x)
@@ -603,6 +610,32 @@ class _Ref:
     def lut_mlp_step(self, x, t, widths, classes, idx_list, W_list, use_mse=False, lr=0.001):
         """One training step (forward, loss, backward, Adam) of stacked DifferentiableLut6 layers + Reduce through the reference's Sequential."""
         return self._lut_mlp_step(x, t, list(widths), classes, idx_list, W_list, int(use_mse), lr)
+
+
+    CNN_WIDTHS = (216, 36, 32, 216, 36, 32, 384, 64, 384, 64, 1024, 420, 70, 10)
+
+    @staticmethod
+    def cnn_input_widths(hw=32):
+        """Input node counts of the 14 LUT layers of the LUT-CNN on {3, hw, hw} images (the first dense layer reads 64 * (hw/4)^2 nodes)."""
+        return (27, 216, 36, 288, 216, 36, 288, 384, 576, 384, 64 * (hw // 4) ** 2, 1024, 420, 70)
+
+    def lut_cnn_step(self, x, dy, idx_list, W_list, hw=32):
+        """Forward (training) + backward of the LUT-CNN through the reference's Sequential / Convolution2d / MaxPooling / DifferentiableLutN.
+        x [3*hw*hw, B] fp32, dy [10, B]; returns y [10, B], dx, and the table gradients of the 14 LUT layers."""
+        x = np.ascontiguousarray(x, np.float32)
+        dy = np.ascontiguousarray(dy, np.float32)
+        B = x.shape[1]
+        idx = np.ascontiguousarray(np.concatenate([np.asarray(i, np.int32).reshape(-1) for i in idx_list]))
+        W = np.ascontiguousarray(np.concatenate([np.asarray(w, np.float32).reshape(-1) for w in W_list]))
+        y = np.zeros((10, B), np.float32)
+        dx = np.zeros((3 * hw * hw, B), np.float32)
+        dW = np.zeros_like(W)
+        self.lib.bbref_lut_cnn_step(_vp(x), _vp(dy), C.c_int(B), C.c_int(hw), _vp(idx), _vp(W), _vp(y), _vp(dx), _vp(dW))
+        out, o = [], 0
+        for n in self.CNN_WIDTHS:
+            out.append(dW[o:o + n * 64].reshape(n, 64).copy())
+            o += n * 64
+        return dict(y=y, dx=dx, dW=out)
 
 
 port = _Port()

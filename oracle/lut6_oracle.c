@@ -362,7 +362,7 @@ void oracle_adam_update(float *p, float *g, float *mbuf, float *vbuf, size_t n, 
 }
 
 /* ------------------------------------------------------------------------------------------
- * Neighbours used by whole-step parity (config 0 / config 4): bb::Reduce, the two losses.
+ * Neighbours used by whole-step parity: bb::Reduce, the two losses.
  * Reduce                  include/bb/Reduce.h:200-220 (forward), :250-268 (backward)
  * LossSoftmaxCrossEntropy include/bb/LossSoftmaxCrossEntropy.h:151-205 (pix_size = 1 form)
  * LossMeanSquaredError    include/bb/LossMeanSquaredError.h:153-172 (mean reduction)
@@ -425,7 +425,7 @@ double oracle_mean_squared_error(float const *y, float const *t, float *dy, int 
 }
 
 /* ------------------------------------------------------------------------------------------
- * Binary modulation (config 2 neighbours)
+ * Binary modulation
  * RealToBinary  include/bb/RealToBinary.h:309-345 (th == NULL: deterministic) and :352-398 (th[node][out_frame] given)
  * BinaryToReal  include/bb/BinaryToReal.h:247-276 (forward), :312-330 (backward)
  * Layout: x [x_depth * point_size][frames] fp32, y bit rows of `ys` words; output node = (depth * depth_mod + d) * point_size + p.

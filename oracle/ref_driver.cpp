@@ -41,6 +41,7 @@
 #include "bb/ConvolutionIm2Col.h"
 #include "bb/ConvolutionCol2Im.h"
 #include "bb/MaxPooling.h"
+#include "bb/Convolution2d.h"
 
 namespace {
 
@@ -475,6 +476,63 @@ int bbref_lut_mlp_step(float const *x, float const *t, int frames, int layers, i
     return 0;
 }
 
+// The LUT-CNN as one bb::Sequential of the reference's own classes, forward (training mode) and backward of a given dy:
+//   Convolution2d(3x3 same; per-pixel DifferentiableLut6 27 -> 216 -> 36 -> 32), Convolution2d(288 -> 216 -> 36 -> 32), MaxPooling 2x2,
+//   Convolution2d(288 -> 384 -> 64), Convolution2d(576 -> 384 -> 64), MaxPooling 2x2, DifferentiableLut6 4096 -> 1024 -> 420 -> 70 -> 10
+// on images {3, hw, hw} (hw = 32 gives the widths above; the first dense layer reads 64 * (hw/4)^2 nodes).  idx / W hold the wiring and
+// tables of the 14 LUT layers in network order; dW_out receives their table gradients, y_out [10][frames], dx_out [3*hw*hw][frames].
+int bbref_lut_cnn_step(float const *x, float const *dy, int frames, int hw, int const *idx, float const *W, float *y_out, float *dx_out,
+                       float *dW_out)
+{
+    using Lut = bb::DifferentiableLutN<6, float, float>;
+    static const int widths[14] = {216, 36, 32, 216, 36, 32, 384, 64, 384, 64, 1024, 420, 70, 10};
+    std::vector<std::shared_ptr<Lut>> luts;
+    auto make = [&](int w) {
+        Lut::create_t c;
+        c.output_shape = {w};
+        c.binary = false;
+        auto l = Lut::Create(c);
+        luts.push_back(l);
+        return l;
+    };
+    auto conv = [&](int first, int count) {
+        auto seq = bb::Sequential::Create();
+        for (int k = 0; k < count; ++k) seq->Add(make(widths[first + k]));
+        return bb::Convolution2d<float, float>::Create(seq, 3, 3, 1, 1, "same");
+    };
+    auto net = bb::Sequential::Create();
+    net->Add(conv(0, 3));
+    net->Add(conv(3, 3));
+    net->Add(bb::MaxPooling<float, float>::Create(2, 2));
+    net->Add(conv(6, 2));
+    net->Add(conv(8, 2));
+    net->Add(bb::MaxPooling<float, float>::Create(2, 2));
+    for (int k = 10; k < 14; ++k) net->Add(make(widths[k]));
+    net->SendCommand("host_only true");
+    net->SetInputShape({3, hw, hw});
+    size_t io = 0, wo = 0;
+    for (int l = 0; l < 14; ++l) {
+        set_wiring(luts[l], idx + io, widths[l]);
+        set_W(luts[l], W + wo, widths[l]);
+        io += (size_t)widths[l] * 6;
+        wo += (size_t)widths[l] * 64;
+    }
+    bb::FrameBuffer x_buf(frames, {3, hw, hw}, BB_TYPE_FP32, true);
+    put_fp32(x_buf, x, 3 * hw * hw, frames);
+    auto y_buf = net->Forward(x_buf, true);
+    if (y_out) get_fp32(y_buf, y_out, 10, frames);
+    bb::FrameBuffer dy_buf(frames, {10}, BB_TYPE_FP32, true);
+    put_fp32(dy_buf, dy, 10, frames);
+    auto dx_buf = net->Backward(dy_buf);
+    if (dx_out) get_fp32(dx_buf, dx_out, 3 * hw * hw, frames);
+    wo = 0;
+    for (int l = 0; l < 14; ++l) {
+        if (dW_out) get_dW(luts[l], dW_out + wo, widths[l]);
+        wo += (size_t)widths[l] * 64;
+    }
+    return 0;
+}
+
 // bb::RealToBinary<bb::Bit,float>::Forward on an input of node shape {depth, point_size}.  seed == 0: deterministic modulation;
 // otherwise thresholds come from UniformDistributionGenerator<float>(0, 1, seed), data-wise, and th_out [node][out_frame]
 // receives the threshold each comparison used (the same generator is replayed in the draw order of RealToBinary.h:360-392).
@@ -716,6 +774,16 @@ int bbref_num_threads(void)
     return omp_get_max_threads();
 #else
     return 1;
+#endif
+}
+
+// A launcher may have exported OMP_NUM_THREADS=1 to this process (torch.distributed.run does): the timed legs set the team size themselves.
+void bbref_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
 #endif
 }
 

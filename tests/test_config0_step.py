@@ -1,4 +1,4 @@
-"""One whole training step of BASELINE config 0 against the reference's own run of it.
+"""One whole training step of the small MLP (784 -> 1024 -> 420 -> 70 nodes, 512 frames) against the reference's own run of it.
 
 784 -> 1024 -> 420 -> 70 DifferentiableLut6 (fp32, batch norm on, non-binary), bb::Reduce to 10 classes, softmax cross-entropy,
 Adam; 512 frames.  The golden values come from bb::Sequential + LossSoftmaxCrossEntropy + OptimizerAdam of the unmodified

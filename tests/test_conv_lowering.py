@@ -1,4 +1,4 @@
-"""Convolution lowering around the per-pixel LUT layers of BASELINE config 3: ConvolutionIm2Col, ConvolutionCol2Im, MaxPooling,
+"""Convolution lowering around the per-pixel LUT layers of the LUT-CNN: ConvolutionIm2Col, ConvolutionCol2Im, MaxPooling,
 fp32 and bit frames, forward and backward.  Golden values come from the reference's own classes (tests/golden/make_golden.py);
 these operators only move or select values, so every comparison is exact (fp32 gradients of Im2Col, which add up to
 filter_h * filter_w terms, to 1e-6)."""
@@ -92,7 +92,7 @@ def test_conv_lowering_gpu_against_golden(golden):
 
 @pytest.mark.gpu
 def test_config3_block_shapes_gpu_against_oracle():
-    """The lowering of BASELINE config 3's first conv block at full size: 3x32x32 images, batch 256, 3x3 'same' Im2Col (frames
+    """The lowering of the LUT-CNN's first conv block at full size: 3x32x32 images, batch 256, 3x3 'same' Im2Col (frames
     x1024, the bit-frame fast path with 32 pixel groups), Col2Im back from 32 channels and 2x2 MaxPooling, fp32 and bit frames."""
     import torch
     if not torch.cuda.is_available():
@@ -193,25 +193,3 @@ def test_convolution2d_layer_gpu_against_oracle():
     dx = net.backward(dev_fp32(dy))
     assert err(host_fp32(dx, B), dx_w) <= 1e-4 * amp
     assert err(luts[1].dW.cpu().numpy(), dW1) <= 1e-4 * amp and err(luts[0].dW.cpu().numpy(), dW0) <= 1e-4 * amp
-
-
-@pytest.mark.gpu
-def test_config3_network_runs_at_full_shape():
-    """BASELINE config 3 assembled from the host-side classes (two conv blocks with pooling and the dense head), batch 32:
-    one forward and backward; shapes, finiteness, value range and that every table received gradient."""
-    import torch
-    if not torch.cuda.is_available():
-        pytest.skip("no CUDA device")
-    import bench
-    B = 32
-    net = bench.build_config3_network(torch.device("cuda"), seed=5)
-    x = torch.rand((3 * 32 * 32, B), device="cuda")
-    y = net.forward(x, B)
-    assert y.shape[0] == 10 and y.shape[1] >= B
-    assert torch.isfinite(y[:, :B]).all() and float(y[:, :B].min()) >= 0.0 and float(y[:, :B].max()) <= 1.0
-    dx = net.backward(torch.rand_like(y))
-    assert dx.shape[0] == 3 * 32 * 32 and torch.isfinite(dx[:, :B]).all()
-    luts = net.lut_layers()
-    assert len(luts) == 14
-    for layer in luts:
-        assert torch.isfinite(layer.dW).all() and float(layer.dW.abs().sum()) > 0.0

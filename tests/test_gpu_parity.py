@@ -8,6 +8,13 @@ makes a literal 1e-5 meaningless:
   * batch-normalised fp32 outputs are compared with 1e-5 * max(1, gamma*rstd): the normalisation
     multiplies the last-ulp difference between a lerp tree and the CPU's product form by gamma*rstd
     (up to 95 when the variance sits at its 1e-5 floor).
+
+Hard-tanh mask in the DifferentiableLut6 backward: a frame whose pre-activation lies within 1e-4 * gamma*rstd of 0 or 1 may
+take the other side of the mask on the GPU, and through the batch sums (dmean, dvar) one flipped frame moves every gradient of
+its node by a relative 1/frames.  The tests therefore never skip an assert; they make such frames harmless instead: where the
+inputs are the test's own, dy is set to zero on those frames (a masked and an unmasked zero are the same), and where dy is fixed
+by a golden file, the nodes that own such a frame (and the input rows they feed) are left out of that one comparison, the
+same case being checked in full against the oracle with dy zeroed on those frames.
 """
 import numpy as np
 import pytest
@@ -19,6 +26,25 @@ from oracle import port, pack_bits, unpack_bits
 pytestmark = pytest.mark.gpu
 
 TOL = 1e-5
+# Batch-normalised values: the factor in front of gamma*rstd.  Both sides evaluate the LUT to about 2 ulp of a value near 0.5
+# (6e-8 each, different operation order) and the mean to 1 ulp; (raw - mean) * rstd * gamma turns their sum, up to 3e-7, into
+# 3e-7 * gamma*rstd.  The gradients pass through the same rstd once more (dxc = gamma * dy * rstd) and add the rounding of the
+# fp32 atomics that accumulate dx and dW, hence 2 there.
+BN_Y_FACTOR = 3.0
+BN_GRAD_FACTOR = 2.0
+
+
+def _edges(pre, amp):
+    """Frames whose hard-tanh decision the last bits of the pre-activation could flip."""
+    return (np.abs(pre) < 1e-4 * amp) | (np.abs(pre - 1) < 1e-4 * amp)
+
+
+def _untouched(edge, idx, n_in):
+    """(nodes without an edge frame, input rows fed by such nodes only)."""
+    node_ok = ~edge.any(axis=1)
+    row_ok = np.ones(n_in, bool)
+    row_ok[np.unique(idx[~node_ok])] = False
+    return node_ok, row_ok
 
 
 @pytest.fixture(scope="module")
@@ -116,19 +142,18 @@ def _dl6_fp32_check(ops, x, idx, W, dy, rm0, rv0, fl, stride=None):
         bad = yh != p["y"]
         assert (np.abs(p["y_pre"][bad] - 0.5) < 1e-4 * amp).all() and bad.mean() < 1e-2
     else:
-        assert np.abs(yh - p["y"]).max() <= TOL * amp * 3
-    # backward with the oracle's own mean / rstd so that only this operator is under test
+        assert np.abs(yh - p["y"]).max() <= BN_Y_FACTOR * TOL * amp
+    # backward with the oracle's own mean / rstd so that only this operator is under test; dy = 0 on the frames whose mask
+    # decision is within rounding (see the module docstring), so that every other frame is compared without exception
+    edge = _edges(p["y_pre"], amp)
+    dy = np.where(edge, np.float32(0), dy).astype(np.float32)
     dx_w, dW_w = port.dl6_backward(x, dy, idx, W, p["mean"], p["rstd"], I, **fl)
     dWd = torch.zeros((O, 64), device="cuda")
     dx = ops.differentiable_lut6_backward(xd, dev_fp32(dy, stride), dev(idx), dev(W), dWd, dev(p["mean"]), dev(p["rstd"]), I, F, **fl)
     dxh = host_fp32(dx, F)
-    # hard-tanh mask: a frame whose pre-activation sits on 0 or 1 may flip; allow those rows of evidence only
-    pre = p["y_pre"]
-    edge = (np.abs(pre) < 1e-4 * amp) | (np.abs(pre - 1) < 1e-4 * amp)
     scale = max(1.0, float(np.abs(dx_w).max()))
-    if not edge.any():
-        assert np.abs(dxh - dx_w).max() <= 2e-5 * scale * amp
-        assert err(dWd.cpu().numpy(), dW_w) <= 2e-5 * amp
+    assert np.abs(dxh - dx_w).max() <= BN_GRAD_FACTOR * TOL * scale * amp
+    assert err(dWd.cpu().numpy(), dW_w) <= BN_GRAD_FACTOR * TOL * amp
     # inference
     pi = port.dl6_forward_infer(x, idx, W, rm0, rv0, **fl)
     yi = host_fp32(ops.differentiable_lut6_forward_inference(xd, dev(idx), dev(W), dev(rm0), dev(rv0), F, **fl), F)
@@ -136,8 +161,8 @@ def _dl6_fp32_check(ops, x, idx, W, dy, rm0, rv0, fl, stride=None):
         bad = yi != pi["y"]
         assert (np.abs(pi["y_pre"][bad] - 0.5) < 1e-4).all()
     else:
-        assert np.abs(yi - pi["y"]).max() <= TOL * 3
-    return edge.any()
+        assert np.abs(yi - pi["y"]).max() <= BN_Y_FACTOR * TOL
+    return int(edge.sum())
 
 
 @pytest.mark.parametrize("case", golden_cases("dl6"))
@@ -152,7 +177,18 @@ def test_dl6_fp32_golden(ops, golden, case):
     y, mean, rstd = ops.differentiable_lut6_forward_training(dev_fp32(g("x")), dev(g("idx")), dev(g("W")), rm, rv, F, **fl)
     assert err(mean.cpu().numpy(), g("mean")) <= TOL and err(rm.cpu().numpy(), g("rm")) <= TOL
     if not fl["binary"]:
-        assert np.abs(host_fp32(y, F) - g("y")).max() <= TOL * 3 * max(1.0, 0.3 * float(g("rstd").max()))
+        assert np.abs(host_fp32(y, F) - g("y")).max() <= BN_Y_FACTOR * TOL * max(1.0, 0.3 * float(g("rstd").max()))
+    # the reference's own dx / dW for the golden dy, outside the nodes that own a frame with an undecidable mask
+    p = port.dl6_forward_train(g("x"), g("idx"), g("W"), g("rm0"), g("rv0"), **fl)
+    amp = max(1.0, 0.3 * float(p["rstd"].max()))
+    I, O = g("x").shape[0], g("idx").shape[0]
+    node_ok, row_ok = _untouched(_edges(p["y_pre"], amp), g("idx"), I)
+    dWd = torch.zeros((O, 64), device="cuda")
+    dx = ops.differentiable_lut6_backward(dev_fp32(g("x")), dev_fp32(g("dy")), dev(g("idx")), dev(g("W")), dWd, dev(g("mean")), dev(g("rstd")),
+                                          I, F, **fl)
+    scale = max(1.0, float(np.abs(g("dx")).max()))
+    assert np.abs(host_fp32(dx, F) - g("dx"))[row_ok].max(initial=0.0) <= BN_GRAD_FACTOR * TOL * scale * amp
+    assert np.abs(dWd.cpu().numpy() - g("dW"))[node_ok].max(initial=0.0) <= BN_GRAD_FACTOR * TOL * amp * max(1.0, float(np.abs(g("dW")).max()))
 
 
 @pytest.mark.parametrize("I,O,F,stride", [(16, 16, 131, None), (24, 1024, 64, None), (200, 300, 1100, 1104), (6, 2, 39, 64),
@@ -179,7 +215,8 @@ def test_dl6_fp32_fresh_layer_tables(ops):
     W = np.clip(rng.normal(0.5, 0.01, (O, 64)), 0, 1).astype(np.float32)
     x = rng.random((I, F), dtype=np.float32)
     dy = rng.random((O, F), dtype=np.float32)
-    _dl6_fp32_check(ops, x, idx, W, dy, np.zeros(O, np.float32), np.ones(O, np.float32), dict(binary=0, lut_binarize=0))
+    n_edge = _dl6_fp32_check(ops, x, idx, W, dy, np.zeros(O, np.float32), np.ones(O, np.float32), dict(binary=0, lut_binarize=0))
+    assert n_edge < 0.02 * O * F          # the zeroed-dy frames are a small minority: the comparison above covered the rest
 
 
 @pytest.mark.parametrize("case", golden_cases("dl6bit"))
@@ -199,11 +236,20 @@ def test_dl6_bit_golden(ops, golden, case):
     amp = max(1.0, 0.3 * float(g("rstd").max()))
     bad = unpack_bits(host_bits(y, F), F) != unpack_bits(g("y"), F)
     assert (np.abs(p["y_pre"][bad] - 0.5) < 1e-4 * amp).all()
+    # the reference's dx / dW for the golden dy, outside the nodes that own a frame with an undecidable mask ...
+    edge = _edges(p["y_pre"], amp)
+    node_ok, row_ok = _untouched(edge, g("idx"), I)
     dWd = torch.zeros((O, 64), device="cuda")
     dx = ops.differentiable_lut6_backward(xd, dev_fp32(g("dy")), dev(g("idx")), dev(g("W")), dWd, dev(g("mean")), dev(g("rstd")), I, F, **fl)
-    pre = p["y_pre"]
-    if not ((np.abs(pre) < 1e-4 * amp) | (np.abs(pre - 1) < 1e-4 * amp)).any():
-        assert err(host_fp32(dx, F), g("dx")) <= 2e-5 * amp and err(dWd.cpu().numpy(), g("dW")) <= 2e-5 * amp
+    scale = max(1.0, float(np.abs(g("dx")).max()))
+    assert np.abs(host_fp32(dx, F) - g("dx"))[row_ok].max(initial=0.0) <= BN_GRAD_FACTOR * TOL * scale * amp
+    assert np.abs(dWd.cpu().numpy() - g("dW"))[node_ok].max(initial=0.0) <= BN_GRAD_FACTOR * TOL * amp * max(1.0, float(np.abs(g("dW")).max()))
+    # ... and every node against the oracle with dy zeroed on those frames
+    dy0 = np.where(edge, np.float32(0), g("dy")).astype(np.float32)
+    dx_w, dW_w = port.dl6_backward(g("x"), dy0, g("idx"), g("W"), g("mean"), g("rstd"), I, frames=F, **fl)
+    dWd = torch.zeros((O, 64), device="cuda")
+    dx = ops.differentiable_lut6_backward(xd, dev_fp32(dy0), dev(g("idx")), dev(g("W")), dWd, dev(g("mean")), dev(g("rstd")), I, F, **fl)
+    assert err(host_fp32(dx, F), dx_w) <= BN_GRAD_FACTOR * TOL * amp and err(dWd.cpu().numpy(), dW_w) <= BN_GRAD_FACTOR * TOL * amp
     yi = ops.differentiable_lut6_forward_inference(xd, dev(g("idx")), dev(g("W")), dev(g("rm")), dev(g("rv")), F, **fl)
     pi = port.dl6_forward_infer(g("x"), g("idx"), g("W"), g("rm"), g("rv"), frames=F, **fl)
     bad = unpack_bits(host_bits(yi, F), F) != unpack_bits(g("y_infer"), F)
@@ -226,13 +272,11 @@ def test_dl6_bit_oracle_odd_sizes(ops):
         assert err(mean.cpu().numpy(), p["mean"]) <= TOL
         bad = unpack_bits(host_bits(y, F), F) != unpack_bits(p["y_bits"], F)
         assert (np.abs(p["y_pre"][bad] - 0.5) < 1e-4 * amp).all() and bad.mean() < 1e-3
+        dy = np.where(_edges(p["y_pre"], amp), np.float32(0), dy).astype(np.float32)      # frames with an undecidable mask carry no gradient
         dx_w, dW_w = port.dl6_backward(xb, dy, idx, W, p["mean"], p["rstd"], I)
         dWd = torch.zeros((O, 64), device="cuda")
         dx = ops.differentiable_lut6_backward(xd, dev_fp32(dy), dev(idx), dev(W), dWd, dev(p["mean"]), dev(p["rstd"]), I, F)
-        pre = p["y_pre"]
-        edge = (np.abs(pre) < 1e-4 * amp) | (np.abs(pre - 1) < 1e-4 * amp)
-        if not edge.any():
-            assert err(host_fp32(dx, F), dx_w) <= 2e-5 * amp and err(dWd.cpu().numpy(), dW_w) <= 2e-5 * amp
+        assert err(host_fp32(dx, F), dx_w) <= BN_GRAD_FACTOR * TOL * amp and err(dWd.cpu().numpy(), dW_w) <= BN_GRAD_FACTOR * TOL * amp
 
 
 # --------------------------------------------------------------------------------------------- StochasticBatchNormalization
@@ -310,7 +354,7 @@ def test_binary_lut6_host_buffers_bit_exact(ops):
 
 
 def test_binary_lut6_full_size_properties(ops):
-    """BASELINE config 1 shape (16384 -> 16384 nodes, 2^20 frames): properties that need no CPU pass.
+    """The full-size shape (16384 -> 16384 nodes, 2^20 frames): properties that need no CPU pass.
 
     (a) a table that projects input k reproduces that input row bit for bit (gather indexing);
     (b) complementing the table complements the output; (c) a 4096-node x 8192-frame window agrees with the oracle."""

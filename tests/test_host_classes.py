@@ -118,20 +118,23 @@ def test_differentiable_lut6_layer_against_oracle(core, binary, lut_binarize):
     lut.W().set_numpy(W)
     x = rng.random((F, I), dtype=np.float32)
     dy = rng.random((F, O), dtype=np.float32)
+    p = port.dl6_forward_train(x.T.copy(), idx, W, np.zeros(O), np.ones(O), binary=int(binary), lut_binarize=int(lut_binarize))
+    amp = max(1.0, 0.3 * float(p["rstd"].max()))
+    # frames whose hard-tanh decision is within rounding of the pre-activation carry no gradient in this test (a masked and an
+    # unmasked zero are the same), so that every other frame can be compared without exception
+    pre = p["y_pre"]
+    edge = (np.abs(pre) < 1e-4 * amp) | (np.abs(pre - 1) < 1e-4 * amp)
+    dy = np.where(edge.T, np.float32(0), dy).astype(np.float32)
     y = lut.forward(core.FrameBuffer.from_numpy_fp32(x), True).numpy_fp32()
     dx = lut.backward(core.FrameBuffer.from_numpy_fp32(dy)).numpy_fp32()
-    p = port.dl6_forward_train(x.T.copy(), idx, W, np.zeros(O), np.ones(O), binary=int(binary), lut_binarize=int(lut_binarize))
     dx_w, dW_w = port.dl6_backward(x.T.copy(), dy.T.copy(), idx, W, p["mean"], p["rstd"], I, binary=int(binary), lut_binarize=int(lut_binarize))
-    amp = max(1.0, 0.3 * float(p["rstd"].max()))
     if binary:
         assert (y.T != p["y"]).mean() < 1e-3
     else:
         assert np.abs(y.T - p["y"]).max() <= 3e-5 * amp
     assert np.abs(lut.get_mean().numpy() - p["running_mean"]).max() <= 1e-5
-    pre = p["y_pre"]
-    if not ((np.abs(pre) < 1e-4 * amp) | (np.abs(pre - 1) < 1e-4 * amp)).any():
-        assert np.abs(dx.T - dx_w).max() <= 1e-4 * amp * max(1.0, np.abs(dx_w).max())
-        assert np.abs(lut.dW().numpy() - dW_w).max() <= 1e-4 * amp * max(1.0, np.abs(dW_w).max())
+    assert np.abs(dx.T - dx_w).max() <= 1e-4 * amp * max(1.0, np.abs(dx_w).max())
+    assert np.abs(lut.dW().numpy() - dW_w).max() <= 1e-4 * amp * max(1.0, np.abs(dW_w).max())
     # inference uses the running statistics
     yi = lut.forward(core.FrameBuffer.from_numpy_fp32(x), False).numpy_fp32()
     pi = port.dl6_forward_infer(x.T.copy(), idx, W, p["running_mean"], p["running_var"], binary=int(binary), lut_binarize=int(lut_binarize))

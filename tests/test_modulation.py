@@ -1,4 +1,4 @@
-"""Binary modulation around a LUT network (BASELINE config 2): RealToBinary (frame modulation 7, seeded thresholds),
+"""Binary modulation around a LUT network: RealToBinary (frame modulation 7, seeded thresholds),
 two StochasticLut6 layers on the modulated frames, BinaryToReal integration.  Golden values from the reference's own
 RealToBinary / BinaryToReal (tests/golden/make_golden.py); bit outputs are compared bit for bit."""
 import numpy as np

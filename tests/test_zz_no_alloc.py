@@ -7,11 +7,75 @@ that nothing of the first call survives in the shared scratch array.  This file 
 that stops at the first failure has already been through every other test; it also passes on its own in a
 fresh process (the first call on a device does the entry point's one-time set-up).
 """
+import os
+import subprocess
+import sys
+
 import numpy as np
 import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# Runs in a process of its own, where the allocation-free entry point is the FIRST call into the library: nothing an earlier
+# operator may have set up (heap scratch, the per-device fault word) exists yet.  The device heap is capped at one byte, so any
+# request the call made of it would fail; torch allocates the tensors before the call, and the free device memory is read
+# around a second call (the first one loads the library's device code, which the driver accounts as device memory).
+_FRESH_PROCESS = r"""
+import sys
+import numpy as np
+import torch
+sys.path.insert(0, ROOT)
+from binarybrain_b200 import abi
+from oracle import port
+
+L = abi.lib()
+L.bbcu_LocalHeap_SetByteLimit(1)
+rng = np.random.default_rng(21)
+I, O, F = 300, 700, 1100
+S = (F + 7) // 8 * 8
+idx = np.stack([rng.permutation(I)[:6] for _ in range(O)]).astype(np.int32)
+W = np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32)
+x = rng.random((I, F), dtype=np.float32)
+rm0, rv0 = rng.random(O, dtype=np.float32), rng.random(O, dtype=np.float32) + 0.5
+xd = torch.zeros((I, S)); xd[:, :F] = torch.from_numpy(x); xd = xd.cuda()
+idx_d, W_d = torch.from_numpy(idx).cuda(), torch.from_numpy(W).cuda()
+y = torch.full((O, S), -7.0, device="cuda")
+mean, rstd = torch.empty(O, device="cuda"), torch.empty(O, device="cuda")
+rm, rv = torch.from_numpy(rm0).cuda(), torch.from_numpy(rv0).cuda()
+rm2, rv2 = rm.clone(), rv.clone()
+torch.cuda.synchronize()
+
+def call(rm_t, rv_t):
+    rc = L.bbcu_fp32_DifferentiableLut6_ForwardTraining_NoAlloc(xd.data_ptr(), y.data_ptr(), idx_d.data_ptr(), W_d.data_ptr(), mean.data_ptr(),
+                                                                rstd.data_ptr(), rm_t.data_ptr(), rv_t.data_ptr(), 0.3, 0.5, 0.9, 0.25, O, F, S, 0, 0,
+                                                                torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, L.bbcu_b200_error_string(rc)
+    torch.cuda.synchronize()
+
+call(rm, rv)
+assert L.bbcu_LocalHeap_GetAllocatedSize() == 0 and L.bbcu_LocalHeap_GetMaxAllocSize() == 0
+free_before = torch.cuda.mem_get_info()[0]
+call(rm2, rv2)
+assert torch.cuda.mem_get_info()[0] == free_before, "device memory changed across a call"
+assert L.bbcu_LocalHeap_GetAllocatedSize() == 0 and L.bbcu_LocalHeap_GetMaxAllocSize() == 0
+assert L.bbcu_b200_device_fault() == 0
+p = port.dl6_forward_train(x, idx, W, rm0, rv0, binary=False)
+amp = max(1.0, 0.3 * float(p["rstd"].max()))
+assert np.abs(mean.cpu().numpy() - p["mean"]).max() <= 1e-5
+assert np.abs(rm.cpu().numpy() - p["running_mean"]).max() <= 1e-5 and np.abs(rv.cpu().numpy() - p["running_var"]).max() <= 1e-5
+assert np.abs(y[:, :F].cpu().numpy() - p["y"]).max() <= 3e-5 * amp
+print("fresh-process no-alloc ok")
+"""
+
+
+def test_no_alloc_forward_first_call_of_a_fresh_process_allocates_nothing_and_matches_the_oracle():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    r = subprocess.run([sys.executable, "-c", _FRESH_PROCESS.replace("ROOT", repr(ROOT))], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "fresh-process no-alloc ok" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
 
 
 def _run(abi, name, x, idx, W, frames, binary, seed_stats):
