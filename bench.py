@@ -11,7 +11,7 @@ table gradients ([65536, 64] fp32, all-reduced asynchronously under the next lay
 backward + Adam over the whole global batch; `value` = layers x nodes x G / step time (node-frames/s, each counted once for
 its forward and backward together) with the inputs resident in HBM; `e2e` = the same step with this rank's input and target
 shards uploaded from pinned host memory every step (double-buffered on a copy stream) and the loss read back.
-`roofline` is that of the kernel that dominates the step, the fused batch-norm + LUT backward (k_lut6_backward_vec), timed
+`roofline` is that of the kernel that dominates the step, the fused batch-norm + LUT backward (k_lut6_backward_pipe), timed
 with CUDA events around every one of its launches inside the timed steps.
 
 Sub-objects: `binary_lut6` (BinaryLut6 bit-packed inference forward, 16384 -> 16384 nodes, 2^20 frames per GPU, with its own
@@ -50,7 +50,7 @@ FLOPS_FWD, FLOPS_BWD = 126.0, 505.0
 FLOPS_FWD_EXECUTED, FLOPS_BWD_EXECUTED = 126.0 + 12.0, 379.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one k_binary_lut6_pipe launch: ncu on a 131072-frame launch; traffic grows with frames
 NCU_BL6_TRAFFIC_BYTES_PER_FRAME = (449.7e6 + 244.6e6) / 131072
-# the same for one k_lut6_backward_vec<BN> launch on a 65536 -> 65536 x 4096-frame layer (bytes per node-frame), or None until captured
+# the same for one k_lut6_backward_pipe<BN> launch on a 65536 -> 65536 x 4096-frame layer (bytes per node-frame), or None until captured
 NCU_BWD_TRAFFIC_BYTES_PER_NF = None
 
 
@@ -673,9 +673,11 @@ def main():
             "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": config, "clocks": clocks, "gpu_launches": args.steps * TrainingWorkload.LAUNCHES_PER_STEP,
             "allreduce_bytes_per_step": wl.allreduce_bytes(),
-            "roofline": {"bound": "fp32", "kernel": "k_lut6_backward_vec<BN> (bbcu_fp32_DifferentiableLut6_BackwardApply)",
+            "roofline": {"bound": "fp32", "kernel": "k_lut6_backward_pipe<BN> (one bbcu_fp32_DifferentiableLut6_BackwardApply call: dx clear, table conversion, the kernel, dW)",
                          "achieved": achieved_tf, "peak": fp32_peak / 1e12, "unit": "TFLOP/s", "frac": achieved_tf * 1e12 / fp32_peak,
                          "executed_frac": (FLOPS_BWD_EXECUTED + 10.0) * k_nf / (k_ms / 1e3) / fp32_peak,
+                         # the same fraction against the peak at the SM clock sampled during the step (a long step runs under the power cap)
+                         "frac_at_sampled_clock": (achieved_tf * 1e12 / (fp32_peak * clocks["sm_mhz"] * 1e6 / SM_CLOCK_HZ)) if clocks.get("sm_mhz") else None,
                          "peak_source": "FP32 CUDA-core peak = SMs * 128 lanes * 2 * 1.965 GHz; the path has no tensor-core work",
                          "ms_per_launch": k_ms, "launches_timed": len(timed.pairs), "node_frames_per_launch": k_nf,
                          "algorithmic_flops_per_nf": FLOPS_BWD, "algorithmic_bytes_per_nf": 12.0,

@@ -49,6 +49,8 @@ SIGNATURES = {
     "bbcu_host_bit_BinaryLut6_Forward": (_i, [_vp] * 4 + [_i] * 4),
     "bbcu_b200_host_alloc": (_vp, [_sz]),
     "bbcu_b200_host_free": (None, [_vp]),
+    "bbcu_int32_FrameBufferCopy": (_i, [_vp, _vp] + [_i] * 8 + [_vp]),
+    "bbcu_fp32_ConvBitToReal": (_i, [_vp, _vp, _f, _f] + [_i] * 4 + [_vp]),
     "bbcu_fp32_Vector_clamp": (_i, [_vp, _vp, _f, _f, _i, _vp]),
     "bbcu_fp32_Vector_set": (_i, [_vp, _f, _i, _vp]),
     "bbcu_fp32_OptimizerAdam": (_i, [_i] + [_vp] * 5 + [_f] * 3 + [_vp]),

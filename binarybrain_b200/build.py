@@ -12,7 +12,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libbbcu_b200.so")
 
-CU_SOURCES = ["runtime.cu", "lut6_layers.cu", "binary_lut6.cu", "stochastic_bn.cu", "no_alloc.cu", "host_io.cu", "losses.cu", "modulation.cu", "conv_lowering.cu", "binary_mode.cu"]
+CU_SOURCES = ["runtime.cu", "lut6_layers.cu", "binary_lut6.cu", "stochastic_bn.cu", "no_alloc.cu", "host_io.cu", "losses.cu", "modulation.cu", "conv_lowering.cu", "binary_mode.cu", "frame_buffer.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--extended-lambda",
               "-Xcompiler", "-fPIC"]
 

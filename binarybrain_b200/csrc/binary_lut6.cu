@@ -44,7 +44,7 @@ __device__ __forceinline__ uint32_t lut6_word(uint32_t x0, uint32_t x1, uint32_t
     return (v[0] & ~x5) | (v[1] & x5);
 }
 
-template <bool VEC>
+// Word-at-a-time kernel for rows that are not 16-byte aligned (any stride, any base address).
 __global__ void __launch_bounds__(kBlWarps * 32)
 k_binary_lut6(const BlArgs a)
 {
@@ -70,25 +70,11 @@ k_binary_lut6(const BlArgs a)
 
     const int w_begin = tile * a.Tw;
     const int w_end   = min(a.nwords, w_begin + a.Tw);
-    if (VEC) {
-        for (int w = w_begin + 4 * lane; w < w_end; w += 128) {
-            uint4 xv[6];
+    for (int w = w_begin + lane; w < w_end; w += 32) {
+        uint32_t xv[6];
 #pragma unroll
-            for (int j = 0; j < 6; ++j) xv[j] = __ldg(reinterpret_cast<const uint4 *>(rows[j] + w));
-            uint4 o;
-            o.x = lut6_word(xv[0].x, xv[1].x, xv[2].x, xv[3].x, xv[4].x, xv[5].x, A, B);
-            o.y = lut6_word(xv[0].y, xv[1].y, xv[2].y, xv[3].y, xv[4].y, xv[5].y, A, B);
-            o.z = lut6_word(xv[0].z, xv[1].z, xv[2].z, xv[3].z, xv[4].z, xv[5].z, A, B);
-            o.w = lut6_word(xv[0].w, xv[1].w, xv[2].w, xv[3].w, xv[4].w, xv[5].w, A, B);
-            *reinterpret_cast<uint4 *>(yrow + w) = o;
-        }
-    } else {
-        for (int w = w_begin + lane; w < w_end; w += 32) {
-            uint32_t xv[6];
-#pragma unroll
-            for (int j = 0; j < 6; ++j) xv[j] = __ldg(rows[j] + w);
-            yrow[w] = lut6_word(xv[0], xv[1], xv[2], xv[3], xv[4], xv[5], A, B);
-        }
+        for (int j = 0; j < 6; ++j) xv[j] = __ldg(rows[j] + w);
+        yrow[w] = lut6_word(xv[0], xv[1], xv[2], xv[3], xv[4], xv[5], A, B);
     }
 }
 
@@ -203,13 +189,8 @@ struct MuxTree<1, K, NW> {
 // while the copies of j+1 and j+2 are in flight.  No warp ever waits on a load it has only just issued, and no
 // CTA-wide barrier exists after set-up.
 // ---------------------------------------------------------------------------------------------
-#ifndef BB200_BL6_NW
-#define BB200_BL6_NW 8
-#endif
-#ifndef BB200_BL6_CTAS
-#define BB200_BL6_CTAS 2
-#endif
-constexpr int kPipeNW     = BB200_BL6_NW;             // words per lane and item
+constexpr int kPipeCtas   = 2;                        // resident CTAs per SM
+constexpr int kPipeNW     = 8;                        // words per lane and item
 constexpr int kPipeWords  = 32 * kPipeNW;             // words per row segment and item (1 KiB)
 constexpr int kPipeStages = 2;
 // dynamic shared memory layout: [rows: warp x stage x 6 x 256 words][barriers: warp x stage, padded to 128 B][level-1 pairs: warp x 32 x int2]
@@ -250,7 +231,7 @@ __device__ __forceinline__ int pipe_row(const BlArgs &a, PipePos pos, int warp, 
     return lane < 6 ? __ldg(a.idx + (size_t)node * 6 + lane) : 0;
 }
 
-__global__ void __launch_bounds__(kBlWarps * 32, BB200_BL6_CTAS)
+__global__ void __launch_bounds__(kBlWarps * 32, kPipeCtas)
 k_binary_lut6_pipe(const BlArgs a, int n_tiles, int *fault)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -374,7 +355,7 @@ extern "C" int bbcu_bit_BinaryLut6_Forward(const int *x, int *y, const int *idx,
         if (attr_ok && fault != nullptr) {
             const long long n_items = (long long)((a.nwords + kPipeWords - 1) / kPipeWords) * a.groups;
             BB200_REQUIRE(n_items < (1LL << 31) - 4096, BBCU_ERR_TOO_LARGE);      // 32-bit item arithmetic in the kernel
-            long long grid = (long long)BB200_BL6_CTAS * device_info().sm_count;
+            long long grid = (long long)kPipeCtas * device_info().sm_count;
             if (grid > n_items) grid = n_items;
             k_binary_lut6_pipe<<<(unsigned)grid, kBlWarps * 32, kPipeSmem, as_stream(stream)>>>(a, (a.nwords + kPipeWords - 1) / kPipeWords, fault);
             return launch_status();
@@ -382,7 +363,7 @@ extern "C" int bbcu_bit_BinaryLut6_Forward(const int *x, int *y, const int *idx,
     }
     // aligned rows without the shared-memory opt-in (or without a fault word): the non-pipelined 128-bit kernel; otherwise word loads
     if (vec) k_binary_lut6_2pipe<<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
-    else     k_binary_lut6<false><<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
+    else     k_binary_lut6<<<(unsigned)blocks, kBlWarps * 32, 0, as_stream(stream)>>>(a);
     return launch_status();
 }
 

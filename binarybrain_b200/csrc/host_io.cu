@@ -74,6 +74,13 @@ extern "C" int bbcu_host_bit_BinaryLut6_Forward(const int *host_x_buf, int *host
     BB200_CUDA(cudaMemcpyAsync(io.table, host_table, sizeof(int) * 2 * (size_t)node_size, cudaMemcpyHostToDevice, io.stream[0]));
     BB200_CUDA(cudaStreamSynchronize(io.stream[0]));
 
+    // On any error the copies already enqueued into the caller's host_y_buf are drained before the status goes back: the caller
+    // may free or reuse its buffers as soon as this function returns.
+    auto drain = [&](int status) {
+        for (int s = 0; s < kSlots; ++s)
+            if (cudaStreamSynchronize(io.stream[s]) != cudaSuccess) cudaGetLastError();
+        return status;
+    };
     const int chunks = (words + cw - 1) / cw;
     for (int k = 0; k < chunks; ++k) {
         const int s = k % kSlots;
@@ -81,15 +88,20 @@ extern "C" int bbcu_host_bit_BinaryLut6_Forward(const int *host_x_buf, int *host
         const int w0 = k * cw;
         const int nw = words - w0 < cw ? words - w0 : cw;
         const int frames_k = (k == chunks - 1) ? frame_size - w0 * 32 : nw * 32;
-        BB200_CUDA(cudaMemcpy2DAsync(io.x[s], sizeof(int) * (size_t)cw, host_x_buf + w0, sizeof(int) * (size_t)frame_stride, sizeof(int) * (size_t)nw,
-                                     (size_t)input_node_size, cudaMemcpyHostToDevice, st));
+        cudaError_t e = cudaMemcpy2DAsync(io.x[s], sizeof(int) * (size_t)cw, host_x_buf + w0, sizeof(int) * (size_t)frame_stride, sizeof(int) * (size_t)nw,
+                                          (size_t)input_node_size, cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) { cudaGetLastError(); return drain((int)e); }
         rc = bbcu_bit_BinaryLut6_Forward(static_cast<const int *>(io.x[s]), static_cast<int *>(io.y[s]), static_cast<const int *>(io.idx),
                                          static_cast<const int *>(io.table), node_size, frames_k, cw, st);
-        if (rc) return rc;
-        BB200_CUDA(cudaMemcpy2DAsync(host_y_buf + w0, sizeof(int) * (size_t)frame_stride, io.y[s], sizeof(int) * (size_t)cw, sizeof(int) * (size_t)nw,
-                                     (size_t)node_size, cudaMemcpyDeviceToHost, st));
+        if (rc) return drain(rc);
+        e = cudaMemcpy2DAsync(host_y_buf + w0, sizeof(int) * (size_t)frame_stride, io.y[s], sizeof(int) * (size_t)cw, sizeof(int) * (size_t)nw,
+                              (size_t)node_size, cudaMemcpyDeviceToHost, st);
+        if (e != cudaSuccess) { cudaGetLastError(); return drain((int)e); }
     }
-    for (int s = 0; s < kSlots; ++s) BB200_CUDA(cudaStreamSynchronize(io.stream[s]));
+    for (int s = 0; s < kSlots; ++s) {
+        const cudaError_t e = cudaStreamSynchronize(io.stream[s]);
+        if (e != cudaSuccess) { cudaGetLastError(); return drain((int)e); }
+    }
     return BBCU_OK;
 }
 

@@ -112,12 +112,10 @@ __device__ __forceinline__ void condition_raw(float (&xv)[4][6], const uint32_t 
             xv[q][j] = XBIT ? (((raw[q][j] >> lane) & 1u) ? bias : -bias) : condition_u(__uint_as_float(raw[q][j]), binary, bias);
 }
 
-#ifndef BB200_FWD_CTAS
-#define BB200_FWD_CTAS 2      // resident CTAs per SM the forward kernels are compiled for (register cap 65536 / (256 * n))
-#endif
+constexpr int kFwdCtas = 2;   // resident CTAs per SM the forward kernels are compiled for (register cap 65536 / (256 * n))
 
 template <bool XBIT, int PHASE, bool YBIT>
-__global__ void __launch_bounds__(kWarpsPerCta * 32, BB200_FWD_CTAS)
+__global__ void __launch_bounds__(kWarpsPerCta * 32, kFwdCtas)
 k_lut6_forward(const FwdArgs a)
 {
     __shared__ float4 s_tab[kWarpsPerCta][32];
@@ -702,21 +700,28 @@ k_lut6_backward(const BwdArgs a)
 }
 
 // ---------------------------------------------------------------------------------------------
-// Persistent, vectorised backward for fp32 frames whose rows start on 16-byte boundaries (the launcher's default).
+// Persistent backward for fp32 frames whose rows start on 16-byte boundaries (the launcher's default).
 //
-// Work item = (frame tile of a.T frames, group of 8 nodes), walked in tile-major order by one CTA per SM, so the CTAs in flight
-// sweep the node groups of one tile together: the tile's x rows come from HBM once, the other consumers of a row hit L2, and the
-// dx reductions of a row meet in L2 too.  The tile is therefore sized for L2, and what a wide tile used to amortise is made cheap
-// instead:
+// Work item = (frame tile of a.T frames, group of 8 nodes), walked in tile-major order by one CTA per SM; each warp owns one node
+// of the group.  What the kernel is bound by: an SM sub-partition issues one instruction per clock and a packed f32x2
+// instruction takes two issue slots (measured: 32 packed FMAs take 65 clocks per warp, and scalar FMAs, logic ops or anything
+// else issued beside them add their own clocks in full), so the time is the weighted instruction count -- 113 packed (226
+// slots) + about 105 others per frame -- over the issue rate.  Everything here is about the "others":
 //   * the per-node table arrives ready to use (k_table_halves has converted every table once per launch);
-//   * a warp streams its item in 128-frame chunks through a three-stage ring in shared memory: every lane copies, with 16-byte
-//     cp.async, the four consecutive frames of each of the six input rows and of dy that it will itself use, two chunks ahead
-//     of the arithmetic, so no lane ever waits for a barrier or for another lane, and the prefetch costs no registers;
-//   * a lane's four frames leave as one 128-bit reduction per input row (red.global.add.v4.f32);
+//   * global -> shared: a warp streams its item in 128-frame chunks through a three-stage ring; every lane copies 16 bytes (four
+//     consecutive frames) of each of the six input rows and of dy with cp.async, two chunks ahead of the arithmetic, so the
+//     prefetch holds no registers and the loop has no global address arithmetic per frame;
+//   * arithmetic: lane l takes the frame pairs 64 h + 2 l + {0, 1}, h = 0, 1, of the chunk: one conflict-free 64-bit shared load
+//     per row and pair;
+//   * the six input gradients of a pair go to a staging area in shared memory (conflict-free 64-bit stores); after the chunk's
+//     four frames every lane adds its four consecutive frames of each row to dx with one 128-bit reduction
+//     (red.global.add.v4.f32), which L2 resolves;
 //   * at the end of an item the 64 per-lane gradient sums are added across lanes through a padded transpose in shared memory
 //     (16 stores, 32 loads and 32 packed adds per lane instead of 62 shuffles with two selects each) and leave as one 8-byte
 //     reduction per lane into the coefficient-gradient scratch dC, which k_coeff_grads_to_dw maps to table gradients once per
 //     launch.
+// The tile is wide (1024-2048 frames) to amortise that flush: measured, the extra L2 misses of a wide tile cost less than
+// flushing more often, because the kernel is issue-bound, not memory-bound.
 // dx rows must be zero on entry.
 // ---------------------------------------------------------------------------------------------
 constexpr int kBvStages     = 3;
@@ -726,9 +731,11 @@ constexpr int kBvTabSlots   = 3;                                  // the copy si
 constexpr int kBvTabBytes   = 16 * 16;
 constexpr int kBvTrStride   = 68;                                 // floats per lane row of the transpose: 64 + 4 keeps 128-bit stores and
 constexpr int kBvTrBytes    = 32 * kBvTrStride * 4;               // 64-bit loads free of bank conflicts
+// per warp: the ring, the table slots, and the transpose buffer, which doubles as the dx staging area (6 x 512 bytes)
 constexpr int kBvWarpBytes  = kBvStages * kBvStageBytes + kBvTabSlots * kBvTabBytes + kBvTrBytes;
 constexpr int kBvSmem       = kWarpsPerCta * kBvWarpBytes;
 static_assert(kBvSmem <= 227 * 1024, "one CTA per SM must fit");
+static_assert(6 * kBvRowBytes <= kBvTrBytes, "dx staging fits the transpose buffer");
 
 // Every node's table in the half-packed form of lut6_forward_keep_halves: 16 x (c[2k], c[2k+32], c[2k+1], c[2k+33]).
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
@@ -760,13 +767,6 @@ k_coeff_grads_to_dw(const float4 *__restrict__ dC, float *__restrict__ dW, int O
     *dst = cur;
 }
 
-#ifdef BB200_TUNING
-__constant__ int g_bv_dbg;          // tuning builds only: bit 0 skips the dx reductions, bit 1 the per-item flush, bit 2 the reverse pass
-#define BV_DBG(bit) ((g_bv_dbg >> (bit)) & 1)
-#else
-#define BV_DBG(bit) 0
-#endif
-
 // Position of a 128-frame chunk in a warp's sequence: item (tile, group), chunk c of the item's n, table slot of the item.
 struct BvCursor {
     int tile, group, c, n, slot;
@@ -774,13 +774,13 @@ struct BvCursor {
 
 template <bool BN, bool BINARY>
 __global__ void __launch_bounds__(kWarpsPerCta * 32, 1)
-k_lut6_backward_vec(const BwdArgs a, const float4 *__restrict__ coef, float *__restrict__ dC, int n_tiles, int n_full, int n_last)
+k_lut6_backward_pipe(const BwdArgs a, const float4 *__restrict__ coef, float *__restrict__ dC, int n_tiles, int n_full, int n_last)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned char *my = smem_raw + (size_t)warp * kBvWarpBytes;
     unsigned char *my_tabs = my + kBvStages * kBvStageBytes;
-    float *tr = reinterpret_cast<float *>(my_tabs + kBvTabSlots * kBvTabBytes);
+    float *tr = reinterpret_cast<float *>(my_tabs + (kBvTabSlots * kBvTabBytes));
 
     const int step = (int)gridDim.x;
     const int dt = step / a.groups, dg = step - dt * a.groups;
@@ -795,16 +795,15 @@ k_lut6_backward_vec(const BwdArgs a, const float4 *__restrict__ coef, float *__r
     auto node_of = [&](const BvCursor &p) { return min(p.group * kWarpsPerCta + warp, a.O - 1); };      // a ragged last group repeats the last node
     auto row_of = [&](const BvCursor &p) { return (p.tile < n_tiles && lane < 6) ? __ldg(a.idx + (size_t)node_of(p) * 6 + lane) : 0; };
 
-    // ---- copy side: runs two chunks ahead of the arithmetic
     BvCursor ic;
     ic.tile = (int)blockIdx.x / a.groups;
     ic.group = (int)blockIdx.x - ic.tile * a.groups;
     ic.c = 0;
     ic.n = ic.tile == n_tiles - 1 ? n_last : n_full;
     ic.slot = 0;
-    BvCursor cc = ic;                              // arithmetic side
-    int ist = 0;                                   // ring stage the next copy fills
-    int row_i = row_of(ic), row_in;                // lanes 0..5: input rows of the copy side's item and of the item after it
+    BvCursor cc = ic;
+    int ist = 0;
+    int row_i = row_of(ic), row_in;
     {
         BvCursor t = ic;
         next_item(t);
@@ -813,7 +812,7 @@ k_lut6_backward_vec(const BwdArgs a, const float4 *__restrict__ coef, float *__r
     const float *xf = static_cast<const float *>(a.x);
     auto issue = [&]() {
         if (ic.tile < n_tiles) {
-            const int f = ic.tile * a.T + ic.c * kFramesPerIter + 4 * lane;          // first of this lane's four frames
+            const int f = ic.tile * a.T + ic.c * kFramesPerIter + 4 * lane;
             const bool in_row = f < a.xs;
             unsigned char *st = my + ist * kBvStageBytes + lane * 16;
 #pragma unroll
@@ -832,13 +831,13 @@ k_lut6_backward_vec(const BwdArgs a, const float4 *__restrict__ coef, float *__r
                 row_in = row_of(t);
             }
         }
-        cp_async_commit();                          // always: the group count per chunk stays uniform
+        cp_async_commit();
         ist = ist == kBvStages - 1 ? 0 : ist + 1;
     };
-    issue();
-    issue();
+#pragma unroll
+    for (int k = 0; k < kBvStages - 1; ++k) issue();
 
-    int cst = 0;                                    // ring stage of the chunk being computed
+    int cst = 0;
     int row_c = row_of(cc), row_cn;
     float mean_n = 0.0f, rstd_n = 0.0f, dmean_n = 0.0f, dvar_n = 0.0f;
     if (BN && cc.tile < n_tiles) {
@@ -851,7 +850,7 @@ k_lut6_backward_vec(const BwdArgs a, const float4 *__restrict__ coef, float *__r
         const bool live_node = node_raw < a.O;
         const int node = min(node_raw, a.O - 1);
         const float mean = mean_n, rstd = rstd_n, dmean = dmean_n, dvar = dvar_n;
-        {   // the next item's rows and batch-norm constants travel one item ahead of their use
+        {
             BvCursor t = cc;
             next_item(t);
             row_cn = row_of(t);
@@ -865,54 +864,57 @@ k_lut6_backward_vec(const BwdArgs a, const float4 *__restrict__ coef, float *__r
         for (int i = 0; i < 32; ++i) acc2[i] = 0ull;
         const int f_tile = cc.tile * a.T;
         for (; cc.c < cc.n; ++cc.c) {
-            issue();                                 // chunk k + 2 goes into the stage chunk k - 1 was read from
-            cp_async_wait<2>();                      // chunk k (and this item's table) has landed
-            const unsigned char *st = my + cst * kBvStageBytes + lane * 16;
+            issue();                                 // refills the stage read kBvStages - 1 chunks ago (all lanes are past the barrier below)
+            cp_async_wait<kBvStages - 1>();
+            __syncwarp();                            // every lane's part of chunk k (and of this item's table) has landed
+            const float *st2 = reinterpret_cast<const float *>(my + cst * kBvStageBytes) + 2 * lane;
             cst = cst == kBvStages - 1 ? 0 : cst + 1;
-            float4 xq[6];
+            const int f0 = f_tile + cc.c * kFramesPerIter;
+            // lane l takes the frame pairs 64 h + 2 l + {0, 1}, h = 0, 1: one 64-bit shared load per row and pair, one 64-bit store per
+            // input gradient and pair (both conflict-free)
 #pragma unroll
-            for (int j = 0; j < 6; ++j) xq[j] = *reinterpret_cast<const float4 *>(st + j * kBvRowBytes);
-            const float4 dyq = *reinterpret_cast<const float4 *>(st + 6 * kBvRowBytes);
-            const int f0 = f_tile + cc.c * kFramesPerIter + 4 * lane;
-            float dxq[6][4];
+            for (int h = 0; h < 2; ++h) {
+                float2 xp[6];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                float u[6];
+                for (int j = 0; j < 6; ++j) xp[j] = *reinterpret_cast<const float2 *>(st2 + j * kFramesPerIter + 64 * h);
+                const float2 gp = *reinterpret_cast<const float2 *>(st2 + 6 * kFramesPerIter + 64 * h);
+                float dxp[6][2];
 #pragma unroll
-                for (int j = 0; j < 6; ++j) {
-                    const float v = i == 0 ? xq[j].x : i == 1 ? xq[j].y : i == 2 ? xq[j].z : xq[j].w;
-                    u[j] = BINARY ? (v > 0.5f ? a.bias : -a.bias) : __saturatef(v) - 0.5f;           // the same values as condition_u()
+                for (int e = 0; e < 2; ++e) {
+                    float u[6];
+#pragma unroll
+                    for (int j = 0; j < 6; ++j) {
+                        const float v = e ? xp[j].y : xp[j].x;
+                        u[j] = BINARY ? (v > 0.5f ? a.bias : -a.bias) : __saturatef(v) - 0.5f;           // the same values as condition_u()
+                    }
+                    KeptHalves D;
+                    const float v = lut6_forward_keep_halves(tab, u, D);
+                    float g = e ? gp.y : gp.x;
+                    if (BN) {
+                        const float tanh_x = ((v - mean) * rstd) * a.gamma + a.beta;
+                        if (tanh_x <= 0.0f || tanh_x >= 1.0f) g = 0.0f;
+                        const float dxc = (g * a.gamma) * rstd;
+                        g = dxc + dmean + (v * dvar * a.rF);
+                    }
+                    if (f0 + 64 * h + 2 * lane + e >= a.F || !live_node) g = 0.0f;
+                    float dxv[6];
+                    lut6_reverse_halves(tab, u, D, g, acc2, dxv);
+#pragma unroll
+                    for (int j = 0; j < 6; ++j) dxp[j][e] = dxv[j];
                 }
-                KeptHalves D;
-                const float v = lut6_forward_keep_halves(tab, u, D);
-                float g = i == 0 ? dyq.x : i == 1 ? dyq.y : i == 2 ? dyq.z : dyq.w;
-                if (BN) {
-                    const float tanh_x = ((v - mean) * rstd) * a.gamma + a.beta;
-                    if (tanh_x <= 0.0f || tanh_x >= 1.0f) g = 0.0f;
-                    const float dxc = (g * a.gamma) * rstd;
-                    g = dxc + dmean + (v * dvar * a.rF);
-                }
-                if (f0 + i >= a.F || !live_node) g = 0.0f;
-                float dxv[6];
-                if (BV_DBG(2)) {
 #pragma unroll
-                    for (int j = 0; j < 6; ++j) dxv[j] = g * u[j] + v;
-                    acc2[i] = add2(acc2[i], pack2(v, g));
-                } else
-                lut6_reverse_halves(tab, u, D, g, acc2, dxv);
-#pragma unroll
-                for (int j = 0; j < 6; ++j) dxq[j][i] = dxv[j];
+                for (int j = 0; j < 6; ++j) *reinterpret_cast<float2 *>(tr + j * kFramesPerIter + 64 * h + 2 * lane) = make_float2(dxp[j][0], dxp[j][1]);
             }
-            const bool write = f0 < a.F && live_node;
+            __syncwarp();
+            const bool write = f0 + 4 * lane < a.F && live_node;
 #pragma unroll
             for (int j = 0; j < 6; ++j) {
-                const int r = __shfl_sync(kFull, row_c, j);          // every lane takes part in the shuffle
-                if (write && !BV_DBG(0)) red_add_v4(a.dx + (size_t)r * a.dxs + f0, dxq[j][0], dxq[j][1], dxq[j][2], dxq[j][3]);
+                const int r = __shfl_sync(kFull, row_c, j);
+                const float4 d = *reinterpret_cast<const float4 *>(tr + j * kFramesPerIter + 4 * lane);
+                if (write) red_add_v4(a.dx + (size_t)r * a.dxs + f0 + 4 * lane, d.x, d.y, d.z, d.w);
             }
         }
-        // ---- item done: sum the 64 accumulators over the lanes.  Lane l stores its 64 values as row l (16 x float4 in the table's
-        // half-packed order), then adds up columns 2l, 2l + 1 of all 32 rows.
-        if (BV_DBG(1)) { next_item(cc); row_c = row_cn; if (acc2[5] == 0x12345ull) dC[0] = 1.0f; continue; }
+        // ---- item done: sum the 64 accumulators over the lanes through the (padded) transpose
         __syncwarp();
 #pragma unroll
         for (int k = 0; k < 16; ++k) {
@@ -933,6 +935,7 @@ k_lut6_backward_vec(const BwdArgs a, const float4 *__restrict__ coef, float *__r
         float lo, hi;
         unpack2(add2(add2(s0, s1), add2(s2, s3)), lo, hi);
         if (live_node) red_add_v2(dC + (size_t)node * 64 + 2 * lane, lo, hi);
+        __syncwarp();                                // the transpose buffer is the next chunk's dx staging area
         next_item(cc);
         row_c = row_cn;
     }
@@ -1192,25 +1195,25 @@ k_lut6_backward_stg(const BwdArgs a, const float4 *__restrict__ coef, float *__r
     cp_async_wait<0>();
 }
 
-// Frames per tile of the persistent backward: the tile's x rows and dx rows (8 bytes per row and frame) get half of L2.
-static int backward_vec_tile(long long rows, int groups, int F)
+// Frames per tile of the persistent backward.  A wide tile amortises the per-item flush of the 64 gradient sums; a narrow one keeps
+// the tile's x and dx rows (8 bytes per row and frame) in L2.  The kernel is issue-bound, so the wide tile wins until the rows
+// exceed L2 several times over -- measured on B200: 8192 rows 1.60 / 1.54 / 1.52 ms at 512 / 1024 / 2048 frames, 65536 rows
+// 3.57 / 3.42 / 3.46 ms -- hence four times L2, between 512 and 2048 frames.
+static int backward_pipe_tile(long long rows, int groups, int F)
 {
     const DeviceInfo &di = device_info();
-    long long t = (long long)(di.l2_bytes / 2) / (8 * (rows > 0 ? rows : 1));
+    long long t = (long long)(4 * di.l2_bytes) / (8 * (rows > 0 ? rows : 1));
     t = (t / kFramesPerIter) * kFramesPerIter;
     if (t > 2048) t = 2048;
-    if (t < kFramesPerIter) t = kFramesPerIter;
-#ifdef BB200_TUNING
-    if (const char *e = getenv("BB200_BWD_TILE")) t = atoi(e);
-#endif
+    if (t < 512) t = 512;
     // small layers: narrow the tile until every SM has a couple of items
     while (t > kFramesPerIter && (long long)groups * ((F + t - 1) / t) < 2LL * di.sm_count) t -= kFramesPerIter;
     return (int)t;
 }
 
-// The persistent vectorised backward (k_lut6_backward_vec); BBCU_ERR_NO_MEMORY when its scratch (512 bytes per node) cannot be had.
+// The persistent backward (k_lut6_backward_pipe); BBCU_ERR_NO_MEMORY when its scratch (512 bytes per node) cannot be had.
 // `tmp` / `tmp_bytes`: scratch handed in by the caller (the reference's dev_dx_tmp), used when it is large enough and 16-byte aligned.
-static int launch_backward_vec(BwdArgs a, bool bn, int I, void *tmp, size_t tmp_bytes, cudaStream_t st)
+static int launch_backward_pipe(BwdArgs a, bool bn, int I, void *tmp, size_t tmp_bytes, cudaStream_t st)
 {
     const size_t need = (size_t)a.O * 512;
     unsigned char *scratch = nullptr;
@@ -1219,27 +1222,11 @@ static int launch_backward_vec(BwdArgs a, bool bn, int I, void *tmp, size_t tmp_
     if (scratch == nullptr) return BBCU_ERR_NO_MEMORY;
     float4 *coef = reinterpret_cast<float4 *>(scratch);
     float *dC = reinterpret_cast<float *>(scratch + (size_t)a.O * 256);
-    auto kern = bn ? (a.binary ? k_lut6_backward_vec<true, true> : k_lut6_backward_vec<true, false>)
-                   : (a.binary ? k_lut6_backward_vec<false, true> : k_lut6_backward_vec<false, false>);
-    int smem = kBvSmem, nw = kWarpsPerCta;
-#ifdef BB200_TUNING
-    if (const char *e = getenv("BB200_BWD_KERNEL")) {
-        if (atoi(e) == 8) {
-            kern = bn ? (a.binary ? k_lut6_backward_stg<true, true, 8, 3> : k_lut6_backward_stg<true, false, 8, 3>)
-                      : (a.binary ? k_lut6_backward_stg<false, true, 8, 3> : k_lut6_backward_stg<false, false, 8, 3>);
-            smem = BsLayout<8, 3>::kSmem;
-        } else if (atoi(e) == 12) {
-            kern = bn ? (a.binary ? k_lut6_backward_stg<true, true, 12, 2> : k_lut6_backward_stg<true, false, 12, 2>)
-                      : (a.binary ? k_lut6_backward_stg<false, true, 12, 2> : k_lut6_backward_stg<false, false, 12, 2>);
-            smem = BsLayout<12, 2>::kSmem;
-            nw = 12;
-            a.groups = (a.O + 11) / 12;
-        }
-    }
-#endif
-    if (!allow_big_smem(kern, smem)) return BBCU_ERR_NO_MEMORY;
+    auto kern = bn ? (a.binary ? k_lut6_backward_pipe<true, true> : k_lut6_backward_pipe<true, false>)
+                   : (a.binary ? k_lut6_backward_pipe<false, true> : k_lut6_backward_pipe<false, false>);
+    if (!allow_big_smem(kern, kBvSmem)) return BBCU_ERR_NO_MEMORY;
     const long long rows = (long long)(I < 6LL * a.O ? I : 6LL * a.O);
-    a.T = backward_vec_tile(rows, a.groups, a.F);
+    a.T = backward_pipe_tile(rows, a.groups, a.F);
     const int n_tiles = (a.F + a.T - 1) / a.T;
     const long long n_items = (long long)n_tiles * a.groups;
     BB200_REQUIRE(n_items < (1LL << 31) - 4096, BBCU_ERR_TOO_LARGE);          // 32-bit item arithmetic in the kernel
@@ -1247,14 +1234,11 @@ static int launch_backward_vec(BwdArgs a, bool bn, int I, void *tmp, size_t tmp_
     const int n_last = (a.F - (n_tiles - 1) * a.T + kFramesPerIter - 1) / kFramesPerIter;
     long long grid = device_info().sm_count;
     if (grid > n_items) grid = n_items;
-#ifdef BB200_TUNING
-    { int dbg = getenv("BB200_BV_DBG") ? atoi(getenv("BB200_BV_DBG")) : 0; cudaMemcpyToSymbolAsync(g_bv_dbg, &dbg, sizeof(int), 0, cudaMemcpyHostToDevice, st); }
-#endif
     const int groups8 = (a.O + kWarpsPerCta - 1) / kWarpsPerCta;
     k_table_halves<<<groups8, kWarpsPerCta * 32, 0, st>>>(a.W, coef, a.O, a.lut_binarize);
     BB200_CUDA(cudaPeekAtLastError());
     BB200_CUDA(cudaMemsetAsync(dC, 0, (size_t)a.O * 256, st));
-    kern<<<(unsigned)grid, nw * 32, smem, st>>>(a, coef, dC, n_tiles, n_full, n_last);
+    kern<<<(unsigned)grid, kWarpsPerCta * 32, kBvSmem, st>>>(a, coef, dC, n_tiles, n_full, n_last);
     BB200_CUDA(cudaPeekAtLastError());
     k_coeff_grads_to_dw<<<groups8, kWarpsPerCta * 32, 0, st>>>(reinterpret_cast<const float4 *>(dC), a.dW, a.O);
     return launch_status();
@@ -1301,20 +1285,14 @@ static int backward_common(BwdArgs a, bool bn, long long total_frames, float *dm
         a.dmean = dmean_out; a.dvar = dvar_out;
     }
     if (!XBIT) {
-        // rows on 16-byte boundaries (the FrameBuffer layout gives them): the persistent vectorised kernel
+        // rows on 16-byte boundaries (the FrameBuffer layout gives them): the persistent kernel
         const bool aligned = ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.dy) | reinterpret_cast<uintptr_t>(a.dx) |
                                reinterpret_cast<uintptr_t>(a.dW)) & 15) == 0 && (a.xs % 4) == 0 && (a.dys % 4) == 0 && (a.dxs % 4) == 0;
-#ifdef BB200_TUNING
-        if (getenv("BB200_BWD_OLD")) goto old_kernel;
-#endif
         if (aligned) {
-            const int rc = launch_backward_vec(a, bn, I, tmp, tmp_bytes, st);
+            const int rc = launch_backward_pipe(a, bn, I, tmp, tmp_bytes, st);
             if (rc != BBCU_ERR_NO_MEMORY) return rc;
         }
     }
-#ifdef BB200_TUNING
-old_kernel:
-#endif
     if (bn) k_lut6_backward<XBIT, true><<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(a);
     else    k_lut6_backward<XBIT, false><<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(a);
     return launch_status();

@@ -11,8 +11,11 @@
 
 #include <cuda_runtime_api.h>
 
+#include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
+#include <new>
 #include <memory>
 #include <sstream>
 #include <stdexcept>
@@ -78,51 +81,72 @@ public:
 };
 
 
-// Host/device mirrored byte buffer.
+// Host/device mirrored byte buffer.  The host mirror of a buffer of kPinnedFrom bytes or more is page-locked (cudaMallocHost, as the
+// reference's include/bbcu/bbcu_util.h:121 does for every host buffer) so that its transfers run at full PCIe rate and
+// asynchronously; small buffers and processes without a device use plain heap memory.
 class Memory
 {
-    std::size_t                 m_size = 0;
-    std::vector<std::uint8_t>   m_host;
-    void                       *m_dev = nullptr;
-    bool                        m_host_valid = true;    // host copy holds the current contents
-    bool                        m_dev_valid  = false;   // device copy holds the current contents
+    static constexpr std::size_t kPinnedFrom = 64 * 1024;
+
+    std::size_t     m_size = 0;
+    std::uint8_t   *m_host = nullptr;
+    bool            m_pinned = false;
+    void           *m_dev = nullptr;
+    bool            m_host_valid = true;    // host copy holds the current contents
+    bool            m_dev_valid  = false;   // device copy holds the current contents
+
+    void release_host()
+    {
+        if (m_host) { if (m_pinned) bbcu_b200_host_free(m_host); else std::free(m_host); }
+        m_host = nullptr;
+        m_pinned = false;
+    }
 
 public:
     Memory() {}
     explicit Memory(std::size_t size) { Resize(size); }
     Memory(Memory const &) = delete;
     Memory &operator=(Memory const &) = delete;
-    ~Memory() { if (m_dev) bbcu_LocalHeap_Free(m_dev); }
+    ~Memory() { if (m_dev) bbcu_LocalHeap_Free(m_dev); release_host(); }
 
     void Resize(std::size_t size)
     {
         if (m_dev) { bbcu_LocalHeap_Free(m_dev); m_dev = nullptr; }
+        release_host();
         m_size = size;
-        m_host.assign(size, 0);
+        if (size >= kPinnedFrom && Manager::IsDeviceAvailable()) {
+            m_host = static_cast<std::uint8_t *>(bbcu_b200_host_alloc(size));
+            m_pinned = m_host != nullptr;
+        }
+        if (!m_host) m_host = static_cast<std::uint8_t *>(std::malloc(size ? size : 1));
+        if (!m_host) throw std::bad_alloc();
+        std::memset(m_host, 0, size);
         m_host_valid = true;
         m_dev_valid  = false;
     }
     std::size_t GetSize() const { return m_size; }
+    bool IsHostPinned() const { return m_pinned; }
+    bool IsDeviceCurrent() const { return m_dev_valid; }
 
     // new_buf: the caller overwrites everything, so nothing is copied (reference: Lock(true)).
     void *Host(bool new_buf = false)
     {
         if (!m_host_valid && !new_buf && m_dev) {
-            BB_CUDA_CHECK(cudaMemcpyAsync(m_host.data(), m_dev, m_size, cudaMemcpyDeviceToHost, Manager::Stream()));
+            BB_CUDA_CHECK(cudaMemcpyAsync(m_host, m_dev, m_size, cudaMemcpyDeviceToHost, Manager::Stream()));
             BB_CUDA_CHECK(cudaStreamSynchronize(Manager::Stream()));
         }
         m_host_valid = true;
         m_dev_valid  = false;
-        return m_host.data();
+        return m_host;
     }
     void const *HostConst()
     {
         if (!m_host_valid && m_dev) {
-            BB_CUDA_CHECK(cudaMemcpyAsync(m_host.data(), m_dev, m_size, cudaMemcpyDeviceToHost, Manager::Stream()));
+            BB_CUDA_CHECK(cudaMemcpyAsync(m_host, m_dev, m_size, cudaMemcpyDeviceToHost, Manager::Stream()));
             BB_CUDA_CHECK(cudaStreamSynchronize(Manager::Stream()));
         }
         m_host_valid = true;
-        return m_host.data();
+        return m_host;
     }
     void *Dev(bool new_buf = false)
     {
@@ -139,8 +163,10 @@ public:
             m_dev_valid = false;
         }
         if (!m_dev_valid && !new_buf && m_size) {
-            // pageable host memory: the runtime stages the copy before returning, so m_host may change afterwards
-            BB_CUDA_CHECK(cudaMemcpyAsync(m_dev, m_host.data(), m_size, cudaMemcpyHostToDevice, Manager::Stream()));
+            BB_CUDA_CHECK(cudaMemcpyAsync(m_dev, m_host, m_size, cudaMemcpyHostToDevice, Manager::Stream()));
+            // a page-locked source is read by the copy engine after this call returns: the host side may write it again only once
+            // the copy is done (a pageable source has been staged by the runtime already)
+            if (m_pinned) BB_CUDA_CHECK(cudaStreamSynchronize(Manager::Stream()));
         }
         m_dev_valid = true;
         return m_dev;
@@ -219,6 +245,101 @@ public:
     void const *LockMemoryConst() const                { return m_mem->HostConst(); }
 
     void FillZero() { std::memset(m_mem->Host(true), 0, m_mem->GetSize()); }
+    bool IsHostPinned() const { return m_mem && m_mem->IsHostPinned(); }
+
+    // ---- copies and views (include/bb/FrameBuffer.h:372-395, 465-560, 843-900, 1370-1460).  Where the data is current on the
+    // device the work is done there (bbcu_int32_FrameBufferCopy, bbcu_fp32_ConvBitToReal); otherwise on the host mirror.
+    FrameBuffer Clone() const
+    {
+        FrameBuffer dst(m_frame_size, m_shape, m_type);
+        CopyTo(dst);
+        return dst;
+    }
+
+    // Block copy of frame_size frames x node_size nodes (0 = as many as fit).  Bit buffers: frame offsets and sizes are multiples of 32
+    // on the device path; other bit ranges go through the host mirror bit by bit.
+    void CopyTo(FrameBuffer &dst, index_t frame_size = 0, index_t src_frame_offset = 0, index_t dst_frame_offset = 0, index_t node_size = 0,
+                index_t src_node_offset = 0, index_t dst_node_offset = 0) const
+    {
+        BB_ASSERT(dst.GetType() == GetType());
+        if (node_size <= 0)  node_size  = std::min(dst.GetNodeSize() - dst_node_offset, GetNodeSize() - src_node_offset);
+        if (frame_size <= 0) frame_size = std::min(dst.GetFrameSize() - dst_frame_offset, GetFrameSize() - src_frame_offset);
+        BB_ASSERT(frame_size + src_frame_offset <= GetFrameSize() && frame_size + dst_frame_offset <= dst.GetFrameSize());
+        BB_ASSERT(node_size + src_node_offset <= GetNodeSize() && node_size + dst_node_offset <= dst.GetNodeSize());
+        const bool bit = m_type == BB_TYPE_BIT;
+        const bool word_aligned = !bit || (frame_size % 32 == 0 && src_frame_offset % 32 == 0 && dst_frame_offset % 32 == 0);
+        if (m_mem->IsDeviceCurrent() && word_aligned && Manager::IsDeviceAvailable()) {
+            const index_t per = bit ? 32 : 1;
+            BBCU_CHECK(bbcu_int32_FrameBufferCopy(static_cast<int *>(dst.m_mem->Dev()), static_cast<int const *>(m_mem->DevConst()), (int)node_size,
+                                                  (int)dst_node_offset, (int)src_node_offset, (int)(frame_size / per), (int)(dst_frame_offset / per),
+                                                  (int)(src_frame_offset / per), (int)(dst.m_frame_stride / 4), (int)(m_frame_stride / 4),
+                                                  Manager::Stream()));
+            return;
+        }
+        auto sp = static_cast<std::uint8_t const *>(m_mem->HostConst());
+        auto dp = static_cast<std::uint8_t *>(dst.m_mem->Host());
+        for (index_t n = 0; n < node_size; ++n) {
+            auto srow = sp + (n + src_node_offset) * m_frame_stride;
+            auto drow = dp + (n + dst_node_offset) * dst.m_frame_stride;
+            if (!bit) {
+                std::memcpy(drow + 4 * dst_frame_offset, srow + 4 * src_frame_offset, 4 * (std::size_t)frame_size);
+            } else {
+                for (index_t f = 0; f < frame_size; ++f) {
+                    const index_t sf = f + src_frame_offset, df = f + dst_frame_offset;
+                    const std::uint32_t b = (reinterpret_cast<std::uint32_t const *>(srow)[sf >> 5] >> (sf & 31)) & 1u;
+                    auto &w = reinterpret_cast<std::uint32_t *>(drow)[df >> 5];
+                    w = (w & ~(1u << (df & 31))) | (b << (df & 31));
+                }
+            }
+        }
+    }
+
+    // `size` frames from `offset` on, as a new buffer (FrameBuffer.h:1370-1405)
+    FrameBuffer FrameRange(index_t size, index_t offset = 0) const
+    {
+        BB_ASSERT(offset >= 0 && offset < m_frame_size && size >= 0 && size <= m_frame_size - offset);
+        FrameBuffer dst(size, m_shape, m_type);
+        if (size > 0) CopyTo(dst, size, offset, 0);
+        return dst;
+    }
+
+    // `size` nodes from `offset` on, as a new 1-D buffer (FrameBuffer.h:1408-1424)
+    FrameBuffer Range(index_t size, index_t offset = 0) const
+    {
+        BB_ASSERT(offset >= 0 && offset < GetNodeSize() && size >= 0 && size <= GetNodeSize() - offset);
+        FrameBuffer dst(m_frame_size, {size}, m_type);
+        if (size > 0 && m_frame_size > 0) CopyTo(dst, m_frame_size, 0, 0, size, offset, 0);
+        return dst;
+    }
+
+    // the nodes of `buf` appended to this buffer's (FrameBuffer.h:1427-1455)
+    FrameBuffer Concatenate(FrameBuffer const &buf) const
+    {
+        BB_ASSERT(buf.GetType() == GetType() && buf.m_frame_size == m_frame_size);
+        FrameBuffer dst(m_frame_size, {GetNodeSize() + buf.GetNodeSize()}, m_type);
+        if (m_frame_size > 0) {
+            CopyTo(dst, m_frame_size, 0, 0, GetNodeSize(), 0, 0);
+            buf.CopyTo(dst, m_frame_size, 0, 0, buf.GetNodeSize(), 0, GetNodeSize());
+        }
+        return dst;
+    }
+
+    // bit <-> fp32 with the values of the reference's CPU branch ((float)bit, i.e. 0 / 1; fp32 -> bit by > 0.5 as everywhere on this path)
+    FrameBuffer ConvertTo(int data_type) const
+    {
+        if (data_type == m_type) return Clone();
+        FrameBuffer dst(m_frame_size, m_shape, data_type);
+        if (m_type == BB_TYPE_BIT && data_type == BB_TYPE_FP32 && m_mem->IsDeviceCurrent() && Manager::IsDeviceAvailable()) {
+            BBCU_CHECK(bbcu_fp32_ConvBitToReal(static_cast<int const *>(m_mem->DevConst()), static_cast<float *>(dst.m_mem->Dev(true)), 0.0f, 1.0f,
+                                               (int)GetNodeSize(), (int)m_frame_size, (int)(m_frame_stride / 4), (int)(dst.m_frame_stride / 4),
+                                               Manager::Stream()));
+            return dst;
+        }
+        dst.FillZero();
+        for (index_t n = 0; n < GetNodeSize(); ++n)
+            for (index_t f = 0; f < m_frame_size; ++f) dst.SetFP32(f, n, GetFP32(f, n));
+        return dst;
+    }
 
     // element access on the host mirror (slow path, as in the reference: FrameBuffer.h:1077-1146)
     float GetFP32(index_t frame, index_t node) const

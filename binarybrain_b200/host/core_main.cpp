@@ -97,6 +97,15 @@ PYBIND11_MODULE(core, m)
         .def("get_node_size", &FrameBuffer::GetNodeSize)
         .def("get_node_shape", &FrameBuffer::GetShape)
         .def("fill_zero", &FrameBuffer::FillZero)
+        .def("clone", &FrameBuffer::Clone)
+        .def("copy_to", &FrameBuffer::CopyTo, py::arg("dst"), py::arg("frame_size") = 0, py::arg("src_frame_offset") = 0, py::arg("dst_frame_offset") = 0,
+             py::arg("node_size") = 0, py::arg("src_node_offset") = 0, py::arg("dst_node_offset") = 0)
+        .def("frame_range", &FrameBuffer::FrameRange, py::arg("size"), py::arg("offset") = 0)
+        .def("range", &FrameBuffer::Range, py::arg("size"), py::arg("offset") = 0)
+        .def("concatenate", &FrameBuffer::Concatenate)
+        .def("convert_to", &FrameBuffer::ConvertTo)
+        .def("is_host_pinned", &FrameBuffer::IsHostPinned)
+        .def("lock_device", [](FrameBuffer &b) { return (std::uintptr_t)b.LockDeviceMemory(); })
         .def("get_fp32", &FrameBuffer::GetFP32)
         .def("set_fp32", &FrameBuffer::SetFP32)
         .def_static("calc_frame_stride", &FrameBuffer::CalcFrameStride)

@@ -180,6 +180,16 @@ int bbcu_host_bit_BinaryLut6_Forward(const int *host_x_buf, int *host_y_buf, con
 void *bbcu_b200_host_alloc(size_t bytes);
 void  bbcu_b200_host_free(void *ptr);
 
+/* ------------------------------------------------------------------ FrameBuffer helpers (the container either side of the path) */
+/* bbcu_int32_FrameBufferCopy, include/bbcu/bbcu.h:265-278 (FrameBuffer::CopyTo, include/bb/FrameBuffer.h:481-535): copies a block of
+ * node_size rows x frame_size 32-bit words between two frame buffers; offsets and strides in words (fp32 frames, or 32 bit frames). */
+int bbcu_int32_FrameBufferCopy(int *dev_dst_buf, const int *dev_src_buf, int node_size, int dst_node_offset, int src_node_offset,
+                               int frame_size, int dst_frame_offset, int src_frame_offset, int dst_frame_stride, int src_frame_stride,
+                               bbcu_stream_t stream);
+/* bbcu_ConvBitToReal<float>, include/bbcu/bbcu.h:247-258 (FrameBuffer::ConvertTo, include/bb/FrameBuffer.h:843-866): y = bit ? value1 : value0. */
+int bbcu_fp32_ConvBitToReal(const int *dev_x_buf, float *dev_y_buf, float value0, float value1, int node_size, int frame_size,
+                            int x_frame_stride, int y_frame_stride, bbcu_stream_t stream);
+
 /* ------------------------------------------------------------------ Neighbours of the path that its callers need every step */
 /* bbcu_fp32_Vector_clamp, include/bbcu/bbcu.h:191-198 (the W clamp of DifferentiableLutN.h:605-608 / StochasticLutN.h:451). */
 int bbcu_fp32_Vector_clamp(float *dev_dst, const float *dev_src, float lo, float hi, int size, bbcu_stream_t stream);

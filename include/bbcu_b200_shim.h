@@ -205,6 +205,22 @@ inline int bbcu_bit_BinatyLut6_Forward(const int * dev_x_buf, int * dev_y_buf, c
         frame_stride, (bbcu_stream_t)streamId));
 }
 
+inline int bbcu_int32_FrameBufferCopy(int * dev_dst_buf, const int * dev_src_buf, int node_size, int dst_node_offset, int src_node_offset,
+        int frame_size, int dst_frame_offset, int src_frame_offset, int dst_frame_stride, int src_frame_stride, cudaStream_t streamId)
+{
+    return bbcu_b200_shim_check(bbcu_b200::bbcu_int32_FrameBufferCopy(dev_dst_buf, dev_src_buf, node_size, dst_node_offset, src_node_offset,
+            frame_size, dst_frame_offset, src_frame_offset, dst_frame_stride, src_frame_stride, (bbcu_stream_t)streamId));
+}
+
+/* a template on the value type in BinaryBrain (include/bbcu/bbcu.h:247-258); float is the one instance its headers use */
+template <typename T> inline int bbcu_ConvBitToReal(const int * dev_x_buf, T * dev_y_buf, T value0, T value1, int node_size, int frame_size,
+        int x_frame_stride, int y_frame_stride, cudaStream_t streamId)
+{
+    static_assert(sizeof(T) == sizeof(float) && T(0.5) > T(0), "libbbcu_b200 provides the float conversion only");
+    return bbcu_b200_shim_check(bbcu_b200::bbcu_fp32_ConvBitToReal(dev_x_buf, (float *)dev_y_buf, (float)value0, (float)value1, node_size,
+            frame_size, x_frame_stride, y_frame_stride, (bbcu_stream_t)streamId));
+}
+
 /* Leave these two out (define BBCU_B200_SHIM_NO_VECTOR) when cuda/Vector.cu stays in the build for the tensor arithmetic. */
 #ifndef BBCU_B200_SHIM_NO_VECTOR
 inline int bbcu_fp32_Vector_clamp(float * dev_dst, const float * dev_src, float lo, float hi, int size, cudaStream_t streamId)

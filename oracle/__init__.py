@@ -464,6 +464,13 @@ class _Ref:
         self.lib.bbref_init_layer(C.c_int(n_in), C.c_int(n_out), C.c_uint64(seed), C.c_char_p(connection.encode()), _vp(idx), _vp(W))
         return idx, W
 
+    def init_connection(self, in_shape, out_shape, seed=1, connection=""):
+        """[out_nodes, 6] wiring of a fresh reference layer with these node shapes under a connection rule."""
+        ins, outs = np.asarray(in_shape, np.int32), np.asarray(out_shape, np.int32)
+        idx = np.zeros((int(np.prod(outs)), 6), np.int32)
+        self.lib.bbref_init_connection(C.c_int(len(ins)), _vp(ins), _vp(outs), C.c_uint64(seed), C.c_char_p(connection.encode()), _vp(idx))
+        return idx
+
     def differentiable_lut6_adam(self, x, idx, W, dy, steps, batch_norm=True, binary=False, lut_binarize=False, gamma=0.3, beta=0.5,
                                  momentum=0.9, lr=0.001, beta1=0.9, beta2=0.999):
         x = np.ascontiguousarray(x, np.float32)

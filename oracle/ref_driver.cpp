@@ -368,6 +368,23 @@ int bbref_init_layer(int I, int O, std::uint64_t seed, char const *connection, i
     return 0;
 }
 
+// The wiring a fresh reference layer draws for node shapes of `dims` axes (in_shape / out_shape) under a connection rule
+// ("", "random", "serial", "pointwise", "depthwise", "gauss").
+int bbref_init_connection(int dims, int const *in_shape, int const *out_shape, std::uint64_t seed, char const *connection, int *idx)
+{
+    bb::DifferentiableLutN<6, float, float>::create_t c;
+    c.output_shape = bb::indices_t(out_shape, out_shape + dims);
+    c.seed         = seed;
+    c.connection   = connection ? connection : "";
+    auto lut = bb::DifferentiableLutN<6, float, float>::Create(c);
+    lut->SetInputShape(bb::indices_t(in_shape, in_shape + dims));
+    const int O = (int)lut->GetOutputNodeSize();
+    for (int n = 0; n < O; ++n)
+        for (int i = 0; i < 6; ++i)
+            idx[n * 6 + i] = (int)lut->GetNodeConnectionIndex(n, i);
+    return 0;
+}
+
 // steps x { DifferentiableLutN forward(train) -> backward(dy) -> OptimizerAdam::Update } on fixed x, dy.
 int bbref_differentiable_lut6_adam(float const *x, int I, int O, int F, int const *idx, float *W,
                                    int batch_norm, int binary, int lut_binarize,

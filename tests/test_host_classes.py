@@ -67,6 +67,35 @@ def test_seeded_wiring_and_tables_match_the_reference(core, golden):
     assert (other.get_connection() != golden["init_32_16_s1_idx"]).any()
 
 
+def test_every_wiring_rule_draws_the_reference_tables(core):
+    """random / serial / pointwise / depthwise / gauss (include/bb/ConnectionTable.h:150-284): the same seed gives the table the
+    reference's layer draws, for 1-D and {c, h, w} node shapes (golden from the unmodified reference; live where it is built)."""
+    import sys
+    sys.path.insert(0, os.path.join(ROOT, "tests", "golden"))
+    from make_golden_wiring import CASES, key
+    from oracle import ref
+    z = np.load(os.path.join(ROOT, "tests", "golden", "wiring_golden.npz"))
+    for rule, ins, outs, seed in CASES:
+        layer = core.DifferentiableLut6_fp32_fp32.create(outs, connection=rule, seed=seed)
+        assert layer.set_input_shape(ins) == outs
+        got = layer.get_connection()
+        assert np.array_equal(got, z[key(rule, ins, outs, seed)]), (rule, ins, outs)
+        assert all(len(set(r)) == 6 for r in got.tolist()) or rule == "serial"
+        if ref.available():
+            assert np.array_equal(got, ref.init_connection(ins, outs, seed=seed, connection=rule))
+    # structure: pointwise stays inside the pixel, depthwise inside the channel
+    pw = core.DifferentiableLut6_fp32_fp32.create([9, 5, 4], connection="pointwise", seed=7)
+    pw.set_input_shape([12, 5, 4])
+    idx = pw.get_connection()
+    assert ((idx % 20) == (np.arange(9 * 20) % 20)[:, None]).all()
+    dw = core.DifferentiableLut6_fp32_fp32.create([7, 3, 4], connection="depthwise", seed=7)
+    dw.set_input_shape([7, 6, 5])
+    assert ((dw.get_connection() // 30) == (np.arange(7 * 12) // 12)[:, None]).all()
+    with pytest.raises(Exception):
+        bad = core.DifferentiableLut6_fp32_fp32.create([8], connection="no_such_rule")
+        bad.set_input_shape([16])
+
+
 def test_framebuffer_layout_and_numpy_round_trip(core):
     rng = np.random.default_rng(0)
     a = rng.random((39, 5), dtype=np.float32)                  # [frames, nodes]
@@ -83,6 +112,75 @@ def test_framebuffer_layout_and_numpy_round_trip(core):
     assert fbb.get_fp32(0, 0) == 1.0 - bits[0, 0]
     shaped = core.FrameBuffer(8, [3, 4], core.TYPE_FP32)
     assert shaped.get_node_shape() == [3, 4] and shaped.get_node_size() == 12
+
+
+def _framebuffer_views(core, on_device):
+    """CopyTo / FrameRange / Range / Concatenate / ConvertTo / Clone against numpy slicing, on the host mirror or (on_device) with the
+    source made current on the GPU first, which routes through bbcu_int32_FrameBufferCopy / bbcu_fp32_ConvBitToReal."""
+    rng = np.random.default_rng(12)
+    F, N = 200, 9
+    a = rng.random((F, N), dtype=np.float32)
+    for dtype, ref in ((core.TYPE_FP32, a), (core.TYPE_BIT, (a > 0.5).astype(np.float32))):
+        def make():
+            fb = core.FrameBuffer.from_numpy_fp32(a, dtype)
+            if on_device:
+                assert fb.lock_device() != 0
+            return fb
+        assert np.array_equal(make().clone().numpy_fp32(), ref)
+        assert np.array_equal(make().range(4, 3).numpy_fp32(), ref[:, 3:7])
+        assert np.array_equal(make().frame_range(64, 96).numpy_fp32(), ref[96:160])             # word-aligned: the device path for bit frames too
+        assert np.array_equal(make().frame_range(50, 7).numpy_fp32(), ref[7:57])                # ragged bit ranges go through the host mirror
+        cat = make().concatenate(make().range(2, 0))
+        assert cat.get_node_size() == N + 2 and np.array_equal(cat.numpy_fp32(), np.concatenate([ref, ref[:, :2]], axis=1))
+        dst = core.FrameBuffer(F, [N], dtype)
+        dst.fill_zero()
+        make().copy_to(dst, 32, 64, 128, 3, 1, 5)
+        want = np.zeros_like(ref)
+        want[128:160, 5:8] = ref[64:96, 1:4]
+        assert np.array_equal(dst.numpy_fp32(), want)
+    bits = core.FrameBuffer.from_numpy_fp32(a, core.TYPE_BIT)
+    if on_device:
+        bits.lock_device()
+    real = bits.convert_to(core.TYPE_FP32)
+    assert real.get_type() == core.TYPE_FP32 and np.array_equal(real.numpy_fp32(), (a > 0.5).astype(np.float32))       # 0 / 1, as the reference's CPU branch
+    back = core.FrameBuffer.from_numpy_fp32(a, core.TYPE_FP32).convert_to(core.TYPE_BIT)
+    assert np.array_equal(back.numpy_fp32(), (a > 0.5).astype(np.float32))
+
+
+def test_framebuffer_copies_and_views_on_the_host(core):
+    _framebuffer_views(core, on_device=False)
+
+
+@pytest.mark.gpu
+def test_framebuffer_copies_and_views_on_the_device(core):
+    _framebuffer_views(core, on_device=True)
+    big = core.FrameBuffer(40000, [4], core.TYPE_FP32)
+    assert big.is_host_pinned()                               # 640 KB mirror: page-locked
+
+
+@pytest.mark.gpu
+def test_frame_buffer_copy_and_bit_to_real_operators():
+    """bbcu_int32_FrameBufferCopy / bbcu_fp32_ConvBitToReal through the C ABI: odd offsets, strides that are not multiples of four words,
+    rows longer than one CTA's segment."""
+    import torch
+    from binarybrain_b200 import abi
+    g = torch.Generator(device="cuda").manual_seed(5)
+    for (nodes, words, ss, ds, so, do_, n_off) in [(7, 9000, 9001, 9003, 1, 2, 1), (3, 4096, 4096, 8192, 0, 4096, 0), (5, 33, 40, 48, 3, 7, 2)]:
+        src = torch.randint(-2**31, 2**31 - 1, (nodes + n_off, ss), dtype=torch.int32, device="cuda", generator=g)
+        dst = torch.full((nodes + 1, ds), 17, dtype=torch.int32, device="cuda")
+        abi.call("bbcu_int32_FrameBufferCopy", dst.data_ptr(), src.data_ptr(), nodes, 1, n_off, words - so, do_, so, ds, ss,
+                 torch.cuda.current_stream().cuda_stream)
+        want = torch.full_like(dst, 17)
+        want[1:1 + nodes, do_:do_ + words - so] = src[n_off:n_off + nodes, so:words]
+        assert torch.equal(dst, want)
+    for (nodes, frames, xs, ys) in [(5, 1000, 32, 1000), (3, 8193, 264, 8200), (2, 31, 1, 33)]:
+        x = torch.randint(-2**31, 2**31 - 1, (nodes, xs), dtype=torch.int32, device="cuda", generator=g)
+        y = torch.full((nodes, ys), 9.0, device="cuda")
+        abi.call("bbcu_fp32_ConvBitToReal", x.data_ptr(), y.data_ptr(), -1.0, 2.5, nodes, frames, xs, ys, torch.cuda.current_stream().cuda_stream)
+        f = torch.arange(frames, device="cuda")
+        bit = (x[:, (f >> 5)] >> (f & 31)[None, :]) & 1
+        assert torch.equal(y[:, :frames], torch.where(bit.bool(), torch.tensor(2.5, device="cuda"), torch.tensor(-1.0, device="cuda")))
+        assert (y[:, frames:] == 9.0).all()
 
 
 def test_commands_and_defaults(core):

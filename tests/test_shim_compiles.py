@@ -17,8 +17,7 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REFERENCE = os.environ.get("BB_REFERENCE", "/root/reference")
 CUDA_INC = os.environ.get("CUDA_INC", "/usr/local/cuda/include")
-NOT_ON_THE_PATH = ("bbcu_ConvBitToReal", "bbcu_fp32_Vector_sqrt", "bbcu_fp32_Vector_add_ex", "bbcu_fp32_Vector_sub_ex", "bbcu_fp32_Vector_mul_ex",
-                   "bbcu_fp32_Vector_div_ex", "bbcu_int32_FrameBufferCopy", "bbcu_fp32_Vector_")
+NOT_ON_THE_PATH = ("bbcu_fp32_Vector_sqrt", "bbcu_fp32_Vector_add_ex", "bbcu_fp32_Vector_sub_ex", "bbcu_fp32_Vector_mul_ex", "bbcu_fp32_Vector_div_ex")
 
 
 @pytest.fixture(scope="module")
@@ -48,7 +47,7 @@ def test_every_call_site_resolves_to_the_c_abi(undefined_symbols):
             "bbcu_fp32_StochasticBatchNormalization_ForwardTraining", "bbcu_fp32_StochasticBatchNormalization_ReForward",
             "bbcu_fp32_StochasticBatchNormalization_ForwardInference", "bbcu_fp32_StochasticBatchNormalization_Backward",
             "bbcu_bit_BinatyLut6_Forward", "bbcu_LocalHeap_Malloc", "bbcu_LocalHeap_Free", "bbcu_GetDevice", "bbcu_IsHostOnly",
-            "bbcu_fp32_OptimizerAdam", "bbcu_fp32_Vector_clamp", "bbcu_fp32_Im2Col_Forward", "bbcu_fp32_Col2Im_Forward", "bbcu_fp32_MaxPooling_Forward"}
+            "bbcu_fp32_OptimizerAdam", "bbcu_fp32_Vector_clamp", "bbcu_fp32_ConvBitToReal", "bbcu_fp32_Im2Col_Forward", "bbcu_fp32_Col2Im_Forward", "bbcu_fp32_MaxPooling_Forward"}
     assert must <= plain, must - plain
 
 
