@@ -354,6 +354,11 @@ def binary_lut6_section(torch, ops, dist, world, rank, steps, warmup, frames, ex
            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
                         "traffic": NCU_BL6_TRAFFIC_BYTES_PER_FRAME * frames, "peak_source": f"of {which}", "kernel": "k_binary_lut6_pipe",
                         "algorithmic_bytes_per_launch": algo_bytes}}
+    if extras and rank == 0:
+        # the same launch through the truth-table-immediate kernel (15 logic operations per word instead of 63, one indexed branch per
+        # table byte): kept measurable because it is the formulation with the fewest operations and still the slower one
+        sec_imm = time_op(torch, lambda: ops.binary_lut6_forward(x, idx, table, frames, y=y, lop3_immediate=True), max(2, min(steps, 5)))
+        out["lop3_immediate_variant"] = {"ms_per_step": sec_imm * 1e3, "frac": algo_bytes / sec_imm / 1e9 / hbm, "kernel": "k_binary_lut6_imm"}
     if extras and world == 1:
         # end to end through the operator with host buffers: H2D of x, kernel, D2H of y, every step (chunk-pipelined inside the call)
         hx = torch.empty(x.shape, dtype=torch.int32).pin_memory()

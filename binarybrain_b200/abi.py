@@ -46,6 +46,7 @@ SIGNATURES = {
     "bbcu_fp32_StochasticBatchNormalization_Backward": (_i, [_vp] * 5 + [_f] * 2 + [_i] * 4 + [_vp]),
     "bbcu_bit_BinaryLut6_Forward": (_i, [_vp] * 4 + [_i] * 3 + [_vp]),
     "bbcu_bit_BinatyLut6_Forward": (_i, [_vp] * 4 + [_i] * 3 + [_vp]),
+    "bbcu_bit_BinaryLut6_Forward_Lop3Immediate": (_i, [_vp] * 4 + [_i] * 3 + [_vp]),
     "bbcu_host_bit_BinaryLut6_Forward": (_i, [_vp] * 4 + [_i] * 4),
     "bbcu_b200_host_alloc": (_vp, [_sz]),
     "bbcu_b200_host_free": (None, [_vp]),

@@ -16,6 +16,9 @@
 // Reference semantics: the bit-input branches of include/bb/StochasticLutN.h:432-560 and include/bb/DifferentiableLutN.h:
 // 747-905 (CPU), operators bbcu_bit_bit_fp32_StochasticLut_Forward, bbcu_bit_fp32_DifferentiableLutN_ForwardTraining /
 // _ForwardInference (include/bbcu/bbcu.h:540-560, 600-618, 712-727).
+#include <map>
+#include <mutex>
+
 #include "common.cuh"
 #include "lut6_core.cuh"
 
@@ -383,11 +386,13 @@ __device__ __forceinline__ float2 pattern_sums_to_table_grads(float2 v, int lane
 
 // One warp per node.  BN = false: dW += K^T Hdy.  BN = true: the batch sums, dmean / dvar, then dW += K^T Hg with
 // Hg[p] = mask[p] gamma rstd Hdy[p] + (dmean + Y[p] dvar / F) H[p].
+// `sums_out` (frame-sharded callers): the node's local (dstd, dmeanx) go out as fp64 and nothing else is done.
+// `sums_in`: the sums over ALL ranks' frames come in instead of being formed from this rank's Hdy; rF = 1 / total frames.
 template <bool BN>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 k_bit_backward_finalize(const float *__restrict__ hdy, const uint32_t *__restrict__ hist, const float *__restrict__ Y, float *dW,
                         const float *__restrict__ mean_buf, const float *__restrict__ rstd_buf, float *dmean_out, float *dvar_out, float gamma,
-                        float beta, float bias, int O, int F)
+                        float beta, float bias, int O, float rF, double *sums_out, const double *__restrict__ sums_in)
 {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int node = blockIdx.x * kWarpsPerCta + warp;
@@ -396,14 +401,24 @@ k_bit_backward_finalize(const float *__restrict__ hdy, const uint32_t *__restric
     if (BN) {
         const float2 y = reinterpret_cast<const float2 *>(Y + (size_t)node * 64)[lane];
         const uint2 h = reinterpret_cast<const uint2 *>(hist + (size_t)node * 64)[lane];
-        const float mean = mean_buf[node], rstd = rstd_buf[node], rstd2 = rstd * rstd, rF = 1.0f / (float)F;
+        const float mean = mean_buf[node], rstd = rstd_buf[node], rstd2 = rstd * rstd;
         const float t0 = ((y.x - mean) * rstd) * gamma + beta, t1 = ((y.y - mean) * rstd) * gamma + beta;
         const float m0 = (t0 <= 0.0f || t0 >= 1.0f) ? 0.0f : 1.0f, m1 = (t1 <= 0.0f || t1 >= 1.0f) ? 0.0f : 1.0f;
         const float dxn0 = gamma * (m0 * hg.x), dxn1 = gamma * (m1 * hg.y);                   // sum over the pattern's frames of gamma * masked dy
-        double dstd = -((double)(dxn0 * (y.x - mean) * rstd2) + (double)(dxn1 * (y.y - mean) * rstd2));
-        double dmeanx = -((double)(dxn0 * rstd) + (double)(dxn1 * rstd));
-        dstd = warp_sum(dstd);
-        dmeanx = warp_sum(dmeanx);
+        double dstd, dmeanx;
+        if (sums_in != nullptr) {
+            dstd = sums_in[2 * (size_t)node];
+            dmeanx = sums_in[2 * (size_t)node + 1];
+        } else {
+            dstd = -((double)(dxn0 * (y.x - mean) * rstd2) + (double)(dxn1 * (y.y - mean) * rstd2));
+            dmeanx = -((double)(dxn0 * rstd) + (double)(dxn1 * rstd));
+            dstd = warp_sum(dstd);
+            dmeanx = warp_sum(dmeanx);
+        }
+        if (sums_out != nullptr) {
+            if (lane == 0) { sums_out[2 * (size_t)node] = dstd; sums_out[2 * (size_t)node + 1] = dmeanx; }
+            return;
+        }
         const float dvar = (float)dstd * rstd;
         const float dmean = ((float)dmeanx - (mean * dvar)) * rF;
         if (lane == 0) { dvar_out[node] = dvar; dmean_out[node] = dmean; }
@@ -541,8 +556,30 @@ struct Scratch {
     unsigned char *pat; // extra bytes asked for by the caller (pattern bytes of the fp32 binary-mode training forward)
 };
 
+// What the statistics half of a frame-sharded backward left in a stream's scratch (pattern counts, per-pattern dy sums, pattern
+// bytes), so that the apply half that follows it on the same stream need not repeat that pass.  Any other use of the scratch
+// forgets it; the apply half checks every field and redoes the pass when something differs.
+struct PassOneRecord {
+    const void *x = nullptr, *dy = nullptr, *W = nullptr;
+    int O = 0, F = 0;
+    long long fs = 0;
+};
+std::mutex g_record_mu;
+std::map<std::pair<int, cudaStream_t>, PassOneRecord> g_records;
+
+std::pair<int, cudaStream_t> record_key(cudaStream_t st)
+{
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return std::make_pair(dev, st);
+}
+
 bool carve(Scratch &s, int O, cudaStream_t st, size_t extra = 0)
 {
+    {
+        std::lock_guard<std::mutex> g(g_record_mu);
+        g_records.erase(record_key(st));
+    }
     const size_t per_node = 64 * 4 + 64 * 4 + 8 + 64 * 4;        // Y, pattern counts, truth table, per-pattern dy sums
     const size_t fixed = (per_node * (size_t)O + 255) & ~(size_t)255;
     unsigned char *base = static_cast<unsigned char *>(stream_scratch(st, fixed + extra, 1));
@@ -716,7 +753,7 @@ int bit_backward_by_table(bool bn, bool x_is_fp32, const void *x, const float *d
         if (x_is_fp32) k_bit_backward_frames<kBwdPlainAll, true><<<nb, threads, 0, st>>>(a);
         else           k_bit_backward_frames<kBwdPlainAll, false><<<nb, threads, 0, st>>>(a);
         BB200_CUDA(cudaPeekAtLastError());
-        k_bit_backward_finalize<false><<<a.groups, threads, 0, st>>>(hdy, nullptr, nullptr, dW, nullptr, nullptr, nullptr, nullptr, 0.0f, 0.0f, bias, O, F);
+        k_bit_backward_finalize<false><<<a.groups, threads, 0, st>>>(hdy, nullptr, nullptr, dW, nullptr, nullptr, nullptr, nullptr, 0.0f, 0.0f, bias, O, 0.0f, nullptr, nullptr);
         return launch_status();
     }
     k_pattern_values<kTableNone><<<a.groups, threads, 0, st>>>(W, s.Y, nullptr, nullptr, nullptr, 0.0f, 0.0f, bias, O, lut_binarize);
@@ -732,10 +769,112 @@ int bit_backward_by_table(bool bn, bool x_is_fp32, const void *x, const float *d
     if (x_is_fp32) k_bit_backward_frames<kBwdHistOnly, true><<<nb, threads, 0, st>>>(a);
     else           k_bit_backward_frames<kBwdHistOnly, false><<<nb, threads, 0, st>>>(a);
     BB200_CUDA(cudaPeekAtLastError());
-    k_bit_backward_finalize<true><<<a.groups, threads, 0, st>>>(hdy, s.hist, s.Y, dW, mean, rstd, dmean_out, dvar_out, gamma, beta, bias, O, F);
+    k_bit_backward_finalize<true><<<a.groups, threads, 0, st>>>(hdy, s.hist, s.Y, dW, mean, rstd, dmean_out, dvar_out, gamma, beta, bias, O, 1.0f / (float)F, nullptr, nullptr);
     BB200_CUDA(cudaPeekAtLastError());
     if (x_is_fp32) k_bit_backward_frames<kBwdNormDx, true><<<nb, threads, 0, st>>>(a);
     else           k_bit_backward_frames<kBwdNormDx, false><<<nb, threads, 0, st>>>(a);
+    return launch_status();
+}
+
+
+// ---- the two halves of the batch-norm backward for frame-sharded callers (binary mode; bit rows or fp32 rows)
+namespace {
+
+// pass 1: pattern values, pattern counts and per-pattern dy sums (and, for fp32 rows, the pattern bytes) of this rank's frames
+int backward_pass_one(bool x_is_fp32, BitBwdArgs &a, Scratch &s, float *&hdy, const void *x, const float *dy, const int *idx, const float *W,
+                      float bias, int O, int F, long long xs, long long fs, int lut_binarize, cudaStream_t st, bool reuse)
+{
+    const size_t pat_bytes = x_is_fp32 ? (size_t)O * (size_t)fs : 0;
+    if (pat_bytes > ((size_t)1 << 30)) return BBCU_ERR_NO_MEMORY;
+    PassOneRecord want;
+    want.x = x; want.dy = dy; want.W = W; want.O = O; want.F = F; want.fs = fs;
+    bool have = false;
+    if (reuse) {
+        std::lock_guard<std::mutex> g(g_record_mu);
+        auto it = g_records.find(record_key(st));
+        have = it != g_records.end() && it->second.x == x && it->second.dy == dy && it->second.W == W && it->second.O == O && it->second.F == F &&
+               it->second.fs == fs;
+    }
+    if (!carve(s, O, st, pat_bytes)) return BBCU_ERR_NO_MEMORY;           // same size as before: the same block (and it forgets the record)
+    hdy = reinterpret_cast<float *>(s.hist) + (size_t)O * 64;
+    a = BitBwdArgs{};
+    a.x = static_cast<const uint32_t *>(x); a.dy = dy; a.idx = idx; a.W = W; a.hdy = hdy; a.hist = s.hist; a.pat = pat_bytes ? s.pat : nullptr;
+    a.bias = bias; a.O = O; a.F = F; a.xs = xs; a.fs = fs; a.lut_binarize = lut_binarize;
+    a.groups = (O + kWarpsPerCta - 1) / kWarpsPerCta;
+    const int words = (F + 31) / 32;
+    a.tile_words = 128;
+    while (a.tile_words > 32 && (long long)a.groups * ((words + a.tile_words - 1) / a.tile_words) < 2LL * device_info().sm_count) a.tile_words /= 2;
+    const long long blocks = (long long)a.groups * ((words + a.tile_words - 1) / a.tile_words);
+    BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+    if (!have) {
+        const unsigned threads = kWarpsPerCta * 32;
+        BB200_CUDA(cudaMemsetAsync(hdy, 0, (size_t)O * 256, st));
+        k_pattern_values<kTableNone><<<a.groups, threads, 0, st>>>(W, s.Y, nullptr, nullptr, nullptr, 0.0f, 0.0f, bias, O, lut_binarize);
+        BB200_CUDA(cudaPeekAtLastError());
+        BB200_CUDA(cudaMemsetAsync(s.hist, 0, (size_t)O * 256, st));
+        if (!x_is_fp32) {
+            int tw = 4096;
+            while (tw > 32 && (long long)a.groups * ((words + tw - 1) / tw) < 2LL * device_info().sm_count) tw /= 2;
+            const long long hb = (long long)a.groups * ((words + tw - 1) / tw);
+            k_pattern_histogram<<<(unsigned)hb, threads, 0, st>>>(a.x, idx, s.hist, O, F, xs, a.groups, tw);
+            BB200_CUDA(cudaPeekAtLastError());
+        }
+        if (x_is_fp32) k_bit_backward_frames<kBwdHistOnly, true><<<(unsigned)blocks, threads, 0, st>>>(a);
+        else           k_bit_backward_frames<kBwdHistOnly, false><<<(unsigned)blocks, threads, 0, st>>>(a);
+        BB200_CUDA(cudaPeekAtLastError());
+    }
+    return BBCU_OK;
+}
+
+}   // namespace
+
+// Statistics half: this rank's (dstd, dmeanx) per node into `sums` ([O][2] fp64), to be added over the ranks by the caller.
+int bit_backward_stats_by_table(bool x_is_fp32, const void *x, const float *dy, const int *idx, const float *W, const float *mean, const float *rstd,
+                                double *sums, float gamma, float beta, float bias, int O, int F, long long xs, long long fs, int lut_binarize,
+                                cudaStream_t st)
+{
+    if (x_is_fp32 && xs != fs) return BBCU_ERR_NO_MEMORY;
+    if (O == 0) return BBCU_OK;
+    if (F == 0) { BB200_CUDA(cudaMemsetAsync(sums, 0, sizeof(double) * 2 * (size_t)O, st)); return BBCU_OK; }
+    BitBwdArgs a;
+    Scratch s;
+    float *hdy = nullptr;
+    int rc = backward_pass_one(x_is_fp32, a, s, hdy, x, dy, idx, W, bias, O, F, xs, fs, lut_binarize, st, false);
+    if (rc) return rc;
+    k_bit_backward_finalize<true><<<a.groups, kWarpsPerCta * 32, 0, st>>>(hdy, s.hist, s.Y, nullptr, mean, rstd, nullptr, nullptr, gamma, beta, bias, O,
+                                                                          0.0f, sums, nullptr);
+    rc = launch_status();
+    if (rc == BBCU_OK) {
+        PassOneRecord r;
+        r.x = x; r.dy = dy; r.W = W; r.O = O; r.F = F; r.fs = fs;
+        std::lock_guard<std::mutex> g(g_record_mu);
+        g_records[record_key(st)] = r;
+    }
+    return rc;
+}
+
+// Apply half: `sums` hold (dstd, dmeanx) over the frames of ALL ranks, total_frames is their number.  dx must be zero on entry;
+// dW receives this rank's share.
+int bit_backward_apply_by_table(bool x_is_fp32, const void *x, const float *dy, float *dx, const int *idx, const float *W, float *dW, const float *mean,
+                                const float *rstd, const double *sums, float *dmean_out, float *dvar_out, float gamma, float beta, float bias, int O,
+                                int F, long long xs, long long fs, long long total_frames, int lut_binarize, cudaStream_t st)
+{
+    if (x_is_fp32 && xs != fs) return BBCU_ERR_NO_MEMORY;
+    if (O == 0 || F == 0) return BBCU_OK;
+    BitBwdArgs a;
+    Scratch s;
+    float *hdy = nullptr;
+    int rc = backward_pass_one(x_is_fp32, a, s, hdy, x, dy, idx, W, bias, O, F, xs, fs, lut_binarize, st, true);
+    if (rc) return rc;
+    const float rF = 1.0f / (float)total_frames;
+    const unsigned threads = kWarpsPerCta * 32;
+    k_bit_backward_finalize<true><<<a.groups, threads, 0, st>>>(hdy, s.hist, s.Y, dW, mean, rstd, dmean_out, dvar_out, gamma, beta, bias, O, rF, nullptr,
+                                                                sums);
+    BB200_CUDA(cudaPeekAtLastError());
+    a.dx = dx; a.mean = mean; a.rstd = rstd; a.dmean = dmean_out; a.dvar = dvar_out; a.gamma = gamma; a.beta = beta; a.rF = rF;
+    const long long blocks = (long long)a.groups * (((F + 31) / 32 + a.tile_words - 1) / a.tile_words);
+    if (x_is_fp32) k_bit_backward_frames<kBwdNormDx, true><<<(unsigned)blocks, threads, 0, st>>>(a);
+    else           k_bit_backward_frames<kBwdNormDx, false><<<(unsigned)blocks, threads, 0, st>>>(a);
     return launch_status();
 }
 

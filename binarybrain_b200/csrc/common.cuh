@@ -60,6 +60,15 @@ int bit_backward_by_table(bool bn, bool x_is_fp32, const void *x, const float *d
                           const float *mean, const float *rstd, float *dmean_out, float *dvar_out, float gamma, float beta, float bias, int O, int F,
                           long long xs, long long fs, int lut_binarize, cudaStream_t st);
 
+// The batch-norm backward of a binary-mode layer in two halves for frame-sharded callers (the caller adds `sums` over the ranks in
+// between); both decline with BBCU_ERR_NO_MEMORY like the calls above.
+int bit_backward_stats_by_table(bool x_is_fp32, const void *x, const float *dy, const int *idx, const float *W, const float *mean, const float *rstd,
+                                double *sums, float gamma, float beta, float bias, int O, int F, long long xs, long long fs, int lut_binarize,
+                                cudaStream_t st);
+int bit_backward_apply_by_table(bool x_is_fp32, const void *x, const float *dy, float *dx, const int *idx, const float *W, float *dW, const float *mean,
+                                const float *rstd, const double *sums, float *dmean_out, float *dvar_out, float gamma, float beta, float bias, int O,
+                                int F, long long xs, long long fs, long long total_frames, int lut_binarize, cudaStream_t st);
+
 int f32_binary_forward_by_table(int mode, const float *x, float *y, const int *idx, const float *W, float *mean, float *rstd, float *rmean,
                                 float *rvar, float gamma, float beta, float momentum, float bias, int O, int F, long long fs, int lut_binarize,
                                 cudaStream_t st);

@@ -1258,6 +1258,12 @@ static int backward_common(BwdArgs a, bool bn, long long total_frames, float *dm
                                              a.bias, a.O, a.F, a.xs, a.dxs, a.lut_binarize, st);
         if (rc != BBCU_ERR_NO_MEMORY) return rc;
     }
+    if ((XBIT || a.binary) && bn && ext_sums != nullptr && a.dys == a.dxs) {
+        // frame-sharded caller: the apply half of the same route, with the batch sums of all ranks
+        const int rc = bit_backward_apply_by_table(!XBIT, a.x, a.dy, a.dx, a.idx, a.W, a.dW, a.mean, a.rstd, ext_sums, dmean_out, dvar_out, a.gamma,
+                                                   a.beta, a.bias, a.O, a.F, a.xs, a.dxs, total_frames, a.lut_binarize, st);
+        if (rc != BBCU_ERR_NO_MEMORY) return rc;
+    }
     a.groups = (a.O + kWarpsPerCta - 1) / kWarpsPerCta;
     const long long rows = (long long)(I < 6LL * a.O ? I : 6LL * a.O);
     // Wide tiles: a warp reduces its 64 dW accumulators across lanes once per (node, tile), about 250 instructions, so the
@@ -1610,6 +1616,11 @@ extern "C" int bbcu_fp32_DifferentiableLut6_BackwardStats(const float *x, const 
     BB200_REQUIRE_PTR(dy); BB200_REQUIRE_PTR(mean); BB200_REQUIRE_PTR(rstd);
     BB200_REQUIRE(frame_stride >= frame_size, BBCU_ERR_BAD_STRIDE);
     cudaStream_t st = as_stream(stream);
+    if (binary_mode) {        // two-valued inputs: the sums follow from the per-pattern dy sums (binary_mode.cu)
+        rc = bit_backward_stats_by_table(true, x, dy, idx, W, mean, rstd, dev_sums, gamma, beta, unbinarize_bias, node_size, frame_size, frame_stride,
+                                         frame_stride, lut_binarize, st);
+        if (rc != BBCU_ERR_NO_MEMORY) return rc;
+    }
     BB200_CUDA(cudaMemsetAsync(dev_sums, 0, sizeof(double) * 2 * (size_t)node_size, st));
     if (node_size == 0 || frame_size == 0) return BBCU_OK;
     BwdArgs a = {};

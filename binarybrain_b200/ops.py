@@ -173,13 +173,15 @@ def stochastic_bn_backward(x, dy, mean, rstd, frames, gamma=0.2):
 
 
 # ------------------------------------------------------------------------------------------ BinaryLut6
-def binary_lut6_forward(x, idx, table, frames, y=None):
-    """Bit-packed inference forward; ``table`` is [nodes, 2] int32 (64-entry truth table per node)."""
+def binary_lut6_forward(x, idx, table, frames, y=None, lop3_immediate=False):
+    """Bit-packed inference forward; ``table`` is [nodes, 2] int32 (64-entry truth table per node).
+    lop3_immediate: evaluate through the truth-table-immediate kernel (same results; aligned rows only)."""
     _chk(x, torch.int32, "x"); _chk(idx, torch.int32, "idx"); _chk(table, torch.int32, "table")
     O = idx.shape[0]
     if y is None:
         y = torch.empty((O, x.shape[1]), dtype=torch.int32, device=x.device)
-    abi.call("bbcu_bit_BinaryLut6_Forward", _p(x), _p(y), _p(idx), _p(table), O, frames, x.shape[1], _stream())
+    name = "bbcu_bit_BinaryLut6_Forward_Lop3Immediate" if lop3_immediate else "bbcu_bit_BinaryLut6_Forward"
+    abi.call(name, _p(x), _p(y), _p(idx), _p(table), O, frames, x.shape[1], _stream())
     return y
 
 

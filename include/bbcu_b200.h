@@ -171,6 +171,13 @@ int bbcu_bit_BinaryLut6_Forward(const int *dev_x_buf, int *dev_y_buf, const int 
 int bbcu_bit_BinatyLut6_Forward(const int *dev_x_buf, int *dev_y_buf, const int *dev_input_index, const int *dev_table,
                                 int node_size, int frame_size, int frame_stride, bbcu_stream_t stream);
 
+/* Additive: the same operator evaluated with the table bytes as lop3 immediates (15 logic operations per 32 frames instead of 63, one
+ * indexed branch per table byte).  Bit-identical results; measured slower than the default on B200 (instruction fetch of the
+ * dispatched case bodies) and kept so that the comparison can be re-measured.  Rows must be 16-byte aligned: frame_stride a
+ * multiple of 4 words and aligned base pointers, BBCU_ERR_BAD_STRIDE otherwise. */
+int bbcu_bit_BinaryLut6_Forward_Lop3Immediate(const int *dev_x_buf, int *dev_y_buf, const int *dev_input_index, const int *dev_table,
+                                              int node_size, int frame_size, int frame_stride, bbcu_stream_t stream);
+
 /* Additive: the same operator on HOST frame buffers (what a caller does that keeps its FrameBuffers in host memory,
  * include/bb/Memory.h:524-662).  Uploads x in frame chunks, runs the kernel per chunk and downloads y, with upload, kernel and
  * download of neighbouring chunks overlapped on three internal streams; returns when y is complete.  frame_stride is the HOST row

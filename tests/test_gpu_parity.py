@@ -335,6 +335,25 @@ def test_binary_lut6_oracle_bit_exact(ops, I, O, F, stride):
     assert (unpack_bits(host_bits(y, F), F) == unpack_bits(want, F)).all()
 
 
+@pytest.mark.parametrize("I,O,F", [(16, 16, 32), (40, 33, 300), (1000, 3000, 5000), (64, 9000, 16384 + 96), (6, 1, 1)])
+def test_binary_lut6_lop3_immediate_kernel_bit_exact(ops, I, O, F):
+    """The truth-table-immediate evaluation (one indexed branch per table byte) against the oracle: ragged last item, ragged last
+    word, node counts that do not fill the last group, every table byte value."""
+    from gpu_util import dev_bits, dev, host_bits, wiring
+    rng = np.random.default_rng(I + O + F + 1)
+    idx = wiring(rng, I, O)
+    table = rng.integers(-2**31, 2**31, (O, 2)).astype(np.int32)
+    if O >= 256:        # every byte value 0..255 in every byte position
+        t64 = np.zeros(256, np.uint64)
+        for pos in range(8):
+            t64 ^= (np.arange(256, dtype=np.uint64) ^ np.uint64(37 * pos)) % np.uint64(256) << np.uint64(8 * pos)
+        table[:256] = np.stack([(t64 & np.uint64(0xFFFFFFFF)), (t64 >> np.uint64(32))], axis=1).astype(np.uint32).view(np.int32)
+    xb = pack_bits(rng.random((I, F)) > 0.5)
+    want = port.binary_lut6_forward(xb, idx, table, F)
+    y = ops.binary_lut6_forward(dev_bits(xb, F), dev(idx), dev(table), F, lop3_immediate=True)
+    assert (unpack_bits(host_bits(y, F), F) == unpack_bits(want, F)).all()
+
+
 def test_binary_lut6_host_buffers_bit_exact(ops):
     """The host-buffer entry point (chunked upload / kernel / download) against the oracle; ragged last chunk and last word."""
     from gpu_util import wiring
@@ -547,7 +566,8 @@ def test_fp32_binary_layer_equals_bit_layer(ops, I, O, F):
 
 def test_single_rank_binary_layer_uses_the_unsplit_operators(ops):
     """On one rank a binary-mode layer of binarybrain_b200.dist runs the unsplit operators (per-pattern table route); its results equal
-    the split halves (tree kernels) that the sharded path uses: outputs except next to the threshold, gradients to 1e-4."""
+    the split halves that the sharded path uses (the same route, cut at the two exchange points): outputs except next to the
+    threshold, gradients to 1e-4."""
     from binarybrain_b200.dist import ShardedDifferentiableLut6
     from gpu_util import dev, wiring
     rng = np.random.default_rng(41)
@@ -575,3 +595,45 @@ def test_single_rank_binary_layer_uses_the_unsplit_operators(ops):
     amp = max(1.0, 0.3 * float(rstd.max()))
     assert float((dx - dx_h).abs().max()) <= 1e-4 * amp * max(1.0, float(dx_h.abs().max()))
     assert float((dW - dW_h).abs().max()) <= 1e-4 * amp * max(1.0, float(dW_h.abs().max()))
+
+
+@pytest.mark.parametrize("binary", [True, False])
+def test_two_frame_shards_equal_the_whole_batch(ops, binary):
+    """The split operators on two frame shards, with the host adding the [O, 2] sums in between (what the all-reduce does), against the
+    unsplit operators on the whole batch: binary mode takes the per-pattern table route in both halves, probability mode the tree
+    kernels.  Also: an apply half that does not follow its own statistics half (other pointers) recomputes instead of reusing."""
+    from gpu_util import dev, wiring
+    rng = np.random.default_rng(43)
+    I, O, F, H = 200, 300, 1024, 512
+    idx, W = dev(wiring(rng, I, O)), dev(np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32))
+    x, dy = dev(rng.random((I, F), dtype=np.float32)), dev(rng.random((O, F), dtype=np.float32))
+    rm, rv = torch.zeros(O, device="cuda"), torch.ones(O, device="cuda")
+    y_w, mean_w, rstd_w = ops.differentiable_lut6_forward_training(x, idx, W, rm.clone(), rv.clone(), F, binary=binary)
+    dW_w = torch.zeros((O, 64), device="cuda")
+    dx_w = ops.differentiable_lut6_backward(x, dy, idx, W, dW_w, mean_w, rstd_w, I, F, binary=binary)
+    xs = [x[:, :H].contiguous(), x[:, H:].contiguous()]
+    dys = [dy[:, :H].contiguous(), dy[:, H:].contiguous()]
+    ys = [torch.empty((O, H), device="cuda") for _ in range(2)]
+    sums = [torch.zeros((O, 2), dtype=torch.float64, device="cuda") for _ in range(2)]
+    for k in range(2):
+        ops.dl6_forward_stats(xs[k], idx, W, H, ys[k], sums[k], binary=binary)
+    total = sums[0] + sums[1]
+    mean, rstd = torch.empty(O, device="cuda"), torch.empty(O, device="cuda")
+    for k in range(2):
+        ops.dl6_forward_normalize(ys[k], total.clone(), mean, rstd, rm.clone(), rv.clone(), H, F, binary=binary)
+    assert torch.allclose(mean, mean_w, atol=1e-6) and torch.allclose(rstd, rstd_w, rtol=1e-4)
+    assert float((torch.cat(ys, dim=1) != y_w).float().mean()) < (1e-3 if binary else 1.0)
+    if not binary:
+        assert float((torch.cat(ys, dim=1) - y_w).abs().max()) <= 1e-4 * max(1.0, 0.3 * float(rstd_w.max()))
+    # backward: statistics of both shards first (as two ranks would), then the applies -- the second shard's statistics are the last
+    # thing left in the stream's scratch, so shard 0's apply must notice that and recompute, shard 1's may reuse
+    for k in range(2):
+        ops.dl6_backward_stats(xs[k], dys[k], idx, W, mean_w, rstd_w, H, sums[k], binary=binary)
+    total = sums[0] + sums[1]
+    dW = torch.zeros((O, 64), device="cuda")
+    dxs = [torch.empty((I, H), device="cuda") for _ in range(2)]
+    for k in range(2):
+        ops.dl6_backward_apply(xs[k], dys[k], dxs[k], idx, W, dW, mean_w, rstd_w, total.clone(), I, H, F, binary=binary)
+    amp = max(1.0, 0.3 * float(rstd_w.max()))
+    assert float((torch.cat(dxs, dim=1) - dx_w).abs().max()) <= 1e-4 * amp * max(1.0, float(dx_w.abs().max()))
+    assert float((dW - dW_w).abs().max()) <= 1e-4 * amp * max(1.0, float(dW_w.abs().max()))
