@@ -641,7 +641,7 @@ def main():
     dist = None
     if world > 1:
         if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"          # keep NCCL's version banner off stdout: stdout carries exactly one JSON line
+            os.environ.pop("NCCL_DEBUG", None)         # NCCL prints its version banner on stdout at VERSION and above: stdout carries one JSON line
         import torch.distributed as dist
         import datetime
         # a collective that is not matched on every rank fails after three minutes instead of holding the GPUs for NCCL's default ten
@@ -690,8 +690,11 @@ def main():
                          "hbm_peak_source": f"of {which}",
                          "traffic": None if NCU_BWD_TRAFFIC_BYTES_PER_NF is None else NCU_BWD_TRAFFIC_BYTES_PER_NF * k_nf}}
 
+    dbg = (lambda m: print(f"[bench rank {rank}] {m}", file=sys.stderr, flush=True)) if os.environ.get("BENCH_DEBUG") else (lambda m: None)
+    dbg("headline done")
     if not args.no_extras:
         line["e2e"] = train_e2e(torch, dist, wl, max(2, min(args.steps, 5)))
+    dbg("e2e done")
     del wl
     torch.cuda.empty_cache()
     if args.only == "train" or args.no_extras:
@@ -705,6 +708,7 @@ def main():
     k = max(2, min(args.steps, 5))
     line["binary_lut6"] = binary_lut6_section(torch, ops, dist, world, rank, max(3, min(args.steps, 10)), 3, args.bl6_frames, True)
     torch.cuda.empty_cache()
+    dbg("binary_lut6 done")
     # the same six layers in the reference's binary mode (inputs 0.5 +- bias by x > 0.5, outputs binarised), 4096 frames per GPU
     wb = TrainingWorkload(torch, ops, world, rank, 4096, 4096 * world, binary=True)
     sec_b = timed_steps(torch, dist, wb.step, k, 2)
@@ -712,6 +716,7 @@ def main():
                             "node_frames_per_s": TRAIN_LAYERS * TRAIN_NODES * 4096 * world / sec_b, "ms_per_step": sec_b * 1e3, "steps": k, "n_gpus": world}
     del wb
     torch.cuda.empty_cache()
+    dbg("train_binary done")
     if rank == 0:
         line["fp32"] = fp32_section(torch, ops, max(3, min(args.steps, 10)))
         torch.cuda.empty_cache()
@@ -721,6 +726,7 @@ def main():
         if world == 1:
             line["cpu_baseline"], _ = cpu_train_reference(2, 1)
             line["fp32"]["cpu_baseline"] = fp32_cpu_reference()
+    dbg("sections done")
     if dist:
         dist.barrier()
         dist.destroy_process_group()

@@ -9,6 +9,7 @@
 #include <algorithm>
 #include <cmath>
 #include <deque>
+#include <functional>
 #include <random>
 #include <string>
 
@@ -313,6 +314,20 @@ class DifferentiableLutN : public SparseLutBase<N>
     Tensor m_mean, m_rstd, m_running_mean, m_running_var;
 
 public:
+    // Adds, over all ranks, `count` doubles / floats that live in DEVICE memory, in place and in order on `stream` (with NCCL:
+    // ncclAllReduce(p, p, count, ncclDouble / ncclFloat, ncclSum, comm, stream)).  Injected so that this header needs no
+    // communication library.
+    using AllReduceF64 = std::function<void(double *dev, std::size_t count, cudaStream_t stream)>;
+    using AllReduceF32 = std::function<void(float *dev, std::size_t count, cudaStream_t stream)>;
+
+private:
+    index_t        m_total_frames = 0;          // > 0: this object holds one frame shard of a batch of that many frames
+    AllReduceF64   m_allreduce_sums;
+    AllReduceF32   m_allreduce_grads;
+    Tensor_<double> m_sums;                     // [O][2] batch sums on their way through the exchange
+    FrameBuffer    m_y_saved;                   // the training output, kept for the backward statistics (probability mode)
+
+public:
     struct create_t {
         indices_t     output_shape;
         bool          batch_norm = true;
@@ -348,6 +363,22 @@ public:
         c.momentum = (float)momentum; c.gamma = (float)gamma; c.beta = (float)beta; c.seed = seed;
         return Create(c);
     }
+
+    // Frame sharding (no counterpart in the reference, which has no multi-device path: include/bb/Memory.h:215-216).  After this
+    // call Forward(train) / Backward treat their buffers as ONE SHARD of a batch of total_frames frames that is spread over the
+    // ranks of a job: the batch-norm statistics of both passes are formed from per-rank sums that `allreduce_sums` adds over
+    // the ranks ([output nodes][2] fp64, twice per step, on the critical path), and, when `allreduce_grads` is given, the
+    // table gradients are added over the ranks at the end of Backward.  fp32 frames with batch norm only.  total_frames = 0
+    // switches sharding off again.
+    void SetFrameShard(index_t total_frames, AllReduceF64 allreduce_sums, AllReduceF32 allreduce_grads = nullptr)
+    {
+        BB_ASSERT(!kBit && m_batch_norm);
+        BB_ASSERT(total_frames == 0 || static_cast<bool>(allreduce_sums));
+        m_total_frames = total_frames;
+        m_allreduce_sums = allreduce_sums;
+        m_allreduce_grads = allreduce_grads;
+    }
+    index_t GetTotalFrames() const { return m_total_frames; }
 
     std::string GetModelName() const override { return "DifferentiableLut" + std::to_string(N); }
     std::string GetObjectName() const override { return GetModelName() + "_" + DataType<BinType>::Name() + "_" + DataType<RealType>::Name(); }
@@ -473,6 +504,18 @@ public:
                 else BBCU_CHECK(bbcu_bit_fp32_DifferentiableLut6_ForwardInference(
                         (int const *)x_buf.LockDeviceMemoryConst(), (int *)y_buf.LockDeviceMemory(true), idx, this->m_W->DevConst(),
                         m_running_mean.DevConst(), m_running_var.DevConst(), m_gamma, m_beta, this->m_unbinarize_bias, O, F, ys, this->m_lut_binarize, st));
+            } else if (train && m_total_frames > 0) {
+                // one shard of a larger batch: raw values and per-rank sums, the exchange, then the normalisation with the batch statistics
+                BB_ASSERT(xs == ys && m_total_frames >= F);
+                m_sums.Resize({(index_t)O, 2});
+                BBCU_CHECK(bbcu_fp32_DifferentiableLut6_ForwardStats(
+                        (float const *)x_buf.LockDeviceMemoryConst(), (float *)y_buf.LockDeviceMemory(true), idx, this->m_W->DevConst(), m_sums.Dev(true),
+                        this->m_unbinarize_bias, O, F, ys, this->m_lut_binarize, this->m_binary_mode, st));
+                m_allreduce_sums(m_sums.Dev(), (std::size_t)O * 2, st);
+                BBCU_CHECK(bbcu_fp32_DifferentiableLut6_ForwardNormalize(
+                        (float *)y_buf.LockDeviceMemory(), m_sums.DevConst(), m_mean.Dev(true), m_rstd.Dev(true), m_running_mean.Dev(), m_running_var.Dev(),
+                        m_gamma, m_beta, m_momentum, O, F, ys, (long long)m_total_frames, this->m_binary_mode, st));
+                if (!this->m_binary_mode) m_y_saved = y_buf;
             } else {
                 BB_ASSERT(xs == ys);
                 if (train) BBCU_CHECK(bbcu_fp32_DifferentiableLut6_ForwardTraining(
@@ -507,7 +550,27 @@ public:
         int I = (int)dx_buf.GetNodeSize(), O = (int)dy_buf.GetNodeSize(), F = (int)dy_buf.GetFrameSize();
         int fs = (int)(dy_buf.GetFrameStride() / 4), xs = (int)(x_buf.GetFrameStride() / 4);
         auto idx = this->m_connection_table.LockDeviceMemConst_InputTable();
-        if (m_batch_norm) {
+        if (m_batch_norm && !kBit && m_total_frames > 0) {
+            Tensor dmean(indices_t{O}), dvar(indices_t{O});
+            m_sums.Resize({(index_t)O, 2});
+            float const *xp = (float const *)x_buf.LockDeviceMemoryConst(), *dyp = (float const *)dy_buf.LockDeviceMemoryConst();
+            if (!this->m_binary_mode && !m_y_saved.Empty() && m_y_saved.GetFrameSize() == dy_buf.GetFrameSize()) {
+                // probability mode: the sums come from the saved output (8 bytes per node-frame) instead of a second LUT evaluation
+                BBCU_CHECK(bbcu_fp32_DifferentiableLut6_BackwardStatsFromOutput((float const *)m_y_saved.LockDeviceMemoryConst(), dyp, m_rstd.DevConst(),
+                                                                                m_sums.Dev(true), m_gamma, m_beta, O, F, fs, 0, st));
+            } else {
+                BBCU_CHECK(bbcu_fp32_DifferentiableLut6_BackwardStats(xp, dyp, idx, this->m_W->DevConst(), m_mean.DevConst(), m_rstd.DevConst(),
+                                                                      m_sums.Dev(true), m_gamma, m_beta, this->m_unbinarize_bias, O, F, fs,
+                                                                      this->m_lut_binarize, this->m_binary_mode, st));
+            }
+            m_y_saved = FrameBuffer();
+            m_allreduce_sums(m_sums.Dev(), (std::size_t)O * 2, st);
+            BBCU_CHECK(bbcu_fp32_DifferentiableLut6_BackwardApply(xp, dyp, (float *)dx_buf.LockDeviceMemory(true), idx, this->m_W->DevConst(),
+                                                                  this->m_dW->Dev(), m_mean.DevConst(), m_rstd.DevConst(), m_sums.DevConst(),
+                                                                  dmean.Dev(true), dvar.Dev(true), m_gamma, m_beta, this->m_unbinarize_bias, I, O, F, fs,
+                                                                  (long long)m_total_frames, this->m_lut_binarize, this->m_binary_mode, st));
+            if (m_allreduce_grads) m_allreduce_grads(this->m_dW->Dev(), (std::size_t)this->m_dW->GetSize(), st);
+        } else if (m_batch_norm) {
             Tensor dmean(indices_t{O}), dvar(indices_t{O});
             if (kBit) BBCU_CHECK(bbcu_bit_fp32_DifferentiableLut6_Backward(
                     (int const *)x_buf.LockDeviceMemoryConst(), (float const *)dy_buf.LockDeviceMemoryConst(), (float *)dx_buf.LockDeviceMemory(true), nullptr,

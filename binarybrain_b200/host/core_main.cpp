@@ -3,6 +3,7 @@
 // the C++ host classes of host/bb/*.h over the bbcu_* C ABI.
 #include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
+#include <pybind11/functional.h>
 #include <pybind11/stl.h>
 
 #include "bb/LutModels.h"
@@ -149,6 +150,17 @@ PYBIND11_MODULE(core, m)
                      py::arg("connection") = "", py::arg("momentum") = 0.0, py::arg("gamma") = 0.3, py::arg("beta") = 0.5, py::arg("seed") = 1)
          .def("get_mean", [](DifferentiableLut6_fp32_fp32 &l) -> Tensor & { return l.running_mean(); }, py::return_value_policy::reference_internal)
          .def("get_var", [](DifferentiableLut6_fp32_fp32 &l) -> Tensor & { return l.running_var(); }, py::return_value_policy::reference_internal)
+         .def("set_frame_shard", [](DifferentiableLut6_fp32_fp32 &l, index_t total_frames, py::object allreduce_sums, py::object allreduce_grads) {
+             // the callbacks receive (device pointer, element count, stream) as integers, e.g. to wrap the memory for torch.distributed
+             DifferentiableLut6_fp32_fp32::AllReduceF64 f64;
+             DifferentiableLut6_fp32_fp32::AllReduceF32 f32;
+             if (!allreduce_sums.is_none())
+                 f64 = [allreduce_sums](double *p, std::size_t n, cudaStream_t s) { allreduce_sums((std::uintptr_t)p, n, (std::uintptr_t)s); };
+             if (!allreduce_grads.is_none())
+                 f32 = [allreduce_grads](float *p, std::size_t n, cudaStream_t s) { allreduce_grads((std::uintptr_t)p, n, (std::uintptr_t)s); };
+             l.SetFrameShard(total_frames, f64, f32);
+         }, py::arg("total_frames"), py::arg("allreduce_sums"), py::arg("allreduce_grads") = py::none())
+         .def("get_total_frames", &DifferentiableLut6_fp32_fp32::GetTotalFrames)
          .def("get_gamma", &DifferentiableLut6_fp32_fp32::GetGamma)
          .def("get_beta", &DifferentiableLut6_fp32_fp32::GetBeta)
          .def("forward_node", &DifferentiableLut6_fp32_fp32::ForwardNode, py::arg("node"), py::arg("input_value"));

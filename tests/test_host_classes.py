@@ -354,6 +354,82 @@ def test_convolution2d_and_maxpooling_classes_against_oracle(core):
     assert np.array_equal(yb.reshape(B, -1).T > 0.5, want.astype(bool))
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("binary", [False, True])
+def test_cpp_layer_frame_shards_equal_the_whole_batch(core, binary):
+    """bb::DifferentiableLutN::SetFrameShard: two layer objects, each holding one half of the frames, with the exchange callback
+    played by the host (it copies the per-shard sums out, adds them, and hands the totals back -- what an all-reduce does), against
+    one object that sees the whole batch."""
+    import torch
+    from binarybrain_b200 import abi
+
+    def dev_copy(dst, src, doubles):            # device -> device through the library's own block copy (2 words per double), default stream
+        abi.call("bbcu_int32_FrameBufferCopy", dst, src, 1, 0, 0, 2 * doubles, 0, 0, 2 * doubles, 2 * doubles, None)
+
+    def d2h(ptr, count):
+        t = torch.empty(count, dtype=torch.float64, device="cuda")
+        dev_copy(t.data_ptr(), ptr, count)
+        return t.cpu().numpy()
+
+    def h2d(ptr, a):
+        t = torch.from_numpy(np.ascontiguousarray(a, np.float64)).cuda()
+        dev_copy(ptr, t.data_ptr(), t.numel())
+        torch.cuda.synchronize()
+
+    rng = np.random.default_rng(8)
+    I, O, F, H = 48, 40, 512, 256
+    W = np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32)
+    x = rng.random((F, I), dtype=np.float32)
+    dy = rng.random((F, O), dtype=np.float32)
+
+    def make():
+        layer = core.DifferentiableLut6_fp32_fp32.create([O], momentum=0.9)
+        layer.send_command("binary " + ("true" if binary else "false"))
+        layer.set_input_shape([I])
+        layer.W().set_numpy(W)
+        return layer
+
+    whole = make()
+    idx = whole.get_connection()
+    y_w = whole.forward(core.FrameBuffer.from_numpy_fp32(x), True).numpy_fp32()
+    dx_w = whole.backward(core.FrameBuffer.from_numpy_fp32(dy)).numpy_fp32()
+    dW_w = whole.dW().numpy()
+    shards = [make(), make()]
+    for s_ in shards:
+        s_.set_connection(idx)
+    xs, dys = [x[:H], x[H:]], [dy[:H], dy[H:]]
+    rec = {}
+    for phase in ("record", "apply"):                      # forward: first collect every shard's sums, then run with their total
+        ys = []
+        for k, layer in enumerate(shards):
+            if phase == "record":
+                layer.set_frame_shard(F, lambda p, n, st, k=k: rec.__setitem__(k, d2h(p, n)))
+            else:
+                layer.set_frame_shard(F, lambda p, n, st: h2d(p, rec[0] + rec[1]))
+            ys.append(layer.forward(core.FrameBuffer.from_numpy_fp32(xs[k]), True).numpy_fp32())
+    y = np.concatenate(ys, axis=0)
+    assert np.isfinite(shards[0].get_mean().numpy()).all()
+    if binary:
+        assert (y != y_w).mean() < 1e-3
+    else:
+        assert np.abs(y - y_w).max() <= 1e-4
+    grads = {}
+    for phase in ("record", "apply"):                      # backward, the same way (each forward above saved one copy of the input)
+        dxs = []
+        for k, layer in enumerate(shards):
+            layer.dW().fill_zero()
+            if phase == "record":
+                layer.set_frame_shard(F, lambda p, n, st, k=k: rec.__setitem__(k, d2h(p, n)))
+            else:
+                layer.set_frame_shard(F, lambda p, n, st: h2d(p, rec[0] + rec[1]))
+            dxs.append(layer.backward(core.FrameBuffer.from_numpy_fp32(dys[k])).numpy_fp32())
+            grads[k] = layer.dW().numpy().copy()
+    dx = np.concatenate(dxs, axis=0)
+    assert np.abs(dx - dx_w).max() <= 1e-4 * max(1.0, float(np.abs(dx_w).max()))
+    assert np.abs(grads[0] + grads[1] - dW_w).max() <= 1e-4 * max(1.0, float(np.abs(dW_w).max()))
+    assert shards[0].get_total_frames() == F
+
+
 # ------------------------------------------------------------------------------------------------ serialisation (CPU)
 def _ser_state():
     from oracle import det_wiring, det_uniform
