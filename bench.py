@@ -50,8 +50,9 @@ FLOPS_FWD, FLOPS_BWD = 126.0, 505.0
 FLOPS_FWD_EXECUTED, FLOPS_BWD_EXECUTED = 126.0 + 12.0, 379.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one k_binary_lut6_pipe launch: ncu on a 131072-frame launch; traffic grows with frames
 NCU_BL6_TRAFFIC_BYTES_PER_FRAME = (449.7e6 + 244.6e6) / 131072
-# the same for one k_lut6_backward_pipe<BN> launch on a 65536 -> 65536 x 4096-frame layer (bytes per node-frame), or None until captured
-NCU_BWD_TRAFFIC_BYTES_PER_NF = None
+# the same for one k_lut6_backward_pipe<BN> launch on a 65536 -> 65536 x 4096-frame layer: 11.379 GB read + 5.201 GB written for 2.68e8
+# node-frames; the tile width does not depend on the frame count, so the traffic grows in proportion to the frames of a launch
+NCU_BWD_TRAFFIC_BYTES_PER_NF = (11.379342e9 + 5.201327e9) / (65536 * 4096)
 
 
 def measured_peaks():
@@ -464,47 +465,59 @@ def fp32_section(torch, ops, steps, nodes=TRAIN_NODES, frames=4096):
     return out
 
 
-def build_lut_cnn(dev, seed=5, ops=None):
-    """The LUT-CNN from the host-side classes: two conv blocks (each two Convolution2d of per-pixel DifferentiableLut6 layers with 3x3
-    'same' lowering, then 2x2 MaxPooling) and a dense head 4096 -> 1024 -> 420 -> 70 -> 10.  Random 6-distinct wiring, tables
-    N(0.5, 0.01), fp32, batch norm on."""
-    import torch
-    from binarybrain_b200.conv import Convolution2d, MaxPooling, Sequential
-    from binarybrain_b200.dist import ShardedDifferentiableLut6
-    g = torch.Generator(device=dev).manual_seed(seed)
+def build_lut_cnn(core):
+    """The LUT-CNN from the C++ host classes (binarybrain_b200.core): two conv blocks (each two bb::Convolution2d of per-pixel
+    DifferentiableLut6 layers with 3x3 'same' lowering, then 2x2 bb::MaxPooling) and a dense head 4096 -> 1024 -> 420 -> 70 -> 10.  Seeded
+    random 6-distinct wiring and N(0.5, 0.01) tables as the classes draw them, fp32, batch norm on, probability mode."""
+    luts = []
 
-    def lut(n_in, n_out):
-        idx = torch.rand((n_out, n_in), device=dev, generator=g).argsort(dim=1)[:, :6].to(torch.int32).contiguous()
-        W = (torch.randn((n_out, 64), device=dev, generator=g) * 0.01 + 0.5).clamp_(0, 1)
-        return ShardedDifferentiableLut6(idx, W, n_in, ops=ops, binary=False, sharded=False)       # runs on one rank only: no collectives
+    def lut(n):
+        layer = core.DifferentiableLut6_fp32_fp32.create([n], seed=1 + len(luts))
+        layer.send_command("binary false")
+        luts.append(layer)
+        return layer
 
-    def conv(c, hw, widths):
-        return Convolution2d([lut(a, b) for a, b in zip(widths[:-1], widths[1:])], c, hw, hw, 3, 3, padding="same", ops=ops)
+    def conv(widths):
+        seq = core.Sequential.create()
+        for n in widths:
+            seq.add(lut(n))
+        return core.Convolution2d_fp32_fp32.create(seq, 3, 3, padding="same")
 
-    return Sequential([
-        conv(3, 32, [27, 216, 36, 32]), conv(32, 32, [288, 216, 36, 32]), MaxPooling(32, 32, 32, 2, 2, ops=ops),
-        conv(32, 16, [288, 384, 64]), conv(64, 16, [576, 384, 64]), MaxPooling(64, 16, 16, 2, 2, ops=ops),
-        lut(4096, 1024), lut(1024, 420), lut(420, 70), lut(70, 10)])
+    net = core.Sequential.create()
+    net.add(conv([216, 36, 32]))
+    net.add(conv([216, 36, 32]))
+    net.add(core.MaxPooling_fp32_fp32.create(2, 2))
+    net.add(conv([384, 64]))
+    net.add(conv([384, 64]))
+    net.add(core.MaxPooling_fp32_fp32.create(2, 2))
+    for n in (1024, 420, 70, 10):
+        net.add(lut(n))
+    net.set_input_shape([3, 32, 32])
+    return net, luts
 
 
-def cnn_section(torch, ops, steps):
-    """LUT-CNN forward + backward on 256 synthetic 3x32x32 images (one GPU).  Node-frames count the LUT evaluations of one forward
+def cnn_section(torch, steps):
+    """LUT-CNN forward + backward on 256 synthetic 3x32x32 images (one GPU), driven through the C++ host classes (bb::Sequential,
+    bb::Convolution2d, bb::MaxPooling, bb::DifferentiableLutN over the C ABI).  Node-frames count the LUT evaluations of one forward
     pass (per-pixel layers run on 256 * oh * ow frames)."""
+    import numpy as np
+    import binarybrain_b200.core as core
     B = 256
-    net = build_lut_cnn(torch.device("cuda"))
-    x = torch.rand((3 * 32 * 32, B), device="cuda")
-    dy = torch.rand((10, ops.fp32_stride(B)), device="cuda")
+    net, _ = build_lut_cnn(core)
+    rng = np.random.default_rng(5)
+    x = core.FrameBuffer.from_numpy_fp32(rng.random((B, 3, 32, 32), dtype=np.float32))
+    dy = core.FrameBuffer.from_numpy_fp32(rng.random((B, 10), dtype=np.float32))
+    x.lock_device()
+    dy.lock_device()                                 # both stay current on the device: the steps below move nothing over PCIe
 
     def step():
-        for l in net.lut_layers():
-            ops.clamp_(l.W)
-        net.forward(x, B)
+        net.forward(x, True)
         net.backward(dy)
 
     sec = time_op(torch, step, steps)
     nf = B * (1024 * (216 + 36 + 32) * 2 + 256 * (384 + 64) * 2 + (1024 + 420 + 70 + 10))
     return {"workload": "LUT-CNN: 3x32x32 images, batch 256, 2 conv blocks of per-pixel DifferentiableLut6 trees with 3x3 Im2Col / "
-                        "Col2Im and 2x2 MaxPooling, dense head 4096->1024->420->70->10, fp32, batch norm; forward + backward",
+                        "Col2Im and 2x2 MaxPooling, dense head 4096->1024->420->70->10, fp32, batch norm; forward + backward through the C++ host classes",
             "node_frames_per_s": nf / sec, "ms_per_step": sec * 1e3, "steps": steps, "n_gpus": 1}
 
 
@@ -720,7 +733,7 @@ def main():
     if rank == 0:
         line["fp32"] = fp32_section(torch, ops, max(3, min(args.steps, 10)))
         torch.cuda.empty_cache()
-        line["cnn"] = cnn_section(torch, ops, k)
+        line["cnn"] = cnn_section(torch, k)
         torch.cuda.empty_cache()
         line["operators"] = operators_section(torch, ops, max(3, min(args.steps, 10)))
         if world == 1:
