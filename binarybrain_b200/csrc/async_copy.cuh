@@ -45,12 +45,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
     return ok != 0;
 }
 
-// Bounded wait: false when the phase did not complete within kWaitSpins attempts.
+// Bounded wait, called by all 32 lanes of a warp together: false when the phase did not complete within kWaitSpins attempts.
+// The outcome is made warp-uniform (a lane that saw the phase complete on its last attempt does not carry on alone while its
+// neighbours give up).
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity)
 {
-    for (int i = 0; i < kWaitSpins; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
+    bool ok = false;
+    for (int i = 0; i < kWaitSpins && !ok; ++i) ok = mbar_try_wait(bar, parity);
+    return __all_sync(0xffffffffu, ok);
 }
 
 // orders this thread's earlier generic-proxy accesses of shared memory before later async-proxy (bulk copy) accesses

@@ -786,8 +786,6 @@ int backward_pass_one(bool x_is_fp32, BitBwdArgs &a, Scratch &s, float *&hdy, co
 {
     const size_t pat_bytes = x_is_fp32 ? (size_t)O * (size_t)fs : 0;
     if (pat_bytes > ((size_t)1 << 30)) return BBCU_ERR_NO_MEMORY;
-    PassOneRecord want;
-    want.x = x; want.dy = dy; want.W = W; want.O = O; want.F = F; want.fs = fs;
     bool have = false;
     if (reuse) {
         std::lock_guard<std::mutex> g(g_record_mu);

@@ -67,16 +67,16 @@ def stochastic_lut6_forward(x, idx, W, frames, y=None, binary=False, lut_binariz
     return y
 
 
-def stochastic_lut6_backward(x, dy, idx, W, dW, n_in, frames, dx=None, binary=False, lut_binarize=False, bias=BIAS):
-    """dx is overwritten, dW accumulated into."""
+def stochastic_lut6_backward(x, dy, idx, W, dW, n_in, frames, dx=None, binary=False, lut_binarize=False, bias=BIAS, dx_tmp=None):
+    """dx is overwritten, dW accumulated into.  dx_tmp: optional fp32 scratch [6 * nodes, tmp_stride] as the reference's callers pass it."""
     O = idx.shape[0]
     _chk(dy, torch.float32, "dy"); _chk(dW, torch.float32, "dW")
     if dx is None:
         dx = torch.empty((n_in, dy.shape[1]), dtype=torch.float32, device=dy.device)
     if x.dtype == torch.float32:
         assert x.shape[1] == dy.shape[1], "x, dy and dx share one frame stride"
-        abi.call("bbcu_fp32_StochasticLut6_Backward", _p(x), _p(dy), _p(dx), 0, _p(idx), 0, _p(W), _p(dW), 0, n_in, O, frames, dy.shape[1],
-                 0, 0, int(binary), int(lut_binarize), bias, _stream())
+        abi.call("bbcu_fp32_StochasticLut6_Backward", _p(x), _p(dy), _p(dx), _p(dx_tmp), _p(idx), 0, _p(W), _p(dW), 0, n_in, O, frames, dy.shape[1],
+                 0 if dx_tmp is None else dx_tmp.shape[1], 0 if dx_tmp is None else dx_tmp.shape[1], int(binary), int(lut_binarize), bias, _stream())
     else:
         _chk(x, torch.int32, "x")
         abi.call("bbcu_bit_fp32_StochasticLut6_Backward", _p(x), _p(dy), _p(dx), 0, _p(idx), 0, _p(W), _p(dW), 0, n_in, O, frames,
@@ -123,7 +123,7 @@ def differentiable_lut6_forward_inference(x, idx, W, running_mean, running_var, 
 
 
 def differentiable_lut6_backward(x, dy, idx, W, dW, mean, rstd, n_in, frames, dx=None, gamma=0.3, beta=0.5, bias=BIAS, lut_binarize=False,
-                                 binary=True):
+                                 binary=True, dx_tmp=None):
     O = idx.shape[0]
     dev = dy.device
     if dx is None:
@@ -132,8 +132,9 @@ def differentiable_lut6_backward(x, dy, idx, W, dW, mean, rstd, n_in, frames, dx
     dvar = torch.empty(O, dtype=torch.float32, device=dev)
     if x.dtype == torch.float32:
         assert x.shape[1] == dy.shape[1]
-        abi.call("bbcu_fp32_DifferentiableLut6_Backward", _p(x), _p(dy), _p(dx), 0, _p(idx), 0, _p(W), _p(dW), _p(mean), _p(rstd), _p(dmean),
-                 _p(dvar), gamma, beta, bias, 0, n_in, O, frames, dy.shape[1], 0, 0, int(lut_binarize), int(binary), _stream())
+        abi.call("bbcu_fp32_DifferentiableLut6_Backward", _p(x), _p(dy), _p(dx), _p(dx_tmp), _p(idx), 0, _p(W), _p(dW), _p(mean), _p(rstd), _p(dmean),
+                 _p(dvar), gamma, beta, bias, 0, n_in, O, frames, dy.shape[1], 0 if dx_tmp is None else dx_tmp.shape[1],
+                 0 if dx_tmp is None else dx_tmp.shape[1], int(lut_binarize), int(binary), _stream())
     else:
         abi.call("bbcu_bit_fp32_DifferentiableLut6_Backward", _p(x), _p(dy), _p(dx), 0, _p(idx), 0, _p(W), _p(dW), _p(mean), _p(rstd),
                  _p(dmean), _p(dvar), gamma, beta, bias, 0, n_in, O, frames, dy.shape[1], x.shape[1], 0, 0, int(lut_binarize), _stream())

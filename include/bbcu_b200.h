@@ -15,21 +15,26 @@
  *   - input_index is [output_node][6] int32, W is [output_node][64] fp32, bit k of the table index
  *     is input k;
  *   - the last argument is the CUDA stream (a cudaStream_t passed as void*, NULL = default
- *     stream).  All work is enqueued on that stream and nothing synchronises the host;
+ *     stream).  All work is enqueued on that stream.  The host is not synchronised, with one exception: a call that has
+ *     to grow its per-stream scratch (below) allocates, and waits for the stream before it returns the outgrown block; such
+ *     a call -- the first one on a stream, or the first one of a larger layer -- belongs outside of stream capture;
  *   - return value: 0 on success, BBCU_ERR_* (< 0) for a rejected argument, a cudaError_t (> 0)
- *     if the CUDA runtime reported one.  Nothing exits the process (the reference's macros call
+ *     if the CUDA runtime reported one (reported once, then cleared).  Nothing exits the process (the reference's macros call
  *     exit(1), include/bbcu/bbcu_util.h:17-36);
- *   - scratch: the LUT operators keep per-stream work areas in the device heap below: per-node sums, coefficient and pattern
- *     tables (at most ~1 KiB per output node) and, for DifferentiableLut6 in binary mode on fp32 frames, one pattern byte per
- *     node-frame (node_size * frame_stride bytes; above 1 GiB the operator runs its scratch-free kernels instead).  The first
- *     call on a stream allocates them, later calls reuse them, and bbcu_LocalHeap_GarbageCollect releases them.
+ *   - scratch: the fp32 backward operators use the caller's dev_dx_tmp when it is given, 16-byte aligned and at least 512 bytes
+ *     per output node.  Otherwise, and for the operators whose reference signature carries no scratch, the LUT operators keep
+ *     per-stream work areas in the device heap below: per-node sums, coefficient and pattern tables (at most ~1 KiB per output
+ *     node) and, for DifferentiableLut6 in binary mode on fp32 frames, one pattern byte per node-frame (node_size *
+ *     frame_stride bytes; above 1 GiB the operator runs its scratch-free kernels instead).  The first call on a stream
+ *     allocates them, later calls reuse them, and bbcu_LocalHeap_GarbageCollect releases them.
  *     ..._ForwardTraining_NoAlloc is the variant that never allocates.
  *
  * Results follow the reference's CPU branches (the header-only path in include/bb), which is what
  * parity is measured against; where the reference's old CUDA kernels differ from its CPU code the
- * CPU code wins.  dev_dx_tmp and dev_reverse_index of the backward operators are
- * accepted for signature compatibility and are not read or written: dx is accumulated with
- * vector reductions in L2 instead of a [nodes*6][frames] temporary.
+ * CPU code wins.  dev_reverse_index of the backward operators is accepted for signature compatibility and
+ * not read: the input gradients of a node are added to dx with 128-bit floating-point reductions
+ * (red.global.add.v4.f32) that L2 resolves, instead of going through a [nodes*6][frames] temporary and a
+ * gather by reverse index; dev_dx_tmp serves as plain scratch (see above).
  */
 #ifndef BBCU_B200_H
 #define BBCU_B200_H

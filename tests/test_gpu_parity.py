@@ -405,6 +405,50 @@ def test_binary_lut6_full_size_properties(ops):
 
 
 # --------------------------------------------------------------------------------------------- behaviour of the ABI
+def test_backward_uses_the_callers_scratch_and_falls_back_for_unaligned_rows(ops):
+    """dev_dx_tmp, as the reference's callers hand it in, serves as the backward's scratch (the device heap does not grow); a buffer
+    that is too small is ignored; rows that are not 16-byte aligned (odd stride) take the plain-load kernels.  All against the oracle."""
+    from gpu_util import dev_fp32, dev, host_fp32, err, wiring
+    rng = np.random.default_rng(17)
+    I, O, F = 120, 200, 700
+    idx = wiring(rng, I, O)
+    W = np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32)
+    x, dy = rng.random((I, F), dtype=np.float32), rng.random((O, F), dtype=np.float32)
+    dx_w, dW_w = port.sl6_backward(x, dy, idx, W, I)
+    L = ops.abi.lib()
+    for stride, tmp_cols in ((704, 256), (704, 8), (701, 256), (703, None)):
+        xd, dyd = dev_fp32(x, stride), dev_fp32(dy, stride)
+        tmp = None if tmp_cols is None else torch.empty((6 * O, tmp_cols), device="cuda")
+        dW = torch.zeros((O, 64), device="cuda")
+        torch.cuda.synchronize()
+        before = L.bbcu_LocalHeap_GetAllocatedSize()
+        dx = ops.stochastic_lut6_backward(xd, dyd, dev(idx), dev(W), dW, I, F, dx_tmp=tmp)
+        torch.cuda.synchronize()
+        if stride % 4 == 0 and tmp_cols == 256:
+            assert L.bbcu_LocalHeap_GetAllocatedSize() == before           # the caller's buffer was enough
+        assert err(host_fp32(dx, F), dx_w) <= TOL and err(dW.cpu().numpy(), dW_w) <= TOL, (stride, tmp_cols)
+    # DifferentiableLut6 through the same two routes, and the forward on unaligned rows
+    p = port.dl6_forward_train(x, idx, W, np.zeros(O), np.ones(O), binary=False)
+    amp = max(1.0, 0.3 * float(p["rstd"].max()))
+    dyz = np.where(_edges(p["y_pre"], amp), np.float32(0), dy).astype(np.float32)
+    dx_w, dW_w = port.dl6_backward(x, dyz, idx, W, p["mean"], p["rstd"], I, binary=False)
+    for stride, tmp_cols in ((704, 256), (701, None)):
+        xd = dev_fp32(x, stride)
+        y, mean, rstd = ops.differentiable_lut6_forward_training(xd, dev(idx), dev(W), torch.zeros(O, device="cuda"), torch.ones(O, device="cuda"), F,
+                                                                 binary=False)
+        assert np.abs(host_fp32(y, F) - p["y"]).max() <= BN_Y_FACTOR * TOL * amp and err(mean.cpu().numpy(), p["mean"]) <= TOL
+        tmp = None if tmp_cols is None else torch.empty((6 * O, tmp_cols), device="cuda")
+        dW = torch.zeros((O, 64), device="cuda")
+        dx = ops.differentiable_lut6_backward(xd, dev_fp32(dyz, stride), dev(idx), dev(W), dW, dev(p["mean"]), dev(p["rstd"]), I, F, binary=False,
+                                              dx_tmp=tmp)
+        scale = max(1.0, float(np.abs(dx_w).max()))
+        assert np.abs(host_fp32(dx, F) - dx_w).max() <= BN_GRAD_FACTOR * TOL * scale * amp
+        assert err(dW.cpu().numpy(), dW_w) <= BN_GRAD_FACTOR * TOL * amp
+        ys = ops.stochastic_lut6_forward(xd, dev(idx), dev(W), F)
+        assert err(host_fp32(ys, F), port.sl6_forward(x, idx, W)) <= TOL
+
+
+
 def test_determinism_and_dw_accumulation(ops):
     from gpu_util import dev_fp32, dev, wiring
     rng = np.random.default_rng(3)
