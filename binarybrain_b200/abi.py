@@ -17,6 +17,7 @@ SIGNATURES = {
     "bbcu_b200_error_string": (C.c_char_p, [_i]),
     "bbcu_b200_abi_version": (_i, []),
     "bbcu_b200_device_fault": (_i, []),
+    "bbcu_b200_selftest_wait_expiry": (_i, [_vp]),
     "bbcu_GetDeviceCount": (_i, []),
     "bbcu_GetDevice": (_i, []),
     "bbcu_SetDevice": (None, [_i]),

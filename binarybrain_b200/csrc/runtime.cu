@@ -170,6 +170,35 @@ extern "C" int bbcu_b200_device_fault(void)
     return v;
 }
 
+// Self-test of the bounded-wait path that the pipelined kernels share: one warp arms a barrier for 16 bytes that no copy will ever
+// deliver, waits with a small attempt limit, gives up as a whole warp, records the fault code and returns.  Nothing hangs and
+// nothing faults; afterwards bbcu_b200_device_fault() reports 1 once.
+namespace bb200 {
+__global__ void k_selftest_wait_expiry(int *fault, int attempts)
+{
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_init_fence();
+    }
+    __syncwarp();
+    if (threadIdx.x == 0) mbar_arrive_expect_tx(&bar, 16u);
+    __syncwarp();
+    bool ok = false;
+    for (int i = 0; i < attempts && !ok; ++i) ok = mbar_try_wait(&bar, 0u);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok && threadIdx.x == 0) atomicCAS(fault, 0, kFaultBarrierTimeout);
+}
+}   // namespace bb200
+
+extern "C" int bbcu_b200_selftest_wait_expiry(bbcu_stream_t stream)
+{
+    int *w = fault_word();
+    if (w == nullptr) return BBCU_ERR_NO_DEVICE;
+    k_selftest_wait_expiry<<<1, 32, 0, as_stream(stream)>>>(w, 2000);
+    return launch_status();
+}
+
 // ---------------------------------------------------------------------------------------------- manager
 extern "C" int bbcu_GetDeviceCount(void)
 {

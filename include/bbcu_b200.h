@@ -63,6 +63,9 @@ int bbcu_b200_abi_version(void);
  * (0 = none, 1 = a bounded wait on an asynchronous copy expired, -1 = the query itself failed).  Kernels never trap or spin
  * forever: a wait that does not complete is abandoned, recorded here, and the kernel returns. */
 int bbcu_b200_device_fault(void);
+/* Self-test of that path: one warp waits, with a small attempt limit, on a barrier that nothing completes, gives up, records fault
+ * code 1 and returns (nothing hangs, nothing faults); bbcu_b200_device_fault() then reports 1 once. */
+int bbcu_b200_selftest_wait_expiry(bbcu_stream_t stream);
 
 /* ------------------------------------------------------------------ Manager: include/bbcu/bbcu.h:49-55, cuda/Manager.cu:15-55 */
 int  bbcu_GetDeviceCount(void);

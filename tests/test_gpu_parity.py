@@ -497,6 +497,25 @@ def test_no_kernel_recorded_a_fault(ops):
     assert abi.lib().bbcu_b200_device_fault() == 0
 
 
+def test_a_wait_that_nothing_completes_gives_up_and_is_reported(ops):
+    """The bounded-wait path itself: the library's self-test arms a barrier that no copy completes; the warp gives up after its
+    attempt limit, records fault code 1 and returns.  The context stays usable and the next query is clean."""
+    from binarybrain_b200 import abi
+    from gpu_util import dev_bits, dev, host_bits, wiring
+    L = abi.lib()
+    assert L.bbcu_b200_device_fault() == 0
+    abi.call("bbcu_b200_selftest_wait_expiry", torch.cuda.current_stream().cuda_stream)
+    assert L.bbcu_b200_device_fault() == 1          # reported once ...
+    assert L.bbcu_b200_device_fault() == 0          # ... and cleared
+    rng = np.random.default_rng(6)
+    I, O, F = 64, 40, 3000
+    idx, table = wiring(rng, I, O), rng.integers(-2**31, 2**31, (O, 2)).astype(np.int32)
+    xb = pack_bits(rng.random((I, F)) > 0.5)
+    y = ops.binary_lut6_forward(dev_bits(xb, F), dev(idx), dev(table), F)
+    assert (unpack_bits(host_bits(y, F), F) == unpack_bits(port.binary_lut6_forward(xb, idx, table, F), F)).all()
+    assert L.bbcu_b200_device_fault() == 0
+
+
 def test_heap_cache_and_out_of_memory(ops):
     from binarybrain_b200 import abi
     L = abi.lib()
