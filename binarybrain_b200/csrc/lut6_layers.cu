@@ -1015,186 +1015,6 @@ static int forward_plain(const void *x, float *y, uint32_t *ybits, const int *id
     return launch_forward<XBIT, PH_PLAIN, false>(a, 2048, st);
 }
 
-// ---------------------------------------------------------------------------------------------
-// The same persistent backward with BOTH sides staged through shared memory, so that the mapping of frames to lanes in the
-// arithmetic is independent of the mapping used for global memory:
-//   * global -> shared: every lane copies 16 bytes (four consecutive frames) of each of the seven rows of a chunk with cp.async,
-//     STAGES - 1 chunks ahead;
-//   * arithmetic: lane l takes frames 32 q + l, q = 0..3, of the chunk, one conflict-free 32-bit shared load per row and frame --
-//     no frame quads are held in registers, which takes 50 registers of operand staging out of the kernel;
-//   * the six input gradients of a frame go to a staging area in shared memory (conflict-free 32-bit stores), and after the
-//     chunk's four frames every lane adds its four consecutive frames of each row to dx with one 128-bit reduction.
-// NW warps (= nodes per group) per CTA, one CTA per SM.
-// ---------------------------------------------------------------------------------------------
-template <int NW, int STAGES>
-struct BsLayout {
-    static constexpr int kStage = 7 * kBvRowBytes;
-    static constexpr int kTabs  = kBvTabSlots * kBvTabBytes;
-    static constexpr int kWarp  = STAGES * kStage + kTabs + kBvTrBytes;       // the transpose buffer doubles as the dx staging area (6 x 512 bytes)
-    static constexpr int kSmem  = NW * kWarp;
-    static_assert(kSmem <= 227 * 1024, "one CTA per SM must fit");
-    static_assert(6 * kBvRowBytes <= kBvTrBytes, "dx staging fits the transpose buffer");
-};
-
-template <bool BN, bool BINARY, int NW, int STAGES>
-__global__ void __launch_bounds__(NW * 32, 1)
-k_lut6_backward_stg(const BwdArgs a, const float4 *__restrict__ coef, float *__restrict__ dC, int n_tiles, int n_full, int n_last)
-{
-    using L = BsLayout<NW, STAGES>;
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    unsigned char *my = smem_raw + (size_t)warp * L::kWarp;
-    unsigned char *my_tabs = my + STAGES * L::kStage;
-    float *tr = reinterpret_cast<float *>(my_tabs + L::kTabs);
-
-    const int step = (int)gridDim.x;
-    const int dt = step / a.groups, dg = step - dt * a.groups;
-    auto next_item = [&](BvCursor &p) {
-        p.group += dg;
-        p.tile += dt;
-        if (p.group >= a.groups) { p.group -= a.groups; ++p.tile; }
-        p.c = 0;
-        p.n = p.tile == n_tiles - 1 ? n_last : n_full;
-        p.slot = p.slot == kBvTabSlots - 1 ? 0 : p.slot + 1;
-    };
-    auto node_of = [&](const BvCursor &p) { return min(p.group * NW + warp, a.O - 1); };      // a ragged last group repeats the last node
-    auto row_of = [&](const BvCursor &p) { return (p.tile < n_tiles && lane < 6) ? __ldg(a.idx + (size_t)node_of(p) * 6 + lane) : 0; };
-
-    BvCursor ic;
-    ic.tile = (int)blockIdx.x / a.groups;
-    ic.group = (int)blockIdx.x - ic.tile * a.groups;
-    ic.c = 0;
-    ic.n = ic.tile == n_tiles - 1 ? n_last : n_full;
-    ic.slot = 0;
-    BvCursor cc = ic;
-    int ist = 0;
-    int row_i = row_of(ic), row_in;
-    {
-        BvCursor t = ic;
-        next_item(t);
-        row_in = row_of(t);
-    }
-    const float *xf = static_cast<const float *>(a.x);
-    auto issue = [&]() {
-        if (ic.tile < n_tiles) {
-            const int f = ic.tile * a.T + ic.c * kFramesPerIter + 4 * lane;
-            const bool in_row = f < a.xs;
-            unsigned char *st = my + ist * L::kStage + lane * 16;
-#pragma unroll
-            for (int j = 0; j < 6; ++j) {
-                const int r = __shfl_sync(kFull, row_i, j);
-                cp_async16(st + j * kBvRowBytes, xf + (size_t)r * a.xs + (in_row ? f : 0), in_row);
-            }
-            const int node = node_of(ic);
-            cp_async16(st + 6 * kBvRowBytes, a.dy + (size_t)node * a.dys + (f < a.dys ? f : 0), f < a.dys);
-            if (ic.c == 0 && lane < 16) cp_async16(my_tabs + ic.slot * kBvTabBytes + lane * 16, coef + (size_t)node * 16 + lane, true);
-            if (++ic.c == ic.n) {
-                next_item(ic);
-                row_i = row_in;
-                BvCursor t = ic;
-                next_item(t);
-                row_in = row_of(t);
-            }
-        }
-        cp_async_commit();
-        ist = ist == STAGES - 1 ? 0 : ist + 1;
-    };
-#pragma unroll
-    for (int k = 0; k < STAGES - 1; ++k) issue();
-
-    int cst = 0;
-    int row_c = row_of(cc), row_cn;
-    float mean_n = 0.0f, rstd_n = 0.0f, dmean_n = 0.0f, dvar_n = 0.0f;
-    if (BN && cc.tile < n_tiles) {
-        const int n0 = node_of(cc);
-        mean_n = a.mean[n0]; rstd_n = a.rstd[n0]; dmean_n = a.dmean[n0]; dvar_n = a.dvar[n0];
-    }
-    f32x2 acc2[32];
-    while (cc.tile < n_tiles) {
-        const int node_raw = cc.group * NW + warp;
-        const bool live_node = node_raw < a.O;
-        const int node = min(node_raw, a.O - 1);
-        const float mean = mean_n, rstd = rstd_n, dmean = dmean_n, dvar = dvar_n;
-        {
-            BvCursor t = cc;
-            next_item(t);
-            row_cn = row_of(t);
-            if (BN && t.tile < n_tiles) {
-                const int n1 = node_of(t);
-                mean_n = a.mean[n1]; rstd_n = a.rstd[n1]; dmean_n = a.dmean[n1]; dvar_n = a.dvar[n1];
-            }
-        }
-        const float4 *tab = reinterpret_cast<const float4 *>(my_tabs + cc.slot * kBvTabBytes);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) acc2[i] = 0ull;
-        const int f_tile = cc.tile * a.T;
-        for (; cc.c < cc.n; ++cc.c) {
-            issue();                                 // refills the stage read STAGES - 1 chunks ago (all lanes are past the barrier below)
-            cp_async_wait<STAGES - 1>();
-            __syncwarp();                            // every lane's part of chunk k (and of this item's table) has landed
-            const float *st = reinterpret_cast<const float *>(my + cst * L::kStage) + lane;
-            cst = cst == STAGES - 1 ? 0 : cst + 1;
-            const int f0 = f_tile + cc.c * kFramesPerIter;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                float u[6];
-#pragma unroll
-                for (int j = 0; j < 6; ++j) {
-                    const float v = st[j * kFramesPerIter + 32 * q];
-                    u[j] = BINARY ? (v > 0.5f ? a.bias : -a.bias) : __saturatef(v) - 0.5f;           // the same values as condition_u()
-                }
-                KeptHalves D;
-                const float v = lut6_forward_keep_halves(tab, u, D);
-                float g = st[6 * kFramesPerIter + 32 * q];
-                if (BN) {
-                    const float tanh_x = ((v - mean) * rstd) * a.gamma + a.beta;
-                    if (tanh_x <= 0.0f || tanh_x >= 1.0f) g = 0.0f;
-                    const float dxc = (g * a.gamma) * rstd;
-                    g = dxc + dmean + (v * dvar * a.rF);
-                }
-                if (f0 + 32 * q + lane >= a.F || !live_node) g = 0.0f;
-                float dxv[6];
-                lut6_reverse_halves(tab, u, D, g, acc2, dxv);
-#pragma unroll
-                for (int j = 0; j < 6; ++j) tr[j * kFramesPerIter + 32 * q + lane] = dxv[j];
-            }
-            __syncwarp();
-            const bool write = f0 + 4 * lane < a.F && live_node;
-#pragma unroll
-            for (int j = 0; j < 6; ++j) {
-                const int r = __shfl_sync(kFull, row_c, j);
-                const float4 d = *reinterpret_cast<const float4 *>(tr + j * kFramesPerIter + 4 * lane);
-                if (write) red_add_v4(a.dx + (size_t)r * a.dxs + f0 + 4 * lane, d.x, d.y, d.z, d.w);
-            }
-        }
-        // ---- item done: sum the 64 accumulators over the lanes through the (padded) transpose
-        __syncwarp();
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-            float4 v;
-            unpack2(acc2[2 * k], v.x, v.y);
-            unpack2(acc2[2 * k + 1], v.z, v.w);
-            *reinterpret_cast<float4 *>(tr + lane * kBvTrStride + 4 * k) = v;
-        }
-        __syncwarp();
-        f32x2 s0 = 0ull, s1 = 0ull, s2 = 0ull, s3 = 0ull;
-#pragma unroll
-        for (int r = 0; r < 32; r += 4) {
-            s0 = add2(s0, *reinterpret_cast<const f32x2 *>(tr + (r + 0) * kBvTrStride + 2 * lane));
-            s1 = add2(s1, *reinterpret_cast<const f32x2 *>(tr + (r + 1) * kBvTrStride + 2 * lane));
-            s2 = add2(s2, *reinterpret_cast<const f32x2 *>(tr + (r + 2) * kBvTrStride + 2 * lane));
-            s3 = add2(s3, *reinterpret_cast<const f32x2 *>(tr + (r + 3) * kBvTrStride + 2 * lane));
-        }
-        float lo, hi;
-        unpack2(add2(add2(s0, s1), add2(s2, s3)), lo, hi);
-        if (live_node) red_add_v2(dC + (size_t)node * 64 + 2 * lane, lo, hi);
-        __syncwarp();                                // the transpose buffer is the next chunk's dx staging area
-        next_item(cc);
-        row_c = row_cn;
-    }
-    cp_async_wait<0>();
-}
-
 // Frames per tile of the persistent backward.  A wide tile amortises the per-item flush of the 64 gradient sums; a narrow one keeps
 // the tile's x and dx rows (8 bytes per row and frame) in L2.  The kernel is issue-bound, so the wide tile wins until the rows
 // exceed L2 several times over -- measured on B200: 8192 rows 1.60 / 1.54 / 1.52 ms at 512 / 1024 / 2048 frames, 65536 rows
