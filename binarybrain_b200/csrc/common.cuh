@@ -23,6 +23,7 @@ inline int launch_status() { return (int)cudaGetLastError(); }
 struct DeviceInfo {
     int sm_count;
     size_t l2_bytes;
+    size_t total_bytes;          // device memory
 };
 const DeviceInfo &device_info();
 

@@ -83,7 +83,9 @@ public:
 
 // Host/device mirrored byte buffer.  The host mirror of a buffer of kPinnedFrom bytes or more is page-locked (cudaMallocHost, as the
 // reference's include/bbcu/bbcu_util.h:121 does for every host buffer) so that its transfers run at full PCIe rate and
-// asynchronously; small buffers and processes without a device use plain heap memory.
+// asynchronously; small buffers and processes without a device use plain heap memory.  Either side is materialised on first use:
+// a frame buffer that only ever lives on the device (every activation of a training step) never allocates or clears host memory.
+// A buffer that nothing has written yet reads as zeros on whichever side is asked for first.
 class Memory
 {
     static constexpr std::size_t kPinnedFrom = 64 * 1024;
@@ -92,14 +94,37 @@ class Memory
     std::uint8_t   *m_host = nullptr;
     bool            m_pinned = false;
     void           *m_dev = nullptr;
-    bool            m_host_valid = true;    // host copy holds the current contents
-    bool            m_dev_valid  = false;   // device copy holds the current contents
+    bool            m_host_valid = false;   // host copy holds the current contents
+    bool            m_dev_valid  = false;   // device copy holds the current contents; neither: the contents are zeros
 
     void release_host()
     {
         if (m_host) { if (m_pinned) bbcu_b200_host_free(m_host); else std::free(m_host); }
         m_host = nullptr;
         m_pinned = false;
+    }
+    bool want_pinned() const { return m_size >= kPinnedFrom && Manager::IsDeviceAvailable(); }
+    void ensure_host()
+    {
+        if (m_host) return;
+        if (want_pinned()) {
+            m_host = static_cast<std::uint8_t *>(bbcu_b200_host_alloc(m_size));
+            m_pinned = m_host != nullptr;
+        }
+        if (!m_host) m_host = static_cast<std::uint8_t *>(std::malloc(m_size ? m_size : 1));
+        if (!m_host) throw std::bad_alloc();
+    }
+    // bring the host copy up to date: from the device when that holds the contents, zeros when nothing does
+    void refresh_host(bool new_buf)
+    {
+        ensure_host();
+        if (m_host_valid || new_buf) return;
+        if (m_dev && m_dev_valid) {
+            BB_CUDA_CHECK(cudaMemcpyAsync(m_host, m_dev, m_size, cudaMemcpyDeviceToHost, Manager::Stream()));
+            BB_CUDA_CHECK(cudaStreamSynchronize(Manager::Stream()));
+        } else {
+            std::memset(m_host, 0, m_size);
+        }
     }
 
 public:
@@ -114,37 +139,24 @@ public:
         if (m_dev) { bbcu_LocalHeap_Free(m_dev); m_dev = nullptr; }
         release_host();
         m_size = size;
-        if (size >= kPinnedFrom && Manager::IsDeviceAvailable()) {
-            m_host = static_cast<std::uint8_t *>(bbcu_b200_host_alloc(size));
-            m_pinned = m_host != nullptr;
-        }
-        if (!m_host) m_host = static_cast<std::uint8_t *>(std::malloc(size ? size : 1));
-        if (!m_host) throw std::bad_alloc();
-        std::memset(m_host, 0, size);
-        m_host_valid = true;
+        m_host_valid = false;
         m_dev_valid  = false;
     }
     std::size_t GetSize() const { return m_size; }
-    bool IsHostPinned() const { return m_pinned; }
+    bool IsHostPinned() const { return m_host ? m_pinned : want_pinned(); }      // what the mirror is, or will be once it exists
     bool IsDeviceCurrent() const { return m_dev_valid; }
 
     // new_buf: the caller overwrites everything, so nothing is copied (reference: Lock(true)).
     void *Host(bool new_buf = false)
     {
-        if (!m_host_valid && !new_buf && m_dev) {
-            BB_CUDA_CHECK(cudaMemcpyAsync(m_host, m_dev, m_size, cudaMemcpyDeviceToHost, Manager::Stream()));
-            BB_CUDA_CHECK(cudaStreamSynchronize(Manager::Stream()));
-        }
+        refresh_host(new_buf);
         m_host_valid = true;
         m_dev_valid  = false;
         return m_host;
     }
     void const *HostConst()
     {
-        if (!m_host_valid && m_dev) {
-            BB_CUDA_CHECK(cudaMemcpyAsync(m_host, m_dev, m_size, cudaMemcpyDeviceToHost, Manager::Stream()));
-            BB_CUDA_CHECK(cudaStreamSynchronize(Manager::Stream()));
-        }
+        refresh_host(false);
         m_host_valid = true;
         return m_host;
     }
@@ -163,10 +175,14 @@ public:
             m_dev_valid = false;
         }
         if (!m_dev_valid && !new_buf && m_size) {
-            BB_CUDA_CHECK(cudaMemcpyAsync(m_dev, m_host, m_size, cudaMemcpyHostToDevice, Manager::Stream()));
-            // a page-locked source is read by the copy engine after this call returns: the host side may write it again only once
-            // the copy is done (a pageable source has been staged by the runtime already)
-            if (m_pinned) BB_CUDA_CHECK(cudaStreamSynchronize(Manager::Stream()));
+            if (m_host && m_host_valid) {
+                BB_CUDA_CHECK(cudaMemcpyAsync(m_dev, m_host, m_size, cudaMemcpyHostToDevice, Manager::Stream()));
+                // a page-locked source is read by the copy engine after this call returns: the host side may write it again only once
+                // the copy is done (a pageable source has been staged by the runtime already)
+                if (m_pinned) BB_CUDA_CHECK(cudaStreamSynchronize(Manager::Stream()));
+            } else {
+                BB_CUDA_CHECK(cudaMemsetAsync(m_dev, 0, m_size, Manager::Stream()));
+            }
         }
         m_dev_valid = true;
         return m_dev;
