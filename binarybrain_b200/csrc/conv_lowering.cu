@@ -4,8 +4,9 @@
 // output frame  fo = fi * P + p  (fi = input frame, p = oy * OW + ox, P = OH * OW).  Every operator here is pure
 // data movement, so the only thing to get right is that both the reads and the writes are made of full lines:
 //   * Im2Col / Col2Im exchange the roles of "pixel" and "frame" (pixels are nodes on one side and part of the frame
-//     index on the other), i.e. they are 32 x 32 tile transposes through shared memory (fp32) or 32 x 32 bit-matrix
-//     transposes by warp ballot (bit frames);
+//     index on the other), i.e. they are transposes through shared memory (fp32: a band of image rows x 32 frames per
+//     block for Im2Col, 32 x 32 tiles for Col2Im and for images too wide for a band) or 32 x 32 bit-matrix transposes by
+//     warp ballot (bit frames);
 //   * MaxPooling keeps the frame axis and is a straight per-frame window scan.
 //
 // Semantics follow the reference's CPU branches:
@@ -162,6 +163,201 @@ k_im2col_backward_f32(const float *__restrict__ dy, float *__restrict__ dx, Im2C
     for (int r = ty; r < 32; r += 8) {
         const int qq = qt * 32 + r, fi = ft * 32 + tx;
         if (qq < Q && fi < g.in_frames) dx[(size_t)(c * Q + qq) * g.in_fs + fi] = tile[tx][r];
+    }
+}
+
+// --------------------------------------------------------------------------------------------- Im2Col fp32, banded
+// The two tile kernels above spend ~38 instructions per element on index arithmetic that does not depend on the frame (two
+// integer divisions and the border logic per pixel, 64-bit offsets per element).  The banded kernels work that out once per
+// CTA and reuse it over 32 frames and all filter taps:
+//   block = one channel x one band of image rows x 32 input frames;
+//   * forward: the band's input rows (with the filter's halo) are read once into shared memory, [pixel][frame], lanes along
+//     frames; a table [tap][output pixel of the band] holds the shared-memory offset of the source pixel (or "border value", or a
+//     global pixel index when a border mode maps outside the band); then every (tap, frame) pair is one contiguous run of the
+//     output row, written by a warp with lanes along pixels -- one table read, one tile read, one store per element;
+//   * backward: a table [tap][input pixel of the band] holds the output pixel that tap reads (the reference's own enumeration:
+//     taps aligned with the pixel's position modulo the stride, in increasing order, include/bb/ConvolutionIm2Col.h:439-482);
+//     a lane owns one input pixel and four frames, sums its taps in registers (reads along output pixels), and the band is turned
+//     through shared memory so that the writes run along frames.
+// kBandPitch = 33 keeps both the frame-major fill and the pixel-major read-out free of bank conflicts.
+constexpr int kBandPitch = 33;
+constexpr int kBandSmemLimit = 64 * 1024;
+
+// Input pixel iy * in_w + ix (within a channel) read by output pixel (oy, ox) through tap (fy, fx), or -1 for the border value.
+__device__ __forceinline__ int im2col_source_pixel(const Im2ColGeom &g, int fy, int fx, int oy, int ox)
+{
+    int iy = oy * g.y_stride - g.y_offset + fy;
+    int ix = ox * g.x_stride - g.x_offset + fx;
+    if (iy >= 0 && iy < g.in_h && ix >= 0 && ix < g.in_w) return iy * g.in_w + ix;
+    if (border_remap(g.border_mode, ix, iy, g.in_w, g.in_h)) {
+        if (iy >= 0 && iy < g.in_h && ix >= 0 && ix < g.in_w) return iy * g.in_w + ix;
+    }
+    return -1;
+}
+
+__global__ void __launch_bounds__(256)
+k_im2col_forward_band_f32(const float *__restrict__ x, float *__restrict__ y, Im2ColGeom g, float border_value, int R, int rows_in, int bands,
+                          int f_tiles)
+{
+    extern __shared__ __align__(16) unsigned char band_smem[];
+    float *tile = reinterpret_cast<float *>(band_smem);                                   // [rows_in * in_w][kBandPitch]
+    int *src = reinterpret_cast<int *>(tile + (size_t)rows_in * g.in_w * kBandPitch);      // [taps][R * out_w]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int b = blockIdx.x;
+    const int ft = b % f_tiles; b /= f_tiles;
+    const int band = b % bands; b /= bands;
+    const int c = b;
+    const int oy0 = band * R, rows = min(R, g.out_h - oy0);
+    const int npix = rows * g.out_w, pitch = R * g.out_w;
+    const int iy0 = oy0 * g.y_stride - g.y_offset;                 // first input row an unremapped tap of the band reads
+    const int f0 = ft * 32;
+    const int taps = g.filter_h * g.filter_w;
+    const int Q = g.in_h * g.in_w, P = g.out_h * g.out_w;
+
+    for (int pl = threadIdx.x; pl < npix; pl += 256) {
+        const int oy = pl / g.out_w, ox = pl - oy * g.out_w;
+        for (int fy = 0, tap = 0; fy < g.filter_h; ++fy)
+            for (int fx = 0; fx < g.filter_w; ++fx, ++tap) {
+                const int pix = im2col_source_pixel(g, fy, fx, oy0 + oy, ox);
+                int s = -1;
+                if (pix >= 0) {
+                    const int local = pix - iy0 * g.in_w;          // in the band when 0 <= local < rows_in * in_w
+                    s = (local >= 0 && local < rows_in * g.in_w) ? local * (kBandPitch * 4) : -2 - pix;      // byte offset into the tile
+                }
+                src[tap * pitch + pl] = s;
+            }
+    }
+    {
+        const bool f_ok = f0 + lane < g.in_frames;
+        const float *xc = x + (size_t)c * Q * g.in_fs + f0 + lane;
+        const int n_in = rows_in * g.in_w;
+#pragma unroll 4
+        for (int q = warp; q < n_in; q += 8) {
+            const int pix = iy0 * g.in_w + q;
+            float v = 0.0f;
+            if (f_ok && pix >= 0 && pix < Q) v = xc[(size_t)pix * g.in_fs];
+            tile[q * kBandPitch + lane] = v;
+        }
+    }
+    __syncthreads();
+
+    // (tap, frame) pairs: each is one contiguous run of an output row.  The table holds byte offsets into the tile, so an element
+    // costs a table read, a tile read, a select (border value) and a store; pixels whose source lies outside the band (s < -1,
+    // only the wrapping / reflecting border modes at a band edge) are patched afterwards by the lanes that own them.
+    const int pairs = taps * 32;
+    const unsigned char *tile_b = reinterpret_cast<const unsigned char *>(tile);
+    for (int pr = warp; pr < pairs; pr += 8) {
+        const int tap = pr >> 5, fl = pr & 31;                     // warp-uniform
+        if (f0 + fl >= g.in_frames) continue;
+        float *yp = y + (size_t)(c * taps + tap) * g.out_fs + (size_t)(f0 + fl) * P + oy0 * g.out_w + lane;
+        const int *sp = src + tap * pitch + lane;
+        const unsigned char *tp = tile_b + 4 * fl;
+        int pl = lane;
+        bool outside = false;
+        for (; pl + 96 < npix; pl += 128, sp += 128, yp += 128) {
+            int sv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sv[i] = sp[32 * i];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float v = *reinterpret_cast<const float *>(tp + max(sv[i], 0));
+                yp[32 * i] = sv[i] >= 0 ? v : border_value;
+                outside |= sv[i] < -1;
+            }
+        }
+        for (; pl < npix; pl += 32, sp += 32, yp += 32) {
+            const int sv = sp[0];
+            const float v = *reinterpret_cast<const float *>(tp + max(sv, 0));
+            yp[0] = sv >= 0 ? v : border_value;
+            outside |= sv < -1;
+        }
+        if (__any_sync(0xffffffffu, outside)) {
+            const float *xg = x + (size_t)c * Q * g.in_fs + f0 + fl;
+            float *yq = y + (size_t)(c * taps + tap) * g.out_fs + (size_t)(f0 + fl) * P + oy0 * g.out_w;
+            const int *sq = src + tap * pitch;
+            for (int q = lane; q < npix; q += 32) {
+                const int sv = sq[q];
+                if (sv < -1) yq[q] = xg[(size_t)(-2 - sv) * g.in_fs];
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+k_im2col_backward_band_f32(const float *__restrict__ dy, float *__restrict__ dx, Im2ColGeom g, int R, int bands, int f_tiles)
+{
+    extern __shared__ __align__(16) unsigned char band_smem[];
+    float *tile = reinterpret_cast<float *>(band_smem);                                   // [R * in_w][kBandPitch]
+    int *src = reinterpret_cast<int *>(tile + (size_t)R * g.in_w * kBandPitch);            // [taps][R * in_w]: output pixel, or -1
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int b = blockIdx.x;
+    const int ft = b % f_tiles; b /= f_tiles;
+    const int band = b % bands; b /= bands;
+    const int c = b;
+    const int y0 = band * R, rows = min(R, g.in_h - y0);
+    const int npix = rows * g.in_w, pitch = R * g.in_w;
+    const int f0 = ft * 32;
+    const int taps = g.filter_h * g.filter_w;
+    const int Q = g.in_h * g.in_w, P = g.out_h * g.out_w;
+    const int iy_limit = (g.out_h - 1) * g.y_stride, ix_limit = (g.out_w - 1) * g.x_stride;
+
+    // the reference visits fy = yy % y_stride, + y_stride, ... and fx likewise; every other tap sends nothing to this pixel
+    for (int ql = threadIdx.x; ql < npix; ql += 256) {
+        const int yl = ql / g.in_w, xx = ql - yl * g.in_w, yy = y0 + yl;
+        const bool ys1 = g.y_stride == 1, xs1 = g.x_stride == 1;
+        const int ya = ys1 ? 0 : yy % g.y_stride, xa = xs1 ? 0 : xx % g.x_stride;
+        for (int fy = 0, tap = 0; fy < g.filter_h; ++fy) {
+            const int iy = yy - fy + g.y_offset;
+            const bool y_ok = fy >= ya && (ys1 || (fy - ya) % g.y_stride == 0) && iy >= 0 && iy <= iy_limit;
+            const int row = (ys1 ? iy : iy / g.y_stride) * g.out_w;
+            for (int fx = 0; fx < g.filter_w; ++fx, ++tap) {
+                const int ix = xx - fx + g.x_offset;
+                const bool ok = y_ok && fx >= xa && (xs1 || (fx - xa) % g.x_stride == 0) && ix >= 0 && ix <= ix_limit;
+                src[tap * pitch + ql] = ok ? row + (xs1 ? ix : ix / g.x_stride) : -1;
+            }
+        }
+    }
+    __syncthreads();
+
+    // warp w owns frames f0 + w + 8 k, k = 0..3
+    const float *base[4];
+    bool ok[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const int fi = f0 + warp + 8 * k;
+        ok[k] = fi < g.in_frames;
+        base[k] = dy + (size_t)c * taps * g.out_fs + (size_t)(ok[k] ? fi : 0) * P;
+    }
+    // Two pixels per lane and trip, three taps unrolled: 24 independent loads in flight per lane.  Every tap is loaded (a tap that
+    // sends nothing reads element 0 of its row and adds zero) so that the loads do not wait for the table; x + 0 differs from x only
+    // in the sign of a zero, which the final 0.0f + acc removes.
+    for (int ql = lane; ql < npix; ql += 64) {
+        const bool second = ql + 32 < npix;
+        const int qb = second ? ql + 32 : ql;
+        float acc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+#pragma unroll 3
+        for (int tap = 0; tap < taps; ++tap) {
+            const int sa = src[tap * pitch + ql], sb = src[tap * pitch + qb];
+            const size_t row = (size_t)tap * g.out_fs;
+            const size_t offa = row + (sa >= 0 ? sa : 0), offb = row + (sb >= 0 ? sb : 0);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float va = base[k][offa], vb = base[k][offb];
+                acc[0][k] += (sa >= 0 && ok[k]) ? va : 0.0f;
+                acc[1][k] += (sb >= 0 && ok[k]) ? vb : 0.0f;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            tile[ql * kBandPitch + warp + 8 * k] = 0.0f + acc[0][k];
+            if (second) tile[qb * kBandPitch + warp + 8 * k] = 0.0f + acc[1][k];
+        }
+    }
+    __syncthreads();
+    if (f0 + lane < g.in_frames) {
+        float *dxc = dx + ((size_t)c * Q + (size_t)y0 * g.in_w) * g.in_fs + f0 + lane;
+#pragma unroll 4
+        for (int ql = warp; ql < npix; ql += 8) dxc[(size_t)ql * g.in_fs] = tile[ql * kBandPitch + lane];
     }
 }
 
@@ -394,6 +590,18 @@ k_maxpool_backward(const void *__restrict__ sel, const float *__restrict__ dy, f
     }
 }
 
+// Rows per band of the banded Im2Col kernels: at most `fit` (what shared memory holds) and at most 8, halved while the grid has fewer
+// than four blocks per SM.  Measured on B200 (32 channels of 32 x 32, 256 frames, 3 x 3): forward 0.161 / 0.105 / 0.077 / 0.076 /
+// 0.104 ms at 1 / 2 / 4 / 8 / 10 rows -- short bands write short runs per frame, tall ones leave too few blocks.
+int band_rows_for_occupancy(int fit, int rows_total, long long other_blocks)
+{
+    int R = fit < rows_total ? fit : rows_total;
+    if (R > 8) R = 8;
+    const long long want = 4LL * device_info().sm_count;
+    while (R > 1 && other_blocks * ((rows_total + R - 1) / R) < want) R = (R + 1) / 2;
+    return R;
+}
+
 int check_im2col(const void *a, const void *b, int x_stride, int y_stride, int in_frames, long long in_fs, int in_w, int in_h, int in_c, int out_w,
                  int out_h, long long out_fs, int filter_w, int filter_h, int frames_per_unit_in, int frames_per_unit_out)
 {
@@ -453,7 +661,33 @@ extern "C" int bbcu_fp32_Im2Col_Forward(const float *dev_x_buf, float *dev_y_buf
     if (P == 0 || input_frame_size == 0 || out_nodes == 0) return BBCU_OK;
     const Im2ColGeom g = make_geom(x_stride, y_stride, x_offset, y_offset, input_frame_size, input_frame_stride, input_w_size, input_h_size,
                                    input_c_size, output_w_size, output_h_size, output_frame_stride, filter_w_size, filter_h_size, border_mode);
-    const int p_tiles = (int)((P + 32 * kIm2ColTiles - 1) / (32 * kIm2ColTiles)), f_tiles = (input_frame_size + 31) / 32;
+    const int f_tiles = (input_frame_size + 31) / 32;
+    {
+        // banded kernel: the widest band of output rows whose input rows and source table fit the shared-memory budget
+        const int taps = filter_h_size * filter_w_size;
+        auto rows_in_of = [&](int R) { return (long long)(R - 1) * y_stride + filter_h_size; };
+        auto smem_of = [&](int R) { return (rows_in_of(R) * input_w_size * kBandPitch + (long long)taps * R * output_w_size) * 4; };
+        // smem_of(R) = R * per_row + fixed
+        const long long per_row = ((long long)y_stride * input_w_size * kBandPitch + (long long)taps * output_w_size) * 4;
+        const long long fixed = (long long)(filter_h_size - y_stride) * input_w_size * kBandPitch * 4;
+        long long fit = (kBandSmemLimit - fixed) / per_row;
+        if (fit > output_h_size) fit = output_h_size;
+        while (fit >= 1 && smem_of((int)fit) > kBandSmemLimit) --fit;
+        int R = fit >= 1 ? (int)fit : 0;
+        if (R > 0) {
+            R = band_rows_for_occupancy(R, output_h_size, (long long)input_c_size * f_tiles);
+            const int bands = (output_h_size + R - 1) / R;
+            const long long blocks = (long long)input_c_size * bands * f_tiles;
+            BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+            const int smem = (int)smem_of(R);
+            BB200_CUDA(cudaFuncSetAttribute(k_im2col_forward_band_f32, cudaFuncAttributeMaxDynamicSharedMemorySize, kBandSmemLimit));
+            k_im2col_forward_band_f32<<<(unsigned)blocks, 256, smem, as_stream(stream)>>>(dev_x_buf, dev_y_buf, g, border_value, R, (int)rows_in_of(R),
+                                                                                       bands, f_tiles);
+            return launch_status();
+        }
+    }
+    // images too wide for a band in shared memory: 32 x 32 tile transposes
+    const int p_tiles = (int)((P + 32 * kIm2ColTiles - 1) / (32 * kIm2ColTiles));
     const long long blocks = out_nodes * p_tiles * f_tiles;
     BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
     k_im2col_forward_f32<<<(unsigned)blocks, dim3(32, 8), 0, as_stream(stream)>>>(dev_x_buf, dev_y_buf, g, border_value, p_tiles, f_tiles);
@@ -499,7 +733,23 @@ extern "C" int bbcu_fp32_Im2Col_Backward(const float *dev_dy_buf, float *dev_dx_
     if (input_c_size == 0 || input_frame_size == 0) return BBCU_OK;
     const Im2ColGeom g = make_geom(x_stride, y_stride, x_offset, y_offset, input_frame_size, input_frame_stride, input_w_size, input_h_size,
                                    input_c_size, output_w_size, output_h_size, output_frame_stride, filter_w_size, filter_h_size, kBorderConstant);
-    const int q_tiles = (input_w_size * input_h_size + 31) / 32, f_tiles = (input_frame_size + 31) / 32;
+    const int f_tiles = (input_frame_size + 31) / 32;
+    {
+        const int taps = filter_h_size * filter_w_size;
+        const long long per_row = (long long)input_w_size * (kBandPitch + taps) * 4;
+        int R = (int)(kBandSmemLimit / per_row);
+        if (R > input_h_size) R = input_h_size;
+        if (R > 0 && output_w_size > 0 && output_h_size > 0) {        // (the banded kernel reads element 0 of a row for a tap that sends nothing)
+            R = band_rows_for_occupancy(R, input_h_size, (long long)input_c_size * f_tiles);
+            const int bands = (input_h_size + R - 1) / R;
+            const long long blocks = (long long)input_c_size * bands * f_tiles;
+            BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+            BB200_CUDA(cudaFuncSetAttribute(k_im2col_backward_band_f32, cudaFuncAttributeMaxDynamicSharedMemorySize, kBandSmemLimit));
+            k_im2col_backward_band_f32<<<(unsigned)blocks, 256, (int)(per_row * R), as_stream(stream)>>>(dev_dy_buf, dev_dx_buf, g, R, bands, f_tiles);
+            return launch_status();
+        }
+    }
+    const int q_tiles = (input_w_size * input_h_size + 31) / 32;
     const long long blocks = (long long)input_c_size * q_tiles * f_tiles;
     BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
     k_im2col_backward_f32<<<(unsigned)blocks, dim3(32, 8), 0, as_stream(stream)>>>(dev_dy_buf, dev_dx_buf, g, q_tiles, f_tiles);

@@ -91,6 +91,33 @@ def test_conv_lowering_gpu_against_golden(golden):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("c,h,w,fh,fw,ys,xs,pad,F", [
+    (4, 32, 32, 3, 3, 1, 1, "same", 70),        # several bands of several rows, frame tail
+    (2, 40, 24, 5, 5, 1, 1, "same", 33),        # halo of two rows each side
+    (3, 33, 31, 3, 3, 2, 2, "same", 40),        # strides, odd sizes
+    (2, 30, 20, 3, 2, 2, 1, "valid", 9),
+    (1, 3, 600, 3, 3, 1, 1, "same", 8),         # a row too wide for a band in shared memory: the tile kernels
+])
+def test_im2col_fp32_bands_against_oracle(c, h, w, fh, fw, ys, xs, pad, F):
+    """Im2Col fp32 forward (every border mode) and backward where the image splits into several bands, and where it does not fit
+    a band at all; the forward moves values (exact), the backward adds at most filter_h * filter_w of them in the reference's order."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from binarybrain_b200 import ops
+    from gpu_util import dev_fp32, host_fp32
+    oh, ow, _, _ = port.im2col_geometry(h, w, fh, fw, ys, xs, pad)
+    x = det_uniform((c * h * w, F), 410)
+    xd = dev_fp32(x)
+    for border in BORDERS:
+        y = ops.im2col_forward(xd, F, c, h, w, fh, fw, ys, xs, pad, border)
+        assert np.array_equal(host_fp32(y, F * oh * ow), port.im2col_forward(x, c, h, w, fh, fw, ys, xs, pad, border)), border
+    dy = det_uniform((c * fh * fw, F * oh * ow), 411)
+    dx = ops.im2col_backward(dev_fp32(dy), F, c, h, w, fh, fw, ys, xs, pad)
+    assert np.array_equal(host_fp32(dx, F), port.im2col_backward(dy, c, h, w, fh, fw, ys, xs, pad))
+
+
+@pytest.mark.gpu
 def test_config3_block_shapes_gpu_against_oracle():
     """The lowering of the LUT-CNN's first conv block at full size: 3x32x32 images, batch 256, 3x3 'same' Im2Col (frames
     x1024, the bit-frame fast path with 32 pixel groups), Col2Im back from 32 channels and 2x2 MaxPooling, fp32 and bit frames."""
