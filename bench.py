@@ -522,11 +522,14 @@ def cnn_section(torch, steps):
 
 
 def operators_section(torch, ops, steps):
-    """Every other operator of the path on an 8192 -> 8192 x 16384-frame layer (bit inputs: same node counts, 16384 frames), each with
-    its algorithmic bytes / flops per node-frame and the fraction of max(HBM, FP32) roofline time, plus the lowering operators at the
-    LUT-CNN's first conv block shape and Adam.  One launch sequence per operator call, timed with CUDA events over `steps` calls."""
+    """Every other operator of the path on an 8192 -> 8192 x 16384-frame layer, each with its algorithmic bytes / flops per node-frame
+    and the fraction of max(HBM, FP32) roofline time, plus the lowering operators on 32-channel 32x32 images and Adam.  One launch
+    sequence per operator call, timed with CUDA events over `steps` back-to-back calls; operators whose device time at the layer's
+    shape would be below the ~20 us a call costs on the host run on a larger case (bit -> bit forwards: 262144 frames; Col2Im and
+    MaxPooling: batch 2048; Adam: eight 65536 x 64 tables), named in `layer`."""
     I = O = 8192
     F = 16384
+    FB = 262144                                       # frames of the bit -> bit forwards
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(4)
     idx = torch.rand((O, I), device=dev, generator=g).argsort(dim=1)[:, :6].to(torch.int32).contiguous()
@@ -538,11 +541,14 @@ def operators_section(torch, ops, steps):
     rm, rv = torch.zeros(O, device=dev), torch.ones(O, device=dev)
     yf = torch.empty((O, F), device=dev)
     ybit = torch.zeros((O, ops.bit_stride(F)), dtype=torch.int32, device=dev)
+    xbb = torch.randint(-2**31, 2**31 - 1, (I, ops.bit_stride(FB)), device=dev, generator=g, dtype=torch.int32)
+    ybb = torch.zeros((O, ops.bit_stride(FB)), dtype=torch.int32, device=dev)
     dx = torch.empty((I, F), device=dev)
     st = {}
+    _, st["mean"], st["rstd"] = ops.differentiable_lut6_forward_training(xb, idx, W, rm, rv, F, y=ybit)      # statistics of the bit backward case
 
     def dl_bit_fwd():
-        _, st["mean"], st["rstd"] = ops.differentiable_lut6_forward_training(xb, idx, W, rm, rv, F, y=ybit)
+        ops.differentiable_lut6_forward_training(xbb, idx, W, rm, rv, FB, y=ybb)
 
     def dl_binary_fwd():
         _, st["bmean"], st["brstd"] = ops.differentiable_lut6_forward_training(xf, idx, W, rm, rv, F, y=yf, binary=True)
@@ -550,24 +556,28 @@ def operators_section(torch, ops, steps):
     def sbn_fwd():
         st["sy"], st["smean"], st["srstd"] = ops.stochastic_bn_forward_training(xf, rm, rv, F)
 
-    adam = ops.Adam([W], [dW])
-    # lowering at the first conv block of the LUT-CNN: 32 channels, 32x32, batch 256
-    c, hw, B = 32, 32, 256
+    tables = [(torch.randn((65536, 64), device=dev, generator=g) * 0.01 + 0.5) for _ in range(8)]
+    adam = ops.Adam(tables, [torch.rand((65536, 64), device=dev, generator=g) for _ in range(8)])
+    # lowering at the LUT-CNN's 32-channel conv: 32x32 images, batch 256 for Im2Col (its output is 9x the image), 2048 for the rest
+    c, hw, B, B2 = 32, 32, 256, 2048
     img = torch.rand((c * hw * hw, B), device=dev, generator=g)
     cols = ops.im2col_forward(img, B, c, hw, hw, 3, 3, padding="same")
-    colsb_in = torch.randint(-2**31, 2**31 - 1, (c * hw * hw, ops.bit_stride(B)), device=dev, generator=g, dtype=torch.int32)
-    z = torch.rand((c, B * hw * hw), device=dev, generator=g)
-    pooled, am = ops.maxpool_forward(img, B, c, hw, hw, 2, 2)
+    colsb_in = torch.randint(-2**31, 2**31 - 1, (c * hw * hw, ops.bit_stride(B2)), device=dev, generator=g, dtype=torch.int32)
+    img2 = torch.rand((c * hw * hw, B2), device=dev, generator=g)
+    z = torch.rand((c, B2 * hw * hw), device=dev, generator=g)
+    pooled, am = ops.maxpool_forward(img2, B2, c, hw, hw, 2, 2)
     gp = torch.rand_like(pooled)
     nf = float(O) * F
+    nfb = float(O) * FB
     px = float(c) * hw * hw * B                       # image elements
+    px2 = float(c) * hw * hw * B2
     cases = {   # name: (callable, units per call, algorithmic bytes per unit, algorithmic flops per unit)
         "sl6_forward_bit_fp32": (lambda: ops.stochastic_lut6_forward(xb, idx, W, F, y=yf), nf, 4.125, 0.0),       # per-pattern value lookup
         # bit in, bit out: evaluated as a BinaryLut6 forward with a per-node truth table (no per-frame fp32 tree), so the bound is HBM
-        "sl6_forward_bit_bit": (lambda: ops.stochastic_lut6_forward(xb, idx, W, F, y=ybit, bit_output=True), nf, 0.25, 0.0),
+        "sl6_forward_bit_bit": (lambda: ops.stochastic_lut6_forward(xbb, idx, W, FB, y=ybb, bit_output=True), nfb, 0.25, 0.0),
         "sl6_backward_bit": (lambda: ops.stochastic_lut6_backward(xb, dy, idx, W, dW, I, F, dx=dx), nf, 8.125, 505.0),
-        "dl6_forward_training_bit": (dl_bit_fwd, nf, 0.375, 0.0),       # x read twice (pattern histogram, then the table forward)
-        "dl6_forward_inference_bit": (lambda: ops.differentiable_lut6_forward_inference(xb, idx, W, rm, rv, F, y=ybit), nf, 0.25, 0.0),
+        "dl6_forward_training_bit": (dl_bit_fwd, nfb, 0.375, 0.0),      # x read twice (pattern histogram, then the table forward)
+        "dl6_forward_inference_bit": (lambda: ops.differentiable_lut6_forward_inference(xbb, idx, W, rm, rv, FB, y=ybb), nfb, 0.25, 0.0),
         "dl6_forward_inference_fp32": (lambda: ops.differentiable_lut6_forward_inference(xf, idx, W, rm, rv, F, y=yf, binary=False), nf, 8.0, 136.0),
         "dl6_backward_bit": (lambda: ops.differentiable_lut6_backward(xb, dy, idx, W, dW, st["mean"], st["rstd"], I, F, dx=dx), nf, 12.125, 651.0),
         # binary mode on fp32 frames (the reference's default mode): forward by the fp32 tree, backward through the per-pattern tables
@@ -578,18 +588,19 @@ def operators_section(torch, ops, steps):
         "sl6_backward_fp32_binary": (lambda: ops.stochastic_lut6_backward(xf, dy, idx, W, dW, I, F, dx=dx, binary=True), nf, 12.0, 505.0),
         "sbn_forward_training": (sbn_fwd, nf, 12.0, 8.0),
         "sbn_backward": (lambda: ops.stochastic_bn_backward(xf, dy, st["smean"], st["srstd"], F), nf, 20.0, 12.0),
-        "adam_update": (lambda: adam.update(), float(W.numel()), 28.0, 12.0),
+        "adam_update": (lambda: adam.update(), 8.0 * 65536 * 64, 28.0, 12.0),
         "im2col_forward_fp32": (lambda: ops.im2col_forward(img, B, c, hw, hw, 3, 3, padding="same"), px * 9, 4.0 + 4.0 / 9, 0.0),
-        "im2col_forward_bit": (lambda: ops.im2col_forward(colsb_in, B, c, hw, hw, 3, 3, padding="same"), px * 9, (1 + 1.0 / 9) / 8, 0.0),
+        "im2col_forward_bit": (lambda: ops.im2col_forward(colsb_in, B2, c, hw, hw, 3, 3, padding="same"), px2 * 9, (1 + 1.0 / 9) / 8, 0.0),
         "im2col_backward_fp32": (lambda: ops.im2col_backward(cols, B, c, hw, hw, 3, 3, padding="same"), px * 9, 4.0 + 4.0 / 9, 1.0),
-        "col2im_forward_fp32": (lambda: ops.col2im_forward(z, c, hw, hw, B), px, 8.0, 0.0),
-        "col2im_backward_fp32": (lambda: ops.col2im_backward(img, c, hw, hw, B), px, 8.0, 0.0),
-        "maxpool_forward_fp32": (lambda: ops.maxpool_forward(img, B, c, hw, hw, 2, 2), px, 4.0 + 2.0, 1.0),
-        "maxpool_backward_fp32": (lambda: ops.maxpool_backward(am, gp, B, c, hw, hw, 2, 2), px, 4.0 + 2.0, 0.0),
+        "col2im_forward_fp32": (lambda: ops.col2im_forward(z, c, hw, hw, B2), px2, 8.0, 0.0),
+        "col2im_backward_fp32": (lambda: ops.col2im_backward(img2, c, hw, hw, B2), px2, 8.0, 0.0),
+        "maxpool_forward_fp32": (lambda: ops.maxpool_forward(img2, B2, c, hw, hw, 2, 2), px2, 4.0 + 2.0, 1.0),
+        "maxpool_backward_fp32": (lambda: ops.maxpool_backward(am, gp, B2, c, hw, hw, 2, 2), px2, 4.0 + 2.0, 0.0),
     }
     hbm, which, _ = measured_peaks()
     fp32_peak = fp32_peak_flops(torch)
-    out = {"layer": f"{I}->{O} nodes, {F} frames (bit inputs: same frames, 32 per word); lowering: {c} channels {hw}x{hw}, batch {B}, 3x3 same / 2x2 pool",
+    out = {"layer": f"{I}->{O} nodes, {F} frames (bit -> bit forwards: {FB} frames); lowering: {c} channels {hw}x{hw}, 3x3 same / 2x2 pool, batch {B} "
+                    f"(Im2Col fp32) and {B2} (Im2Col bit, Col2Im, MaxPooling); Adam: 8 tables of 65536 x 64",
            "unit": "node-frames (LUT, SBN), table entries (Adam), output elements (lowering: Im2Col counts the 9x expanded buffer)",
            "hbm_peak": f"{hbm} GB/s of {which}"}
     for name, (fn, units, bytes_, flops) in cases.items():
@@ -621,7 +632,7 @@ def main():
     ap.add_argument("--global-batch", type=int, default=TRAIN_GLOBAL_BATCH, help="frames per step over all GPUs (default: 32768)")
     ap.add_argument("--bl6-frames", type=int, default=BL6_FRAMES, help="frames per GPU of the BinaryLut6 section (default: 2^20)")
     ap.add_argument("--no-extras", action="store_true", help="headline only: no e2e leg, no sub-sections, no CPU baseline")
-    ap.add_argument("--only", default=None, choices=["train", "binary_lut6", "fp32"], help="run and print one section (profiling aid)")
+    ap.add_argument("--only", default=None, choices=["train", "binary_lut6", "fp32", "operators"], help="run and print one section (profiling aid)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -662,6 +673,9 @@ def main():
     W = max(args.warmup, 3)
     if args.only == "fp32":
         print(json.dumps({"fp32": fp32_section(torch, ops, max(1, args.steps))}))
+        return 0
+    if args.only == "operators":
+        print(json.dumps({"operators": operators_section(torch, ops, max(1, args.steps))}))
         return 0
     if args.only == "binary_lut6":
         print(json.dumps({"binary_lut6": binary_lut6_section(torch, ops, dist, world, rank, args.steps, W, args.bl6_frames, False)}))
