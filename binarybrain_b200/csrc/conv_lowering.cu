@@ -362,16 +362,19 @@ k_im2col_backward_band_f32(const float *__restrict__ dy, float *__restrict__ dx,
 }
 
 // 32 x 32 bit-matrix transpose across a warp: lane k holds row k; afterwards lane j holds column j (bit k of the result =
-// bit j of lane k's word).
-__device__ __forceinline__ uint32_t warp_bit_transpose(uint32_t row, int lane)
+// bit j of lane k's word).  Five exchange stages: at distance s the lanes r and r + s swap the off-diagonal s x s blocks of every
+// 2s x 2s block (bits with (c & s) != 0 of the lower lane against bits with (c & s) == 0 of the upper one) -- one shuffle and four
+// logic operations per stage instead of 32 ballots.
+__device__ __forceinline__ uint32_t warp_bit_transpose(uint32_t v, int lane)
 {
-    uint32_t mine = 0;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        const uint32_t col = __ballot_sync(0xffffffffu, (row >> j) & 1u);
-        if (lane == j) mine = col;
+    for (int k = 0; k < 5; ++k) {
+        const int s = 16 >> k;
+        const uint32_t low = k == 0 ? 0x0000ffffu : k == 1 ? 0x00ff00ffu : k == 2 ? 0x0f0f0f0fu : k == 3 ? 0x33333333u : 0x55555555u;
+        const uint32_t other = __shfl_xor_sync(0xffffffffu, v, s);
+        v = (lane & s) ? ((v & ~low) | ((other >> s) & low)) : ((v & low) | ((other << s) & ~low));
     }
-    return mine;
+    return v;
 }
 
 // --------------------------------------------------------------------------------------------- Im2Col bit
