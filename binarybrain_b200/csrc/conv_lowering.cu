@@ -363,44 +363,72 @@ k_im2col_backward_band_f32(const float *__restrict__ dy, float *__restrict__ dx,
 
 // 32 x 32 bit-matrix transpose across a warp: lane k holds row k; afterwards lane j holds column j (bit k of the result =
 // bit j of lane k's word).  Five exchange stages: at distance s the lanes r and r + s swap the off-diagonal s x s blocks of every
-// 2s x 2s block (bits with (c & s) != 0 of the lower lane against bits with (c & s) == 0 of the upper one) -- one shuffle and four
-// logic operations per stage instead of 32 ballots.
-__device__ __forceinline__ uint32_t warp_bit_transpose(uint32_t v, int lane)
-{
+// 2s x 2s block (bits with (c & s) != 0 of the lower lane against bits with (c & s) == 0 of the upper one).  The partner's word is
+// rotated by s (lower lane) or 32 - s (upper lane) -- inside the bits that are taken a rotation equals the shift -- and merged by
+// one bit-select: a shuffle, a funnel shift and a logic operation per stage instead of 32 ballots.
+struct BitTranspose {
+    uint32_t keep[5];          // bits a lane keeps at stage k
+    int rot[5];                // left rotation of the partner's word at stage k
+    __device__ __forceinline__ explicit BitTranspose(int lane)
+    {
 #pragma unroll
-    for (int k = 0; k < 5; ++k) {
-        const int s = 16 >> k;
-        const uint32_t low = k == 0 ? 0x0000ffffu : k == 1 ? 0x00ff00ffu : k == 2 ? 0x0f0f0f0fu : k == 3 ? 0x33333333u : 0x55555555u;
-        const uint32_t other = __shfl_xor_sync(0xffffffffu, v, s);
-        v = (lane & s) ? ((v & ~low) | ((other >> s) & low)) : ((v & low) | ((other << s) & ~low));
+        for (int k = 0; k < 5; ++k) {
+            const int s = 16 >> k;
+            const uint32_t low = k == 0 ? 0x0000ffffu : k == 1 ? 0x00ff00ffu : k == 2 ? 0x0f0f0f0fu : k == 3 ? 0x33333333u : 0x55555555u;
+            keep[k] = (lane & s) ? ~low : low;
+            rot[k]  = (lane & s) ? 32 - s : s;
+        }
     }
-    return v;
-}
+    __device__ __forceinline__ uint32_t operator()(uint32_t v) const
+    {
+#pragma unroll
+        for (int k = 0; k < 5; ++k) {
+            const uint32_t other = __shfl_xor_sync(0xffffffffu, v, 16 >> k);
+            const uint32_t r = __funnelshift_l(other, other, rot[k]);
+            v = (v & keep[k]) | (r & ~keep[k]);
+        }
+        return v;
+    }
+};
+
+__device__ __forceinline__ uint32_t warp_bit_transpose(uint32_t v, int lane) { return BitTranspose(lane)(v); }
 
 // --------------------------------------------------------------------------------------------- Im2Col bit
-// P % 32 == 0: an output word is 32 consecutive pixels of one input frame.  A warp takes one input word column (32 input
-// frames) and one group of 32 pixels: lane k reads the word of pixel k, the ballot transpose gives lane j the output word of
-// input frame j.  A block covers up to 32 consecutive pixel groups, so each frame's words leave as one contiguous run.
+// P % 32 == 0: an output word is 32 consecutive pixels of one input frame.  A warp takes one group of 32 pixels (lane k owns pixel
+// k and works out its source node once) and walks W input word columns (32 input frames each): lane k reads the word of its pixel,
+// the transpose gives lane j the output word of input frame j.  A block covers up to 32 consecutive pixel groups, so each frame's
+// words leave as one contiguous run, and W columns, so the source arithmetic (two divisions and the border logic per pixel) is
+// spread over 32 W frames.
+constexpr int kBitColumns = 8;
+
 __global__ void __launch_bounds__(256)
-k_im2col_forward_bit(const uint32_t *__restrict__ x, uint32_t *__restrict__ y, Im2ColGeom g, int groups, int g_tiles, int in_words)
+k_im2col_forward_bit(const uint32_t *__restrict__ x, uint32_t *__restrict__ y, Im2ColGeom g, int groups, int g_tiles, int in_words, int w_tiles)
 {
-    __shared__ uint32_t tile[32][33];                             // [input frame j][pixel group]
+    __shared__ uint32_t tile[kBitColumns][32][33];                // [word column][input frame j][pixel group]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     int b = blockIdx.x;
     const int gt = b % g_tiles; b /= g_tiles;
-    const int wi = b % in_words; b /= in_words;
+    const int wt = b % w_tiles; b /= w_tiles;
     const int on = b;
     const int fx = on % g.filter_w, fy = (on / g.filter_w) % g.filter_h, c = on / (g.filter_w * g.filter_h);
     const int g0 = gt * 32, gn = min(32, groups - g0);
+    const int w0 = wt * kBitColumns, wn = min(kBitColumns, in_words - w0);
+    const BitTranspose transpose(lane);
     for (int gl = warp; gl < gn; gl += 8) {
         const int in = im2col_source(g, c, fy, fx, (g0 + gl) * 32 + lane);
-        const uint32_t row = in >= 0 ? x[(size_t)in * g.in_fs + wi] : 0u;
-        tile[lane][gl] = warp_bit_transpose(row, lane);
+        const uint32_t *row = x + (size_t)(in >= 0 ? in : 0) * g.in_fs + w0;
+        uint32_t v[kBitColumns];
+#pragma unroll
+        for (int wl = 0; wl < kBitColumns; ++wl) v[wl] = (in >= 0 && wl < wn) ? row[wl] : 0u;
+        // (columns past the end of the row transpose zeros that nothing reads)
+#pragma unroll
+        for (int wl = 0; wl < kBitColumns; ++wl) tile[wl][lane][gl] = transpose(v[wl]);
     }
     __syncthreads();
-    for (int j = warp; j < 32; j += 8) {
-        const int fi = wi * 32 + j;
-        if (fi < g.in_frames && lane < gn) y[(size_t)on * g.out_fs + (size_t)fi * groups + g0 + lane] = tile[j][lane];
+    for (int r = warp; r < wn * 32; r += 8) {
+        const int wl = r >> 5, j = r & 31;
+        const int fi = (w0 + wl) * 32 + j;
+        if (fi < g.in_frames && lane < gn) y[(size_t)on * g.out_fs + (size_t)fi * groups + g0 + lane] = tile[wl][j][lane];
     }
 }
 
@@ -427,40 +455,44 @@ k_im2col_forward_bit_any(const uint32_t *__restrict__ x, uint32_t *__restrict__ 
 
 // --------------------------------------------------------------------------------------------- Col2Im
 // FORWARD: y[c * hw + xy][fo] = x[c][fo * hw + xy];  otherwise dx[c][fo * hw + xy] = dy[c * hw + xy][fo].
-// Block = one channel x 32 pixels x 32 output frames; the image-side array is walked along frames, the column-side one along pixels.
+// Block = one channel x 64 pixels x 64 output frames, turned through shared memory: both sides move 256 contiguous bytes per row
+// and every thread has 16 independent loads in flight before the barrier.  The image-side array is walked along frames, the
+// column-side one along pixels.
+constexpr int kCol2ImTile = 64;
+
 template <bool FORWARD>
 __global__ void __launch_bounds__(256)
 k_col2im_f32(const float *__restrict__ src, float *__restrict__ dst, int hw, int out_frames, long long col_fs, long long img_fs, int xy_tiles,
              int f_tiles)
 {
-    __shared__ float tile[32][33];
-    const int tx = threadIdx.x, ty = threadIdx.y;
+    __shared__ float tile[kCol2ImTile][kCol2ImTile + 1];
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
     int b = blockIdx.x;
     const int xt = b % xy_tiles; b /= xy_tiles;
     const int ft = b % f_tiles; b /= f_tiles;
     const int c = b;
-    const int xy0 = xt * 32, f0 = ft * 32;
+    const int xy0 = xt * kCol2ImTile, f0 = ft * kCol2ImTile;
     if (FORWARD) {
 #pragma unroll
-        for (int r = ty; r < 32; r += 8) {                        // r = frame, tx = pixel
+        for (int r = ty; r < kCol2ImTile; r += 4) {               // r = frame, tx = pixel
             const int fo = f0 + r, xy = xy0 + tx;
             tile[r][tx] = (fo < out_frames && xy < hw) ? src[(size_t)c * col_fs + (size_t)fo * hw + xy] : 0.0f;
         }
         __syncthreads();
 #pragma unroll
-        for (int r = ty; r < 32; r += 8) {                        // r = pixel, tx = frame
+        for (int r = ty; r < kCol2ImTile; r += 4) {               // r = pixel, tx = frame
             const int xy = xy0 + r, fo = f0 + tx;
             if (fo < out_frames && xy < hw) dst[(size_t)(c * hw + xy) * img_fs + fo] = tile[tx][r];
         }
     } else {
 #pragma unroll
-        for (int r = ty; r < 32; r += 8) {                        // r = pixel, tx = frame
+        for (int r = ty; r < kCol2ImTile; r += 4) {               // r = pixel, tx = frame
             const int xy = xy0 + r, fo = f0 + tx;
             tile[r][tx] = (fo < out_frames && xy < hw) ? src[(size_t)(c * hw + xy) * img_fs + fo] : 0.0f;
         }
         __syncthreads();
 #pragma unroll
-        for (int r = ty; r < 32; r += 8) {                        // r = frame, tx = pixel
+        for (int r = ty; r < kCol2ImTile; r += 4) {               // r = frame, tx = pixel
             const int fo = f0 + r, xy = xy0 + tx;
             if (fo < out_frames && xy < hw) dst[(size_t)c * col_fs + (size_t)fo * hw + xy] = tile[tx][r];
         }
@@ -514,29 +546,52 @@ struct PoolGeom {
     int filter_h, filter_w, in_w, in_h, out_w, out_h, c_size, frames;
 };
 
-// One thread per (output node, frame); grid.y walks the output nodes.
+// One thread per (output node, V consecutive frames); grid.y walks the output nodes.  V = 4 (rows 16-byte aligned): 128-bit loads
+// and stores, and the node arithmetic (three divisions per output node) is spread over four frames.
+template <int V>
 __global__ void __launch_bounds__(256)
 k_maxpool_forward_f32(const float *__restrict__ x, float *__restrict__ y, int *__restrict__ argmax, PoolGeom g, long long fs)
 {
-    const int f = blockIdx.x * blockDim.x + threadIdx.x;
+    const int f = (blockIdx.x * blockDim.x + threadIdx.x) * V;
     if (f >= g.frames) return;
+    const bool full = f + V <= g.frames;
     for (int on = blockIdx.y; on < g.c_size * g.out_h * g.out_w; on += gridDim.y) {
         const int ox = on % g.out_w, oy = (on / g.out_w) % g.out_h, c = on / (g.out_w * g.out_h);
-        float best = -3.402823466e+38f;                           // std::numeric_limits<float>::lowest()
-        int am = 0, arg = 0;
+        float best[V];
+        int am[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) { best[k] = -3.402823466e+38f; am[k] = 0; }      // std::numeric_limits<float>::lowest()
+        int arg = 0;
         for (int fy = 0; fy < g.filter_h; ++fy) {
             const int iy = oy * g.filter_h + fy;
             if (iy >= g.in_h) break;
             for (int fx = 0; fx < g.filter_w; ++fx) {
                 const int ix = ox * g.filter_w + fx;
                 if (ix >= g.in_w) break;
-                const float v = x[(size_t)((c * g.in_h + iy) * g.in_w + ix) * fs + f];
-                if (v > best) { best = v; am = arg; }
+                const float *p = x + (size_t)((c * g.in_h + iy) * g.in_w + ix) * fs + f;
+                float v[V];
+                if (V == 4) {              // inside the row's stride even when the last frames of the group do not exist
+                    const float4 q = *reinterpret_cast<const float4 *>(p);
+                    v[0] = q.x; v[1 % V] = q.y; v[2 % V] = q.z; v[3 % V] = q.w;
+                } else {
+                    v[0] = p[0];
+                }
+#pragma unroll
+                for (int k = 0; k < V; ++k)
+                    if (v[k] > best[k]) { best[k] = v[k]; am[k] = arg; }
                 ++arg;
             }
         }
-        y[(size_t)on * fs + f] = best;
-        if (argmax) argmax[(size_t)on * fs + f] = am;
+        float *yp = y + (size_t)on * fs + f;
+        int *ap = argmax ? argmax + (size_t)on * fs + f : nullptr;
+        if (V == 4 && full) {
+            *reinterpret_cast<float4 *>(yp) = make_float4(best[0], best[1 % V], best[2 % V], best[3 % V]);
+            if (ap) *reinterpret_cast<int4 *>(ap) = make_int4(am[0], am[1 % V], am[2 % V], am[3 % V]);
+        } else {
+#pragma unroll
+            for (int k = 0; k < V; ++k)
+                if (f + k < g.frames) { yp[k] = best[k]; if (ap) ap[k] = am[k]; }
+        }
     }
 }
 
@@ -561,17 +616,29 @@ k_maxpool_forward_bit(const uint32_t *__restrict__ x, uint32_t *__restrict__ y, 
     }
 }
 
-// XBITS = false: routed by argmax; XBITS = true: the first set input bit of the window takes the gradient.
-template <bool XBITS>
+// XBITS = false: routed by argmax; XBITS = true: the first set input bit of the window takes the gradient.  V as in the forward.
+template <bool XBITS, int V>
 __global__ void __launch_bounds__(256)
 k_maxpool_backward(const void *__restrict__ sel, const float *__restrict__ dy, float *__restrict__ dx, PoolGeom g, long long sel_fs, long long fs)
 {
-    const int f = blockIdx.x * blockDim.x + threadIdx.x;
+    const int f = (blockIdx.x * blockDim.x + threadIdx.x) * V;
     if (f >= g.frames) return;
+    const bool full = f + V <= g.frames;
     for (int on = blockIdx.y; on < g.c_size * g.out_h * g.out_w; on += gridDim.y) {
         const int ox = on % g.out_w, oy = (on / g.out_w) % g.out_h, c = on / (g.out_w * g.out_h);
-        float grad = dy[(size_t)on * fs + f];
-        const int am = XBITS ? 0 : static_cast<const int *>(sel)[(size_t)on * sel_fs + f];
+        float grad[V];
+        int am[V];
+        if (V == 4) {
+            const float4 q = *reinterpret_cast<const float4 *>(dy + (size_t)on * fs + f);
+            grad[0] = q.x; grad[1 % V] = q.y; grad[2 % V] = q.z; grad[3 % V] = q.w;
+            if (!XBITS) {
+                const int4 a = *reinterpret_cast<const int4 *>(static_cast<const int *>(sel) + (size_t)on * sel_fs + f);
+                am[0] = a.x; am[1 % V] = a.y; am[2 % V] = a.z; am[3 % V] = a.w;
+            }
+        } else {
+            grad[0] = dy[(size_t)on * fs + f];
+            am[0] = XBITS ? 0 : static_cast<const int *>(sel)[(size_t)on * sel_fs + f];
+        }
         int arg = 0;
         for (int fy = 0; fy < g.filter_h; ++fy) {
             const int iy = oy * g.filter_h + fy;
@@ -580,13 +647,27 @@ k_maxpool_backward(const void *__restrict__ sel, const float *__restrict__ dy, f
                 const int ix = ox * g.filter_w + fx;
                 if (ix >= g.in_w) break;
                 const size_t in = (size_t)((c * g.in_h + iy) * g.in_w + ix);
+                float out[V];
                 if (XBITS) {
-                    const bool bit = (static_cast<const uint32_t *>(sel)[in * sel_fs + (f >> 5)] >> (f & 31)) & 1u;
-                    dx[in * fs + f] = bit ? grad : 0.0f;
-                    if (bit) grad = 0.0f;
+                    const uint32_t word = static_cast<const uint32_t *>(sel)[in * sel_fs + (f >> 5)];      // V frames from a multiple of V: one word
+#pragma unroll
+                    for (int k = 0; k < V; ++k) {
+                        const bool bit = (word >> ((f + k) & 31)) & 1u;
+                        out[k] = bit ? grad[k] : 0.0f;
+                        if (bit) grad[k] = 0.0f;
+                    }
                 } else {
-                    dx[in * fs + f] = (arg == am) ? grad : 0.0f;
+#pragma unroll
+                    for (int k = 0; k < V; ++k) out[k] = (arg == am[k]) ? grad[k] : 0.0f;
                     ++arg;
+                }
+                float *dp = dx + in * fs + f;
+                if (V == 4 && full) {
+                    *reinterpret_cast<float4 *>(dp) = make_float4(out[0], out[1 % V], out[2 % V], out[3 % V]);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < V; ++k)
+                        if (f + k < g.frames) dp[k] = out[k];
                 }
             }
         }
@@ -713,9 +794,10 @@ extern "C" int bbcu_bit_Im2Col_Forward(const int *dev_x_buf, int *dev_y_buf, int
     uint32_t *y = reinterpret_cast<uint32_t *>(dev_y_buf);
     if (P % 32 == 0) {
         const int groups = (int)(P / 32), g_tiles = (groups + 31) / 32, in_words = (input_frame_size + 31) / 32;
-        const long long blocks = out_nodes * in_words * g_tiles;
+        const int w_tiles = (in_words + kBitColumns - 1) / kBitColumns;
+        const long long blocks = out_nodes * w_tiles * g_tiles;
         BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
-        k_im2col_forward_bit<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(x, y, g, groups, g_tiles, in_words);
+        k_im2col_forward_bit<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(x, y, g, groups, g_tiles, in_words, w_tiles);
     } else {
         const long long out_words = ((long long)input_frame_size * P + 31) / 32;
         const long long blocks = (out_words * out_nodes + 255) / 256;
@@ -775,10 +857,10 @@ static int col2im_f32(const float *src, float *dst, int w, int h, int c, int col
     int rc = check_col2im(src, dst, w, h, c, col_fs, out_frames, img_fs, 1);
     if (rc) return rc;
     if (c == 0 || out_frames == 0) return BBCU_OK;
-    const int hw = w * h, xy_tiles = (hw + 31) / 32, f_tiles = (out_frames + 31) / 32;
+    const int hw = w * h, xy_tiles = (hw + kCol2ImTile - 1) / kCol2ImTile, f_tiles = (out_frames + kCol2ImTile - 1) / kCol2ImTile;
     const long long blocks = (long long)c * xy_tiles * f_tiles;
     BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
-    k_col2im_f32<FORWARD><<<(unsigned)blocks, dim3(32, 8), 0, st>>>(src, dst, hw, out_frames, col_fs, img_fs, xy_tiles, f_tiles);
+    k_col2im_f32<FORWARD><<<(unsigned)blocks, 256, 0, st>>>(src, dst, hw, out_frames, col_fs, img_fs, xy_tiles, f_tiles);
     return launch_status();
 }
 
@@ -831,8 +913,12 @@ extern "C" int bbcu_fp32_MaxPooling_Forward(const float *dev_x_buf, float *dev_y
     BB200_REQUIRE(frame_stride >= frame_size, BBCU_ERR_BAD_STRIDE);
     if (c_size == 0 || frame_size == 0) return BBCU_OK;
     const PoolGeom g = make_pool(filter_h_size, filter_w_size, input_w_size, input_h_size, output_w_size, output_h_size, c_size, frame_size);
-    dim3 grid((frame_size + 255) / 256, grid_y((long long)c_size * output_h_size * output_w_size));
-    k_maxpool_forward_f32<<<grid, 256, 0, as_stream(stream)>>>(dev_x_buf, dev_y_buf, dev_argmax_buf, g, frame_stride);
+    const bool vec = frame_stride % 4 == 0 && ((reinterpret_cast<uintptr_t>(dev_x_buf) | reinterpret_cast<uintptr_t>(dev_y_buf) |
+                                               reinterpret_cast<uintptr_t>(dev_argmax_buf)) & 15) == 0;
+    const int per = vec ? 4 : 1;
+    dim3 grid(((frame_size + per - 1) / per + 255) / 256, grid_y((long long)c_size * output_h_size * output_w_size));
+    if (vec) k_maxpool_forward_f32<4><<<grid, 256, 0, as_stream(stream)>>>(dev_x_buf, dev_y_buf, dev_argmax_buf, g, frame_stride);
+    else     k_maxpool_forward_f32<1><<<grid, 256, 0, as_stream(stream)>>>(dev_x_buf, dev_y_buf, dev_argmax_buf, g, frame_stride);
     return launch_status();
 }
 
@@ -862,8 +948,12 @@ extern "C" int bbcu_fp32_MaxPooling_Backward(const int *dev_argmax_buf, const fl
     BB200_REQUIRE(frame_stride >= frame_size, BBCU_ERR_BAD_STRIDE);
     if (c_size == 0 || frame_size == 0) return BBCU_OK;
     const PoolGeom g = make_pool(filter_h_size, filter_w_size, input_w_size, input_h_size, output_w_size, output_h_size, c_size, frame_size);
-    dim3 grid((frame_size + 255) / 256, grid_y((long long)c_size * output_h_size * output_w_size));
-    k_maxpool_backward<false><<<grid, 256, 0, as_stream(stream)>>>(dev_argmax_buf, dev_dy_buf, dev_dx_buf, g, frame_stride, frame_stride);
+    const bool vec = frame_stride % 4 == 0 && ((reinterpret_cast<uintptr_t>(dev_argmax_buf) | reinterpret_cast<uintptr_t>(dev_dy_buf) |
+                                               reinterpret_cast<uintptr_t>(dev_dx_buf)) & 15) == 0;
+    const int per = vec ? 4 : 1;
+    dim3 grid(((frame_size + per - 1) / per + 255) / 256, grid_y((long long)c_size * output_h_size * output_w_size));
+    if (vec) k_maxpool_backward<false, 4><<<grid, 256, 0, as_stream(stream)>>>(dev_argmax_buf, dev_dy_buf, dev_dx_buf, g, frame_stride, frame_stride);
+    else     k_maxpool_backward<false, 1><<<grid, 256, 0, as_stream(stream)>>>(dev_argmax_buf, dev_dy_buf, dev_dx_buf, g, frame_stride, frame_stride);
     return launch_status();
 }
 
@@ -878,7 +968,10 @@ extern "C" int bbcu_bit_fp32_MaxPooling_Backward(const int *dev_x_buf, const flo
     BB200_REQUIRE(backward_frame_stride >= frame_size && (long long)forward_frame_stride * 32 >= frame_size, BBCU_ERR_BAD_STRIDE);
     if (c_size == 0 || frame_size == 0) return BBCU_OK;
     const PoolGeom g = make_pool(filter_h_size, filter_w_size, input_w_size, input_h_size, output_w_size, output_h_size, c_size, frame_size);
-    dim3 grid((frame_size + 255) / 256, grid_y((long long)c_size * output_h_size * output_w_size));
-    k_maxpool_backward<true><<<grid, 256, 0, as_stream(stream)>>>(dev_x_buf, dev_dy_buf, dev_dx_buf, g, forward_frame_stride, backward_frame_stride);
+    const bool vec = backward_frame_stride % 4 == 0 && ((reinterpret_cast<uintptr_t>(dev_dy_buf) | reinterpret_cast<uintptr_t>(dev_dx_buf)) & 15) == 0;
+    const int per = vec ? 4 : 1;
+    dim3 grid(((frame_size + per - 1) / per + 255) / 256, grid_y((long long)c_size * output_h_size * output_w_size));
+    if (vec) k_maxpool_backward<true, 4><<<grid, 256, 0, as_stream(stream)>>>(dev_x_buf, dev_dy_buf, dev_dx_buf, g, forward_frame_stride, backward_frame_stride);
+    else     k_maxpool_backward<true, 1><<<grid, 256, 0, as_stream(stream)>>>(dev_x_buf, dev_dy_buf, dev_dx_buf, g, forward_frame_stride, backward_frame_stride);
     return launch_status();
 }
