@@ -563,6 +563,7 @@ def operators_section(torch, ops, steps):
     img = torch.rand((c * hw * hw, B), device=dev, generator=g)
     cols = ops.im2col_forward(img, B, c, hw, hw, 3, 3, padding="same")
     colsb_in = torch.randint(-2**31, 2**31 - 1, (c * hw * hw, ops.bit_stride(B2)), device=dev, generator=g, dtype=torch.int32)
+    colsb_out = torch.empty((c * 9, ops.bit_stride(B2 * hw * hw)), device=dev, dtype=torch.int32)
     img2 = torch.rand((c * hw * hw, B2), device=dev, generator=g)
     z = torch.rand((c, B2 * hw * hw), device=dev, generator=g)
     pooled, am = ops.maxpool_forward(img2, B2, c, hw, hw, 2, 2)
@@ -590,7 +591,7 @@ def operators_section(torch, ops, steps):
         "sbn_backward": (lambda: ops.stochastic_bn_backward(xf, dy, st["smean"], st["srstd"], F), nf, 20.0, 12.0),
         "adam_update": (lambda: adam.update(), 8.0 * 65536 * 64, 28.0, 12.0),
         "im2col_forward_fp32": (lambda: ops.im2col_forward(img, B, c, hw, hw, 3, 3, padding="same"), px * 9, 4.0 + 4.0 / 9, 0.0),
-        "im2col_forward_bit": (lambda: ops.im2col_forward(colsb_in, B2, c, hw, hw, 3, 3, padding="same"), px2 * 9, (1 + 1.0 / 9) / 8, 0.0),
+        "im2col_forward_bit": (lambda: ops.im2col_forward(colsb_in, B2, c, hw, hw, 3, 3, padding="same", y=colsb_out), px2 * 9, (1 + 1.0 / 9) / 8, 0.0),
         "im2col_backward_fp32": (lambda: ops.im2col_backward(cols, B, c, hw, hw, 3, 3, padding="same"), px * 9, 4.0 + 4.0 / 9, 1.0),
         "col2im_forward_fp32": (lambda: ops.col2im_forward(z, c, hw, hw, B2), px2, 8.0, 0.0),
         "col2im_backward_fp32": (lambda: ops.col2im_backward(img2, c, hw, hw, B2), px2, 8.0, 0.0),

@@ -31,8 +31,8 @@ const DeviceInfo &device_info();
 // later calls on the same stream and is released by bbcu_LocalHeap_GarbageCollect().  Stream order
 // makes back-to-back calls on one stream safe; different streams get different blocks.  A stream has
 // kScratchSlots independent blocks, for callers whose scratch is alive at the same time (slot 0: batch-norm
-// sums, slot 1: per-node coefficient tables of the pipelined forward).
-constexpr int kScratchSlots = 2;
+// sums, slot 1: per-node coefficient / pattern tables of the LUT operators, slot 2: the piece table of the bit Im2Col).
+constexpr int kScratchSlots = 3;
 void *stream_scratch(cudaStream_t stream, size_t bytes, int slot = 0);
 
 // Pass 1 of the DifferentiableLut6 training forward (raw LUT values into y, fp64 sums per node); with may_allocate = false

@@ -391,8 +391,6 @@ struct BitTranspose {
     }
 };
 
-__device__ __forceinline__ uint32_t warp_bit_transpose(uint32_t v, int lane) { return BitTranspose(lane)(v); }
-
 // --------------------------------------------------------------------------------------------- Im2Col bit
 // P % 32 == 0: an output word is 32 consecutive pixels of one input frame.  A warp takes one group of 32 pixels (lane k owns pixel
 // k and works out its source node once) and walks W input word columns (32 input frames each): lane k reads the word of its pixel,
@@ -429,6 +427,131 @@ k_im2col_forward_bit(const uint32_t *__restrict__ x, uint32_t *__restrict__ y, I
         const int wl = r >> 5, j = r & 31;
         const int fi = (w0 + wl) * 32 + j;
         if (fi < g.in_frames && lane < gn) y[(size_t)on * g.out_fs + (size_t)fi * groups + g0 + lane] = tile[wl][j][lane];
+    }
+}
+
+// Bit Im2Col for any geometry, by words.  The 32 input frames of one word column become 32 bit vectors over the channel's pixels
+// (one 32 x 32 bit transpose per 32 pixels -- per input tile, not per filter tap).  Those 32 frames are exactly P consecutive
+// output words of every tap, and an output word is the OR of a few masked 32-bit windows of such vectors: inside one image row
+// the source pixels of consecutive output pixels are consecutive, so a window at bit offset (source pixel - output bit) yields all
+// of them at once, and border pixels with their own offsets add a window each.  The windows of a word depend on the tap and on the
+// word's position modulo the period (P / gcd(P, 32) words = 32 / gcd(P, 32) frames) only, so a small table built once per launch
+// (k_im2col_bit_pieces) holds, per (tap, word of the period), up to kPieces entries {frame of the period, offset, mask}.
+// A word that needs more windows than that (tiny images, strides above one) is marked and gathered bit by bit.
+constexpr int kPieces = 12;
+constexpr int kPieceBias = 64;                  // offsets are stored biased: they start at -31
+constexpr unsigned kPieceOverflow = 0xffffffffu;
+
+// One warp per (tap, word of the period); lane b owns output bit b, and the lanes whose (frame, offset) keys agree form one window.
+__global__ void __launch_bounds__(256)
+k_im2col_bit_pieces(Im2ColGeom g, int period_words, int2 *__restrict__ pieces)
+{
+    const int lane = threadIdx.x & 31;
+    const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int taps = g.filter_h * g.filter_w;
+    if (e >= taps * period_words) return;                          // warp-uniform
+    const int tap = e / period_words, wp = e - tap * period_words;
+    const int fy = tap / g.filter_w, fx = tap - fy * g.filter_w;
+    const int P = g.out_h * g.out_w;
+    const int o = 32 * wp + lane;
+    const int dj = o / P, p = o - dj * P;
+    const int oy = p / g.out_w, ox = p - oy * g.out_w;
+    const int pix = im2col_source_pixel(g, fy, fx, oy, ox);        // -1: the border value of bit frames, 0
+    const int key = pix >= 0 ? ((dj << 24) | (pix - lane + kPieceBias)) : -1;
+    const unsigned same = __match_any_sync(0xffffffffu, key);      // the lanes of this lane's window
+    const bool leader = pix >= 0 && (__ffs(same) - 1) == lane;
+    const unsigned leaders = __ballot_sync(0xffffffffu, leader);
+    const int n = __popc(leaders);
+    int2 *out = pieces + (size_t)e * kPieces;
+    if (n > kPieces) {
+        if (lane == 0) out[0] = make_int2((int)kPieceOverflow, 0);
+        return;
+    }
+    if (leader) out[__popc(leaders & ((1u << lane) - 1u))] = make_int2(key, (int)same);
+    if (lane >= n && lane < kPieces) out[lane] = make_int2(0, 0);
+}
+
+__global__ void __launch_bounds__(256)
+k_im2col_forward_bit_words(const uint32_t *__restrict__ x, uint32_t *__restrict__ y, Im2ColGeom g, const int2 *__restrict__ pieces, int period_words,
+                           int period_frames, int qw, int in_words, long long out_words)
+{
+    extern __shared__ uint32_t bit_rows[];                        // [32 frames][qw + 2]: one zero word before and after every row
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wi = blockIdx.x % in_words, c = blockIdx.x / in_words;
+    const int Q = g.in_h * g.in_w, P = g.out_h * g.out_w, pitch = qw + 2;
+    const int taps = g.filter_h * g.filter_w;
+    const BitTranspose transpose(lane);
+    const bool frame_ok = wi * 32 + lane < g.in_frames;            // frames past the end read as zeros
+    for (int k = warp; k < qw; k += 8) {
+        const int pix = 32 * k + lane;
+        const uint32_t v = pix < Q ? x[((size_t)c * Q + pix) * g.in_fs + wi] : 0u;
+        const uint32_t t = transpose(v);
+        bit_rows[lane * pitch + k + 1] = frame_ok ? t : 0u;
+    }
+    if (threadIdx.x < 64) bit_rows[(threadIdx.x >> 1) * pitch + ((threadIdx.x & 1) ? qw + 1 : 0)] = 0u;
+    __syncthreads();
+
+    // A lane keeps the windows of its word of the period (the first four in registers) and applies them to every period of the
+    // block's 32 frames; the warps share the periods.
+    const int periods = P / period_words;                          // = gcd(P, 32)
+    const long long w_base = (long long)wi * P;
+    const int w_limit = (int)min((long long)P, out_words - w_base);        // words of this block that exist (the last frames may not)
+    for (int tap = 0; tap < taps; ++tap) {
+        uint32_t *yrow = y + (size_t)(c * taps + tap) * g.out_fs + w_base;
+        for (int wp = lane; wp < period_words; wp += 32) {
+            const int2 *pc = pieces + ((size_t)tap * period_words + wp) * kPieces;
+            int2 e[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) e[k] = __ldg(pc + k);
+            if ((unsigned)e[0].x == kPieceOverflow) {
+                const int fy = tap / g.filter_w, fx = tap - fy * g.filter_w;
+                for (int np = warp; np < periods; np += 8) {
+                    const int w = np * period_words + wp;
+                    if (w >= w_limit) break;
+                    const uint32_t *rows = bit_rows + np * period_frames * pitch;
+                    uint32_t word = 0u;
+                    for (int b = 0; b < 32; ++b) {
+                        const int o = 32 * wp + b;
+                        const int dj = o / P, p = o - dj * P;
+                        const int oy = p / g.out_w, ox = p - oy * g.out_w;
+                        const int pix = im2col_source_pixel(g, fy, fx, oy, ox);
+                        if (pix >= 0) word |= ((rows[dj * pitch + 1 + (pix >> 5)] >> (pix & 31)) & 1u) << b;
+                    }
+                    yrow[w] = word;
+                }
+                continue;
+            }
+            // offsets inside the padded rows: word index and shift of every window; an unused window reads word 0 under an empty mask
+            int at[4], sh[4];
+            uint32_t mk[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int pos = (e[k].x & 0xffffff) - kPieceBias + 32;
+                const bool used = e[k].y != 0;
+                at[k] = used ? (e[k].x >> 24) * pitch + (pos >> 5) : 0;
+                sh[k] = used ? (pos & 31) : 0;
+                mk[k] = (uint32_t)e[k].y;
+            }
+            const bool more = e[3].y != 0 && __ldg(pc + 4).y != 0;
+            for (int np = warp; np < periods; np += 8) {
+                const int w = np * period_words + wp;
+                if (w >= w_limit) break;
+                const uint32_t *rows = bit_rows + np * period_frames * pitch;
+                uint32_t word = 0u;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) word |= __funnelshift_r(rows[at[k]], rows[at[k] + 1], sh[k]) & mk[k];
+                if (more) {
+                    for (int k = 4; k < kPieces; ++k) {
+                        const int2 f = __ldg(pc + k);
+                        if (f.y == 0) break;
+                        const int pos = (f.x & 0xffffff) - kPieceBias + 32;
+                        const uint32_t *r = rows + (f.x >> 24) * pitch + (pos >> 5);
+                        word |= __funnelshift_r(r[0], r[1], pos & 31) & (uint32_t)f.y;
+                    }
+                }
+                yrow[w] = word;
+            }
+        }
     }
 }
 
@@ -499,12 +622,13 @@ k_col2im_f32(const float *__restrict__ src, float *__restrict__ dst, int hw, int
     }
 }
 
-// hw % 32 == 0: warp = (channel, output word wo, pixel group); lane j reads the input word of output frame 32 wo + j that
-// holds the group's 32 pixels, the transpose gives lane k the output word of pixel k.  A block takes 32 consecutive output
-// words of the same pixel group, so every pixel's row receives one contiguous run.
+// Warp = (channel, output word wo, group of 32 pixels): lane j takes, from the bit vector of output frame 32 wo + j (hw bits,
+// starting at bit (32 wo + j) * hw of the channel's row, on no particular word boundary), the 32-bit window of the group's pixels;
+// the transpose gives lane k the output word of pixel k.  A block takes 32 consecutive output words of the same pixel group, so
+// every pixel's row receives one contiguous run.
 __global__ void __launch_bounds__(256)
 k_col2im_forward_bit(const uint32_t *__restrict__ x, uint32_t *__restrict__ y, int hw, int out_frames, long long in_fs, long long out_fs,
-                     int groups, int w_tiles, int out_words)
+                     int groups, int w_tiles, int out_words, long long in_words)
 {
     __shared__ uint32_t tile[32][33];                             // [pixel k][output word]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -513,32 +637,24 @@ k_col2im_forward_bit(const uint32_t *__restrict__ x, uint32_t *__restrict__ y, i
     const int gp = b % groups; b /= groups;
     const int c = b;
     const int w0 = wt * 32, wn = min(32, out_words - w0);
+    const uint32_t *xr = x + (size_t)c * in_fs;
+    const BitTranspose transpose(lane);
     for (int wl = warp; wl < wn; wl += 8) {
         const long long fo = (long long)(w0 + wl) * 32 + lane;
-        const uint32_t row = fo < out_frames ? x[(size_t)c * in_fs + (size_t)fo * groups + gp] : 0u;
-        tile[lane][wl] = warp_bit_transpose(row, lane);
+        uint32_t row = 0u;
+        if (fo < out_frames) {
+            const long long pos = fo * hw + 32 * gp;
+            const long long wi = pos >> 5;
+            const int sh = (int)(pos & 31);
+            const uint32_t lo = xr[wi];
+            const uint32_t hi = (sh != 0 && wi + 1 < in_words) ? xr[wi + 1] : 0u;       // (bits past the last frame belong to no pixel)
+            row = __funnelshift_r(lo, hi, sh);
+        }
+        tile[lane][wl] = transpose(row);
     }
     __syncthreads();
     for (int k = warp; k < 32; k += 8)
-        if (lane < wn) y[(size_t)(c * hw + gp * 32 + k) * out_fs + w0 + lane] = tile[k][lane];
-}
-
-__global__ void __launch_bounds__(256)
-k_col2im_forward_bit_any(const uint32_t *__restrict__ x, uint32_t *__restrict__ y, int hw, int out_frames, long long in_fs, long long out_fs,
-                         int out_words, int out_nodes)
-{
-    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= (long long)out_words * out_nodes) return;
-    const int on = (int)(t / out_words), wo = (int)(t % out_words);
-    const int c = on / hw, xy = on % hw;
-    uint32_t word = 0;
-    for (int k = 0; k < 32; ++k) {
-        const long long fo = (long long)wo * 32 + k;
-        if (fo >= out_frames) break;
-        const long long fi = fo * hw + xy;
-        word |= ((x[(size_t)c * in_fs + (fi >> 5)] >> (fi & 31)) & 1u) << k;
-    }
-    y[(size_t)on * out_fs + wo] = word;
+        if (lane < wn && gp * 32 + k < hw) y[(size_t)(c * hw + gp * 32 + k) * out_fs + w0 + lane] = tile[k][lane];
 }
 
 // --------------------------------------------------------------------------------------------- MaxPooling
@@ -792,6 +908,29 @@ extern "C" int bbcu_bit_Im2Col_Forward(const int *dev_x_buf, int *dev_y_buf, int
                                    input_c_size, output_w_size, output_h_size, output_frame_stride, filter_w_size, filter_h_size, border_mode);
     const uint32_t *x = reinterpret_cast<const uint32_t *>(dev_x_buf);
     uint32_t *y = reinterpret_cast<uint32_t *>(dev_y_buf);
+    {
+        // by words: the piece table lives in the stream's scratch; images whose 32 bit rows do not fit shared memory, or a heap
+        // that declines the table, take the kernels below
+        int gcd = 32;
+        while (P % gcd != 0) gcd >>= 1;
+        const int period_words = (int)(P / gcd), period_frames = 32 / gcd;
+        const int taps = filter_h_size * filter_w_size, in_words = (input_frame_size + 31) / 32;
+        const int qw = (input_w_size * input_h_size + 31) / 32;
+        const size_t smem = (size_t)32 * (qw + 2) * 4, table_bytes = (size_t)taps * period_words * kPieces * sizeof(int2);
+        const long long blocks = (long long)input_c_size * in_words;
+        if (smem <= 48 * 1024 && table_bytes <= (64u << 20) && blocks < (1LL << 31)) {
+            int2 *pieces = static_cast<int2 *>(stream_scratch(as_stream(stream), table_bytes, 2));
+            if (pieces != nullptr) {
+                const int entries = taps * period_words;
+                k_im2col_bit_pieces<<<(entries + 7) / 8, 256, 0, as_stream(stream)>>>(g, period_words, pieces);
+                BB200_CUDA(cudaPeekAtLastError());
+                const long long out_words = ((long long)input_frame_size * P + 31) / 32;
+                k_im2col_forward_bit_words<<<(unsigned)blocks, 256, smem, as_stream(stream)>>>(x, y, g, pieces, period_words, period_frames, qw, in_words,
+                                                                                              out_words);
+                return launch_status();
+            }
+        }
+    }
     if (P % 32 == 0) {
         const int groups = (int)(P / 32), g_tiles = (groups + 31) / 32, in_words = (input_frame_size + 31) / 32;
         const int w_tiles = (in_words + kBitColumns - 1) / kBitColumns;
@@ -887,19 +1026,12 @@ extern "C" int bbcu_bit_Col2Im_Forward(const int *dev_x_buf, int *dev_y_buf, int
     const uint32_t *x = reinterpret_cast<const uint32_t *>(dev_x_buf);
     uint32_t *y = reinterpret_cast<uint32_t *>(dev_y_buf);
     const int hw = w_size * h_size, out_words = (output_frame_size + 31) / 32;
-    if (hw % 32 == 0) {
-        const int groups = hw / 32, w_tiles = (out_words + 31) / 32;
-        const long long blocks = (long long)c_size * groups * w_tiles;
-        BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
-        k_col2im_forward_bit<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(x, y, hw, output_frame_size, input_frame_stride, output_frame_stride,
-                                                                             groups, w_tiles, out_words);
-    } else {
-        const long long out_nodes = (long long)c_size * hw;
-        const long long blocks = (out_nodes * out_words + 255) / 256;
-        BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
-        k_col2im_forward_bit_any<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(x, y, hw, output_frame_size, input_frame_stride,
-                                                                                 output_frame_stride, out_words, (int)out_nodes);
-    }
+    const int groups = (hw + 31) / 32, w_tiles = (out_words + 31) / 32;
+    const long long in_words = ((long long)output_frame_size * hw + 31) / 32;
+    const long long blocks = (long long)c_size * groups * w_tiles;
+    BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
+    k_col2im_forward_bit<<<(unsigned)blocks, 256, 0, as_stream(stream)>>>(x, y, hw, output_frame_size, input_frame_stride, output_frame_stride, groups,
+                                                                         w_tiles, out_words, in_words);
     return launch_status();
 }
 

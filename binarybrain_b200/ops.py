@@ -282,10 +282,15 @@ def im2col_geometry(h, w, fh, fw, y_stride=1, x_stride=1, padding="valid"):
     raise ValueError(f"unknown padding {padding!r}")
 
 
-def im2col_forward(x, frames, c, h, w, fh, fw, y_stride=1, x_stride=1, padding="valid", border_mode="reflect_101", border_value=0.0):
-    """bb::ConvolutionIm2Col forward: [c*h*w, frames] (fp32, or int32 bit words) -> [c*fh*fw, frames*oh*ow]."""
+def im2col_forward(x, frames, c, h, w, fh, fw, y_stride=1, x_stride=1, padding="valid", border_mode="reflect_101", border_value=0.0, y=None):
+    """bb::ConvolutionIm2Col forward: [c*h*w, frames] (fp32, or int32 bit words) -> [c*fh*fw, frames*oh*ow].  `y`: an output buffer of
+    that shape to write into (every word up to the last frame is written; nothing needs clearing)."""
     oh, ow, yo, xo = im2col_geometry(h, w, fh, fw, y_stride, x_stride, padding)
     of = frames * oh * ow
+    if y is not None:
+        abi.call("bbcu_bit_Im2Col_Forward" if x.dtype == torch.int32 else "bbcu_fp32_Im2Col_Forward", _p(x), _p(y), x_stride, y_stride, xo, yo, frames,
+                 x.shape[1], w, h, c, ow, oh, y.shape[1], fw, fh, BORDER_MODES[border_mode], *(() if x.dtype == torch.int32 else (border_value,)), _stream())
+        return y
     if x.dtype == torch.int32:
         y = torch.zeros((c * fh * fw, bit_stride(of)), dtype=torch.int32, device=x.device)
         abi.call("bbcu_bit_Im2Col_Forward", _p(x), _p(y), x_stride, y_stride, xo, yo, frames, x.shape[1], w, h, c, ow, oh, y.shape[1], fw, fh,

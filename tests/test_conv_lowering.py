@@ -97,24 +97,47 @@ def test_conv_lowering_gpu_against_golden(golden):
     (3, 33, 31, 3, 3, 2, 2, "same", 40),        # strides, odd sizes
     (2, 30, 20, 3, 2, 2, 1, "valid", 9),
     (1, 3, 600, 3, 3, 1, 1, "same", 8),         # a row too wide for a band in shared memory: the tile kernels
+    (2, 28, 28, 3, 3, 1, 1, "same", 70),        # 784 pixels: bit words straddle frames (period of 49 words = 2 frames)
+    (2, 28, 28, 5, 5, 1, 1, "valid", 33),
+    (1, 27, 27, 3, 3, 1, 1, "same", 40),        # odd pixel count: the period is all 32 frames
+    (1, 5, 4, 3, 3, 1, 1, "same", 40),          # tiny image: more windows per bit word than the table holds
 ])
-def test_im2col_fp32_bands_against_oracle(c, h, w, fh, fw, ys, xs, pad, F):
+def test_im2col_bands_and_bit_words_against_oracle(c, h, w, fh, fw, ys, xs, pad, F):
     """Im2Col fp32 forward (every border mode) and backward where the image splits into several bands, and where it does not fit
-    a band at all; the forward moves values (exact), the backward adds at most filter_h * filter_w of them in the reference's order."""
+    a band at all; the forward moves values (exact), the backward adds at most filter_h * filter_w of them in the reference's order.
+    Bit frames through the word-wise kernel on the same geometries (exact)."""
     import torch
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     from binarybrain_b200 import ops
-    from gpu_util import dev_fp32, host_fp32
+    from gpu_util import dev_fp32, dev_bits, host_fp32, host_bits
     oh, ow, _, _ = port.im2col_geometry(h, w, fh, fw, ys, xs, pad)
     x = det_uniform((c * h * w, F), 410)
     xd = dev_fp32(x)
+    xb = pack_bits(x > 0.5)
+    xbd = dev_bits(xb, F)
     for border in BORDERS:
         y = ops.im2col_forward(xd, F, c, h, w, fh, fw, ys, xs, pad, border)
         assert np.array_equal(host_fp32(y, F * oh * ow), port.im2col_forward(x, c, h, w, fh, fw, ys, xs, pad, border)), border
+        yb = ops.im2col_forward(xbd, F, c, h, w, fh, fw, ys, xs, pad, border)
+        assert np.array_equal(host_bits(yb, F * oh * ow), port.im2col_forward(xb, c, h, w, fh, fw, ys, xs, pad, border, frames=F)), border
     dy = det_uniform((c * fh * fw, F * oh * ow), 411)
     dx = ops.im2col_backward(dev_fp32(dy), F, c, h, w, fh, fw, ys, xs, pad)
     assert np.array_equal(host_fp32(dx, F), port.im2col_backward(dy, c, h, w, fh, fw, ys, xs, pad))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("c,h,w,Fo", [(3, 28, 28, 70), (2, 27, 27, 40), (2, 7, 5, 1100), (1, 32, 32, 33)])
+def test_col2im_bit_any_pixel_count_against_oracle(c, h, w, Fo):
+    """Col2Im on bit frames: the bit vector of an output frame (h * w bits) starts on no particular word boundary."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from binarybrain_b200 import ops
+    from gpu_util import dev_bits, host_bits
+    xb = pack_bits(det_uniform((c, Fo * h * w), 420) > 0.5)
+    yb = ops.col2im_forward(dev_bits(xb, Fo * h * w), c, h, w, Fo)
+    assert np.array_equal(host_bits(yb, Fo), port.col2im_forward(xb, c, h, w, Fo))
 
 
 @pytest.mark.gpu

@@ -449,6 +449,34 @@ def test_backward_uses_the_callers_scratch_and_falls_back_for_unaligned_rows(ops
 
 
 
+def test_binary_mode_takes_the_tree_kernels_when_the_pattern_scratch_is_refused(ops):
+    """Binary mode on fp32 frames normally goes through per-pattern tables that need one byte of scratch per node-frame; when the
+    device heap refuses that block the operators must decline to the per-frame tree kernels and give the same results.  The heap's
+    byte limit is set to what is already allocated (the small per-stream scratch of a plain-mode call), so nothing on the GPU runs
+    out of memory."""
+    from gpu_util import dev_fp32, dev, wiring
+    rng = np.random.default_rng(23)
+    I, O, F = 48, 64, 2048
+    idx = wiring(rng, I, O)
+    W = np.clip(rng.normal(0.5, 0.25, (O, 64)), 0, 1).astype(np.float32)
+    x, dy = rng.random((I, F), dtype=np.float32), rng.random((O, F), dtype=np.float32)
+    rm0, rv0 = np.zeros(O, np.float32), np.ones(O, np.float32)
+    L = ops.abi.lib()
+    torch.cuda.synchronize()
+    L.bbcu_LocalHeap_GarbageCollect()                                # earlier tests' scratch (possibly large enough already) goes back
+    ops.differentiable_lut6_forward_training(dev_fp32(x), dev(idx), dev(W), dev(rm0.copy()), dev(rv0.copy()), F, binary=False)
+    torch.cuda.synchronize()
+    allocated = L.bbcu_LocalHeap_GetAllocatedSize()
+    assert allocated > 0
+    L.bbcu_LocalHeap_SetByteLimit(allocated)
+    try:
+        for lut_binarize in (0, 1):
+            _dl6_fp32_check(ops, x, idx, W, dy, rm0, rv0, dict(binary=1, lut_binarize=lut_binarize))
+        assert L.bbcu_LocalHeap_GetAllocatedSize() == allocated      # nothing grew
+    finally:
+        L.bbcu_LocalHeap_SetByteLimit(0)
+
+
 def test_determinism_and_dw_accumulation(ops):
     from gpu_util import dev_fp32, dev, wiring
     rng = np.random.default_rng(3)
