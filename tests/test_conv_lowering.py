@@ -101,6 +101,8 @@ def test_conv_lowering_gpu_against_golden(golden):
     (2, 28, 28, 5, 5, 1, 1, "valid", 33),
     (1, 27, 27, 3, 3, 1, 1, "same", 40),        # odd pixel count: the period is all 32 frames
     (1, 5, 4, 3, 3, 1, 1, "same", 40),          # tiny image: more windows per bit word than the table holds
+    (1, 112, 112, 3, 3, 1, 1, "same", 33),      # 32 bit rows of the image exceed shared memory: the per-tap transpose kernel ...
+    (1, 113, 111, 3, 3, 1, 1, "same", 33),      # ... and, for a pixel count that is no multiple of 32, the per-bit gather
 ])
 def test_im2col_bands_and_bit_words_against_oracle(c, h, w, fh, fw, ys, xs, pad, F):
     """Im2Col fp32 forward (every border mode) and backward where the image splits into several bands, and where it does not fit
