@@ -491,12 +491,14 @@ k_im2col_forward_bit_words(const uint32_t *__restrict__ x, uint32_t *__restrict_
     if (threadIdx.x < 64) bit_rows[(threadIdx.x >> 1) * pitch + ((threadIdx.x & 1) ? qw + 1 : 0)] = 0u;
     __syncthreads();
 
-    // A lane keeps the windows of its word of the period (the first four in registers) and applies them to every period of the
-    // block's 32 frames; the warps share the periods.
+    // A lane keeps the windows of its word of the period (the first four in registers) and applies them to a run of up to eight
+    // periods of the block's 32 frames; the warps share the (tap, run) units.
     const int periods = P / period_words;                          // = gcd(P, 32)
     const long long w_base = (long long)wi * P;
     const int w_limit = (int)min((long long)P, out_words - w_base);        // words of this block that exist (the last frames may not)
-    for (int tap = 0; tap < taps; ++tap) {
+    const int run = min(8, periods), runs = (periods + run - 1) / run;
+    for (int unit = warp; unit < taps * runs; unit += 8) {
+        const int tap = unit / runs, np0 = (unit - tap * runs) * run, np1 = min(periods, np0 + run);
         uint32_t *yrow = y + (size_t)(c * taps + tap) * g.out_fs + w_base;
         for (int wp = lane; wp < period_words; wp += 32) {
             const int2 *pc = pieces + ((size_t)tap * period_words + wp) * kPieces;
@@ -505,7 +507,7 @@ k_im2col_forward_bit_words(const uint32_t *__restrict__ x, uint32_t *__restrict_
             for (int k = 0; k < 4; ++k) e[k] = __ldg(pc + k);
             if ((unsigned)e[0].x == kPieceOverflow) {
                 const int fy = tap / g.filter_w, fx = tap - fy * g.filter_w;
-                for (int np = warp; np < periods; np += 8) {
+                for (int np = np0; np < np1; ++np) {
                     const int w = np * period_words + wp;
                     if (w >= w_limit) break;
                     const uint32_t *rows = bit_rows + np * period_frames * pitch;
@@ -533,7 +535,7 @@ k_im2col_forward_bit_words(const uint32_t *__restrict__ x, uint32_t *__restrict_
                 mk[k] = (uint32_t)e[k].y;
             }
             const bool more = e[3].y != 0 && __ldg(pc + 4).y != 0;
-            for (int np = warp; np < periods; np += 8) {
+            for (int np = np0; np < np1; ++np) {
                 const int w = np * period_words + wp;
                 if (w >= w_limit) break;
                 const uint32_t *rows = bit_rows + np * period_frames * pitch;
