@@ -521,6 +521,48 @@ def cnn_section(torch, steps):
             "node_frames_per_s": nf / sec, "ms_per_step": sec * 1e3, "steps": steps, "n_gpus": 1}
 
 
+def train_cpp_section(torch, steps):
+    """The headline's six layers at the headline's shape (one GPU, all of the global batch) through the C++ host classes: bb::Sequential
+    of bb::DifferentiableLutN forward (training) + backward, bb::OptimizerAdam update.  Frame buffers come from the library's device
+    heap; input and output gradient are filled on the device once."""
+    import binarybrain_b200.core as core
+    from binarybrain_b200 import abi
+    F, nodes = TRAIN_GLOBAL_BATCH, TRAIN_NODES
+    net, layers = core.Sequential.create(), []
+    for k in range(TRAIN_LAYERS):
+        layer = core.DifferentiableLut6_fp32_fp32.create([nodes], seed=1 + k)
+        layer.send_command("binary false")
+        net.add(layer)
+        layers.append(layer)
+    net.set_input_shape([nodes])
+    opt = core.OptimizerAdam_fp32.create()
+    for layer in layers:
+        opt.set_variables(layer.W(), layer.dW())
+
+    def device_frames(seed):
+        fb = core.FrameBuffer(F, [nodes])
+        src = torch.rand((nodes, F), device="cuda", generator=torch.Generator(device="cuda").manual_seed(seed))
+        abi.call("bbcu_int32_FrameBufferCopy", fb.lock_device(), src.data_ptr(), nodes, 0, 0, F, 0, 0, fb.get_frame_stride() // 4, F, None)
+        torch.cuda.synchronize()
+        return fb
+
+    x, dy = device_frames(11), device_frames(12)
+    torch.cuda.empty_cache()
+
+    def step():
+        net.forward(x, True)
+        net.backward(dy)
+        opt.update()
+
+    sec = time_op(torch, step, steps)
+    del net, layers, opt, x, dy
+    torch.cuda.synchronize()
+    abi.lib().bbcu_LocalHeap_GarbageCollect()         # the section's frame buffers go back to the driver before the next one allocates
+    return {"workload": f"{TRAIN_LAYERS} x DifferentiableLut6 {TRAIN_NODES}->{TRAIN_NODES}, fp32, batch norm, {F} frames, forward + backward + Adam "
+                        "through the C++ host classes (bb::Sequential, bb::DifferentiableLutN, bb::OptimizerAdam), one GPU",
+            "node_frames_per_s": TRAIN_LAYERS * nodes * F / sec, "ms_per_step": sec * 1e3, "steps": steps}
+
+
 def operators_section(torch, ops, steps):
     """Every other operator of the path on an 8192 -> 8192 x 16384-frame layer, each with its algorithmic bytes / flops per node-frame
     and the fraction of max(HBM, FP32) roofline time, plus the lowering operators on 32-channel 32x32 images and Adam.  One launch
@@ -633,7 +675,7 @@ def main():
     ap.add_argument("--global-batch", type=int, default=TRAIN_GLOBAL_BATCH, help="frames per step over all GPUs (default: 32768)")
     ap.add_argument("--bl6-frames", type=int, default=BL6_FRAMES, help="frames per GPU of the BinaryLut6 section (default: 2^20)")
     ap.add_argument("--no-extras", action="store_true", help="headline only: no e2e leg, no sub-sections, no CPU baseline")
-    ap.add_argument("--only", default=None, choices=["train", "binary_lut6", "fp32", "operators"], help="run and print one section (profiling aid)")
+    ap.add_argument("--only", default=None, choices=["train", "binary_lut6", "fp32", "operators", "train_cpp"], help="run and print one section (profiling aid)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -674,6 +716,9 @@ def main():
     W = max(args.warmup, 3)
     if args.only == "fp32":
         print(json.dumps({"fp32": fp32_section(torch, ops, max(1, args.steps))}))
+        return 0
+    if args.only == "train_cpp":
+        print(json.dumps({"train_cpp": train_cpp_section(torch, max(1, args.steps))}))
         return 0
     if args.only == "operators":
         print(json.dumps({"operators": operators_section(torch, ops, max(1, args.steps))}))
@@ -746,6 +791,9 @@ def main():
     torch.cuda.empty_cache()
     dbg("train_binary done")
     if rank == 0:
+        if world == 1:
+            line["train_cpp"] = train_cpp_section(torch, k)
+            torch.cuda.empty_cache()
         line["fp32"] = fp32_section(torch, ops, max(3, min(args.steps, 10)))
         torch.cuda.empty_cache()
         line["cnn"] = cnn_section(torch, k)

@@ -52,7 +52,7 @@ def build_host_module(force=False):
         return None
     ext = sysconfig.get_config_var("EXT_SUFFIX")
     out = os.path.join(HERE, "core" + ext)
-    deps = [os.path.join(host, f) for f in os.listdir(host)] + [LIB]
+    deps = [os.path.join(d, f) for d, _, files in os.walk(host) for f in files] + [LIB, os.path.join(HERE, "..", "include", "bbcu_b200.h")]
     if force or _newer(out, deps):
         cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
         cmd = [cxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", src, "-o", out,

@@ -7,7 +7,7 @@
 //   - free blocks are kept in a size-ordered multimap, so reuse is a lower_bound lookup instead of
 //     a std::sort on every free (cuda/LocalHeap.cu:142-153);
 //   - out of memory returns NULL after one garbage-collect-and-retry; nothing exits the process;
-//   - freed blocks stay cached until they add up to a quarter of the device's memory (the reference gives its cache back at 1.5x
+//   - freed blocks stay cached until they add up to half of the device's memory (the reference gives its cache back at 1.5x
 //     the high-water mark, i.e. on nearly every step of a network with layers of different sizes);
 //   - block sizes are rounded up to 512 bytes so that every row a caller carves out of a block
 //     keeps the 256-byte alignment cudaMalloc gives.
@@ -257,8 +257,8 @@ extern "C" void *bbcu_LocalHeap_Malloc(size_t size)
     // The reference trims its cache whenever live + cached passes 1.5x the high-water mark (cuda/LocalHeap.cu:115-117).  A network
     // whose layers have different buffer sizes crosses that mark every step, and each trim is a cudaFree per block (a device
     // synchronisation plus the unmapping: measured 100 ms per layer of a LUT-CNN forward, against 0.4 ms of kernels).  Here the
-    // cache is only given back when it holds more than a quarter of the device's memory, on a byte limit, or when cudaMalloc fails.
-    if (p.cached_bytes > 0 && p.cached_bytes + size > device_info().total_bytes / 4) release_cached_locked(p);
+    // cache is only given back when it holds more than half of the device's memory, on a byte limit, or when cudaMalloc fails.
+    if (p.cached_bytes > 0 && p.cached_bytes + size > device_info().total_bytes / 2) release_cached_locked(p);
 
     void *ptr = nullptr;
     cudaError_t e = cudaMalloc(&ptr, size);

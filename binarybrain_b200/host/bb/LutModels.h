@@ -249,7 +249,7 @@ public:
     }
     void PushFrameBuffer(FrameBuffer b) { m_stack.push_back(b); }
     FrameBuffer PopFrameBuffer() { BB_ASSERT(!m_stack.empty()); FrameBuffer b = m_stack.back(); m_stack.pop_back(); return b; }
-    void Clear() { m_stack.clear(); }
+    virtual void Clear() { m_stack.clear(); }
 };
 
 
@@ -325,7 +325,8 @@ private:
     AllReduceF64   m_allreduce_sums;
     AllReduceF32   m_allreduce_grads;
     Tensor_<double> m_sums;                     // [O][2] batch sums on their way through the exchange
-    FrameBuffer    m_y_saved;                   // the training output, kept for the backward statistics (probability mode)
+    std::vector<FrameBuffer> m_y_stack;         // training outputs, kept for the backward statistics (probability mode); pushed and
+                                                // popped with the inputs, so several forwards may precede their backwards
 
 public:
     struct create_t {
@@ -515,13 +516,18 @@ public:
                 BBCU_CHECK(bbcu_fp32_DifferentiableLut6_ForwardNormalize(
                         (float *)y_buf.LockDeviceMemory(), m_sums.DevConst(), m_mean.Dev(true), m_rstd.Dev(true), m_running_mean.Dev(), m_running_var.Dev(),
                         m_gamma, m_beta, m_momentum, O, F, ys, (long long)m_total_frames, this->m_binary_mode, st));
-                if (!this->m_binary_mode) m_y_saved = y_buf;
+                m_y_stack.push_back(this->m_binary_mode ? FrameBuffer() : y_buf);
             } else {
                 BB_ASSERT(xs == ys);
-                if (train) BBCU_CHECK(bbcu_fp32_DifferentiableLut6_ForwardTraining(
+                if (train) {
+                    BBCU_CHECK(bbcu_fp32_DifferentiableLut6_ForwardTraining(
                         (float const *)x_buf.LockDeviceMemoryConst(), (float *)y_buf.LockDeviceMemory(true), idx, this->m_W->DevConst(), m_mean.Dev(true),
                         m_rstd.Dev(true), m_running_mean.Dev(), m_running_var.Dev(), m_gamma, m_beta, m_momentum, this->m_unbinarize_bias, O, F, ys,
                         this->m_lut_binarize, this->m_binary_mode, st));
+                    // probability mode: the backward takes its batch-norm sums from this output (8 bytes per node-frame) instead of
+                    // evaluating the LUT a second time; the buffer is the one the next layer holds anyway
+                    m_y_stack.push_back(this->m_binary_mode ? FrameBuffer() : y_buf);
+                }
                 else BBCU_CHECK(bbcu_fp32_DifferentiableLut6_ForwardInference(
                         (float const *)x_buf.LockDeviceMemoryConst(), (float *)y_buf.LockDeviceMemory(true), idx, this->m_W->DevConst(),
                         m_running_mean.DevConst(), m_running_var.DevConst(), m_gamma, m_beta, this->m_unbinarize_bias, O, F, ys, this->m_lut_binarize,
@@ -550,26 +556,31 @@ public:
         int I = (int)dx_buf.GetNodeSize(), O = (int)dy_buf.GetNodeSize(), F = (int)dy_buf.GetFrameSize();
         int fs = (int)(dy_buf.GetFrameStride() / 4), xs = (int)(x_buf.GetFrameStride() / 4);
         auto idx = this->m_connection_table.LockDeviceMemConst_InputTable();
-        if (m_batch_norm && !kBit && m_total_frames > 0) {
+        FrameBuffer y_saved;
+        if (!m_y_stack.empty()) { y_saved = m_y_stack.back(); m_y_stack.pop_back(); }
+        const bool from_output = !this->m_binary_mode && !y_saved.Empty() && y_saved.GetFrameSize() == dy_buf.GetFrameSize();
+        if (m_batch_norm && !kBit && (m_total_frames > 0 || from_output)) {
+            // the two halves of the backward: per-rank sums, their exchange when this object holds a frame shard, then the gradients
+            const long long total = m_total_frames > 0 ? (long long)m_total_frames : (long long)F;
             Tensor dmean(indices_t{O}), dvar(indices_t{O});
             m_sums.Resize({(index_t)O, 2});
             float const *xp = (float const *)x_buf.LockDeviceMemoryConst(), *dyp = (float const *)dy_buf.LockDeviceMemoryConst();
-            if (!this->m_binary_mode && !m_y_saved.Empty() && m_y_saved.GetFrameSize() == dy_buf.GetFrameSize()) {
+            if (from_output) {
                 // probability mode: the sums come from the saved output (8 bytes per node-frame) instead of a second LUT evaluation
-                BBCU_CHECK(bbcu_fp32_DifferentiableLut6_BackwardStatsFromOutput((float const *)m_y_saved.LockDeviceMemoryConst(), dyp, m_rstd.DevConst(),
+                BBCU_CHECK(bbcu_fp32_DifferentiableLut6_BackwardStatsFromOutput((float const *)y_saved.LockDeviceMemoryConst(), dyp, m_rstd.DevConst(),
                                                                                 m_sums.Dev(true), m_gamma, m_beta, O, F, fs, 0, st));
             } else {
                 BBCU_CHECK(bbcu_fp32_DifferentiableLut6_BackwardStats(xp, dyp, idx, this->m_W->DevConst(), m_mean.DevConst(), m_rstd.DevConst(),
                                                                       m_sums.Dev(true), m_gamma, m_beta, this->m_unbinarize_bias, O, F, fs,
                                                                       this->m_lut_binarize, this->m_binary_mode, st));
             }
-            m_y_saved = FrameBuffer();
-            m_allreduce_sums(m_sums.Dev(), (std::size_t)O * 2, st);
+            y_saved = FrameBuffer();
+            if (m_total_frames > 0) m_allreduce_sums(m_sums.Dev(), (std::size_t)O * 2, st);
             BBCU_CHECK(bbcu_fp32_DifferentiableLut6_BackwardApply(xp, dyp, (float *)dx_buf.LockDeviceMemory(true), idx, this->m_W->DevConst(),
                                                                   this->m_dW->Dev(), m_mean.DevConst(), m_rstd.DevConst(), m_sums.DevConst(),
                                                                   dmean.Dev(true), dvar.Dev(true), m_gamma, m_beta, this->m_unbinarize_bias, I, O, F, fs,
-                                                                  (long long)m_total_frames, this->m_lut_binarize, this->m_binary_mode, st));
-            if (m_allreduce_grads) m_allreduce_grads(this->m_dW->Dev(), (std::size_t)this->m_dW->GetSize(), st);
+                                                                  total, this->m_lut_binarize, this->m_binary_mode, st));
+            if (m_total_frames > 0 && m_allreduce_grads) m_allreduce_grads(this->m_dW->Dev(), (std::size_t)this->m_dW->GetSize(), st);
         } else if (m_batch_norm) {
             Tensor dmean(indices_t{O}), dvar(indices_t{O});
             if (kBit) BBCU_CHECK(bbcu_bit_fp32_DifferentiableLut6_Backward(
@@ -593,6 +604,8 @@ public:
         }
         return dx_buf;
     }
+
+    void Clear() override { Model::Clear(); m_y_stack.clear(); }
 
 protected:
     void CommandProc(std::vector<std::string> const &args) override
