@@ -201,7 +201,7 @@ k_im2col_forward_band_f32(const float *__restrict__ x, float *__restrict__ y, Im
 {
     extern __shared__ __align__(16) unsigned char band_smem[];
     float *tile = reinterpret_cast<float *>(band_smem);                                   // [rows_in * in_w][kBandPitch]
-    int *src = reinterpret_cast<int *>(tile + (size_t)rows_in * g.in_w * kBandPitch);      // [taps][R * out_w]
+    int *src = reinterpret_cast<int *>(tile + ((size_t)rows_in * g.in_w + 1) * kBandPitch);  // [taps][R * out_w], then [taps] flags
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int b = blockIdx.x;
     const int ft = b % f_tiles; b /= f_tiles;
@@ -214,15 +214,24 @@ k_im2col_forward_band_f32(const float *__restrict__ x, float *__restrict__ y, Im
     const int taps = g.filter_h * g.filter_w;
     const int Q = g.in_h * g.in_w, P = g.out_h * g.out_w;
 
+    // Source table: byte offset into the tile for every (tap, output pixel of the band).  A border pixel points at one extra tile
+    // row that holds the border value in all 32 frames, so the copy loop needs no select; a source outside the band (only the
+    // wrapping / reflecting border modes at a band edge) also points there for now and is remembered per tap in `patch` as
+    // -2 - pixel, to be fetched from global memory afterwards.
+    const int n_in = rows_in * g.in_w;
+    int *patch = src + taps * pitch;                               // [taps]: 0, or 1 when the tap has sources outside the band
+    if (threadIdx.x < taps) patch[threadIdx.x] = 0;
+    __syncthreads();
     for (int pl = threadIdx.x; pl < npix; pl += 256) {
         const int oy = pl / g.out_w, ox = pl - oy * g.out_w;
         for (int fy = 0, tap = 0; fy < g.filter_h; ++fy)
             for (int fx = 0; fx < g.filter_w; ++fx, ++tap) {
                 const int pix = im2col_source_pixel(g, fy, fx, oy0 + oy, ox);
-                int s = -1;
+                int s = n_in * (kBandPitch * 4);                   // the border row
                 if (pix >= 0) {
-                    const int local = pix - iy0 * g.in_w;          // in the band when 0 <= local < rows_in * in_w
-                    s = (local >= 0 && local < rows_in * g.in_w) ? local * (kBandPitch * 4) : -2 - pix;      // byte offset into the tile
+                    const int local = pix - iy0 * g.in_w;          // in the band when 0 <= local < n_in
+                    if (local >= 0 && local < n_in) s = local * (kBandPitch * 4);
+                    else patch[tap] = 1;
                 }
                 src[tap * pitch + pl] = s;
             }
@@ -230,7 +239,6 @@ k_im2col_forward_band_f32(const float *__restrict__ x, float *__restrict__ y, Im
     {
         const bool f_ok = f0 + lane < g.in_frames;
         const float *xc = x + (size_t)c * Q * g.in_fs + f0 + lane;
-        const int n_in = rows_in * g.in_w;
 #pragma unroll 4
         for (int q = warp; q < n_in; q += 8) {
             const int pix = iy0 * g.in_w + q;
@@ -238,46 +246,37 @@ k_im2col_forward_band_f32(const float *__restrict__ x, float *__restrict__ y, Im
             if (f_ok && pix >= 0 && pix < Q) v = xc[(size_t)pix * g.in_fs];
             tile[q * kBandPitch + lane] = v;
         }
+        if (warp == 0) tile[n_in * kBandPitch + lane] = border_value;
     }
     __syncthreads();
 
-    // (tap, frame) pairs: each is one contiguous run of an output row.  The table holds byte offsets into the tile, so an element
-    // costs a table read, a tile read, a select (border value) and a store; pixels whose source lies outside the band (s < -1,
-    // only the wrapping / reflecting border modes at a band edge) are patched afterwards by the lanes that own them.
+    // (tap, frame) pairs: each is one contiguous run of an output row; an element is a table read, a tile read and a store.
     const int pairs = taps * 32;
     const unsigned char *tile_b = reinterpret_cast<const unsigned char *>(tile);
     for (int pr = warp; pr < pairs; pr += 8) {
         const int tap = pr >> 5, fl = pr & 31;                     // warp-uniform
         if (f0 + fl >= g.in_frames) continue;
-        float *yp = y + (size_t)(c * taps + tap) * g.out_fs + (size_t)(f0 + fl) * P + oy0 * g.out_w + lane;
+        float *yrun = y + (size_t)(c * taps + tap) * g.out_fs + (size_t)(f0 + fl) * P + oy0 * g.out_w;
+        float *yp = yrun + lane;
         const int *sp = src + tap * pitch + lane;
         const unsigned char *tp = tile_b + 4 * fl;
         int pl = lane;
-        bool outside = false;
         for (; pl + 96 < npix; pl += 128, sp += 128, yp += 128) {
             int sv[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) sv[i] = sp[32 * i];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float v = *reinterpret_cast<const float *>(tp + max(sv[i], 0));
-                yp[32 * i] = sv[i] >= 0 ? v : border_value;
-                outside |= sv[i] < -1;
-            }
+            for (int i = 0; i < 4; ++i) yp[32 * i] = *reinterpret_cast<const float *>(tp + sv[i]);
         }
-        for (; pl < npix; pl += 32, sp += 32, yp += 32) {
-            const int sv = sp[0];
-            const float v = *reinterpret_cast<const float *>(tp + max(sv, 0));
-            yp[0] = sv >= 0 ? v : border_value;
-            outside |= sv < -1;
-        }
-        if (__any_sync(0xffffffffu, outside)) {
+        for (; pl < npix; pl += 32, sp += 32, yp += 32) yp[0] = *reinterpret_cast<const float *>(tp + sp[0]);
+        if (patch[tap]) {
+            const int fy = tap / g.filter_w, fx = tap - fy * g.filter_w;
             const float *xg = x + (size_t)c * Q * g.in_fs + f0 + fl;
-            float *yq = y + (size_t)(c * taps + tap) * g.out_fs + (size_t)(f0 + fl) * P + oy0 * g.out_w;
-            const int *sq = src + tap * pitch;
             for (int q = lane; q < npix; q += 32) {
-                const int sv = sq[q];
-                if (sv < -1) yq[q] = xg[(size_t)(-2 - sv) * g.in_fs];
+                const int oy = q / g.out_w, ox = q - oy * g.out_w;
+                const int pix = im2col_source_pixel(g, fy, fx, oy0 + oy, ox);
+                const int local = pix - iy0 * g.in_w;
+                if (pix >= 0 && (local < 0 || local >= n_in)) yrun[q] = xg[(size_t)pix * g.in_fs];
             }
         }
     }
@@ -868,10 +867,10 @@ extern "C" int bbcu_fp32_Im2Col_Forward(const float *dev_x_buf, float *dev_y_buf
         // banded kernel: the widest band of output rows whose input rows and source table fit the shared-memory budget
         const int taps = filter_h_size * filter_w_size;
         auto rows_in_of = [&](int R) { return (long long)(R - 1) * y_stride + filter_h_size; };
-        auto smem_of = [&](int R) { return (rows_in_of(R) * input_w_size * kBandPitch + (long long)taps * R * output_w_size) * 4; };
+        auto smem_of = [&](int R) { return ((rows_in_of(R) * input_w_size + 1) * kBandPitch + (long long)taps * R * output_w_size + taps) * 4; };
         // smem_of(R) = R * per_row + fixed
         const long long per_row = ((long long)y_stride * input_w_size * kBandPitch + (long long)taps * output_w_size) * 4;
-        const long long fixed = (long long)(filter_h_size - y_stride) * input_w_size * kBandPitch * 4;
+        const long long fixed = ((long long)(filter_h_size - y_stride) * input_w_size * kBandPitch + kBandPitch + taps) * 4;
         long long fit = (kBandSmemLimit - fixed) / per_row;
         if (fit > output_h_size) fit = output_h_size;
         while (fit >= 1 && smem_of((int)fit) > kBandSmemLimit) --fit;
