@@ -631,7 +631,7 @@ def operators_section(torch, ops, steps):
         "sl6_backward_fp32_binary": (lambda: ops.stochastic_lut6_backward(xf, dy, idx, W, dW, I, F, dx=dx, binary=True), nf, 12.0, 505.0),
         "sbn_forward_training": (sbn_fwd, nf, 12.0, 8.0),
         "sbn_backward": (lambda: ops.stochastic_bn_backward(xf, dy, st["smean"], st["srstd"], F), nf, 20.0, 12.0),
-        "adam_update": (lambda: adam.update(), 8.0 * 65536 * 64, 28.0, 12.0),
+        "adam_update": (lambda: adam.update(), 8.0 * 65536 * 64, 32.0, 12.0),      # W, m, v read and written, dW read, then cleared (Update = Step + ZeroGrad)
         "im2col_forward_fp32": (lambda: ops.im2col_forward(img, B, c, hw, hw, 3, 3, padding="same"), px * 9, 4.0 + 4.0 / 9, 0.0),
         "im2col_forward_bit": (lambda: ops.im2col_forward(colsb_in, B2, c, hw, hw, 3, 3, padding="same", y=colsb_out), px2 * 9, (1 + 1.0 / 9) / 8, 0.0),
         "im2col_backward_fp32": (lambda: ops.im2col_backward(cols, B, c, hw, hw, 3, 3, padding="same"), px * 9, 4.0 + 4.0 / 9, 1.0),
