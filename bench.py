@@ -207,16 +207,25 @@ def train_e2e(torch, dist, wl, steps):
     """The training step fed from pinned host memory: every step uploads this rank's input and target shards (on a copy stream,
     into the spare one of two device buffers, while the previous step computes) and reads the loss back."""
     nbytes = wl.x0.numel() * 4
+    hx = ht = None
+    why = None
     try:
         with open("/proc/meminfo") as f:
             avail = next(int(l.split()[1]) * 1024 for l in f if l.startswith("MemAvailable"))
-        local_ranks = int(os.environ.get("LOCAL_WORLD_SIZE", "1"))
-        if avail < 3 * 2 * nbytes * local_ranks:
-            return {"value": None, "unavailable": f"host memory: {avail >> 30} GiB available, {2 * nbytes * local_ranks >> 30} GiB of pinned buffers needed"}
-        hx = torch.empty(wl.x0.shape, dtype=torch.float32, pin_memory=True)
-        ht = torch.empty(wl.target.shape, dtype=torch.float32, pin_memory=True)
+        if avail < 3 * 2 * nbytes:          # this rank's two buffers, with room to spare (the other ranks pin theirs at the same time)
+            why = f"host memory: {avail >> 30} GiB available, {2 * nbytes >> 30} GiB of pinned buffers needed per rank"
+        else:
+            hx = torch.empty(wl.x0.shape, dtype=torch.float32, pin_memory=True)
+            ht = torch.empty(wl.target.shape, dtype=torch.float32, pin_memory=True)
     except (RuntimeError, OSError, StopIteration) as e:
-        return {"value": None, "unavailable": f"pinned host buffers: {e}"}
+        why = f"pinned host buffers: {e}"
+    # every rank takes the same branch: the timed loop below holds collectives, so one rank without its buffers means no rank runs it
+    ok = torch.tensor([0 if why else 1], device="cuda", dtype=torch.int32)
+    if dist:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if int(ok.item()) == 0:
+        del hx, ht
+        return {"value": None, "unavailable": why or "another rank could not pin its host buffers"}
     hx.copy_(wl.x0)
     ht.copy_(wl.target)
     bufs = [(wl.x0, wl.target), (torch.empty_like(wl.x0), torch.empty_like(wl.target))]
