@@ -745,9 +745,14 @@ def main():
     sampler = ClockSampler(local_rank)
     sec = timed_steps(torch, dist, wl.step, args.steps, 0, sampler)
     timed.enabled = False
-    t_keep = time.time()
-    while len(sampler.rows) < 3 and time.time() - t_keep < 1.5:      # let the sampler see the loaded clocks at least a few times
-        wl.step()
+    # let the sampler see the loaded clocks at least a few times.  The step holds collectives, so every rank runs the same number of
+    # extra steps: whether to run them is agreed on (MAX over ranks), and their count follows from `sec`, which is the same everywhere
+    short = torch.tensor([1 if len(sampler.rows) < 3 else 0], device="cuda", dtype=torch.int32)
+    if dist:
+        dist.all_reduce(short, op=dist.ReduceOp.MAX)
+    if int(short.item()):
+        for _ in range(int(min(64, max(1, round(0.8 / sec))))):
+            wl.step()
         torch.cuda.synchronize()
     clocks = sampler.stop()
     value = TRAIN_LAYERS * TRAIN_NODES * frames * world / sec
