@@ -203,6 +203,31 @@ def timed_steps(torch, dist, fn, steps, warmup, sampler=None):
     return ms / 1e3 / steps
 
 
+def bind_to_gpu_numa_node(torch, local_rank):
+    """Keeps this rank's threads (and with them the first touch of its page-locked buffers) on the NUMA node its GPU hangs off, so that
+    eight ranks' host-to-device copies do not all cross the socket interconnect.  Returns the node, or None when the platform does not
+    say (no sysfs entry, node -1, or none of the node's cores in this process's affinity mask)."""
+    try:
+        prop = torch.cuda.get_device_properties(local_rank)
+        bdf = f"{prop.pci_domain_id:04x}:{prop.pci_bus_id:02x}:{prop.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read())
+        if node < 0:
+            return None
+        cpus = set()
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0) & cpus
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except (AttributeError, OSError, ValueError):
+        return None
+
+
 def train_e2e(torch, dist, wl, steps):
     """The training step fed from pinned host memory: every step uploads this rank's input and target shards (on a copy stream,
     into the spare one of two device buffers, while the previous step computes) and reads the loss back."""
@@ -715,6 +740,7 @@ def main():
     assert torch.cuda.is_available(), "bench.py --impl ours needs a CUDA device"
     torch.cuda.set_device(local_rank)
     dist = None
+    numa_node = bind_to_gpu_numa_node(torch, local_rank) if world > 1 else None       # (one rank alone keeps every core for the CPU baseline)
     if world > 1:
         if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
             os.environ.pop("NCCL_DEBUG", None)         # NCCL prints its version banner on stdout at VERSION and above: stdout carries one JSON line
@@ -781,6 +807,7 @@ def main():
     dbg("headline done")
     if not args.no_extras:
         line["e2e"] = train_e2e(torch, dist, wl, max(2, min(args.steps, 5)))
+        line["e2e"]["host_numa_node"] = numa_node
     dbg("e2e done")
     del wl
     torch.cuda.empty_cache()
