@@ -257,7 +257,8 @@ int bbcu_fp32_Im2Col_Forward(const float *dev_x_buf, float *dev_y_buf, int x_str
                              int input_frame_size, int input_frame_stride, int input_w_size, int input_h_size, int input_c_size,
                              int output_w_size, int output_h_size, int output_frame_stride, int filter_w_size, int filter_h_size,
                              int border_mode, float border_value, bbcu_stream_t stream);
-/* bbcu_bit_Im2Col_Forward, bbcu.h:1099-1119. */
+/* bbcu_bit_Im2Col_Forward, bbcu.h:1099-1119.  Keeps a table of a few KiB per (geometry) in the stream's heap scratch: the first call
+ * on a stream allocates (outside of stream capture); a heap that declines it is answered by slower kernels, not by an error. */
 int bbcu_bit_Im2Col_Forward(const int *dev_x_buf, int *dev_y_buf, int x_stride, int y_stride, int x_offset, int y_offset,
                             int input_frame_size, int input_frame_stride, int input_w_size, int input_h_size, int input_c_size,
                             int output_w_size, int output_h_size, int output_frame_stride, int filter_w_size, int filter_h_size,
