@@ -155,7 +155,7 @@ def main():
     r = ref.differentiable_lut6_adam(x, idx, W, dy, 100, batch_norm=False, binary=False)
     g.update({"adamnobn_W0": W, "adamnobn_W100": r["W"], "adamnobn_y100": r["y"]})
 
-    # One whole training step of BASELINE config 0: 784 -> 1024 -> 420 -> 70 DifferentiableLut6 (fp32, batch norm, non-binary),
+    # One whole training step of the small MLP: 784 -> 1024 -> 420 -> 70 DifferentiableLut6 (fp32, batch norm, non-binary),
     # Reduce to 10 classes, softmax cross-entropy, Adam, 512 frames.  Inputs come from integer hashing (oracle.det_uniform), so only
     # the results are stored: logits, loss, dx and W checksums plus a few rows.
     widths, classes, F = [784, 1024, 420, 70], 10, 512
