@@ -74,6 +74,14 @@ __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src,
                  : "memory");
 }
 
+// The same copy with both addresses given as a base register plus a compile-time byte offset, so that a run of copies off one
+// base costs no address arithmetic.  `smem_base` is a shared-window address (smem_addr), `gmem_base` a global-space address.
+template <int SMEM_OFF, int GMEM_OFF>
+__device__ __forceinline__ void cp_async16_at(uint32_t smem_base, uint64_t gmem_base)
+{
+    asm volatile("cp.async.cg.shared.global [%0+%2], [%1+%3], 16;" ::"r"(smem_base), "l"(gmem_base), "n"(SMEM_OFF), "n"(GMEM_OFF) : "memory");
+}
+
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 
 template <int N>

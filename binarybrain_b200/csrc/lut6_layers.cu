@@ -187,12 +187,14 @@ k_lut6_forward(const FwdArgs a)
 }
 
 // ---------------------------------------------------------------------------------------------
-// Persistent, bulk-copy-pipelined forward for fp32 inputs with 16-byte aligned rows (the launcher's default).
+// Persistent, copy-pipelined forward for fp32 inputs with 16-byte aligned rows (the launcher's default).
 // Work item = (frame tile of a.T = 128 or 256 frames, group of 8 nodes); CTA c takes items c, c + gridDim, ... so
 // the CTAs in flight sweep the node groups of one tile together and the tile's rows stay in L2.  Each warp owns one
-// node of the group and runs its own two-stage pipeline: seven lanes start one bulk copy each (six gathered row
-// segments and the node's table) for item j+2 once item j has been read out of shared memory, and the
-// warp computes item j while the copies of j+1 (and j+2) are in flight.
+// node of the group and runs its own two-stage pipeline of cp.async copies: every lane copies the 16-byte pieces of the six
+// gathered row segments that it will itself read (frames 128 h + 4 lane .. + 3) and one piece of the node's table, for item
+// j+2 once item j has been read out of shared memory, and the warp computes item j while the copies of j+1 (and j+2) are in
+// flight.  (Bulk copies with an mbarrier did the same with seven copy instructions per item, but each of them cost five moves
+// into uniform registers plus the election of the issuing lane: a fifth of the kernel's issue slots.)
 // The table normally arrives ready to use: a small kernel in front (k_table_coeffs) has turned every node's 64 entries
 // into the 32 x (c0, c0, c1, c1) packed-operand form once per launch, so no warp repeats that butterfly (ten shuffles
 // in a dependent chain) for every item.  Tables have a ring of three slots per warp because the table of item j is
@@ -204,12 +206,10 @@ constexpr int kFpCtas          = 2;
 constexpr int kFpStages        = 2;
 constexpr int kFpStageBytes    = 6 * kFpMaxItemFrames * 4;                             // six row segments
 constexpr int kFpRowsBytes     = kWarpsPerCta * kFpStages * kFpStageBytes;
-constexpr int kFpBarBytes      = 128;
 constexpr int kFpTabSlots      = 3;
 constexpr int kFpTabSlotBytes  = 32 * 16;
 constexpr int kFpTabBytes      = kWarpsPerCta * kFpTabSlots * kFpTabSlotBytes;
-constexpr int kFpSmem          = kFpRowsBytes + kFpBarBytes + kFpTabBytes;
-static_assert(kWarpsPerCta * kFpStages * 8 <= kFpBarBytes, "barrier block too small");
+constexpr int kFpSmem          = kFpRowsBytes + kFpTabBytes;
 static_assert(kFpCtas * (kFpSmem + 1024) <= 227 * 1024, "the CTAs of one SM must fit");
 
 // Position of a work item, advanced incrementally (item index + gridDim) so that no division runs per item.
@@ -225,31 +225,62 @@ __device__ __forceinline__ FpPos fp_advance(FpPos p, int dt, int dg, int groups)
     return p;
 }
 
-// Lanes 0..5 each start the bulk copy of one gathered row segment and lane 6 that of the node's table (one
-// instruction issue covers all seven); lane 0 has armed the barrier with the byte count just before.
-// `row` is the lane's input row of the item's node (fp_row), fetched an item earlier so that the copy does not wait for it.
+// The copies of input rows J..5 of an item: one shuffle and one 64-bit multiply-add per row, offsets as immediates.
+template <int J, bool TWO>
+struct FpRowCopies {
+    static __device__ __forceinline__ void issue(uint32_t sb, uint64_t gb, int row, size_t row_bytes)
+    {
+        const uint64_t src = gb + (uint64_t)__shfl_sync(0xffffffffu, row, J) * row_bytes;
+        cp_async16_at<J * kFpMaxItemFrames * 4, 0>(sb, src);
+        if (TWO) cp_async16_at<J * kFpMaxItemFrames * 4 + kFramesPerIter * 4, kFramesPerIter * 4>(sb, src);
+        FpRowCopies<J + 1, TWO>::issue(sb, gb, row, row_bytes);
+    }
+};
+template <bool TWO>
+struct FpRowCopies<6, TWO> {
+    static __device__ __forceinline__ void issue(uint32_t, uint64_t, int, size_t) {}
+};
+
+// `row` is the lane's input row of the item's node (lanes 0..5; fp_row), fetched an item earlier so that the copies do not wait
+// for it.  One commit group per call, whether or not the item exists, so that the consumer's wait counts items.
 __device__ __forceinline__ int fp_row(const FwdArgs &a, FpPos pos, int warp, int lane)
 {
     const int node = min(pos.group * kWarpsPerCta + warp, a.O - 1);
     return lane < 6 ? __ldg(a.idx + (size_t)node * 6 + lane) : 0;
 }
 
-__device__ __forceinline__ void fp_issue(const FwdArgs &a, FpPos pos, int row, int warp, int lane, unsigned char *stage, unsigned char *tab_slot,
-                                         uint64_t *bar)
+__device__ __forceinline__ void fp_issue(const FwdArgs &a, FpPos pos, bool exists, int row, int warp, int lane, unsigned char *stage,
+                                         unsigned char *tab_slot)
 {
-    const int node = min(pos.group * kWarpsPerCta + warp, a.O - 1);
-    const int f0   = pos.tile * a.T;
-    const uint32_t bytes = (uint32_t)min((long long)a.T, a.xs - f0) * 4u;       // row stride is a multiple of 4 floats
-    const uint32_t tab_bytes = a.coef ? (uint32_t)kFpTabSlotBytes : 256u;
-    if (lane == 0) mbar_arrive_expect_tx(bar, 6u * bytes + tab_bytes);
-    __syncwarp();
-    if (lane < 6) {
-        const float *src = static_cast<const float *>(a.x) + (size_t)row * a.xs + f0;
-        bulk_copy_g2s(stage + lane * (kFpMaxItemFrames * 4), src, bytes, bar);
-    } else if (lane == 6) {
-        if (a.coef) bulk_copy_g2s(tab_slot, a.coef + (size_t)node * 32, tab_bytes, bar);
-        else        bulk_copy_g2s(tab_slot, a.W + (size_t)node * 64, tab_bytes, bar);
+    if (exists) {
+        const int node = min(pos.group * kWarpsPerCta + warp, a.O - 1);
+        const int f0 = pos.tile * a.T;
+        const size_t row_bytes = (size_t)a.xs * 4;
+        const unsigned char *xb = static_cast<const unsigned char *>(a.x) + ((size_t)f0 + 4 * lane) * 4;      // this lane's first piece of row 0
+        unsigned char *dst = stage + 16 * lane;
+        constexpr int kRow = kFpMaxItemFrames * 4, kHalf = kFramesPerIter * 4;
+        if (f0 + a.T <= a.xs) {                                                 // every piece of the item lies inside the rows (all but a last tile)
+            const uint32_t sb = smem_addr(dst);
+            const uint64_t gb = (uint64_t)__cvta_generic_to_global(xb);
+            if (a.T > kFramesPerIter) FpRowCopies<0, true>::issue(sb, gb, row, row_bytes);
+            else                      FpRowCopies<0, false>::issue(sb, gb, row, row_bytes);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 6; ++j) {
+                const unsigned char *src = xb + (size_t)__shfl_sync(kFull, row, j) * row_bytes;
+#pragma unroll
+                for (int h = 0; h < kFpMaxItemFrames / kFramesPerIter; ++h) {
+                    if (kFramesPerIter * h < a.T) {                             // (a.T is 128 or 256)
+                        const bool in_row = f0 + 4 * lane + kFramesPerIter * h < a.xs;      // row stride is a multiple of 4 floats
+                        cp_async16(dst + j * kRow + h * kHalf, in_row ? src + h * kHalf : static_cast<const unsigned char *>(a.x), in_row);
+                    }
+                }
+            }
+        }
+        if (a.coef)         cp_async16(tab_slot + 16 * lane, a.coef + (size_t)node * 32 + lane, true);
+        else if (lane < 16) cp_async16(tab_slot + 16 * lane, a.W + (size_t)node * 64 + 4 * lane, true);
     }
+    cp_async_commit();
 }
 
 // Every node's table as 32 x (c0, c0, c1, c1): the polynomial coefficients, each duplicated for the two halves of a packed operand.
@@ -267,19 +298,12 @@ k_table_coeffs(const float *__restrict__ W, float4 *__restrict__ coef, int O, in
 
 template <int PHASE, bool BINARY>            // BINARY: the layer's binary mode, compiled in so that input conditioning is one instruction
 __global__ void __launch_bounds__(kWarpsPerCta * 32, kFpCtas)
-k_lut6_forward_pipe(const FwdArgs a, int n_tiles, int *fault)
+k_lut6_forward_pipe(const FwdArgs a, int n_tiles)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned char *my_stages = smem_raw + (size_t)warp * kFpStages * kFpStageBytes;
-    uint64_t *my_bar = reinterpret_cast<uint64_t *>(smem_raw + kFpRowsBytes) + warp * kFpStages;
-    unsigned char *my_tabs = smem_raw + kFpRowsBytes + kFpBarBytes + (size_t)warp * kFpTabSlots * kFpTabSlotBytes;
-
-    if (lane == 0) {
-        for (int s = 0; s < kFpStages; ++s) mbar_init(my_bar + s, 1);
-        mbar_init_fence();
-    }
-    __syncwarp();
+    unsigned char *my_tabs = smem_raw + kFpRowsBytes + (size_t)warp * kFpTabSlots * kFpTabSlotBytes;
 
     // items blockIdx, blockIdx + gridDim, ...: position of the current item and of the next two
     const int step = (int)gridDim.x;
@@ -289,8 +313,9 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles, int *fault)
     p0.group = (int)blockIdx.x - p0.tile * a.groups;
     FpPos p1 = fp_advance(p0, dt, dg, a.groups);
     FpPos p2 = fp_advance(p1, dt, dg, a.groups);
-    if (p0.tile < n_tiles) fp_issue(a, p0, fp_row(a, p0, warp, lane), warp, lane, my_stages, my_tabs, my_bar);
-    if (p1.tile < n_tiles) fp_issue(a, p1, fp_row(a, p1, warp, lane), warp, lane, my_stages + kFpStageBytes, my_tabs + kFpTabSlotBytes, my_bar + 1);
+    fp_issue(a, p0, p0.tile < n_tiles, p0.tile < n_tiles ? fp_row(a, p0, warp, lane) : 0, warp, lane, my_stages, my_tabs);
+    fp_issue(a, p1, p1.tile < n_tiles, p1.tile < n_tiles ? fp_row(a, p1, warp, lane) : 0, warp, lane, my_stages + kFpStageBytes,
+             my_tabs + kFpTabSlotBytes);
     int row2 = p2.tile < n_tiles ? fp_row(a, p2, warp, lane) : 0;            // input rows of item k+2, one item ahead of their use
     int ts = 0;                                   // table slot of the current item: k mod 3
 
@@ -304,7 +329,6 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles, int *fault)
 
     for (int k = 0; p0.tile < n_tiles; ++k) {
         const int s = k & 1;
-        const uint32_t parity = (uint32_t)(k >> 1) & 1u;
         unsigned char *stage = my_stages + s * kFpStageBytes;
         const int node_raw = p0.group * kWarpsPerCta + warp;
         const bool store = node_raw < a.O;
@@ -320,11 +344,8 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles, int *fault)
             scale_n = a.rstd[n1];
         }
 
-        if (!mbar_wait(my_bar + s, parity)) {          // bounded: record the fault, let the other stage's copies land, leave
-            if (lane == 0) atomicCAS(fault, 0, kFaultBarrierTimeout);
-            if (have_next) mbar_wait(my_bar + (s ^ 1), (uint32_t)((k + 1) >> 1) & 1u);
-            return;
-        }
+        cp_async_wait<1>();                            // this item's group has landed (the next item's may still be in flight)
+        __syncwarp();                                  // the table was copied by other lanes
         float4 *tab = reinterpret_cast<float4 *>(my_tabs + ts * kFpTabSlotBytes);
         unsigned char *tab_refill = my_tabs + (ts == 0 ? 2 : ts - 1) * kFpTabSlotBytes;      // slot (k + 2) mod 3, last read by item k - 1
         ts = ts == 2 ? 0 : ts + 1;
@@ -363,10 +384,7 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles, int *fault)
             }
             // the stage has been read out: hand it back to the copy engine for item k+2 before doing the math
             __syncwarp();
-            if (p2.tile < n_tiles) {
-                proxy_fence_async();
-                fp_issue(a, p2, row2, warp, lane, stage, tab_refill, my_bar + s);
-            }
+            fp_issue(a, p2, p2.tile < n_tiles, row2, warp, lane, stage, tab_refill);
             if (p3.tile < n_tiles) row2 = fp_row(a, p3, warp, lane);
             lut6_forward_x2<NP>(tab, up, yp);
 #pragma unroll
@@ -410,6 +428,7 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles, int *fault)
         }
         p0 = p1; p1 = p2; p2 = p3;
     }
+    cp_async_wait<0>();
 }
 
 // mean / var / rstd and the running statistics from the fp64 sums (DifferentiableLutN.h:804-812).
@@ -973,9 +992,8 @@ static int launch_forward(FwdArgs a, int max_tile, cudaStream_t st)
         // pipelined path: rows and tables must start on 16-byte boundaries for the bulk copies and the 128-bit stores
         const bool aligned = ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.W) | reinterpret_cast<uintptr_t>(a.y)) & 15) == 0 &&
                              (a.xs % 4) == 0 && (a.ys % 4) == 0;
-        int *fault = aligned ? fault_word() : nullptr;
         auto kern = a.binary ? k_lut6_forward_pipe<PHASE, true> : k_lut6_forward_pipe<PHASE, false>;
-        if (aligned && fault != nullptr && allow_big_smem(kern, kFpSmem)) {
+        if (aligned && allow_big_smem(kern, kFpSmem)) {
             // 256-frame items whenever there are that many frames: four frame pairs per lane share every table read and the
             // per-item costs halve.  Measured on B200: 65536 -> 65536 nodes x 4096 frames 1.89 ms (128) vs 1.49 ms (256), although
             // the 256-frame tile of such a layer (64 MiB of gathered rows) no longer fits a fifth of L2.
@@ -993,7 +1011,7 @@ static int launch_forward(FwdArgs a, int max_tile, cudaStream_t st)
                     a.coef = coef;
                 }
             }
-            kern<<<(unsigned)grid, kWarpsPerCta * 32, kFpSmem, st>>>(a, (a.F + a.T - 1) / a.T, fault);
+            kern<<<(unsigned)grid, kWarpsPerCta * 32, kFpSmem, st>>>(a, (a.F + a.T - 1) / a.T);
             return launch_status();
         }
     }
