@@ -786,6 +786,20 @@ k_coeff_grads_to_dw(const float4 *__restrict__ dC, float *__restrict__ dW, int O
     *dst = cur;
 }
 
+// The copies of input rows J..5 of a chunk: one shuffle and one 64-bit multiply-add per row, shared-memory offsets as immediates.
+template <int J>
+struct BvRowCopies {
+    static __device__ __forceinline__ void issue(uint32_t sb, uint64_t gb, int row, uint64_t row_bytes)
+    {
+        cp_async16_at<J * kBvRowBytes, 0>(sb, gb + (uint64_t)__shfl_sync(0xffffffffu, row, J) * row_bytes);
+        BvRowCopies<J + 1>::issue(sb, gb, row, row_bytes);
+    }
+};
+template <>
+struct BvRowCopies<6> {
+    static __device__ __forceinline__ void issue(uint32_t, uint64_t, int, uint64_t) {}
+};
+
 // Position of a 128-frame chunk in a warp's sequence: item (tile, group), chunk c of the item's n, table slot of the item.
 struct BvCursor {
     int tile, group, c, n, slot;
@@ -829,18 +843,28 @@ k_lut6_backward_pipe(const BwdArgs a, const float4 *__restrict__ coef, float *__
         row_in = row_of(t);
     }
     const float *xf = static_cast<const float *>(a.x);
+    const uint64_t x_global = (uint64_t)__cvta_generic_to_global(xf), dy_global = (uint64_t)__cvta_generic_to_global(a.dy);
+    const uint64_t row_bytes = (uint64_t)a.xs * 4;
     auto issue = [&]() {
         if (ic.tile < n_tiles) {
-            const int f = ic.tile * a.T + ic.c * kFramesPerIter + 4 * lane;
-            const bool in_row = f < a.xs;
+            const int fc = ic.tile * a.T + ic.c * kFramesPerIter;              // first frame of the chunk
+            const int f = fc + 4 * lane;
             unsigned char *st = my + ist * kBvStageBytes + lane * 16;
-#pragma unroll
-            for (int j = 0; j < 6; ++j) {
-                const int r = __shfl_sync(kFull, row_i, j);
-                cp_async16(st + j * kBvRowBytes, xf + (size_t)r * a.xs + (in_row ? f : 0), in_row);
-            }
             const int node = node_of(ic);
-            cp_async16(st + 6 * kBvRowBytes, a.dy + (size_t)node * a.dys + (f < a.dys ? f : 0), f < a.dys);
+            if (fc + kFramesPerIter <= a.xs && fc + kFramesPerIter <= a.dys) {
+                // the whole chunk lies inside the rows (all but a last one): one 64-bit multiply-add per row, offsets as immediates
+                const uint32_t sb = smem_addr(st);
+                BvRowCopies<0>::issue(sb, x_global + (uint64_t)f * 4, row_i, row_bytes);
+                cp_async16_at<6 * kBvRowBytes, 0>(sb, dy_global + ((uint64_t)node * (uint64_t)a.dys + (uint64_t)f) * 4);
+            } else {
+                const bool in_row = f < a.xs;
+#pragma unroll
+                for (int j = 0; j < 6; ++j) {
+                    const int r = __shfl_sync(kFull, row_i, j);
+                    cp_async16(st + j * kBvRowBytes, xf + (size_t)r * a.xs + (in_row ? f : 0), in_row);
+                }
+                cp_async16(st + 6 * kBvRowBytes, a.dy + (size_t)node * a.dys + (f < a.dys ? f : 0), f < a.dys);
+            }
             if (ic.c == 0 && lane < 16) cp_async16(my_tabs + ic.slot * kBvTabBytes + lane * 16, coef + (size_t)node * 16 + lane, true);
             if (++ic.c == ic.n) {
                 next_item(ic);
