@@ -20,6 +20,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "bit_transpose.cuh"
 #include "lut6_core.cuh"
 
 namespace bb200 {
@@ -179,9 +180,10 @@ __device__ __forceinline__ uint32_t lane_pattern(const uint32_t (&w)[6], int lan
 }
 
 // StochasticLut6 bit -> fp32: y[f] = clip(Y[p(f)], 0, 1).  Warp = one node for a tile of words.  Each lane loads one word of each of
-// the six rows (32 words per row and step, coalesced), then the warp walks the 32 words: word k is broadcast by shuffle, lane l
-// takes frame l of it, looks its pattern up in the node's 64 clipped values (shared memory) and the warp stores 32 consecutive
-// frames.
+// the six rows (32 words per row and step, coalesced); a 32 x 32 bit transpose per row then gives lane l the bits of frame l of
+// all 32 words.  The patterns of four consecutive words are assembled at once, one per byte (a four-bit field of every row is
+// spread over the bytes by one multiplication), and for each of the 32 words the warp looks its 32 patterns up in the node's 64
+// clipped values (shared memory) and stores 32 consecutive frames.
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 k_bit_gather_forward(const uint32_t *__restrict__ x, float *__restrict__ y, const int *__restrict__ idx, const float *__restrict__ Y, int O, int F,
                      long long xs, long long ys, int groups, int tile_words)
@@ -201,18 +203,25 @@ k_bit_gather_forward(const uint32_t *__restrict__ x, float *__restrict__ y, cons
     const int words = (F + 31) >> 5;
     const int w_end = min(words, (tile + 1) * tile_words);
     float *yrow = y + (size_t)node * ys;
+    const BitTranspose transpose(lane);
     for (int w0 = tile * tile_words; w0 < w_end; w0 += 32) {
-        uint32_t xw[6];
+        uint32_t t[6];
 #pragma unroll
-        for (int j = 0; j < 6; ++j) xw[j] = (w0 + lane < w_end) ? __ldg(rows[j] + w0 + lane) : 0u;
+        for (int j = 0; j < 6; ++j) t[j] = transpose((w0 + lane < w_end) ? __ldg(rows[j] + w0 + lane) : 0u);      // bit k: frame `lane` of word w0 + k
         const int kn = min(32, w_end - w0);
-        for (int k = 0; k < kn; ++k) {
-            uint32_t wk[6];
+        float *yw = yrow + (size_t)w0 * 32 + lane;
+        const bool whole = kn == 32 && (long long)(w0 + 32) * 32 <= F;         // 32 full words: no guards
 #pragma unroll
-            for (int j = 0; j < 6; ++j) wk[j] = __shfl_sync(kFull, xw[j], k);
-            const uint32_t p = lane_pattern(wk, lane);
-            const long long f = (long long)(w0 + k) * 32 + lane;
-            if (f < F) yrow[f] = val[p];
+        for (int k0 = 0; k0 < 32; k0 += 4) {
+            if (!whole && k0 >= kn) break;
+            uint32_t p4 = 0u;                                                   // the patterns of words k0 .. k0 + 3, one per byte
+#pragma unroll
+            for (int j = 0; j < 6; ++j) p4 |= ((((t[j] >> k0) & 0xfu) * 0x00204081u) & 0x01010101u) << j;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float v = val[(p4 >> (8 * i)) & 63u];
+                if (whole || (k0 + i < kn && (long long)(w0 + k0 + i) * 32 + lane < F)) yw[(k0 + i) * 32] = v;
+            }
         }
     }
 }
