@@ -169,16 +169,6 @@ __global__ void k_clear_tail_bits(uint32_t *y, int O, int F, long long ys)
     y[(size_t)node * ys + (F >> 5)] &= (1u << (F & 31)) - 1u;
 }
 
-// Pattern of lane l's frame from six 32-frame words: bit l of word j has to land on bit j.  One rotation (funnel shift by (l - j) mod 32)
-// and one masked OR per input.
-__device__ __forceinline__ uint32_t lane_pattern(const uint32_t (&w)[6], int lane)
-{
-    uint32_t p = 0;
-#pragma unroll
-    for (int j = 0; j < 6; ++j) p |= __funnelshift_r(w[j], w[j], (lane - j) & 31) & (1u << j);
-    return p;
-}
-
 // StochasticLut6 bit -> fp32: y[f] = clip(Y[p(f)], 0, 1).  Warp = one node for a tile of words.  Each lane loads one word of each of
 // the six rows (32 words per row and step, coalesced); a 32 x 32 bit transpose per row then gives lane l the bits of frame l of
 // all 32 words.  The patterns of four consecutive words are assembled at once, one per byte (a four-bit field of every row is
@@ -233,7 +223,8 @@ k_bit_gather_forward(const uint32_t *__restrict__ x, float *__restrict__ y, cons
 //                                        k = 0.5 + bias where the bits agree, 0.5 - bias where they differ (one butterfly per input)
 // and for the batch-norm form g(f) = mask[p] dy(f) gamma rstd + dmean + Y[p] dvar / F, so Hg and the two batch sums
 // (include/bb/DifferentiableLutN.h:1190-1258) follow from Hdy[p] = sum of dy per pattern and the pattern counts H[p].
-// Per frame that leaves: the pattern (6 shuffles, ~18 integer ops), 6 table reads, 6 multiplies and the 6 dx reductions.
+// Per frame that leaves: the pattern (bit inputs: a 32 x 32 bit transpose per row and 32 words, then four patterns at a time, one per
+// byte), 6 table reads, 6 multiplies and the 6 dx reductions.
 
 enum { kBwdPlainAll = 0, kBwdHistOnly = 1, kBwdNormDx = 2 };
 
@@ -310,12 +301,14 @@ k_bit_backward_frames(const BitBwdArgs a)
     const int words = (a.F + 31) >> 5;
     const int w_end = min(words, (tile + 1) * a.tile_words);
     const float *dyrow = a.dy + (size_t)node * a.fs;
+    const BitTranspose transpose(lane);
     for (int w0 = tile * a.tile_words; w0 < w_end; w0 += 32) {
-        uint32_t xw[6];
+        uint32_t xw[6];                       // bit inputs: after the transpose, bit k of xw[j] is frame `lane` of word w0 + k
         if (!XF32) {
 #pragma unroll
-            for (int j = 0; j < 6; ++j) xw[j] = (w0 + lane < w_end) ? __ldg(rows[j] + w0 + lane) : 0u;
+            for (int j = 0; j < 6; ++j) xw[j] = transpose((w0 + lane < w_end) ? __ldg(rows[j] + w0 + lane) : 0u);
         }
+        uint32_t p4 = 0u;                     // bit inputs: the patterns of four consecutive words, one per byte
         const int kn = min(32, w_end - w0);
         // dy of the next word is fetched while this one is processed
         long long f = (long long)w0 * 32 + lane;
@@ -347,10 +340,12 @@ k_bit_backward_frames(const BitBwdArgs a)
                 }
                 if (MODE == kBwdHistOnly && f < a.F) const_cast<unsigned char *>(prow)[f] = (unsigned char)p;
             } else {
-                uint32_t wk[6];
+                if ((k & 3) == 0) {
+                    p4 = 0u;
 #pragma unroll
-                for (int j = 0; j < 6; ++j) wk[j] = __shfl_sync(kFull, xw[j], k);
-                p = lane_pattern(wk, lane);
+                    for (int j = 0; j < 6; ++j) p4 |= ((((xw[j] >> k) & 0xfu) * 0x00204081u) & 0x01010101u) << j;
+                }
+                p = (p4 >> (8 * (k & 3))) & 63u;
             }
             const float dyv = dy_next;
             if (k + 1 < kn && f + 32 < a.F) dy_next = __ldg(dyrow + f + 32);
