@@ -170,8 +170,8 @@ class TrainingWorkload:
         self.opt.update()
 
     # our kernels per step: per layer clamp, table conversion, statistics forward, finalize, normalise; the loss; per layer the
-    # backward statistics, finalize, table conversion, the backward kernel, the table-gradient kernel; Adam
-    LAUNCHES_PER_STEP = TRAIN_LAYERS * 5 + 1 + TRAIN_LAYERS * 5 + 1
+    # backward statistics, finalize, the clear of dx, table conversion, the backward kernel, the table-gradient kernel; Adam
+    LAUNCHES_PER_STEP = TRAIN_LAYERS * 5 + 1 + TRAIN_LAYERS * 6 + 1
 
     def allreduce_bytes(self):
         return TRAIN_LAYERS * (TRAIN_NODES * 64 * 4 + 2 * TRAIN_NODES * 2 * 8) if self.world > 1 else 0

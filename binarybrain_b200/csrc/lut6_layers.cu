@@ -1106,12 +1106,37 @@ static int launch_backward_pipe(BwdArgs a, bool bn, int I, void *tmp, size_t tmp
     return launch_status();
 }
 
+// Zero fill with 128-bit stores from a grid sized to the GPU.  A large cudaMemsetAsync ran at about half of the copy bandwidth
+// (8 GiB of dx in 2.7 ms); the clear is 6 % of a training step, so it gets a kernel.
+__global__ void __launch_bounds__(256)
+k_zero_fill(float4 *__restrict__ p, size_t n)
+{
+    const float4 z = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) p[i] = z;
+}
+
+static int zero_async(void *ptr, size_t bytes, cudaStream_t st)
+{
+    if (bytes >= ((size_t)1 << 20) && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
+        const size_t n = bytes / 16;
+        k_zero_fill<<<(unsigned)(8 * device_info().sm_count), 256, 0, st>>>(static_cast<float4 *>(ptr), n);
+        BB200_CUDA(cudaPeekAtLastError());
+        if (bytes % 16) BB200_CUDA(cudaMemsetAsync(static_cast<unsigned char *>(ptr) + n * 16, 0, bytes % 16, st));
+        return BBCU_OK;
+    }
+    BB200_CUDA(cudaMemsetAsync(ptr, 0, bytes, st));
+    return BBCU_OK;
+}
+
 template <bool XBIT>
 static int backward_common(BwdArgs a, bool bn, long long total_frames, float *dmean_out, float *dvar_out, const double *ext_sums,
                            int I, cudaStream_t st, void *tmp = nullptr, size_t tmp_bytes = 0)
 {
     // dx starts from zero (the reference's CPU path: dx_buf.FillZero(), DifferentiableLutN.h:1159)
-    if (I > 0 && a.dxs > 0) BB200_CUDA(cudaMemsetAsync(a.dx, 0, sizeof(float) * (size_t)I * a.dxs, st));
+    if (I > 0 && a.dxs > 0) {
+        const int rc = zero_async(a.dx, sizeof(float) * (size_t)I * a.dxs, st);
+        if (rc) return rc;
+    }
     if (a.O == 0 || a.F == 0) return BBCU_OK;
     if ((XBIT || a.binary) && ext_sums == nullptr && a.dys == a.dxs && total_frames == a.F) {
         // two-valued inputs (bit frames, or fp32 frames in binary mode): everything factors through the 6-bit input pattern of a
