@@ -17,7 +17,8 @@ with CUDA events around every one of its launches inside the timed steps.
 Sub-objects: `binary_lut6` (BinaryLut6 bit-packed inference forward, 16384 -> 16384 nodes, 2^20 frames per GPU, with its own
 roofline, host-buffer e2e and CPU baseline), `fp32` (StochasticLut6 / DifferentiableLut6 forward and backward on one 65536 -> 65536
 x 4096-frame layer, each against the roofline that bounds it), `train_binary` (the same six layers in the reference's binary
-mode, 4096 frames per GPU), `cnn` (the LUT-CNN step) and `operators` (every other operator of the path).
+mode, 4096 frames per GPU), `train_cpp` (one GPU: the headline's six layers, forward + backward + Adam, through the C++ host
+classes), `cnn` (the LUT-CNN step through the C++ host classes) and `operators` (every other operator of the path).
 
 `--impl reference` times the reference's own CPU implementation (oracle/_ref, the unmodified BinaryBrain headers, OpenMP on all
 host cores) on a bounded sample of the headline workload.
