@@ -23,6 +23,7 @@ enum Phase {
     PH_PLAIN = 0,   // y = clip(raw, 0, 1)           (bit out: raw > 0.5)
     PH_STATS = 1,   // per-node sum(raw), sum(raw^2) into fp64 sums; fp32 out: raw stored for the normalise pass
     PH_NORM  = 2,   // y = act((raw - mean) * rstd * gamma + beta)
+    PH_BWD   = 3,   // pipelined kernel only: the two batch-norm sums of the backward pass from a re-evaluated raw value and dy; no output
 };
 
 struct FwdArgs {
@@ -38,6 +39,8 @@ struct FwdArgs {
     int O, F, T;
     long long xs, ys;       // row strides in elements (floats / words)
     int lut_binarize, binary, stat_is_var, groups;
+    const float *dy;        // PH_BWD: the output gradient, rows of dys floats
+    long long dys;
     const float4 *coef;     // pipelined kernel only: per-node tables already in packed-operand form, or nullptr
     int no_scratch;         // launcher: do not take the coefficient table from the stream's scratch (which may allocate)
 };
@@ -321,7 +324,7 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles)
 
     // per-node batch-norm constants travel one item ahead of their use
     float mean_n = 0.0f, scale_n = 0.0f;
-    if (PHASE == PH_NORM && p0.tile < n_tiles) {
+    if ((PHASE == PH_NORM || PHASE == PH_BWD) && p0.tile < n_tiles) {
         const int n0 = min(p0.group * kWarpsPerCta + warp, a.O - 1);
         mean_n = a.mean[n0];
         scale_n = a.rstd[n0];
@@ -338,7 +341,7 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles)
         float mean = mean_n, scale = scale_n;
         if (PHASE == PH_NORM && a.stat_is_var) scale = 1.0f / sqrtf(scale);        // DifferentiableLutN.h:866-868
         const bool have_next = p1.tile < n_tiles;
-        if (PHASE == PH_NORM && have_next) {
+        if ((PHASE == PH_NORM || PHASE == PH_BWD) && have_next) {
             const int n1 = min(p1.group * kWarpsPerCta + warp, a.O - 1);
             mean_n = a.mean[n1];
             scale_n = a.rstd[n1];
@@ -359,7 +362,9 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles)
         }
         double s1 = 0.0, s2 = 0.0;
         const float *xs0 = reinterpret_cast<const float *>(stage);
-        float *yrow = a.y + (size_t)node * a.ys + f0 + 4 * lane;
+        float *yrow = PHASE == PH_BWD ? nullptr : a.y + (size_t)node * a.ys + f0 + 4 * lane;
+        const float *dyrow = PHASE == PH_BWD ? a.dy + (size_t)node * a.dys + f0 + 4 * lane : nullptr;
+        const float rstd2 = scale * scale;                 // PH_BWD
         // One walk of the tree carries NP frame pairs per lane.  A lane owns four consecutive frames of every 128 (frames 128h + 4 lane
         // + 0..3, h < NP/2; pairs (0, 1) and (2, 3)), so its inputs come out of shared memory with one 128-bit load per row and half and
         // its outputs leave with one 128-bit store per half: 4 pairs when the item is 256 frames wide, 2 pairs for a 128-frame item.
@@ -367,6 +372,20 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles)
         auto walk = [&](auto np_tag) {
             constexpr int NP = decltype(np_tag)::value;
             f32x2 up[6][NP], yp[NP];
+            float g4[NP / 2][4];                                   // PH_BWD: dy of the lane's frames, fetched ahead of the tree
+            if (PHASE == PH_BWD) {
+#pragma unroll
+                for (int h = 0; h < NP / 2; ++h) {
+                    const int fl = 128 * h + 4 * lane;
+                    if (fl + 3 < nf) {
+                        const float4 q = __ldg(reinterpret_cast<const float4 *>(dyrow + 128 * h));
+                        g4[h][0] = q.x; g4[h][1] = q.y; g4[h][2] = q.z; g4[h][3] = q.w;
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) g4[h][i] = fl + i < nf ? __ldg(dyrow + 128 * h + i) : 0.0f;
+                    }
+                }
+            }
 #pragma unroll
             for (int j = 0; j < 6; ++j) {
 #pragma unroll
@@ -397,6 +416,15 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles)
                 for (int i = 0; i < 4; ++i) {
                     if (PHASE == PH_STATS) {
                         if (store && fl + i < nf) { s1 += (double)v[i]; s2 += (double)v[i] * (double)v[i]; }
+                    } else if (PHASE == PH_BWD) {
+                        if (store && fl + i < nf) {                // DifferentiableLutN.h:1190-1215, as k_lut6_backward_stats
+                            const float tanh_x = ((v[i] - mean) * scale) * a.gamma + a.beta;
+                            float g = g4[h][i];
+                            if (tanh_x <= 0.0f || tanh_x >= 1.0f) g = 0.0f;
+                            const float dxn = a.gamma * g;
+                            s1 -= (double)(dxn * (v[i] - mean) * rstd2);
+                            s2 -= (double)(dxn * scale);
+                        }
                     } else if (PHASE == PH_NORM) {
                         v[i] = (v[i] - mean) * scale;
                         v[i] = v[i] * a.gamma + a.beta;
@@ -405,7 +433,7 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles)
                         v[i] = __saturatef(v[i]);
                     }
                 }
-                if (store) {
+                if (store && PHASE != PH_BWD) {
                     if (fl + 3 < nf) {
                         *reinterpret_cast<float4 *>(yrow + 128 * h) = make_float4(v[0], v[1], v[2], v[3]);
                     } else {
@@ -418,7 +446,7 @@ k_lut6_forward_pipe(const FwdArgs a, int n_tiles)
         };
         if (kFpMaxItemFrames > kFramesPerIter && nf > kFramesPerIter) walk(std::integral_constant<int, kFpMaxItemFrames / 64>());
         else                                                          walk(std::integral_constant<int, 2>());
-        if (PHASE == PH_STATS && store) {
+        if ((PHASE == PH_STATS || PHASE == PH_BWD) && store) {
             s1 = warp_sum(s1);
             s2 = warp_sum(s2);
             if (lane == 0) {
@@ -1046,6 +1074,40 @@ static int launch_forward(FwdArgs a, int max_tile, cudaStream_t st)
     return launch_status();
 }
 
+// The statistics half of the fp32 backward (the two batch-norm sums from a re-evaluated LUT value and dy) through the pipelined
+// forward kernel, which evaluates the tree at nearly twice the rate of k_lut6_backward_stats.  Returns false, having launched
+// nothing, when the rows are not 16-byte aligned or the shared-memory opt-in is refused; *rc is the launch status otherwise.
+// b.sums must be zero on entry.
+static bool backward_stats_pipe(const BwdArgs &b, cudaStream_t st, int *rc, void *tmp = nullptr, size_t tmp_bytes = 0)
+{
+    const bool aligned = ((reinterpret_cast<uintptr_t>(b.x) | reinterpret_cast<uintptr_t>(b.W) | reinterpret_cast<uintptr_t>(b.dy)) & 15) == 0 &&
+                         (b.xs % 4) == 0 && (b.dys % 4) == 0;
+    auto kern = b.binary ? k_lut6_forward_pipe<PH_BWD, true> : k_lut6_forward_pipe<PH_BWD, false>;
+    if (!aligned || !allow_big_smem(kern, kFpSmem)) return false;
+    FwdArgs a = {};
+    a.x = b.x; a.idx = b.idx; a.W = b.W; a.mean = b.mean; a.rstd = b.rstd; a.sums = b.sums; a.dy = b.dy; a.dys = b.dys;
+    a.gamma = b.gamma; a.beta = b.beta; a.bias = b.bias;
+    a.O = b.O; a.F = b.F; a.xs = b.xs; a.ys = b.xs; a.lut_binarize = b.lut_binarize; a.binary = b.binary;
+    a.groups = (a.O + kWarpsPerCta - 1) / kWarpsPerCta;
+    a.T = a.F > kFramesPerIter ? kFpMaxItemFrames : kFramesPerIter;
+    const long long n_items = (long long)((a.F + a.T - 1) / a.T) * a.groups;
+    if (n_items >= (1LL << 31) - 4096) return false;
+    long long grid = (long long)kFpCtas * device_info().sm_count;
+    if (grid > n_items) grid = n_items;
+    // converted tables: the caller's scratch when it is large enough (the backward proper reuses it afterwards, in stream order),
+    // else slot 1 of the stream's scratch; without either the kernel converts the raw tables itself
+    const size_t need = (size_t)a.O * kFpTabSlotBytes;
+    float4 *coef = (tmp != nullptr && tmp_bytes >= need && (reinterpret_cast<uintptr_t>(tmp) & 15) == 0)
+                       ? static_cast<float4 *>(tmp) : static_cast<float4 *>(stream_scratch(st, need, 1));
+    if (coef != nullptr) {
+        k_table_coeffs<<<a.groups, kWarpsPerCta * 32, 0, st>>>(a.W, coef, a.O, a.lut_binarize);
+        a.coef = coef;
+    }
+    kern<<<(unsigned)grid, kWarpsPerCta * 32, kFpSmem, st>>>(a, (a.F + a.T - 1) / a.T);
+    *rc = launch_status();
+    return true;
+}
+
 template <bool XBIT>
 static int forward_plain(const void *x, float *y, uint32_t *ybits, const int *idx, const float *W, int O, int F, long long xs, long long ys,
                          int binary, int lut_binarize, float bias, cudaStream_t st)
@@ -1169,8 +1231,12 @@ static int backward_common(BwdArgs a, bool bn, long long total_frames, float *dm
             BB200_REQUIRE(sums != nullptr, BBCU_ERR_NO_MEMORY);
             BB200_CUDA(cudaMemsetAsync(sums, 0, sizeof(double) * 2 * (size_t)a.O, st));
             a.sums = sums;
-            k_lut6_backward_stats<XBIT><<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(a);
-            BB200_CUDA(cudaPeekAtLastError());
+            int rc = BBCU_OK;
+            if (XBIT || !backward_stats_pipe(a, st, &rc, tmp, tmp_bytes)) {
+                k_lut6_backward_stats<XBIT><<<(unsigned)blocks, kWarpsPerCta * 32, 0, st>>>(a);
+                rc = launch_status();
+            }
+            if (rc) return rc;
             ext_sums = sums;
         }
         k_bn_backward_finalize<<<(a.O + 255) / 256, 256, 0, st>>>(ext_sums, a.mean, a.rstd, dmean_out, dvar_out, a.O, total_frames);
@@ -1515,6 +1581,7 @@ extern "C" int bbcu_fp32_DifferentiableLut6_BackwardStats(const float *x, const 
     a.gamma = gamma; a.beta = beta; a.bias = unbinarize_bias;
     a.O = node_size; a.F = frame_size; a.xs = frame_stride; a.dys = frame_stride; a.lut_binarize = lut_binarize; a.binary = binary_mode;
     a.groups = (a.O + kWarpsPerCta - 1) / kWarpsPerCta;
+    if (backward_stats_pipe(a, st, &rc)) return rc;
     a.T = frame_tile(3LL * a.O, 32, a.groups, a.F, 2048);
     const long long blocks = (long long)((a.F + a.T - 1) / a.T) * a.groups;
     BB200_REQUIRE(blocks < (1LL << 31), BBCU_ERR_TOO_LARGE);
