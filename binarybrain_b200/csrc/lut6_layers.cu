@@ -1041,7 +1041,7 @@ static int launch_forward(FwdArgs a, int max_tile, cudaStream_t st)
     // input count is not part of this ABI: between O (square layer) and 6*O rows are touched
     a.T = frame_tile(3LL * a.O, XBIT ? 1 : 32, a.groups, a.F, max_tile);
     if (!XBIT && !YBIT) {
-        // pipelined path: rows and tables must start on 16-byte boundaries for the bulk copies and the 128-bit stores
+        // pipelined path: rows and tables must start on 16-byte boundaries for the 16-byte copies and the 128-bit stores
         const bool aligned = ((reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.W) | reinterpret_cast<uintptr_t>(a.y)) & 15) == 0 &&
                              (a.xs % 4) == 0 && (a.ys % 4) == 0;
         auto kern = a.binary ? k_lut6_forward_pipe<PHASE, true> : k_lut6_forward_pipe<PHASE, false>;
